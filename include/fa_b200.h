@@ -1,0 +1,210 @@
+/*
+ * fa_b200 — C ABI of the B200 (sm_100a) attention library.
+ *
+ * The reference project (chelokot/flash-attention-rdna3, package fa_rdna3) has no FFI: its Python
+ * launch glue calls Triton kernels directly. Each entry point below replaces one of those launch
+ * sites; the comment on it names the launch it stands for (paths are relative to the reference
+ * repository). The Python package fa_b200 binds these symbols with ctypes and is the only caller
+ * the library needs, but any host language that can pass plain pointers can use it.
+ *
+ * Conventions
+ *  - Every pointer is a device pointer unless stated otherwise. The caller owns every buffer: the
+ *    library allocates nothing (outputs and scratch are passed in, the way the reference allocates
+ *    them with torch.empty before a launch).
+ *  - Strides are in ELEMENTS of the tensor's dtype, one per dimension, as in the reference kernels'
+ *    signatures (e.g. fa_rdna3/kernels/forward.py:30-40).
+ *  - `stream` is a cudaStream_t passed as void*; work is enqueued on it and the call returns without
+ *    synchronising.
+ *  - Return value: 0 on success, a negative FA_ERR_* code otherwise; fa_last_error_string() gives a
+ *    message for the calling thread's last failure. Nothing throws.
+ *  - `status` fields point at one int32 in device memory that a kernel sets non-zero when one of its
+ *    bounded internal waits ran out (the kernel then abandons its tile and exits); may be NULL.
+ */
+#ifndef FA_B200_H_
+#define FA_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FA_B200_ABI_VERSION 1
+
+enum fa_dtype { FA_F16 = 0, FA_BF16 = 1, FA_F32 = 2 };
+
+enum fa_error {
+  FA_OK = 0,
+  FA_ERR_INVALID_ARGUMENT = -1,
+  FA_ERR_UNSUPPORTED = -2,
+  FA_ERR_LAUNCH = -3,
+  FA_ERR_DEVICE = -4
+};
+
+/* Which kernel family served the last fa_fwd / fa_bwd call (diagnostics and tests). */
+enum fa_path { FA_PATH_NONE = 0, FA_PATH_TCGEN05 = 1, FA_PATH_SIMT = 2 };
+
+/*
+ * Dense or packed (varlen) attention problem; shared by forward and backward.
+ *
+ * Dense layout: q (batch, heads_q, seqlen_q, head_dim); k, v (batch, heads_kv, seqlen_k, head_dim);
+ * lse/delta (batch, heads_q, seqlen_q). Stride arrays are ordered (batch, head, seq, dim).
+ * Varlen layout (varlen != 0): q (total_q, heads_q, head_dim), k, v (total_k, heads_kv, head_dim),
+ * lse/delta (heads_q, total_q); stride arrays keep the (batch, head, seq, dim) order with the batch
+ * stride ignored and the `seq` stride being the token stride; `batch` is the number of sequences and
+ * seqlen_q / seqlen_k are max_seqlen_q / max_seqlen_k. cu_seqlens_* hold batch + 1 int32 entries and
+ * are clamped into [0, total] by the kernels (fa_rdna3/kernels/varlen.py:22-27).
+ */
+typedef struct fa_attn_params {
+  int32_t dtype;            /* fa_dtype of q, k, v, out, dout, dq, dk, dv */
+  int32_t varlen;
+  int32_t batch, heads_q, heads_kv, seqlen_q, seqlen_k, head_dim;
+  int32_t total_q, total_k; /* varlen only */
+  const int32_t* cu_seqlens_q;
+  const int32_t* cu_seqlens_k;
+
+  const void* q; int64_t q_strides[4];
+  const void* k; int64_t k_strides[4];
+  const void* v; int64_t v_strides[4];
+  void* out;     int64_t o_strides[4];
+  float* lse;    int64_t lse_strides[3];   /* (batch, head, seq); varlen: (unused, head, token) */
+
+  /* backward only */
+  const void* dout; int64_t do_strides[4];
+  float* delta;     int64_t delta_strides[3];
+  void* dq; int64_t dq_strides[4];
+  void* dk; int64_t dk_strides[4];
+  void* dv; int64_t dv_strides[4];
+
+  /* score modifiers, applied in the reference's order: scale, softcap, bias, ALiBi, mask
+     (fa_rdna3/kernels/_common.py:275-308) */
+  float softmax_scale;
+  float softcap;            /* 0 disables */
+  const void* bias;         /* may be NULL; broadcast dims carry stride 0 */
+  int32_t bias_dtype;       /* fa_dtype of bias */
+  int64_t bias_strides[4];  /* (batch, head, seq_q, seq_k) */
+  const float* alibi_slopes;/* (heads_q,) fp32, may be NULL */
+  int32_t causal;           /* bottom-right aligned */
+  int32_t window_left;      /* -1 = unbounded */
+  int32_t window_right;     /* -1 = unbounded */
+  float dropout_p;          /* dense only */
+  uint64_t dropout_seed;
+
+  int32_t* status;          /* device int32 or NULL */
+  int32_t force_path;       /* 0 = automatic, else an fa_path to force (tests) */
+} fa_attn_params;
+
+/* Split-K decode: q (batch, heads_q, seqlen_q, head_dim), k/v (batch, heads_kv, seqlen_k, head_dim).
+   o_partial (num_splits, batch, heads_q, seqlen_q, head_dim) fp32 contiguous and
+   lse_partial (num_splits, batch, heads_q, seqlen_q) fp32 contiguous are caller-allocated scratch. */
+typedef struct fa_decode_params {
+  int32_t dtype;
+  int32_t batch, heads_q, heads_kv, seqlen_q, seqlen_k, head_dim;
+  const void* q; int64_t q_strides[4];
+  const void* k; int64_t k_strides[4];
+  const void* v; int64_t v_strides[4];
+  void* out;     int64_t o_strides[4];
+  float softmax_scale;
+  int32_t num_splits;
+  float* o_partial;
+  float* lse_partial;
+} fa_decode_params;
+
+/* LSE-weighted merge of `num_splits` partial results for `rows` independent rows.
+   o_partial element (s, r, d) at o_partial[s*o_split_stride + r*o_row_stride + d];
+   lse_partial element (s, r) at lse_partial[s*lse_split_stride + r*lse_row_stride].
+   out row r at out + r*out_row_stride (elements of out_dtype); lse_out (fp32, may be NULL) gets the
+   merged log-sum-exp per row. */
+typedef struct fa_combine_params {
+  int32_t out_dtype;
+  int32_t rows, head_dim, num_splits;
+  const float* o_partial; int64_t o_split_stride, o_row_stride;
+  const float* lse_partial; int64_t lse_split_stride, lse_row_stride;
+  void* out; int64_t out_row_stride;
+  float* lse_out;
+} fa_combine_params;
+
+/* Paged-KV decode: q (batch, heads_q, head_dim); caches (num_blocks, block_size, heads_kv, head_dim);
+   block_table int32 (batch, max_blocks) and context_lens int32 (batch) with arbitrary strides.
+   first_block / block_step restrict the call to logical blocks first_block, first_block + block_step, ...
+   (a KV shard of a multi-GPU decode; 0 and 1 for the whole context).
+   With num_splits == 1 and lse_out == NULL the result goes straight to out; otherwise
+   o_partial (batch, heads_q, num_splits, head_dim) fp32 and lse_partial (batch, heads_q, num_splits) fp32
+   are caller-allocated scratch and the merged result is written to out (and lse_out if not NULL). */
+typedef struct fa_paged_params {
+  int32_t dtype;
+  int32_t batch, heads_q, heads_kv, head_dim;
+  int32_t num_blocks, block_size, max_blocks;
+  const void* q; int64_t q_strides[3];
+  const void* k_cache; int64_t k_strides[4];
+  const void* v_cache; int64_t v_strides[4];
+  const int32_t* block_table; int64_t bt_strides[2];
+  const int32_t* context_lens; int64_t cl_stride;
+  void* out; int64_t o_strides[3];
+  float softmax_scale;
+  int32_t num_splits;
+  int32_t first_block, block_step;
+  float* o_partial;
+  float* lse_partial;
+  float* lse_out;           /* (batch, heads_q) fp32 contiguous or NULL */
+  int32_t out_is_f32;       /* write out as fp32 regardless of dtype (shard partials) */
+} fa_paged_params;
+
+/* FP32 short-sequence attention: q, k, v, out (batch, heads, seqlen <= 32, 128), optional bias. */
+typedef struct fa_tiny_params {
+  int32_t batch, heads, seqlen, head_dim;
+  const float* q; int64_t q_strides[4];
+  const float* k; int64_t k_strides[4];
+  const float* v; int64_t v_strides[4];
+  float* out;     int64_t o_strides[4];
+  const void* bias; int32_t bias_dtype; int64_t bias_strides[4];
+  float softmax_scale;
+} fa_tiny_params;
+
+/* Library / device queries. */
+int32_t fa_abi_version(void);
+/* 0 when `device` is a compute-capability-10.x GPU, else a negative code (replaces the gfx1100 gate,
+   fa_rdna3/_validation.py:22-37). */
+int32_t fa_device_supported(int32_t device);
+const char* fa_last_error_string(void);
+/* fa_path of the calling thread's last fa_fwd / fa_bwd / fa_varlen_* call. */
+int32_t fa_last_path(void);
+
+/* Dense forward: writes out and lse. Replaces the _attention_forward launch,
+   fa_rdna3/interface.py:154-199 (kernel fa_rdna3/kernels/forward.py:28-164). */
+int32_t fa_fwd(const fa_attn_params* p, void* stream);
+
+/* delta = rowsum(out * dout). Replaces the _attention_bwd_preprocess launch,
+   fa_rdna3/interface.py:225-233 (kernel fa_rdna3/kernels/backward.py:18-46); varlen form
+   fa_rdna3/interface.py:530-538. */
+int32_t fa_bwd_delta(const fa_attn_params* p, void* stream);
+
+/* Dense backward: computes delta, then dk/dv and dq. Replaces the three launches of
+   fa_rdna3/interface.py:202-277 (kernels fa_rdna3/kernels/backward.py:56-322). */
+int32_t fa_bwd(const fa_attn_params* p, void* stream);
+
+/* Packed variable-length forward / backward (p->varlen must be 1). Replace
+   fa_rdna3/interface.py:482-511 and :514-580 (kernels fa_rdna3/kernels/varlen.py:42-421). */
+int32_t fa_varlen_fwd(const fa_attn_params* p, void* stream);
+int32_t fa_varlen_bwd(const fa_attn_params* p, void* stream);
+
+/* Split-K decode (partials + merge). Replaces the _attention_split and _attention_combine launches,
+   fa_rdna3/interface.py:457-478 (kernels fa_rdna3/kernels/decode.py:13-125). */
+int32_t fa_decode_splitk(const fa_decode_params* p, void* stream);
+
+/* Stand-alone LSE merge; also merges per-GPU shard partials. Replaces the _attention_combine launch,
+   fa_rdna3/kernels/decode.py:80-125. */
+int32_t fa_combine(const fa_combine_params* p, void* stream);
+
+/* Paged-KV decode. Replaces the _attention_decode_paged (+ combine) launches,
+   fa_rdna3/interface.py:703-727 (kernel fa_rdna3/kernels/paged.py:17-89). */
+int32_t fa_decode_paged(const fa_paged_params* p, void* stream);
+
+/* FP32 short-sequence forward. Replaces the _attention_tiny_forward launch,
+   fa_rdna3/interface.py:84-104 (kernel fa_rdna3/kernels/tiny.py:10-85). */
+int32_t fa_tiny_fwd(const fa_tiny_params* p, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FA_B200_H_ */
