@@ -1,0 +1,167 @@
+// extern "C" entry points of the library: argument checks, choice of kernel family, error strings.
+// Declarations and the reference launch sites they replace are in include/fa_b200.h.
+#include <stdarg.h>
+#include <stdio.h>
+
+#include "fa_common.cuh"
+
+namespace fa {
+
+namespace {
+thread_local char g_error[512] = "";
+thread_local int g_path = FA_PATH_NONE;
+}  // namespace
+
+int set_error(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+void set_path(int path) { g_path = path; }
+
+namespace {
+
+bool is_pow2(int x) { return x > 0 && (x & (x - 1)) == 0; }
+
+int check_attn(const fa_attn_params* p, bool backward, bool want_varlen) {
+  if (p == nullptr) return set_error(FA_ERR_INVALID_ARGUMENT, "params is NULL");
+  if (p->dtype != FA_F16 && p->dtype != FA_BF16 && p->dtype != FA_F32)
+    return set_error(FA_ERR_INVALID_ARGUMENT, "unsupported dtype %d; expected float16, bfloat16, float32", p->dtype);
+  if ((p->varlen != 0) != want_varlen)
+    return set_error(FA_ERR_INVALID_ARGUMENT, "varlen flag does not match the entry point");
+  if (p->batch <= 0 || p->heads_q <= 0 || p->heads_kv <= 0 || p->seqlen_q <= 0 || p->seqlen_k <= 0 || p->head_dim <= 0)
+    return set_error(FA_ERR_INVALID_ARGUMENT, "batch, heads, sequence lengths and head_dim must be positive");
+  if (p->heads_q % p->heads_kv != 0)
+    return set_error(FA_ERR_INVALID_ARGUMENT, "query heads must be a multiple of key/value heads");
+  if (!is_pow2(p->head_dim) || p->head_dim < 16 || p->head_dim > 512)
+    return set_error(FA_ERR_UNSUPPORTED, "head_dim %d not supported; expected a power of two in [16, 512]",
+                     p->head_dim);
+  if (p->q == nullptr || p->k == nullptr || p->v == nullptr || p->out == nullptr || p->lse == nullptr)
+    return set_error(FA_ERR_INVALID_ARGUMENT, "q, k, v, out and lse must not be NULL");
+  if (p->varlen) {
+    if (p->cu_seqlens_q == nullptr || p->cu_seqlens_k == nullptr || p->total_q <= 0 || p->total_k <= 0)
+      return set_error(FA_ERR_INVALID_ARGUMENT, "varlen needs cu_seqlens_q, cu_seqlens_k and positive totals");
+    if (p->bias != nullptr || p->dropout_p > 0.f)
+      return set_error(FA_ERR_UNSUPPORTED, "additive bias and dropout are dense-only");
+  }
+  if (p->window_left < -1 || p->window_right < -1)
+    return set_error(FA_ERR_INVALID_ARGUMENT, "window values must be integers greater than or equal to -1");
+  if (!(p->softcap >= 0.f)) return set_error(FA_ERR_INVALID_ARGUMENT, "softcap must be nonnegative");
+  if (!(p->dropout_p >= 0.f && p->dropout_p < 1.f))
+    return set_error(FA_ERR_INVALID_ARGUMENT, "dropout_p must satisfy 0 <= dropout_p < 1");
+  if (p->bias != nullptr && p->bias_dtype != p->dtype && p->bias_dtype != FA_F32)
+    return set_error(FA_ERR_INVALID_ARGUMENT, "bias dtype must match query dtype or be float32");
+  if (backward) {
+    if (p->dout == nullptr || p->delta == nullptr || p->dq == nullptr || p->dk == nullptr || p->dv == nullptr)
+      return set_error(FA_ERR_INVALID_ARGUMENT, "dout, delta, dq, dk and dv must not be NULL");
+  }
+  if (p->force_path != FA_PATH_NONE && p->force_path != FA_PATH_TCGEN05 && p->force_path != FA_PATH_SIMT)
+    return set_error(FA_ERR_INVALID_ARGUMENT, "force_path must be 0, FA_PATH_TCGEN05 or FA_PATH_SIMT");
+  return 0;
+}
+
+int run_fwd(const fa_attn_params* p, void* stream, bool varlen) {
+  int rc = check_attn(p, false, varlen);
+  if (rc) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool tc_ok = fwd_tcgen05_supported(*p);
+  if (p->force_path == FA_PATH_TCGEN05 && !tc_ok)
+    return set_error(FA_ERR_UNSUPPORTED, "the tcgen05 forward needs fp16/bf16, head_dim 64 or 128, unit inner "
+                                         "strides and 16-byte aligned rows");
+  if (tc_ok && p->force_path != FA_PATH_SIMT) {
+    set_path(FA_PATH_TCGEN05);
+    return launch_fwd_tcgen05(*p, s);
+  }
+  set_path(FA_PATH_SIMT);
+  return launch_fwd_simt(*p, s);
+}
+
+int run_bwd(const fa_attn_params* p, void* stream, bool varlen) {
+  int rc = check_attn(p, true, varlen);
+  if (rc) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  rc = launch_bwd_delta(*p, s);
+  if (rc) return rc;
+  const bool tc_ok = bwd_tcgen05_supported(*p);
+  if (p->force_path == FA_PATH_TCGEN05 && !tc_ok)
+    return set_error(FA_ERR_UNSUPPORTED, "the tcgen05 backward needs fp16/bf16, head_dim 64 or 128, unit inner "
+                                         "strides and 16-byte aligned rows");
+  if (tc_ok && p->force_path != FA_PATH_SIMT) {
+    set_path(FA_PATH_TCGEN05);
+    return launch_bwd_tcgen05(*p, s);
+  }
+  set_path(FA_PATH_SIMT);
+  return launch_bwd_simt(*p, s);
+}
+
+}  // namespace
+}  // namespace fa
+
+extern "C" {
+
+int32_t fa_abi_version(void) { return FA_B200_ABI_VERSION; }
+
+int32_t fa_device_supported(int32_t device) {
+  cudaDeviceProp prop;
+  cudaError_t e = cudaGetDeviceProperties(&prop, device);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fa::set_error(FA_ERR_DEVICE, "cannot query CUDA device %d: %s", device, cudaGetErrorString(e));
+  }
+  if (prop.major != 10)
+    return fa::set_error(FA_ERR_UNSUPPORTED, "fa_b200 supports compute capability 10.x (B200), got %d.%d", prop.major,
+                         prop.minor);
+  return 0;
+}
+
+const char* fa_last_error_string(void) { return fa::g_error; }
+int32_t fa_last_path(void) { return fa::g_path; }
+
+int32_t fa_fwd(const fa_attn_params* p, void* stream) { return fa::run_fwd(p, stream, false); }
+int32_t fa_varlen_fwd(const fa_attn_params* p, void* stream) { return fa::run_fwd(p, stream, true); }
+int32_t fa_bwd(const fa_attn_params* p, void* stream) { return fa::run_bwd(p, stream, false); }
+int32_t fa_varlen_bwd(const fa_attn_params* p, void* stream) { return fa::run_bwd(p, stream, true); }
+
+int32_t fa_bwd_delta(const fa_attn_params* p, void* stream) {
+  if (p == nullptr || p->out == nullptr || p->dout == nullptr || p->delta == nullptr)
+    return fa::set_error(FA_ERR_INVALID_ARGUMENT, "delta needs out, dout and delta");
+  if (p->batch <= 0 || p->heads_q <= 0 || p->seqlen_q <= 0 || p->head_dim <= 0)
+    return fa::set_error(FA_ERR_INVALID_ARGUMENT, "batch, heads, sequence length and head_dim must be positive");
+  return fa::launch_bwd_delta(*p, static_cast<cudaStream_t>(stream));
+}
+
+int32_t fa_decode_splitk(const fa_decode_params* p, void* stream) {
+  if (p == nullptr) return fa::set_error(FA_ERR_INVALID_ARGUMENT, "params is NULL");
+  if (p->batch <= 0 || p->heads_q <= 0 || p->heads_kv <= 0 || p->seqlen_q <= 0 || p->seqlen_k <= 0)
+    return fa::set_error(FA_ERR_INVALID_ARGUMENT, "batch, heads and sequence lengths must be positive");
+  if (p->q == nullptr || p->k == nullptr || p->v == nullptr || p->out == nullptr)
+    return fa::set_error(FA_ERR_INVALID_ARGUMENT, "q, k, v and out must not be NULL");
+  return fa::launch_decode_splitk(*p, static_cast<cudaStream_t>(stream));
+}
+
+int32_t fa_combine(const fa_combine_params* p, void* stream) {
+  if (p == nullptr || p->o_partial == nullptr || p->lse_partial == nullptr || p->out == nullptr)
+    return fa::set_error(FA_ERR_INVALID_ARGUMENT, "combine needs o_partial, lse_partial and out");
+  return fa::launch_combine(*p, static_cast<cudaStream_t>(stream));
+}
+
+int32_t fa_decode_paged(const fa_paged_params* p, void* stream) {
+  if (p == nullptr) return fa::set_error(FA_ERR_INVALID_ARGUMENT, "params is NULL");
+  if (p->batch <= 0 || p->heads_q <= 0 || p->heads_kv <= 0 || p->num_blocks <= 0 || p->max_blocks <= 0)
+    return fa::set_error(FA_ERR_INVALID_ARGUMENT, "paged batch, heads, blocks and block table width must be positive");
+  if (p->q == nullptr || p->k_cache == nullptr || p->v_cache == nullptr || p->out == nullptr ||
+      p->block_table == nullptr || p->context_lens == nullptr)
+    return fa::set_error(FA_ERR_INVALID_ARGUMENT, "q, caches, block_table, context_lens and out must not be NULL");
+  return fa::launch_decode_paged(*p, static_cast<cudaStream_t>(stream));
+}
+
+int32_t fa_tiny_fwd(const fa_tiny_params* p, void* stream) {
+  if (p == nullptr || p->q == nullptr || p->k == nullptr || p->v == nullptr || p->out == nullptr)
+    return fa::set_error(FA_ERR_INVALID_ARGUMENT, "tiny forward needs q, k, v and out");
+  return fa::launch_tiny(*p, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,213 @@
+// Device-side helpers shared by every attention kernel: dtype conversion, the score-modifier chain
+// (scale -> softcap -> bias -> ALiBi -> mask, in the order of fa_rdna3/kernels/_common.py:275-308),
+// the dropout generator, and error bookkeeping for the C ABI.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+
+#include "../../include/fa_b200.h"
+
+namespace fa {
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+// ---------------------------------------------------------------------------------------------
+// dtype helpers
+// ---------------------------------------------------------------------------------------------
+template <typename T> struct DType;
+template <> struct DType<__half> {
+  static constexpr int kFormat = 0;
+  __device__ static __forceinline__ float to_float(__half x) { return __half2float(x); }
+  __device__ static __forceinline__ __half from_float(float x) { return __float2half_rn(x); }
+  __device__ static __forceinline__ uint32_t pack2(float lo, float hi) {
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+  __device__ static __forceinline__ float2 unpack2(uint32_t u) {
+    return __half22float2(*reinterpret_cast<__half2*>(&u));
+  }
+};
+template <> struct DType<__nv_bfloat16> {
+  static constexpr int kFormat = 1;
+  __device__ static __forceinline__ float to_float(__nv_bfloat16 x) { return __bfloat162float(x); }
+  __device__ static __forceinline__ __nv_bfloat16 from_float(float x) { return __float2bfloat16_rn(x); }
+  __device__ static __forceinline__ uint32_t pack2(float lo, float hi) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+  __device__ static __forceinline__ float2 unpack2(uint32_t u) {
+    return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u));
+  }
+};
+template <> struct DType<float> {
+  static constexpr int kFormat = 2;
+  __device__ static __forceinline__ float to_float(float x) { return x; }
+  __device__ static __forceinline__ float from_float(float x) { return x; }
+};
+
+__device__ __forceinline__ float load_as_float(const void* base, int64_t index, int dtype) {
+  if (dtype == FA_F16) return __half2float(reinterpret_cast<const __half*>(base)[index]);
+  if (dtype == FA_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(base)[index]);
+  return reinterpret_cast<const float*>(base)[index];
+}
+
+__device__ __forceinline__ void store_from_float(void* base, int64_t index, int dtype, float x) {
+  if (dtype == FA_F16) reinterpret_cast<__half*>(base)[index] = __float2half_rn(x);
+  else if (dtype == FA_BF16) reinterpret_cast<__nv_bfloat16*>(base)[index] = __float2bfloat16_rn(x);
+  else reinterpret_cast<float*>(base)[index] = x;
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+constexpr float kNegInf = -INFINITY;
+
+// ---------------------------------------------------------------------------------------------
+// Dropout generator: Philox-4x32-10 keyed by the 64-bit seed, counter = (lo32(offset), hi32(offset), 0, 0),
+// first output word mapped to [0, 1) the way Triton's tl.rand does (the reference draws its mask with
+// tl.rand(seed, offset), fa_rdna3/kernels/_common.py:338-339). An element is kept when u > p.
+// ---------------------------------------------------------------------------------------------
+__host__ __device__ __forceinline__ uint32_t philox_first_word(uint64_t seed, uint64_t offset) {
+  uint32_t c0 = static_cast<uint32_t>(offset), c1 = static_cast<uint32_t>(offset >> 32), c2 = 0, c3 = 0;
+  uint32_t k0 = static_cast<uint32_t>(seed), k1 = static_cast<uint32_t>(seed >> 32);
+  for (int r = 0; r < 10; ++r) {
+    const uint64_t pa = static_cast<uint64_t>(0xD2511F53u) * c0;
+    const uint64_t pb = static_cast<uint64_t>(0xCD9E8D57u) * c2;
+    const uint32_t n0 = static_cast<uint32_t>(pb >> 32) ^ c1 ^ k0;
+    const uint32_t n2 = static_cast<uint32_t>(pa >> 32) ^ c3 ^ k1;
+    c1 = static_cast<uint32_t>(pb);
+    c3 = static_cast<uint32_t>(pa);
+    c0 = n0;
+    c2 = n2;
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+  return c0;
+}
+
+__host__ __device__ __forceinline__ float philox_uniform(uint64_t seed, uint64_t offset) {
+  int32_t x = static_cast<int32_t>(philox_first_word(seed, offset));
+  if (x < 0) x = -x - 1;
+  return static_cast<float>(x) * 4.6566127342e-10f;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Score modifiers for one (batch, head): everything a kernel needs to turn a raw q.k dot product at
+// (query row i, key column j) of one sequence into a log2-domain logit, or -inf when masked.
+// ---------------------------------------------------------------------------------------------
+struct ScoreMods {
+  float scale_log2;      // softmax_scale * log2(e)
+  float cap_log2;        // softcap * log2(e); 0 disables
+  float alibi_slope_log2;// slope * log2(e); 0 disables
+  const void* bias;      // already offset to this (batch, head); nullptr disables
+  int bias_dtype;
+  int64_t bias_stride_m, bias_stride_n;
+  int causal, window_left, window_right;
+  int seqlen_q, seqlen_k;  // of this sequence
+  float dropout_p;         // 0 disables
+  float inv_keep;
+  uint64_t dropout_seed;
+  uint64_t dropout_base;   // (batch * heads + head) * seqlen_q
+
+  __device__ __forceinline__ bool keep(int i, int j) const {
+    const int qpos = i + (seqlen_k - seqlen_q);
+    bool k = j < seqlen_k;
+    if (causal) k = k && (qpos >= j);
+    if (window_left >= 0) k = k && (j >= qpos - window_left);
+    if (window_right >= 0) k = k && (j <= qpos + window_right);
+    return k;
+  }
+
+  // Unmasked logit in the log2 domain. tanh_out receives tanh(s / cap) when softcap is on (the
+  // backward chain factor is 1 - tanh^2), else 0.
+  __device__ __forceinline__ float logit(float raw, int i, int j, float* tanh_out) const {
+    float s = raw * scale_log2;
+    float t = 0.f;
+    if (cap_log2 > 0.f) {
+      t = tanhf(s / cap_log2);
+      s = cap_log2 * t;
+    }
+    if (bias != nullptr) {
+      // rows/columns outside the sequence read nothing (the caller masks them afterwards)
+      if (i < seqlen_q && j < seqlen_k)
+        s += load_as_float(bias, static_cast<int64_t>(i) * bias_stride_m + static_cast<int64_t>(j) * bias_stride_n,
+                           bias_dtype) * kLog2e;
+    }
+    if (alibi_slope_log2 != 0.f) {
+      const int dist = j - i - (seqlen_k - seqlen_q);
+      s -= alibi_slope_log2 * static_cast<float>(dist < 0 ? -dist : dist);
+    }
+    if (tanh_out) *tanh_out = t;
+    return s;
+  }
+
+  __device__ __forceinline__ bool dropout_keep(int i, int j) const {
+    const uint64_t offs = (dropout_base + static_cast<uint64_t>(i)) * static_cast<uint64_t>(seqlen_k) +
+                          static_cast<uint64_t>(j);
+    return philox_uniform(dropout_seed, offs) > dropout_p;
+  }
+};
+
+// First and one-past-last key index any row of query rows [r0, r1] (inclusive, r1 < seqlen_q) may attend.
+__device__ __forceinline__ void key_range_for_rows(const ScoreMods& m, int r0, int r1, int* lo, int* hi) {
+  const int off = m.seqlen_k - m.seqlen_q;
+  int h = m.seqlen_k;
+  if (m.causal) h = min(h, r1 + off + 1);
+  else if (m.window_right >= 0) h = min(h, r1 + off + m.window_right + 1);
+  int l = 0;
+  if (m.window_left >= 0) l = max(0, r0 + off - m.window_left);
+  *lo = l;
+  *hi = max(h, 0);
+}
+
+// First and one-past-last query row any key of [c0, c1] (inclusive, c1 < seqlen_k) may be attended by.
+__device__ __forceinline__ void query_range_for_keys(const ScoreMods& m, int c0, int c1, int* lo, int* hi) {
+  const int off = m.seqlen_k - m.seqlen_q;
+  int l = 0;
+  // keep needs qpos >= j (causal) or j <= qpos + right  =>  i >= j - off [- right]
+  if (m.causal) l = max(l, c0 - off);
+  else if (m.window_right >= 0) l = max(l, c0 - off - m.window_right);
+  int h = m.seqlen_q;
+  // keep needs j >= qpos - left  =>  i <= j - off + left
+  if (m.window_left >= 0) h = min(h, c1 - off + m.window_left + 1);
+  *lo = l;
+  *hi = max(h, 0);
+}
+
+// Sequence bounds of packed batch entry b, clamped into storage (fa_rdna3/kernels/varlen.py:22-27).
+__device__ __forceinline__ void bounded_sequence(const int32_t* cu, int b, int total, int* start, int* len) {
+  int s = cu[b], e = cu[b + 1];
+  s = min(max(s, 0), total);
+  e = min(max(e, 0), total);
+  *start = s;
+  *len = max(e - s, 0);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host-side error bookkeeping (definitions in fa_api.cu)
+// ---------------------------------------------------------------------------------------------
+int set_error(int code, const char* fmt, ...);
+void set_path(int path);
+
+// Per-family launchers implemented in their own translation units; all return 0 or a negative fa_error.
+int launch_fwd_tcgen05(const fa_attn_params& p, cudaStream_t stream);   // fa_fwd_sm100.cu
+bool fwd_tcgen05_supported(const fa_attn_params& p);
+int launch_bwd_tcgen05(const fa_attn_params& p, cudaStream_t stream);   // fa_bwd_sm100.cu (after delta)
+bool bwd_tcgen05_supported(const fa_attn_params& p);
+int launch_fwd_simt(const fa_attn_params& p, cudaStream_t stream);      // fa_simt.cu
+int launch_bwd_simt(const fa_attn_params& p, cudaStream_t stream);      // fa_simt.cu (after delta)
+int launch_bwd_delta(const fa_attn_params& p, cudaStream_t stream);     // fa_simt.cu
+int launch_decode_splitk(const fa_decode_params& p, cudaStream_t stream);  // fa_decode.cu
+int launch_combine(const fa_combine_params& p, cudaStream_t stream);       // fa_decode.cu
+int launch_decode_paged(const fa_paged_params& p, cudaStream_t stream);    // fa_paged.cu
+int launch_tiny(const fa_tiny_params& p, cudaStream_t stream);             // fa_tiny.cu
+
+}  // namespace fa

@@ -1,0 +1,614 @@
+// Split-K decode and the LSE merge. Memory-bound: every K and V byte is read once with 128-bit
+// loads, dot products run on the CUDA cores, and the lanes that share a key reduce with shuffles.
+//
+// One CTA streams one contiguous key slice of one (batch, kv head) for up to R query rows that share
+// that kv head (the rows of the GQA group times seqlen_q), so grouped queries read K/V once.
+// A "worker" is the set of lanes that covers one key row with 16-byte loads; each worker keeps its
+// own running (max, sum, accumulator) and the workers of a CTA are merged through shared memory.
+//
+// Semantics: fa_rdna3/kernels/decode.py:13-125 (partials are normalised, LSE is natural-log and -inf
+// for an empty slice; the merge ignores -inf partials and returns zeros when every slice is empty).
+#include "fa_common.cuh"
+
+namespace fa {
+namespace {
+
+constexpr int kDecodeThreads = 256;
+constexpr int kKeysPerIter = 4;
+
+struct DecodeArgs {
+  fa_decode_params p;
+  int group;
+  int rows_total;      // group * seqlen_q
+  int keys_per_split;
+};
+
+template <typename T>
+__device__ __forceinline__ void unpack8(const uint4& raw, float (&f)[8]) {
+  const float2 a = DType<T>::unpack2(raw.x), b = DType<T>::unpack2(raw.y), c = DType<T>::unpack2(raw.z),
+               d = DType<T>::unpack2(raw.w);
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
+
+__device__ __forceinline__ uint4 ldg_stream(const void* p) {
+  uint4 r;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+               : "l"(p));
+  return r;
+}
+
+// Shared by the dense and paged kernels: merges the per-worker states in shared memory and writes
+// either the final output row (single split, no LSE wanted) or a normalised fp32 partial plus LSE.
+//   sm layout: [worker][row][D + 2] floats: acc[D], m (log2 domain), l.
+template <int D, int R>
+__device__ __forceinline__ void merge_workers_and_store(const float* sm, int workers, int rows_here, int tid,
+                                                        int nthreads, float* opart_rows[R], float* lse_rows[R],
+                                                        void* out_rows[R], int out_dtype, int64_t out_stride_d) {
+  constexpr int kRow = D + 2;
+  for (int idx = tid; idx < rows_here * D; idx += nthreads) {
+    const int r = idx / D, d = idx % D;
+    float M = kNegInf;
+    for (int w = 0; w < workers; ++w) M = fmaxf(M, sm[(w * R + r) * kRow + D]);
+    const float Ms = (M == kNegInf) ? 0.f : M;
+    float num = 0.f, den = 0.f;
+    for (int w = 0; w < workers; ++w) {
+      const float* st = sm + (w * R + r) * kRow;
+      const float sc = exp2f(st[D] - Ms);
+      num += sc * st[d];
+      den += sc * st[D + 1];
+    }
+    const float den_safe = (den == 0.f) ? 1.f : den;
+    const float o = num / den_safe;
+    if (opart_rows[r] != nullptr) opart_rows[r][d] = o;
+    else store_from_float(out_rows[r], (int64_t)d * out_stride_d, out_dtype, o);
+    if (d == 0 && lse_rows[r] != nullptr) lse_rows[r][0] = (den == 0.f) ? kNegInf : (M * kLn2 + logf(den));
+  }
+}
+
+template <typename T, int D, int R>
+__global__ void __launch_bounds__(kDecodeThreads) decode_splitk_kernel(const DecodeArgs a) {
+  constexpr int LPK = (D / 8 < 32) ? D / 8 : 32;  // lanes per key row
+  constexpr int CH = D / (8 * LPK);               // 16-byte chunks per lane per key
+  constexpr int WORKERS = kDecodeThreads / LPK;
+  constexpr int E = CH * 8;                        // elements of the head dimension per lane
+  extern __shared__ float sm[];
+
+  const fa_decode_params& p = a.p;
+  const int tid = threadIdx.x;
+  const int worker = tid / LPK, wl = tid % LPK;
+  const int split = blockIdx.x;
+  const int b = blockIdx.y / p.heads_kv, hk = blockIdx.y % p.heads_kv;
+  const int row0 = blockIdx.z * R;
+  const int rows_here = min(R, a.rows_total - row0);
+
+  const int n_start = min(split * a.keys_per_split, p.seqlen_k);
+  const int n_end = min(n_start + a.keys_per_split, p.seqlen_k);
+
+  const T* kbase = reinterpret_cast<const T*>(p.k) + (int64_t)b * p.k_strides[0] + (int64_t)hk * p.k_strides[1];
+  const T* vbase = reinterpret_cast<const T*>(p.v) + (int64_t)b * p.v_strides[0] + (int64_t)hk * p.v_strides[1];
+
+  // this lane's slice of each query row, pre-scaled into the log2 domain
+  float q[R][E];
+  const float qscale = p.softmax_scale * kLog2e;
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const int row = row0 + r;
+    const int g = row / p.seqlen_q, sq = row % p.seqlen_q;
+    const T* qrow = reinterpret_cast<const T*>(p.q) + (int64_t)b * p.q_strides[0] +
+                    (int64_t)(hk * a.group + g) * p.q_strides[1] + (int64_t)sq * p.q_strides[2];
+#pragma unroll
+    for (int c = 0; c < CH; ++c)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const int d = (c * LPK + wl) * 8 + e;
+        q[r][c * 8 + e] = (r < rows_here) ? DType<T>::to_float(qrow[(int64_t)d * p.q_strides[3]]) * qscale : 0.f;
+      }
+  }
+
+  float m[R], l[R], acc[R][E];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    m[r] = kNegInf;
+    l[r] = 0.f;
+#pragma unroll
+    for (int e = 0; e < E; ++e) acc[r][e] = 0.f;
+  }
+
+  for (int base = n_start; base < n_end; base += WORKERS * kKeysPerIter) {
+    uint4 kraw[kKeysPerIter][CH], vraw[kKeysPerIter][CH];
+#pragma unroll
+    for (int u = 0; u < kKeysPerIter; ++u) {
+      const int key = base + u * WORKERS + worker;
+      const bool valid = key < n_end;
+#pragma unroll
+      for (int c = 0; c < CH; ++c) {
+        const int d = (c * LPK + wl) * 8;
+        kraw[u][c] = valid ? ldg_stream(kbase + (int64_t)key * p.k_strides[2] + d) : make_uint4(0, 0, 0, 0);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kKeysPerIter; ++u) {
+      const int key = base + u * WORKERS + worker;
+      const bool valid = key < n_end;
+#pragma unroll
+      for (int c = 0; c < CH; ++c) {
+        const int d = (c * LPK + wl) * 8;
+        vraw[u][c] = valid ? ldg_stream(vbase + (int64_t)key * p.v_strides[2] + d) : make_uint4(0, 0, 0, 0);
+      }
+    }
+
+    float s[kKeysPerIter][R];
+#pragma unroll
+    for (int u = 0; u < kKeysPerIter; ++u) {
+      float kf[E];
+#pragma unroll
+      for (int c = 0; c < CH; ++c) unpack8<T>(kraw[u][c], *reinterpret_cast<float(*)[8]>(&kf[c * 8]));
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        float d = 0.f;
+#pragma unroll
+        for (int e = 0; e < E; ++e) d += q[r][e] * kf[e];
+        s[u][r] = d;
+      }
+    }
+#pragma unroll
+    for (int o = LPK / 2; o > 0; o >>= 1)
+#pragma unroll
+      for (int u = 0; u < kKeysPerIter; ++u)
+#pragma unroll
+        for (int r = 0; r < R; ++r) s[u][r] += __shfl_xor_sync(0xffffffffu, s[u][r], o);
+
+    float pr[kKeysPerIter][R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      float mt = m[r];
+#pragma unroll
+      for (int u = 0; u < kKeysPerIter; ++u) {
+        const bool valid = (base + u * WORKERS + worker) < n_end;
+        if (!valid) s[u][r] = kNegInf;
+        mt = fmaxf(mt, s[u][r]);
+      }
+      const float ms = (mt == kNegInf) ? 0.f : mt;
+      const float alpha = exp2f(m[r] - ms);
+      float sum = 0.f;
+#pragma unroll
+      for (int u = 0; u < kKeysPerIter; ++u) {
+        pr[u][r] = exp2f(s[u][r] - ms);
+        sum += pr[u][r];
+      }
+      l[r] = l[r] * alpha + sum;
+#pragma unroll
+      for (int e = 0; e < E; ++e) acc[r][e] *= alpha;
+      m[r] = mt;
+    }
+#pragma unroll
+    for (int u = 0; u < kKeysPerIter; ++u) {
+      float vf[E];
+#pragma unroll
+      for (int c = 0; c < CH; ++c) unpack8<T>(vraw[u][c], *reinterpret_cast<float(*)[8]>(&vf[c * 8]));
+#pragma unroll
+      for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int e = 0; e < E; ++e) acc[r][e] += pr[u][r] * vf[e];
+    }
+  }
+
+  // publish worker state
+  constexpr int kRow = D + 2;
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    float* st = sm + (worker * R + r) * kRow;
+#pragma unroll
+    for (int c = 0; c < CH; ++c)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) st[(c * LPK + wl) * 8 + e] = acc[r][c * 8 + e];
+    if (wl == 0) {
+      st[D] = m[r];
+      st[D + 1] = l[r];
+    }
+  }
+  __syncthreads();
+
+  float* opart_rows[R];
+  float* lse_rows[R];
+  void* out_rows[R];
+  const bool direct = (p.num_splits == 1);
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const int row = row0 + ((r < rows_here) ? r : 0);
+    const int g = row / p.seqlen_q, sq = row % p.seqlen_q;
+    const int h = hk * a.group + g;
+    const int64_t flat = (((int64_t)split * p.batch + b) * p.heads_q + h) * p.seqlen_q + sq;
+    opart_rows[r] = direct ? nullptr : p.o_partial + flat * D;
+    lse_rows[r] = direct ? nullptr : p.lse_partial + flat;
+    out_rows[r] = reinterpret_cast<T*>(p.out) + (int64_t)b * p.o_strides[0] + (int64_t)h * p.o_strides[1] +
+                  (int64_t)sq * p.o_strides[2];
+  }
+  merge_workers_and_store<D, R>(sm, WORKERS, rows_here, tid, kDecodeThreads, opart_rows, lse_rows, out_rows,
+                                p.dtype, p.o_strides[3]);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Paged-KV decode (fa_rdna3/kernels/paged.py:17-89): one query row per (batch, query head); keys live
+// in fixed-size physical pages reached through a per-sequence block table. One CTA serves one
+// (split, batch, kv head) and all query heads of that kv head's group, so a page slice is read once
+// per group instead of once per query head. Out-of-range context lengths are clamped and invalid
+// page ids are skipped without being dereferenced (paged.py:37-38, 58-63).
+// ---------------------------------------------------------------------------------------------
+struct PagedArgs {
+  fa_paged_params p;
+  int group;
+};
+
+template <typename T, int D, int R>
+__global__ void __launch_bounds__(kDecodeThreads) decode_paged_kernel(const PagedArgs a) {
+  constexpr int LPK = (D / 8 < 32) ? D / 8 : 32;
+  constexpr int CH = D / (8 * LPK);
+  constexpr int WORKERS = kDecodeThreads / LPK;
+  constexpr int E = CH * 8;
+  extern __shared__ float sm[];
+
+  const fa_paged_params& p = a.p;
+  const int tid = threadIdx.x;
+  const int worker = tid / LPK, wl = tid % LPK;
+  const int split = blockIdx.x;
+  const int b = blockIdx.y / p.heads_kv, hk = blockIdx.y % p.heads_kv;
+  const int row0 = blockIdx.z * R;
+  const int rows_here = min(R, a.group - row0);
+  const int bs = p.block_size;
+
+  int ctx = p.context_lens[(int64_t)b * p.cl_stride];
+  const int64_t cap = (int64_t)p.max_blocks * bs;
+  ctx = (int)min((int64_t)max(ctx, 0), cap);
+  const int nblk = (ctx + bs - 1) / bs;
+  // logical blocks of this call: first_block, first_block + block_step, ...
+  const int nlocal = (nblk > p.first_block) ? (nblk - p.first_block + p.block_step - 1) / p.block_step : 0;
+  const int per = nlocal / p.num_splits, extra = nlocal % p.num_splits;
+  const int blk_begin = split * per + min(split, extra);
+  const int blk_end = blk_begin + per + (split < extra ? 1 : 0);
+  const int n_start = blk_begin * bs, n_end = blk_end * bs;   // local key indices
+
+  float q[R][E];
+  const float qscale = p.softmax_scale * kLog2e;
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const T* qrow = reinterpret_cast<const T*>(p.q) + (int64_t)b * p.q_strides[0] +
+                    (int64_t)(hk * a.group + row0 + r) * p.q_strides[1];
+#pragma unroll
+    for (int c = 0; c < CH; ++c)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const int d = (c * LPK + wl) * 8 + e;
+        q[r][c * 8 + e] = (r < rows_here) ? DType<T>::to_float(qrow[(int64_t)d * p.q_strides[2]]) * qscale : 0.f;
+      }
+  }
+  float m[R], l[R], acc[R][E];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    m[r] = kNegInf;
+    l[r] = 0.f;
+#pragma unroll
+    for (int e = 0; e < E; ++e) acc[r][e] = 0.f;
+  }
+
+  const T* kc = reinterpret_cast<const T*>(p.k_cache) + (int64_t)hk * p.k_strides[2];
+  const T* vc = reinterpret_cast<const T*>(p.v_cache) + (int64_t)hk * p.v_strides[2];
+
+  for (int base = n_start; base < n_end; base += WORKERS * kKeysPerIter) {
+    uint4 kraw[kKeysPerIter][CH], vraw[kKeysPerIter][CH];
+    bool valid[kKeysPerIter];
+    int64_t koff[kKeysPerIter], voff[kKeysPerIter];
+#pragma unroll
+    for (int u = 0; u < kKeysPerIter; ++u) {
+      const int key = base + u * WORKERS + worker;
+      valid[u] = false;
+      koff[u] = voff[u] = 0;
+      if (key < n_end) {
+        const int lb = p.first_block + (key / bs) * p.block_step;
+        const int pos = lb * bs + key % bs;
+        const int phys = p.block_table[(int64_t)b * p.bt_strides[0] + (int64_t)lb * p.bt_strides[1]];
+        if (pos < ctx && phys >= 0 && phys < p.num_blocks) {
+          valid[u] = true;
+          koff[u] = (int64_t)phys * p.k_strides[0] + (int64_t)(key % bs) * p.k_strides[1];
+          voff[u] = (int64_t)phys * p.v_strides[0] + (int64_t)(key % bs) * p.v_strides[1];
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kKeysPerIter; ++u)
+#pragma unroll
+      for (int c = 0; c < CH; ++c)
+        kraw[u][c] = valid[u] ? ldg_stream(kc + koff[u] + (c * LPK + wl) * 8) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int u = 0; u < kKeysPerIter; ++u)
+#pragma unroll
+      for (int c = 0; c < CH; ++c)
+        vraw[u][c] = valid[u] ? ldg_stream(vc + voff[u] + (c * LPK + wl) * 8) : make_uint4(0, 0, 0, 0);
+
+    float s[kKeysPerIter][R];
+#pragma unroll
+    for (int u = 0; u < kKeysPerIter; ++u) {
+      float kf[E];
+#pragma unroll
+      for (int c = 0; c < CH; ++c) unpack8<T>(kraw[u][c], *reinterpret_cast<float(*)[8]>(&kf[c * 8]));
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        float d = 0.f;
+#pragma unroll
+        for (int e = 0; e < E; ++e) d += q[r][e] * kf[e];
+        s[u][r] = d;
+      }
+    }
+#pragma unroll
+    for (int o = LPK / 2; o > 0; o >>= 1)
+#pragma unroll
+      for (int u = 0; u < kKeysPerIter; ++u)
+#pragma unroll
+        for (int r = 0; r < R; ++r) s[u][r] += __shfl_xor_sync(0xffffffffu, s[u][r], o);
+
+    float pr[kKeysPerIter][R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      float mt = m[r];
+#pragma unroll
+      for (int u = 0; u < kKeysPerIter; ++u) {
+        if (!valid[u]) s[u][r] = kNegInf;
+        mt = fmaxf(mt, s[u][r]);
+      }
+      const float ms = (mt == kNegInf) ? 0.f : mt;
+      const float alpha = exp2f(m[r] - ms);
+      float sum = 0.f;
+#pragma unroll
+      for (int u = 0; u < kKeysPerIter; ++u) {
+        pr[u][r] = exp2f(s[u][r] - ms);
+        sum += pr[u][r];
+      }
+      l[r] = l[r] * alpha + sum;
+#pragma unroll
+      for (int e = 0; e < E; ++e) acc[r][e] *= alpha;
+      m[r] = mt;
+    }
+#pragma unroll
+    for (int u = 0; u < kKeysPerIter; ++u) {
+      float vf[E];
+#pragma unroll
+      for (int c = 0; c < CH; ++c) unpack8<T>(vraw[u][c], *reinterpret_cast<float(*)[8]>(&vf[c * 8]));
+#pragma unroll
+      for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int e = 0; e < E; ++e) acc[r][e] += pr[u][r] * vf[e];
+    }
+  }
+
+  constexpr int kRow = D + 2;
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    float* st = sm + (worker * R + r) * kRow;
+#pragma unroll
+    for (int c = 0; c < CH; ++c)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) st[(c * LPK + wl) * 8 + e] = acc[r][c * 8 + e];
+    if (wl == 0) {
+      st[D] = m[r];
+      st[D + 1] = l[r];
+    }
+  }
+  __syncthreads();
+
+  float* opart_rows[R];
+  float* lse_rows[R];
+  void* out_rows[R];
+  const bool direct = (p.num_splits == 1);
+  const int out_dtype = p.out_is_f32 ? (int)FA_F32 : p.dtype;
+  const int esz = (out_dtype == FA_F32) ? 4 : 2;
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const int h = hk * a.group + row0 + ((r < rows_here) ? r : 0);
+    const int64_t flat = ((int64_t)b * p.heads_q + h) * p.num_splits + split;
+    opart_rows[r] = direct ? nullptr : p.o_partial + flat * D;
+    lse_rows[r] = direct ? (p.lse_out ? p.lse_out + (int64_t)b * p.heads_q + h : nullptr) : p.lse_partial + flat;
+    out_rows[r] = reinterpret_cast<char*>(p.out) + ((int64_t)b * p.o_strides[0] + (int64_t)h * p.o_strides[1]) * esz;
+  }
+  merge_workers_and_store<D, R>(sm, WORKERS, rows_here, tid, kDecodeThreads, opart_rows, lse_rows, out_rows,
+                                out_dtype, p.o_strides[2]);
+}
+
+// ---------------------------------------------------------------------------------------------
+// LSE merge (fa_rdna3/kernels/decode.py:80-125). One warp per output row.
+// ---------------------------------------------------------------------------------------------
+struct CombineArgs {
+  int rows, D, splits;
+  const float* o_partial; int64_t o_split_stride, o_row_stride;
+  const float* lse_partial; int64_t lse_split_stride, lse_row_stride;
+  void* out; int out_dtype;
+  int n1, n2;                       // row = (i0 * n1 + i1) * n2 + i2
+  int64_t os0, os1, os2, osd;       // element strides of out for (i0, i1, i2, d)
+  float* lse_out;
+};
+
+__global__ void __launch_bounds__(128) combine_kernel(const CombineArgs a) {
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int row = blockIdx.x * 4 + warp;
+  if (row >= a.rows) return;
+  float M = kNegInf;
+  for (int s = lane; s < a.splits; s += 32)
+    M = fmaxf(M, a.lse_partial[(int64_t)s * a.lse_split_stride + (int64_t)row * a.lse_row_stride]);
+  for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+  const float Ms = (M == kNegInf) ? 0.f : M;
+  float den = 0.f;
+  for (int s = 0; s < a.splits; ++s) {
+    const float ls = a.lse_partial[(int64_t)s * a.lse_split_stride + (int64_t)row * a.lse_row_stride];
+    den += (ls == kNegInf) ? 0.f : expf(ls - Ms);
+  }
+  const float den_safe = (den == 0.f) ? 1.f : den;
+  const int i2 = row % a.n2, i1 = (row / a.n2) % a.n1, i0 = row / (a.n2 * a.n1);
+  const int64_t obase = (int64_t)i0 * a.os0 + (int64_t)i1 * a.os1 + (int64_t)i2 * a.os2;
+  for (int d = lane; d < a.D; d += 32) {
+    float num = 0.f;
+    for (int s = 0; s < a.splits; ++s) {
+      const float ls = a.lse_partial[(int64_t)s * a.lse_split_stride + (int64_t)row * a.lse_row_stride];
+      const float w = (ls == kNegInf) ? 0.f : expf(ls - Ms);
+      num += w * a.o_partial[(int64_t)s * a.o_split_stride + (int64_t)row * a.o_row_stride + d];
+    }
+    store_from_float(a.out, obase + (int64_t)d * a.osd, a.out_dtype, num / den_safe);
+  }
+  if (lane == 0 && a.lse_out != nullptr) a.lse_out[row] = (den == 0.f) ? kNegInf : (Ms + logf(den));
+}
+
+int check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "%s launch failed: %s", what, cudaGetErrorString(e));
+  return 0;
+}
+
+template <typename T, int D, int R>
+int launch_split_typed(const DecodeArgs& a, cudaStream_t stream) {
+  constexpr int LPK = (D / 8 < 32) ? D / 8 : 32;
+  constexpr int WORKERS = kDecodeThreads / LPK;
+  const size_t smem = sizeof(float) * WORKERS * R * (D + 2);
+  auto kern = decode_splitk_kernel<T, D, R>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "decode smem opt-in failed: %s", cudaGetErrorString(e));
+  }
+  dim3 grid(a.p.num_splits, a.p.batch * a.p.heads_kv, (a.rows_total + R - 1) / R);
+  kern<<<grid, kDecodeThreads, smem, stream>>>(a);
+  return check_launch("split-K decode");
+}
+
+template <typename T, int D>
+int launch_split_rows(const DecodeArgs& a, cudaStream_t stream) {
+  if (a.rows_total == 1) return launch_split_typed<T, D, 1>(a, stream);
+  if (a.rows_total == 2) return launch_split_typed<T, D, 2>(a, stream);
+  if (D >= 256) return launch_split_typed<T, D, 2>(a, stream);
+  return launch_split_typed<T, D, 4>(a, stream);
+}
+
+template <typename T>
+int launch_split_dim(const DecodeArgs& a, cudaStream_t stream) {
+  switch (a.p.head_dim) {
+    case 16: return launch_split_rows<T, 16>(a, stream);
+    case 32: return launch_split_rows<T, 32>(a, stream);
+    case 64: return launch_split_rows<T, 64>(a, stream);
+    case 128: return launch_split_rows<T, 128>(a, stream);
+    case 256: return launch_split_rows<T, 256>(a, stream);
+    case 512: return launch_split_rows<T, 512>(a, stream);
+  }
+  return set_error(FA_ERR_UNSUPPORTED, "decode head_dim %d is not a supported power of two", a.p.head_dim);
+}
+
+template <typename T, int D, int R>
+int launch_paged_typed(const PagedArgs& a, cudaStream_t stream) {
+  constexpr int LPK = (D / 8 < 32) ? D / 8 : 32;
+  constexpr int WORKERS = kDecodeThreads / LPK;
+  const size_t smem = sizeof(float) * WORKERS * R * (D + 2);
+  auto kern = decode_paged_kernel<T, D, R>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "paged smem opt-in failed: %s", cudaGetErrorString(e));
+  }
+  dim3 grid(a.p.num_splits, a.p.batch * a.p.heads_kv, (a.group + R - 1) / R);
+  kern<<<grid, kDecodeThreads, smem, stream>>>(a);
+  return check_launch("paged decode");
+}
+
+template <typename T, int D>
+int launch_paged_rows(const PagedArgs& a, cudaStream_t stream) {
+  if (a.group == 1) return launch_paged_typed<T, D, 1>(a, stream);
+  if (a.group == 2) return launch_paged_typed<T, D, 2>(a, stream);
+  if (D >= 256) return launch_paged_typed<T, D, 2>(a, stream);
+  return launch_paged_typed<T, D, 4>(a, stream);
+}
+
+template <typename T>
+int launch_paged_dim(const PagedArgs& a, cudaStream_t stream) {
+  switch (a.p.head_dim) {
+    case 16: return launch_paged_rows<T, 16>(a, stream);
+    case 32: return launch_paged_rows<T, 32>(a, stream);
+    case 64: return launch_paged_rows<T, 64>(a, stream);
+    case 128: return launch_paged_rows<T, 128>(a, stream);
+    case 256: return launch_paged_rows<T, 256>(a, stream);
+    case 512: return launch_paged_rows<T, 512>(a, stream);
+  }
+  return set_error(FA_ERR_UNSUPPORTED, "paged head_dim %d is not a supported power of two", a.p.head_dim);
+}
+
+}  // namespace
+
+int launch_combine_internal(int rows, int D, int splits, const float* o_partial, int64_t o_split_stride,
+                            int64_t o_row_stride, const float* lse_partial, int64_t lse_split_stride,
+                            int64_t lse_row_stride, void* out, int out_dtype, int n1, int n2, int64_t os0,
+                            int64_t os1, int64_t os2, int64_t osd, float* lse_out, cudaStream_t stream) {
+  CombineArgs a{rows, D, splits, o_partial, o_split_stride, o_row_stride, lse_partial, lse_split_stride,
+                lse_row_stride, out, out_dtype, n1, n2, os0, os1, os2, osd, lse_out};
+  combine_kernel<<<(rows + 3) / 4, 128, 0, stream>>>(a);
+  return check_launch("combine");
+}
+
+int launch_combine(const fa_combine_params& p, cudaStream_t stream) {
+  if (p.rows <= 0 || p.head_dim <= 0 || p.num_splits <= 0)
+    return set_error(FA_ERR_INVALID_ARGUMENT, "combine: rows, head_dim and num_splits must be positive");
+  return launch_combine_internal(p.rows, p.head_dim, p.num_splits, p.o_partial, p.o_split_stride, p.o_row_stride,
+                                 p.lse_partial, p.lse_split_stride, p.lse_row_stride, p.out, p.out_dtype, 1, p.rows,
+                                 0, 0, p.out_row_stride, 1, p.lse_out, stream);
+}
+
+int launch_decode_splitk(const fa_decode_params& p, cudaStream_t stream) {
+  if (p.dtype != FA_F16 && p.dtype != FA_BF16)
+    return set_error(FA_ERR_UNSUPPORTED, "decode supports float16 and bfloat16 only");
+  if (p.heads_kv <= 0 || p.heads_q % p.heads_kv != 0)
+    return set_error(FA_ERR_INVALID_ARGUMENT, "query heads must be a multiple of key/value heads");
+  if (p.num_splits < 1) return set_error(FA_ERR_INVALID_ARGUMENT, "num_splits must be at least 1");
+  if (p.k_strides[3] != 1 || p.v_strides[3] != 1 || p.k_strides[2] % 8 || p.v_strides[2] % 8 ||
+      p.k_strides[1] % 8 || p.v_strides[1] % 8 || p.k_strides[0] % 8 || p.v_strides[0] % 8 ||
+      (reinterpret_cast<uintptr_t>(p.k) & 15) || (reinterpret_cast<uintptr_t>(p.v) & 15))
+    return set_error(FA_ERR_UNSUPPORTED, "decode needs K/V with unit inner stride and 16-byte aligned rows");
+  if (p.num_splits > 1 && (p.o_partial == nullptr || p.lse_partial == nullptr))
+    return set_error(FA_ERR_INVALID_ARGUMENT, "decode with several splits needs partial buffers");
+  DecodeArgs a;
+  a.p = p;
+  a.group = p.heads_q / p.heads_kv;
+  a.rows_total = a.group * p.seqlen_q;
+  const int blocks64 = (p.seqlen_k + 63) / 64;
+  a.keys_per_split = ((blocks64 + p.num_splits - 1) / p.num_splits) * 64;
+  int rc = (p.dtype == FA_F16) ? launch_split_dim<__half>(a, stream) : launch_split_dim<__nv_bfloat16>(a, stream);
+  if (rc) return rc;
+  if (p.num_splits > 1) {
+    const int rows = p.batch * p.heads_q * p.seqlen_q;
+    rc = launch_combine_internal(rows, p.head_dim, p.num_splits, p.o_partial, (int64_t)rows * p.head_dim, p.head_dim,
+                                 p.lse_partial, rows, 1, p.out, p.dtype, p.heads_q, p.seqlen_q, p.o_strides[0],
+                                 p.o_strides[1], p.o_strides[2], p.o_strides[3], nullptr, stream);
+  }
+  return rc;
+}
+
+int launch_decode_paged(const fa_paged_params& p, cudaStream_t stream) {
+  if (p.dtype != FA_F16 && p.dtype != FA_BF16)
+    return set_error(FA_ERR_UNSUPPORTED, "paged decode supports float16 and bfloat16 only");
+  if (p.heads_kv <= 0 || p.heads_q % p.heads_kv != 0)
+    return set_error(FA_ERR_INVALID_ARGUMENT, "query heads must be a multiple of cache heads");
+  if (p.num_splits < 1 || p.block_size < 1 || p.block_step < 1 || p.first_block < 0)
+    return set_error(FA_ERR_INVALID_ARGUMENT, "paged decode: bad num_splits / block_size / block range");
+  if (p.k_strides[3] != 1 || p.v_strides[3] != 1 || p.k_strides[0] % 8 || p.k_strides[1] % 8 || p.k_strides[2] % 8 ||
+      p.v_strides[0] % 8 || p.v_strides[1] % 8 || p.v_strides[2] % 8 ||
+      (reinterpret_cast<uintptr_t>(p.k_cache) & 15) || (reinterpret_cast<uintptr_t>(p.v_cache) & 15))
+    return set_error(FA_ERR_UNSUPPORTED, "paged decode needs caches with unit inner stride and 16-byte aligned rows");
+  if (p.num_splits > 1 && (p.o_partial == nullptr || p.lse_partial == nullptr))
+    return set_error(FA_ERR_INVALID_ARGUMENT, "paged decode with several splits needs partial buffers");
+  PagedArgs a;
+  a.p = p;
+  a.group = p.heads_q / p.heads_kv;
+  int rc = (p.dtype == FA_F16) ? launch_paged_dim<__half>(a, stream) : launch_paged_dim<__nv_bfloat16>(a, stream);
+  if (rc) return rc;
+  if (p.num_splits > 1) {
+    const int rows = p.batch * p.heads_q;
+    rc = launch_combine_internal(rows, p.head_dim, p.num_splits, p.o_partial, p.head_dim,
+                                 (int64_t)p.num_splits * p.head_dim, p.lse_partial, 1, p.num_splits, p.out,
+                                 p.out_is_f32 ? (int)FA_F32 : p.dtype, p.heads_q, 1, p.o_strides[0], p.o_strides[1], 0,
+                                 p.o_strides[2], p.lse_out, stream);
+  }
+  return rc;
+}
+
+}  // namespace fa

@@ -1,0 +1,511 @@
+// FlashAttention-2 forward for sm_100a: tcgen05 MMAs with the score and output accumulators in tensor
+// memory, K/V tiles streamed by TMA through a shared-memory ring, warp-specialised roles.
+//
+// One CTA owns 256 query rows (two 128-row tiles) of one (batch, head):
+//   warps 0-3   softmax group for tile 0   (thread = one query row; TMEM lane = row)
+//   warps 4-7   softmax group for tile 1
+//   warp  8     TMA producer (one lane): Q once, then K_j, V_j, K_j+1, V_j+1 ... into the ring
+//   warp  9     MMA issuer (one lane):   S_t = Q_t K_j^T,  O_t += P_t V_j
+// The MMA order is QK0, QK1, then per key tile { PV0, QK0', PV1, QK1' } so that while one group runs
+// its softmax the tensor core works for the other. P (16-bit) overwrites the first 64 columns of its
+// S tile in TMEM and is consumed from there as the A operand of the PV MMA; V is used straight from
+// the TMA-swizzled tile as an MN-major B operand. The running maximum is only refreshed (and O
+// rescaled in TMEM) when it grows by more than 2^8, so the O round trip is rare.
+//
+// TMEM columns: S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [256+D,256+2D).
+//
+// Semantics follow fa_rdna3/kernels/forward.py:28-164 and fa_rdna3/kernels/_common.py:233-345
+// (varlen: fa_rdna3/kernels/varlen.py:42-149): modifier order, bottom-right causal alignment,
+// O = 0 / LSE = -inf for rows with no visible key, natural-log LSE.
+#include "fa_common.cuh"
+#include "fa_sm100.cuh"
+#include "fa_tma_host.h"
+
+namespace fa {
+namespace {
+
+constexpr int kFwdThreads = 320;
+constexpr float kRescaleThreshold = 8.0f;  // log2 units
+
+struct FwdArgs {
+  int varlen, heads_q, heads_kv, seqlen_q, seqlen_k, total_q, total_k;
+  const int32_t* cu_q;
+  const int32_t* cu_k;
+  void* out;
+  int64_t o_sb, o_sh, o_ss;
+  float* lse;
+  int64_t l_sb, l_sh, l_ss;
+  float softmax_scale, softcap;
+  const void* bias;
+  int bias_dtype;
+  int64_t bias_sb, bias_sh, bias_sm, bias_sn;
+  const float* alibi;
+  int causal, wl, wr;
+  float dropout_p;
+  uint64_t seed;
+  int num_pairs;
+  int* status;
+};
+
+__device__ __forceinline__ void report_timeout(int* status, int code) {
+  if (status != nullptr) atomicCAS(status, 0, code);
+}
+
+template <typename T, int D, bool kMods>
+__global__ void __launch_bounds__(kFwdThreads, 1)
+fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+           const __grid_constant__ CUtensorMap map_v, const FwdArgs a) {
+  constexpr int kChunks = D / 64;
+  constexpr int kTileBytes = kChunks * 16384;  // one 128-row operand tile (rows of 128 B, 128-byte swizzle)
+  constexpr int kSlots = (D == 128) ? 4 : 6;
+  constexpr uint32_t kFull = 0xffffffffu;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sKV = smem + 2 * kTileBytes;
+  __shared__ uint64_t q_full[2], kv_full[kSlots], kv_empty[kSlots], s_full[2], p_full[2], o_ready[2];
+  __shared__ uint32_t tmem_base_s;
+
+  const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+  const int pair = a.num_pairs - 1 - blockIdx.x;  // longest (causal) work first
+  const int b = blockIdx.y / a.heads_q, h = blockIdx.y % a.heads_q;
+  const int hk = h / (a.heads_q / a.heads_kv);
+
+  int q_start = 0, k_start = 0, Sq = a.seqlen_q, Sk = a.seqlen_k;
+  if (a.varlen) {
+    bounded_sequence(a.cu_q, b, a.total_q, &q_start, &Sq);
+    bounded_sequence(a.cu_k, b, a.total_k, &k_start, &Sk);
+  }
+  const int row_base = pair * 256;
+  if (row_base >= Sq) return;  // uniform: nothing allocated yet
+  const int tb = a.varlen ? 0 : b;  // batch coordinate of the tensor maps
+
+  ScoreMods mods;
+  mods.scale_log2 = a.softmax_scale * kLog2e;
+  mods.cap_log2 = a.softcap > 0.f ? a.softcap * kLog2e : 0.f;
+  mods.alibi_slope_log2 = a.alibi ? a.alibi[h] * kLog2e : 0.f;
+  mods.bias = nullptr;
+  mods.bias_dtype = a.bias_dtype;
+  mods.bias_stride_m = a.bias_sm;
+  mods.bias_stride_n = a.bias_sn;
+  if (a.bias) {
+    const int esz = a.bias_dtype == FA_F32 ? 4 : 2;
+    mods.bias = reinterpret_cast<const char*>(a.bias) + ((int64_t)b * a.bias_sb + (int64_t)h * a.bias_sh) * esz;
+  }
+  mods.causal = a.causal;
+  mods.window_left = a.wl;
+  mods.window_right = a.wr;
+  mods.seqlen_q = Sq;
+  mods.seqlen_k = Sk;
+  mods.dropout_p = a.dropout_p;
+  mods.inv_keep = a.dropout_p > 0.f ? 1.f / (1.f - a.dropout_p) : 1.f;
+  mods.dropout_seed = a.seed;
+  mods.dropout_base = ((uint64_t)b * (uint64_t)a.heads_q + (uint64_t)h) * (uint64_t)Sq;
+
+  // key-tile range [lo, hi) of each query tile; a tile past the sequence end is inactive
+  int lo[2], hi[2];
+  bool active[2];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int r0 = row_base + t * 128;
+    active[t] = r0 < Sq;
+    lo[t] = hi[t] = 0;
+    if (active[t]) {
+      int klo, khi;
+      key_range_for_rows(mods, r0, min(r0 + 127, Sq - 1), &klo, &khi);
+      lo[t] = klo / 128;
+      hi[t] = (khi + 127) / 128;
+      if (hi[t] <= lo[t]) lo[t] = hi[t] = 0;
+    }
+  }
+  const bool any0 = hi[0] > lo[0], any1 = hi[1] > lo[1];
+  const int jlo = any0 && any1 ? min(lo[0], lo[1]) : (any0 ? lo[0] : lo[1]);
+  const int jhi = any0 && any1 ? max(hi[0], hi[1]) : (any0 ? hi[0] : hi[1]);
+  const bool any_work = any0 || any1;
+
+  if (tid == 0) {
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(&q_full[t], 1);
+      mbar_init(&s_full[t], 1);
+      mbar_init(&p_full[t], 128);
+      mbar_init(&o_ready[t], 1);
+    }
+#pragma unroll
+    for (int s = 0; s < kSlots; ++s) {
+      mbar_init(&kv_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 9) {
+    tmem_alloc(&tmem_base_s, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_base_s;
+
+  if (warp == 8) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0 && any_work) {
+      tma_prefetch_desc(&map_q);
+      tma_prefetch_desc(&map_k);
+      tma_prefetch_desc(&map_v);
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        if (hi[t] > lo[t]) {
+          mbar_arrive_expect_tx(&q_full[t], kTileBytes);
+#pragma unroll
+          for (int c = 0; c < kChunks; ++c)
+            tma_load_4d(sQ + t * kTileBytes + c * 16384, &map_q, &q_full[t], c * 64, q_start + row_base + t * 128, h,
+                        tb);
+        }
+      }
+      int n = 0;
+      bool ok = true;
+      for (int j = jlo; j < jhi && ok; ++j) {
+#pragma unroll
+        for (int which = 0; which < 2; ++which) {
+          const int slot = n % kSlots;
+          const uint32_t par = ((n / kSlots) & 1) ^ 1;
+          if (!mbar_wait(&kv_empty[slot], par)) {
+            report_timeout(a.status, 101);
+            ok = false;
+            break;
+          }
+          mbar_arrive_expect_tx(&kv_full[slot], kTileBytes);
+#pragma unroll
+          for (int c = 0; c < kChunks; ++c)
+            tma_load_4d(sKV + slot * kTileBytes + c * 16384, which == 0 ? &map_k : &map_v, &kv_full[slot], c * 64,
+                        k_start + j * 128, hk, tb);
+          ++n;
+        }
+      }
+    }
+  } else if (warp == 9) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0 && any_work) {
+      constexpr uint32_t idesc_qk = make_idesc(DType<T>::kFormat, 128, 128, 0, 0);
+      constexpr uint32_t idesc_pv = make_idesc(DType<T>::kFormat, 128, D, 0, 1);
+      const uint32_t sq_addr = smem_u32(sQ), skv_addr = smem_u32(sKV);
+      bool ok = true;
+      auto slot_addr = [&](int n) { return skv_addr + (n % kSlots) * kTileBytes; };
+      auto wait_full = [&](int n) {
+        if (!mbar_wait(&kv_full[n % kSlots], (n / kSlots) & 1)) {
+          report_timeout(a.status, 102);
+          ok = false;
+        }
+      };
+      auto in_range = [&](int t, int j) { return j >= lo[t] && j < hi[t]; };
+      auto issue_qk = [&](int t, int n) {
+        const uint32_t qa = sq_addr + t * kTileBytes, ka = slot_addr(n);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk / 4) * 16384 + (kk % 4) * 32;
+          mma_ss(tmem_base + t * 128, make_smem_desc(qa + off, 16, 1024), make_smem_desc(ka + off, 16, 1024),
+                 idesc_qk, kk > 0);
+        }
+        tc_commit(&s_full[t]);
+      };
+      auto issue_pv = [&](int t, int n, bool first) {
+        const uint32_t va = slot_addr(n);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          mma_ts(tmem_base + 256 + t * D, tmem_base + t * 128 + kk * 8, make_smem_desc(va + kk * 2048, 16384, 1024),
+                 idesc_pv, !(first && kk == 0));
+        }
+        tc_commit(&o_ready[t]);
+      };
+
+#pragma unroll
+      for (int t = 0; t < 2; ++t)
+        if (hi[t] > lo[t] && ok && !mbar_wait(&q_full[t], 0)) {
+          report_timeout(a.status, 103);
+          ok = false;
+        }
+      tc_fence_after_sync();
+      if (ok) {
+        wait_full(0);
+        if (ok) {
+          tc_fence_after_sync();
+          if (in_range(0, jlo)) issue_qk(0, 0);
+          if (in_range(1, jlo)) issue_qk(1, 0);
+          tc_commit(&kv_empty[0 % kSlots]);
+        }
+      }
+      for (int j = jlo; j < jhi && ok; ++j) {
+        const int nk = 2 * (j - jlo), nv = nk + 1, nk_next = nk + 2;
+        const bool have_next = j + 1 < jhi;
+        wait_full(nv);
+        if (!ok) break;
+        if (have_next) {
+          wait_full(nk_next);
+          if (!ok) break;
+        }
+        tc_fence_after_sync();
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          if (in_range(t, j)) {
+            if (!mbar_wait(&p_full[t], (j - lo[t]) & 1)) {
+              report_timeout(a.status, 104);
+              ok = false;
+              break;
+            }
+            tc_fence_after_sync();
+            issue_pv(t, nv, j == lo[t]);
+          }
+          if (t == 1) tc_commit(&kv_empty[nv % kSlots]);
+          if (have_next && in_range(t, j + 1)) issue_qk(t, nk_next);
+          if (t == 1 && have_next) tc_commit(&kv_empty[nk_next % kSlots]);
+        }
+      }
+    }
+  } else if (warp < 8) {
+    // ------------------------------------------------------------------ softmax groups
+    const int t = warp / 4, w4 = warp % 4;
+    const int r_tile = w4 * 32 + lane;
+    const int row = row_base + t * 128 + r_tile;
+    const int r0 = row_base + t * 128;
+    const uint32_t lane_addr = static_cast<uint32_t>(w4 * 32) << 16;
+    const uint32_t tS = tmem_base + lane_addr + t * 128;
+    const uint32_t tO = tmem_base + lane_addr + 256 + t * D;
+    const int off = Sk - Sq;
+
+    if (active[t]) {
+      float m_used = kNegInf, l = 0.f;
+      bool ok = true;
+      const int n_tiles = hi[t] - lo[t];
+      for (int it = 0; it < n_tiles; ++it) {
+        const int j = lo[t] + it;
+        bool w_ok = mbar_wait(&s_full[t], it & 1);
+        if (w_ok && it > 0) w_ok = mbar_wait(&o_ready[t], (it - 1) & 1);
+        if (!__all_sync(kFull, w_ok)) {
+          report_timeout(a.status, 105);
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+
+        uint32_t r[128];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
+        tc_wait_ld();
+
+        const int k0 = j * 128;
+        const bool tile_masked = (k0 + 128 > Sk) || (a.causal && (k0 + 127 > r0 + off)) ||
+                                 (a.wl >= 0 && (k0 < r0 + 127 + off - a.wl)) ||
+                                 (!a.causal && a.wr >= 0 && (k0 + 127 > r0 + off + a.wr));
+        float m_tile = kNegInf;
+        if (kMods) {
+#pragma unroll
+          for (int c = 0; c < 128; ++c) {
+            float x = mods.logit(__uint_as_float(r[c]), row, k0 + c, nullptr);
+            if (tile_masked && !mods.keep(row, k0 + c)) x = kNegInf;
+            r[c] = __float_as_uint(x);
+            m_tile = fmaxf(m_tile, x);
+          }
+        } else {
+          if (tile_masked) {
+#pragma unroll
+            for (int c = 0; c < 128; ++c)
+              if (!mods.keep(row, k0 + c)) r[c] = __float_as_uint(kNegInf);
+          }
+#pragma unroll
+          for (int c = 0; c < 128; ++c) m_tile = fmaxf(m_tile, __uint_as_float(r[c]));
+          m_tile *= mods.scale_log2;  // scale > 0 on this path
+        }
+
+        const float m_new = fmaxf(m_used, m_tile);
+        const bool grow = m_new > m_used + kRescaleThreshold;
+        if (__any_sync(kFull, grow)) {
+          const float alpha = (m_new == kNegInf) ? 1.f : exp2f(m_used - m_new);
+          l *= alpha;
+          if (it > 0) {
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+              uint32_t o[32];
+              tmem_ld32(tO + c * 32, o);
+              tc_wait_ld();
+#pragma unroll
+              for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+              tmem_st32(tO + c * 32, o);
+            }
+            tc_wait_st();
+          }
+          m_used = m_new;
+        }
+        const float m_eff = (m_used == kNegInf) ? 0.f : m_used;
+
+        float sum = 0.f;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t pk[32];
+#pragma unroll
+          for (int c = 0; c < 32; ++c) {
+            const int e0 = half * 64 + 2 * c;
+            float p0, p1;
+            if (kMods) {
+              p0 = fast_exp2(__uint_as_float(r[e0]) - m_eff);
+              p1 = fast_exp2(__uint_as_float(r[e0 + 1]) - m_eff);
+            } else {
+              p0 = fast_exp2(fmaf(__uint_as_float(r[e0]), mods.scale_log2, -m_eff));
+              p1 = fast_exp2(fmaf(__uint_as_float(r[e0 + 1]), mods.scale_log2, -m_eff));
+            }
+            sum += p0 + p1;
+            if (kMods && mods.dropout_p > 0.f) {
+              p0 = mods.dropout_keep(row, k0 + e0) ? p0 * mods.inv_keep : 0.f;
+              p1 = mods.dropout_keep(row, k0 + e0 + 1) ? p1 * mods.inv_keep : 0.f;
+            }
+            pk[c] = DType<T>::pack2(p0, p1);
+          }
+          tmem_st32(tS + half * 32, pk);
+        }
+        l += sum;
+        tc_wait_st();
+        tc_fence_before_sync();
+        mbar_arrive(&p_full[t]);
+      }
+
+      // epilogue: O / l -> global, LSE
+      T* orow = reinterpret_cast<T*>(a.out) + (a.varlen ? 0 : (int64_t)b * a.o_sb) + (int64_t)h * a.o_sh +
+                (int64_t)(q_start + row) * a.o_ss;
+      if (n_tiles > 0) {
+        bool w_ok = ok && mbar_wait(&o_ready[t], (n_tiles - 1) & 1);
+        if (!__all_sync(kFull, w_ok)) {
+          if (ok) report_timeout(a.status, 106);
+          ok = false;
+        }
+      }
+      if (ok) {
+        tc_fence_after_sync();
+        const float l_safe = (l == 0.f) ? 1.f : l;
+        const float inv = 1.f / l_safe;
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t o[32];
+          if (n_tiles > 0) {
+            tmem_ld32(tO + c * 32, o);
+            tc_wait_ld();
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) o[e] = 0u;
+          }
+          if (row < Sq) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint4 pkt;
+              pkt.x = DType<T>::pack2(__uint_as_float(o[v * 8 + 0]) * inv, __uint_as_float(o[v * 8 + 1]) * inv);
+              pkt.y = DType<T>::pack2(__uint_as_float(o[v * 8 + 2]) * inv, __uint_as_float(o[v * 8 + 3]) * inv);
+              pkt.z = DType<T>::pack2(__uint_as_float(o[v * 8 + 4]) * inv, __uint_as_float(o[v * 8 + 5]) * inv);
+              pkt.w = DType<T>::pack2(__uint_as_float(o[v * 8 + 6]) * inv, __uint_as_float(o[v * 8 + 7]) * inv);
+              *reinterpret_cast<uint4*>(orow + c * 32 + v * 8) = pkt;
+            }
+          }
+        }
+        if (row < Sq) {
+          float* lrow = a.lse + (a.varlen ? 0 : (int64_t)b * a.l_sb) + (int64_t)h * a.l_sh +
+                        (int64_t)(q_start + row) * a.l_ss;
+          *lrow = (l == 0.f) ? kNegInf : (m_used * kLn2 + logf(l));
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 9) tmem_dealloc(tmem_base, 512);
+}
+
+template <typename T, int D, bool kMods>
+int launch_typed(const fa_attn_params& p, const FwdArgs& a, cudaStream_t stream) {
+  constexpr int kChunks = D / 64;
+  constexpr int kTileBytes = kChunks * 16384;
+  constexpr int kSlots = (D == 128) ? 4 : 6;
+  const int smem = (2 + kSlots) * kTileBytes + 1024;
+  CUtensorMap mq, mk, mv;
+  const int rows_q = p.varlen ? p.total_q : p.seqlen_q;
+  const int rows_k = p.varlen ? p.total_k : p.seqlen_k;
+  const int nb = p.varlen ? 1 : p.batch;
+  int rc = make_tile_map(&mq, p.q, p.dtype, D, rows_q, p.heads_q, nb, p.q_strides[2], p.q_strides[1], p.q_strides[0]);
+  if (rc) return rc;
+  rc = make_tile_map(&mk, p.k, p.dtype, D, rows_k, p.heads_kv, nb, p.k_strides[2], p.k_strides[1], p.k_strides[0]);
+  if (rc) return rc;
+  rc = make_tile_map(&mv, p.v, p.dtype, D, rows_k, p.heads_kv, nb, p.v_strides[2], p.v_strides[1], p.v_strides[0]);
+  if (rc) return rc;
+  auto kern = fwd_kernel<T, D, kMods>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "forward smem opt-in failed: %s", cudaGetErrorString(e));
+  dim3 grid(a.num_pairs, p.batch * p.heads_q);
+  kern<<<grid, kFwdThreads, smem, stream>>>(mq, mk, mv, a);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "forward launch failed: %s", cudaGetErrorString(e));
+  return 0;
+}
+
+}  // namespace
+
+bool fwd_tcgen05_supported(const fa_attn_params& p) {
+  if (p.dtype != FA_F16 && p.dtype != FA_BF16) return false;
+  if (p.head_dim != 64 && p.head_dim != 128) return false;
+  const int64_t nb = p.varlen ? 1 : p.batch;
+  const int64_t sq[3] = {nb, p.heads_q, p.varlen ? p.total_q : p.seqlen_q};
+  const int64_t sk[3] = {nb, p.heads_kv, p.varlen ? p.total_k : p.seqlen_k};
+  if (!tma_operand_ok(p.q, p.q_strides, sq) || !tma_operand_ok(p.k, p.k_strides, sk) ||
+      !tma_operand_ok(p.v, p.v_strides, sk))
+    return false;
+  if (!tma_operand_ok(p.out, p.o_strides, sq)) return false;  // 16-byte vector stores need the same alignment
+  return true;
+}
+
+int launch_fwd_tcgen05(const fa_attn_params& p, cudaStream_t stream) {
+  FwdArgs a;
+  a.varlen = p.varlen;
+  a.heads_q = p.heads_q;
+  a.heads_kv = p.heads_kv;
+  a.seqlen_q = p.seqlen_q;
+  a.seqlen_k = p.seqlen_k;
+  a.total_q = p.total_q;
+  a.total_k = p.total_k;
+  a.cu_q = p.cu_seqlens_q;
+  a.cu_k = p.cu_seqlens_k;
+  a.out = p.out;
+  a.o_sb = p.o_strides[0];
+  a.o_sh = p.o_strides[1];
+  a.o_ss = p.o_strides[2];
+  a.lse = p.lse;
+  a.l_sb = p.lse_strides[0];
+  a.l_sh = p.lse_strides[1];
+  a.l_ss = p.lse_strides[2];
+  a.softmax_scale = p.softmax_scale;
+  a.softcap = p.softcap;
+  a.bias = p.bias;
+  a.bias_dtype = p.bias_dtype;
+  a.bias_sb = p.bias_strides[0];
+  a.bias_sh = p.bias_strides[1];
+  a.bias_sm = p.bias_strides[2];
+  a.bias_sn = p.bias_strides[3];
+  a.alibi = p.alibi_slopes;
+  a.causal = p.causal;
+  a.wl = p.window_left;
+  a.wr = p.window_right;
+  a.dropout_p = p.dropout_p;
+  a.seed = p.dropout_seed;
+  a.num_pairs = (p.seqlen_q + 255) / 256;
+  a.status = p.status;
+  const bool mods = p.softcap > 0.f || p.bias != nullptr || p.alibi_slopes != nullptr || p.dropout_p > 0.f ||
+                    !(p.softmax_scale > 0.f);
+  const bool f16 = p.dtype == FA_F16;
+  if (p.head_dim == 128) {
+    if (f16) return mods ? launch_typed<__half, 128, true>(p, a, stream) : launch_typed<__half, 128, false>(p, a, stream);
+    return mods ? launch_typed<__nv_bfloat16, 128, true>(p, a, stream)
+                : launch_typed<__nv_bfloat16, 128, false>(p, a, stream);
+  }
+  if (f16) return mods ? launch_typed<__half, 64, true>(p, a, stream) : launch_typed<__half, 64, false>(p, a, stream);
+  return mods ? launch_typed<__nv_bfloat16, 64, true>(p, a, stream)
+              : launch_typed<__nv_bfloat16, 64, false>(p, a, stream);
+}
+
+}  // namespace fa

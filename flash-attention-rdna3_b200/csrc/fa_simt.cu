@@ -1,0 +1,371 @@
+// CUDA-core attention kernels that accept everything the public API accepts: fp16 / bf16 / fp32,
+// any head_dim up to 512, arbitrary strides, every score modifier, dense and packed layouts.
+// They serve the shapes the tensor-core kernels do not take (fp32 inputs, head_dim outside {64, 128},
+// non-unit inner strides) and compute in fp32 throughout. One warp owns one query row (forward, dQ)
+// or one key row (dK/dV); the lanes of the warp take 32 keys (or queries) at a time.
+//
+// Semantics follow fa_rdna3/kernels/_common.py:233-508 (inner loops) and
+// fa_rdna3/kernels/forward.py:154-161 (empty rows: O = 0, LSE = -inf).
+#include "fa_common.cuh"
+
+namespace fa {
+namespace {
+
+constexpr int kWarpsPerBlock = 4;
+constexpr int kMaxD = 512;
+constexpr int kMaxDPerLane = kMaxD / 32;
+
+struct SeqView {
+  int b, h, hk;
+  int seqlen_q, seqlen_k;
+  int64_t q_off, k_off, v_off, o_off, do_off, dq_off, dk_off, dv_off;  // element offsets of row 0, this head
+  int64_t lse_off, delta_off;                                        // offset of row 0
+  int64_t lse_row_stride, delta_row_stride;
+};
+
+__device__ __forceinline__ bool make_view(const fa_attn_params& P, int b, int h, SeqView* s) {
+  s->b = b;
+  s->h = h;
+  const int group = P.heads_q / P.heads_kv;
+  s->hk = h / group;
+  int q_start = 0, k_start = 0;
+  if (P.varlen) {
+    bounded_sequence(P.cu_seqlens_q, b, P.total_q, &q_start, &s->seqlen_q);
+    bounded_sequence(P.cu_seqlens_k, b, P.total_k, &k_start, &s->seqlen_k);
+  } else {
+    s->seqlen_q = P.seqlen_q;
+    s->seqlen_k = P.seqlen_k;
+  }
+  const int64_t bq = P.varlen ? 0 : b, tq = q_start, tk = k_start;
+  s->q_off = bq * P.q_strides[0] + (int64_t)h * P.q_strides[1] + tq * P.q_strides[2];
+  s->k_off = bq * P.k_strides[0] + (int64_t)s->hk * P.k_strides[1] + tk * P.k_strides[2];
+  s->v_off = bq * P.v_strides[0] + (int64_t)s->hk * P.v_strides[1] + tk * P.v_strides[2];
+  s->o_off = bq * P.o_strides[0] + (int64_t)h * P.o_strides[1] + tq * P.o_strides[2];
+  s->do_off = bq * P.do_strides[0] + (int64_t)h * P.do_strides[1] + tq * P.do_strides[2];
+  s->dq_off = bq * P.dq_strides[0] + (int64_t)h * P.dq_strides[1] + tq * P.dq_strides[2];
+  s->dk_off = bq * P.dk_strides[0] + (int64_t)s->hk * P.dk_strides[1] + tk * P.dk_strides[2];
+  s->dv_off = bq * P.dv_strides[0] + (int64_t)s->hk * P.dv_strides[1] + tk * P.dv_strides[2];
+  s->lse_off = bq * P.lse_strides[0] + (int64_t)h * P.lse_strides[1] + tq * P.lse_strides[2];
+  s->delta_off = bq * P.delta_strides[0] + (int64_t)h * P.delta_strides[1] + tq * P.delta_strides[2];
+  s->lse_row_stride = P.lse_strides[2];
+  s->delta_row_stride = P.delta_strides[2];
+  return true;
+}
+
+__device__ __forceinline__ ScoreMods make_mods(const fa_attn_params& P, const SeqView& s) {
+  ScoreMods m;
+  m.scale_log2 = P.softmax_scale * kLog2e;
+  m.cap_log2 = P.softcap > 0.f ? P.softcap * kLog2e : 0.f;
+  m.alibi_slope_log2 = P.alibi_slopes ? P.alibi_slopes[s.h] * kLog2e : 0.f;
+  m.bias = nullptr;
+  m.bias_dtype = P.bias_dtype;
+  m.bias_stride_m = P.bias_strides[2];
+  m.bias_stride_n = P.bias_strides[3];
+  if (P.bias) {
+    const int64_t off = (int64_t)s.b * P.bias_strides[0] + (int64_t)s.h * P.bias_strides[1];
+    const int esz = P.bias_dtype == FA_F32 ? 4 : 2;
+    m.bias = reinterpret_cast<const char*>(P.bias) + off * esz;
+  }
+  m.causal = P.causal;
+  m.window_left = P.window_left;
+  m.window_right = P.window_right;
+  m.seqlen_q = s.seqlen_q;
+  m.seqlen_k = s.seqlen_k;
+  m.dropout_p = P.dropout_p;
+  m.inv_keep = P.dropout_p > 0.f ? 1.f / (1.f - P.dropout_p) : 1.f;
+  m.dropout_seed = P.dropout_seed;
+  m.dropout_base = ((uint64_t)s.b * (uint64_t)P.heads_q + (uint64_t)s.h) * (uint64_t)s.seqlen_q;
+  return m;
+}
+
+__device__ __forceinline__ float warp_max(float x) {
+  for (int o = 16; o > 0; o >>= 1) x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, o));
+  return x;
+}
+__device__ __forceinline__ float warp_sum(float x) {
+  for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+  return x;
+}
+
+// Full dot product of a staged fp32 vector with one global row.
+__device__ __forceinline__ float dot_row(const float* vec_s, const void* base, int64_t row_off, int64_t stride_d,
+                                         int D, int dtype) {
+  float acc = 0.f;
+  for (int d = 0; d < D; ++d) acc += vec_s[d] * load_as_float(base, row_off + (int64_t)d * stride_d, dtype);
+  return acc;
+}
+
+// ---------------------------------------------------------------------------------------------
+// delta = rowsum(out * dout)           (fa_rdna3/kernels/backward.py:18-46)
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kWarpsPerBlock * 32) simt_delta_kernel(const fa_attn_params P) {
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int i = blockIdx.x * kWarpsPerBlock + warp;
+  const int b = blockIdx.y / P.heads_q, h = blockIdx.y % P.heads_q;
+  SeqView s;
+  make_view(P, b, h, &s);
+  if (i >= s.seqlen_q) return;
+  float acc = 0.f;
+  for (int d = lane; d < P.head_dim; d += 32) {
+    acc += load_as_float(P.out, s.o_off + (int64_t)i * P.o_strides[2] + (int64_t)d * P.o_strides[3], P.dtype) *
+           load_as_float(P.dout, s.do_off + (int64_t)i * P.do_strides[2] + (int64_t)d * P.do_strides[3], P.dtype);
+  }
+  acc = warp_sum(acc);
+  if (lane == 0) P.delta[s.delta_off + (int64_t)i * s.delta_row_stride] = acc;
+}
+
+// ---------------------------------------------------------------------------------------------
+// forward
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kWarpsPerBlock * 32) simt_fwd_kernel(const fa_attn_params P) {
+  __shared__ float q_s[kWarpsPerBlock][kMaxD];
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int i = blockIdx.x * kWarpsPerBlock + warp;
+  const int b = blockIdx.y / P.heads_q, h = blockIdx.y % P.heads_q;
+  const int D = P.head_dim;
+  SeqView s;
+  make_view(P, b, h, &s);
+  if (i >= s.seqlen_q) return;
+  const ScoreMods mods = make_mods(P, s);
+
+  for (int d = lane; d < D; d += 32)
+    q_s[warp][d] = load_as_float(P.q, s.q_off + (int64_t)i * P.q_strides[2] + (int64_t)d * P.q_strides[3], P.dtype);
+  __syncwarp();
+
+  int lo, hi;
+  key_range_for_rows(mods, i, i, &lo, &hi);
+  float m = kNegInf, l = 0.f;
+  float acc[kMaxDPerLane];
+#pragma unroll
+  for (int r = 0; r < kMaxDPerLane; ++r) acc[r] = 0.f;
+
+  for (int j0 = lo; j0 < hi; j0 += 32) {
+    const int j = j0 + lane;
+    float x = kNegInf;
+    if (j < hi) {
+      const float raw = dot_row(q_s[warp], P.k, s.k_off + (int64_t)j * P.k_strides[2], P.k_strides[3], D, P.dtype);
+      x = mods.logit(raw, i, j, nullptr);
+      if (!mods.keep(i, j)) x = kNegInf;
+    }
+    const float m_new = fmaxf(m, warp_max(x));
+    const float m_safe = (m_new == kNegInf) ? 0.f : m_new;
+    const float alpha = exp2f(m - m_safe);
+    float p = exp2f(x - m_safe);
+    l = l * alpha + warp_sum(p);
+    if (mods.dropout_p > 0.f && j < hi) p = mods.dropout_keep(i, j) ? p * mods.inv_keep : 0.f;
+#pragma unroll
+    for (int r = 0; r < kMaxDPerLane; ++r) acc[r] *= alpha;
+    const int jn = min(32, hi - j0);
+    for (int jj = 0; jj < jn; ++jj) {
+      const float pj = __shfl_sync(0xffffffffu, p, jj);
+      if (pj == 0.f) continue;
+      const int64_t voff = s.v_off + (int64_t)(j0 + jj) * P.v_strides[2];
+#pragma unroll
+      for (int r = 0; r < kMaxDPerLane; ++r) {
+        const int d = lane + 32 * r;
+        if (d < D) acc[r] += pj * load_as_float(P.v, voff + (int64_t)d * P.v_strides[3], P.dtype);
+      }
+    }
+    if (m_new != kNegInf) m = m_new;
+  }
+
+  const float l_safe = (l == 0.f) ? 1.f : l;
+  const float inv = 1.f / l_safe;
+#pragma unroll
+  for (int r = 0; r < kMaxDPerLane; ++r) {
+    const int d = lane + 32 * r;
+    if (d < D)
+      store_from_float(P.out, s.o_off + (int64_t)i * P.o_strides[2] + (int64_t)d * P.o_strides[3], P.dtype,
+                       acc[r] * inv);
+  }
+  if (lane == 0) P.lse[s.lse_off + (int64_t)i * s.lse_row_stride] = m * kLn2 + logf(l_safe);
+}
+
+// Probability and score-gradient factor of one (i, j) pair in the backward pass.
+//   p      = exp2(logit - lse*log2e), 0 when masked or when the row's lse is -inf
+//   p_drop = p with the dropout mask applied (what multiplies dO for dV)
+//   ds     = p * (dp_dropped - delta) * (1 - tanh^2)         (fa_rdna3/kernels/_common.py:385-432)
+struct PairGrad { float p_drop; float ds; };
+
+__device__ __forceinline__ PairGrad pair_grad(const ScoreMods& mods, float raw_qk, float raw_dp, float lse,
+                                              float delta, int i, int j) {
+  PairGrad g{0.f, 0.f};
+  if (!mods.keep(i, j) || lse == kNegInf) return g;
+  float t;
+  const float x = mods.logit(raw_qk, i, j, &t);
+  const float p = exp2f(x - lse * kLog2e);
+  float dp = raw_dp;
+  float p_drop = p;
+  if (mods.dropout_p > 0.f) {
+    const bool kd = mods.dropout_keep(i, j);
+    p_drop = kd ? p * mods.inv_keep : 0.f;
+    dp = kd ? dp * mods.inv_keep : 0.f;
+  }
+  float ds = p * (dp - delta);
+  if (mods.cap_log2 > 0.f) ds *= (1.f - t * t);
+  g.p_drop = p_drop;
+  g.ds = ds;
+  return g;
+}
+
+// ---------------------------------------------------------------------------------------------
+// dQ: one warp per query row                         (fa_rdna3/kernels/backward.py:210-322)
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kWarpsPerBlock * 32) simt_bwd_dq_kernel(const fa_attn_params P) {
+  __shared__ float q_s[kWarpsPerBlock][kMaxD];
+  __shared__ float do_s[kWarpsPerBlock][kMaxD];
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int i = blockIdx.x * kWarpsPerBlock + warp;
+  const int b = blockIdx.y / P.heads_q, h = blockIdx.y % P.heads_q;
+  const int D = P.head_dim;
+  SeqView s;
+  make_view(P, b, h, &s);
+  if (i >= s.seqlen_q) return;
+  const ScoreMods mods = make_mods(P, s);
+  for (int d = lane; d < D; d += 32) {
+    q_s[warp][d] = load_as_float(P.q, s.q_off + (int64_t)i * P.q_strides[2] + (int64_t)d * P.q_strides[3], P.dtype);
+    do_s[warp][d] =
+        load_as_float(P.dout, s.do_off + (int64_t)i * P.do_strides[2] + (int64_t)d * P.do_strides[3], P.dtype);
+  }
+  __syncwarp();
+  const float lse = P.lse[s.lse_off + (int64_t)i * s.lse_row_stride];
+  const float delta = P.delta[s.delta_off + (int64_t)i * s.delta_row_stride];
+
+  int lo, hi;
+  key_range_for_rows(mods, i, i, &lo, &hi);
+  float acc[kMaxDPerLane];
+#pragma unroll
+  for (int r = 0; r < kMaxDPerLane; ++r) acc[r] = 0.f;
+
+  for (int j0 = lo; j0 < hi; j0 += 32) {
+    const int j = j0 + lane;
+    float ds = 0.f;
+    if (j < hi) {
+      const float raw = dot_row(q_s[warp], P.k, s.k_off + (int64_t)j * P.k_strides[2], P.k_strides[3], D, P.dtype);
+      const float dp = dot_row(do_s[warp], P.v, s.v_off + (int64_t)j * P.v_strides[2], P.v_strides[3], D, P.dtype);
+      ds = pair_grad(mods, raw, dp, lse, delta, i, j).ds;
+    }
+    const int jn = min(32, hi - j0);
+    for (int jj = 0; jj < jn; ++jj) {
+      const float dj = __shfl_sync(0xffffffffu, ds, jj);
+      if (dj == 0.f) continue;
+      const int64_t koff = s.k_off + (int64_t)(j0 + jj) * P.k_strides[2];
+#pragma unroll
+      for (int r = 0; r < kMaxDPerLane; ++r) {
+        const int d = lane + 32 * r;
+        if (d < D) acc[r] += dj * load_as_float(P.k, koff + (int64_t)d * P.k_strides[3], P.dtype);
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < kMaxDPerLane; ++r) {
+    const int d = lane + 32 * r;
+    if (d < D)
+      store_from_float(P.dq, s.dq_off + (int64_t)i * P.dq_strides[2] + (int64_t)d * P.dq_strides[3], P.dtype,
+                       acc[r] * P.softmax_scale);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// dK, dV: one warp per key row of one kv head; sums over the query heads of the group in registers,
+// no atomics (fa_rdna3/kernels/backward.py:56-200).
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kWarpsPerBlock * 32) simt_bwd_dkdv_kernel(const fa_attn_params P) {
+  __shared__ float k_s[kWarpsPerBlock][kMaxD];
+  __shared__ float v_s[kWarpsPerBlock][kMaxD];
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int j = blockIdx.x * kWarpsPerBlock + warp;
+  const int b = blockIdx.y / P.heads_kv, hk = blockIdx.y % P.heads_kv;
+  const int D = P.head_dim;
+  const int group = P.heads_q / P.heads_kv;
+  SeqView s;
+  make_view(P, b, hk * group, &s);
+  if (j >= s.seqlen_k) return;
+  for (int d = lane; d < D; d += 32) {
+    k_s[warp][d] = load_as_float(P.k, s.k_off + (int64_t)j * P.k_strides[2] + (int64_t)d * P.k_strides[3], P.dtype);
+    v_s[warp][d] = load_as_float(P.v, s.v_off + (int64_t)j * P.v_strides[2] + (int64_t)d * P.v_strides[3], P.dtype);
+  }
+  __syncwarp();
+
+  float dk[kMaxDPerLane], dv[kMaxDPerLane];
+#pragma unroll
+  for (int r = 0; r < kMaxDPerLane; ++r) dk[r] = dv[r] = 0.f;
+
+  for (int g = 0; g < group; ++g) {
+    make_view(P, b, hk * group + g, &s);
+    const ScoreMods mods = make_mods(P, s);
+    int lo, hi;
+    query_range_for_keys(mods, j, j, &lo, &hi);
+    for (int i0 = lo; i0 < hi; i0 += 32) {
+      const int i = i0 + lane;
+      PairGrad pg{0.f, 0.f};
+      if (i < hi) {
+        const float raw = dot_row(k_s[warp], P.q, s.q_off + (int64_t)i * P.q_strides[2], P.q_strides[3], D, P.dtype);
+        const float dp =
+            dot_row(v_s[warp], P.dout, s.do_off + (int64_t)i * P.do_strides[2], P.do_strides[3], D, P.dtype);
+        const float lse = P.lse[s.lse_off + (int64_t)i * s.lse_row_stride];
+        const float delta = P.delta[s.delta_off + (int64_t)i * s.delta_row_stride];
+        pg = pair_grad(mods, raw, dp, lse, delta, i, j);
+      }
+      const int in = min(32, hi - i0);
+      for (int ii = 0; ii < in; ++ii) {
+        const float pd = __shfl_sync(0xffffffffu, pg.p_drop, ii);
+        const float ds = __shfl_sync(0xffffffffu, pg.ds, ii);
+        if (pd == 0.f && ds == 0.f) continue;
+        const int64_t qoff = s.q_off + (int64_t)(i0 + ii) * P.q_strides[2];
+        const int64_t dooff = s.do_off + (int64_t)(i0 + ii) * P.do_strides[2];
+#pragma unroll
+        for (int r = 0; r < kMaxDPerLane; ++r) {
+          const int d = lane + 32 * r;
+          if (d < D) {
+            dv[r] += pd * load_as_float(P.dout, dooff + (int64_t)d * P.do_strides[3], P.dtype);
+            dk[r] += ds * load_as_float(P.q, qoff + (int64_t)d * P.q_strides[3], P.dtype);
+          }
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < kMaxDPerLane; ++r) {
+    const int d = lane + 32 * r;
+    if (d < D) {
+      store_from_float(P.dk, s.dk_off + (int64_t)j * P.dk_strides[2] + (int64_t)d * P.dk_strides[3], P.dtype,
+                       dk[r] * P.softmax_scale);
+      store_from_float(P.dv, s.dv_off + (int64_t)j * P.dv_strides[2] + (int64_t)d * P.dv_strides[3], P.dtype, dv[r]);
+    }
+  }
+}
+
+int check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "%s launch failed: %s", what, cudaGetErrorString(e));
+  return 0;
+}
+
+}  // namespace
+
+int launch_bwd_delta(const fa_attn_params& p, cudaStream_t stream) {
+  dim3 grid((p.seqlen_q + kWarpsPerBlock - 1) / kWarpsPerBlock, p.batch * p.heads_q);
+  simt_delta_kernel<<<grid, kWarpsPerBlock * 32, 0, stream>>>(p);
+  return check_launch("delta");
+}
+
+int launch_fwd_simt(const fa_attn_params& p, cudaStream_t stream) {
+  if (p.head_dim > kMaxD) return set_error(FA_ERR_UNSUPPORTED, "head_dim %d exceeds %d", p.head_dim, kMaxD);
+  dim3 grid((p.seqlen_q + kWarpsPerBlock - 1) / kWarpsPerBlock, p.batch * p.heads_q);
+  simt_fwd_kernel<<<grid, kWarpsPerBlock * 32, 0, stream>>>(p);
+  return check_launch("simt forward");
+}
+
+int launch_bwd_simt(const fa_attn_params& p, cudaStream_t stream) {
+  if (p.head_dim > kMaxD) return set_error(FA_ERR_UNSUPPORTED, "head_dim %d exceeds %d", p.head_dim, kMaxD);
+  dim3 gq((p.seqlen_q + kWarpsPerBlock - 1) / kWarpsPerBlock, p.batch * p.heads_q);
+  simt_bwd_dq_kernel<<<gq, kWarpsPerBlock * 32, 0, stream>>>(p);
+  int rc = check_launch("simt dq");
+  if (rc) return rc;
+  dim3 gk((p.seqlen_k + kWarpsPerBlock - 1) / kWarpsPerBlock, p.batch * p.heads_kv);
+  simt_bwd_dkdv_kernel<<<gk, kWarpsPerBlock * 32, 0, stream>>>(p);
+  return check_launch("simt dkdv");
+}
+
+}  // namespace fa

@@ -31,6 +31,12 @@ extern "C" {
 
 #define FA_B200_ABI_VERSION 1
 
+#if defined(__GNUC__)
+#define FA_API __attribute__((visibility("default")))
+#else
+#define FA_API
+#endif
+
 enum fa_dtype { FA_F16 = 0, FA_BF16 = 1, FA_F32 = 2 };
 
 enum fa_error {
@@ -162,47 +168,47 @@ typedef struct fa_tiny_params {
 } fa_tiny_params;
 
 /* Library / device queries. */
-int32_t fa_abi_version(void);
+FA_API int32_t fa_abi_version(void);
 /* 0 when `device` is a compute-capability-10.x GPU, else a negative code (replaces the gfx1100 gate,
    fa_rdna3/_validation.py:22-37). */
-int32_t fa_device_supported(int32_t device);
-const char* fa_last_error_string(void);
+FA_API int32_t fa_device_supported(int32_t device);
+FA_API const char* fa_last_error_string(void);
 /* fa_path of the calling thread's last fa_fwd / fa_bwd / fa_varlen_* call. */
-int32_t fa_last_path(void);
+FA_API int32_t fa_last_path(void);
 
 /* Dense forward: writes out and lse. Replaces the _attention_forward launch,
    fa_rdna3/interface.py:154-199 (kernel fa_rdna3/kernels/forward.py:28-164). */
-int32_t fa_fwd(const fa_attn_params* p, void* stream);
+FA_API int32_t fa_fwd(const fa_attn_params* p, void* stream);
 
 /* delta = rowsum(out * dout). Replaces the _attention_bwd_preprocess launch,
    fa_rdna3/interface.py:225-233 (kernel fa_rdna3/kernels/backward.py:18-46); varlen form
    fa_rdna3/interface.py:530-538. */
-int32_t fa_bwd_delta(const fa_attn_params* p, void* stream);
+FA_API int32_t fa_bwd_delta(const fa_attn_params* p, void* stream);
 
 /* Dense backward: computes delta, then dk/dv and dq. Replaces the three launches of
    fa_rdna3/interface.py:202-277 (kernels fa_rdna3/kernels/backward.py:56-322). */
-int32_t fa_bwd(const fa_attn_params* p, void* stream);
+FA_API int32_t fa_bwd(const fa_attn_params* p, void* stream);
 
 /* Packed variable-length forward / backward (p->varlen must be 1). Replace
    fa_rdna3/interface.py:482-511 and :514-580 (kernels fa_rdna3/kernels/varlen.py:42-421). */
-int32_t fa_varlen_fwd(const fa_attn_params* p, void* stream);
-int32_t fa_varlen_bwd(const fa_attn_params* p, void* stream);
+FA_API int32_t fa_varlen_fwd(const fa_attn_params* p, void* stream);
+FA_API int32_t fa_varlen_bwd(const fa_attn_params* p, void* stream);
 
 /* Split-K decode (partials + merge). Replaces the _attention_split and _attention_combine launches,
    fa_rdna3/interface.py:457-478 (kernels fa_rdna3/kernels/decode.py:13-125). */
-int32_t fa_decode_splitk(const fa_decode_params* p, void* stream);
+FA_API int32_t fa_decode_splitk(const fa_decode_params* p, void* stream);
 
 /* Stand-alone LSE merge; also merges per-GPU shard partials. Replaces the _attention_combine launch,
    fa_rdna3/kernels/decode.py:80-125. */
-int32_t fa_combine(const fa_combine_params* p, void* stream);
+FA_API int32_t fa_combine(const fa_combine_params* p, void* stream);
 
 /* Paged-KV decode. Replaces the _attention_decode_paged (+ combine) launches,
    fa_rdna3/interface.py:703-727 (kernel fa_rdna3/kernels/paged.py:17-89). */
-int32_t fa_decode_paged(const fa_paged_params* p, void* stream);
+FA_API int32_t fa_decode_paged(const fa_paged_params* p, void* stream);
 
 /* FP32 short-sequence forward. Replaces the _attention_tiny_forward launch,
    fa_rdna3/interface.py:84-104 (kernel fa_rdna3/kernels/tiny.py:10-85). */
-int32_t fa_tiny_fwd(const fa_tiny_params* p, void* stream);
+FA_API int32_t fa_tiny_fwd(const fa_tiny_params* p, void* stream);
 
 #ifdef __cplusplus
 }

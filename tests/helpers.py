@@ -1,0 +1,42 @@
+"""Shared helpers of the parity tests: seeded inputs and the acceptance metrics.
+
+Tolerances (from the build's stated targets, tighter than the reference's own 3e-3 / 2e-2):
+  O and LSE   max-abs <= 2e-3 (fp16), 1e-2 (bf16)
+  dQ/dK/dV    relative L2 <= 1e-2
+  FP32 tiny   max-abs <= 2e-6
+"""
+import torch
+
+O_TOL = {torch.float16: 2e-3, torch.bfloat16: 1e-2, torch.float32: 2e-3}
+GRAD_REL_L2 = 1e-2
+TINY_TOL = 2e-6
+
+
+def seeded(seed, *shape, dtype=torch.float16, device="cuda"):
+    """N(0, 1) drawn in fp32 on the CPU from `seed`, then cast, so CPU oracle and GPU see the same bits."""
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(*shape, generator=g, dtype=torch.float32).to(dtype).to(device)
+
+
+def max_abs(a, b):
+    a, b = a.float().cpu(), b.float().cpu()
+    both_ninf = torch.isinf(a) & torch.isinf(b) & (a < 0) & (b < 0)
+    d = torch.where(both_ninf, torch.zeros_like(a), (a - b).abs())
+    return float(d.max()) if d.numel() else 0.0
+
+
+def rel_l2(a, b):
+    a, b = a.float().cpu(), b.float().cpu()
+    return float((a - b).norm() / b.norm().clamp_min(1e-12))
+
+
+def assert_close_o(got, want, dtype, what="out"):
+    err = max_abs(got, want)
+    assert err <= O_TOL[dtype], f"{what}: max-abs {err:.3e} > {O_TOL[dtype]:.1e}"
+    assert not torch.isnan(got.float()).any(), f"{what}: NaN"
+
+
+def assert_close_grad(got, want, what):
+    err = rel_l2(got, want)
+    assert err <= GRAD_REL_L2, f"{what}: rel-L2 {err:.3e} > {GRAD_REL_L2:.1e}"
+    assert not torch.isnan(got.float()).any(), f"{what}: NaN"

@@ -1,0 +1,168 @@
+"""Dense forward parity against the fp32 oracle, through the public API and the C ABI.
+
+Grid modelled on the reference's tests/test_forward.py, tests/test_causal_align.py, tests/test_gqa.py,
+tests/test_window.py, tests/test_softcap.py, tests/test_alibi.py, tests/test_bias.py.
+"""
+import math
+
+import pytest
+import torch
+
+from helpers import assert_close_o, max_abs, seeded
+from oracle.attention_oracle import alibi_slopes_ref, attention_ref
+
+pytestmark = pytest.mark.gpu
+
+
+def run_case(dtype, B, H, Hk, Sq, Sk, D, path="auto", seed=0, **opts):
+    import fa_b200
+    from fa_b200 import interface
+
+    q = seeded(seed + 1, B, H, Sq, D, dtype=dtype)
+    k = seeded(seed + 2, B, Hk, Sk, D, dtype=dtype)
+    v = seeded(seed + 3, B, Hk, Sk, D, dtype=dtype)
+    scale = 1.0 / math.sqrt(D)
+    causal = opts.get("causal", False)
+    window = opts.get("window", (-1, -1))
+    softcap = opts.get("softcap", 0.0)
+    bias = opts.get("bias")
+    slopes = alibi_slopes_ref(H).cuda() if opts.get("alibi") else None
+    with interface.force_kernel_path(path):
+        out, lse = interface._forward(q, k, v, causal, scale, window, softcap, bias, slopes, 0.0, 0)
+        used = interface.last_kernel_path()
+    torch.cuda.synchronize()
+    ref_o, ref_l = attention_ref(q.cpu(), k.cpu(), v.cpu(), causal=causal, softmax_scale=scale, window=window,
+                                 softcap=softcap, bias=None if bias is None else bias.cpu(),
+                                 alibi_slopes=None if slopes is None else slopes.cpu())
+    assert_close_o(out, ref_o, dtype)
+    assert_close_o(lse, ref_l, dtype, "lse")
+    return used
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("head_dim", [64, 128])
+@pytest.mark.parametrize("seqlen", [128, 200, 512, 1000, 2048])
+def test_forward_tensor_core(dtype, causal, head_dim, seqlen):
+    used = run_case(dtype, 2, 4, 4, seqlen, seqlen, head_dim, path="tcgen05", seed=seqlen + head_dim, causal=causal)
+    assert used == "tcgen05"
+
+
+@pytest.mark.parametrize("head_dim", [16, 32, 64, 128, 256])
+def test_forward_head_dims(head_dim):
+    run_case(torch.float16, 1, 2, 2, 300, 300, head_dim, seed=head_dim)
+
+
+def test_forward_single_token():
+    run_case(torch.float16, 1, 1, 1, 1, 1, 64, seed=5)
+
+
+@pytest.mark.parametrize("path", ["tcgen05", "simt"])
+@pytest.mark.parametrize("sq,sk", [(333, 777), (777, 333), (1, 500), (129, 1)])
+def test_forward_cross_attention(path, sq, sk):
+    run_case(torch.float16, 2, 4, 4, sq, sk, 64, path=path, seed=sq + sk)
+
+
+@pytest.mark.parametrize("path", ["tcgen05", "simt"])
+@pytest.mark.parametrize("sq,sk", [(128, 384), (384, 128), (256, 64), (200, 333)])
+def test_forward_causal_bottom_right(path, sq, sk):
+    # Sq > Sk leaves the first rows without any visible key: O = 0, LSE = -inf
+    run_case(torch.float16, 1, 4, 4, sq, sk, 64, path=path, seed=sq * 3 + sk, causal=True)
+
+
+@pytest.mark.parametrize("path", ["tcgen05", "simt"])
+@pytest.mark.parametrize("hq,hk", [(32, 8), (16, 4), (8, 1)])
+def test_forward_gqa(path, hq, hk):
+    run_case(torch.float16, 1, hq, hk, 300, 300, 64, path=path, seed=hq + hk, causal=True)
+
+
+@pytest.mark.parametrize("path", ["tcgen05", "simt"])
+@pytest.mark.parametrize("window,causal,sq,sk", [((63, 0), True, 512, 512), ((255, 0), True, 700, 700),
+                                                 ((48, 48), False, 400, 400), ((100, 0), False, 300, 300),
+                                                 ((31, 17), False, 96, 257), ((31, 17), False, 257, 96)])
+def test_forward_window(path, window, causal, sq, sk):
+    run_case(torch.float16, 1, 4, 4, sq, sk, 64, path=path, seed=window[0] + sq, causal=causal, window=window)
+
+
+@pytest.mark.parametrize("path", ["tcgen05", "simt"])
+@pytest.mark.parametrize("softcap", [30.0, 50.0])
+def test_forward_softcap(path, softcap):
+    run_case(torch.float16, 1, 4, 4, 384, 384, 128, path=path, seed=int(softcap), softcap=softcap, causal=True)
+
+
+@pytest.mark.parametrize("path", ["tcgen05", "simt"])
+@pytest.mark.parametrize("heads", [8, 12])
+def test_forward_alibi(path, heads):
+    run_case(torch.float16, 1, heads, heads, 300, 420, 64, path=path, seed=heads, alibi=True, causal=True)
+
+
+@pytest.mark.parametrize("path", ["tcgen05", "simt"])
+@pytest.mark.parametrize("kind", ["full", "batch_broadcast", "head_broadcast", "hard_mask", "all_masked_rows"])
+def test_forward_bias(path, kind):
+    B, H, Sq, Sk = 2, 4, 200, 264
+    g = torch.Generator().manual_seed(7)
+    shape = {"full": (B, H, Sq, Sk), "batch_broadcast": (1, H, Sq, Sk), "head_broadcast": (B, 1, Sq, Sk),
+             "hard_mask": (1, 1, Sq, Sk), "all_masked_rows": (1, 1, Sq, Sk)}[kind]
+    bias = torch.randn(shape, generator=g)
+    if kind == "hard_mask":
+        bias = torch.where(torch.rand(shape, generator=g) < 0.3, torch.full(shape, float("-inf")), bias)
+    if kind == "all_masked_rows":
+        bias[..., 5:9, :] = float("-inf")          # rows with no visible key at all
+        bias[..., 40:60, :130] = float("-inf")     # a whole 128-key tile masked, then very negative logits
+        bias[..., 40:60, 130:] -= 1000.0
+    run_case(torch.float16, B, H, H, Sq, Sk, 64, path=path, seed=3, bias=bias.cuda())
+
+
+def test_forward_fp32_and_transposed_layout():
+    import fa_b200
+
+    q = seeded(1, 2, 300, 4, 64, dtype=torch.float32).transpose(1, 2)   # (B, H, S, D) view of (B, S, H, D)
+    k = seeded(2, 2, 300, 4, 64, dtype=torch.float32).transpose(1, 2)
+    v = seeded(3, 2, 300, 4, 64, dtype=torch.float32).transpose(1, 2)
+    out = fa_b200.flash_attention(q, k, v, causal=True)
+    ref, _ = attention_ref(q.cpu(), k.cpu(), v.cpu(), causal=True)
+    assert max_abs(out, ref) <= 2e-3
+
+
+def test_forward_transposed_layout_stays_on_tensor_cores():
+    from fa_b200 import interface
+    import fa_b200
+
+    q = seeded(1, 2, 384, 4, 128).transpose(1, 2)
+    k = seeded(2, 2, 384, 4, 128).transpose(1, 2)
+    v = seeded(3, 2, 384, 4, 128).transpose(1, 2)
+    out = fa_b200.flash_attention(q, k, v)
+    assert interface.last_kernel_path() == "tcgen05"
+    ref, _ = attention_ref(q.cpu(), k.cpu(), v.cpu())
+    assert_close_o(out, ref, torch.float16)
+
+
+@pytest.mark.parametrize("head_dim", [48, 80, 96, 192])
+def test_forward_padded_head_dim(head_dim):
+    import fa_b200
+
+    q, k, v = (seeded(i, 1, 2, 150, head_dim) for i in (1, 2, 3))
+    out = fa_b200.flash_attention(q, k, v, causal=True)
+    assert out.shape == q.shape
+    ref, _ = attention_ref(q.cpu(), k.cpu(), v.cpu(), causal=True)
+    assert_close_o(out, ref, torch.float16)
+
+
+def test_forward_run_to_run_identical():
+    import fa_b200
+
+    q, k, v = (seeded(i, 2, 8, 1024, 128) for i in (1, 2, 3))
+    a = fa_b200.flash_attention(q, k, v, causal=True)
+    b = fa_b200.flash_attention(q, k, v, causal=True)
+    assert torch.equal(a, b)
+
+
+def test_forward_matches_between_kernel_families():
+    from fa_b200 import interface
+
+    q, k, v = (seeded(i, 1, 4, 640, 128) for i in (1, 2, 3))
+    with interface.force_kernel_path("tcgen05"):
+        a, la = interface._forward(q, k, v, True, 0.0884, (-1, -1), 0.0, None, None, 0.0, 0)
+    with interface.force_kernel_path("simt"):
+        b, lb = interface._forward(q, k, v, True, 0.0884, (-1, -1), 0.0, None, None, 0.0, 0)
+    assert max_abs(a, b) <= 2e-3 and max_abs(la, lb) <= 2e-3
