@@ -1,0 +1,154 @@
+"""Dense backward parity (dQ, dK, dV relative L2 <= 1e-2) against autograd over the fp32 oracle.
+
+Grid modelled on the reference's tests/test_backward.py, tests/test_causal_align.py, tests/test_gqa.py,
+tests/test_window.py, tests/test_softcap.py, tests/test_alibi.py, tests/test_bias.py, tests/test_dropout.py.
+"""
+import math
+
+import pytest
+import torch
+
+from helpers import assert_close_grad, assert_close_o, max_abs, seeded
+from oracle.attention_oracle import alibi_slopes_ref, attention_grads_ref
+
+pytestmark = pytest.mark.gpu
+
+
+def run_case(dtype, B, H, Hk, Sq, Sk, D, path="auto", seed=0, **opts):
+    from fa_b200 import interface
+
+    q = seeded(seed + 1, B, H, Sq, D, dtype=dtype)
+    k = seeded(seed + 2, B, Hk, Sk, D, dtype=dtype)
+    v = seeded(seed + 3, B, Hk, Sk, D, dtype=dtype)
+    dout = seeded(seed + 4, B, H, Sq, D, dtype=dtype)
+    scale = 1.0 / math.sqrt(D)
+    causal = opts.get("causal", False)
+    window = opts.get("window", (-1, -1))
+    softcap = opts.get("softcap", 0.0)
+    bias = opts.get("bias")
+    p, dseed = opts.get("dropout_p", 0.0), opts.get("dropout_seed", 0)
+    slopes = alibi_slopes_ref(H).cuda() if opts.get("alibi") else None
+    with interface.force_kernel_path(path):
+        out, lse = interface._forward(q, k, v, causal, scale, window, softcap, bias, slopes, p, dseed)
+        dq, dk, dv = interface._backward(dout, q, k, v, out, lse, causal, scale, window, softcap, bias, slopes, p,
+                                         dseed)
+        used = interface.last_kernel_path()
+    torch.cuda.synchronize()
+    ro, rl, rdq, rdk, rdv = attention_grads_ref(
+        q.cpu(), k.cpu(), v.cpu(), dout.cpu(), causal=causal, softmax_scale=scale, window=window, softcap=softcap,
+        bias=None if bias is None else bias.cpu(), alibi_slopes=None if slopes is None else slopes.cpu(),
+        dropout_p=p, dropout_seed=dseed)
+    assert_close_o(out, ro, dtype)
+    assert_close_grad(dq, rdq, "dq")
+    assert_close_grad(dk, rdk, "dk")
+    assert_close_grad(dv, rdv, "dv")
+    return used
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("head_dim", [64, 128])
+@pytest.mark.parametrize("seqlen", [128, 200, 512, 1000])
+def test_backward_tensor_core(dtype, causal, head_dim, seqlen):
+    used = run_case(dtype, 2, 4, 4, seqlen, seqlen, head_dim, path="tcgen05", seed=seqlen + head_dim, causal=causal)
+    assert used == "tcgen05"
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("head_dim", [16, 32, 256])
+def test_backward_other_head_dims(causal, head_dim):
+    run_case(torch.float16, 1, 2, 2, 200, 200, head_dim, seed=head_dim, causal=causal)
+
+
+@pytest.mark.parametrize("path", ["tcgen05", "simt"])
+@pytest.mark.parametrize("sq,sk,causal", [(333, 777, False), (777, 333, False), (128, 384, True), (384, 128, True),
+                                          (256, 64, True), (200, 333, True)])
+def test_backward_cross_and_alignment(path, sq, sk, causal):
+    run_case(torch.float16, 1, 4, 4, sq, sk, 64, path=path, seed=sq + sk, causal=causal)
+
+
+@pytest.mark.parametrize("path", ["tcgen05", "simt"])
+@pytest.mark.parametrize("hq,hk", [(32, 8), (8, 1)])
+def test_backward_gqa(path, hq, hk):
+    run_case(torch.float16, 1, hq, hk, 300, 300, 64, path=path, seed=hq + hk, causal=True)
+
+
+@pytest.mark.parametrize("path", ["tcgen05", "simt"])
+@pytest.mark.parametrize("window,causal,sq,sk", [((63, 0), True, 512, 512), ((48, 48), False, 400, 400),
+                                                 ((31, 17), False, 96, 257), ((31, 17), False, 257, 96)])
+def test_backward_window(path, window, causal, sq, sk):
+    run_case(torch.float16, 1, 4, 4, sq, sk, 64, path=path, seed=window[0] + sq, causal=causal, window=window)
+
+
+@pytest.mark.parametrize("path", ["tcgen05", "simt"])
+def test_backward_softcap_alibi(path):
+    run_case(torch.float16, 1, 8, 8, 384, 384, 128, path=path, seed=9, softcap=30.0, alibi=True, causal=True)
+    run_case(torch.bfloat16, 1, 12, 12, 200, 333, 64, path=path, seed=10, softcap=50.0, alibi=True)
+
+
+@pytest.mark.parametrize("path", ["tcgen05", "simt"])
+def test_backward_bias_and_masked_rows(path):
+    B, H, Sq, Sk = 2, 4, 200, 264
+    g = torch.Generator().manual_seed(7)
+    bias = torch.randn(1, H, Sq, Sk, generator=g)
+    bias[..., 5:9, :] = float("-inf")  # fully masked rows: zero output, zero dQ
+    bias[..., :, 100:140] = float("-inf")
+    run_case(torch.float16, B, H, H, Sq, Sk, 64, path=path, seed=3, bias=bias.cuda())
+
+
+@pytest.mark.parametrize("path", ["tcgen05", "simt"])
+def test_backward_dropout_fixed_seed(path):
+    # the oracle regenerates the same Philox mask, so forward and backward masks are pinned bit for bit
+    run_case(torch.float16, 2, 2, 2, 200, 264, 64, path=path, seed=5, dropout_p=0.2, dropout_seed=777)
+
+
+def test_dropout_p0_is_exact_and_unbiased():
+    import fa_b200
+
+    q, k, v = (seeded(i, 1, 4, 256, 64) for i in (1, 2, 3))
+    ref = fa_b200.flash_attention(q, k, v, causal=True)
+    assert torch.equal(ref, fa_b200.flash_attention(q, k, v, causal=True, dropout_p=0.0))
+    base = fa_b200.flash_attention(q, k, v).float()
+    torch.manual_seed(1)
+    acc = torch.zeros_like(base)
+    n = 200
+    for _ in range(n):
+        acc += fa_b200.flash_attention(q, k, v, dropout_p=0.25).float()
+    assert (acc / n - base).abs().mean().item() < 8e-3
+
+
+def test_autograd_through_public_api():
+    import fa_b200
+
+    q, k, v = (seeded(i, 2, 4, 300, 128).requires_grad_(True) for i in (1, 2, 3))
+    dout = seeded(4, 2, 4, 300, 128)
+    fa_b200.flash_attention(q, k, v, causal=True).backward(dout)
+    _, _, rdq, rdk, rdv = attention_grads_ref(q.detach().cpu(), k.detach().cpu(), v.detach().cpu(), dout.cpu(),
+                                              causal=True)
+    assert_close_grad(q.grad, rdq, "dq")
+    assert_close_grad(k.grad, rdk, "dk")
+    assert_close_grad(v.grad, rdv, "dv")
+
+
+def test_fp32_and_padded_head_dim_gradients():
+    import fa_b200
+
+    q, k, v = (seeded(i, 1, 2, 150, 80, dtype=torch.float32).requires_grad_(True) for i in (1, 2, 3))
+    dout = seeded(4, 1, 2, 150, 80, dtype=torch.float32)
+    fa_b200.flash_attention(q, k, v, causal=True).backward(dout)
+    assert q.grad.shape == q.shape
+    _, _, rdq, rdk, rdv = attention_grads_ref(q.detach().cpu(), k.detach().cpu(), v.detach().cpu(), dout.cpu(),
+                                              causal=True)
+    assert_close_grad(q.grad, rdq, "dq")
+    assert_close_grad(k.grad, rdk, "dk")
+    assert_close_grad(v.grad, rdv, "dv")
+
+
+def test_backward_run_to_run_identical():
+    from fa_b200 import interface
+
+    q, k, v, dout = (seeded(i, 1, 8, 1024, 128) for i in (1, 2, 3, 4))
+    out, lse = interface._forward(q, k, v, True, 0.0884, (-1, -1), 0.0, None, None, 0.0, 0)
+    a = interface._backward(dout, q, k, v, out, lse, True, 0.0884, (-1, -1), 0.0, None, None, 0.0, 0)
+    b = interface._backward(dout, q, k, v, out, lse, True, 0.0884, (-1, -1), 0.0, None, None, 0.0, 0)
+    assert all(torch.equal(x, y) for x, y in zip(a, b))

@@ -1,0 +1,202 @@
+"""Split-K decode, LSE merge, paged-KV decode and the FP32 short-sequence kernel against the oracle.
+
+Modelled on the reference's tests/test_decode.py, tests/test_paged.py, tests/test_tiny.py, tests/test_gqa.py.
+"""
+import ctypes as C
+import math
+
+import pytest
+import torch
+
+from helpers import O_TOL, TINY_TOL, assert_close_o, max_abs, seeded
+from oracle import attention_oracle as oracle
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("head_dim", [64, 128])
+@pytest.mark.parametrize("sq", [1, 4])
+@pytest.mark.parametrize("sk", [128, 1000, 4096, 16384])
+def test_decode(dtype, head_dim, sq, sk):
+    import fa_b200
+
+    q = seeded(1, 2, 8, sq, head_dim, dtype=dtype)
+    k = seeded(2, 2, 8, sk, head_dim, dtype=dtype)
+    v = seeded(3, 2, 8, sk, head_dim, dtype=dtype)
+    out = fa_b200.flash_attention_decode(q, k, v)
+    ref, _ = oracle.decode_ref(q.cpu(), k.cpu(), v.cpu())
+    assert_close_o(out, ref, dtype)
+
+
+@pytest.mark.parametrize("head_dim", [16, 32, 256, 512])
+def test_decode_other_head_dims(head_dim):
+    import fa_b200
+
+    q, k, v = seeded(1, 1, 4, 2, head_dim), seeded(2, 1, 2, 700, head_dim), seeded(3, 1, 2, 700, head_dim)
+    out = fa_b200.flash_attention_decode(q, k, v)
+    ref, _ = oracle.decode_ref(q.cpu(), k.cpu(), v.cpu())
+    assert_close_o(out, ref, torch.float16)
+
+
+def test_decode_gqa_long_cache_and_strided_views():
+    import fa_b200
+
+    q = seeded(1, 2, 32, 1, 128)
+    k = seeded(2, 2, 8192, 8, 128).transpose(1, 2)  # (B, Hkv, Sk, D) view of a (B, Sk, Hkv, D) cache
+    v = seeded(3, 2, 8192, 8, 128).transpose(1, 2)
+    out = fa_b200.flash_attention_decode(q, k, v, softmax_scale=0.07)
+    ref, _ = oracle.decode_ref(q.cpu(), k.cpu(), v.cpu(), softmax_scale=0.07)
+    assert_close_o(out, ref, torch.float16)
+
+
+def test_decode_forced_split_counts_agree():
+    from fa_b200 import interface
+
+    q, k, v = seeded(1, 1, 4, 3, 64), seeded(2, 1, 4, 1000, 64), seeded(3, 1, 4, 1000, 64)
+    ref, _ = oracle.decode_ref(q.cpu(), k.cpu(), v.cpu())
+    for splits in (1, 2, 7, 16, 32):  # 32 leaves some slices empty (LSE = -inf partials)
+        out = interface._decode_impl(q, k, v, 0.125, splits)
+        assert_close_o(out, ref, torch.float16, f"splits={splits}")
+
+
+def test_decode_rejects_autograd_and_fp32():
+    import fa_b200
+
+    q = seeded(1, 1, 2, 1, 64).requires_grad_(True)
+    k = seeded(2, 1, 2, 64, 64)
+    with pytest.raises(RuntimeError, match="inference-only"):
+        fa_b200.flash_attention_decode(q, k, k)
+    with pytest.raises(ValueError, match="unsupported dtype"):
+        fa_b200.flash_attention_decode(q.detach().float(), k.float(), k.float())
+
+
+def test_combine_entry_point():
+    from fa_b200 import _lib
+
+    lib = _lib.load()
+    S, R, D = 5, 37, 64
+    o = seeded(1, S, R, D, dtype=torch.float32)
+    lse = seeded(2, S, R, dtype=torch.float32)
+    lse[1] = float("-inf")
+    lse[:, 3] = float("-inf")  # a row with no contribution at all -> zeros, LSE -inf
+    out = torch.empty(R, D, dtype=torch.float16, device="cuda")
+    lse_out = torch.empty(R, dtype=torch.float32, device="cuda")
+    p = _lib.CombineParams()
+    p.out_dtype, p.rows, p.head_dim, p.num_splits = _lib.FA_F16, R, D, S
+    p.o_partial, p.o_split_stride, p.o_row_stride = o.data_ptr(), R * D, D
+    p.lse_partial, p.lse_split_stride, p.lse_row_stride = lse.data_ptr(), R, 1
+    p.out, p.out_row_stride, p.lse_out = out.data_ptr(), D, lse_out.data_ptr()
+    _lib.check(lib.fa_combine(C.byref(p), C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    torch.cuda.synchronize()
+    ro, rl = oracle.combine_ref(o.cpu(), lse.cpu())
+    assert max_abs(out, ro) <= 2e-3 and max_abs(lse_out, rl) <= 1e-5
+    assert torch.all(out[3] == 0) and torch.isinf(lse_out[3])
+
+
+# ------------------------------------------------------------------------------------------ paged
+def make_paged(B, Hq, Hk, D, bs, contexts, dtype=torch.float16, seed=0, shuffle=True):
+    max_blocks = max(1, math.ceil(max(contexts) / bs))
+    nb = B * max_blocks
+    g = torch.Generator().manual_seed(seed)
+    q = seeded(seed + 1, B, Hq, D, dtype=dtype)
+    kc = seeded(seed + 2, nb, bs, Hk, D, dtype=dtype)
+    vc = seeded(seed + 3, nb, bs, Hk, D, dtype=dtype)
+    ids = torch.randperm(nb, generator=g) if shuffle else torch.arange(nb)
+    table = ids.to(torch.int32).reshape(B, max_blocks).cuda()
+    ctx = torch.tensor(contexts, dtype=torch.int32, device="cuda")
+    return q, kc, vc, table, ctx
+
+
+def check_paged(q, kc, vc, table, ctx, dtype=torch.float16, **kw):
+    import fa_b200
+
+    out = fa_b200.flash_attention_decode_paged(q, kc, vc, table, ctx, **kw)
+    ref, _ = oracle.paged_ref(q.cpu(), kc.cpu(), vc.cpu(), table.cpu(), ctx.cpu(), kw.get("softmax_scale"))
+    assert_close_o(out, ref, dtype)
+    return out
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("hq,hk", [(8, 8), (8, 2)])
+@pytest.mark.parametrize("head_dim", [64, 128])
+def test_paged(dtype, hq, hk, head_dim):
+    check_paged(*make_paged(3, hq, hk, head_dim, 16, [100, 63, 16], dtype=dtype, seed=hq + hk + head_dim), dtype=dtype)
+
+
+def test_paged_zero_context_returns_zeros():
+    q, kc, vc, table, ctx = make_paged(2, 4, 4, 64, 16, [0, 40])
+    out = check_paged(q, kc, vc, table, ctx)
+    assert torch.all(out[0] == 0)
+
+
+@pytest.mark.parametrize("splits", [1, 3, 7, 32])
+def test_paged_forced_splits(splits):
+    check_paged(*make_paged(2, 8, 2, 128, 16, [1000, 333], seed=splits), num_splits=splits)
+
+
+@pytest.mark.parametrize("block_size", [8, 32, 64])
+def test_paged_block_sizes(block_size):
+    check_paged(*make_paged(2, 4, 4, 64, block_size, [257, 64], seed=block_size))
+
+
+def test_paged_strided_metadata_invalid_ids_and_clamped_context():
+    q, kc, vc, table, ctx = make_paged(3, 8, 2, 64, 16, [200, 90, 48], seed=4)
+    wide = torch.zeros(3, table.shape[1] * 2, dtype=torch.int32, device="cuda")
+    wide[:, ::2] = table
+    ctx_wide = torch.zeros(6, dtype=torch.int32, device="cuda")
+    ctx_wide[::2] = ctx
+    check_paged(q, kc, vc, wide[:, ::2], ctx_wide[::2])
+    bad = table.clone()
+    bad[0, 2] = -1                      # never dereferenced, contributes nothing
+    bad[1, 0] = kc.shape[0] + 5
+    check_paged(q, kc, vc, bad, ctx)
+    huge = torch.tensor([10 ** 9, -5, 48], dtype=torch.int32, device="cuda")  # clamped to [0, capacity]
+    check_paged(q, kc, vc, table, huge)
+
+
+def test_paged_long_context_auto_split():
+    contexts = [16384, 1, 9000, 4097]
+    check_paged(*make_paged(4, 32, 8, 128, 16, contexts, seed=6), max_context_len=16384)
+
+
+def test_paged_kv_shards_merge_to_whole():
+    """Every G-th logical block per shard, merged with the LSE rule, equals the unsharded result."""
+    from fa_b200 import interface
+
+    q, kc, vc, table, ctx = make_paged(2, 8, 2, 128, 16, [1500, 700], seed=8)
+    whole, _ = oracle.paged_ref(q.cpu(), kc.cpu(), vc.cpu(), table.cpu(), ctx.cpu())
+    for G in (2, 4):
+        parts = [interface._paged_launch(q, kc, vc, table, ctx, 1 / math.sqrt(128), 2, first_block=r, block_step=G,
+                                         want_lse=True, out_f32=True) for r in range(G)]
+        o, _ = oracle.combine_ref(torch.stack([p[0] for p in parts]).cpu(), torch.stack([p[1] for p in parts]).cpu())
+        assert max_abs(o, whole) <= 2e-3
+
+
+# ------------------------------------------------------------------------------------------ tiny
+@pytest.mark.parametrize("seqlen", [1, 6, 19, 32])
+@pytest.mark.parametrize("bias_kind", ["none", "fp32", "masked_rows"])
+def test_tiny_fp32(seqlen, bias_kind):
+    import fa_b200
+    from fa_b200 import interface
+
+    q, k, v = (seeded(i + seqlen, 2, 8, seqlen, 128, dtype=torch.float32) for i in (1, 2, 3))
+    bias = None
+    if bias_kind != "none":
+        bias = seeded(9, 1, 8, seqlen, seqlen, dtype=torch.float32)
+        if bias_kind == "masked_rows":
+            bias[:, :, 0, :] = float("-inf")
+    assert interface._can_use_tiny_forward(q, k, v, False, (-1, -1), 0.0, None, 0.0, 128)
+    out = fa_b200.flash_attention(q, k, v, bias=bias)
+    ref = oracle.tiny_ref(q.cpu(), k.cpu(), v.cpu(), bias=None if bias is None else bias.cpu())
+    assert max_abs(out, ref) <= TINY_TOL
+    if bias_kind == "masked_rows":
+        assert torch.all(out[:, :, 0] == 0)
+
+
+def test_tiny_transposed_layout():
+    import fa_b200
+
+    q, k, v = (seeded(i, 2, 19, 8, 128, dtype=torch.float32).transpose(1, 2) for i in (1, 2, 3))
+    out = fa_b200.flash_attention(q, k, v)
+    assert max_abs(out, oracle.tiny_ref(q.cpu(), k.cpu(), v.cpu())) <= TINY_TOL
