@@ -1,0 +1,404 @@
+"""Benchmark of the attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--skip-extras]
+
+One "step" is one forward + backward pass of causal attention at the headline configuration
+(batch 2, 16 heads, sequence 2048, head_dim 128, fp16, bottom-right causal mask, seeded N(0,1) inputs).
+With N > 1 (launched under torchrun, one rank per GPU) every rank runs the same step on its own batch
+(the path partitions by batch x head and needs no communication), so scaling is weak and the reported
+value is N x FLOPs / max-over-ranks time.
+
+The single JSON line printed by rank 0 carries
+  value      device-resident throughput: algorithmic FLOPs of fwd+bwd / CUDA-event time of the four kernels
+  e2e        the same metric through the public API with pinned HOST buffers (H2D of q, k, v, dO and D2H of
+             O, dQ, dK, dV inside the timed region)
+  roofline   the dominant kernel against the measured tensor-core peak (kernels are timed one by one)
+  kernels    every kernel of the step: time, algorithmic work, achieved rate
+  decode     secondary headline numbers: split-K and paged decode KV GB/s against the measured HBM peak
+  cpu_baseline  the fp32 math-attention oracle on the host cores, on a bounded sample of the same workload
+
+`--impl reference` times that CPU path alone (the reference's kernels cannot run without an AMD GPU; its
+CPU-capable path is fp32 math attention, which the oracle restates).
+"""
+import argparse
+import ctypes as C
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "flash-attention-rdna3_b200"))
+
+import torch
+
+METRIC = "fwd/bwd TFLOP/s (% tcgen05 peak) 2x16x2048x128 causal; decode KV GB/s (% HBM)"
+B, H, S, D = 2, 16, 2048, 128
+FWD_FLOPS = 4 * B * H * S * S * D / 2          # causal: half of 4*B*H*S^2*D
+BWD_FLOPS = 2.5 * FWD_FLOPS                    # reference convention (bench/benchmark.py:123 of fa_rdna3)
+STEP_FLOPS = FWD_FLOPS + BWD_FLOPS
+# Algorithmic share of the backward matmuls: dK/dV kernel = S^T, dP^T, dV, dK (4 of 5), dQ kernel = dQ (1 of 5;
+# its recomputed S and dP are not counted).
+KERNEL_FLOPS = {"fwd": FWD_FLOPS, "bwd_dkdv": 0.8 * BWD_FLOPS, "bwd_dq": 0.2 * BWD_FLOPS}
+DELTA_BYTES = 2 * B * H * S * D * 2 + B * H * S * 4   # reads O and dO, writes delta
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the committed ncu captures (profiles/); null
+# where no capture exists yet.
+NCU_TRAFFIC_BYTES = {"fwd": None, "bwd_dkdv": None, "bwd_dq": None}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"tflops": d["bf16_tflops"], "tflops_sustained": d.get("bf16_tflops_sustained"),
+                "hbm_gbs": d["hbm_gbs"], "source": "measured"}
+    return {"tflops": 1590.0, "tflops_sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        clocks, cmax, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                clocks.append(float(parts[0]))
+                cmax = float(parts[1])
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[2:6]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": cmax,
+                "reasons": sorted(reasons), "samples": len(clocks)}
+
+
+def seeded(seed, *shape, dtype=torch.float16):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(*shape, generator=g, dtype=torch.float32).to(dtype)
+
+
+# ---------------------------------------------------------------------------------------------------------
+# CPU arm: fp32 math attention (the oracle) on the host cores, bounded sample of the headline workload
+# ---------------------------------------------------------------------------------------------------------
+def cpu_sample_step(heads):
+    """One fwd+bwd of batch 1 x `heads` heads x 2048 x 128 causal in fp32; returns (seconds, flops)."""
+    from oracle.attention_oracle import attention_grads_ref
+
+    q, k, v, dout = (seeded(1002 + i, 1, heads, S, D).float() for i in range(4))
+    t0 = time.perf_counter()
+    attention_grads_ref(q, k, v, dout, causal=True, softmax_scale=1.0 / math.sqrt(D))
+    dt = time.perf_counter() - t0
+    return dt, STEP_FLOPS * heads / (B * H)
+
+
+def cpu_baseline(steps=3, heads=8):
+    torch.set_num_threads(os.cpu_count() or 1)
+    cpu_sample_step(1)  # warm-up
+    times, flops = [], 0.0
+    for _ in range(steps):
+        dt, flops = cpu_sample_step(heads)
+        times.append(dt)
+    t = statistics.median(times)
+    return {"value": flops / t / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"fp32 math attention fwd+bwd (autograd) of 1 batch x {heads} heads of the "
+                      f"{B}x{H}x{S}x{D} causal workload, median of {steps}; FLOPs counted as for the GPU arm"}
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    torch.set_num_threads(os.cpu_count() or 1)
+    heads = 2
+    for _ in range(max(1, min(args.warmup, 1))):
+        cpu_sample_step(1)
+    times, flops = [], 0.0
+    for _ in range(args.steps):
+        dt, flops = cpu_sample_step(heads)
+        times.append(dt)
+    total = sum(times)
+    value = flops * args.steps / total / 1e12
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": total / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"fwd+bwd causal attention {B}x{H}x{S}x{D}, seeded N(0,1); each step is a bounded "
+                               f"sample of 1 batch x {heads} heads on the host cores"},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": f"1 batch x {heads} heads per step, fp32 math attention with autograd backward"},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+# ---------------------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------------------
+class Flusher:
+    """Writes a buffer larger than L2 (126 MB) so the next timed launch starts from a cold cache. The write
+    also gives the host time to queue the next launch behind it, so launch latency is not timed."""
+
+    def __init__(self, device, mbytes=512):
+        self.buf = torch.empty(mbytes * 1024 * 1024, dtype=torch.uint8, device=device)
+
+    def __call__(self):
+        self.buf.zero_()
+
+
+def timed(fn, flush, stream_events=True):
+    flush()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    fn()
+    e.record()
+    return s, e
+
+
+def gpu_arm(args):
+    import fa_b200
+    from fa_b200 import _lib, interface
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    distributed = world > 1
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if distributed:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=device)
+    reason = fa_b200.unsupported_reason(device)
+    if reason is not None:
+        raise RuntimeError(reason)
+    lib = _lib.load()
+    peaks = load_peaks()
+    scale = 1.0 / math.sqrt(D)
+
+    # every rank owns its own batch: weak scaling over batch x heads, no data-path collective
+    host = [seeded(1002 + 10 * rank + i, B, H, S, D).pin_memory() for i in range(4)]
+    q, k, v, dout = (t.to(device) for t in host)
+    flush = Flusher(device)
+    stream = torch.cuda.current_stream(device)
+
+    # one parameter block reused by every launch: outputs and scratch are allocated once
+    out = torch.empty_like(q)
+    lse = torch.empty(B, H, S, dtype=torch.float32, device=device)
+    delta = torch.empty_like(lse)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    p = interface._attn_params(q, k, v, out, lse, True, scale, (-1, -1), 0.0, None, None, 0.0, 0)
+    interface._fill_backward(p, dout, delta, dq, dk, dv, False)
+    sptr = C.c_void_p(stream.cuda_stream)
+
+    def launch_fwd():
+        _lib.check(lib.fa_fwd(C.byref(p), sptr))
+
+    def launch_bwd(parts):
+        p.bwd_parts = parts
+        _lib.check(lib.fa_bwd(C.byref(p), sptr))
+
+    parts = [("fwd", launch_fwd), ("bwd_delta", lambda: launch_bwd(_lib.FA_BWD_DELTA)),
+             ("bwd_dkdv", lambda: launch_bwd(_lib.FA_BWD_DKDV)), ("bwd_dq", lambda: launch_bwd(_lib.FA_BWD_DQ))]
+
+    def step():
+        """One fwd+bwd pass; every kernel is timed on its own with a cold L2. Returns per-kernel ms."""
+        evs = [(name, *timed(fn, flush)) for name, fn in parts]
+        return evs
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    if interface.last_kernel_path() != "tcgen05":
+        raise RuntimeError("the headline configuration did not run on the tcgen05 kernels")
+    if distributed:
+        dist.barrier()
+    torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    recorded = [step() for _ in range(args.steps)]
+    torch.cuda.synchronize()
+    if distributed:
+        dist.barrier()
+    torch.cuda.synchronize()
+    clocks = sampler.stop() if rank == 0 else None
+    fa_b200.check_status(device)
+
+    per_kernel = {name: [] for name, _ in parts}
+    step_ms = []
+    for evs in recorded:
+        total = 0.0
+        for name, s, e in evs:
+            ms = s.elapsed_time(e)
+            per_kernel[name].append(ms)
+            total += ms
+        step_ms.append(total)
+    total_ms = torch.tensor([sum(step_ms)], dtype=torch.float64, device=device)
+    if distributed:
+        dist.all_reduce(total_ms, op=dist.ReduceOp.MAX)
+    total_ms = float(total_ms.item())
+    ms_per_step = total_ms / args.steps
+    value = world * STEP_FLOPS / (ms_per_step * 1e-3) / 1e12
+
+    # end to end through the public API: pinned host tensors in, O and gradients back to pinned host memory
+    host_out = [torch.empty(B, H, S, D, dtype=torch.float16).pin_memory() for _ in range(4)]
+
+    def e2e_step():
+        qd, kd, vd, dod = (t.to(device, non_blocking=True) for t in host)
+        qd.requires_grad_(True)
+        kd.requires_grad_(True)
+        vd.requires_grad_(True)
+        o = fa_b200.flash_attention(qd, kd, vd, causal=True)
+        o.backward(dod)
+        for dst, src in zip(host_out, (o.detach(), qd.grad, kd.grad, vd.grad)):
+            dst.copy_(src, non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    torch.cuda.synchronize()
+    if distributed:
+        dist.barrier()
+    e2e_ms = []
+    for _ in range(args.steps):
+        s, e = timed(e2e_step, flush)
+        e2e_ms.append((s, e))
+    torch.cuda.synchronize()
+    e2e_total = torch.tensor([sum(s.elapsed_time(e) for s, e in e2e_ms)], dtype=torch.float64, device=device)
+    if distributed:
+        dist.all_reduce(e2e_total, op=dist.ReduceOp.MAX)
+    e2e_value = world * STEP_FLOPS / (float(e2e_total.item()) / args.steps * 1e-3) / 1e12
+    tensor_bytes = B * H * S * D * 2
+
+    if rank != 0:
+        if distributed:
+            dist.destroy_process_group()
+        return
+
+    kernels = {}
+    for name, times in per_kernel.items():
+        ms = statistics.mean(times)
+        entry = {"ms": ms, "share": sum(times) / sum(step_ms)}
+        if name in KERNEL_FLOPS:
+            entry["algorithmic_flops"] = KERNEL_FLOPS[name]
+            entry["tflops"] = KERNEL_FLOPS[name] / (ms * 1e-3) / 1e12
+        else:
+            entry["algorithmic_bytes"] = DELTA_BYTES
+            entry["gbs"] = DELTA_BYTES / (ms * 1e-3) / 1e9
+        kernels[name] = entry
+    dominant = max(KERNEL_FLOPS, key=lambda n: kernels[n]["ms"])
+    achieved = kernels[dominant]["tflops"]
+    roofline = {"bound": "tensor", "kernel": dominant, "achieved": achieved, "peak": peaks["tflops"],
+                "unit": "TFLOP/s", "frac": achieved / peaks["tflops"], "traffic": NCU_TRAFFIC_BYTES.get(dominant),
+                "peak_source": f"{peaks['source']} bf16 burst GEMM", "frac_of_nominal_2250": achieved / 2250.0}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": f"fwd+bwd causal attention {B}x{H}x{S}x{D} fp16 per GPU, seeded N(0,1) "
+                               "(BASELINE configs[1])", "l2": "512 MB flush before every timed launch",
+                   "parallelism": f"batch x head partition over {world} GPU(s), no collective"},
+        "frac_of_measured_peak": value / world / peaks["tflops"],
+        "fwd_tflops": kernels["fwd"]["tflops"],
+        "bwd_tflops": BWD_FLOPS / ((kernels["bwd_delta"]["ms"] + kernels["bwd_dkdv"]["ms"] + kernels["bwd_dq"]["ms"])
+                                   * 1e-3) / 1e12,
+        "kernels": kernels, "roofline": roofline, "clocks": clocks,
+        "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": 4 * tensor_bytes,
+                "d2h_bytes_per_step": 4 * tensor_bytes},
+        "gpu_launches": 4 * args.steps,
+    }
+    if not args.skip_extras and world == 1:
+        line["decode"] = decode_extras(device, flush, peaks)
+        line["cpu_baseline"] = cpu_baseline()
+    print(json.dumps(line))
+    if distributed:
+        dist.destroy_process_group()
+
+
+def decode_extras(device, flush, peaks, iters=20):
+    """Split-K decode (4x32x8192x128) and paged decode (4 seqs, 32/8 heads, page 16, 16384 tokens each)."""
+    import fa_b200
+
+    res = {}
+    q = seeded(1004, 4, 32, 1, 128).to(device)
+    k, v = seeded(1005, 4, 32, 8192, 128).to(device), seeded(1006, 4, 32, 8192, 128).to(device)
+
+    def med(fn):
+        for _ in range(3):
+            fn()
+        evs = [timed(fn, flush) for _ in range(iters)]
+        torch.cuda.synchronize()
+        return statistics.median(s.elapsed_time(e) for s, e in evs)
+
+    ms = med(lambda: fa_b200.flash_attention_decode(q, k, v))
+    nbytes = 2 * 4 * 32 * 8192 * 128 * 2
+    res["splitk_4x32x8192x128"] = {"us": ms * 1e3, "gbs": nbytes / ms / 1e6, "frac_hbm": nbytes / ms / 1e6 / peaks["hbm_gbs"]}
+    del k, v
+    nblocks = 4096
+    g = torch.Generator().manual_seed(1006)
+    kc = seeded(1007, nblocks, 16, 8, 128).to(device)
+    vc = seeded(1008, nblocks, 16, 8, 128).to(device)
+    table = torch.randperm(nblocks, generator=g).to(torch.int32).reshape(4, 1024).to(device)
+    ctx = torch.full((4,), 16384, dtype=torch.int32, device=device)
+    qp = seeded(1009, 4, 32, 128).to(device)
+    ms = med(lambda: fa_b200.flash_attention_decode_paged(qp, kc, vc, table, ctx, max_context_len=16384))
+    nbytes = 4 * 16384 * 2 * 8 * 128 * 2
+    res["paged_4x32/8x16384x128"] = {"us": ms * 1e3, "gbs": nbytes / ms / 1e6, "frac_hbm": nbytes / ms / 1e6 / peaks["hbm_gbs"]}
+    res["note"] = "KV bytes read once (kv heads), timed through the public API with a cold L2; peak = measured copy"
+    return res
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--skip-extras", action="store_true", help="skip decode numbers and the CPU baseline")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

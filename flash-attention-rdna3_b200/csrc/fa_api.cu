@@ -83,18 +83,22 @@ int run_bwd(const fa_attn_params* p, void* stream, bool varlen) {
   int rc = check_attn(p, true, varlen);
   if (rc) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  rc = launch_bwd_delta(*p, s);
-  if (rc) return rc;
+  const int parts = p->bwd_parts == 0 ? (FA_BWD_DELTA | FA_BWD_DKDV | FA_BWD_DQ) : p->bwd_parts;
+  if (parts & FA_BWD_DELTA) {
+    rc = launch_bwd_delta(*p, s);
+    if (rc) return rc;
+  }
+  if (!(parts & (FA_BWD_DKDV | FA_BWD_DQ))) return 0;
   const bool tc_ok = bwd_tcgen05_supported(*p);
   if (p->force_path == FA_PATH_TCGEN05 && !tc_ok)
     return set_error(FA_ERR_UNSUPPORTED, "the tcgen05 backward needs fp16/bf16, head_dim 64 or 128, unit inner "
                                          "strides and 16-byte aligned rows");
   if (tc_ok && p->force_path != FA_PATH_SIMT) {
     set_path(FA_PATH_TCGEN05);
-    return launch_bwd_tcgen05(*p, s);
+    return launch_bwd_tcgen05(*p, parts, s);
   }
   set_path(FA_PATH_SIMT);
-  return launch_bwd_simt(*p, s);
+  return launch_bwd_simt(*p, parts, s);
 }
 
 }  // namespace

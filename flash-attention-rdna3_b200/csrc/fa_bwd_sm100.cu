@@ -590,7 +590,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
 }
 
 template <typename T, int D, bool kMods>
-int launch_typed(const fa_attn_params& p, const BwdArgs& a0, cudaStream_t stream) {
+int launch_typed(const fa_attn_params& p, const BwdArgs& a0, int parts, cudaStream_t stream) {
   constexpr int kTileBytes = (D / 64) * 16384;
   const int smem = 6 * kTileBytes + 1024;
   CUtensorMap mq, mk, mv, mdo;
@@ -614,14 +614,18 @@ int launch_typed(const fa_attn_params& p, const BwdArgs& a0, cudaStream_t stream
   if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "backward smem opt-in failed: %s", cudaGetErrorString(e));
 
   BwdArgs a = a0;
-  a.num_tiles_x = (p.seqlen_k + 127) / 128;
-  kdkdv<<<dim3(a.num_tiles_x, p.batch * p.heads_kv), kBwdThreads, smem, stream>>>(mq, mk, mv, mdo, a);
-  e = cudaGetLastError();
-  if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "dK/dV launch failed: %s", cudaGetErrorString(e));
-  a.num_tiles_x = (p.seqlen_q + 127) / 128;
-  kdq<<<dim3(a.num_tiles_x, p.batch * p.heads_q), kBwdThreads, smem, stream>>>(mq, mk, mv, mdo, a);
-  e = cudaGetLastError();
-  if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "dQ launch failed: %s", cudaGetErrorString(e));
+  if (parts & FA_BWD_DKDV) {
+    a.num_tiles_x = (p.seqlen_k + 127) / 128;
+    kdkdv<<<dim3(a.num_tiles_x, p.batch * p.heads_kv), kBwdThreads, smem, stream>>>(mq, mk, mv, mdo, a);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "dK/dV launch failed: %s", cudaGetErrorString(e));
+  }
+  if (parts & FA_BWD_DQ) {
+    a.num_tiles_x = (p.seqlen_q + 127) / 128;
+    kdq<<<dim3(a.num_tiles_x, p.batch * p.heads_q), kBwdThreads, smem, stream>>>(mq, mk, mv, mdo, a);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "dQ launch failed: %s", cudaGetErrorString(e));
+  }
   return 0;
 }
 
@@ -639,7 +643,7 @@ bool bwd_tcgen05_supported(const fa_attn_params& p) {
          tma_operand_ok(p.dv, p.dv_strides, sk);
 }
 
-int launch_bwd_tcgen05(const fa_attn_params& p, cudaStream_t stream) {
+int launch_bwd_tcgen05(const fa_attn_params& p, int parts, cudaStream_t stream) {
   BwdArgs a;
   a.varlen = p.varlen;
   a.heads_q = p.heads_q;
@@ -689,13 +693,13 @@ int launch_bwd_tcgen05(const fa_attn_params& p, cudaStream_t stream) {
   const bool mods = p.softcap > 0.f || p.bias != nullptr || p.alibi_slopes != nullptr || p.dropout_p > 0.f;
   const bool f16 = p.dtype == FA_F16;
   if (p.head_dim == 128) {
-    if (f16) return mods ? launch_typed<__half, 128, true>(p, a, stream) : launch_typed<__half, 128, false>(p, a, stream);
-    return mods ? launch_typed<__nv_bfloat16, 128, true>(p, a, stream)
-                : launch_typed<__nv_bfloat16, 128, false>(p, a, stream);
+    if (f16) return mods ? launch_typed<__half, 128, true>(p, a, parts, stream) : launch_typed<__half, 128, false>(p, a, parts, stream);
+    return mods ? launch_typed<__nv_bfloat16, 128, true>(p, a, parts, stream)
+                : launch_typed<__nv_bfloat16, 128, false>(p, a, parts, stream);
   }
-  if (f16) return mods ? launch_typed<__half, 64, true>(p, a, stream) : launch_typed<__half, 64, false>(p, a, stream);
-  return mods ? launch_typed<__nv_bfloat16, 64, true>(p, a, stream)
-              : launch_typed<__nv_bfloat16, 64, false>(p, a, stream);
+  if (f16) return mods ? launch_typed<__half, 64, true>(p, a, parts, stream) : launch_typed<__half, 64, false>(p, a, parts, stream);
+  return mods ? launch_typed<__nv_bfloat16, 64, true>(p, a, parts, stream)
+              : launch_typed<__nv_bfloat16, 64, false>(p, a, parts, stream);
 }
 
 }  // namespace fa

@@ -200,10 +200,10 @@ void set_path(int path);
 // Per-family launchers implemented in their own translation units; all return 0 or a negative fa_error.
 int launch_fwd_tcgen05(const fa_attn_params& p, cudaStream_t stream);   // fa_fwd_sm100.cu
 bool fwd_tcgen05_supported(const fa_attn_params& p);
-int launch_bwd_tcgen05(const fa_attn_params& p, cudaStream_t stream);   // fa_bwd_sm100.cu (after delta)
+int launch_bwd_tcgen05(const fa_attn_params& p, int parts, cudaStream_t stream);   // fa_bwd_sm100.cu
 bool bwd_tcgen05_supported(const fa_attn_params& p);
 int launch_fwd_simt(const fa_attn_params& p, cudaStream_t stream);      // fa_simt.cu
-int launch_bwd_simt(const fa_attn_params& p, cudaStream_t stream);      // fa_simt.cu (after delta)
+int launch_bwd_simt(const fa_attn_params& p, int parts, cudaStream_t stream);      // fa_simt.cu
 int launch_bwd_delta(const fa_attn_params& p, cudaStream_t stream);     // fa_simt.cu
 int launch_decode_splitk(const fa_decode_params& p, cudaStream_t stream);  // fa_decode.cu
 int launch_combine(const fa_combine_params& p, cudaStream_t stream);       // fa_decode.cu

@@ -357,15 +357,20 @@ int launch_fwd_simt(const fa_attn_params& p, cudaStream_t stream) {
   return check_launch("simt forward");
 }
 
-int launch_bwd_simt(const fa_attn_params& p, cudaStream_t stream) {
+int launch_bwd_simt(const fa_attn_params& p, int parts, cudaStream_t stream) {
   if (p.head_dim > kMaxD) return set_error(FA_ERR_UNSUPPORTED, "head_dim %d exceeds %d", p.head_dim, kMaxD);
-  dim3 gq((p.seqlen_q + kWarpsPerBlock - 1) / kWarpsPerBlock, p.batch * p.heads_q);
-  simt_bwd_dq_kernel<<<gq, kWarpsPerBlock * 32, 0, stream>>>(p);
-  int rc = check_launch("simt dq");
-  if (rc) return rc;
-  dim3 gk((p.seqlen_k + kWarpsPerBlock - 1) / kWarpsPerBlock, p.batch * p.heads_kv);
-  simt_bwd_dkdv_kernel<<<gk, kWarpsPerBlock * 32, 0, stream>>>(p);
-  return check_launch("simt dkdv");
+  if (parts & FA_BWD_DKDV) {
+    dim3 gk((p.seqlen_k + kWarpsPerBlock - 1) / kWarpsPerBlock, p.batch * p.heads_kv);
+    simt_bwd_dkdv_kernel<<<gk, kWarpsPerBlock * 32, 0, stream>>>(p);
+    int rc = check_launch("simt dkdv");
+    if (rc) return rc;
+  }
+  if (parts & FA_BWD_DQ) {
+    dim3 gq((p.seqlen_q + kWarpsPerBlock - 1) / kWarpsPerBlock, p.batch * p.heads_q);
+    simt_bwd_dq_kernel<<<gq, kWarpsPerBlock * 32, 0, stream>>>(p);
+    return check_launch("simt dq");
+  }
+  return 0;
 }
 
 }  // namespace fa

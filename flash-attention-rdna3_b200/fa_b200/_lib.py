@@ -12,6 +12,7 @@ LIB_PATH = os.path.join(_HERE, "libfa_b200.so")
 
 FA_F16, FA_BF16, FA_F32 = 0, 1, 2
 FA_PATH_NONE, FA_PATH_TCGEN05, FA_PATH_SIMT = 0, 1, 2
+FA_BWD_DELTA, FA_BWD_DKDV, FA_BWD_DQ = 1, 2, 4
 
 I64x4 = C.c_int64 * 4
 I64x3 = C.c_int64 * 3
@@ -40,7 +41,7 @@ class AttnParams(C.Structure):
         ("alibi_slopes", C.c_void_p),
         ("causal", C.c_int32), ("window_left", C.c_int32), ("window_right", C.c_int32),
         ("dropout_p", C.c_float), ("dropout_seed", C.c_uint64),
-        ("status", C.c_void_p), ("force_path", C.c_int32),
+        ("status", C.c_void_p), ("force_path", C.c_int32), ("bwd_parts", C.c_int32),
     ]
 
 

@@ -98,7 +98,11 @@ typedef struct fa_attn_params {
 
   int32_t* status;          /* device int32 or NULL */
   int32_t force_path;       /* 0 = automatic, else an fa_path to force (tests) */
+  int32_t bwd_parts;        /* fa_bwd only: 0 = everything, else a mask of FA_BWD_* parts to run
+                               (lets a caller time or schedule the three kernels separately) */
 } fa_attn_params;
+
+enum fa_bwd_part { FA_BWD_DELTA = 1, FA_BWD_DKDV = 2, FA_BWD_DQ = 4 };
 
 /* Split-K decode: q (batch, heads_q, seqlen_q, head_dim), k/v (batch, heads_kv, seqlen_k, head_dim).
    o_partial (num_splits, batch, heads_q, seqlen_q, head_dim) fp32 contiguous and
