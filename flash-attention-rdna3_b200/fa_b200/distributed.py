@@ -1,0 +1,115 @@
+"""Multi-GPU use of the attention path: one process per GPU, ``torch.distributed`` for the plumbing.
+
+The reference is single-GPU (no communication code anywhere in fa_rdna3); two modes are added here.
+
+1. Batch x head partition (dense, varlen, decode): every (batch, kv-head group) is independent, so ranks
+   take disjoint slices and nothing is exchanged. :func:`partition_batch_heads` gives the slices.
+
+2. KV-sharded long-context paged decode: rank r owns the pages of logical blocks r, r + G, r + 2G, ...
+   of every sequence (block-cyclic, so ragged context lengths stay balanced), holds the whole query, runs
+   the paged kernel over its blocks only and produces a partial ``(O_r fp32, LSE_r)``. One all-gather of
+   ``batch * heads * (head_dim + 1)`` floats per rank brings the partials into local memory and the
+   LSE-weighted merge (``fa_combine``, the rule of fa_rdna3/kernels/decode.py:101-122) runs locally on
+   every rank. Shards without keys contribute ``LSE = -inf`` and are ignored by the merge.
+
+The collective only ever reads local memory: partials are gathered by NCCL first and merged afterwards.
+"""
+import ctypes as C
+import math
+
+import torch
+
+from . import _lib
+from .interface import _DTYPE_CODE, _paged_launch, _paged_num_splits, _stream
+from ._validation import validate_inference_only, validate_paged_inputs, validate_softmax_scale
+
+
+def partition_batch_heads(batch, kv_heads, world_size, rank):
+    """Contiguous range [start, stop) of flattened (batch, kv_head) groups owned by `rank`.
+
+    Groups are dealt as evenly as possible; the first ``total % world_size`` ranks get one extra."""
+    if world_size < 1 or not 0 <= rank < world_size:
+        raise ValueError("rank must satisfy 0 <= rank < world_size")
+    total = batch * kv_heads
+    base, extra = divmod(total, world_size)
+    start = rank * base + min(rank, extra)
+    return start, start + base + (1 if rank < extra else 0)
+
+
+def shard_dense_by_heads(query, key, value, world_size, rank):
+    """Slices of (batch, heads, seq, dim) tensors for `rank` when the partition falls on whole kv heads of
+    every batch entry (kv_heads % world_size == 0): returns (q, k, v) views, no copies."""
+    kv_heads = key.shape[1]
+    if kv_heads % world_size != 0:
+        raise ValueError("kv heads must divide evenly over the ranks for a head-sliced view")
+    per = kv_heads // world_size
+    group = query.shape[1] // kv_heads
+    ks = slice(rank * per, (rank + 1) * per)
+    qs = slice(rank * per * group, (rank + 1) * per * group)
+    return query[:, qs], key[:, ks], value[:, ks]
+
+
+def _merge_partials_cuda(gathered_o, gathered_lse, out_dtype):
+    """gathered_o (G, rows, D) fp32, gathered_lse (G, rows) fp32, contiguous, on the GPU."""
+    lib = _lib.load()
+    G, rows, D = gathered_o.shape
+    out = torch.empty(rows, D, dtype=out_dtype, device=gathered_o.device)
+    p = _lib.CombineParams()
+    p.out_dtype, p.rows, p.head_dim, p.num_splits = _DTYPE_CODE[out_dtype], rows, D, G
+    p.o_partial, p.o_split_stride, p.o_row_stride = gathered_o.data_ptr(), rows * D, D
+    p.lse_partial, p.lse_split_stride, p.lse_row_stride = gathered_lse.data_ptr(), rows, 1
+    p.out, p.out_row_stride = out.data_ptr(), D
+    with torch.cuda.device(out.device):
+        _lib.check(lib.fa_combine(C.byref(p), _stream(out.device)))
+    return out
+
+
+def paged_decode_kv_sharded(query, k_cache, v_cache, block_table, context_lens, softmax_scale=None, *,
+                            group=None, max_context_len=None, num_splits=None,
+                            _local_partial=None, _merge=None):
+    """Paged decode with the KV pages of each sequence sharded block-cyclically over the ranks of `group`.
+
+    Every rank passes the full ``query``, ``block_table`` and ``context_lens`` and its own page pool
+    (only the pages of its logical blocks are read). Returns the merged ``(batch, q_heads, head_dim)``
+    result on every rank. ``_local_partial`` / ``_merge`` replace the CUDA kernels in CPU tests of the
+    protocol.
+    """
+    import torch.distributed as dist
+
+    if not dist.is_available() or not dist.is_initialized():
+        raise RuntimeError("paged_decode_kv_sharded needs an initialised torch.distributed process group")
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    if _local_partial is None:
+        validate_paged_inputs(query, k_cache, v_cache, block_table, context_lens)
+        validate_inference_only(query, k_cache, v_cache)
+    validate_softmax_scale(softmax_scale)
+    batch, q_heads, head_dim = query.shape
+    scale = 1.0 / math.sqrt(head_dim) if softmax_scale is None else float(softmax_scale)
+
+    # every rank must describe the same problem; a mismatch would corrupt the merge silently
+    meta = [batch, q_heads, head_dim, int(block_table.shape[1]), int(k_cache.shape[1])]
+    all_meta = [None] * world
+    dist.all_gather_object(all_meta, meta, group=group)
+    if any(m != meta for m in all_meta):
+        raise ValueError(f"ranks disagree on the decode problem: {all_meta}")
+
+    if _local_partial is None:
+        target = 2 * torch.cuda.get_device_properties(query.device).multi_processor_count
+        local_ctx = None if max_context_len is None else -(-int(max_context_len) // world)
+        splits = int(_paged_num_splits(batch, q_heads, k_cache.shape[1], block_table.shape[1], target,
+                                       max_context_len=local_ctx, requested_splits=num_splits))
+        o_r, lse_r = _paged_launch(query, k_cache, v_cache, block_table, context_lens, scale, splits,
+                                   first_block=rank, block_step=world, want_lse=True, out_f32=True)
+    else:
+        o_r, lse_r = _local_partial(query, k_cache, v_cache, block_table, context_lens, scale, rank, world)
+
+    rows = batch * q_heads
+    packed = torch.cat([o_r.reshape(rows, head_dim).float(), lse_r.reshape(rows, 1).float()], dim=1).contiguous()
+    flat = torch.empty((world * rows, head_dim + 1), dtype=torch.float32, device=packed.device)
+    dist.all_gather_into_tensor(flat, packed, group=group)
+    gathered = flat.view(world, rows, head_dim + 1)
+    g_o = gathered[:, :, :head_dim].contiguous()
+    g_lse = gathered[:, :, head_dim].contiguous()
+    merge = _merge_partials_cuda if _merge is None else _merge
+    return merge(g_o, g_lse, query.dtype).reshape(batch, q_heads, head_dim)

@@ -1,0 +1,84 @@
+"""The C-ABI shared library loads on a machine without a GPU and exports every symbol the header declares."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "fa_b200.h")
+
+
+def declared_symbols():
+    text = open(HEADER).read()
+    return re.findall(r"^FA_API\s+[\w\s\*]+?\b(fa_\w+)\s*\(", text, flags=re.M)
+
+
+def test_header_and_binding_agree():
+    from fa_b200 import _lib
+
+    names = declared_symbols()
+    assert len(names) >= 13
+    assert sorted(names) == sorted(_lib.SYMBOLS)
+
+
+def test_library_loads_and_exports_every_symbol():
+    from fa_b200 import _lib
+
+    assert os.path.exists(_lib.LIB_PATH), "build with: python flash-attention-rdna3_b200/build.py"
+    lib = ctypes.CDLL(_lib.LIB_PATH)
+    for name in declared_symbols():
+        assert hasattr(lib, name), name
+    assert _lib.load().fa_abi_version() == 1
+
+
+def test_struct_sizes_match_the_header():
+    """Compile a tiny C program against the header and compare sizeof with the ctypes mirrors."""
+    import subprocess
+    import tempfile
+
+    from fa_b200 import _lib
+
+    src = ('#include "fa_b200.h"\n#include <stdio.h>\nint main(void){printf("%zu %zu %zu %zu %zu\\n",'
+           "sizeof(fa_attn_params),sizeof(fa_decode_params),sizeof(fa_combine_params),sizeof(fa_paged_params),"
+           "sizeof(fa_tiny_params));return 0;}\n")
+    with tempfile.TemporaryDirectory() as d:
+        c = os.path.join(d, "sz.c")
+        open(c, "w").write(src)
+        exe = os.path.join(d, "sz")
+        subprocess.run(["gcc", "-I", os.path.join(ROOT, "include"), c, "-o", exe], check=True)
+        sizes = [int(x) for x in subprocess.run([exe], capture_output=True, text=True, check=True).stdout.split()]
+    mirrors = [_lib.AttnParams, _lib.DecodeParams, _lib.CombineParams, _lib.PagedParams, _lib.TinyParams]
+    assert sizes == [ctypes.sizeof(m) for m in mirrors]
+
+
+def test_argument_errors_are_reported_without_a_gpu():
+    from fa_b200 import _lib
+
+    lib = _lib.load()
+    p = _lib.AttnParams()
+    assert lib.fa_fwd(ctypes.byref(p), None) == -1          # FA_ERR_INVALID_ARGUMENT, nothing launched
+    assert b"positive" in lib.fa_last_error_string() or b"dtype" in lib.fa_last_error_string()
+    assert lib.fa_fwd(None, None) == -1
+    d = _lib.DecodeParams()
+    assert lib.fa_decode_splitk(ctypes.byref(d), None) == -1
+    t = _lib.TinyParams()
+    assert lib.fa_tiny_fwd(ctypes.byref(t), None) == -1
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    from fa_b200 import _lib
+
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "nope.so"))
+    with pytest.raises(RuntimeError, match="no fallback"):
+        _lib.load()
+
+
+def test_product_does_not_import_the_oracle():
+    pkg = os.path.join(ROOT, "flash-attention-rdna3_b200")
+    for dirpath, _, files in os.walk(pkg):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".h")):
+                text = open(os.path.join(dirpath, f)).read()
+                assert "oracle" not in text.replace("forced-split oracle", ""), os.path.join(dirpath, f)
