@@ -47,8 +47,37 @@ struct FwdArgs {
   int* status;
 };
 
+// Optional cycle accounting for kernel tuning (compiled only with -DFA_PROF): per CTA and role, cycles spent in
+// each phase, read back through fa_debug_read_prof().
+#ifdef FA_PROF
+__device__ long long g_prof[4096 * 4 * 8];
+#define PROF_DECL long long prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long prof_t = clock64(); (void)prof_t
+#define PROF_MARK(slot) do { long long now_ = clock64(); prof_acc[slot] += now_ - prof_t; prof_t = now_; } while (0)
+#define PROF_FLUSH(role, cond) do { if (cond) { const int cta_ = blockIdx.x * gridDim.y + blockIdx.y; \
+    if (cta_ < 4096) for (int s_ = 0; s_ < 8; ++s_) g_prof[(cta_ * 4 + (role)) * 8 + s_] = prof_acc[s_]; } } while (0)
+#else
+#define PROF_DECL
+#define PROF_MARK(slot)
+#define PROF_FLUSH(role, cond)
+#endif
+
 __device__ __forceinline__ void report_timeout(int* status, int code) {
   if (status != nullptr) atomicCAS(status, 0, code);
+}
+
+// Multiplies this thread's row of the O accumulator (D fp32 columns in TMEM) by alpha.
+template <int D>
+__device__ __forceinline__ void rescale_o(uint32_t tO, float alpha) {
+#pragma unroll
+  for (int c = 0; c < D / 32; ++c) {
+    uint32_t o[32];
+    tmem_ld32(tO + c * 32, o);
+    tc_wait_ld();
+#pragma unroll
+    for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+    tmem_st32(tO + c * 32, o);
+  }
+  tc_wait_st();
 }
 
 template <typename T, int D, bool kMods>
@@ -68,8 +97,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
   __shared__ uint32_t tmem_base_s;
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
-  const int pair = a.num_pairs - 1 - blockIdx.x;  // longest (causal) work first
-  const int b = blockIdx.y / a.heads_q, h = blockIdx.y % a.heads_q;
+  const int pair = a.num_pairs - 1 - blockIdx.y;  // blocks are issued x-fastest: all the long (causal) tiles go first
+  const int b = blockIdx.x / a.heads_q, h = blockIdx.x % a.heads_q;
   const int hk = h / (a.heads_q / a.heads_kv);
 
   int q_start = 0, k_start = 0, Sq = a.seqlen_q, Sk = a.seqlen_k;
@@ -192,6 +221,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       constexpr uint32_t idesc_pv = make_idesc(DType<T>::kFormat, 128, D, 0, 1);
       const uint32_t sq_addr = smem_u32(sQ), skv_addr = smem_u32(sKV);
       bool ok = true;
+      PROF_DECL;
       auto slot_addr = [&](int n) { return skv_addr + (n % kSlots) * kTileBytes; };
       auto wait_full = [&](int n) {
         if (!mbar_wait(&kv_full[n % kSlots], (n / kSlots) & 1)) {
@@ -239,6 +269,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       for (int j = jlo; j < jhi && ok; ++j) {
         const int nk = 2 * (j - jlo), nv = nk + 1, nk_next = nk + 2;
         const bool have_next = j + 1 < jhi;
+        PROF_MARK(2);
         wait_full(nv);
         if (!ok) break;
         if (have_next) {
@@ -246,14 +277,17 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
           if (!ok) break;
         }
         tc_fence_after_sync();
+        PROF_MARK(0);
 #pragma unroll
         for (int t = 0; t < 2; ++t) {
           if (in_range(t, j)) {
+            PROF_MARK(2);
             if (!mbar_wait(&p_full[t], (j - lo[t]) & 1)) {
               report_timeout(a.status, 104);
               ok = false;
               break;
             }
+            PROF_MARK(1);
             tc_fence_after_sync();
             issue_pv(t, nv, j == lo[t]);
           }
@@ -262,6 +296,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
           if (t == 1 && have_next) tc_commit(&kv_empty[nk_next % kSlots]);
         }
       }
+      PROF_MARK(2);
+      PROF_FLUSH(2, true);
     }
   } else if (warp < 8) {
     // ------------------------------------------------------------------ softmax groups
@@ -274,12 +310,18 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
     const uint32_t tO = tmem_base + lane_addr + 256 + t * D;
     const int off = Sk - Sq;
 
-    if (active[t]) {
+    // scalars instead of runtime-indexed arrays (those would live in local memory)
+    const bool active_t = t ? active[1] : active[0];
+    const int lo_t = t ? lo[1] : lo[0];
+    const int n_tiles = (t ? hi[1] : hi[0]) - lo_t;
+
+    if (active_t) {
       float m_used = kNegInf, l = 0.f;
       bool ok = true;
-      const int n_tiles = hi[t] - lo[t];
+      PROF_DECL;
       for (int it = 0; it < n_tiles; ++it) {
-        const int j = lo[t] + it;
+        const int j = lo_t + it;
+        PROF_MARK(7);
         bool w_ok = mbar_wait(&s_full[t], it & 1);
         if (w_ok && it > 0) w_ok = mbar_wait(&o_ready[t], (it - 1) & 1);
         if (!__all_sync(kFull, w_ok)) {
@@ -288,85 +330,141 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
           break;
         }
         tc_fence_after_sync();
-
-        uint32_t r[128];
-#pragma unroll
-        for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
-        tc_wait_ld();
+        PROF_MARK(0);
 
         const int k0 = j * 128;
         const bool tile_masked = (k0 + 128 > Sk) || (a.causal && (k0 + 127 > r0 + off)) ||
                                  (a.wl >= 0 && (k0 < r0 + 127 + off - a.wl)) ||
                                  (!a.causal && a.wr >= 0 && (k0 + 127 > r0 + off + a.wr));
-        float m_tile = kNegInf;
+        // Every mask (key bound, causal, window) keeps one interval [c_lo, c_hi] of this row's 128 columns.
+        int c_lo = 0, c_hi = 127;
+        if (tile_masked) {
+          c_hi = min(c_hi, Sk - 1 - k0);
+          if (a.causal) c_hi = min(c_hi, row + off - k0);
+          else if (a.wr >= 0) c_hi = min(c_hi, row + off + a.wr - k0);
+          if (a.wl >= 0) c_lo = max(0, row + off - a.wl - k0);
+        }
+
         if (kMods) {
+          // General path: the whole row is transformed in registers (softcap, bias, ALiBi, dropout).
+          uint32_t r[128];
+#pragma unroll
+          for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
+          tc_wait_ld();
+          PROF_MARK(1);
+          float m_tile = kNegInf;
 #pragma unroll
           for (int c = 0; c < 128; ++c) {
             float x = mods.logit(__uint_as_float(r[c]), row, k0 + c, nullptr);
-            if (tile_masked && !mods.keep(row, k0 + c)) x = kNegInf;
+            if (tile_masked && (c < c_lo || c > c_hi)) x = kNegInf;
             r[c] = __float_as_uint(x);
             m_tile = fmaxf(m_tile, x);
           }
+          PROF_MARK(2);
+          const float m_new = fmaxf(m_used, m_tile);
+          const bool grow = m_new > m_used + kRescaleThreshold;
+          if (__any_sync(kFull, grow)) {
+            const float alpha = (m_new == kNegInf) ? 1.f : exp2f(m_used - m_new);
+            l *= alpha;
+            if (it > 0) rescale_o<D>(tO, alpha);
+            m_used = m_new;
+          }
+          const float m_eff = (m_used == kNegInf) ? 0.f : m_used;
+          PROF_MARK(3);
+          float sum = 0.f;
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            uint32_t pk[32];
+#pragma unroll
+            for (int c = 0; c < 32; ++c) {
+              const int e0 = half * 64 + 2 * c;
+              float p0 = fast_exp2(__uint_as_float(r[e0]) - m_eff);
+              float p1 = fast_exp2(__uint_as_float(r[e0 + 1]) - m_eff);
+              sum += p0 + p1;
+              if (mods.dropout_p > 0.f) {
+                p0 = mods.dropout_keep(row, k0 + e0) ? p0 * mods.inv_keep : 0.f;
+                p1 = mods.dropout_keep(row, k0 + e0 + 1) ? p1 * mods.inv_keep : 0.f;
+              }
+              pk[c] = DType<T>::pack2(p0, p1);
+            }
+            tmem_st32(tS + half * 32, pk);
+          }
+          l += sum;
         } else {
-          if (tile_masked) {
+          // Fast path, two streaming passes over the S row in TMEM so that few registers stay live.
+          // Pass 1: row maximum (four independent chains of three-input max).
+          float mx[4] = {kNegInf, kNegInf, kNegInf, kNegInf};
 #pragma unroll
-            for (int c = 0; c < 128; ++c)
-              if (!mods.keep(row, k0 + c)) r[c] = __float_as_uint(kNegInf);
+          for (int half = 0; half < 2; ++half) {
+            uint32_t r[64];
+            tmem_ld32(tS + half * 64, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+            tmem_ld32(tS + half * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+            tc_wait_ld_regs(*reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+            tc_wait_ld_regs(*reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+            if (tile_masked) {
+#pragma unroll
+              for (int c = 0; c < 64; ++c)
+                if (half * 64 + c < c_lo || half * 64 + c > c_hi) r[c] = __float_as_uint(kNegInf);
+            }
+#pragma unroll
+            for (int c = 0; c < 64; c += 8) {
+#pragma unroll
+              for (int u = 0; u < 4; ++u)
+                mx[u] = fmax3(mx[u], __uint_as_float(r[c + 2 * u]), __uint_as_float(r[c + 2 * u + 1]));
+            }
           }
-#pragma unroll
-          for (int c = 0; c < 128; ++c) m_tile = fmaxf(m_tile, __uint_as_float(r[c]));
-          m_tile *= mods.scale_log2;  // scale > 0 on this path
-        }
+          const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * mods.scale_log2;  // scale > 0 here
+          PROF_MARK(2);
+          const float m_new = fmaxf(m_used, m_tile);
+          const bool grow = m_new > m_used + kRescaleThreshold;
+          if (__any_sync(kFull, grow)) {
+            const float alpha = (m_new == kNegInf) ? 1.f : exp2f(m_used - m_new);
+            l *= alpha;
+            if (it > 0) rescale_o<D>(tO, alpha);
+            m_used = m_new;
+          }
+          const float m_eff = (m_used == kNegInf) ? 0.f : m_used;
+          PROF_MARK(3);
 
-        const float m_new = fmaxf(m_used, m_tile);
-        const bool grow = m_new > m_used + kRescaleThreshold;
-        if (__any_sync(kFull, grow)) {
-          const float alpha = (m_new == kNegInf) ? 1.f : exp2f(m_used - m_new);
-          l *= alpha;
-          if (it > 0) {
+          // Pass 2: p = exp2(s*scale - m) with packed fp32x2 FMA/ADD, 32 columns at a time; the 16-bit P chunk
+          // goes to columns [16c, 16c+16), which only covers S columns this thread has already consumed.
+          const uint64_t sc2 = pack_f32x2(mods.scale_log2, mods.scale_log2);
+          const uint64_t nm2 = pack_f32x2(-m_eff, -m_eff);
+          uint64_t acc2[4] = {0ull, 0ull, 0ull, 0ull};
+          uint32_t rb[2][32];
+          tmem_ld32(tS, rb[0]);
+          tc_wait_ld_regs(rb[0]);
 #pragma unroll
-            for (int c = 0; c < D / 32; ++c) {
-              uint32_t o[32];
-              tmem_ld32(tO + c * 32, o);
-              tc_wait_ld();
+          for (int c = 0; c < 4; ++c) {
+            if (c < 3) tmem_ld32(tS + (c + 1) * 32, rb[(c + 1) & 1]);
+            uint32_t (&r)[32] = rb[c & 1];
+            if (tile_masked) {
 #pragma unroll
-              for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
-              tmem_st32(tO + c * 32, o);
+              for (int e = 0; e < 32; ++e)
+                if (c * 32 + e < c_lo || c * 32 + e > c_hi) r[e] = __float_as_uint(kNegInf);
             }
-            tc_wait_st();
+            uint32_t pk[16];
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+              const uint64_t x2 = fma_f32x2(pack_u32x2(r[2 * e], r[2 * e + 1]), sc2, nm2);
+              float x0, x1;
+              unpack_f32x2(x2, &x0, &x1);
+              const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+              acc2[e & 3] = add_f32x2(acc2[e & 3], pack_f32x2(p0, p1));
+              pk[e] = DType<T>::pack2(p0, p1);
+            }
+            tmem_st16(tS + c * 16, pk);
+            if (c < 3) tc_wait_ld_regs(rb[(c + 1) & 1]);
           }
-          m_used = m_new;
+          float s0, s1;
+          unpack_f32x2(add_f32x2(add_f32x2(acc2[0], acc2[1]), add_f32x2(acc2[2], acc2[3])), &s0, &s1);
+          l += s0 + s1;
         }
-        const float m_eff = (m_used == kNegInf) ? 0.f : m_used;
-
-        float sum = 0.f;
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint32_t pk[32];
-#pragma unroll
-          for (int c = 0; c < 32; ++c) {
-            const int e0 = half * 64 + 2 * c;
-            float p0, p1;
-            if (kMods) {
-              p0 = fast_exp2(__uint_as_float(r[e0]) - m_eff);
-              p1 = fast_exp2(__uint_as_float(r[e0 + 1]) - m_eff);
-            } else {
-              p0 = fast_exp2(fmaf(__uint_as_float(r[e0]), mods.scale_log2, -m_eff));
-              p1 = fast_exp2(fmaf(__uint_as_float(r[e0 + 1]), mods.scale_log2, -m_eff));
-            }
-            sum += p0 + p1;
-            if (kMods && mods.dropout_p > 0.f) {
-              p0 = mods.dropout_keep(row, k0 + e0) ? p0 * mods.inv_keep : 0.f;
-              p1 = mods.dropout_keep(row, k0 + e0 + 1) ? p1 * mods.inv_keep : 0.f;
-            }
-            pk[c] = DType<T>::pack2(p0, p1);
-          }
-          tmem_st32(tS + half * 32, pk);
-        }
-        l += sum;
+        PROF_MARK(4);
         tc_wait_st();
         tc_fence_before_sync();
         mbar_arrive(&p_full[t]);
+        PROF_MARK(5);
       }
 
       // epilogue: O / l -> global, LSE
@@ -411,6 +509,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
           *lrow = (l == 0.f) ? kNegInf : (m_used * kLn2 + logf(l));
         }
       }
+      PROF_MARK(6);
+      PROF_FLUSH(t, lane == 0 && w4 == 0);
     }
   }
 
@@ -438,7 +538,7 @@ int launch_typed(const fa_attn_params& p, const FwdArgs& a, cudaStream_t stream)
   auto kern = fwd_kernel<T, D, kMods>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "forward smem opt-in failed: %s", cudaGetErrorString(e));
-  dim3 grid(a.num_pairs, p.batch * p.heads_q);
+  dim3 grid(p.batch * p.heads_q, a.num_pairs);
   kern<<<grid, kFwdThreads, smem, stream>>>(mq, mk, mv, a);
   e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "forward launch failed: %s", cudaGetErrorString(e));
@@ -446,6 +546,12 @@ int launch_typed(const fa_attn_params& p, const FwdArgs& a, cudaStream_t stream)
 }
 
 }  // namespace
+
+#ifdef FA_PROF
+extern "C" __attribute__((visibility("default"))) int fa_debug_read_prof(long long* host, int count) {
+  return (int)cudaMemcpyFromSymbol(host, g_prof, sizeof(long long) * count);
+}
+#endif
 
 bool fwd_tcgen05_supported(const fa_attn_params& p) {
   if (p.dtype != FA_F16 && p.dtype != FA_BF16) return false;
