@@ -1,23 +1,25 @@
 // FlashAttention-2 backward for sm_100a as two tcgen05 kernels (delta = rowsum(O*dO) is computed
-// before them). Accumulators live in tensor memory; operand tiles arrive by TMA; both kernels use
-//   warps 0-3, 4-7  two compute groups, each owning 64 of the 128 score columns of a tile
-//   warp 8          TMA producer (one lane)
-//   warp 9          MMA issuer (one lane)
+// before them). Accumulators live in tensor memory; operand tiles arrive by TMA. Both kernels walk their
+// streamed operand in steps of 64 rows and double-buffer the two score tiles of a step in TMEM, so the
+// tensor core works on step n+1 / n+2 while a compute group does the elementwise math of step n:
+//   warps 0-3   compute group 0: even steps, TMEM buffer 0   (thread = one TMEM lane = one row)
+//   warps 4-7   compute group 1: odd steps,  TMEM buffer 1
+//   warp  8     TMA producer (one lane)
+//   warp  9     MMA issuer (one lane)
 //
 // dK/dV kernel: one CTA per 128-key tile of one (batch, kv head); K and V stay in shared memory and
-// the CTA walks the query tiles of every query head of the GQA group (no atomics, fixed summation
-// order). Per query tile:
-//     S^T  = K Q^T          dP^T = V dO^T                  (M = keys, N = queries)
+// the CTA walks 64-query steps of every query head of the GQA group (no atomics, fixed summation order):
+//     S^T  = K Q^T          dP^T = V dO^T                  (M = 128 keys, N = 64 queries)
 //     P^T  = exp2(S^T*c - lse[q]) ;  dS^T = P^T * (dP^T - delta[q])      (registers; lse/delta per column)
 //     dV  += P^T dO         dK  += dS^T Q                  (A from TMEM, B = the same smem tiles, MN-major)
-// TMEM: S^T [0,128) dP^T [128,256) dK [256,256+D) dV [256+D,256+2D).
+// TMEM: S^T bufs [0,64) [64,128); dP^T bufs [128,192) [192,256); dK [256,256+D); dV [256+D,256+2D).
 //
-// dQ kernel: one CTA per 128-query tile of one (batch, head); Q and dO stay resident, K/V stream:
-//     S = Q K^T    dP = dO V^T    dS = P*(dP - delta[row])    dQ += dS K
-// TMEM: S [0,128) dP [128,256) dQ [256,256+D).
+// dQ kernel: one CTA per 128-query tile of one (batch, head); Q and dO stay resident, K/V stream in
+// 64-key steps:   S = Q K^T    dP = dO V^T    dS = P*(dP - delta[row])    dQ += dS K
+// TMEM: S bufs [0,64) [64,128); dP bufs [128,192) [192,256); dQ [256,256+D).
 //
-// The 16-bit P^T / dS^T (and dS) operands overwrite the first 32 columns of the 64-column block of
-// S^T / dP^T that the writing group itself owns, so no group overwrites data another group still reads.
+// The 16-bit P^T / dS^T (and dS) operands overwrite the first 32 columns of their own 64-column score
+// buffer, 16 columns at a time, only over columns the writing thread has already consumed.
 //
 // Math follows fa_rdna3/kernels/_common.py:347-508 and fa_rdna3/kernels/backward.py:56-322 (varlen:
 // fa_rdna3/kernels/varlen.py:193-421): P recomputed from LSE, rows with LSE = -inf contribute nothing,
@@ -31,6 +33,7 @@ namespace fa {
 namespace {
 
 constexpr int kBwdThreads = 320;
+constexpr int kStages = 4;
 constexpr uint32_t kFull = 0xffffffffu;
 
 struct BwdArgs {
@@ -55,7 +58,7 @@ struct BwdArgs {
   int causal, wl, wr;
   float dropout_p;
   uint64_t seed;
-  int num_tiles_x;
+  int num_tiles;
   int* status;
 };
 
@@ -88,33 +91,28 @@ __device__ __forceinline__ ScoreMods make_mods(const BwdArgs& a, int b, int h, i
   return m;
 }
 
-// True when some (query, key) pair of the tile rows [r0, r0+127] x keys [k0, k0+127] may be masked.
-__device__ __forceinline__ bool tile_needs_mask(const ScoreMods& m, int r0, int k0) {
+// True when some pair of query rows [r0, r0+nr) x keys [k0, k0+nk) may be masked by bounds, causal or window.
+__device__ __forceinline__ bool block_needs_mask(const ScoreMods& m, int r0, int nr, int k0, int nk) {
   const int off = m.seqlen_k - m.seqlen_q;
-  return (k0 + 128 > m.seqlen_k) || (r0 + 128 > m.seqlen_q) || (m.causal && (k0 + 127 > r0 + off)) ||
-         (m.window_left >= 0 && (k0 < r0 + 127 + off - m.window_left)) ||
-         (!m.causal && m.window_right >= 0 && (k0 + 127 > r0 + off + m.window_right));
+  return (k0 + nk > m.seqlen_k) || (m.causal && (k0 + nk - 1 > r0 + off)) ||
+         (m.window_left >= 0 && (k0 < r0 + nr - 1 + off - m.window_left)) ||
+         (!m.causal && m.window_right >= 0 && (k0 + nk - 1 > r0 + off + m.window_right));
 }
 
-// One score element of the backward pass. lse2 = lse*log2(e), or +inf for rows that contribute nothing.
-template <bool kMods>
-__device__ __forceinline__ void bwd_element(const ScoreMods& m, bool masked_tile, float raw_s, float raw_dp, float lse2,
-                                            float delta, int i, int j, float* p_drop, float* ds) {
-  float p, t = 0.f;
-  if (kMods) {
-    p = fast_exp2(m.logit(raw_s, i, j, &t) - lse2);
-  } else {
-    p = fast_exp2(fmaf(raw_s, m.scale_log2, -lse2));
-  }
-  if (masked_tile && !m.keep(i, j)) p = 0.f;
+// General (slow) element: softcap / bias / ALiBi / dropout. nlse2 = -lse*log2(e) (or -inf), ndelta = -delta.
+__device__ __forceinline__ void bwd_element_mods(const ScoreMods& m, bool inside, float raw_s, float raw_dp, float nlse2,
+                                                 float ndelta, int i, int j, float* p_drop, float* ds) {
+  float t = 0.f;
+  float p = fast_exp2(m.logit(raw_s, i, j, &t) + nlse2);
+  if (!inside) p = 0.f;
   float dp = raw_dp, pd = p;
-  if (kMods && m.dropout_p > 0.f) {
+  if (m.dropout_p > 0.f) {
     const bool kd = m.dropout_keep(i, j);
     pd = kd ? p * m.inv_keep : 0.f;
     dp = kd ? dp * m.inv_keep : 0.f;
   }
-  float d = p * (dp - delta);
-  if (kMods && m.cap_log2 > 0.f) d *= (1.f - t * t);
+  float d = p * (dp + ndelta);
+  if (m.cap_log2 > 0.f) d *= (1.f - t * t);
   *p_drop = pd;
   *ds = d;
 }
@@ -133,8 +131,8 @@ __device__ __forceinline__ void store_row_slice(T* dst, const uint32_t (&o)[32],
   }
 }
 
-__device__ __forceinline__ void compute_group_sync() {
-  asm volatile("bar.sync 1, 256;" ::: "memory");  // the eight compute warps only
+__device__ __forceinline__ void group_sync(int wg) {
+  asm volatile("bar.sync %0, 128;" ::"r"(1 + wg) : "memory");  // the four warps of one compute group
 }
 
 // =============================================================================================
@@ -142,25 +140,25 @@ __device__ __forceinline__ void compute_group_sync() {
 // =============================================================================================
 template <typename T, int D, bool kMods>
 __global__ void __launch_bounds__(kBwdThreads, 1)
-bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
+bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q64, const __grid_constant__ CUtensorMap map_k,
+                const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do64,
                 const BwdArgs a) {
   constexpr int kChunks = D / 64;
-  constexpr int kTileBytes = kChunks * 16384;
-  constexpr int kStages = 2;
+  constexpr int kTileBytes = kChunks * 16384;  // resident 128-row tile
+  constexpr int kStepBytes = kChunks * 8192;   // streamed 64-row tile
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sK = smem;
   uint8_t* sV = smem + kTileBytes;
-  uint8_t* sQdO = smem + 2 * kTileBytes;  // [stage][Q | dO]
-  __shared__ uint64_t kv_full, qdo_full[kStages], qdo_empty[kStages], s_full, p_full, acc_done;
+  uint8_t* sRing = smem + 2 * kTileBytes;  // [stage][Q step | dO step]
+  __shared__ uint64_t kv_full, qdo_full[kStages], qdo_empty[kStages], s_full[2], p_full[2], acc_done;
   __shared__ uint32_t tmem_base_s;
-  __shared__ float lse_s[2][128], delta_s[2][128];
+  __shared__ __align__(16) float nlse_s[2][2][64], ndelta_s[2][2][64];  // [group][parity][query]
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
-  const int ktile = blockIdx.x;
-  const int b = blockIdx.y / a.heads_kv, hk = blockIdx.y % a.heads_kv;
+  const int ktile = blockIdx.y;
+  const int b = blockIdx.x / a.heads_kv, hk = blockIdx.x % a.heads_kv;
   const int group = a.heads_q / a.heads_kv;
 
   int q_start = 0, k_start = 0, Sq = a.seqlen_q, Sk = a.seqlen_k;
@@ -172,20 +170,23 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   if (k0 >= Sk) return;
   const int tb = a.varlen ? 0 : b;
 
-  // query-tile range; the mask geometry does not depend on the head
+  // 64-query steps that can see this key tile; the mask geometry does not depend on the head
   ScoreMods mods = make_mods(a, b, hk * group, Sq, Sk);
   int ilo, ihi;
   query_range_for_keys(mods, k0, min(k0 + 127, Sk - 1), &ilo, &ihi);
-  int tlo = ilo / 128, thi = (ihi + 127) / 128;
-  if (thi <= tlo) tlo = thi = 0;
-  const int tiles_per_head = thi - tlo;
-  const int n_total = tiles_per_head * group;
+  int slo = ilo / 64, shi = (ihi + 63) / 64;
+  if (shi <= slo) slo = shi = 0;
+  const int steps_per_head = shi - slo;
+  const int n_total = steps_per_head * group;
 
   if (tid == 0) {
     mbar_init(&kv_full, 1);
-    mbar_init(&s_full, 1);
-    mbar_init(&p_full, 256);
     mbar_init(&acc_done, 1);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s_full[i], 1);
+      mbar_init(&p_full[i], 128);
+    }
 #pragma unroll
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&qdo_full[s], 1);
@@ -205,8 +206,8 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 
   if (warp == 8) {
     if (lane == 0 && n_total > 0) {
-      tma_prefetch_desc(&map_q);
-      tma_prefetch_desc(&map_do);
+      tma_prefetch_desc(&map_q64);
+      tma_prefetch_desc(&map_do64);
       mbar_arrive_expect_tx(&kv_full, 2 * kTileBytes);
 #pragma unroll
       for (int c = 0; c < kChunks; ++c) {
@@ -219,125 +220,168 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           report_timeout(a.status, 201);
           break;
         }
-        const int h = hk * group + n / tiles_per_head;
-        const int row = q_start + (tlo + n % tiles_per_head) * 128;
-        uint8_t* dst = sQdO + stage * 2 * kTileBytes;
-        mbar_arrive_expect_tx(&qdo_full[stage], 2 * kTileBytes);
+        const int h = hk * group + n / steps_per_head;
+        const int row = q_start + (slo + n % steps_per_head) * 64;
+        uint8_t* dst = sRing + stage * 2 * kStepBytes;
+        mbar_arrive_expect_tx(&qdo_full[stage], 2 * kStepBytes);
 #pragma unroll
         for (int c = 0; c < kChunks; ++c) {
-          tma_load_4d(dst + c * 16384, &map_q, &qdo_full[stage], c * 64, row, h, tb);
-          tma_load_4d(dst + kTileBytes + c * 16384, &map_do, &qdo_full[stage], c * 64, row, h, tb);
+          tma_load_4d(dst + c * 8192, &map_q64, &qdo_full[stage], c * 64, row, h, tb);
+          tma_load_4d(dst + kStepBytes + c * 8192, &map_do64, &qdo_full[stage], c * 64, row, h, tb);
         }
       }
     }
   } else if (warp == 9) {
     if (lane == 0 && n_total > 0) {
-      constexpr uint32_t idesc_s = make_idesc(DType<T>::kFormat, 128, 128, 0, 0);
+      constexpr uint32_t idesc_s = make_idesc(DType<T>::kFormat, 128, 64, 0, 0);
       constexpr uint32_t idesc_acc = make_idesc(DType<T>::kFormat, 128, D, 0, 1);
-      const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), qdo_addr = smem_u32(sQdO);
+      const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), ring_addr = smem_u32(sRing);
       bool ok = mbar_wait(&kv_full, 0);
       if (!ok) report_timeout(a.status, 202);
-      for (int n = 0; n < n_total && ok; ++n) {
-        const int stage = n % kStages;
+
+      auto issue_scores = [&](int n) {  // S^T and dP^T of step n into buffer n & 1
+        const int stage = n % kStages, buf = n & 1;
         if (!mbar_wait(&qdo_full[stage], (n / kStages) & 1)) {
           report_timeout(a.status, 203);
-          break;
+          ok = false;
+          return;
         }
         tc_fence_after_sync();
-        const uint32_t q_addr = qdo_addr + stage * 2 * kTileBytes, do_addr = q_addr + kTileBytes;
+        const uint32_t q_addr = ring_addr + stage * 2 * kStepBytes, do_addr = q_addr + kStepBytes;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk / 4) * 16384 + (kk % 4) * 32;
-          mma_ss(tmem_base + kColS, make_smem_desc(k_addr + off, 16, 1024), make_smem_desc(q_addr + off, 16, 1024),
-                 idesc_s, kk > 0);
+          const uint32_t offa = (kk / 4) * 16384 + (kk % 4) * 32, offb = (kk / 4) * 8192 + (kk % 4) * 32;
+          mma_ss(tmem_base + kColS + buf * 64, make_smem_desc(k_addr + offa, 16, 1024),
+                 make_smem_desc(q_addr + offb, 16, 1024), idesc_s, kk > 0);
         }
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk / 4) * 16384 + (kk % 4) * 32;
-          mma_ss(tmem_base + kColDP, make_smem_desc(v_addr + off, 16, 1024), make_smem_desc(do_addr + off, 16, 1024),
-                 idesc_s, kk > 0);
+          const uint32_t offa = (kk / 4) * 16384 + (kk % 4) * 32, offb = (kk / 4) * 8192 + (kk % 4) * 32;
+          mma_ss(tmem_base + kColDP + buf * 64, make_smem_desc(v_addr + offa, 16, 1024),
+                 make_smem_desc(do_addr + offb, 16, 1024), idesc_s, kk > 0);
         }
-        tc_commit(&s_full);
-        if (!mbar_wait(&p_full, n & 1)) {
+        tc_commit(&s_full[buf]);
+      };
+
+      if (ok) issue_scores(0);
+      if (ok && n_total > 1) issue_scores(1);
+      for (int n = 0; n < n_total && ok; ++n) {
+        const int stage = n % kStages, buf = n & 1;
+        if (!mbar_wait(&p_full[buf], (n >> 1) & 1)) {
           report_timeout(a.status, 204);
           break;
         }
         tc_fence_after_sync();
+        const uint32_t q_addr = ring_addr + stage * 2 * kStepBytes, do_addr = q_addr + kStepBytes;
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {  // 16 queries per step
-          const uint32_t a_col = (kk / 4) * 64 + (kk % 4) * 8;
-          mma_ts(tmem_base + kColDV, tmem_base + kColS + a_col, make_smem_desc(do_addr + kk * 2048, 16384, 1024),
-                 idesc_acc, !(n == 0 && kk == 0));
-        }
+        for (int kk = 0; kk < 4; ++kk)  // 16 queries per instruction
+          mma_ts(tmem_base + kColDV, tmem_base + kColS + buf * 64 + kk * 8,
+                 make_smem_desc(do_addr + kk * 2048, 8192, 1024), idesc_acc, !(n == 0 && kk == 0));
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t a_col = (kk / 4) * 64 + (kk % 4) * 8;
-          mma_ts(tmem_base + kColDK, tmem_base + kColDP + a_col, make_smem_desc(q_addr + kk * 2048, 16384, 1024),
-                 idesc_acc, !(n == 0 && kk == 0));
-        }
+        for (int kk = 0; kk < 4; ++kk)
+          mma_ts(tmem_base + kColDK, tmem_base + kColDP + buf * 64 + kk * 8,
+                 make_smem_desc(q_addr + kk * 2048, 8192, 1024), idesc_acc, !(n == 0 && kk == 0));
         tc_commit(&qdo_empty[stage]);
-        if (n == n_total - 1) tc_commit(&acc_done);
+        if (n + 2 < n_total) issue_scores(n + 2);
       }
+      if (ok) tc_commit(&acc_done);
     }
   } else {
     const int wg = warp / 4, w4 = warp % 4;
-    const int ctid = tid;  // 0..255 among compute threads
+    const int gtid = tid - wg * 128;  // 0..127 inside the group
     const int key_row = w4 * 32 + lane;
     const int j = k0 + key_row;
     const uint32_t lane_addr = static_cast<uint32_t>(w4 * 32) << 16;
     const uint32_t tS = tmem_base + lane_addr + kColS + wg * 64;
     const uint32_t tDP = tmem_base + lane_addr + kColDP + wg * 64;
+    const int off = Sk - Sq;
+    const int64_t bo = a.varlen ? 0 : (int64_t)b;
     bool ok = true;
 
-    for (int n = 0; n < n_total; ++n) {
-      const int h = hk * group + n / tiles_per_head;
-      const int q0 = (tlo + n % tiles_per_head) * 128;
-      if (n % tiles_per_head == 0) mods = make_mods(a, b, h, Sq, Sk);
-      // stage this tile's per-query LSE (log2 domain; +inf = contributes nothing) and delta
-      if (ctid < 128) {
-        const int i = q0 + ctid;
-        float l2 = INFINITY, dl = 0.f;
+    for (int n = wg; n < n_total; n += 2) {
+      const int h = hk * group + n / steps_per_head;
+      const int q0 = (slo + n % steps_per_head) * 64;
+      const int par = (n >> 1) & 1;
+      if (kMods) mods = make_mods(a, b, h, Sq, Sk);
+      // stage -lse*log2(e) (-inf = contributes nothing) and -delta of this step's 64 queries
+      if (gtid < 64) {
+        const int i = q0 + gtid;
+        float nl2 = kNegInf, nd = 0.f;
         if (i < Sq) {
-          const int64_t bo = a.varlen ? 0 : (int64_t)b;
           const float l = a.lse[bo * a.l_sb + (int64_t)h * a.l_sh + (int64_t)(q_start + i) * a.l_ss];
-          l2 = (l == kNegInf) ? INFINITY : l * kLog2e;
-          dl = a.delta[bo * a.d_sb + (int64_t)h * a.d_sh + (int64_t)(q_start + i) * a.d_ss];
+          nl2 = (l == kNegInf) ? kNegInf : -l * kLog2e;
+          nd = -a.delta[bo * a.d_sb + (int64_t)h * a.d_sh + (int64_t)(q_start + i) * a.d_ss];
         }
-        lse_s[n & 1][ctid] = l2;
-        delta_s[n & 1][ctid] = dl;
+        nlse_s[wg][par][gtid] = nl2;
+        ndelta_s[wg][par][gtid] = nd;
       }
-      compute_group_sync();
-      const bool w_ok = mbar_wait(&s_full, n & 1);
+      group_sync(wg);
+      const bool w_ok = mbar_wait(&s_full[wg], par);
       if (!__all_sync(kFull, w_ok)) {
         report_timeout(a.status, 205);
         ok = false;
         break;
       }
       tc_fence_after_sync();
-      uint32_t s[64], dp[64];
-      tmem_ld32(tS, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
-      tmem_ld32(tS + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
-      tmem_ld32(tDP, *reinterpret_cast<uint32_t(*)[32]>(&dp[0]));
-      tmem_ld32(tDP + 32, *reinterpret_cast<uint32_t(*)[32]>(&dp[32]));
-      tc_wait_ld();
-      const bool masked = tile_needs_mask(mods, q0, k0);
-      uint32_t pk[32], dsk[32];
-#pragma unroll
-      for (int c = 0; c < 32; ++c) {
-        const int col = wg * 64 + 2 * c;
-        float p0, p1, d0, d1;
-        bwd_element<kMods>(mods, masked, __uint_as_float(s[2 * c]), __uint_as_float(dp[2 * c]), lse_s[n & 1][col],
-                           delta_s[n & 1][col], q0 + col, j, &p0, &d0);
-        bwd_element<kMods>(mods, masked, __uint_as_float(s[2 * c + 1]), __uint_as_float(dp[2 * c + 1]),
-                           lse_s[n & 1][col + 1], delta_s[n & 1][col + 1], q0 + col + 1, j, &p1, &d1);
-        pk[c] = DType<T>::pack2(p0, p1);
-        dsk[c] = DType<T>::pack2(d0, d1);
+
+      // queries this key row keeps: one interval [c_lo, c_hi] of the step's 64 columns
+      const bool masked = block_needs_mask(mods, q0, 64, k0, 128);
+      int c_lo = 0, c_hi = 63;
+      if (masked) {
+        if (a.causal) c_lo = max(c_lo, j - off - q0);
+        else if (a.wr >= 0) c_lo = max(c_lo, j - off - a.wr - q0);
+        if (a.wl >= 0) c_hi = min(c_hi, j - off + a.wl - q0);
+        if (j >= Sk) c_hi = -1;
       }
-      tmem_st32(tS, pk);
-      tmem_st32(tDP, dsk);
+      const uint64_t sc2 = pack_f32x2(mods.scale_log2, mods.scale_log2);
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t s[32], dp[32];
+        tmem_ld32(tS + c * 32, s);
+        tmem_ld32(tDP + c * 32, dp);
+        tc_wait_ld_regs(s);
+        tc_wait_ld_regs(dp);
+        uint32_t pk[16], dsk[16];
+#pragma unroll
+        for (int e4 = 0; e4 < 8; ++e4) {  // four queries at a time: one 16-byte read of lse and of delta
+          const float4 nl = *reinterpret_cast<const float4*>(&nlse_s[wg][par][c * 32 + e4 * 4]);
+          const float4 nd = *reinterpret_cast<const float4*>(&ndelta_s[wg][par][c * 32 + e4 * 4]);
+          const float nls[4] = {nl.x, nl.y, nl.z, nl.w}, nds[4] = {nd.x, nd.y, nd.z, nd.w};
+#pragma unroll
+          for (int e2 = 0; e2 < 2; ++e2) {
+            const int e = e4 * 2 + e2;     // pair index inside the chunk
+            const int col = c * 32 + 2 * e;  // column inside the step
+            float p0, p1, d0, d1;
+            if (kMods) {
+              bwd_element_mods(mods, !masked || (col >= c_lo && col <= c_hi), __uint_as_float(s[2 * e]),
+                               __uint_as_float(dp[2 * e]), nls[2 * e2], nds[2 * e2], q0 + col, j, &p0, &d0);
+              bwd_element_mods(mods, !masked || (col + 1 >= c_lo && col + 1 <= c_hi), __uint_as_float(s[2 * e + 1]),
+                               __uint_as_float(dp[2 * e + 1]), nls[2 * e2 + 1], nds[2 * e2 + 1], q0 + col + 1, j, &p1,
+                               &d1);
+            } else {
+              const uint64_t x2 = fma_f32x2(pack_u32x2(s[2 * e], s[2 * e + 1]), sc2,
+                                            pack_f32x2(nls[2 * e2], nls[2 * e2 + 1]));
+              float x0, x1;
+              unpack_f32x2(x2, &x0, &x1);
+              p0 = fast_exp2(x0);
+              p1 = fast_exp2(x1);
+              if (masked) {
+                if (col < c_lo || col > c_hi) p0 = 0.f;
+                if (col + 1 < c_lo || col + 1 > c_hi) p1 = 0.f;
+              }
+              const uint64_t dd = add_f32x2(pack_u32x2(dp[2 * e], dp[2 * e + 1]), pack_f32x2(nds[2 * e2], nds[2 * e2 + 1]));
+              unpack_f32x2(mul_f32x2(pack_f32x2(p0, p1), dd), &d0, &d1);
+            }
+            pk[e] = DType<T>::pack2(p0, p1);
+            dsk[e] = DType<T>::pack2(d0, d1);
+          }
+        }
+        tmem_st16(tS + c * 16, pk);
+        tmem_st16(tDP + c * 16, dsk);
+      }
       tc_wait_st();
       tc_fence_before_sync();
-      mbar_arrive(&p_full);
+      mbar_arrive(&p_full[wg]);
     }
 
     // epilogue: group 0 writes dK (scaled), group 1 writes dV
@@ -350,7 +394,6 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     }
     if (ok) {
       tc_fence_after_sync();
-      const int64_t bo = a.varlen ? 0 : (int64_t)b;
       T* row_ptr = (wg == 0)
                        ? reinterpret_cast<T*>(a.dk) + bo * a.dk_sb + (int64_t)hk * a.dk_sh + (int64_t)(k_start + j) * a.dk_ss
                        : reinterpret_cast<T*>(a.dv) + bo * a.dv_sb + (int64_t)hk * a.dv_sh + (int64_t)(k_start + j) * a.dv_ss;
@@ -361,7 +404,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         uint32_t o[32];
         if (n_total > 0) {
           tmem_ld32(tAcc + c * 32, o);
-          tc_wait_ld();
+          tc_wait_ld_regs(o);
         } else {
 #pragma unroll
           for (int e = 0; e < 32; ++e) o[e] = 0u;
@@ -381,24 +424,24 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 // =============================================================================================
 template <typename T, int D, bool kMods>
 __global__ void __launch_bounds__(kBwdThreads, 1)
-bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-              const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
+bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k64,
+              const __grid_constant__ CUtensorMap map_v64, const __grid_constant__ CUtensorMap map_do,
               const BwdArgs a) {
   constexpr int kChunks = D / 64;
   constexpr int kTileBytes = kChunks * 16384;
-  constexpr int kStages = 2;
+  constexpr int kStepBytes = kChunks * 8192;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
   uint8_t* sdO = smem + kTileBytes;
-  uint8_t* sKV = smem + 2 * kTileBytes;  // [stage][K | V]
-  __shared__ uint64_t qdo_full, kv_full[kStages], kv_empty[kStages], s_full, ds_full, acc_done;
+  uint8_t* sRing = smem + 2 * kTileBytes;  // [stage][K step | V step]
+  __shared__ uint64_t qdo_full, kv_full[kStages], kv_empty[kStages], s_full[2], ds_full[2], acc_done;
   __shared__ uint32_t tmem_base_s;
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
-  const int qtile = a.num_tiles_x - 1 - blockIdx.x;
-  const int b = blockIdx.y / a.heads_q, h = blockIdx.y % a.heads_q;
+  const int qtile = a.num_tiles - 1 - blockIdx.y;  // longest (causal) rows first
+  const int b = blockIdx.x / a.heads_q, h = blockIdx.x % a.heads_q;
   const int hk = h / (a.heads_q / a.heads_kv);
 
   int q_start = 0, k_start = 0, Sq = a.seqlen_q, Sk = a.seqlen_k;
@@ -413,15 +456,18 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
   const ScoreMods mods = make_mods(a, b, h, Sq, Sk);
   int klo, khi;
   key_range_for_rows(mods, q0, min(q0 + 127, Sq - 1), &klo, &khi);
-  int jlo = klo / 128, jhi = (khi + 127) / 128;
-  if (jhi <= jlo) jlo = jhi = 0;
-  const int n_total = jhi - jlo;
+  int slo = klo / 64, shi = (khi + 63) / 64;
+  if (shi <= slo) slo = shi = 0;
+  const int n_total = shi - slo;
 
   if (tid == 0) {
     mbar_init(&qdo_full, 1);
-    mbar_init(&s_full, 1);
-    mbar_init(&ds_full, 256);
     mbar_init(&acc_done, 1);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s_full[i], 1);
+      mbar_init(&ds_full[i], 128);
+    }
 #pragma unroll
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&kv_full[s], 1);
@@ -441,8 +487,8 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
 
   if (warp == 8) {
     if (lane == 0 && n_total > 0) {
-      tma_prefetch_desc(&map_k);
-      tma_prefetch_desc(&map_v);
+      tma_prefetch_desc(&map_k64);
+      tma_prefetch_desc(&map_v64);
       mbar_arrive_expect_tx(&qdo_full, 2 * kTileBytes);
 #pragma unroll
       for (int c = 0; c < kChunks; ++c) {
@@ -455,58 +501,66 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
           report_timeout(a.status, 301);
           break;
         }
-        const int row = k_start + (jlo + n) * 128;
-        uint8_t* dst = sKV + stage * 2 * kTileBytes;
-        mbar_arrive_expect_tx(&kv_full[stage], 2 * kTileBytes);
+        const int row = k_start + (slo + n) * 64;
+        uint8_t* dst = sRing + stage * 2 * kStepBytes;
+        mbar_arrive_expect_tx(&kv_full[stage], 2 * kStepBytes);
 #pragma unroll
         for (int c = 0; c < kChunks; ++c) {
-          tma_load_4d(dst + c * 16384, &map_k, &kv_full[stage], c * 64, row, hk, tb);
-          tma_load_4d(dst + kTileBytes + c * 16384, &map_v, &kv_full[stage], c * 64, row, hk, tb);
+          tma_load_4d(dst + c * 8192, &map_k64, &kv_full[stage], c * 64, row, hk, tb);
+          tma_load_4d(dst + kStepBytes + c * 8192, &map_v64, &kv_full[stage], c * 64, row, hk, tb);
         }
       }
     }
   } else if (warp == 9) {
     if (lane == 0 && n_total > 0) {
-      constexpr uint32_t idesc_s = make_idesc(DType<T>::kFormat, 128, 128, 0, 0);
+      constexpr uint32_t idesc_s = make_idesc(DType<T>::kFormat, 128, 64, 0, 0);
       constexpr uint32_t idesc_acc = make_idesc(DType<T>::kFormat, 128, D, 0, 1);
-      const uint32_t q_addr = smem_u32(sQ), do_addr = smem_u32(sdO), kv_addr = smem_u32(sKV);
+      const uint32_t q_addr = smem_u32(sQ), do_addr = smem_u32(sdO), ring_addr = smem_u32(sRing);
       bool ok = mbar_wait(&qdo_full, 0);
       if (!ok) report_timeout(a.status, 302);
-      for (int n = 0; n < n_total && ok; ++n) {
-        const int stage = n % kStages;
+
+      auto issue_scores = [&](int n) {
+        const int stage = n % kStages, buf = n & 1;
         if (!mbar_wait(&kv_full[stage], (n / kStages) & 1)) {
           report_timeout(a.status, 303);
-          break;
+          ok = false;
+          return;
         }
         tc_fence_after_sync();
-        const uint32_t k_addr = kv_addr + stage * 2 * kTileBytes, v_addr = k_addr + kTileBytes;
+        const uint32_t k_addr = ring_addr + stage * 2 * kStepBytes, v_addr = k_addr + kStepBytes;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk / 4) * 16384 + (kk % 4) * 32;
-          mma_ss(tmem_base + kColS, make_smem_desc(q_addr + off, 16, 1024), make_smem_desc(k_addr + off, 16, 1024),
-                 idesc_s, kk > 0);
+          const uint32_t offa = (kk / 4) * 16384 + (kk % 4) * 32, offb = (kk / 4) * 8192 + (kk % 4) * 32;
+          mma_ss(tmem_base + kColS + buf * 64, make_smem_desc(q_addr + offa, 16, 1024),
+                 make_smem_desc(k_addr + offb, 16, 1024), idesc_s, kk > 0);
         }
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk / 4) * 16384 + (kk % 4) * 32;
-          mma_ss(tmem_base + kColDP, make_smem_desc(do_addr + off, 16, 1024), make_smem_desc(v_addr + off, 16, 1024),
-                 idesc_s, kk > 0);
+          const uint32_t offa = (kk / 4) * 16384 + (kk % 4) * 32, offb = (kk / 4) * 8192 + (kk % 4) * 32;
+          mma_ss(tmem_base + kColDP + buf * 64, make_smem_desc(do_addr + offa, 16, 1024),
+                 make_smem_desc(v_addr + offb, 16, 1024), idesc_s, kk > 0);
         }
-        tc_commit(&s_full);
-        if (!mbar_wait(&ds_full, n & 1)) {
+        tc_commit(&s_full[buf]);
+      };
+
+      if (ok) issue_scores(0);
+      if (ok && n_total > 1) issue_scores(1);
+      for (int n = 0; n < n_total && ok; ++n) {
+        const int stage = n % kStages, buf = n & 1;
+        if (!mbar_wait(&ds_full[buf], (n >> 1) & 1)) {
           report_timeout(a.status, 304);
           break;
         }
         tc_fence_after_sync();
+        const uint32_t k_addr = ring_addr + stage * 2 * kStepBytes;
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {  // 16 keys per step
-          const uint32_t a_col = (kk / 4) * 64 + (kk % 4) * 8;
-          mma_ts(tmem_base + kColDQ, tmem_base + kColS + a_col, make_smem_desc(k_addr + kk * 2048, 16384, 1024),
-                 idesc_acc, !(n == 0 && kk == 0));
-        }
+        for (int kk = 0; kk < 4; ++kk)  // 16 keys per instruction
+          mma_ts(tmem_base + kColDQ, tmem_base + kColS + buf * 64 + kk * 8,
+                 make_smem_desc(k_addr + kk * 2048, 8192, 1024), idesc_acc, !(n == 0 && kk == 0));
         tc_commit(&kv_empty[stage]);
-        if (n == n_total - 1) tc_commit(&acc_done);
+        if (n + 2 < n_total) issue_scores(n + 2);
       }
+      if (ok) tc_commit(&acc_done);
     }
   } else {
     const int wg = warp / 4, w4 = warp % 4;
@@ -516,44 +570,71 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     const uint32_t tS = tmem_base + lane_addr + kColS + wg * 64;
     const uint32_t tDP = tmem_base + lane_addr + kColDP + wg * 64;
     const int64_t bo = a.varlen ? 0 : (int64_t)b;
-    float lse2 = INFINITY, delta = 0.f;
+    const int off = Sk - Sq;
+    float nlse2 = kNegInf, ndelta = 0.f;
     if (i < Sq) {
       const float l = a.lse[bo * a.l_sb + (int64_t)h * a.l_sh + (int64_t)(q_start + i) * a.l_ss];
-      lse2 = (l == kNegInf) ? INFINITY : l * kLog2e;
-      delta = a.delta[bo * a.d_sb + (int64_t)h * a.d_sh + (int64_t)(q_start + i) * a.d_ss];
+      nlse2 = (l == kNegInf) ? kNegInf : -l * kLog2e;
+      ndelta = -a.delta[bo * a.d_sb + (int64_t)h * a.d_sh + (int64_t)(q_start + i) * a.d_ss];
     }
+    const uint64_t sc2 = pack_f32x2(mods.scale_log2, mods.scale_log2);
+    const uint64_t nl2 = pack_f32x2(nlse2, nlse2), nd2 = pack_f32x2(ndelta, ndelta);
     bool ok = true;
-    for (int n = 0; n < n_total; ++n) {
-      const int k0 = (jlo + n) * 128;
-      const bool w_ok = mbar_wait(&s_full, n & 1);
+    for (int n = wg; n < n_total; n += 2) {
+      const int ks = (slo + n) * 64;
+      const bool w_ok = mbar_wait(&s_full[wg], (n >> 1) & 1);
       if (!__all_sync(kFull, w_ok)) {
         report_timeout(a.status, 305);
         ok = false;
         break;
       }
       tc_fence_after_sync();
-      uint32_t s[64], dp[64];
-      tmem_ld32(tS, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
-      tmem_ld32(tS + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
-      tmem_ld32(tDP, *reinterpret_cast<uint32_t(*)[32]>(&dp[0]));
-      tmem_ld32(tDP + 32, *reinterpret_cast<uint32_t(*)[32]>(&dp[32]));
-      tc_wait_ld();
-      const bool masked = tile_needs_mask(mods, q0, k0);
-      uint32_t dsk[32];
-#pragma unroll
-      for (int c = 0; c < 32; ++c) {
-        const int col = k0 + wg * 64 + 2 * c;
-        float p0, p1, d0, d1;
-        bwd_element<kMods>(mods, masked, __uint_as_float(s[2 * c]), __uint_as_float(dp[2 * c]), lse2, delta, i, col, &p0,
-                           &d0);
-        bwd_element<kMods>(mods, masked, __uint_as_float(s[2 * c + 1]), __uint_as_float(dp[2 * c + 1]), lse2, delta, i,
-                           col + 1, &p1, &d1);
-        dsk[c] = DType<T>::pack2(d0, d1);
+      // keys this query row keeps: one interval [c_lo, c_hi] of the step's 64 columns
+      const bool masked = block_needs_mask(mods, q0, 128, ks, 64);
+      int c_lo = 0, c_hi = 63;
+      if (masked) {
+        c_hi = min(c_hi, Sk - 1 - ks);
+        if (a.causal) c_hi = min(c_hi, i + off - ks);
+        else if (a.wr >= 0) c_hi = min(c_hi, i + off + a.wr - ks);
+        if (a.wl >= 0) c_lo = max(0, i + off - a.wl - ks);
       }
-      tmem_st32(tS, dsk);
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t s[32], dp[32];
+        tmem_ld32(tS + c * 32, s);
+        tmem_ld32(tDP + c * 32, dp);
+        tc_wait_ld_regs(s);
+        tc_wait_ld_regs(dp);
+        uint32_t dsk[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          const int col = c * 32 + 2 * e;
+          float d0, d1;
+          if (kMods) {
+            float p0, p1;
+            bwd_element_mods(mods, !masked || (col >= c_lo && col <= c_hi), __uint_as_float(s[2 * e]),
+                             __uint_as_float(dp[2 * e]), nlse2, ndelta, i, ks + col, &p0, &d0);
+            bwd_element_mods(mods, !masked || (col + 1 >= c_lo && col + 1 <= c_hi), __uint_as_float(s[2 * e + 1]),
+                             __uint_as_float(dp[2 * e + 1]), nlse2, ndelta, i, ks + col + 1, &p1, &d1);
+          } else {
+            const uint64_t x2 = fma_f32x2(pack_u32x2(s[2 * e], s[2 * e + 1]), sc2, nl2);
+            float x0, x1;
+            unpack_f32x2(x2, &x0, &x1);
+            float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+            if (masked) {
+              if (col < c_lo || col > c_hi) p0 = 0.f;
+              if (col + 1 < c_lo || col + 1 > c_hi) p1 = 0.f;
+            }
+            const uint64_t dd = add_f32x2(pack_u32x2(dp[2 * e], dp[2 * e + 1]), nd2);
+            unpack_f32x2(mul_f32x2(pack_f32x2(p0, p1), dd), &d0, &d1);
+          }
+          dsk[e] = DType<T>::pack2(d0, d1);
+        }
+        tmem_st16(tS + c * 16, dsk);
+      }
       tc_wait_st();
       tc_fence_before_sync();
-      mbar_arrive(&ds_full);
+      mbar_arrive(&ds_full[wg]);
     }
 
     if (n_total > 0) {
@@ -566,15 +647,14 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     if (ok) {
       tc_fence_after_sync();
       T* row_ptr = reinterpret_cast<T*>(a.dq) + bo * a.dq_sb + (int64_t)h * a.dq_sh + (int64_t)(q_start + i) * a.dq_ss;
-      // each group writes half of the head dimension
-      constexpr int kSlices = D / 32 / 2;
+      constexpr int kSlices = D / 32 / 2;  // each group writes half of the head dimension
 #pragma unroll
       for (int cc = 0; cc < kSlices; ++cc) {
         const int c = wg * kSlices + cc;
         uint32_t o[32];
         if (n_total > 0) {
           tmem_ld32(tmem_base + lane_addr + kColDQ + c * 32, o);
-          tc_wait_ld();
+          tc_wait_ld_regs(o);
         } else {
 #pragma unroll
           for (int e = 0; e < 32; ++e) o[e] = 0u;
@@ -592,37 +672,43 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
 template <typename T, int D, bool kMods>
 int launch_typed(const fa_attn_params& p, const BwdArgs& a0, int parts, cudaStream_t stream) {
   constexpr int kTileBytes = (D / 64) * 16384;
-  const int smem = 6 * kTileBytes + 1024;
-  CUtensorMap mq, mk, mv, mdo;
+  constexpr int kStepBytes = (D / 64) * 8192;
+  const int smem = 2 * kTileBytes + kStages * 2 * kStepBytes + 1024;
   const int rows_q = p.varlen ? p.total_q : p.seqlen_q;
   const int rows_k = p.varlen ? p.total_k : p.seqlen_k;
   const int nb = p.varlen ? 1 : p.batch;
-  int rc = make_tile_map(&mq, p.q, p.dtype, D, rows_q, p.heads_q, nb, p.q_strides[2], p.q_strides[1], p.q_strides[0]);
-  if (rc) return rc;
-  rc = make_tile_map(&mk, p.k, p.dtype, D, rows_k, p.heads_kv, nb, p.k_strides[2], p.k_strides[1], p.k_strides[0]);
-  if (rc) return rc;
-  rc = make_tile_map(&mv, p.v, p.dtype, D, rows_k, p.heads_kv, nb, p.v_strides[2], p.v_strides[1], p.v_strides[0]);
-  if (rc) return rc;
-  rc = make_tile_map(&mdo, p.dout, p.dtype, D, rows_q, p.heads_q, nb, p.do_strides[2], p.do_strides[1],
-                     p.do_strides[0]);
-  if (rc) return rc;
-
-  auto kdkdv = bwd_dkdv_kernel<T, D, kMods>;
-  auto kdq = bwd_dq_kernel<T, D, kMods>;
-  cudaError_t e = cudaFuncSetAttribute(kdkdv, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-  if (e == cudaSuccess) e = cudaFuncSetAttribute(kdq, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-  if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "backward smem opt-in failed: %s", cudaGetErrorString(e));
-
+  auto map_of = [&](CUtensorMap* m, const void* ptr, int rows, int heads, const int64_t* st, int box_rows) {
+    return make_tile_map(m, ptr, p.dtype, D, rows, heads, nb, st[2], st[1], st[0], box_rows);
+  };
+  cudaError_t e;
   BwdArgs a = a0;
   if (parts & FA_BWD_DKDV) {
-    a.num_tiles_x = (p.seqlen_k + 127) / 128;
-    kdkdv<<<dim3(a.num_tiles_x, p.batch * p.heads_kv), kBwdThreads, smem, stream>>>(mq, mk, mv, mdo, a);
+    CUtensorMap mq, mk, mv, mdo;
+    int rc = map_of(&mq, p.q, rows_q, p.heads_q, p.q_strides, 64);
+    if (!rc) rc = map_of(&mk, p.k, rows_k, p.heads_kv, p.k_strides, 128);
+    if (!rc) rc = map_of(&mv, p.v, rows_k, p.heads_kv, p.v_strides, 128);
+    if (!rc) rc = map_of(&mdo, p.dout, rows_q, p.heads_q, p.do_strides, 64);
+    if (rc) return rc;
+    auto kern = bwd_dkdv_kernel<T, D, kMods>;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "backward smem opt-in failed: %s", cudaGetErrorString(e));
+    a.num_tiles = (p.seqlen_k + 127) / 128;
+    kern<<<dim3(p.batch * p.heads_kv, a.num_tiles), kBwdThreads, smem, stream>>>(mq, mk, mv, mdo, a);
     e = cudaGetLastError();
     if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "dK/dV launch failed: %s", cudaGetErrorString(e));
   }
   if (parts & FA_BWD_DQ) {
-    a.num_tiles_x = (p.seqlen_q + 127) / 128;
-    kdq<<<dim3(a.num_tiles_x, p.batch * p.heads_q), kBwdThreads, smem, stream>>>(mq, mk, mv, mdo, a);
+    CUtensorMap mq, mk, mv, mdo;
+    int rc = map_of(&mq, p.q, rows_q, p.heads_q, p.q_strides, 128);
+    if (!rc) rc = map_of(&mk, p.k, rows_k, p.heads_kv, p.k_strides, 64);
+    if (!rc) rc = map_of(&mv, p.v, rows_k, p.heads_kv, p.v_strides, 64);
+    if (!rc) rc = map_of(&mdo, p.dout, rows_q, p.heads_q, p.do_strides, 128);
+    if (rc) return rc;
+    auto kern = bwd_dq_kernel<T, D, kMods>;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "backward smem opt-in failed: %s", cudaGetErrorString(e));
+    a.num_tiles = (p.seqlen_q + 127) / 128;
+    kern<<<dim3(p.batch * p.heads_q, a.num_tiles), kBwdThreads, smem, stream>>>(mq, mk, mv, mdo, a);
     e = cudaGetLastError();
     if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "dQ launch failed: %s", cudaGetErrorString(e));
   }
@@ -688,16 +774,20 @@ int launch_bwd_tcgen05(const fa_attn_params& p, int parts, cudaStream_t stream) 
   a.wr = p.window_right;
   a.dropout_p = p.dropout_p;
   a.seed = p.dropout_seed;
-  a.num_tiles_x = 0;
+  a.num_tiles = 0;
   a.status = p.status;
   const bool mods = p.softcap > 0.f || p.bias != nullptr || p.alibi_slopes != nullptr || p.dropout_p > 0.f;
   const bool f16 = p.dtype == FA_F16;
   if (p.head_dim == 128) {
-    if (f16) return mods ? launch_typed<__half, 128, true>(p, a, parts, stream) : launch_typed<__half, 128, false>(p, a, parts, stream);
+    if (f16)
+      return mods ? launch_typed<__half, 128, true>(p, a, parts, stream)
+                  : launch_typed<__half, 128, false>(p, a, parts, stream);
     return mods ? launch_typed<__nv_bfloat16, 128, true>(p, a, parts, stream)
                 : launch_typed<__nv_bfloat16, 128, false>(p, a, parts, stream);
   }
-  if (f16) return mods ? launch_typed<__half, 64, true>(p, a, parts, stream) : launch_typed<__half, 64, false>(p, a, parts, stream);
+  if (f16)
+    return mods ? launch_typed<__half, 64, true>(p, a, parts, stream)
+                : launch_typed<__half, 64, false>(p, a, parts, stream);
   return mods ? launch_typed<__nv_bfloat16, 64, true>(p, a, parts, stream)
               : launch_typed<__nv_bfloat16, 64, false>(p, a, parts, stream);
 }

@@ -114,6 +114,34 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) simt_delta_kernel(const f
   if (lane == 0) P.delta[s.delta_off + (int64_t)i * s.delta_row_stride] = acc;
 }
 
+// Same, for 16-bit rows of 64 or 128 contiguous elements: D/8 lanes cover one row with 16-byte loads,
+// so a warp reduces 4 (D=64) or 2 (D=128) rows at a time. HBM-bound: reads O and dO once.
+template <typename T, int D>
+__global__ void __launch_bounds__(256) delta_vec_kernel(const fa_attn_params P) {
+  constexpr int LPR = D / 8;         // lanes per row
+  constexpr int RPW = 32 / LPR;      // rows per warp
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int i = (blockIdx.x * 8 + warp) * RPW + lane / LPR;
+  const int b = blockIdx.y / P.heads_q, h = blockIdx.y % P.heads_q;
+  SeqView s;
+  make_view(P, b, h, &s);
+  float acc = 0.f;
+  if (i < s.seqlen_q) {
+    const T* o = reinterpret_cast<const T*>(P.out) + s.o_off + (int64_t)i * P.o_strides[2] + (lane % LPR) * 8;
+    const T* d = reinterpret_cast<const T*>(P.dout) + s.do_off + (int64_t)i * P.do_strides[2] + (lane % LPR) * 8;
+    const uint4 ov = *reinterpret_cast<const uint4*>(o), dv = *reinterpret_cast<const uint4*>(d);
+    const uint32_t ow[4] = {ov.x, ov.y, ov.z, ov.w}, dw[4] = {dv.x, dv.y, dv.z, dv.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 a = DType<T>::unpack2(ow[e]), c = DType<T>::unpack2(dw[e]);
+      acc += a.x * c.x + a.y * c.y;
+    }
+  }
+#pragma unroll
+  for (int o = LPR / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (i < s.seqlen_q && lane % LPR == 0) P.delta[s.delta_off + (int64_t)i * s.delta_row_stride] = acc;
+}
+
 // ---------------------------------------------------------------------------------------------
 // forward
 // ---------------------------------------------------------------------------------------------
@@ -342,9 +370,28 @@ int check_launch(const char* what) {
   return 0;
 }
 
+template <typename T, int D>
+int launch_delta_vec(const fa_attn_params& p, cudaStream_t stream) {
+  constexpr int rows_per_block = 8 * (32 / (D / 8));
+  dim3 grid((p.seqlen_q + rows_per_block - 1) / rows_per_block, p.batch * p.heads_q);
+  delta_vec_kernel<T, D><<<grid, 256, 0, stream>>>(p);
+  return check_launch("delta");
+}
+
+bool rows_vectorisable(const void* ptr, const int64_t st[4]) {
+  return st[3] == 1 && (reinterpret_cast<uintptr_t>(ptr) & 15) == 0 && st[0] % 8 == 0 && st[1] % 8 == 0 && st[2] % 8 == 0;
+}
+
 }  // namespace
 
 int launch_bwd_delta(const fa_attn_params& p, cudaStream_t stream) {
+  if ((p.dtype == FA_F16 || p.dtype == FA_BF16) && (p.head_dim == 64 || p.head_dim == 128) &&
+      rows_vectorisable(p.out, p.o_strides) && rows_vectorisable(p.dout, p.do_strides)) {
+    if (p.dtype == FA_F16)
+      return p.head_dim == 64 ? launch_delta_vec<__half, 64>(p, stream) : launch_delta_vec<__half, 128>(p, stream);
+    return p.head_dim == 64 ? launch_delta_vec<__nv_bfloat16, 64>(p, stream)
+                            : launch_delta_vec<__nv_bfloat16, 128>(p, stream);
+  }
   dim3 grid((p.seqlen_q + kWarpsPerBlock - 1) / kWarpsPerBlock, p.batch * p.heads_q);
   simt_delta_kernel<<<grid, kWarpsPerBlock * 32, 0, stream>>>(p);
   return check_launch("delta");

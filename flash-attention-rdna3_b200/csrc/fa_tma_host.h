@@ -39,10 +39,11 @@ inline bool tma_operand_ok(const void* ptr, const int64_t strides[4], const int6
   return true;
 }
 
-// Tensor map over (dim, rows, heads, batch) with a box of 64 elements x 128 rows and the 128-byte
+// Tensor map over (dim, rows, heads, batch) with a box of 64 elements x box_rows rows and the 128-byte
 // swizzle; out-of-range rows read as zero. Strides are in elements.
 inline int make_tile_map(CUtensorMap* map, const void* ptr, int dtype, int head_dim, int64_t rows, int64_t heads,
-                         int64_t batch, int64_t stride_row, int64_t stride_head, int64_t stride_batch) {
+                         int64_t batch, int64_t stride_row, int64_t stride_head, int64_t stride_batch,
+                         int box_rows = 128) {
   TensorMapEncodeFn enc = tensor_map_encoder();
   if (enc == nullptr) return set_error(FA_ERR_DEVICE, "cuTensorMapEncodeTiled is not available from this driver");
   const cuuint64_t dims[4] = {(cuuint64_t)head_dim, (cuuint64_t)rows, (cuuint64_t)heads, (cuuint64_t)batch};
@@ -50,7 +51,7 @@ inline int make_tile_map(CUtensorMap* map, const void* ptr, int dtype, int head_
   const int64_t legal = (int64_t)head_dim;
   auto bytes = [&](int64_t s, int64_t n) { return (cuuint64_t)((n > 1 && s > 0) ? s : legal) * 2; };
   const cuuint64_t strides[3] = {bytes(stride_row, rows), bytes(stride_head, heads), bytes(stride_batch, batch)};
-  const cuuint32_t box[4] = {64, 128, 1, 1};
+  const cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
   const cuuint32_t estr[4] = {1, 1, 1, 1};
   const CUtensorMapDataType dt = (dtype == FA_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   CUresult r = enc(map, dt, 4, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
