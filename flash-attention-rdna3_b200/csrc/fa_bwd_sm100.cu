@@ -28,6 +28,7 @@
 #include "fa_common.cuh"
 #include "fa_sm100.cuh"
 #include "fa_tma_host.h"
+#include "fa_prof.cuh"
 
 namespace fa {
 namespace {
@@ -238,10 +239,14 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q64, const __grid_consta
       const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), ring_addr = smem_u32(sRing);
       bool ok = mbar_wait(&kv_full, 0);
       if (!ok) report_timeout(a.status, 202);
+      PROF_DECL;
 
       auto issue_scores = [&](int n) {  // S^T and dP^T of step n into buffer n & 1
         const int stage = n % kStages, buf = n & 1;
-        if (!mbar_wait(&qdo_full[stage], (n / kStages) & 1)) {
+        PROF_MARK(2);
+        const bool got = mbar_wait(&qdo_full[stage], (n / kStages) & 1);
+        PROF_MARK(0);
+        if (!got) {
           report_timeout(a.status, 203);
           ok = false;
           return;
@@ -267,7 +272,10 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q64, const __grid_consta
       if (ok && n_total > 1) issue_scores(1);
       for (int n = 0; n < n_total && ok; ++n) {
         const int stage = n % kStages, buf = n & 1;
-        if (!mbar_wait(&p_full[buf], (n >> 1) & 1)) {
+        PROF_MARK(2);
+        const bool gotp = mbar_wait(&p_full[buf], (n >> 1) & 1);
+        PROF_MARK(1);
+        if (!gotp) {
           report_timeout(a.status, 204);
           break;
         }
@@ -285,6 +293,8 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q64, const __grid_consta
         if (n + 2 < n_total) issue_scores(n + 2);
       }
       if (ok) tc_commit(&acc_done);
+      PROF_MARK(2);
+      PROF_FLUSH(2, true);
     }
   } else {
     const int wg = warp / 4, w4 = warp % 4;
@@ -297,8 +307,10 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q64, const __grid_consta
     const int off = Sk - Sq;
     const int64_t bo = a.varlen ? 0 : (int64_t)b;
     bool ok = true;
+    PROF_DECL;
 
     for (int n = wg; n < n_total; n += 2) {
+      PROF_MARK(7);
       const int h = hk * group + n / steps_per_head;
       const int q0 = (slo + n % steps_per_head) * 64;
       const int par = (n >> 1) & 1;
@@ -316,6 +328,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q64, const __grid_consta
         ndelta_s[wg][par][gtid] = nd;
       }
       group_sync(wg);
+      PROF_MARK(6);
       const bool w_ok = mbar_wait(&s_full[wg], par);
       if (!__all_sync(kFull, w_ok)) {
         report_timeout(a.status, 205);
@@ -323,6 +336,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q64, const __grid_consta
         break;
       }
       tc_fence_after_sync();
+      PROF_MARK(0);
 
       // queries this key row keeps: one interval [c_lo, c_hi] of the step's 64 columns
       const bool masked = block_needs_mask(mods, q0, 64, k0, 128);
@@ -379,10 +393,13 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q64, const __grid_consta
         tmem_st16(tS + c * 16, pk);
         tmem_st16(tDP + c * 16, dsk);
       }
+      PROF_MARK(4);
       tc_wait_st();
       tc_fence_before_sync();
       mbar_arrive(&p_full[wg]);
+      PROF_MARK(5);
     }
+    PROF_FLUSH(wg, lane == 0 && w4 == 0);
 
     // epilogue: group 0 writes dK (scaled), group 1 writes dV
     if (n_total > 0) {
@@ -716,6 +733,8 @@ int launch_typed(const fa_attn_params& p, const BwdArgs& a0, int parts, cudaStre
 }
 
 }  // namespace
+
+PROF_DEFINE_READER(fa_debug_read_prof_bwd)
 
 bool bwd_tcgen05_supported(const fa_attn_params& p) {
   if (p.dtype != FA_F16 && p.dtype != FA_BF16) return false;

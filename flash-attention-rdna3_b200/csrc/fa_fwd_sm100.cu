@@ -20,6 +20,7 @@
 #include "fa_common.cuh"
 #include "fa_sm100.cuh"
 #include "fa_tma_host.h"
+#include "fa_prof.cuh"
 
 namespace fa {
 namespace {
@@ -46,20 +47,6 @@ struct FwdArgs {
   int num_pairs;
   int* status;
 };
-
-// Optional cycle accounting for kernel tuning (compiled only with -DFA_PROF): per CTA and role, cycles spent in
-// each phase, read back through fa_debug_read_prof().
-#ifdef FA_PROF
-__device__ long long g_prof[4096 * 4 * 8];
-#define PROF_DECL long long prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long prof_t = clock64(); (void)prof_t
-#define PROF_MARK(slot) do { long long now_ = clock64(); prof_acc[slot] += now_ - prof_t; prof_t = now_; } while (0)
-#define PROF_FLUSH(role, cond) do { if (cond) { const int cta_ = blockIdx.x * gridDim.y + blockIdx.y; \
-    if (cta_ < 4096) for (int s_ = 0; s_ < 8; ++s_) g_prof[(cta_ * 4 + (role)) * 8 + s_] = prof_acc[s_]; } } while (0)
-#else
-#define PROF_DECL
-#define PROF_MARK(slot)
-#define PROF_FLUSH(role, cond)
-#endif
 
 __device__ __forceinline__ void report_timeout(int* status, int code) {
   if (status != nullptr) atomicCAS(status, 0, code);
@@ -547,11 +534,7 @@ int launch_typed(const fa_attn_params& p, const FwdArgs& a, cudaStream_t stream)
 
 }  // namespace
 
-#ifdef FA_PROF
-extern "C" __attribute__((visibility("default"))) int fa_debug_read_prof(long long* host, int count) {
-  return (int)cudaMemcpyFromSymbol(host, g_prof, sizeof(long long) * count);
-}
-#endif
+PROF_DEFINE_READER(fa_debug_read_prof)
 
 bool fwd_tcgen05_supported(const fa_attn_params& p) {
   if (p.dtype != FA_F16 && p.dtype != FA_BF16) return false;
