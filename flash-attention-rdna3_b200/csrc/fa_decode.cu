@@ -66,78 +66,31 @@ __device__ __forceinline__ void merge_workers_and_store(const float* sm, int wor
   }
 }
 
+// Streaming core shared by the dense and the paged kernel. A worker (LPK lanes) keeps, for each of R query
+// rows, the running maximum m (log2 domain), the sum l and its slice of the accumulator.
 template <typename T, int D, int R>
-__global__ void __launch_bounds__(kDecodeThreads) decode_splitk_kernel(const DecodeArgs a) {
-  constexpr int LPK = (D / 8 < 32) ? D / 8 : 32;  // lanes per key row
-  constexpr int CH = D / (8 * LPK);               // 16-byte chunks per lane per key
-  constexpr int WORKERS = kDecodeThreads / LPK;
-  constexpr int E = CH * 8;                        // elements of the head dimension per lane
-  extern __shared__ float sm[];
+struct Stream {
+  static constexpr int LPK = (D / 8 < 32) ? D / 8 : 32;  // lanes per key row
+  static constexpr int CH = D / (8 * LPK);               // 16-byte chunks per lane per key
+  static constexpr int WORKERS = kDecodeThreads / LPK;
+  static constexpr int E = CH * 8;                        // head-dim elements per lane
 
-  const fa_decode_params& p = a.p;
-  const int tid = threadIdx.x;
-  const int worker = tid / LPK, wl = tid % LPK;
-  const int split = blockIdx.x;
-  const int b = blockIdx.y / p.heads_kv, hk = blockIdx.y % p.heads_kv;
-  const int row0 = blockIdx.z * R;
-  const int rows_here = min(R, a.rows_total - row0);
-
-  const int n_start = min(split * a.keys_per_split, p.seqlen_k);
-  const int n_end = min(n_start + a.keys_per_split, p.seqlen_k);
-
-  const T* kbase = reinterpret_cast<const T*>(p.k) + (int64_t)b * p.k_strides[0] + (int64_t)hk * p.k_strides[1];
-  const T* vbase = reinterpret_cast<const T*>(p.v) + (int64_t)b * p.v_strides[0] + (int64_t)hk * p.v_strides[1];
-
-  // this lane's slice of each query row, pre-scaled into the log2 domain
   float q[R][E];
-  const float qscale = p.softmax_scale * kLog2e;
-#pragma unroll
-  for (int r = 0; r < R; ++r) {
-    const int row = row0 + r;
-    const int g = row / p.seqlen_q, sq = row % p.seqlen_q;
-    const T* qrow = reinterpret_cast<const T*>(p.q) + (int64_t)b * p.q_strides[0] +
-                    (int64_t)(hk * a.group + g) * p.q_strides[1] + (int64_t)sq * p.q_strides[2];
-#pragma unroll
-    for (int c = 0; c < CH; ++c)
-#pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        const int d = (c * LPK + wl) * 8 + e;
-        q[r][c * 8 + e] = (r < rows_here) ? DType<T>::to_float(qrow[(int64_t)d * p.q_strides[3]]) * qscale : 0.f;
-      }
-  }
-
   float m[R], l[R], acc[R][E];
+
+  __device__ __forceinline__ void init() {
 #pragma unroll
-  for (int r = 0; r < R; ++r) {
-    m[r] = kNegInf;
-    l[r] = 0.f;
+    for (int r = 0; r < R; ++r) {
+      m[r] = kNegInf;
+      l[r] = 0.f;
 #pragma unroll
-    for (int e = 0; e < E; ++e) acc[r][e] = 0.f;
+      for (int e = 0; e < E; ++e) acc[r][e] = 0.f;
+    }
   }
 
-  for (int base = n_start; base < n_end; base += WORKERS * kKeysPerIter) {
-    uint4 kraw[kKeysPerIter][CH], vraw[kKeysPerIter][CH];
-#pragma unroll
-    for (int u = 0; u < kKeysPerIter; ++u) {
-      const int key = base + u * WORKERS + worker;
-      const bool valid = key < n_end;
-#pragma unroll
-      for (int c = 0; c < CH; ++c) {
-        const int d = (c * LPK + wl) * 8;
-        kraw[u][c] = valid ? ldg_stream(kbase + (int64_t)key * p.k_strides[2] + d) : make_uint4(0, 0, 0, 0);
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < kKeysPerIter; ++u) {
-      const int key = base + u * WORKERS + worker;
-      const bool valid = key < n_end;
-#pragma unroll
-      for (int c = 0; c < CH; ++c) {
-        const int d = (c * LPK + wl) * 8;
-        vraw[u][c] = valid ? ldg_stream(vbase + (int64_t)key * p.v_strides[2] + d) : make_uint4(0, 0, 0, 0);
-      }
-    }
-
+  // Folds kKeysPerIter keys (raw 16-byte chunks of K and V, already in registers) into the state.
+  __device__ __forceinline__ void consume(const uint4 (&kraw)[kKeysPerIter][CH], const uint4 (&vraw)[kKeysPerIter][CH],
+                                          const bool (&valid)[kKeysPerIter]) {
     float s[kKeysPerIter][R];
 #pragma unroll
     for (int u = 0; u < kKeysPerIter; ++u) {
@@ -165,16 +118,15 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_splitk_kernel(const Dec
       float mt = m[r];
 #pragma unroll
       for (int u = 0; u < kKeysPerIter; ++u) {
-        const bool valid = (base + u * WORKERS + worker) < n_end;
-        if (!valid) s[u][r] = kNegInf;
+        if (!valid[u]) s[u][r] = kNegInf;
         mt = fmaxf(mt, s[u][r]);
       }
       const float ms = (mt == kNegInf) ? 0.f : mt;
-      const float alpha = exp2f(m[r] - ms);
+      const float alpha = fast_exp2(m[r] - ms);
       float sum = 0.f;
 #pragma unroll
       for (int u = 0; u < kKeysPerIter; ++u) {
-        pr[u][r] = exp2f(s[u][r] - ms);
+        pr[u][r] = fast_exp2(s[u][r] - ms);
         sum += pr[u][r];
       }
       l[r] = l[r] * alpha + sum;
@@ -194,20 +146,97 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_splitk_kernel(const Dec
     }
   }
 
-  // publish worker state
-  constexpr int kRow = D + 2;
+  // Publishes the worker state to shared memory: [worker][row][D + 2] floats.
+  __device__ __forceinline__ void publish(float* sm, int worker, int wl) const {
+    constexpr int kRow = D + 2;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      float* st = sm + (worker * R + r) * kRow;
+#pragma unroll
+      for (int c = 0; c < CH; ++c)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) st[(c * LPK + wl) * 8 + e] = acc[r][c * 8 + e];
+      if (wl == 0) {
+        st[D] = m[r];
+        st[D + 1] = l[r];
+      }
+    }
+  }
+};
+
+// Walks keys [n_start, n_end) of one CTA with register double-buffering: the loads of the next group of keys are
+// in flight while the current group is folded in. `issue(base, kraw, vraw, valid)` fills the raw chunks of the
+// keys base + u * WORKERS + worker (zeros and valid = false for keys it must not read).
+template <typename S, typename Issue>
+__device__ __forceinline__ void stream_keys(S& st, int n_start, int n_end, Issue issue) {
+  constexpr int kStride = S::WORKERS * kKeysPerIter;
+  uint4 kA[kKeysPerIter][S::CH], vA[kKeysPerIter][S::CH], kB[kKeysPerIter][S::CH], vB[kKeysPerIter][S::CH];
+  bool validA[kKeysPerIter], validB[kKeysPerIter];
+  issue(n_start, kA, vA, validA);
+  for (int base = n_start; base < n_end; base += 2 * kStride) {
+    issue(base + kStride, kB, vB, validB);
+    st.consume(kA, vA, validA);
+    issue(base + 2 * kStride, kA, vA, validA);
+    st.consume(kB, vB, validB);
+  }
+}
+
+template <typename T, int D, int R>
+__global__ void __launch_bounds__(kDecodeThreads, 2) decode_splitk_kernel(const DecodeArgs a) {
+  using S = Stream<T, D, R>;
+  constexpr int LPK = S::LPK, CH = S::CH, WORKERS = S::WORKERS;
+  extern __shared__ float sm[];
+
+  const fa_decode_params& p = a.p;
+  const int tid = threadIdx.x;
+  const int worker = tid / LPK, wl = tid % LPK;
+  const int split = blockIdx.x;
+  const int b = blockIdx.y / p.heads_kv, hk = blockIdx.y % p.heads_kv;
+  const int row0 = blockIdx.z * R;
+  const int rows_here = min(R, a.rows_total - row0);
+
+  const int n_start = min(split * a.keys_per_split, p.seqlen_k);
+  const int n_end = min(n_start + a.keys_per_split, p.seqlen_k);
+
+  const T* kbase = reinterpret_cast<const T*>(p.k) + (int64_t)b * p.k_strides[0] + (int64_t)hk * p.k_strides[1];
+  const T* vbase = reinterpret_cast<const T*>(p.v) + (int64_t)b * p.v_strides[0] + (int64_t)hk * p.v_strides[1];
+
+  S st;
+  st.init();
+  // this lane's slice of each query row, pre-scaled into the log2 domain
+  const float qscale = p.softmax_scale * kLog2e;
 #pragma unroll
   for (int r = 0; r < R; ++r) {
-    float* st = sm + (worker * R + r) * kRow;
+    const int row = row0 + r;
+    const int g = row / p.seqlen_q, sq = row % p.seqlen_q;
+    const T* qrow = reinterpret_cast<const T*>(p.q) + (int64_t)b * p.q_strides[0] +
+                    (int64_t)(hk * a.group + g) * p.q_strides[1] + (int64_t)sq * p.q_strides[2];
 #pragma unroll
     for (int c = 0; c < CH; ++c)
 #pragma unroll
-      for (int e = 0; e < 8; ++e) st[(c * LPK + wl) * 8 + e] = acc[r][c * 8 + e];
-    if (wl == 0) {
-      st[D] = m[r];
-      st[D + 1] = l[r];
-    }
+      for (int e = 0; e < 8; ++e) {
+        const int d = (c * LPK + wl) * 8 + e;
+        st.q[r][c * 8 + e] = (r < rows_here) ? DType<T>::to_float(qrow[(int64_t)d * p.q_strides[3]]) * qscale : 0.f;
+      }
   }
+
+  const int64_t ksk = p.k_strides[2], vsk = p.v_strides[2];
+  stream_keys(st, n_start, n_end,
+              [&](int base, uint4 (&kraw)[kKeysPerIter][CH], uint4 (&vraw)[kKeysPerIter][CH], bool (&valid)[kKeysPerIter]) {
+#pragma unroll
+                for (int u = 0; u < kKeysPerIter; ++u) {
+                  const int key = base + u * WORKERS + worker;
+                  valid[u] = key < n_end;
+#pragma unroll
+                  for (int c = 0; c < CH; ++c) {
+                    const int d = (c * LPK + wl) * 8;
+                    kraw[u][c] = valid[u] ? ldg_stream(kbase + (int64_t)key * ksk + d) : make_uint4(0, 0, 0, 0);
+                    vraw[u][c] = valid[u] ? ldg_stream(vbase + (int64_t)key * vsk + d) : make_uint4(0, 0, 0, 0);
+                  }
+                }
+              });
+
+  st.publish(sm, worker, wl);
   __syncthreads();
 
   float* opart_rows[R];
@@ -242,11 +271,9 @@ struct PagedArgs {
 };
 
 template <typename T, int D, int R>
-__global__ void __launch_bounds__(kDecodeThreads) decode_paged_kernel(const PagedArgs a) {
-  constexpr int LPK = (D / 8 < 32) ? D / 8 : 32;
-  constexpr int CH = D / (8 * LPK);
-  constexpr int WORKERS = kDecodeThreads / LPK;
-  constexpr int E = CH * 8;
+__global__ void __launch_bounds__(kDecodeThreads, 2) decode_paged_kernel(const PagedArgs a) {
+  using S = Stream<T, D, R>;
+  constexpr int LPK = S::LPK, CH = S::CH, WORKERS = S::WORKERS;
   extern __shared__ float sm[];
 
   const fa_paged_params& p = a.p;
@@ -267,9 +294,10 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_paged_kernel(const Page
   const int per = nlocal / p.num_splits, extra = nlocal % p.num_splits;
   const int blk_begin = split * per + min(split, extra);
   const int blk_end = blk_begin + per + (split < extra ? 1 : 0);
-  const int n_start = blk_begin * bs, n_end = blk_end * bs;   // local key indices
+  const int n_start = blk_begin * bs, n_end = blk_end * bs;  // local key indices
 
-  float q[R][E];
+  S st;
+  st.init();
   const float qscale = p.softmax_scale * kLog2e;
 #pragma unroll
   for (int r = 0; r < R; ++r) {
@@ -280,120 +308,41 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_paged_kernel(const Page
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
         const int d = (c * LPK + wl) * 8 + e;
-        q[r][c * 8 + e] = (r < rows_here) ? DType<T>::to_float(qrow[(int64_t)d * p.q_strides[2]]) * qscale : 0.f;
+        st.q[r][c * 8 + e] = (r < rows_here) ? DType<T>::to_float(qrow[(int64_t)d * p.q_strides[2]]) * qscale : 0.f;
       }
-  }
-  float m[R], l[R], acc[R][E];
-#pragma unroll
-  for (int r = 0; r < R; ++r) {
-    m[r] = kNegInf;
-    l[r] = 0.f;
-#pragma unroll
-    for (int e = 0; e < E; ++e) acc[r][e] = 0.f;
   }
 
   const T* kc = reinterpret_cast<const T*>(p.k_cache) + (int64_t)hk * p.k_strides[2];
   const T* vc = reinterpret_cast<const T*>(p.v_cache) + (int64_t)hk * p.v_strides[2];
+  const int32_t* table = p.block_table + (int64_t)b * p.bt_strides[0];
 
-  for (int base = n_start; base < n_end; base += WORKERS * kKeysPerIter) {
-    uint4 kraw[kKeysPerIter][CH], vraw[kKeysPerIter][CH];
-    bool valid[kKeysPerIter];
-    int64_t koff[kKeysPerIter], voff[kKeysPerIter];
+  stream_keys(st, n_start, n_end,
+              [&](int base, uint4 (&kraw)[kKeysPerIter][CH], uint4 (&vraw)[kKeysPerIter][CH], bool (&valid)[kKeysPerIter]) {
 #pragma unroll
-    for (int u = 0; u < kKeysPerIter; ++u) {
-      const int key = base + u * WORKERS + worker;
-      valid[u] = false;
-      koff[u] = voff[u] = 0;
-      if (key < n_end) {
-        const int lb = p.first_block + (key / bs) * p.block_step;
-        const int pos = lb * bs + key % bs;
-        const int phys = p.block_table[(int64_t)b * p.bt_strides[0] + (int64_t)lb * p.bt_strides[1]];
-        if (pos < ctx && phys >= 0 && phys < p.num_blocks) {
-          valid[u] = true;
-          koff[u] = (int64_t)phys * p.k_strides[0] + (int64_t)(key % bs) * p.k_strides[1];
-          voff[u] = (int64_t)phys * p.v_strides[0] + (int64_t)(key % bs) * p.v_strides[1];
-        }
-      }
-    }
+                for (int u = 0; u < kKeysPerIter; ++u) {
+                  const int key = base + u * WORKERS + worker;
+                  valid[u] = false;
+                  int64_t koff = 0, voff = 0;
+                  if (key < n_end) {
+                    const int lb = p.first_block + (key / bs) * p.block_step;
+                    const int within = key % bs;
+                    const int phys = table[(int64_t)lb * p.bt_strides[1]];
+                    if (lb * bs + within < ctx && phys >= 0 && phys < p.num_blocks) {
+                      valid[u] = true;
+                      koff = (int64_t)phys * p.k_strides[0] + (int64_t)within * p.k_strides[1];
+                      voff = (int64_t)phys * p.v_strides[0] + (int64_t)within * p.v_strides[1];
+                    }
+                  }
 #pragma unroll
-    for (int u = 0; u < kKeysPerIter; ++u)
-#pragma unroll
-      for (int c = 0; c < CH; ++c)
-        kraw[u][c] = valid[u] ? ldg_stream(kc + koff[u] + (c * LPK + wl) * 8) : make_uint4(0, 0, 0, 0);
-#pragma unroll
-    for (int u = 0; u < kKeysPerIter; ++u)
-#pragma unroll
-      for (int c = 0; c < CH; ++c)
-        vraw[u][c] = valid[u] ? ldg_stream(vc + voff[u] + (c * LPK + wl) * 8) : make_uint4(0, 0, 0, 0);
+                  for (int c = 0; c < CH; ++c) {
+                    const int d = (c * LPK + wl) * 8;
+                    kraw[u][c] = valid[u] ? ldg_stream(kc + koff + d) : make_uint4(0, 0, 0, 0);
+                    vraw[u][c] = valid[u] ? ldg_stream(vc + voff + d) : make_uint4(0, 0, 0, 0);
+                  }
+                }
+              });
 
-    float s[kKeysPerIter][R];
-#pragma unroll
-    for (int u = 0; u < kKeysPerIter; ++u) {
-      float kf[E];
-#pragma unroll
-      for (int c = 0; c < CH; ++c) unpack8<T>(kraw[u][c], *reinterpret_cast<float(*)[8]>(&kf[c * 8]));
-#pragma unroll
-      for (int r = 0; r < R; ++r) {
-        float d = 0.f;
-#pragma unroll
-        for (int e = 0; e < E; ++e) d += q[r][e] * kf[e];
-        s[u][r] = d;
-      }
-    }
-#pragma unroll
-    for (int o = LPK / 2; o > 0; o >>= 1)
-#pragma unroll
-      for (int u = 0; u < kKeysPerIter; ++u)
-#pragma unroll
-        for (int r = 0; r < R; ++r) s[u][r] += __shfl_xor_sync(0xffffffffu, s[u][r], o);
-
-    float pr[kKeysPerIter][R];
-#pragma unroll
-    for (int r = 0; r < R; ++r) {
-      float mt = m[r];
-#pragma unroll
-      for (int u = 0; u < kKeysPerIter; ++u) {
-        if (!valid[u]) s[u][r] = kNegInf;
-        mt = fmaxf(mt, s[u][r]);
-      }
-      const float ms = (mt == kNegInf) ? 0.f : mt;
-      const float alpha = exp2f(m[r] - ms);
-      float sum = 0.f;
-#pragma unroll
-      for (int u = 0; u < kKeysPerIter; ++u) {
-        pr[u][r] = exp2f(s[u][r] - ms);
-        sum += pr[u][r];
-      }
-      l[r] = l[r] * alpha + sum;
-#pragma unroll
-      for (int e = 0; e < E; ++e) acc[r][e] *= alpha;
-      m[r] = mt;
-    }
-#pragma unroll
-    for (int u = 0; u < kKeysPerIter; ++u) {
-      float vf[E];
-#pragma unroll
-      for (int c = 0; c < CH; ++c) unpack8<T>(vraw[u][c], *reinterpret_cast<float(*)[8]>(&vf[c * 8]));
-#pragma unroll
-      for (int r = 0; r < R; ++r)
-#pragma unroll
-        for (int e = 0; e < E; ++e) acc[r][e] += pr[u][r] * vf[e];
-    }
-  }
-
-  constexpr int kRow = D + 2;
-#pragma unroll
-  for (int r = 0; r < R; ++r) {
-    float* st = sm + (worker * R + r) * kRow;
-#pragma unroll
-    for (int c = 0; c < CH; ++c)
-#pragma unroll
-      for (int e = 0; e < 8; ++e) st[(c * LPK + wl) * 8 + e] = acc[r][c * 8 + e];
-    if (wl == 0) {
-      st[D] = m[r];
-      st[D + 1] = l[r];
-    }
-  }
+  st.publish(sm, worker, wl);
   __syncthreads();
 
   float* opart_rows[R];

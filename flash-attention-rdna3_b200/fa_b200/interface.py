@@ -78,6 +78,39 @@ def _paged_num_splits(batch, heads, block_size, max_blocks, target_programs,
     return min(cap, max(by_occupancy, by_work))
 
 
+def _fill_splits(base_ctas, max_splits, sm_count, ctas_per_sm=2):
+    """Split count for the B200 decode kernels: the grid is `base_ctas * splits` CTAs and `ctas_per_sm * sm_count`
+    of them are resident at once, so pick the split count whose last wave is fullest (fewest splits within 3 %
+    of the best fill), once there is at least one full wave."""
+    slots = ctas_per_sm * sm_count
+    max_splits = max(1, int(max_splits))
+    best, best_fill = 1, -1.0
+    for s in range(1, max_splits + 1):
+        ctas = base_ctas * s
+        fill = ctas / (_cdiv(ctas, slots) * slots)
+        if ctas < slots and s < max_splits:
+            continue                      # not even one wave yet: keep splitting
+        if fill > best_fill + 0.03:
+            best, best_fill = s, fill
+    return best
+
+
+def _decode_splits_b200(batch, kv_heads, group_rows, seqlen_k, sm_count):
+    """Key slices for split-K decode on B200: CTAs are per (batch, kv head, chunk of 4 query rows); slices are
+    at least 512 keys long and at most 64."""
+    rows_per_cta = 1 if group_rows == 1 else 2 if group_rows == 2 else 4
+    base = batch * kv_heads * _cdiv(group_rows, rows_per_cta)
+    return _fill_splits(base, min(64, max(1, seqlen_k // 512)), sm_count)
+
+
+def _paged_splits_b200(batch, kv_heads, group, block_size, max_blocks, sm_count, max_context_len=None):
+    """Splits of paged decode on B200 (at most 32, each at least 256 tokens of the longest context)."""
+    tokens = max_blocks * block_size if max_context_len is None else min(max_blocks * block_size, max_context_len)
+    rows_per_cta = 1 if group == 1 else 2 if group == 2 else 4
+    base = batch * kv_heads * _cdiv(group, rows_per_cta)
+    return _fill_splits(base, min(32, max(1, tokens // 256)), sm_count)
+
+
 def alibi_slopes(n_heads, device="cuda"):
     """Standard ALiBi per-head slopes (Press et al., 2021) as an fp32 ``(n_heads,)`` tensor
     (fa_rdna3/interface.py:136-151)."""
@@ -482,8 +515,10 @@ def flash_attention_decode(query, key, value, softmax_scale=None):
     if head_dim not in _SUPPORTED_HEAD_DIMS:
         raise ValueError(f"head_dim {head_dim} not supported; expected one of {_SUPPORTED_HEAD_DIMS}")
     softmax_scale = 1.0 / math.sqrt(head_dim) if softmax_scale is None else float(softmax_scale)
-    target_programs = 4 * torch.cuda.get_device_properties(query.device).multi_processor_count
-    num_splits = _decode_num_splits(batch, heads, seqlen_q, seqlen_k, target_programs)
+    # The reference sizes its grid per query head (_decode_num_splits above); these kernels run one CTA per kv head
+    # and slice of keys, so the count comes from the B200 grid-fill rule instead.
+    sm_count = torch.cuda.get_device_properties(query.device).multi_processor_count
+    num_splits = _decode_splits_b200(batch, key.shape[1], (heads // key.shape[1]) * seqlen_q, seqlen_k, sm_count)
     return _decode_op(query, key, value, softmax_scale, num_splits)
 
 
@@ -673,11 +708,13 @@ def flash_attention_decode_paged(query, k_cache, v_cache, block_table, context_l
     batch, q_heads, head_dim = query.shape
     block_size = k_cache.shape[1]
     softmax_scale = 1.0 / math.sqrt(head_dim) if softmax_scale is None else float(softmax_scale)
-    target_programs = 2 * torch.cuda.get_device_properties(query.device).multi_processor_count
-    selected = int(_paged_num_splits(
-        batch, q_heads, block_size, block_table.shape[1], target_programs,
-        max_context_len=None if max_context_len is None else int(max_context_len),
-        requested_splits=None if num_splits is None else int(num_splits)))
+    if num_splits is not None:
+        selected = int(num_splits)
+    else:
+        sm_count = torch.cuda.get_device_properties(query.device).multi_processor_count
+        kv_heads = k_cache.shape[2]
+        selected = _paged_splits_b200(batch, kv_heads, q_heads // kv_heads, block_size, block_table.shape[1],
+                                      sm_count, None if max_context_len is None else int(max_context_len))
     return _paged_op(query, k_cache, v_cache, block_table, context_lens, softmax_scale, selected)
 
 
