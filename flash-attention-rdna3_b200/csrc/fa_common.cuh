@@ -244,5 +244,9 @@ int launch_decode_splitk(const fa_decode_params& p, cudaStream_t stream);  // fa
 int launch_combine(const fa_combine_params& p, cudaStream_t stream);       // fa_decode.cu
 int launch_decode_paged(const fa_paged_params& p, cudaStream_t stream);    // fa_paged.cu
 int launch_tiny(const fa_tiny_params& p, cudaStream_t stream);             // fa_tiny.cu
+bool decode_tc_supported(const fa_decode_params& p);                       // fa_decode_sm100.cu
+int launch_decode_tc(const fa_decode_params& p, cudaStream_t stream);
+bool paged_tc_supported(const fa_paged_params& p);
+int launch_paged_tc(const fa_paged_params& p, cudaStream_t stream);
 
 }  // namespace fa

@@ -364,7 +364,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_paged_kernel(const P
 }
 
 // ---------------------------------------------------------------------------------------------
-// LSE merge (fa_rdna3/kernels/decode.py:80-125). One warp per output row.
+// LSE merge (fa_rdna3/kernels/decode.py:80-125).
 // ---------------------------------------------------------------------------------------------
 struct CombineArgs {
   int rows, D, splits;
@@ -376,33 +376,86 @@ struct CombineArgs {
   float* lse_out;
 };
 
-__global__ void __launch_bounds__(128) combine_kernel(const CombineArgs a) {
-  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-  const int row = blockIdx.x * 4 + warp;
-  if (row >= a.rows) return;
-  float M = kNegInf;
-  for (int s = lane; s < a.splits; s += 32)
-    M = fmaxf(M, a.lse_partial[(int64_t)s * a.lse_split_stride + (int64_t)row * a.lse_row_stride]);
-  for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
-  const float Ms = (M == kNegInf) ? 0.f : M;
-  float den = 0.f;
-  for (int s = 0; s < a.splits; ++s) {
-    const float ls = a.lse_partial[(int64_t)s * a.lse_split_stride + (int64_t)row * a.lse_row_stride];
-    den += (ls == kNegInf) ? 0.f : expf(ls - Ms);
+// One 256-thread CTA per output row. The merge weights of all partials are computed once into shared memory;
+// then eight groups of 32 lanes each take every eighth partial (independent loads, all in flight together)
+// and the group sums are added through shared memory.
+constexpr int kCombineThreads = 256;
+constexpr int kCombineMaxD = 512;
+
+__global__ void __launch_bounds__(kCombineThreads) combine_kernel(const CombineArgs a) {
+  __shared__ float w_s[kCombineThreads];
+  __shared__ float red_s[8][kCombineMaxD];
+  __shared__ float stat_s[2];
+  const int tid = threadIdx.x, grp = tid / 32, lane = tid % 32;
+  const int row = blockIdx.x;
+  const float* lse_row = a.lse_partial + (int64_t)row * a.lse_row_stride;
+  const float* o_row = a.o_partial + (int64_t)row * a.o_row_stride;
+
+  // maximum LSE over the partials (the first warp; splits beyond 256 are walked with a stride)
+  if (grp == 0) {
+    float M = kNegInf;
+    for (int s = lane; s < a.splits; s += 32) M = fmaxf(M, lse_row[(int64_t)s * a.lse_split_stride]);
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+    if (lane == 0) stat_s[0] = (M == kNegInf) ? 0.f : M;
   }
-  const float den_safe = (den == 0.f) ? 1.f : den;
+  __syncthreads();
+  const float Ms = stat_s[0];
+
+  float4 acc4[kCombineMaxD / 128];  // this lane's float4 slots: d4 = lane + 32 * k
+#pragma unroll
+  for (int k = 0; k < kCombineMaxD / 128; ++k) acc4[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+  float den = 0.f;
+  const int nd4 = a.D / 4;
+  for (int s0 = 0; s0 < a.splits; s0 += kCombineThreads) {
+    __syncthreads();
+    const int sw = s0 + tid;
+    float w = 0.f;
+    if (sw < a.splits) {
+      const float ls = lse_row[(int64_t)sw * a.lse_split_stride];
+      w = (ls == kNegInf) ? 0.f : expf(ls - Ms);
+    }
+    w_s[tid] = w;
+    __syncthreads();
+    const int n_here = min(kCombineThreads, a.splits - s0);
+    for (int s = grp; s < n_here; s += 8) {
+      const float ws = w_s[s];
+      den += ws;
+      if (ws == 0.f) continue;
+      const float4* src = reinterpret_cast<const float4*>(o_row + (int64_t)(s0 + s) * a.o_split_stride);
+#pragma unroll
+      for (int k = 0; k < kCombineMaxD / 128; ++k) {
+        const int d4 = lane + 32 * k;
+        if (d4 < nd4) {
+          const float4 v = src[d4];
+          acc4[k].x += ws * v.x;
+          acc4[k].y += ws * v.y;
+          acc4[k].z += ws * v.z;
+          acc4[k].w += ws * v.w;
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < kCombineMaxD / 128; ++k) {
+    const int d4 = lane + 32 * k;
+    if (d4 < nd4) *reinterpret_cast<float4*>(&red_s[grp][d4 * 4]) = acc4[k];
+  }
+  // every group saw a disjoint set of partials: the denominators add up across groups
+  if (lane == 0) w_s[grp] = den;
+  __syncthreads();
+  float den_all = 0.f;
+#pragma unroll
+  for (int g = 0; g < 8; ++g) den_all += w_s[g];
+  const float den_safe = (den_all == 0.f) ? 1.f : den_all;
   const int i2 = row % a.n2, i1 = (row / a.n2) % a.n1, i0 = row / (a.n2 * a.n1);
   const int64_t obase = (int64_t)i0 * a.os0 + (int64_t)i1 * a.os1 + (int64_t)i2 * a.os2;
-  for (int d = lane; d < a.D; d += 32) {
+  for (int d = tid; d < a.D; d += kCombineThreads) {
     float num = 0.f;
-    for (int s = 0; s < a.splits; ++s) {
-      const float ls = a.lse_partial[(int64_t)s * a.lse_split_stride + (int64_t)row * a.lse_row_stride];
-      const float w = (ls == kNegInf) ? 0.f : expf(ls - Ms);
-      num += w * a.o_partial[(int64_t)s * a.o_split_stride + (int64_t)row * a.o_row_stride + d];
-    }
+#pragma unroll
+    for (int g = 0; g < 8; ++g) num += red_s[g][d];
     store_from_float(a.out, obase + (int64_t)d * a.osd, a.out_dtype, num / den_safe);
   }
-  if (lane == 0 && a.lse_out != nullptr) a.lse_out[row] = (den == 0.f) ? kNegInf : (Ms + logf(den));
+  if (tid == 0 && a.lse_out != nullptr) a.lse_out[row] = (den_all == 0.f) ? kNegInf : (Ms + logf(den_all));
 }
 
 int check_launch(const char* what) {
@@ -491,7 +544,10 @@ int launch_combine_internal(int rows, int D, int splits, const float* o_partial,
                             int64_t os1, int64_t os2, int64_t osd, float* lse_out, cudaStream_t stream) {
   CombineArgs a{rows, D, splits, o_partial, o_split_stride, o_row_stride, lse_partial, lse_split_stride,
                 lse_row_stride, out, out_dtype, n1, n2, os0, os1, os2, osd, lse_out};
-  combine_kernel<<<(rows + 3) / 4, 128, 0, stream>>>(a);
+  if (D > kCombineMaxD || D % 4 || o_split_stride % 4 || o_row_stride % 4 ||
+      (reinterpret_cast<uintptr_t>(o_partial) & 15))
+    return set_error(FA_ERR_UNSUPPORTED, "combine needs head_dim <= %d, and 16-byte aligned partial rows", kCombineMaxD);
+  combine_kernel<<<rows, kCombineThreads, 0, stream>>>(a);
   return check_launch("combine");
 }
 
@@ -515,6 +571,15 @@ int launch_decode_splitk(const fa_decode_params& p, cudaStream_t stream) {
     return set_error(FA_ERR_UNSUPPORTED, "decode needs K/V with unit inner stride and 16-byte aligned rows");
   if (p.num_splits > 1 && (p.o_partial == nullptr || p.lse_partial == nullptr))
     return set_error(FA_ERR_INVALID_ARGUMENT, "decode with several splits needs partial buffers");
+  const bool tc_ok = decode_tc_supported(p);
+  if (p.force_path == FA_PATH_TCGEN05 && !tc_ok)
+    return set_error(FA_ERR_UNSUPPORTED, "tcgen05 decode needs fp16/bf16, head_dim 64/128, <= 128 rows per kv head, "
+                                         "TMA-compatible strides and an even num_splits >= 2");
+  if (tc_ok && p.force_path != FA_PATH_SIMT) {
+    set_path(FA_PATH_TCGEN05);
+    return launch_decode_tc(p, stream);
+  }
+  set_path(FA_PATH_SIMT);
   DecodeArgs a;
   a.p = p;
   a.group = p.heads_q / p.heads_kv;
@@ -545,6 +610,15 @@ int launch_decode_paged(const fa_paged_params& p, cudaStream_t stream) {
     return set_error(FA_ERR_UNSUPPORTED, "paged decode needs caches with unit inner stride and 16-byte aligned rows");
   if (p.num_splits > 1 && (p.o_partial == nullptr || p.lse_partial == nullptr))
     return set_error(FA_ERR_INVALID_ARGUMENT, "paged decode with several splits needs partial buffers");
+  const bool tc_ok = paged_tc_supported(p);
+  if (p.force_path == FA_PATH_TCGEN05 && !tc_ok)
+    return set_error(FA_ERR_UNSUPPORTED, "tcgen05 paged decode needs fp16/bf16, head_dim 64/128, block_size <= 128, "
+                                         "TMA-compatible strides and an even num_splits >= 2");
+  if (tc_ok && p.force_path != FA_PATH_SIMT) {
+    set_path(FA_PATH_TCGEN05);
+    return launch_paged_tc(p, stream);
+  }
+  set_path(FA_PATH_SIMT);
   PagedArgs a;
   a.p = p;
   a.group = p.heads_q / p.heads_kv;

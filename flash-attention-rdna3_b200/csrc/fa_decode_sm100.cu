@@ -1,0 +1,629 @@
+// Split-K decode (dense and paged KV) for sm_100a with TMA-fed tiles and tcgen05 MMAs.
+//
+// Decode is bound by reading K and V once from HBM. TMA moves whole 128-key tiles (or whole pages) into
+// shared memory with no register or LSU traffic and keeps several tiles in flight per SM; the query
+// rows that share a kv head (GQA group x seqlen_q, at most 128) are padded to one 128-row MMA tile, so
+// scores and P.V for a tile cost two short bursts of tcgen05.mma whatever the group size, and grouped
+// queries read K/V exactly once.
+//
+// One CTA = one contiguous range of 128-key tiles of one (batch, kv head). The range is dealt to two
+// independent streams (even / odd tiles), each with its own softmax warpgroup, S and O accumulators in
+// TMEM and K/V slots in shared memory, so one stream's softmax overlaps the other's MMAs and loads:
+//   warps 0-3 / 4-7  softmax of stream 0 / 1 (thread = query row = TMEM lane; rows >= R idle along)
+//   warp 8           TMA producer (one lane); paged: one box per page, looked up in the block table
+//   warp 9           MMA issuer (one lane)
+// Each stream ends with a normalised fp32 partial and a natural-log LSE (-inf when it saw no key), written
+// as partial number 2 * blockIdx.x + stream; the LSE merge kernel combines all partials of a row.
+//
+// Paged safety (fa_rdna3/kernels/paged.py:37-63): context lengths are clamped to the table capacity;
+// page ids outside the pool are never dereferenced (the TMA box is aimed past the pool and reads zeros);
+// keys past the context are masked, and V rows past the context are never loaded (the last, ragged page
+// is fetched token by token), so stale cache contents cannot reach the output.
+#include "fa_common.cuh"
+#include "fa_sm100.cuh"
+#include "fa_tma_host.h"
+
+namespace fa {
+
+int launch_combine_internal(int rows, int D, int splits, const float* o_partial, int64_t o_split_stride,
+                            int64_t o_row_stride, const float* lse_partial, int64_t lse_split_stride,
+                            int64_t lse_row_stride, void* out, int out_dtype, int n1, int n2, int64_t os0,
+                            int64_t os1, int64_t os2, int64_t osd, float* lse_out, cudaStream_t stream);
+
+namespace {
+
+constexpr int kThreads = 320;
+constexpr uint32_t kFull = 0xffffffffu;
+constexpr float kRescaleThreshold = 8.0f;
+
+struct DecArgs {
+  int paged;
+  int batch, heads_q, heads_kv, group, seqlen_q, rows;  // rows = query rows sharing a kv head
+  int seqlen_k;                                         // dense
+  // paged
+  int block_size, max_blocks, num_blocks, first_block, block_step;
+  int tpt;  // tokens per unit: a unit is tpt consecutive tokens of one page, all kv heads (tpt * heads_kv rows)
+  int upp;  // units per page  = block_size / tpt
+  int upt;  // units per tile  = 128 / (tpt * heads_kv) when a page is one unit, else 1
+  const int32_t* block_table;
+  int64_t bt_sb, bt_sk;
+  const int32_t* context_lens;
+  int64_t cl_stride;
+  float softmax_scale;
+  int num_partials;  // 2 * gridDim.x
+  float* o_partial;
+  float* lse_partial;
+  int* status;
+};
+
+__device__ __forceinline__ void report_timeout(int* status, int code) {
+  if (status != nullptr) atomicCAS(status, 0, code);
+}
+
+template <int D>
+__device__ __forceinline__ void rescale_o(uint32_t tO, float alpha) {
+#pragma unroll
+  for (int c = 0; c < D / 32; ++c) {
+    uint32_t o[32];
+    tmem_ld32(tO + c * 32, o);
+    tc_wait_ld_regs(o);
+#pragma unroll
+    for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+    tmem_st32(tO + c * 32, o);
+  }
+  tc_wait_st();
+}
+
+template <typename T, int D, bool kPaged>
+__global__ void __launch_bounds__(kThreads, 1)
+decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                 const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_v_row,
+                 const DecArgs a) {
+  constexpr int kChunks = D / 64;
+  constexpr int kTileBytes = kChunks * 16384;
+  constexpr int kSlots = (D == 128) ? 6 : 10;  // ring of 128-key tiles: K_t, V_t, K_t+1, V_t+1, ...
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sRing = smem + kTileBytes;
+  __shared__ uint64_t q_full, full[kSlots], empty[kSlots], s_full[2], p_full[2], o_ready[2];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int nval_s[kSlots][16];  // paged: readable tokens of each unit of the tile in that K slot
+
+  const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+  // dense: one CTA row per (batch, kv head). paged: one per batch entry; a tile interleaves all kv heads
+  // (row = token * heads_kv + head), which is how a page lies in memory, so a page is fetched with few large boxes.
+  const int b = kPaged ? blockIdx.y : blockIdx.y / a.heads_kv;
+  const int hk = kPaged ? 0 : blockIdx.y % a.heads_kv;
+
+  // keys seen by this call, in local order, and this CTA's tile range
+  int nkeys = a.seqlen_k, ctx = 0, nlocal_pages = 0, tiles_total;
+  if (kPaged) {
+    const int bs = a.block_size;
+    ctx = a.context_lens[(int64_t)b * a.cl_stride];
+    ctx = (int)min((int64_t)max(ctx, 0), (int64_t)a.max_blocks * bs);
+    const int nblk = (ctx + bs - 1) / bs;
+    nlocal_pages = (nblk > a.first_block) ? (nblk - a.first_block + a.block_step - 1) / a.block_step : 0;
+    tiles_total = (nlocal_pages * a.upp + a.upt - 1) / a.upt;
+  } else {
+    tiles_total = (nkeys + 127) / 128;
+  }
+  const int tiles_per_cta = (tiles_total + gridDim.x - 1) / gridDim.x;
+  const int jlo = min((int)blockIdx.x * tiles_per_cta, tiles_total);
+  const int jhi = min(jlo + tiles_per_cta, tiles_total);
+  const int ntiles = jhi - jlo;
+
+  if (tid == 0) {
+    mbar_init(&q_full, 1);
+#pragma unroll
+    for (int s = 0; s < kSlots; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&s_full[s], 1);
+      mbar_init(&p_full[s], 128);
+      mbar_init(&o_ready[s], 1);
+    }
+    mbar_fence_init();
+  }
+  if (kPaged) {
+    // V tiles may be read at rows no load ever wrote (keys past the context): start the ring from zeros
+    for (int i = tid; i < kSlots * kTileBytes / 16; i += kThreads) reinterpret_cast<uint4*>(sRing)[i] = make_uint4(0, 0, 0, 0);
+    fence_proxy_async_smem();
+  }
+  if (warp == 9) {
+    tmem_alloc(&tmem_base_s, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_base_s;
+
+  if (warp == 8) {
+    // ------------------------------------------------------------------ TMA producer (whole warp; lane 0 issues)
+    if (ntiles > 0) {
+      if (lane == 0) {
+        tma_prefetch_desc(&map_k);
+        tma_prefetch_desc(&map_v);
+        mbar_arrive_expect_tx(&q_full, kTileBytes);
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c) tma_load_4d(sQ + c * 16384, &map_q, &q_full, c * 64, 0, hk, b);
+      }
+      // paged: lane u < upt holds the page id and the token counts of unit u of a tile
+      const int unit_rows_bytes = kPaged ? a.tpt * a.heads_kv * 128 : 0;
+      auto lookup = [&](int t, int* phys_out, int* nvalid_out, int* tokoff_out) {
+        int phys = a.num_blocks, nvalid = 0, tokoff = 0;
+        if (kPaged) {
+          const int u = (jlo + t) * a.upt + lane;  // local unit index
+          const int lp = u / a.upp;
+          if (t < ntiles && lane < a.upt && lp < nlocal_pages) {
+            const int lb = a.first_block + lp * a.block_step;
+            tokoff = (u % a.upp) * a.tpt;
+            const int id = a.block_table[(int64_t)b * a.bt_sb + (int64_t)lb * a.bt_sk];
+            nvalid = max(0, min(a.tpt, ctx - (lb * a.block_size + tokoff)));
+            if (id >= 0 && id < a.num_blocks) phys = id;
+            else nvalid = -nvalid;  // present but unreadable: box aimed past the pool reads zeros, keys masked
+          }
+        }
+        *phys_out = phys;
+        *nvalid_out = nvalid;
+        *tokoff_out = tokoff;
+      };
+      int phys_next = 0, nvalid_next = 0, tokoff_next = 0;
+      if (kPaged) lookup(0, &phys_next, &nvalid_next, &tokoff_next);
+      bool ok = true;
+      for (int t = 0; t < ntiles && ok; ++t) {
+        const int phys = phys_next, nvalid = nvalid_next, tokoff = tokoff_next;
+        if (kPaged) lookup(t + 1, &phys_next, &nvalid_next, &tokoff_next);  // in flight while this tile is issued
+        for (int which = 0; which < 2 && ok; ++which) {
+          const int n = 2 * t + which, slot = n % kSlots;
+          uint8_t* dst = sRing + slot * kTileBytes;
+          bool w_ok = true;
+          if (lane == 0) w_ok = mbar_wait(&empty[slot], ((n / kSlots) & 1) ^ 1);
+          w_ok = __shfl_sync(kFull, w_ok, 0);
+          if (!w_ok) {
+            if (lane == 0) report_timeout(a.status, 401);
+            ok = false;
+            break;
+          }
+          if (!kPaged) {
+            if (lane == 0) {
+              mbar_arrive_expect_tx(&full[slot], kTileBytes);
+#pragma unroll
+              for (int c = 0; c < kChunks; ++c)
+                tma_load_4d(dst + c * 16384, which == 0 ? &map_k : &map_v, &full[slot], c * 64, (jlo + t) * 128, hk, b);
+            }
+            continue;
+          }
+          // paged: bytes this tile delivers, token counts for the softmax groups, then the boxes
+          const int present = nvalid < 0 ? -nvalid : nvalid;  // tokens inside the context
+          const int readable = nvalid > 0 ? nvalid : 0;       // ... that may be used
+          int mybytes = (which == 0) ? (present > 0 ? a.tpt : 0) : present;
+          mybytes *= a.heads_kv * 128 * kChunks;
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) mybytes += __shfl_xor_sync(kFull, mybytes, o);
+          if (which == 0 && lane < 16) nval_s[slot][lane] = readable;
+          __syncwarp();
+          if (lane == 0) mbar_arrive_expect_tx(&full[slot], (uint32_t)mybytes);
+          __syncwarp();
+          // every lane issues the boxes of its own unit, so the copies of a tile are queued in parallel
+          if (lane < a.upt && present > 0) {
+            uint8_t* udst = dst + lane * unit_rows_bytes;
+            if (which == 0 || present == a.tpt) {
+#pragma unroll
+              for (int c = 0; c < kChunks; ++c)
+                tma_load_4d(udst + c * 16384, which == 0 ? &map_k : &map_v, &full[slot], c * 64, 0, tokoff, phys);
+            } else {
+              for (int tok = 0; tok < present; ++tok)
+#pragma unroll
+                for (int c = 0; c < kChunks; ++c)
+                  tma_load_4d(udst + c * 16384 + tok * a.heads_kv * 128, &map_v_row, &full[slot], c * 64, 0, tokoff + tok,
+                              phys);
+            }
+          }
+          __syncwarp();
+        }
+      }
+    }
+  } else if (warp == 9) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0 && ntiles > 0) {
+      constexpr uint32_t idesc_qk = make_idesc(DType<T>::kFormat, 128, 128, 0, 0);
+      constexpr uint32_t idesc_pv = make_idesc(DType<T>::kFormat, 128, D, 0, 1);
+      const uint32_t q_addr = smem_u32(sQ), ring_addr = smem_u32(sRing);
+      bool ok = mbar_wait(&q_full, 0);
+      if (!ok) report_timeout(a.status, 403);
+
+      auto issue_qk = [&](int t) {  // tile t goes to stream t & 1
+        const int n = 2 * t, slot = n % kSlots, s = t & 1;
+        if (!mbar_wait(&full[slot], (n / kSlots) & 1)) {
+          report_timeout(a.status, 404);
+          ok = false;
+          return;
+        }
+        tc_fence_after_sync();
+        const uint32_t k_addr = ring_addr + slot * kTileBytes;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk / 4) * 16384 + (kk % 4) * 32;
+          mma_ss(tmem_base + s * 128, make_smem_desc(q_addr + off, 16, 1024), make_smem_desc(k_addr + off, 16, 1024),
+                 idesc_qk, kk > 0);
+        }
+        tc_commit(&s_full[s]);
+        if (!kPaged) tc_commit(&empty[slot]);  // paged: the softmax group releases it after reading the validity mask
+      };
+
+      if (ok) issue_qk(0);
+      if (ok && ntiles > 1) issue_qk(1);
+      for (int t = 0; t < ntiles && ok; ++t) {
+        const int n = 2 * t + 1, slot = n % kSlots, s = t & 1;
+        if (!mbar_wait(&full[slot], (n / kSlots) & 1) || !mbar_wait(&p_full[s], (t >> 1) & 1)) {
+          report_timeout(a.status, 405);
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t v_addr = ring_addr + slot * kTileBytes;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          mma_ts(tmem_base + 256 + s * D, tmem_base + s * 128 + kk * 8, make_smem_desc(v_addr + kk * 2048, 16384, 1024),
+                 idesc_pv, !(t < 2 && kk == 0));
+        tc_commit(&o_ready[s]);
+        tc_commit(&empty[slot]);
+        if (t + 2 < ntiles) issue_qk(t + 2);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax of stream s
+    const int s = warp / 4, w4 = warp % 4;
+    const int row = w4 * 32 + lane;
+    const uint32_t lane_addr = static_cast<uint32_t>(w4 * 32) << 16;
+    const uint32_t tS = tmem_base + lane_addr + s * 128;
+    const uint32_t tO = tmem_base + lane_addr + 256 + s * D;
+    const int n_mine = (ntiles + 1 - s) / 2;
+    const bool warp_active = w4 * 32 < a.rows;  // warps whose 32 rows are all padding only keep the barriers moving
+    const float scale_log2 = a.softmax_scale * kLog2e;
+    float m_used = kNegInf, l = 0.f;
+    bool ok = true;
+
+    for (int i = 0; i < n_mine; ++i) {
+      const int t = 2 * i + s, j = jlo + t;
+      bool w_ok = mbar_wait(&s_full[s], i & 1);
+      if (w_ok && i > 0) w_ok = mbar_wait(&o_ready[s], (i - 1) & 1);
+      if (!__all_sync(kFull, w_ok)) {
+        report_timeout(a.status, 406);
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      // validity of the tile's 128 columns for this row as a bit mask
+      uint32_t vmask[4] = {kFull, kFull, kFull, kFull};
+      if (kPaged) {
+        // column = (unit * tpt + token) * heads_kv + kv head: this row only sees the columns of its own kv head,
+        // and of those only the readable tokens
+        const int kslot = (2 * t) % kSlots;
+        const int my_hk = min(row, a.heads_q - 1) / a.group;
+        vmask[0] = vmask[1] = vmask[2] = vmask[3] = 0u;
+        for (int u = 0; u < a.upt; ++u) {
+          const int nv = nval_s[kslot][u];
+          for (int tok = 0; tok < nv; ++tok) {
+            const int c = (u * a.tpt + tok) * a.heads_kv + my_hk;
+            vmask[c >> 5] |= 1u << (c & 31);
+          }
+        }
+        // the K slot (and its counts) may be reused once every thread of this stream has read them
+        asm volatile("bar.sync %0, 128;" ::"r"(1 + s) : "memory");
+        if (w4 == 0 && lane == 0) mbar_arrive(&empty[kslot]);
+      } else if (j * 128 + 128 > nkeys) {
+        const int nv = nkeys - j * 128;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          const int left = nv - w * 32;
+          vmask[w] = left >= 32 ? kFull : (left <= 0 ? 0u : ((1u << left) - 1u));
+        }
+      }
+      const bool masked = (vmask[0] & vmask[1] & vmask[2] & vmask[3]) != kFull;
+      if (warp_active) {
+        // pass 1: row maximum
+        float mx[4] = {kNegInf, kNegInf, kNegInf, kNegInf};
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t r[64];
+          tmem_ld32(tS + half * 64, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+          tmem_ld32(tS + half * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+          tc_wait_ld_regs(*reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+          tc_wait_ld_regs(*reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+          if (masked) {
+#pragma unroll
+            for (int c = 0; c < 64; ++c)
+              if (!((vmask[half * 2 + c / 32] >> (c & 31)) & 1u)) r[c] = __float_as_uint(kNegInf);
+          }
+#pragma unroll
+          for (int c = 0; c < 64; c += 8)
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+              mx[u] = fmax3(mx[u], __uint_as_float(r[c + 2 * u]), __uint_as_float(r[c + 2 * u + 1]));
+        }
+        float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+        m_tile *= scale_log2;  // softmax_scale > 0 on this path
+        const float m_new = fmaxf(m_used, m_tile);
+        const bool grow = m_new > m_used + kRescaleThreshold;
+        if (__any_sync(kFull, grow)) {
+          const float alpha = (m_new == kNegInf) ? 1.f : exp2f(m_used - m_new);
+          l *= alpha;
+          if (i > 0) rescale_o<D>(tO, alpha);
+          m_used = m_new;
+        }
+        const float m_eff = (m_used == kNegInf) ? 0.f : m_used;
+
+        // pass 2: p = exp2(s*scale - m), 32 columns at a time, P written over consumed S columns
+        const uint64_t sc2 = pack_f32x2(scale_log2, scale_log2);
+        const uint64_t nm2 = pack_f32x2(-m_eff, -m_eff);
+        uint64_t acc2[4] = {0ull, 0ull, 0ull, 0ull};
+        uint32_t rb[2][32];
+        tmem_ld32(tS, rb[0]);
+        tc_wait_ld_regs(rb[0]);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          if (c < 3) tmem_ld32(tS + (c + 1) * 32, rb[(c + 1) & 1]);
+          uint32_t (&r)[32] = rb[c & 1];
+          if (masked) {
+#pragma unroll
+            for (int e = 0; e < 32; ++e)
+              if (!((vmask[c] >> e) & 1u)) r[e] = __float_as_uint(kNegInf);
+          }
+          uint32_t pk[16];
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            const uint64_t x2 = fma_f32x2(pack_u32x2(r[2 * e], r[2 * e + 1]), sc2, nm2);
+            float x0, x1;
+            unpack_f32x2(x2, &x0, &x1);
+            const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+            acc2[e & 3] = add_f32x2(acc2[e & 3], pack_f32x2(p0, p1));
+            pk[e] = DType<T>::pack2(p0, p1);
+          }
+          tmem_st16(tS + c * 16, pk);
+          if (c < 3) tc_wait_ld_regs(rb[(c + 1) & 1]);
+        }
+        float s0, s1;
+        unpack_f32x2(add_f32x2(add_f32x2(acc2[0], acc2[1]), add_f32x2(acc2[2], acc2[3])), &s0, &s1);
+        l += s0 + s1;
+        tc_wait_st();
+      } else {
+        // padding-only warp: P rows of its lanes must still be finite zeros for the MMA
+        uint32_t z[32];
+#pragma unroll
+        for (int e = 0; e < 32; ++e) z[e] = 0u;
+        tmem_st32(tS, z);
+        tmem_st32(tS + 32, z);
+        tc_wait_st();
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&p_full[s]);
+    }
+
+    // epilogue: normalised fp32 partial and LSE of this stream
+    if (n_mine > 0) {
+      const bool w_ok = ok && mbar_wait(&o_ready[s], (n_mine - 1) & 1);
+      if (!__all_sync(kFull, w_ok)) {
+        if (ok) report_timeout(a.status, 407);
+        ok = false;
+      }
+    }
+    if (ok && warp_active) {
+      tc_fence_after_sync();
+      const int part = 2 * blockIdx.x + s;
+      const int g = row / a.seqlen_q, sq = row % a.seqlen_q;
+      const int h = kPaged ? row : hk * a.group + g;
+      int64_t flat_o, flat_l;
+      if (kPaged) {  // (batch, heads_q, partials, D) and (batch, heads_q, partials)
+        flat_l = ((int64_t)b * a.heads_q + h) * a.num_partials + part;
+        flat_o = flat_l * D;
+      } else {       // (partials, batch, heads_q, seqlen_q, D) and (partials, batch, heads_q, seqlen_q)
+        flat_l = (((int64_t)part * a.batch + b) * a.heads_q + h) * a.seqlen_q + sq;
+        flat_o = flat_l * D;
+      }
+      const float l_safe = (l == 0.f) ? 1.f : l;
+      const float inv = 1.f / l_safe;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t o[32];
+        if (n_mine > 0) {
+          tmem_ld32(tO + c * 32, o);
+          tc_wait_ld_regs(o);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) o[e] = 0u;
+        }
+        if (row < a.rows) {
+          float4* dst = reinterpret_cast<float4*>(a.o_partial + flat_o + c * 32);
+#pragma unroll
+          for (int v = 0; v < 8; ++v)
+            dst[v] = make_float4(__uint_as_float(o[4 * v]) * inv, __uint_as_float(o[4 * v + 1]) * inv,
+                                 __uint_as_float(o[4 * v + 2]) * inv, __uint_as_float(o[4 * v + 3]) * inv);
+        }
+      }
+      if (row < a.rows) a.lse_partial[flat_l] = (l == 0.f) ? kNegInf : (m_used * kLn2 + logf(l));
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 9) tmem_dealloc(tmem_base, 512);
+}
+
+typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                             const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                             CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// Tensor map over a paged cache (dim, kv head, token in page, page) with a box of 64 x heads_kv x box_tokens x 1:
+// box_tokens tokens of one page, all kv heads, land as rows token * heads_kv + head.
+int make_page_map(CUtensorMap* map, const void* ptr, int dtype, int D, int heads_kv, int block_size, int num_blocks,
+                  const int64_t st[4], int box_tokens) {
+  TensorMapEncodeFn enc = tensor_map_encoder();
+  if (enc == nullptr) return set_error(FA_ERR_DEVICE, "cuTensorMapEncodeTiled is not available from this driver");
+  const cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)heads_kv, (cuuint64_t)block_size, (cuuint64_t)num_blocks};
+  auto bytes = [&](int64_t s, int64_t n) { return (cuuint64_t)((n > 1 && s > 0) ? s : D) * 2; };
+  const cuuint64_t strides[3] = {bytes(st[2], heads_kv), bytes(st[1], block_size), bytes(st[0], num_blocks)};
+  const cuuint32_t box[4] = {64, (cuuint32_t)heads_kv, (cuuint32_t)box_tokens, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUtensorMapDataType dt = (dtype == FA_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUresult r = enc(map, dt, 4, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return set_error(FA_ERR_LAUNCH, "cuTensorMapEncodeTiled (paged cache) failed with code %d", (int)r);
+  return 0;
+}
+
+template <typename T, int D, bool kPaged>
+int launch_kernel(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mvr,
+                  const DecArgs& a, int ctas, cudaStream_t stream) {
+  constexpr int kTileBytes = (D / 64) * 16384;
+  constexpr int kSlots = (D == 128) ? 6 : 10;
+  const int smem = (1 + kSlots) * kTileBytes + 1024;
+  auto kern = decode_tc_kernel<T, D, kPaged>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "decode smem opt-in failed: %s", cudaGetErrorString(e));
+  kern<<<dim3(ctas, kPaged ? a.batch : a.batch * a.heads_kv), kThreads, smem, stream>>>(mq, mk, mv, mvr, a);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "tcgen05 decode launch failed: %s", cudaGetErrorString(e));
+  return 0;
+}
+
+template <bool kPaged>
+int dispatch(int dtype, int D, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
+             const CUtensorMap& mvr, const DecArgs& a, int ctas, cudaStream_t stream) {
+  if (dtype == FA_F16)
+    return D == 128 ? launch_kernel<__half, 128, kPaged>(mq, mk, mv, mvr, a, ctas, stream)
+                    : launch_kernel<__half, 64, kPaged>(mq, mk, mv, mvr, a, ctas, stream);
+  return D == 128 ? launch_kernel<__nv_bfloat16, 128, kPaged>(mq, mk, mv, mvr, a, ctas, stream)
+                  : launch_kernel<__nv_bfloat16, 64, kPaged>(mq, mk, mv, mvr, a, ctas, stream);
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace
+
+// Dense split-K decode on the tcgen05 path. num_splits must be even: each CTA produces two partials.
+bool decode_tc_supported(const fa_decode_params& p) {
+  if (p.dtype != FA_F16 && p.dtype != FA_BF16) return false;
+  if (p.head_dim != 64 && p.head_dim != 128) return false;
+  if (!(p.softmax_scale > 0.f)) return false;
+  if (p.num_splits < 2 || (p.num_splits & 1) || p.o_partial == nullptr || p.lse_partial == nullptr) return false;
+  if (p.heads_kv <= 0 || p.heads_q % p.heads_kv) return false;
+  const int group = p.heads_q / p.heads_kv;
+  if (group * p.seqlen_q > 128) return false;
+  const int64_t sk[3] = {p.batch, p.heads_kv, p.seqlen_k};
+  if (!tma_operand_ok(p.k, p.k_strides, sk) || !tma_operand_ok(p.v, p.v_strides, sk)) return false;
+  // the query rows of one kv head must form one strided row sequence
+  if (!aligned16(p.q) || p.q_strides[3] != 1) return false;
+  if (p.seqlen_q > 1 && group > 1 && p.q_strides[1] != p.q_strides[2] * p.seqlen_q) return false;
+  const int64_t row_stride = p.seqlen_q > 1 ? p.q_strides[2] : p.q_strides[1];
+  if (group * p.seqlen_q > 1 && (row_stride <= 0 || row_stride % 8)) return false;
+  if (p.heads_kv > 1 && ((p.q_strides[1] * group) % 8 || p.q_strides[1] <= 0)) return false;
+  if (p.batch > 1 && (p.q_strides[0] % 8 || p.q_strides[0] <= 0)) return false;
+  return true;
+}
+
+int launch_decode_tc(const fa_decode_params& p, cudaStream_t stream) {
+  const int group = p.heads_q / p.heads_kv, rows = group * p.seqlen_q, D = p.head_dim;
+  const int64_t row_stride = p.seqlen_q > 1 ? p.q_strides[2] : p.q_strides[1];
+  CUtensorMap mq, mk, mv;
+  int rc = make_tile_map(&mq, p.q, p.dtype, D, rows, p.heads_kv, p.batch, row_stride, p.q_strides[1] * group,
+                         p.q_strides[0]);
+  if (!rc) rc = make_tile_map(&mk, p.k, p.dtype, D, p.seqlen_k, p.heads_kv, p.batch, p.k_strides[2], p.k_strides[1],
+                              p.k_strides[0]);
+  if (!rc) rc = make_tile_map(&mv, p.v, p.dtype, D, p.seqlen_k, p.heads_kv, p.batch, p.v_strides[2], p.v_strides[1],
+                              p.v_strides[0]);
+  if (rc) return rc;
+  DecArgs a = {};
+  a.paged = 0;
+  a.batch = p.batch;
+  a.heads_q = p.heads_q;
+  a.heads_kv = p.heads_kv;
+  a.group = group;
+  a.seqlen_q = p.seqlen_q;
+  a.rows = rows;
+  a.seqlen_k = p.seqlen_k;
+  a.softmax_scale = p.softmax_scale;
+  a.num_partials = p.num_splits;
+  a.o_partial = p.o_partial;
+  a.lse_partial = p.lse_partial;
+  a.status = nullptr;
+  rc = dispatch<false>(p.dtype, D, mq, mk, mv, mv, a, p.num_splits / 2, stream);
+  if (rc) return rc;
+  const int nrows = p.batch * p.heads_q * p.seqlen_q;
+  return launch_combine_internal(nrows, D, p.num_splits, p.o_partial, (int64_t)nrows * D, D, p.lse_partial, nrows, 1,
+                                 p.out, p.dtype, p.heads_q, p.seqlen_q, p.o_strides[0], p.o_strides[1], p.o_strides[2],
+                                 p.o_strides[3], nullptr, stream);
+}
+
+bool paged_tc_supported(const fa_paged_params& p) {
+  if (p.dtype != FA_F16 && p.dtype != FA_BF16) return false;
+  if (p.head_dim != 64 && p.head_dim != 128) return false;
+  if (!(p.softmax_scale > 0.f)) return false;
+  if (p.num_splits < 2 || (p.num_splits & 1) || p.o_partial == nullptr || p.lse_partial == nullptr) return false;
+  if (p.heads_kv <= 0 || p.heads_q % p.heads_kv || p.heads_q > 128) return false;  // one MMA row per query head
+  if (p.block_size < 1 || (p.block_size & (p.block_size - 1))) return false;
+  if (p.heads_kv > 128 || (p.heads_kv & (p.heads_kv - 1))) return false;           // rows per token must divide 128
+  if (p.block_size * p.heads_kv < 8) return false;                                  // at most 16 units per tile
+  if (!aligned16(p.k_cache) || !aligned16(p.v_cache) || !aligned16(p.q)) return false;
+  if (p.k_strides[3] != 1 || p.v_strides[3] != 1 || p.q_strides[2] != 1) return false;
+  for (int i = 0; i < 3; ++i)
+    if (p.k_strides[i] <= 0 || p.k_strides[i] % 8 || p.v_strides[i] <= 0 || p.v_strides[i] % 8) return false;
+  const int group = p.heads_q / p.heads_kv;
+  if (p.heads_q > 1 && (p.q_strides[1] <= 0 || p.q_strides[1] % 8)) return false;
+  if (p.batch > 1 && (p.q_strides[0] <= 0 || p.q_strides[0] % 8)) return false;
+  (void)group;
+  return true;
+}
+
+int launch_paged_tc(const fa_paged_params& p, cudaStream_t stream) {
+  const int group = p.heads_q / p.heads_kv, D = p.head_dim;
+  CUtensorMap mq, mk, mv, mvr;
+  // unit = tpt tokens of one page with all kv heads (tpt * heads_kv <= 128 rows); a tile holds upt units
+  const int tpt = p.block_size * p.heads_kv <= 128 ? p.block_size : 128 / p.heads_kv;
+  const int upp = p.block_size / tpt;
+  const int upt = upp == 1 ? 128 / (tpt * p.heads_kv) : 1;
+  int rc = make_tile_map(&mq, p.q, p.dtype, D, p.heads_q, 1, p.batch, p.q_strides[1], 0, p.q_strides[0]);
+  if (!rc) rc = make_page_map(&mk, p.k_cache, p.dtype, D, p.heads_kv, p.block_size, p.num_blocks, p.k_strides, tpt);
+  if (!rc) rc = make_page_map(&mv, p.v_cache, p.dtype, D, p.heads_kv, p.block_size, p.num_blocks, p.v_strides, tpt);
+  if (!rc) rc = make_page_map(&mvr, p.v_cache, p.dtype, D, p.heads_kv, p.block_size, p.num_blocks, p.v_strides, 1);
+  if (rc) return rc;
+  DecArgs a = {};
+  a.paged = 1;
+  a.batch = p.batch;
+  a.heads_q = p.heads_q;
+  a.heads_kv = p.heads_kv;
+  a.group = group;
+  a.seqlen_q = 1;
+  a.rows = p.heads_q;
+  a.tpt = tpt;
+  a.upp = upp;
+  a.upt = upt;
+  a.block_size = p.block_size;
+  a.max_blocks = p.max_blocks;
+  a.num_blocks = p.num_blocks;
+  a.first_block = p.first_block;
+  a.block_step = p.block_step;
+  a.block_table = p.block_table;
+  a.bt_sb = p.bt_strides[0];
+  a.bt_sk = p.bt_strides[1];
+  a.context_lens = p.context_lens;
+  a.cl_stride = p.cl_stride;
+  a.softmax_scale = p.softmax_scale;
+  a.num_partials = p.num_splits;
+  a.o_partial = p.o_partial;
+  a.lse_partial = p.lse_partial;
+  a.status = nullptr;
+  rc = dispatch<true>(p.dtype, D, mq, mk, mv, mvr, a, p.num_splits / 2, stream);
+  if (rc) return rc;
+  const int nrows = p.batch * p.heads_q;
+  return launch_combine_internal(nrows, D, p.num_splits, p.o_partial, D, (int64_t)p.num_splits * D, p.lse_partial, 1,
+                                 p.num_splits, p.out, p.out_is_f32 ? (int)FA_F32 : p.dtype, p.heads_q, 1, p.o_strides[0],
+                                 p.o_strides[1], 0, p.o_strides[2], p.lse_out, stream);
+}
+
+}  // namespace fa

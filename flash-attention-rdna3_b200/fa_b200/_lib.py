@@ -55,7 +55,7 @@ class DecodeParams(C.Structure):
         ("v", C.c_void_p), ("v_strides", I64x4),
         ("out", C.c_void_p), ("o_strides", I64x4),
         ("softmax_scale", C.c_float), ("num_splits", C.c_int32),
-        ("o_partial", C.c_void_p), ("lse_partial", C.c_void_p),
+        ("o_partial", C.c_void_p), ("lse_partial", C.c_void_p), ("force_path", C.c_int32),
     ]
 
 
@@ -83,7 +83,7 @@ class PagedParams(C.Structure):
         ("softmax_scale", C.c_float), ("num_splits", C.c_int32),
         ("first_block", C.c_int32), ("block_step", C.c_int32),
         ("o_partial", C.c_void_p), ("lse_partial", C.c_void_p), ("lse_out", C.c_void_p),
-        ("out_is_f32", C.c_int32),
+        ("out_is_f32", C.c_int32), ("force_path", C.c_int32),
     ]
 
 

@@ -20,7 +20,7 @@ import math
 import torch
 
 from . import _lib
-from .interface import _DTYPE_CODE, _paged_launch, _paged_num_splits, _stream
+from .interface import _DTYPE_CODE, _paged_launch, _paged_splits_b200, _paged_tensor_core_ok, _stream
 from ._validation import validate_inference_only, validate_paged_inputs, validate_softmax_scale
 
 
@@ -95,10 +95,13 @@ def paged_decode_kv_sharded(query, k_cache, v_cache, block_table, context_lens, 
         raise ValueError(f"ranks disagree on the decode problem: {all_meta}")
 
     if _local_partial is None:
-        target = 2 * torch.cuda.get_device_properties(query.device).multi_processor_count
-        local_ctx = None if max_context_len is None else -(-int(max_context_len) // world)
-        splits = int(_paged_num_splits(batch, q_heads, k_cache.shape[1], block_table.shape[1], target,
-                                       max_context_len=local_ctx, requested_splits=num_splits))
+        sm_count = torch.cuda.get_device_properties(query.device).multi_processor_count
+        capacity = block_table.shape[1] * k_cache.shape[1]
+        local_ctx = -(-(capacity if max_context_len is None else min(capacity, int(max_context_len))) // world)
+        kv_heads = k_cache.shape[2]
+        splits = int(num_splits) if num_splits is not None else _paged_splits_b200(
+            batch, kv_heads, q_heads // kv_heads, k_cache.shape[1], block_table.shape[1], sm_count, local_ctx,
+            tensor_core=_paged_tensor_core_ok(query, head_dim, q_heads, kv_heads, k_cache.shape[1], scale))
         o_r, lse_r = _paged_launch(query, k_cache, v_cache, block_table, context_lens, scale, splits,
                                    first_block=rank, block_step=world, want_lse=True, out_f32=True)
     else:

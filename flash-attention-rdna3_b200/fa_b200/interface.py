@@ -95,17 +95,31 @@ def _fill_splits(base_ctas, max_splits, sm_count, ctas_per_sm=2):
     return best
 
 
-def _decode_splits_b200(batch, kv_heads, group_rows, seqlen_k, sm_count):
-    """Key slices for split-K decode on B200: CTAs are per (batch, kv head, chunk of 4 query rows); slices are
-    at least 512 keys long and at most 64."""
+def _decode_splits_b200(batch, kv_heads, group_rows, seqlen_k, sm_count, tensor_core=False):
+    """Key slices for split-K decode on B200. Tensor-core kernel: one CTA per SM, every CTA walks two streams of
+    128-key tiles and emits two partials, so the count is even and each CTA gets at least two tiles.
+    CUDA-core kernel: CTAs are per (batch, kv head, chunk of 4 query rows), two per SM; slices are at least 512
+    keys long and at most 64."""
+    if tensor_core:
+        tiles = _cdiv(seqlen_k, 128)
+        # one wave of long CTAs beats several waves of short ones (per-CTA start-up is not amortised otherwise)
+        heads = batch * kv_heads
+        ctas = max(1, sm_count // heads) if heads < sm_count else 1
+        return 2 * min(ctas, 32, max(1, tiles // 2))
     rows_per_cta = 1 if group_rows == 1 else 2 if group_rows == 2 else 4
     base = batch * kv_heads * _cdiv(group_rows, rows_per_cta)
     return _fill_splits(base, min(64, max(1, seqlen_k // 512)), sm_count)
 
 
-def _paged_splits_b200(batch, kv_heads, group, block_size, max_blocks, sm_count, max_context_len=None):
-    """Splits of paged decode on B200 (at most 32, each at least 256 tokens of the longest context)."""
+def _paged_splits_b200(batch, kv_heads, group, block_size, max_blocks, sm_count, max_context_len=None,
+                       tensor_core=False):
+    """Splits of paged decode on B200 (at most 32, each at least 256 tokens of the longest context); the
+    tensor-core kernel takes an even count, two partials per CTA, one CTA per SM."""
     tokens = max_blocks * block_size if max_context_len is None else min(max_blocks * block_size, max_context_len)
+    if tensor_core:
+        # one CTA row per batch entry; a 128-row tile holds 128 / kv_heads tokens of all kv heads
+        tiles = _cdiv(tokens * kv_heads, 128)
+        return 2 * _fill_splits(batch, min(64, max(1, tiles // 2)), sm_count, ctas_per_sm=1)
     rows_per_cta = 1 if group == 1 else 2 if group == 2 else 4
     base = batch * kv_heads * _cdiv(group, rows_per_cta)
     return _fill_splits(base, min(32, max(1, tokens // 256)), sm_count)
@@ -463,7 +477,19 @@ def _vector_friendly(t):
     return all(s % 8 == 0 for s, n in zip(t.stride()[:-1], t.shape[:-1]) if n > 1)
 
 
-def _decode_impl(query, key, value, softmax_scale, num_splits):
+def _tensor_core_decode_ok(query, head_dim, rows_per_kv_head, softmax_scale):
+    """Host-side mirror of the tcgen05 decode kernel's shape limits (the library re-checks strides itself)."""
+    return (query.dtype in LOW_PRECISION_DTYPES and head_dim in (64, 128) and rows_per_kv_head <= 128
+            and softmax_scale > 0)
+
+
+def _paged_tensor_core_ok(query, head_dim, q_heads, kv_heads, block_size, softmax_scale):
+    """Shape limits of the tcgen05 paged kernel: every query head is one MMA row, kv heads interleave in a tile."""
+    return (query.dtype in LOW_PRECISION_DTYPES and head_dim in (64, 128) and q_heads <= 128 and softmax_scale > 0
+            and kv_heads & (kv_heads - 1) == 0 and block_size * kv_heads >= 8)
+
+
+def _decode_impl(query, key, value, softmax_scale, num_splits, force_path=0):
     lib = _lib.load()
     batch, heads, seqlen_q, head_dim = query.shape
     if not _vector_friendly(key):
@@ -482,6 +508,7 @@ def _decode_impl(query, key, value, softmax_scale, num_splits):
     _set4(p.o_strides, out.stride())
     p.softmax_scale = float(softmax_scale)
     p.num_splits = int(num_splits)
+    p.force_path = int(force_path)
     if num_splits > 1:
         o_partial = torch.empty((num_splits, batch, heads, seqlen_q, head_dim), dtype=torch.float32,
                                 device=query.device)
@@ -518,7 +545,9 @@ def flash_attention_decode(query, key, value, softmax_scale=None):
     # The reference sizes its grid per query head (_decode_num_splits above); these kernels run one CTA per kv head
     # and slice of keys, so the count comes from the B200 grid-fill rule instead.
     sm_count = torch.cuda.get_device_properties(query.device).multi_processor_count
-    num_splits = _decode_splits_b200(batch, key.shape[1], (heads // key.shape[1]) * seqlen_q, seqlen_k, sm_count)
+    rows = (heads // key.shape[1]) * seqlen_q
+    num_splits = _decode_splits_b200(batch, key.shape[1], rows, seqlen_k, sm_count,
+                                     tensor_core=_tensor_core_decode_ok(query, head_dim, rows, softmax_scale))
     return _decode_op(query, key, value, softmax_scale, num_splits)
 
 
@@ -633,7 +662,7 @@ def flash_attention_varlen(query, key, value, cu_seqlens_q, cu_seqlens_k,
 # paged-KV decode
 # ---------------------------------------------------------------------------------------------------
 def _paged_launch(query, k_cache, v_cache, block_table, context_lens, softmax_scale, num_splits,
-                  first_block=0, block_step=1, want_lse=False, out_f32=False):
+                  first_block=0, block_step=1, want_lse=False, out_f32=False, force_path=0):
     """Launch paged decode over logical blocks first_block, first_block + block_step, ...; returns
     (out, lse or None). With want_lse the output is the fp32 partial of a KV shard."""
     lib = _lib.load()
@@ -662,6 +691,7 @@ def _paged_launch(query, k_cache, v_cache, block_table, context_lens, softmax_sc
     p.num_splits = int(num_splits)
     p.first_block, p.block_step = int(first_block), int(block_step)
     p.out_is_f32 = int(out_f32)
+    p.force_path = int(force_path)
     if lse is not None:
         p.lse_out = lse.data_ptr()
     if num_splits > 1:
@@ -713,8 +743,11 @@ def flash_attention_decode_paged(query, k_cache, v_cache, block_table, context_l
     else:
         sm_count = torch.cuda.get_device_properties(query.device).multi_processor_count
         kv_heads = k_cache.shape[2]
-        selected = _paged_splits_b200(batch, kv_heads, q_heads // kv_heads, block_size, block_table.shape[1],
-                                      sm_count, None if max_context_len is None else int(max_context_len))
+        group = q_heads // kv_heads
+        selected = _paged_splits_b200(batch, kv_heads, group, block_size, block_table.shape[1], sm_count,
+                                      None if max_context_len is None else int(max_context_len),
+                                      tensor_core=_paged_tensor_core_ok(query, head_dim, q_heads, kv_heads, block_size,
+                                                                        softmax_scale))
     return _paged_op(query, k_cache, v_cache, block_table, context_lens, softmax_scale, selected)
 
 

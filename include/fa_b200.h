@@ -105,6 +105,9 @@ typedef struct fa_attn_params {
 enum fa_bwd_part { FA_BWD_DELTA = 1, FA_BWD_DKDV = 2, FA_BWD_DQ = 4 };
 
 /* Split-K decode: q (batch, heads_q, seqlen_q, head_dim), k/v (batch, heads_kv, seqlen_k, head_dim).
+   Two kernel families: with fp16/bf16, head_dim 64 or 128, at most 128 query rows per kv head, TMA-compatible
+   strides and an EVEN num_splits >= 2 the TMA + tcgen05 kernel runs (num_splits / 2 CTAs per (batch, kv head),
+   two partials each); anything else runs on the CUDA-core kernel.
    o_partial (num_splits, batch, heads_q, seqlen_q, head_dim) fp32 contiguous and
    lse_partial (num_splits, batch, heads_q, seqlen_q) fp32 contiguous are caller-allocated scratch. */
 typedef struct fa_decode_params {
@@ -118,6 +121,7 @@ typedef struct fa_decode_params {
   int32_t num_splits;
   float* o_partial;
   float* lse_partial;
+  int32_t force_path;  /* 0 = automatic; FA_PATH_TCGEN05 (needs an even num_splits >= 2) or FA_PATH_SIMT */
 } fa_decode_params;
 
 /* LSE-weighted merge of `num_splits` partial results for `rows` independent rows.
@@ -158,6 +162,7 @@ typedef struct fa_paged_params {
   float* lse_partial;
   float* lse_out;           /* (batch, heads_q) fp32 contiguous or NULL */
   int32_t out_is_f32;       /* write out as fp32 regardless of dtype (shard partials) */
+  int32_t force_path;       /* 0 = automatic; FA_PATH_TCGEN05 (needs an even num_splits >= 2) or FA_PATH_SIMT */
 } fa_paged_params;
 
 /* FP32 short-sequence attention: q, k, v, out (batch, heads, seqlen <= 32, 128), optional bias. */

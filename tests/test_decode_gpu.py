@@ -200,3 +200,72 @@ def test_tiny_transposed_layout():
     q, k, v = (seeded(i, 2, 19, 8, 128, dtype=torch.float32).transpose(1, 2) for i in (1, 2, 3))
     out = fa_b200.flash_attention(q, k, v)
     assert max_abs(out, oracle.tiny_ref(q.cpu(), k.cpu(), v.cpu())) <= TINY_TOL
+
+
+# ------------------------------------------------------------------------------------------ kernel families
+@pytest.mark.parametrize("path", [1, 2])  # 1 = TMA + tcgen05 kernel, 2 = CUDA-core kernel
+@pytest.mark.parametrize("hq,hk,sq,sk,splits", [(8, 8, 1, 4096, 8), (32, 8, 1, 8192, 6), (8, 2, 4, 1000, 4),
+                                                (4, 4, 8, 300, 2), (16, 1, 3, 129, 2), (2, 2, 1, 128, 2)])
+def test_decode_both_kernel_families(path, hq, hk, sq, sk, splits):
+    from fa_b200 import _lib, interface
+
+    q, k, v = seeded(1, 2, hq, sq, 128), seeded(2, 2, hk, sk, 128), seeded(3, 2, hk, sk, 128)
+    out = interface._decode_impl(q, k, v, 0.09, splits, force_path=path)
+    assert _lib.load().fa_last_path() == path
+    ref, _ = oracle.decode_ref(q.cpu(), k.cpu(), v.cpu(), softmax_scale=0.09)
+    assert_close_o(out, ref, torch.float16)
+
+
+@pytest.mark.parametrize("path", [1, 2])
+@pytest.mark.parametrize("dtype,head_dim", [(torch.float16, 64), (torch.bfloat16, 128)])
+@pytest.mark.parametrize("block_size,contexts", [(16, [1000, 333, 0, 16]), (8, [257, 64, 5, 1]), (64, [700, 64, 65, 1]),
+                                                 (128, [900, 128, 129, 0])])
+def test_paged_both_kernel_families(path, dtype, head_dim, block_size, contexts):
+    from fa_b200 import _lib, interface
+
+    q, kc, vc, table, ctx = make_paged(4, 8, 2, head_dim, block_size, contexts, dtype=dtype, seed=block_size)
+    scale = 1.0 / math.sqrt(head_dim)
+    out, _ = interface._paged_launch(q, kc, vc, table, ctx, scale, 4, force_path=path)
+    assert _lib.load().fa_last_path() == path
+    ref, _ = oracle.paged_ref(q.cpu(), kc.cpu(), vc.cpu(), table.cpu(), ctx.cpu())
+    assert_close_o(out, ref, dtype)
+
+
+@pytest.mark.parametrize("path", [1, 2])
+def test_paged_never_reads_past_the_context_or_bad_pages(path):
+    """Cache contents past context_len, and whole pages the table does not legitimately reference, are NaN:
+    nothing of them may reach the output."""
+    from fa_b200 import interface
+
+    B, Hq, Hk, D, bs = 3, 8, 2, 128, 16
+    contexts = [200, 77, 33]
+    q, kc, vc, table, ctx = make_paged(B, Hq, Hk, D, bs, contexts, seed=11)
+    kc, vc = kc.clone(), vc.clone()
+    used = torch.zeros(kc.shape[0], bs, dtype=torch.bool, device="cuda")
+    for b, c in enumerate(contexts):
+        for pos in range(c):
+            used[table[b, pos // bs], pos % bs] = True
+    kc[~used] = float("nan")
+    vc[~used] = float("nan")
+    bad = table.clone()
+    bad[0, 3] = -7
+    bad[1, 1] = kc.shape[0] + 3
+    for tbl in (table, bad):
+        out, _ = interface._paged_launch(q, kc, vc, tbl, ctx, 1.0 / math.sqrt(D), 4, force_path=path)
+        assert not torch.isnan(out.float()).any()
+        kz, vz = torch.nan_to_num(kc, nan=0.0), torch.nan_to_num(vc, nan=0.0)
+        ref, _ = oracle.paged_ref(q.cpu(), kz.cpu(), vz.cpu(), tbl.cpu(), ctx.cpu())
+        assert_close_o(out, ref, torch.float16)
+
+
+@pytest.mark.parametrize("path", [1, 2])
+def test_paged_kv_shards_both_families(path):
+    from fa_b200 import interface
+
+    q, kc, vc, table, ctx = make_paged(2, 8, 2, 128, 16, [1500, 700], seed=8)
+    whole, _ = oracle.paged_ref(q.cpu(), kc.cpu(), vc.cpu(), table.cpu(), ctx.cpu())
+    G = 4
+    parts = [interface._paged_launch(q, kc, vc, table, ctx, 1 / math.sqrt(128), 2, first_block=r, block_step=G,
+                                     want_lse=True, out_f32=True, force_path=path) for r in range(G)]
+    o, _ = oracle.combine_ref(torch.stack([p[0] for p in parts]).cpu(), torch.stack([p[1] for p in parts]).cpu())
+    assert max_abs(o, whole) <= 2e-3
