@@ -130,8 +130,13 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     mbar_fence_init();
   }
   if (kPaged) {
-    // V tiles may be read at rows no load ever wrote (keys past the context): start the ring from zeros
-    for (int i = tid; i < kSlots * kTileBytes / 16; i += kThreads) reinterpret_cast<uint4*>(sRing)[i] = make_uint4(0, 0, 0, 0);
+    // V tiles (the odd slots: kSlots is even) may be read at rows no load ever wrote (keys past the context):
+    // start them from zeros
+    static_assert(kSlots % 2 == 0, "K and V tiles must keep to their own slots");
+    for (int i = tid; i < (kSlots / 2) * (kTileBytes / 16); i += kThreads) {
+      const int slot = 2 * (i / (kTileBytes / 16)) + 1, w = i % (kTileBytes / 16);
+      reinterpret_cast<uint4*>(sRing + slot * kTileBytes)[w] = make_uint4(0, 0, 0, 0);
+    }
     fence_proxy_async_smem();
   }
   if (warp == 9) {
@@ -288,6 +293,17 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     const float scale_log2 = a.softmax_scale * kLog2e;
     float m_used = kNegInf, l = 0.f;
     bool ok = true;
+    // paged: columns of this row's kv head when every token of the tile is readable
+    uint32_t full_pat[4] = {0u, 0u, 0u, 0u};
+    const int my_hk = kPaged ? min(row, a.heads_q - 1) / a.group : 0;
+    if (kPaged) {
+      for (int tok = 0; tok < a.upt * a.tpt; ++tok) {
+        const int c = tok * a.heads_kv + my_hk;
+#pragma unroll
+        for (int w = 0; w < 4; ++w)
+          if ((c >> 5) == w) full_pat[w] |= 1u << (c & 31);
+      }
+    }
 
     for (int i = 0; i < n_mine; ++i) {
       const int t = 2 * i + s, j = jlo + t;
@@ -305,13 +321,20 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         // column = (unit * tpt + token) * heads_kv + kv head: this row only sees the columns of its own kv head,
         // and of those only the readable tokens
         const int kslot = (2 * t) % kSlots;
-        const int my_hk = min(row, a.heads_q - 1) / a.group;
-        vmask[0] = vmask[1] = vmask[2] = vmask[3] = 0u;
-        for (int u = 0; u < a.upt; ++u) {
-          const int nv = nval_s[kslot][u];
-          for (int tok = 0; tok < nv; ++tok) {
-            const int c = (u * a.tpt + tok) * a.heads_kv + my_hk;
-            vmask[c >> 5] |= 1u << (c & 31);
+        bool all_full = true;
+        for (int u = 0; u < a.upt; ++u) all_full = all_full && (nval_s[kslot][u] == a.tpt);
+#pragma unroll
+        for (int w = 0; w < 4; ++w) vmask[w] = full_pat[w];
+        if (!all_full) {
+          vmask[0] = vmask[1] = vmask[2] = vmask[3] = 0u;
+          for (int u = 0; u < a.upt; ++u) {
+            const int nv = nval_s[kslot][u];
+            for (int tok = 0; tok < nv; ++tok) {
+              const int c = (u * a.tpt + tok) * a.heads_kv + my_hk;
+#pragma unroll
+              for (int w = 0; w < 4; ++w)
+                if ((c >> 5) == w) vmask[w] |= 1u << (c & 31);
+            }
           }
         }
         // the K slot (and its counts) may be reused once every thread of this stream has read them
