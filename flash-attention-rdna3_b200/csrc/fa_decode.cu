@@ -8,6 +8,8 @@
 //
 // Semantics: fa_rdna3/kernels/decode.py:13-125 (partials are normalised, LSE is natural-log and -inf
 // for an empty slice; the merge ignores -inf partials and returns zeros when every slice is empty).
+#include <mutex>
+
 #include "fa_common.cuh"
 
 namespace fa {
@@ -634,4 +636,82 @@ int launch_decode_paged(const fa_paged_params& p, cudaStream_t stream) {
   return rc;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Split-K decode for callers that cannot allocate device memory.
+//
+// Some callers of a decode step may not call cudaMalloc (or anything that allocates) at the point where
+// they run attention: code that executes inside a serving engine's pre-sized arena, a plug-in that is only
+// handed input and output buffers, or a caller in a latency-critical loop where an allocator call (and the
+// device synchronisation it can imply) is not acceptable. Split-K decode needs scratch for the per-slice
+// partial results; this variant keeps that scratch in a fixed array that is part of the library image.
+//
+// The array lives in every GPU context that loads the library, from load until exit: kNoAllocScratchFloats
+// floats (8 MiB). A problem needs num_splits * batch * heads_q * seqlen_q * (head_dim + 1) floats and is
+// rejected when that is more. All calls on a device share the array and it keeps what the last call wrote,
+// so two calls whose kernels may overlap on the GPU (different streams, or graphs replayed concurrently)
+// race; calls on one stream are safe. Nothing in it has to start from zero: every slice of every row writes
+// its partial and its LSE before the merge reads them.
+//
+// In host code the array's name is only a handle, not a device address. The first call on a device (with
+// that device current) asks the runtime for the real address with cudaGetSymbolAddress and caches it per
+// device; make that first call before any stream capture starts.
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+constexpr size_t kNoAllocScratchFloats = size_t(2) << 20;  // 2 Mi floats = 8 MiB
+static __device__ __align__(256) float g_noalloc_scratch[kNoAllocScratchFloats];
+
+constexpr int kMaxDevices = 64;
+float* g_noalloc_ptr[kMaxDevices] = {};
+std::mutex g_noalloc_mutex;
+
+// Device address of the scratch array in the current device's context, or nullptr with the error set.
+float* noalloc_scratch_for_current_device() {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    set_error(FA_ERR_DEVICE, "cannot identify the current CUDA device: %s", cudaGetErrorString(e));
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (g_noalloc_ptr[dev] == nullptr) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+    if (e != cudaSuccess || ptr == nullptr) {
+      set_error(FA_ERR_DEVICE, "cudaGetSymbolAddress failed for the decode scratch array: %s", cudaGetErrorString(e));
+      return nullptr;
+    }
+    g_noalloc_ptr[dev] = static_cast<float*>(ptr);
+  }
+  return g_noalloc_ptr[dev];
+}
+
+}  // namespace
+
+int launch_decode_splitk_noalloc(const fa_decode_params& p, cudaStream_t stream) {
+  if (p.num_splits < 1) return set_error(FA_ERR_INVALID_ARGUMENT, "num_splits must be at least 1");
+  const size_t rows = (size_t)p.batch * p.heads_q * p.seqlen_q;
+  const size_t need = (size_t)p.num_splits * rows * ((size_t)p.head_dim + 1);
+  if (need > kNoAllocScratchFloats)
+    return set_error(FA_ERR_UNSUPPORTED,
+                     "decode without allocation: num_splits*batch*heads_q*seqlen_q*(head_dim+1) = %zu floats exceeds the "
+                     "built-in scratch of %zu floats; use fewer splits or fa_decode_splitk with caller scratch",
+                     need, kNoAllocScratchFloats);
+  float* scratch = noalloc_scratch_for_current_device();
+  if (scratch == nullptr) return FA_ERR_DEVICE;
+  fa_decode_params q = p;
+  q.o_partial = scratch;                                        // (num_splits, rows, head_dim)
+  q.lse_partial = scratch + (size_t)p.num_splits * rows * p.head_dim;  // (num_splits, rows)
+  return launch_decode_splitk(q, stream);
+}
+
 }  // namespace fa
+
+extern "C" int32_t fa_decode_splitk_noalloc(const fa_decode_params* p, void* stream) {
+  if (p == nullptr) return fa::set_error(FA_ERR_INVALID_ARGUMENT, "params is NULL");
+  if (p->batch <= 0 || p->heads_q <= 0 || p->heads_kv <= 0 || p->seqlen_q <= 0 || p->seqlen_k <= 0 || p->head_dim <= 0)
+    return fa::set_error(FA_ERR_INVALID_ARGUMENT, "batch, heads, sequence lengths and head_dim must be positive");
+  if (p->q == nullptr || p->k == nullptr || p->v == nullptr || p->out == nullptr)
+    return fa::set_error(FA_ERR_INVALID_ARGUMENT, "q, k, v and out must not be NULL");
+  return fa::launch_decode_splitk_noalloc(*p, static_cast<cudaStream_t>(stream));
+}

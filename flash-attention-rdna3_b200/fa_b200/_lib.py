@@ -111,6 +111,7 @@ SYMBOLS = {
     "fa_varlen_fwd": (C.c_int32, [C.POINTER(AttnParams), C.c_void_p]),
     "fa_varlen_bwd": (C.c_int32, [C.POINTER(AttnParams), C.c_void_p]),
     "fa_decode_splitk": (C.c_int32, [C.POINTER(DecodeParams), C.c_void_p]),
+    "fa_decode_splitk_noalloc": (C.c_int32, [C.POINTER(DecodeParams), C.c_void_p]),
     "fa_combine": (C.c_int32, [C.POINTER(CombineParams), C.c_void_p]),
     "fa_decode_paged": (C.c_int32, [C.POINTER(PagedParams), C.c_void_p]),
     "fa_tiny_fwd": (C.c_int32, [C.POINTER(TinyParams), C.c_void_p]),

@@ -207,6 +207,17 @@ FA_API int32_t fa_varlen_bwd(const fa_attn_params* p, void* stream);
    fa_rdna3/interface.py:457-478 (kernels fa_rdna3/kernels/decode.py:13-125). */
 FA_API int32_t fa_decode_splitk(const fa_decode_params* p, void* stream);
 
+/* The same split-K decode for callers that must not allocate device memory (code running inside a pre-sized
+   arena, plug-ins that only receive input and output buffers, latency-critical loops). It has no counterpart
+   in the reference, which always allocates its partial buffers with torch.empty (fa_rdna3/interface.py:451-455).
+   p->o_partial and p->lse_partial are ignored: the partials go to an 8 MiB array built into the library, which
+   every GPU that loads the library holds until exit. The call is refused (FA_ERR_UNSUPPORTED) when
+   num_splits * batch * heads_q * seqlen_q * (head_dim + 1) exceeds 2 Mi floats. It calls no allocator.
+   All calls on a device share that array: calls whose kernels can overlap on the GPU race, calls on one stream
+   do not. The first call on each device looks the array's address up (cudaGetSymbolAddress) with that device
+   current; make it before any stream capture begins. */
+FA_API int32_t fa_decode_splitk_noalloc(const fa_decode_params* p, void* stream);
+
 /* Stand-alone LSE merge; also merges per-GPU shard partials. Replaces the _attention_combine launch,
    fa_rdna3/kernels/decode.py:80-125. */
 FA_API int32_t fa_combine(const fa_combine_params* p, void* stream);
