@@ -38,7 +38,7 @@ constexpr int kStages = 4;
 constexpr uint32_t kFull = 0xffffffffu;
 
 struct BwdArgs {
-  int varlen, heads_q, heads_kv, seqlen_q, seqlen_k, total_q, total_k;
+  int varlen, batch, heads_q, heads_kv, seqlen_q, seqlen_k, total_q, total_k;
   const int32_t* cu_q;
   const int32_t* cu_k;
   const float* lse;
@@ -439,6 +439,57 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q64, const __grid_consta
 // =============================================================================================
 // dQ
 // =============================================================================================
+// Item a persistent CTA takes in its round-th turn: rounds alternate direction over the CTAs ("snake"), so with
+// items ordered longest first every CTA gets nearly the same total length. An index past the item count ends the
+// CTA's walk (later rounds only hold larger indices).
+__device__ __forceinline__ int snake_item(int round, int cta, int num_ctas) {
+  return round * num_ctas + ((round & 1) ? num_ctas - 1 - cta : cta);
+}
+
+// Work item of the persistent dQ kernel: one 128-query tile of one (batch, head).
+struct DqItem {
+  int b, h, hk, q0, q_start, k_start, Sq, Sk, slo, n_total;
+  bool valid;
+};
+
+__device__ __forceinline__ DqItem dq_item(const BwdArgs& a, int w) {
+  DqItem it;
+  const int bh_count = a.batch * a.heads_q;
+  const int qtile = a.num_tiles - 1 - w / bh_count;  // items are dealt longest (causal) rows first
+  const int bh = w % bh_count;
+  it.b = bh / a.heads_q;
+  it.h = bh % a.heads_q;
+  it.hk = it.h / (a.heads_q / a.heads_kv);
+  it.q_start = it.k_start = 0;
+  it.Sq = a.seqlen_q;
+  it.Sk = a.seqlen_k;
+  if (a.varlen) {
+    bounded_sequence(a.cu_q, it.b, a.total_q, &it.q_start, &it.Sq);
+    bounded_sequence(a.cu_k, it.b, a.total_k, &it.k_start, &it.Sk);
+  }
+  it.q0 = qtile * 128;
+  it.valid = it.q0 < it.Sq;
+  it.slo = it.n_total = 0;
+  if (it.valid) {
+    const int off = it.Sk - it.Sq;
+    const int r1 = min(it.q0 + 127, it.Sq - 1);
+    int khi = it.Sk, klo = 0;
+    if (a.causal) khi = min(khi, r1 + off + 1);
+    else if (a.wr >= 0) khi = min(khi, r1 + off + a.wr + 1);
+    if (a.wl >= 0) klo = max(0, it.q0 + off - a.wl);
+    khi = max(khi, 0);
+    const int slo = klo / 64, shi = (khi + 63) / 64;
+    if (shi > slo) {
+      it.slo = slo;
+      it.n_total = shi - slo;
+    }
+  }
+  return it;
+}
+
+// Persistent: gridDim.x CTAs (one per SM) each walk items blockIdx.x, blockIdx.x + gridDim.x, ... All pipeline
+// counters (ring position, score-buffer parity, accumulator uses) run on across items, so the producer prefetches
+// the next item's operands and the MMA warp starts its score MMAs while the compute groups still write out dQ.
 template <typename T, int D, bool kMods>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k64,
@@ -453,33 +504,18 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
   uint8_t* sQ = smem;
   uint8_t* sdO = smem + kTileBytes;
   uint8_t* sRing = smem + 2 * kTileBytes;  // [stage][K step | V step]
-  __shared__ uint64_t qdo_full, kv_full[kStages], kv_empty[kStages], s_full[2], ds_full[2], acc_done;
+  __shared__ uint64_t qdo_full, qdo_empty, kv_full[kStages], kv_empty[kStages], s_full[2], ds_full[2], acc_done,
+      acc_free;
   __shared__ uint32_t tmem_base_s;
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
-  const int qtile = a.num_tiles - 1 - blockIdx.y;  // longest (causal) rows first
-  const int b = blockIdx.x / a.heads_q, h = blockIdx.x % a.heads_q;
-  const int hk = h / (a.heads_q / a.heads_kv);
-
-  int q_start = 0, k_start = 0, Sq = a.seqlen_q, Sk = a.seqlen_k;
-  if (a.varlen) {
-    bounded_sequence(a.cu_q, b, a.total_q, &q_start, &Sq);
-    bounded_sequence(a.cu_k, b, a.total_k, &k_start, &Sk);
-  }
-  const int q0 = qtile * 128;
-  if (q0 >= Sq) return;
-  const int tb = a.varlen ? 0 : b;
-
-  const ScoreMods mods = make_mods(a, b, h, Sq, Sk);
-  int klo, khi;
-  key_range_for_rows(mods, q0, min(q0 + 127, Sq - 1), &klo, &khi);
-  int slo = klo / 64, shi = (khi + 63) / 64;
-  if (shi <= slo) slo = shi = 0;
-  const int n_total = shi - slo;
+  const int n_items = a.num_tiles * a.batch * a.heads_q;
 
   if (tid == 0) {
     mbar_init(&qdo_full, 1);
+    mbar_init(&qdo_empty, 1);
     mbar_init(&acc_done, 1);
+    mbar_init(&acc_free, 256);
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s_full[i], 1);
@@ -503,42 +539,60 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
   constexpr uint32_t kColS = 0, kColDP = 128, kColDQ = 256;
 
   if (warp == 8) {
-    if (lane == 0 && n_total > 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
       tma_prefetch_desc(&map_k64);
       tma_prefetch_desc(&map_v64);
-      mbar_arrive_expect_tx(&qdo_full, 2 * kTileBytes);
-#pragma unroll
-      for (int c = 0; c < kChunks; ++c) {
-        tma_load_4d(sQ + c * 16384, &map_q, &qdo_full, c * 64, q_start + q0, h, tb);
-        tma_load_4d(sdO + c * 16384, &map_do, &qdo_full, c * 64, q_start + q0, h, tb);
-      }
-      for (int n = 0; n < n_total; ++n) {
-        const int stage = n % kStages;
-        if (!mbar_wait(&kv_empty[stage], ((n / kStages) & 1) ^ 1)) {
-          report_timeout(a.status, 301);
+      int ng = 0;       // global step counter (ring position)
+      int used = 0;     // items that used the pipeline so far
+      bool ok = true;
+      for (int round = 0; ok; ++round) {
+        const int w = snake_item(round, blockIdx.x, gridDim.x);
+        if (w >= n_items) break;
+        const DqItem it = dq_item(a, w);
+        if (!it.valid || it.n_total == 0) continue;
+        const int tb = a.varlen ? 0 : it.b;
+        if (!mbar_wait(&qdo_empty, (used & 1) ^ 1)) {
+          report_timeout(a.status, 300);
           break;
         }
-        const int row = k_start + (slo + n) * 64;
-        uint8_t* dst = sRing + stage * 2 * kStepBytes;
-        mbar_arrive_expect_tx(&kv_full[stage], 2 * kStepBytes);
+        mbar_arrive_expect_tx(&qdo_full, 2 * kTileBytes);
 #pragma unroll
         for (int c = 0; c < kChunks; ++c) {
-          tma_load_4d(dst + c * 8192, &map_k64, &kv_full[stage], c * 64, row, hk, tb);
-          tma_load_4d(dst + kStepBytes + c * 8192, &map_v64, &kv_full[stage], c * 64, row, hk, tb);
+          tma_load_4d(sQ + c * 16384, &map_q, &qdo_full, c * 64, it.q_start + it.q0, it.h, tb);
+          tma_load_4d(sdO + c * 16384, &map_do, &qdo_full, c * 64, it.q_start + it.q0, it.h, tb);
         }
+        for (int n = 0; n < it.n_total; ++n, ++ng) {
+          const int stage = ng % kStages;
+          if (!mbar_wait(&kv_empty[stage], ((ng / kStages) & 1) ^ 1)) {
+            report_timeout(a.status, 301);
+            ok = false;
+            break;
+          }
+          const int row = it.k_start + (it.slo + n) * 64;
+          uint8_t* dst = sRing + stage * 2 * kStepBytes;
+          mbar_arrive_expect_tx(&kv_full[stage], 2 * kStepBytes);
+#pragma unroll
+          for (int c = 0; c < kChunks; ++c) {
+            tma_load_4d(dst + c * 8192, &map_k64, &kv_full[stage], c * 64, row, it.hk, tb);
+            tma_load_4d(dst + kStepBytes + c * 8192, &map_v64, &kv_full[stage], c * 64, row, it.hk, tb);
+          }
+        }
+        ++used;
       }
     }
   } else if (warp == 9) {
-    if (lane == 0 && n_total > 0) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc(DType<T>::kFormat, 128, 64, 0, 0);
       constexpr uint32_t idesc_acc = make_idesc(DType<T>::kFormat, 128, D, 0, 1);
       const uint32_t q_addr = smem_u32(sQ), do_addr = smem_u32(sdO), ring_addr = smem_u32(sRing);
-      bool ok = mbar_wait(&qdo_full, 0);
-      if (!ok) report_timeout(a.status, 302);
+      int ng0 = 0, used = 0;
+      bool ok = true;
 
-      auto issue_scores = [&](int n) {
-        const int stage = n % kStages, buf = n & 1;
-        if (!mbar_wait(&kv_full[stage], (n / kStages) & 1)) {
+      auto issue_scores = [&](int ng) {  // global step ng: S and dP into buffer ng & 1
+        const int stage = ng % kStages, buf = ng & 1;
+        if (!mbar_wait(&kv_full[stage], (ng / kStages) & 1)) {
           report_timeout(a.status, 303);
           ok = false;
           return;
@@ -560,130 +614,190 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         tc_commit(&s_full[buf]);
       };
 
-      if (ok) issue_scores(0);
-      if (ok && n_total > 1) issue_scores(1);
-      for (int n = 0; n < n_total && ok; ++n) {
-        const int stage = n % kStages, buf = n & 1;
-        if (!mbar_wait(&ds_full[buf], (n >> 1) & 1)) {
-          report_timeout(a.status, 304);
+      for (int round = 0; ok; ++round) {
+        const int w = snake_item(round, blockIdx.x, gridDim.x);
+        if (w >= n_items) break;
+        const DqItem it = dq_item(a, w);
+        if (!it.valid || it.n_total == 0) continue;
+        if (!mbar_wait(&qdo_full, used & 1)) {
+          report_timeout(a.status, 302);
           break;
         }
         tc_fence_after_sync();
-        const uint32_t k_addr = ring_addr + stage * 2 * kStepBytes;
+        issue_scores(ng0);
+        if (ok && it.n_total > 1) issue_scores(ng0 + 1);
+        if (ok && it.n_total <= 2) tc_commit(&qdo_empty);  // every score MMA of the item is issued: Q/dO may be replaced
+        for (int n = 0; n < it.n_total && ok; ++n) {
+          const int ng = ng0 + n, stage = ng % kStages, buf = ng & 1;
+          if (!mbar_wait(&ds_full[buf], (ng >> 1) & 1)) {
+            report_timeout(a.status, 304);
+            ok = false;
+            break;
+          }
+          if (n == 0 && used > 0 && !mbar_wait(&acc_free, (used - 1) & 1)) {  // previous item's dQ has been read out
+            report_timeout(a.status, 307);
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t k_addr = ring_addr + stage * 2 * kStepBytes;
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)  // 16 keys per instruction
-          mma_ts(tmem_base + kColDQ, tmem_base + kColS + buf * 64 + kk * 8,
-                 make_smem_desc(k_addr + kk * 2048, 8192, 1024), idesc_acc, !(n == 0 && kk == 0));
-        tc_commit(&kv_empty[stage]);
-        if (n + 2 < n_total) issue_scores(n + 2);
+          for (int kk = 0; kk < 4; ++kk)  // 16 keys per instruction
+            mma_ts(tmem_base + kColDQ, tmem_base + kColS + buf * 64 + kk * 8,
+                   make_smem_desc(k_addr + kk * 2048, 8192, 1024), idesc_acc, !(n == 0 && kk == 0));
+          tc_commit(&kv_empty[stage]);
+          if (n + 2 < it.n_total) {
+            issue_scores(ng + 2);
+            if (ok && n + 3 == it.n_total) tc_commit(&qdo_empty);
+          }
+        }
+        if (ok) tc_commit(&acc_done);
+        ng0 += it.n_total;
+        ++used;
       }
-      if (ok) tc_commit(&acc_done);
     }
   } else {
+    // ------------------------------------------------------------------ compute groups
     const int wg = warp / 4, w4 = warp % 4;
     const int q_row = w4 * 32 + lane;
-    const int i = q0 + q_row;
     const uint32_t lane_addr = static_cast<uint32_t>(w4 * 32) << 16;
     const uint32_t tS = tmem_base + lane_addr + kColS + wg * 64;
     const uint32_t tDP = tmem_base + lane_addr + kColDP + wg * 64;
-    const int64_t bo = a.varlen ? 0 : (int64_t)b;
-    const int off = Sk - Sq;
-    float nlse2 = kNegInf, ndelta = 0.f;
-    if (i < Sq) {
-      const float l = a.lse[bo * a.l_sb + (int64_t)h * a.l_sh + (int64_t)(q_start + i) * a.l_ss];
-      nlse2 = (l == kNegInf) ? kNegInf : -l * kLog2e;
-      ndelta = -a.delta[bo * a.d_sb + (int64_t)h * a.d_sh + (int64_t)(q_start + i) * a.d_ss];
-    }
-    const uint64_t sc2 = pack_f32x2(mods.scale_log2, mods.scale_log2);
-    const uint64_t nl2 = pack_f32x2(nlse2, nlse2), nd2 = pack_f32x2(ndelta, ndelta);
+    int ng0 = 0, used = 0;
     bool ok = true;
-    for (int n = wg; n < n_total; n += 2) {
-      const int ks = (slo + n) * 64;
-      const bool w_ok = mbar_wait(&s_full[wg], (n >> 1) & 1);
+
+    for (int round = 0; ok; ++round) {
+      const int w = snake_item(round, blockIdx.x, gridDim.x);
+      if (w >= n_items) break;
+      const DqItem it = dq_item(a, w);
+      if (!it.valid) continue;
+      const int i = it.q0 + q_row;
+      const int64_t bo = a.varlen ? 0 : (int64_t)it.b;
+      T* row_ptr = reinterpret_cast<T*>(a.dq) + bo * a.dq_sb + (int64_t)it.h * a.dq_sh + (int64_t)(it.q_start + i) * a.dq_ss;
+      constexpr int kSlices = D / 32 / 2;  // each group writes half of the head dimension
+      if (it.n_total == 0) {  // rows that see no key: dQ = 0
+        if (i < it.Sq) {
+          uint32_t z[32];
+#pragma unroll
+          for (int e = 0; e < 32; ++e) z[e] = 0u;
+#pragma unroll
+          for (int cc = 0; cc < kSlices; ++cc) store_row_slice<T>(row_ptr + (wg * kSlices + cc) * 32, z, 0.f);
+        }
+        continue;
+      }
+      const ScoreMods mods = make_mods(a, it.b, it.h, it.Sq, it.Sk);
+      const int off = it.Sk - it.Sq;
+      float nlse2 = kNegInf, ndelta = 0.f;
+      if (i < it.Sq) {
+        const float l = a.lse[bo * a.l_sb + (int64_t)it.h * a.l_sh + (int64_t)(it.q_start + i) * a.l_ss];
+        nlse2 = (l == kNegInf) ? kNegInf : -l * kLog2e;
+        ndelta = -a.delta[bo * a.d_sb + (int64_t)it.h * a.d_sh + (int64_t)(it.q_start + i) * a.d_ss];
+      }
+      const uint64_t sc2 = pack_f32x2(mods.scale_log2, mods.scale_log2);
+      const uint64_t nl2 = pack_f32x2(nlse2, nlse2), nd2 = pack_f32x2(ndelta, ndelta);
+
+      // this group takes the global steps whose parity equals its index
+      const int first = ((ng0 & 1) == wg) ? 0 : 1;
+      for (int n = first; n < it.n_total; n += 2) {
+        const int ng = ng0 + n;
+        const int ks = (it.slo + n) * 64;
+        const bool w_ok = mbar_wait(&s_full[wg], (ng >> 1) & 1);
+        if (!__all_sync(kFull, w_ok)) {
+          report_timeout(a.status, 305);
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        // keys this query row keeps: one interval [c_lo, c_hi] of the step's 64 columns
+        const bool masked = block_needs_mask(mods, it.q0, 128, ks, 64);
+        int c_lo = 0, c_hi = 63;
+        if (masked) {
+          c_hi = min(c_hi, it.Sk - 1 - ks);
+          if (a.causal) c_hi = min(c_hi, i + off - ks);
+          else if (a.wr >= 0) c_hi = min(c_hi, i + off + a.wr - ks);
+          if (a.wl >= 0) c_lo = max(0, i + off - a.wl - ks);
+        }
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t s[32], dp[32];
+          tmem_ld32(tS + c * 32, s);
+          tmem_ld32(tDP + c * 32, dp);
+          tc_wait_ld_regs(s);
+          tc_wait_ld_regs(dp);
+          uint32_t dsk[16];
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            const int col = c * 32 + 2 * e;
+            float d0, d1;
+            if (kMods) {
+              float p0, p1;
+              bwd_element_mods(mods, !masked || (col >= c_lo && col <= c_hi), __uint_as_float(s[2 * e]),
+                               __uint_as_float(dp[2 * e]), nlse2, ndelta, i, ks + col, &p0, &d0);
+              bwd_element_mods(mods, !masked || (col + 1 >= c_lo && col + 1 <= c_hi), __uint_as_float(s[2 * e + 1]),
+                               __uint_as_float(dp[2 * e + 1]), nlse2, ndelta, i, ks + col + 1, &p1, &d1);
+            } else {
+              const uint64_t x2 = fma_f32x2(pack_u32x2(s[2 * e], s[2 * e + 1]), sc2, nl2);
+              float x0, x1;
+              unpack_f32x2(x2, &x0, &x1);
+              float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+              if (masked) {
+                if (col < c_lo || col > c_hi) p0 = 0.f;
+                if (col + 1 < c_lo || col + 1 > c_hi) p1 = 0.f;
+              }
+              const uint64_t dd = add_f32x2(pack_u32x2(dp[2 * e], dp[2 * e + 1]), nd2);
+              unpack_f32x2(mul_f32x2(pack_f32x2(p0, p1), dd), &d0, &d1);
+            }
+            dsk[e] = DType<T>::pack2(d0, d1);
+          }
+          tmem_st16(tS + c * 16, dsk);
+        }
+        tc_wait_st();
+        tc_fence_before_sync();
+        mbar_arrive(&ds_full[wg]);
+      }
+      if (!ok) break;
+
+      // epilogue of the item: dQ * softmax_scale -> global, then hand the accumulator back
+      const bool w_ok = mbar_wait(&acc_done, used & 1);
       if (!__all_sync(kFull, w_ok)) {
-        report_timeout(a.status, 305);
+        report_timeout(a.status, 306);
         ok = false;
         break;
       }
       tc_fence_after_sync();
-      // keys this query row keeps: one interval [c_lo, c_hi] of the step's 64 columns
-      const bool masked = block_needs_mask(mods, q0, 128, ks, 64);
-      int c_lo = 0, c_hi = 63;
-      if (masked) {
-        c_hi = min(c_hi, Sk - 1 - ks);
-        if (a.causal) c_hi = min(c_hi, i + off - ks);
-        else if (a.wr >= 0) c_hi = min(c_hi, i + off + a.wr - ks);
-        if (a.wl >= 0) c_lo = max(0, i + off - a.wl - ks);
-      }
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t s[32], dp[32];
-        tmem_ld32(tS + c * 32, s);
-        tmem_ld32(tDP + c * 32, dp);
-        tc_wait_ld_regs(s);
-        tc_wait_ld_regs(dp);
-        uint32_t dsk[16];
-#pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          const int col = c * 32 + 2 * e;
-          float d0, d1;
-          if (kMods) {
-            float p0, p1;
-            bwd_element_mods(mods, !masked || (col >= c_lo && col <= c_hi), __uint_as_float(s[2 * e]),
-                             __uint_as_float(dp[2 * e]), nlse2, ndelta, i, ks + col, &p0, &d0);
-            bwd_element_mods(mods, !masked || (col + 1 >= c_lo && col + 1 <= c_hi), __uint_as_float(s[2 * e + 1]),
-                             __uint_as_float(dp[2 * e + 1]), nlse2, ndelta, i, ks + col + 1, &p1, &d1);
-          } else {
-            const uint64_t x2 = fma_f32x2(pack_u32x2(s[2 * e], s[2 * e + 1]), sc2, nl2);
-            float x0, x1;
-            unpack_f32x2(x2, &x0, &x1);
-            float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
-            if (masked) {
-              if (col < c_lo || col > c_hi) p0 = 0.f;
-              if (col + 1 < c_lo || col + 1 > c_hi) p1 = 0.f;
-            }
-            const uint64_t dd = add_f32x2(pack_u32x2(dp[2 * e], dp[2 * e + 1]), nd2);
-            unpack_f32x2(mul_f32x2(pack_f32x2(p0, p1), dd), &d0, &d1);
-          }
-          dsk[e] = DType<T>::pack2(d0, d1);
-        }
-        tmem_st16(tS + c * 16, dsk);
-      }
-      tc_wait_st();
-      tc_fence_before_sync();
-      mbar_arrive(&ds_full[wg]);
-    }
-
-    if (n_total > 0) {
-      const bool w_ok = ok && mbar_wait(&acc_done, 0);
-      if (!__all_sync(kFull, w_ok)) {
-        if (ok) report_timeout(a.status, 306);
-        ok = false;
-      }
-    }
-    if (ok) {
-      tc_fence_after_sync();
-      T* row_ptr = reinterpret_cast<T*>(a.dq) + bo * a.dq_sb + (int64_t)h * a.dq_sh + (int64_t)(q_start + i) * a.dq_ss;
-      constexpr int kSlices = D / 32 / 2;  // each group writes half of the head dimension
 #pragma unroll
       for (int cc = 0; cc < kSlices; ++cc) {
         const int c = wg * kSlices + cc;
         uint32_t o[32];
-        if (n_total > 0) {
-          tmem_ld32(tmem_base + lane_addr + kColDQ + c * 32, o);
-          tc_wait_ld_regs(o);
-        } else {
-#pragma unroll
-          for (int e = 0; e < 32; ++e) o[e] = 0u;
+        tmem_ld32(tmem_base + lane_addr + kColDQ + c * 32, o);
+        tc_wait_ld_regs(o);
+        if (cc == kSlices - 1) {
+          tc_fence_before_sync();
+          mbar_arrive(&acc_free);  // this thread's last read of dQ is in registers
         }
-        if (i < Sq) store_row_slice<T>(row_ptr + c * 32, o, a.softmax_scale);
+        if (i < it.Sq) store_row_slice<T>(row_ptr + c * 32, o, a.softmax_scale);
       }
+      ng0 += it.n_total;
+      ++used;
     }
   }
 
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 9) tmem_dealloc(tmem_base, 512);
+}
+
+// Number of SMs of the current device (cached per device).
+int sm_count() {
+  static int cached[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
 }
 
 template <typename T, int D, bool kMods>
@@ -725,7 +839,8 @@ int launch_typed(const fa_attn_params& p, const BwdArgs& a0, int parts, cudaStre
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "backward smem opt-in failed: %s", cudaGetErrorString(e));
     a.num_tiles = (p.seqlen_q + 127) / 128;
-    kern<<<dim3(p.batch * p.heads_q, a.num_tiles), kBwdThreads, smem, stream>>>(mq, mk, mv, mdo, a);
+    const int n_items = a.num_tiles * p.batch * p.heads_q;
+    kern<<<dim3(n_items < sm_count() ? n_items : sm_count()), kBwdThreads, smem, stream>>>(mq, mk, mv, mdo, a);
     e = cudaGetLastError();
     if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "dQ launch failed: %s", cudaGetErrorString(e));
   }
@@ -751,6 +866,7 @@ bool bwd_tcgen05_supported(const fa_attn_params& p) {
 int launch_bwd_tcgen05(const fa_attn_params& p, int parts, cudaStream_t stream) {
   BwdArgs a;
   a.varlen = p.varlen;
+  a.batch = p.batch;
   a.heads_q = p.heads_q;
   a.heads_kv = p.heads_kv;
   a.seqlen_q = p.seqlen_q;
