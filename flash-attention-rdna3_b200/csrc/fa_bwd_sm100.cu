@@ -34,7 +34,6 @@ namespace fa {
 namespace {
 
 constexpr int kBwdThreads = 320;
-constexpr int kStages = 4;
 constexpr uint32_t kFull = 0xffffffffu;
 
 struct BwdArgs {
@@ -139,23 +138,114 @@ __device__ __forceinline__ void group_sync(int wg) {
 // =============================================================================================
 // dK / dV
 // =============================================================================================
+// 32 raw scores of one row -> 16 packed 16-bit probabilities: p = exp2(s * scale_log2 + nlse[col]) with columns outside
+// [c_lo, c_hi] (numbered from col0) zeroed when kMasked. nlse points at the 32 per-column values in shared memory.
+template <typename T, bool kMasked>
+__device__ __forceinline__ void probs_chunk(const uint32_t (&s)[32], const float* nlse, uint64_t sc2, int col0, int c_lo,
+                                            int c_hi, uint32_t* pk) {
+#pragma unroll
+  for (int e4 = 0; e4 < 8; ++e4) {  // four columns at a time: one 16-byte read
+    const float4 nl = *reinterpret_cast<const float4*>(nlse + e4 * 4);
+    const float nls[4] = {nl.x, nl.y, nl.z, nl.w};
+#pragma unroll
+    for (int e2 = 0; e2 < 2; ++e2) {
+      const int e = e4 * 2 + e2;
+      const uint64_t x2 = fma_f32x2(pack_u32x2(s[2 * e], s[2 * e + 1]), sc2, pack_f32x2(nls[2 * e2], nls[2 * e2 + 1]));
+      float x0, x1;
+      unpack_f32x2(x2, &x0, &x1);
+      float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+      if (kMasked) {
+        const int col = col0 + 2 * e;
+        if (col < c_lo || col > c_hi) p0 = 0.f;
+        if (col + 1 < c_lo || col + 1 > c_hi) p1 = 0.f;
+      }
+      pk[e] = DType<T>::pack2(p0, p1);
+    }
+  }
+}
+
+// 32 raw dP values of one row and the matching packed probabilities -> 16 packed dS = p * (dp + ndelta[col]).
+template <typename T>
+__device__ __forceinline__ void dscore_chunk(const uint32_t (&dp)[32], const float* ndelta, const uint32_t* pk,
+                                             uint32_t (&dsk)[16]) {
+#pragma unroll
+  for (int e4 = 0; e4 < 8; ++e4) {
+    const float4 nd = *reinterpret_cast<const float4*>(ndelta + e4 * 4);
+    const float nds[4] = {nd.x, nd.y, nd.z, nd.w};
+#pragma unroll
+    for (int e2 = 0; e2 < 2; ++e2) {
+      const int e = e4 * 2 + e2;
+      const float2 pf = DType<T>::unpack2(pk[e]);
+      const uint64_t dd = add_f32x2(pack_u32x2(dp[2 * e], dp[2 * e + 1]), pack_f32x2(nds[2 * e2], nds[2 * e2 + 1]));
+      float d0, d1;
+      unpack_f32x2(mul_f32x2(pack_f32x2(pf.x, pf.y), dd), &d0, &d1);
+      dsk[e] = DType<T>::pack2(d0, d1);
+    }
+  }
+}
+
+// Shared-memory plan of the dK/dV kernel; everything is dynamic so that the tiles can take (almost) all of it.
+template <int D>
+struct DkdvSmem {
+  static constexpr int kChunks = D / 64;
+  static constexpr int kTileBytes = kChunks * 16384;  // one 128-row operand tile
+  static constexpr int kQStages = D == 128 ? 3 : 4;   // Q lives from S^T of its step to dK of the same step
+  static constexpr int kDoStages = D == 128 ? 2 : 3;
+  static constexpr int kOffK = 0;
+  static constexpr int kOffV = kTileBytes;
+  static constexpr int kOffQ = 2 * kTileBytes;
+  static constexpr int kOffDo = kOffQ + kQStages * kTileBytes;
+  static constexpr int kOffStage = kOffDo + kDoStages * kTileBytes;  // 128 x (-lse*log2e), 128 x (-delta)
+  static constexpr int kOffBars = kOffStage + 256 * 4;
+  static constexpr int kNumBars = 7 + 2 * kQStages + 2 * kDoStages;
+  static constexpr int kOffTmemPtr = kOffBars + kNumBars * 8;
+  static constexpr int kBytes = kOffTmemPtr + 8 + 1024;  // + slack to round the base up to 1024
+  static_assert(kBytes <= 232448, "dK/dV shared memory plan exceeds one CTA's 227 KB");
+};
+
+__device__ __forceinline__ void compute_sync() {
+  asm volatile("bar.sync 1, 256;" ::: "memory");  // the eight compute warps
+}
+
+// One CTA per 128-key tile of one (batch, kv head). The tensor pipe is kept busy by a two-phase software pipeline
+// over 128-query steps (step i of the pipe, all issued by one thread, in this order):
+//     dV  += P^T(i) dO(i)         needs phase 1 of step i
+//     S^T(i+1) = K Q(i+1)^T       overwrites P^T(i); phase 1 of step i+1 starts when it lands
+//     dK  += dS^T(i) Q(i)         needs phase 2 of step i
+//     dP^T(i+1) = V dO(i+1)^T     overwrites dS^T(i); phase 2 of step i+1 starts when it lands
+// so each elementwise phase overlaps two MMAs of the neighbouring steps and all 512 TMEM columns are in use
+// without double buffering: S^T/P^T [0,128), dP^T/dS^T [128,256), dK [256,256+D), dV [256+D,256+2D).
 template <typename T, int D, bool kMods>
 __global__ void __launch_bounds__(kBwdThreads, 1)
-bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q64, const __grid_constant__ CUtensorMap map_k,
-                const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do64,
+bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
                 const BwdArgs a) {
-  constexpr int kChunks = D / 64;
-  constexpr int kTileBytes = kChunks * 16384;  // resident 128-row tile
-  constexpr int kStepBytes = kChunks * 8192;   // streamed 64-row tile
+  using L = DkdvSmem<D>;
+  constexpr int kChunks = L::kChunks;
+  constexpr int kTileBytes = L::kTileBytes;
+  constexpr int kQS = L::kQStages, kDS = L::kDoStages;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sK = smem;
-  uint8_t* sV = smem + kTileBytes;
-  uint8_t* sRing = smem + 2 * kTileBytes;  // [stage][Q step | dO step]
-  __shared__ uint64_t kv_full, qdo_full[kStages], qdo_empty[kStages], s_full[2], p_full[2], acc_done;
-  __shared__ uint32_t tmem_base_s;
-  __shared__ __align__(16) float nlse_s[2][2][64], ndelta_s[2][2][64];  // [group][parity][query]
+  uint8_t* sK = smem + L::kOffK;
+  uint8_t* sV = smem + L::kOffV;
+  uint8_t* sQ = smem + L::kOffQ;
+  uint8_t* sDo = smem + L::kOffDo;
+  float* nlse_s = reinterpret_cast<float*>(smem + L::kOffStage);
+  float* ndelta_s = nlse_s + 128;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kOffBars);
+  uint64_t* k_full = bars + 0;
+  uint64_t* v_full = bars + 1;
+  uint64_t* s_full = bars + 2;
+  uint64_t* p_full = bars + 3;
+  uint64_t* dp_full = bars + 4;
+  uint64_t* ds_full = bars + 5;
+  uint64_t* acc_done = bars + 6;
+  uint64_t* q_full = bars + 7;
+  uint64_t* q_empty = q_full + kQS;
+  uint64_t* do_full = q_empty + kQS;
+  uint64_t* do_empty = do_full + kDS;
+  uint32_t* tmem_base_s = reinterpret_cast<uint32_t*>(smem + L::kOffTmemPtr);
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   const int ktile = blockIdx.y;
@@ -171,134 +261,160 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q64, const __grid_consta
   if (k0 >= Sk) return;
   const int tb = a.varlen ? 0 : b;
 
-  // 64-query steps that can see this key tile; the mask geometry does not depend on the head
+  // 128-query steps that can see this key tile; the mask geometry does not depend on the head
   ScoreMods mods = make_mods(a, b, hk * group, Sq, Sk);
   int ilo, ihi;
   query_range_for_keys(mods, k0, min(k0 + 127, Sk - 1), &ilo, &ihi);
-  int slo = ilo / 64, shi = (ihi + 63) / 64;
+  int slo = ilo / 128, shi = (ihi + 127) / 128;
   if (shi <= slo) slo = shi = 0;
   const int steps_per_head = shi - slo;
   const int n_total = steps_per_head * group;
 
   if (tid == 0) {
-    mbar_init(&kv_full, 1);
-    mbar_init(&acc_done, 1);
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&s_full[i], 1);
-      mbar_init(&p_full[i], 128);
+    mbar_init(k_full, 1);
+    mbar_init(v_full, 1);
+    mbar_init(s_full, 1);
+    mbar_init(p_full, 256);
+    mbar_init(dp_full, 1);
+    mbar_init(ds_full, 256);
+    mbar_init(acc_done, 1);
+    for (int i = 0; i < kQS; ++i) {
+      mbar_init(&q_full[i], 1);
+      mbar_init(&q_empty[i], 1);
     }
-#pragma unroll
-    for (int s = 0; s < kStages; ++s) {
-      mbar_init(&qdo_full[s], 1);
-      mbar_init(&qdo_empty[s], 1);
+    for (int i = 0; i < kDS; ++i) {
+      mbar_init(&do_full[i], 1);
+      mbar_init(&do_empty[i], 1);
     }
     mbar_fence_init();
   }
   if (warp == 9) {
-    tmem_alloc(&tmem_base_s, 512);
+    tmem_alloc(tmem_base_s, 512);
     tmem_relinquish();
   }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
-  const uint32_t tmem_base = tmem_base_s;
+  const uint32_t tmem_base = *tmem_base_s;
   constexpr uint32_t kColS = 0, kColDP = 128, kColDK = 256, kColDV = 256 + D;
 
   if (warp == 8) {
+    // ------------------------------------------------------------------ TMA producer
     if (lane == 0 && n_total > 0) {
-      tma_prefetch_desc(&map_q64);
-      tma_prefetch_desc(&map_do64);
-      mbar_arrive_expect_tx(&kv_full, 2 * kTileBytes);
+      tma_prefetch_desc(&map_q);
+      tma_prefetch_desc(&map_do);
+      auto load_tile = [&](uint8_t* dst, const CUtensorMap* map, uint64_t* bar, int row, int head) {
+        mbar_arrive_expect_tx(bar, kTileBytes);
 #pragma unroll
-      for (int c = 0; c < kChunks; ++c) {
-        tma_load_4d(sK + c * 16384, &map_k, &kv_full, c * 64, k_start + k0, hk, tb);
-        tma_load_4d(sV + c * 16384, &map_v, &kv_full, c * 64, k_start + k0, hk, tb);
-      }
+        for (int c = 0; c < kChunks; ++c) tma_load_4d(dst + c * 16384, map, bar, c * 64, row, head, tb);
+      };
+      load_tile(sK, &map_k, k_full, k_start + k0, hk);
       for (int n = 0; n < n_total; ++n) {
-        const int stage = n % kStages;
-        if (!mbar_wait(&qdo_empty[stage], ((n / kStages) & 1) ^ 1)) {
+        const int h = hk * group + n / steps_per_head;
+        const int row = q_start + (slo + n % steps_per_head) * 128;
+        const int qs = n % kQS, ds = n % kDS;
+        if (!mbar_wait(&q_empty[qs], ((n / kQS) & 1) ^ 1)) {
           report_timeout(a.status, 201);
           break;
         }
-        const int h = hk * group + n / steps_per_head;
-        const int row = q_start + (slo + n % steps_per_head) * 64;
-        uint8_t* dst = sRing + stage * 2 * kStepBytes;
-        mbar_arrive_expect_tx(&qdo_full[stage], 2 * kStepBytes);
-#pragma unroll
-        for (int c = 0; c < kChunks; ++c) {
-          tma_load_4d(dst + c * 8192, &map_q64, &qdo_full[stage], c * 64, row, h, tb);
-          tma_load_4d(dst + kStepBytes + c * 8192, &map_do64, &qdo_full[stage], c * 64, row, h, tb);
+        load_tile(sQ + qs * kTileBytes, &map_q, &q_full[qs], row, h);
+        if (n == 0) load_tile(sV, &map_v, v_full, k_start + k0, hk);
+        if (!mbar_wait(&do_empty[ds], ((n / kDS) & 1) ^ 1)) {
+          report_timeout(a.status, 207);
+          break;
         }
+        load_tile(sDo + ds * kTileBytes, &map_do, &do_full[ds], row, h);
       }
     }
   } else if (warp == 9) {
+    // ------------------------------------------------------------------ MMA issuer
     if (lane == 0 && n_total > 0) {
-      constexpr uint32_t idesc_s = make_idesc(DType<T>::kFormat, 128, 64, 0, 0);
+      constexpr uint32_t idesc_s = make_idesc(DType<T>::kFormat, 128, 128, 0, 0);
       constexpr uint32_t idesc_acc = make_idesc(DType<T>::kFormat, 128, D, 0, 1);
-      const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), ring_addr = smem_u32(sRing);
-      bool ok = mbar_wait(&kv_full, 0);
-      if (!ok) report_timeout(a.status, 202);
+      const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), q_base = smem_u32(sQ), do_base = smem_u32(sDo);
+      bool ok = true;
       PROF_DECL;
-
-      auto issue_scores = [&](int n) {  // S^T and dP^T of step n into buffer n & 1
-        const int stage = n % kStages, buf = n & 1;
-        PROF_MARK(2);
-        const bool got = mbar_wait(&qdo_full[stage], (n / kStages) & 1);
-        PROF_MARK(0);
-        if (!got) {
-          report_timeout(a.status, 203);
+      auto wait_or_report = [&](uint64_t* bar, int parity, int code) {
+        if (!ok) return;
+        if (!mbar_wait(bar, parity)) {
+          report_timeout(a.status, code);
           ok = false;
-          return;
         }
-        tc_fence_after_sync();
-        const uint32_t q_addr = ring_addr + stage * 2 * kStepBytes, do_addr = q_addr + kStepBytes;
+      };
+      auto scores = [&](uint32_t col, uint32_t a_addr, uint32_t b_addr) {  // [128 keys x 128 queries] = A B^T over D
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t offa = (kk / 4) * 16384 + (kk % 4) * 32, offb = (kk / 4) * 8192 + (kk % 4) * 32;
-          mma_ss(tmem_base + kColS + buf * 64, make_smem_desc(k_addr + offa, 16, 1024),
-                 make_smem_desc(q_addr + offb, 16, 1024), idesc_s, kk > 0);
+          const uint32_t o = (kk / 4) * 16384 + (kk % 4) * 32;
+          mma_ss(tmem_base + col, make_smem_desc(a_addr + o, 16, 1024), make_smem_desc(b_addr + o, 16, 1024), idesc_s,
+                 kk > 0);
         }
+      };
+      auto accumulate = [&](uint32_t col_acc, uint32_t col_a, uint32_t b_addr, bool first) {  // += A^(tmem) B over queries
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t offa = (kk / 4) * 16384 + (kk % 4) * 32, offb = (kk / 4) * 8192 + (kk % 4) * 32;
-          mma_ss(tmem_base + kColDP + buf * 64, make_smem_desc(v_addr + offa, 16, 1024),
-                 make_smem_desc(do_addr + offb, 16, 1024), idesc_s, kk > 0);
-        }
-        tc_commit(&s_full[buf]);
+        for (int kk = 0; kk < 8; ++kk)  // 16 queries per instruction; each group's operand sits in its own half
+          mma_ts(tmem_base + col_acc, tmem_base + col_a + (kk / 4) * 64 + (kk % 4) * 8,
+                 make_smem_desc(b_addr + kk * 2048, 16384, 1024), idesc_acc, !(first && kk == 0));
       };
 
-      if (ok) issue_scores(0);
-      if (ok && n_total > 1) issue_scores(1);
-      for (int n = 0; n < n_total && ok; ++n) {
-        const int stage = n % kStages, buf = n & 1;
-        PROF_MARK(2);
-        const bool gotp = mbar_wait(&p_full[buf], (n >> 1) & 1);
-        PROF_MARK(1);
-        if (!gotp) {
-          report_timeout(a.status, 204);
-          break;
-        }
+      wait_or_report(k_full, 0, 202);
+      wait_or_report(&q_full[0], 0, 203);
+      if (ok) {
         tc_fence_after_sync();
-        const uint32_t q_addr = ring_addr + stage * 2 * kStepBytes, do_addr = q_addr + kStepBytes;
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk)  // 16 queries per instruction
-          mma_ts(tmem_base + kColDV, tmem_base + kColS + buf * 64 + kk * 8,
-                 make_smem_desc(do_addr + kk * 2048, 8192, 1024), idesc_acc, !(n == 0 && kk == 0));
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          mma_ts(tmem_base + kColDK, tmem_base + kColDP + buf * 64 + kk * 8,
-                 make_smem_desc(q_addr + kk * 2048, 8192, 1024), idesc_acc, !(n == 0 && kk == 0));
-        tc_commit(&qdo_empty[stage]);
-        if (n + 2 < n_total) issue_scores(n + 2);
+        scores(kColS, k_addr, q_base);
+        tc_commit(s_full);
       }
-      if (ok) tc_commit(&acc_done);
-      PROF_MARK(2);
+      wait_or_report(v_full, 0, 202);
+      wait_or_report(&do_full[0], 0, 203);
+      if (ok) {
+        tc_fence_after_sync();
+        scores(kColDP, v_addr, do_base);
+        tc_commit(dp_full);
+      }
+      PROF_MARK(0);
+      for (int n = 0; n < n_total && ok; ++n) {
+        const int qs = n % kQS, ds = n % kDS;
+        const int qs1 = (n + 1) % kQS, ds1 = (n + 1) % kDS;
+        const bool more = n + 1 < n_total;
+        wait_or_report(p_full, n & 1, 204);
+        PROF_MARK(1);
+        if (!ok) break;
+        tc_fence_after_sync();
+        accumulate(kColDV, kColS, do_base + ds * kTileBytes, n == 0);
+        tc_commit(&do_empty[ds]);
+        PROF_MARK(2);
+        if (more) {
+          wait_or_report(&q_full[qs1], ((n + 1) / kQS) & 1, 203);
+          PROF_MARK(3);
+          if (!ok) break;
+          tc_fence_after_sync();
+          scores(kColS, k_addr, q_base + qs1 * kTileBytes);
+          tc_commit(s_full);
+          PROF_MARK(2);
+        }
+        wait_or_report(ds_full, n & 1, 208);
+        PROF_MARK(4);
+        if (!ok) break;
+        tc_fence_after_sync();
+        accumulate(kColDK, kColDP, q_base + qs * kTileBytes, n == 0);
+        tc_commit(&q_empty[qs]);
+        PROF_MARK(2);
+        if (more) {
+          wait_or_report(&do_full[ds1], ((n + 1) / kDS) & 1, 203);
+          PROF_MARK(3);
+          if (!ok) break;
+          tc_fence_after_sync();
+          scores(kColDP, v_addr, do_base + ds1 * kTileBytes);
+          tc_commit(dp_full);
+          PROF_MARK(2);
+        }
+      }
+      if (ok) tc_commit(acc_done);
       PROF_FLUSH(2, true);
     }
   } else {
+    // ------------------------------------------------------------------ compute warps
+    // thread = one key row (TMEM lane); group wg owns query columns [64 wg, 64 wg + 64) of every step
     const int wg = warp / 4, w4 = warp % 4;
-    const int gtid = tid - wg * 128;  // 0..127 inside the group
     const int key_row = w4 * 32 + lane;
     const int j = k0 + key_row;
     const uint32_t lane_addr = static_cast<uint32_t>(w4 * 32) << 16;
@@ -308,28 +424,36 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q64, const __grid_consta
     const int64_t bo = a.varlen ? 0 : (int64_t)b;
     bool ok = true;
     PROF_DECL;
-
-    for (int n = wg; n < n_total; n += 2) {
-      PROF_MARK(7);
+    // threads 0-127 fetch -lse*log2(e) (-inf = contributes nothing), threads 128-255 fetch -delta, of query tid & 127
+    auto fetch_row_stat = [&](int n) {
       const int h = hk * group + n / steps_per_head;
-      const int q0 = (slo + n % steps_per_head) * 64;
-      const int par = (n >> 1) & 1;
-      if (kMods) mods = make_mods(a, b, h, Sq, Sk);
-      // stage -lse*log2(e) (-inf = contributes nothing) and -delta of this step's 64 queries
-      if (gtid < 64) {
-        const int i = q0 + gtid;
-        float nl2 = kNegInf, nd = 0.f;
-        if (i < Sq) {
+      const int i = (slo + n % steps_per_head) * 128 + (tid & 127);
+      float val = tid < 128 ? kNegInf : 0.f;
+      if (i < Sq) {
+        if (tid < 128) {
           const float l = a.lse[bo * a.l_sb + (int64_t)h * a.l_sh + (int64_t)(q_start + i) * a.l_ss];
-          nl2 = (l == kNegInf) ? kNegInf : -l * kLog2e;
-          nd = -a.delta[bo * a.d_sb + (int64_t)h * a.d_sh + (int64_t)(q_start + i) * a.d_ss];
+          val = (l == kNegInf) ? kNegInf : -l * kLog2e;
+        } else {
+          val = -a.delta[bo * a.d_sb + (int64_t)h * a.d_sh + (int64_t)(q_start + i) * a.d_ss];
         }
-        nlse_s[wg][par][gtid] = nl2;
-        ndelta_s[wg][par][gtid] = nd;
       }
-      group_sync(wg);
+      return val;
+    };
+    float staged = n_total > 0 ? fetch_row_stat(0) : 0.f;
+
+    for (int n = 0; n < n_total; ++n) {
+      const int h = hk * group + n / steps_per_head;
+      const int q0 = (slo + n % steps_per_head) * 128;
+      const int par = n & 1;
+      if (kMods) mods = make_mods(a, b, h, Sq, Sk);
+      // publish -lse*log2(e) / -delta of this step's 128 queries (fetched one step ahead), then fetch the next
+      compute_sync();  // every thread is done reading the previous step's values
+      nlse_s[tid] = staged;  // nlse_s[0,128) then ndelta_s[0,128)
+      compute_sync();
+      if (n + 1 < n_total) staged = fetch_row_stat(n + 1);
       PROF_MARK(6);
-      const bool w_ok = mbar_wait(&s_full[wg], par);
+      bool w_ok = mbar_wait(s_full, par);
+      if (kMods) w_ok = mbar_wait(dp_full, par) && w_ok;
       if (!__all_sync(kFull, w_ok)) {
         report_timeout(a.status, 205);
         ok = false;
@@ -338,9 +462,9 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q64, const __grid_consta
       tc_fence_after_sync();
       PROF_MARK(0);
 
-      // queries this key row keeps: one interval [c_lo, c_hi] of the step's 64 columns
-      const bool masked = block_needs_mask(mods, q0, 64, k0, 128);
-      int c_lo = 0, c_hi = 63;
+      // queries this key row keeps: one interval [c_lo, c_hi] of the step's 128 columns
+      const bool masked = block_needs_mask(mods, q0, 128, k0, 128);
+      int c_lo = 0, c_hi = 127;
       if (masked) {
         if (a.causal) c_lo = max(c_lo, j - off - q0);
         else if (a.wr >= 0) c_lo = max(c_lo, j - off - a.wr - q0);
@@ -348,62 +472,90 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q64, const __grid_consta
         if (j >= Sk) c_hi = -1;
       }
       const uint64_t sc2 = pack_f32x2(mods.scale_log2, mods.scale_log2);
+
+      if (!kMods) {
+        // ---- phase 1: P^T = exp2(S^T * c - lse[q]) -> TMEM (16-bit, in place) and registers
+        uint32_t pk[32];
+        {
+          uint32_t s0[32], s1[32];
+          tmem_ld32(tS, s0);
+          tc_wait_ld_regs(s0);
+          tmem_ld32(tS + 32, s1);  // in flight while the first half is processed
+          const float* nl = nlse_s + wg * 64;
+          if (masked) probs_chunk<T, true>(s0, nl, sc2, wg * 64, c_lo, c_hi, &pk[0]);
+          else probs_chunk<T, false>(s0, nl, sc2, wg * 64, c_lo, c_hi, &pk[0]);
+          tmem_st16(tS, *reinterpret_cast<uint32_t(*)[16]>(&pk[0]));
+          tc_wait_ld_regs(s1);
+          if (masked) probs_chunk<T, true>(s1, nl + 32, sc2, wg * 64 + 32, c_lo, c_hi, &pk[16]);
+          else probs_chunk<T, false>(s1, nl + 32, sc2, wg * 64 + 32, c_lo, c_hi, &pk[16]);
+          tmem_st16(tS + 16, *reinterpret_cast<uint32_t(*)[16]>(&pk[16]));
+        }
+        tc_wait_st();
+        tc_fence_before_sync();
+        mbar_arrive(p_full);
+        PROF_MARK(4);
+
+        // ---- phase 2: dS^T = P^T * (dP^T - delta[q]) -> TMEM (16-bit, in place)
+        const bool d_ok = mbar_wait(dp_full, par);
+        if (!__all_sync(kFull, d_ok)) {
+          report_timeout(a.status, 209);
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        PROF_MARK(1);
+        {
+          uint32_t d0[32], d1[32], dsk[16];
+          tmem_ld32(tDP, d0);
+          tc_wait_ld_regs(d0);
+          tmem_ld32(tDP + 32, d1);
+          const float* nd = ndelta_s + wg * 64;
+          dscore_chunk<T>(d0, nd, &pk[0], dsk);
+          tmem_st16(tDP, dsk);
+          tc_wait_ld_regs(d1);
+          dscore_chunk<T>(d1, nd + 32, &pk[16], dsk);
+          tmem_st16(tDP + 16, dsk);
+        }
+        tc_wait_st();
+        tc_fence_before_sync();
+        mbar_arrive(ds_full);
+        PROF_MARK(5);
+      } else {
+        // ---- general element path: both products at once
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t s[32], dp[32];
-        tmem_ld32(tS + c * 32, s);
-        tmem_ld32(tDP + c * 32, dp);
-        tc_wait_ld_regs(s);
-        tc_wait_ld_regs(dp);
-        uint32_t pk[16], dsk[16];
+        for (int c = 0; c < 2; ++c) {
+          uint32_t s[32], dp[32];
+          tmem_ld32(tS + c * 32, s);
+          tmem_ld32(tDP + c * 32, dp);
+          tc_wait_ld_regs(s);
+          tc_wait_ld_regs(dp);
+          uint32_t pkk[16], dsk[16];
 #pragma unroll
-        for (int e4 = 0; e4 < 8; ++e4) {  // four queries at a time: one 16-byte read of lse and of delta
-          const float4 nl = *reinterpret_cast<const float4*>(&nlse_s[wg][par][c * 32 + e4 * 4]);
-          const float4 nd = *reinterpret_cast<const float4*>(&ndelta_s[wg][par][c * 32 + e4 * 4]);
-          const float nls[4] = {nl.x, nl.y, nl.z, nl.w}, nds[4] = {nd.x, nd.y, nd.z, nd.w};
-#pragma unroll
-          for (int e2 = 0; e2 < 2; ++e2) {
-            const int e = e4 * 2 + e2;     // pair index inside the chunk
-            const int col = c * 32 + 2 * e;  // column inside the step
+          for (int e = 0; e < 16; ++e) {
+            const int col = wg * 64 + c * 32 + 2 * e;
             float p0, p1, d0, d1;
-            if (kMods) {
-              bwd_element_mods(mods, !masked || (col >= c_lo && col <= c_hi), __uint_as_float(s[2 * e]),
-                               __uint_as_float(dp[2 * e]), nls[2 * e2], nds[2 * e2], q0 + col, j, &p0, &d0);
-              bwd_element_mods(mods, !masked || (col + 1 >= c_lo && col + 1 <= c_hi), __uint_as_float(s[2 * e + 1]),
-                               __uint_as_float(dp[2 * e + 1]), nls[2 * e2 + 1], nds[2 * e2 + 1], q0 + col + 1, j, &p1,
-                               &d1);
-            } else {
-              const uint64_t x2 = fma_f32x2(pack_u32x2(s[2 * e], s[2 * e + 1]), sc2,
-                                            pack_f32x2(nls[2 * e2], nls[2 * e2 + 1]));
-              float x0, x1;
-              unpack_f32x2(x2, &x0, &x1);
-              p0 = fast_exp2(x0);
-              p1 = fast_exp2(x1);
-              if (masked) {
-                if (col < c_lo || col > c_hi) p0 = 0.f;
-                if (col + 1 < c_lo || col + 1 > c_hi) p1 = 0.f;
-              }
-              const uint64_t dd = add_f32x2(pack_u32x2(dp[2 * e], dp[2 * e + 1]), pack_f32x2(nds[2 * e2], nds[2 * e2 + 1]));
-              unpack_f32x2(mul_f32x2(pack_f32x2(p0, p1), dd), &d0, &d1);
-            }
-            pk[e] = DType<T>::pack2(p0, p1);
+            bwd_element_mods(mods, !masked || (col >= c_lo && col <= c_hi), __uint_as_float(s[2 * e]),
+                             __uint_as_float(dp[2 * e]), nlse_s[col], ndelta_s[col], q0 + col, j, &p0, &d0);
+            bwd_element_mods(mods, !masked || (col + 1 >= c_lo && col + 1 <= c_hi), __uint_as_float(s[2 * e + 1]),
+                             __uint_as_float(dp[2 * e + 1]), nlse_s[col + 1], ndelta_s[col + 1], q0 + col + 1, j, &p1,
+                             &d1);
+            pkk[e] = DType<T>::pack2(p0, p1);
             dsk[e] = DType<T>::pack2(d0, d1);
           }
+          tmem_st16(tS + c * 16, pkk);
+          tmem_st16(tDP + c * 16, dsk);
         }
-        tmem_st16(tS + c * 16, pk);
-        tmem_st16(tDP + c * 16, dsk);
+        tc_wait_st();
+        tc_fence_before_sync();
+        mbar_arrive(p_full);
+        mbar_arrive(ds_full);
       }
-      PROF_MARK(4);
-      tc_wait_st();
-      tc_fence_before_sync();
-      mbar_arrive(&p_full[wg]);
-      PROF_MARK(5);
     }
     PROF_FLUSH(wg, lane == 0 && w4 == 0);
 
     // epilogue: group 0 writes dK (scaled), group 1 writes dV
     if (n_total > 0) {
-      const bool w_ok = ok && mbar_wait(&acc_done, 0);
+      const bool w_ok = ok && mbar_wait(acc_done, 0);
       if (!__all_sync(kFull, w_ok)) {
         if (ok) report_timeout(a.status, 206);
         ok = false;
@@ -478,7 +630,7 @@ __device__ __forceinline__ DqItem dq_item(const BwdArgs& a, int w) {
     else if (a.wr >= 0) khi = min(khi, r1 + off + a.wr + 1);
     if (a.wl >= 0) klo = max(0, it.q0 + off - a.wl);
     khi = max(khi, 0);
-    const int slo = klo / 64, shi = (khi + 63) / 64;
+    const int slo = klo / 128, shi = (khi + 127) / 128;
     if (shi > slo) {
       it.slo = slo;
       it.n_total = shi - slo;
@@ -487,64 +639,135 @@ __device__ __forceinline__ DqItem dq_item(const BwdArgs& a, int w) {
   return it;
 }
 
-// Persistent: gridDim.x CTAs (one per SM) each walk items blockIdx.x, blockIdx.x + gridDim.x, ... All pipeline
-// counters (ring position, score-buffer parity, accumulator uses) run on across items, so the producer prefetches
-// the next item's operands and the MMA warp starts its score MMAs while the compute groups still write out dQ.
+// Shared-memory plan of the dQ kernel (all dynamic).
+template <int D>
+struct DqSmem {
+  static constexpr int kChunks = D / 64;
+  static constexpr int kTileBytes = kChunks * 16384;  // one 128-row operand tile
+  static constexpr int kKStages = D == 128 ? 3 : 4;   // K lives from S of its step to dQ of the same step (two steps later)
+  static constexpr int kVStages = D == 128 ? 2 : 3;
+  static constexpr int kOffQ = 0;
+  static constexpr int kOffDo = kTileBytes;
+  static constexpr int kOffK = 2 * kTileBytes;
+  static constexpr int kOffV = kOffK + kKStages * kTileBytes;
+  static constexpr int kOffBars = kOffV + kVStages * kTileBytes;
+  static constexpr int kNumBars = 9 + 2 * kKStages + 2 * kVStages;
+  static constexpr int kOffTmemPtr = kOffBars + kNumBars * 8;
+  static constexpr int kBytes = kOffTmemPtr + 8 + 1024;  // + slack to round the base up to 1024
+  static_assert(kBytes <= 232448, "dQ shared memory plan exceeds one CTA's 227 KB");
+};
+
+// 32 raw scores of one row -> probabilities in place: p = exp2(s * scale_log2 + nlse2), zero outside [c_lo, c_hi]
+// (columns numbered from col0) when kMasked.
+template <bool kMasked>
+__device__ __forceinline__ void probs_inplace(uint32_t (&s)[32], uint64_t sc2, uint64_t nl2, int col0, int c_lo, int c_hi) {
+#pragma unroll
+  for (int e = 0; e < 16; ++e) {
+    float x0, x1;
+    unpack_f32x2(fma_f32x2(pack_u32x2(s[2 * e], s[2 * e + 1]), sc2, nl2), &x0, &x1);
+    float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+    if (kMasked) {
+      const int col = col0 + 2 * e;
+      if (col < c_lo || col > c_hi) p0 = 0.f;
+      if (col + 1 < c_lo || col + 1 > c_hi) p1 = 0.f;
+    }
+    s[2 * e] = __float_as_uint(p0);
+    s[2 * e + 1] = __float_as_uint(p1);
+  }
+}
+
+// 32 probabilities and raw dP values of one row -> 16 packed dS = p * (dp + ndelta).
+template <typename T>
+__device__ __forceinline__ void dscore_row(const uint32_t (&p)[32], const uint32_t (&dp)[32], uint64_t nd2,
+                                           uint32_t (&dsk)[16]) {
+#pragma unroll
+  for (int e = 0; e < 16; ++e) {
+    float d0, d1;
+    unpack_f32x2(mul_f32x2(pack_u32x2(p[2 * e], p[2 * e + 1]), add_f32x2(pack_u32x2(dp[2 * e], dp[2 * e + 1]), nd2)), &d0,
+                 &d1);
+    dsk[e] = DType<T>::pack2(d0, d1);
+  }
+}
+
+// Persistent: gridDim.x CTAs (one per SM) each walk items snake_item(0), snake_item(1), ... Q and dO of the item stay
+// in shared memory; K/V stream in 128-key steps through two rings. All pipeline counters (ring positions, score
+// buffer parity) run on across items, so the producer prefetches the next item's operands and the MMA warp starts
+// its score MMAs while the compute warps still write out dQ. One thread issues, per step i (g = global step):
+//     dP(i+1) = dO V(i+1)^T       after the compute warps have read dP(i)
+//     dQ    += dS(i) K(i)         dS(i) sits in score buffer g & 1
+//     S(i+2)  = Q K(i+2)^T        into the same buffer, behind dQ(i) in the pipe
+// so phase 1 of step i+1 (P from S, kept in registers) never waits and phase 2 (dS = P * (dP - delta), written over
+// the score buffer) finds dP(i+1) ready. TMEM: S buffers [0,128) [128,256); dP [256,384); dQ [384,384+D).
 template <typename T, int D, bool kMods>
 __global__ void __launch_bounds__(kBwdThreads, 1)
-bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k64,
-              const __grid_constant__ CUtensorMap map_v64, const __grid_constant__ CUtensorMap map_do,
+bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+              const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
               const BwdArgs a) {
-  constexpr int kChunks = D / 64;
-  constexpr int kTileBytes = kChunks * 16384;
-  constexpr int kStepBytes = kChunks * 8192;
+  using L = DqSmem<D>;
+  constexpr int kChunks = L::kChunks;
+  constexpr int kTileBytes = L::kTileBytes;
+  constexpr int kKS = L::kKStages, kVS = L::kVStages;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sQ = smem;
-  uint8_t* sdO = smem + kTileBytes;
-  uint8_t* sRing = smem + 2 * kTileBytes;  // [stage][K step | V step]
-  __shared__ uint64_t qdo_full, qdo_empty, kv_full[kStages], kv_empty[kStages], s_full[2], ds_full[2], acc_done,
-      acc_free;
-  __shared__ uint32_t tmem_base_s;
+  uint8_t* sQ = smem + L::kOffQ;
+  uint8_t* sDo = smem + L::kOffDo;
+  uint8_t* sK = smem + L::kOffK;
+  uint8_t* sV = smem + L::kOffV;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kOffBars);
+  uint64_t* qdo_full = bars + 0;
+  uint64_t* qdo_empty = bars + 1;
+  uint64_t* dp_full = bars + 2;
+  uint64_t* acc_done = bars + 3;
+  uint64_t* acc_free = bars + 4;
+  uint64_t* s_full = bars + 5;   // [2]
+  uint64_t* ds_full = bars + 7;  // [2]
+  uint64_t* k_full = bars + 9;
+  uint64_t* k_empty = k_full + kKS;
+  uint64_t* v_full = k_empty + kKS;
+  uint64_t* v_empty = v_full + kVS;
+  uint32_t* tmem_base_s = reinterpret_cast<uint32_t*>(smem + L::kOffTmemPtr);
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   const int n_items = a.num_tiles * a.batch * a.heads_q;
 
   if (tid == 0) {
-    mbar_init(&qdo_full, 1);
-    mbar_init(&qdo_empty, 1);
-    mbar_init(&acc_done, 1);
-    mbar_init(&acc_free, 256);
-#pragma unroll
+    mbar_init(qdo_full, 1);
+    mbar_init(qdo_empty, 1);
+    mbar_init(dp_full, 1);
+    mbar_init(acc_done, 1);
+    mbar_init(acc_free, 256);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s_full[i], 1);
-      mbar_init(&ds_full[i], 128);
+      mbar_init(&ds_full[i], 256);
     }
-#pragma unroll
-    for (int s = 0; s < kStages; ++s) {
-      mbar_init(&kv_full[s], 1);
-      mbar_init(&kv_empty[s], 1);
+    for (int i = 0; i < kKS; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+    }
+    for (int i = 0; i < kVS; ++i) {
+      mbar_init(&v_full[i], 1);
+      mbar_init(&v_empty[i], 1);
     }
     mbar_fence_init();
   }
   if (warp == 9) {
-    tmem_alloc(&tmem_base_s, 512);
+    tmem_alloc(tmem_base_s, 512);
     tmem_relinquish();
   }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
-  const uint32_t tmem_base = tmem_base_s;
-  constexpr uint32_t kColS = 0, kColDP = 128, kColDQ = 256;
+  const uint32_t tmem_base = *tmem_base_s;
+  constexpr uint32_t kColS = 0, kColDP = 256, kColDQ = 384;
 
   if (warp == 8) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      tma_prefetch_desc(&map_k64);
-      tma_prefetch_desc(&map_v64);
-      int ng = 0;       // global step counter (ring position)
-      int used = 0;     // items that used the pipeline so far
+      tma_prefetch_desc(&map_k);
+      tma_prefetch_desc(&map_v);
+      int g = 0;     // global step counter (ring positions)
+      int used = 0;  // items that used the pipeline so far
       bool ok = true;
       for (int round = 0; ok; ++round) {
         const int w = snake_item(round, blockIdx.x, gridDim.x);
@@ -552,31 +775,34 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         const DqItem it = dq_item(a, w);
         if (!it.valid || it.n_total == 0) continue;
         const int tb = a.varlen ? 0 : it.b;
-        if (!mbar_wait(&qdo_empty, (used & 1) ^ 1)) {
+        auto load_tile = [&](uint8_t* dst, const CUtensorMap* map, uint64_t* bar, int row, int head) {
+#pragma unroll
+          for (int c = 0; c < kChunks; ++c) tma_load_4d(dst + c * 16384, map, bar, c * 64, row, head, tb);
+        };
+        if (!mbar_wait(qdo_empty, (used & 1) ^ 1)) {
           report_timeout(a.status, 300);
           break;
         }
-        mbar_arrive_expect_tx(&qdo_full, 2 * kTileBytes);
-#pragma unroll
-        for (int c = 0; c < kChunks; ++c) {
-          tma_load_4d(sQ + c * 16384, &map_q, &qdo_full, c * 64, it.q_start + it.q0, it.h, tb);
-          tma_load_4d(sdO + c * 16384, &map_do, &qdo_full, c * 64, it.q_start + it.q0, it.h, tb);
-        }
-        for (int n = 0; n < it.n_total; ++n, ++ng) {
-          const int stage = ng % kStages;
-          if (!mbar_wait(&kv_empty[stage], ((ng / kStages) & 1) ^ 1)) {
+        mbar_arrive_expect_tx(qdo_full, 2 * kTileBytes);
+        load_tile(sQ, &map_q, qdo_full, it.q_start + it.q0, it.h);
+        load_tile(sDo, &map_do, qdo_full, it.q_start + it.q0, it.h);
+        for (int n = 0; n < it.n_total; ++n, ++g) {
+          const int ks = g % kKS, vs = g % kVS;
+          const int row = it.k_start + (it.slo + n) * 128;
+          if (!mbar_wait(&k_empty[ks], ((g / kKS) & 1) ^ 1)) {
             report_timeout(a.status, 301);
             ok = false;
             break;
           }
-          const int row = it.k_start + (it.slo + n) * 64;
-          uint8_t* dst = sRing + stage * 2 * kStepBytes;
-          mbar_arrive_expect_tx(&kv_full[stage], 2 * kStepBytes);
-#pragma unroll
-          for (int c = 0; c < kChunks; ++c) {
-            tma_load_4d(dst + c * 8192, &map_k64, &kv_full[stage], c * 64, row, it.hk, tb);
-            tma_load_4d(dst + kStepBytes + c * 8192, &map_v64, &kv_full[stage], c * 64, row, it.hk, tb);
+          mbar_arrive_expect_tx(&k_full[ks], kTileBytes);
+          load_tile(sK + ks * kTileBytes, &map_k, &k_full[ks], row, it.hk);
+          if (!mbar_wait(&v_empty[vs], ((g / kVS) & 1) ^ 1)) {
+            report_timeout(a.status, 308);
+            ok = false;
+            break;
           }
+          mbar_arrive_expect_tx(&v_full[vs], kTileBytes);
+          load_tile(sV + vs * kTileBytes, &map_v, &v_full[vs], row, it.hk);
         }
         ++used;
       }
@@ -584,34 +810,41 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
   } else if (warp == 9) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc_s = make_idesc(DType<T>::kFormat, 128, 64, 0, 0);
+      constexpr uint32_t idesc_s = make_idesc(DType<T>::kFormat, 128, 128, 0, 0);
       constexpr uint32_t idesc_acc = make_idesc(DType<T>::kFormat, 128, D, 0, 1);
-      const uint32_t q_addr = smem_u32(sQ), do_addr = smem_u32(sdO), ring_addr = smem_u32(sRing);
-      int ng0 = 0, used = 0;
+      const uint32_t q_addr = smem_u32(sQ), do_addr = smem_u32(sDo), k_base = smem_u32(sK), v_base = smem_u32(sV);
+      int g0 = 0, used = 0;
       bool ok = true;
-
-      auto issue_scores = [&](int ng) {  // global step ng: S and dP into buffer ng & 1
-        const int stage = ng % kStages, buf = ng & 1;
-        if (!mbar_wait(&kv_full[stage], (ng / kStages) & 1)) {
-          report_timeout(a.status, 303);
+      PROF_DECL;
+      auto wait_or_report = [&](uint64_t* bar, int parity, int code) {
+        if (!ok) return;
+        if (!mbar_wait(bar, parity)) {
+          report_timeout(a.status, code);
           ok = false;
-          return;
         }
+      };
+      auto scores = [&](uint32_t col, uint32_t a_addr, uint32_t b_addr) {  // [128 queries x 128 keys] = A B^T over D
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t o = (kk / 4) * 16384 + (kk % 4) * 32;
+          mma_ss(tmem_base + col, make_smem_desc(a_addr + o, 16, 1024), make_smem_desc(b_addr + o, 16, 1024), idesc_s,
+                 kk > 0);
+        }
+      };
+      auto issue_s = [&](int g) {  // S of global step g into score buffer g & 1
+        wait_or_report(&k_full[g % kKS], (g / kKS) & 1, 303);
+        if (!ok) return;
         tc_fence_after_sync();
-        const uint32_t k_addr = ring_addr + stage * 2 * kStepBytes, v_addr = k_addr + kStepBytes;
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t offa = (kk / 4) * 16384 + (kk % 4) * 32, offb = (kk / 4) * 8192 + (kk % 4) * 32;
-          mma_ss(tmem_base + kColS + buf * 64, make_smem_desc(q_addr + offa, 16, 1024),
-                 make_smem_desc(k_addr + offb, 16, 1024), idesc_s, kk > 0);
-        }
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t offa = (kk / 4) * 16384 + (kk % 4) * 32, offb = (kk / 4) * 8192 + (kk % 4) * 32;
-          mma_ss(tmem_base + kColDP + buf * 64, make_smem_desc(do_addr + offa, 16, 1024),
-                 make_smem_desc(v_addr + offb, 16, 1024), idesc_s, kk > 0);
-        }
-        tc_commit(&s_full[buf]);
+        scores(kColS + (g & 1) * 128, q_addr, k_base + (g % kKS) * kTileBytes);
+        tc_commit(&s_full[g & 1]);
+      };
+      auto issue_dp = [&](int g) {
+        wait_or_report(&v_full[g % kVS], (g / kVS) & 1, 309);
+        if (!ok) return;
+        tc_fence_after_sync();
+        scores(kColDP, do_addr, v_base + (g % kVS) * kTileBytes);
+        tc_commit(dp_full);
+        tc_commit(&v_empty[g % kVS]);
       };
 
       for (int round = 0; ok; ++round) {
@@ -619,52 +852,57 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         if (w >= n_items) break;
         const DqItem it = dq_item(a, w);
         if (!it.valid || it.n_total == 0) continue;
-        if (!mbar_wait(&qdo_full, used & 1)) {
-          report_timeout(a.status, 302);
-          break;
-        }
+        const int n = it.n_total;
+        PROF_MARK(5);
+        wait_or_report(qdo_full, used & 1, 302);
+        if (!ok) break;
         tc_fence_after_sync();
-        issue_scores(ng0);
-        if (ok && it.n_total > 1) issue_scores(ng0 + 1);
-        if (ok && it.n_total <= 2) tc_commit(&qdo_empty);  // every score MMA of the item is issued: Q/dO may be replaced
-        for (int n = 0; n < it.n_total && ok; ++n) {
-          const int ng = ng0 + n, stage = ng % kStages, buf = ng & 1;
-          if (!mbar_wait(&ds_full[buf], (ng >> 1) & 1)) {
-            report_timeout(a.status, 304);
-            ok = false;
-            break;
-          }
-          if (n == 0 && used > 0 && !mbar_wait(&acc_free, (used - 1) & 1)) {  // previous item's dQ has been read out
-            report_timeout(a.status, 307);
-            ok = false;
-            break;
-          }
+        issue_s(g0);
+        issue_dp(g0);
+        if (ok && n == 1) tc_commit(qdo_empty);  // every MMA that reads Q / dO is issued: they may be replaced
+        if (n > 1) issue_s(g0 + 1);
+        PROF_MARK(0);
+        for (int i = 0; i < n && ok; ++i) {
+          const int g = g0 + i;
+          wait_or_report(&ds_full[g & 1], (g >> 1) & 1, 304);
+          if (i == 0 && used > 0) wait_or_report(acc_free, (used - 1) & 1, 307);  // previous dQ has been read out
+          PROF_MARK(1);
+          if (!ok) break;
           tc_fence_after_sync();
-          const uint32_t k_addr = ring_addr + stage * 2 * kStepBytes;
+          if (i + 1 < n) {
+            issue_dp(g + 1);
+            if (ok && i + 2 == n) tc_commit(qdo_empty);
+            PROF_MARK(3);
+          }
+          if (!ok) break;
+          const uint32_t kb = k_base + (g % kKS) * kTileBytes;
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk)  // 16 keys per instruction
-            mma_ts(tmem_base + kColDQ, tmem_base + kColS + buf * 64 + kk * 8,
-                   make_smem_desc(k_addr + kk * 2048, 8192, 1024), idesc_acc, !(n == 0 && kk == 0));
-          tc_commit(&kv_empty[stage]);
-          if (n + 2 < it.n_total) {
-            issue_scores(ng + 2);
-            if (ok && n + 3 == it.n_total) tc_commit(&qdo_empty);
+          for (int kk = 0; kk < 8; ++kk)  // 16 keys per instruction; each compute group's dS sits in its own half
+            mma_ts(tmem_base + kColDQ, tmem_base + kColS + (g & 1) * 128 + (kk / 4) * 64 + (kk % 4) * 8,
+                   make_smem_desc(kb + kk * 2048, 16384, 1024), idesc_acc, !(i == 0 && kk == 0));
+          tc_commit(&k_empty[g % kKS]);
+          PROF_MARK(2);
+          if (i + 2 < n) {
+            issue_s(g + 2);
+            PROF_MARK(4);
           }
         }
-        if (ok) tc_commit(&acc_done);
-        ng0 += it.n_total;
+        if (ok) tc_commit(acc_done);
+        g0 += n;
         ++used;
       }
+      PROF_FLUSH(2, true);
     }
   } else {
-    // ------------------------------------------------------------------ compute groups
+    // ------------------------------------------------------------------ compute warps
+    // thread = one query row (TMEM lane); group wg owns key columns [64 wg, 64 wg + 64) of every step
     const int wg = warp / 4, w4 = warp % 4;
     const int q_row = w4 * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>(w4 * 32) << 16;
-    const uint32_t tS = tmem_base + lane_addr + kColS + wg * 64;
     const uint32_t tDP = tmem_base + lane_addr + kColDP + wg * 64;
-    int ng0 = 0, used = 0;
+    int g0 = 0, used = 0;
     bool ok = true;
+    PROF_DECL;
 
     for (int round = 0; ok; ++round) {
       const int w = snake_item(round, blockIdx.x, gridDim.x);
@@ -695,76 +933,99 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
       }
       const uint64_t sc2 = pack_f32x2(mods.scale_log2, mods.scale_log2);
       const uint64_t nl2 = pack_f32x2(nlse2, nlse2), nd2 = pack_f32x2(ndelta, ndelta);
+      PROF_MARK(6);
 
-      // this group takes the global steps whose parity equals its index
-      const int first = ((ng0 & 1) == wg) ? 0 : 1;
-      for (int n = first; n < it.n_total; n += 2) {
-        const int ng = ng0 + n;
-        const int ks = (it.slo + n) * 64;
-        const bool w_ok = mbar_wait(&s_full[wg], (ng >> 1) & 1);
+      for (int n = 0; n < it.n_total; ++n) {
+        const int g = g0 + n;
+        const int ks = (it.slo + n) * 128;
+        const uint32_t tS = tmem_base + lane_addr + kColS + (g & 1) * 128 + wg * 64;
+        bool w_ok = mbar_wait(&s_full[g & 1], (g >> 1) & 1);
+        if (kMods) w_ok = mbar_wait(dp_full, g & 1) && w_ok;
         if (!__all_sync(kFull, w_ok)) {
           report_timeout(a.status, 305);
           ok = false;
           break;
         }
         tc_fence_after_sync();
-        // keys this query row keeps: one interval [c_lo, c_hi] of the step's 64 columns
-        const bool masked = block_needs_mask(mods, it.q0, 128, ks, 64);
-        int c_lo = 0, c_hi = 63;
+        PROF_MARK(0);
+        // keys this query row keeps: one interval [c_lo, c_hi] of the step's 128 columns
+        const bool masked = block_needs_mask(mods, it.q0, 128, ks, 128);
+        int c_lo = 0, c_hi = 127;
         if (masked) {
           c_hi = min(c_hi, it.Sk - 1 - ks);
           if (a.causal) c_hi = min(c_hi, i + off - ks);
           else if (a.wr >= 0) c_hi = min(c_hi, i + off + a.wr - ks);
           if (a.wl >= 0) c_lo = max(0, i + off - a.wl - ks);
         }
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t s[32], dp[32];
-          tmem_ld32(tS + c * 32, s);
-          tmem_ld32(tDP + c * 32, dp);
-          tc_wait_ld_regs(s);
-          tc_wait_ld_regs(dp);
-          uint32_t dsk[16];
-#pragma unroll
-          for (int e = 0; e < 16; ++e) {
-            const int col = c * 32 + 2 * e;
-            float d0, d1;
-            if (kMods) {
-              float p0, p1;
-              bwd_element_mods(mods, !masked || (col >= c_lo && col <= c_hi), __uint_as_float(s[2 * e]),
-                               __uint_as_float(dp[2 * e]), nlse2, ndelta, i, ks + col, &p0, &d0);
-              bwd_element_mods(mods, !masked || (col + 1 >= c_lo && col + 1 <= c_hi), __uint_as_float(s[2 * e + 1]),
-                               __uint_as_float(dp[2 * e + 1]), nlse2, ndelta, i, ks + col + 1, &p1, &d1);
-            } else {
-              const uint64_t x2 = fma_f32x2(pack_u32x2(s[2 * e], s[2 * e + 1]), sc2, nl2);
-              float x0, x1;
-              unpack_f32x2(x2, &x0, &x1);
-              float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
-              if (masked) {
-                if (col < c_lo || col > c_hi) p0 = 0.f;
-                if (col + 1 < c_lo || col + 1 > c_hi) p1 = 0.f;
-              }
-              const uint64_t dd = add_f32x2(pack_u32x2(dp[2 * e], dp[2 * e + 1]), nd2);
-              unpack_f32x2(mul_f32x2(pack_f32x2(p0, p1), dd), &d0, &d1);
-            }
-            dsk[e] = DType<T>::pack2(d0, d1);
+        if (!kMods) {
+          // ---- phase 1: P = exp2(S * c - lse[row]), kept in registers
+          uint32_t p0[32], p1[32];
+          tmem_ld32(tS, p0);
+          tc_wait_ld_regs(p0);
+          tmem_ld32(tS + 32, p1);  // in flight while the first half is processed
+          if (masked) probs_inplace<true>(p0, sc2, nl2, wg * 64, c_lo, c_hi);
+          else probs_inplace<false>(p0, sc2, nl2, wg * 64, c_lo, c_hi);
+          tc_wait_ld_regs(p1);
+          if (masked) probs_inplace<true>(p1, sc2, nl2, wg * 64 + 32, c_lo, c_hi);
+          else probs_inplace<false>(p1, sc2, nl2, wg * 64 + 32, c_lo, c_hi);
+          PROF_MARK(4);
+
+          // ---- phase 2: dS = P * (dP - delta[row]) -> 16-bit, over the score buffer
+          const bool d_ok = mbar_wait(dp_full, g & 1);
+          if (!__all_sync(kFull, d_ok)) {
+            report_timeout(a.status, 310);
+            ok = false;
+            break;
           }
-          tmem_st16(tS + c * 16, dsk);
+          tc_fence_after_sync();
+          PROF_MARK(1);
+          uint32_t d0[32], d1[32], dsk[16];
+          tmem_ld32(tDP, d0);
+          tc_wait_ld_regs(d0);
+          tmem_ld32(tDP + 32, d1);
+          dscore_row<T>(p0, d0, nd2, dsk);
+          tmem_st16(tS, dsk);
+          tc_wait_ld_regs(d1);
+          dscore_row<T>(p1, d1, nd2, dsk);
+          tmem_st16(tS + 16, dsk);
+        } else {
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            uint32_t sv[32], dp[32];
+            tmem_ld32(tS + c * 32, sv);
+            tmem_ld32(tDP + c * 32, dp);
+            tc_wait_ld_regs(sv);
+            tc_wait_ld_regs(dp);
+            uint32_t dsk[16];
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+              const int col = wg * 64 + c * 32 + 2 * e;
+              float pa, pb, da, db;
+              bwd_element_mods(mods, !masked || (col >= c_lo && col <= c_hi), __uint_as_float(sv[2 * e]),
+                               __uint_as_float(dp[2 * e]), nlse2, ndelta, i, ks + col, &pa, &da);
+              bwd_element_mods(mods, !masked || (col + 1 >= c_lo && col + 1 <= c_hi), __uint_as_float(sv[2 * e + 1]),
+                               __uint_as_float(dp[2 * e + 1]), nlse2, ndelta, i, ks + col + 1, &pb, &db);
+              dsk[e] = DType<T>::pack2(da, db);
+            }
+            tmem_st16(tS + c * 16, dsk);
+          }
         }
         tc_wait_st();
         tc_fence_before_sync();
-        mbar_arrive(&ds_full[wg]);
+        mbar_arrive(&ds_full[g & 1]);
+        PROF_MARK(5);
       }
       if (!ok) break;
 
       // epilogue of the item: dQ * softmax_scale -> global, then hand the accumulator back
-      const bool w_ok = mbar_wait(&acc_done, used & 1);
+      const bool w_ok = mbar_wait(acc_done, used & 1);
       if (!__all_sync(kFull, w_ok)) {
         report_timeout(a.status, 306);
         ok = false;
         break;
       }
       tc_fence_after_sync();
+      PROF_MARK(2);
 #pragma unroll
       for (int cc = 0; cc < kSlices; ++cc) {
         const int c = wg * kSlices + cc;
@@ -773,13 +1034,15 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         tc_wait_ld_regs(o);
         if (cc == kSlices - 1) {
           tc_fence_before_sync();
-          mbar_arrive(&acc_free);  // this thread's last read of dQ is in registers
+          mbar_arrive(acc_free);  // this thread's last read of dQ is in registers
         }
         if (i < it.Sq) store_row_slice<T>(row_ptr + c * 32, o, a.softmax_scale);
       }
-      ng0 += it.n_total;
+      PROF_MARK(3);
+      g0 += it.n_total;
       ++used;
     }
+    PROF_FLUSH(wg, lane == 0 && w4 == 0);
   }
 
   tc_fence_before_sync();
@@ -802,9 +1065,6 @@ int sm_count() {
 
 template <typename T, int D, bool kMods>
 int launch_typed(const fa_attn_params& p, const BwdArgs& a0, int parts, cudaStream_t stream) {
-  constexpr int kTileBytes = (D / 64) * 16384;
-  constexpr int kStepBytes = (D / 64) * 8192;
-  const int smem = 2 * kTileBytes + kStages * 2 * kStepBytes + 1024;
   const int rows_q = p.varlen ? p.total_q : p.seqlen_q;
   const int rows_k = p.varlen ? p.total_k : p.seqlen_k;
   const int nb = p.varlen ? 1 : p.batch;
@@ -815,32 +1075,34 @@ int launch_typed(const fa_attn_params& p, const BwdArgs& a0, int parts, cudaStre
   BwdArgs a = a0;
   if (parts & FA_BWD_DKDV) {
     CUtensorMap mq, mk, mv, mdo;
-    int rc = map_of(&mq, p.q, rows_q, p.heads_q, p.q_strides, 64);
+    int rc = map_of(&mq, p.q, rows_q, p.heads_q, p.q_strides, 128);
     if (!rc) rc = map_of(&mk, p.k, rows_k, p.heads_kv, p.k_strides, 128);
     if (!rc) rc = map_of(&mv, p.v, rows_k, p.heads_kv, p.v_strides, 128);
-    if (!rc) rc = map_of(&mdo, p.dout, rows_q, p.heads_q, p.do_strides, 64);
+    if (!rc) rc = map_of(&mdo, p.dout, rows_q, p.heads_q, p.do_strides, 128);
     if (rc) return rc;
     auto kern = bwd_dkdv_kernel<T, D, kMods>;
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    constexpr int smem_dkdv = DkdvSmem<D>::kBytes;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_dkdv);
     if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "backward smem opt-in failed: %s", cudaGetErrorString(e));
     a.num_tiles = (p.seqlen_k + 127) / 128;
-    kern<<<dim3(p.batch * p.heads_kv, a.num_tiles), kBwdThreads, smem, stream>>>(mq, mk, mv, mdo, a);
+    kern<<<dim3(p.batch * p.heads_kv, a.num_tiles), kBwdThreads, smem_dkdv, stream>>>(mq, mk, mv, mdo, a);
     e = cudaGetLastError();
     if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "dK/dV launch failed: %s", cudaGetErrorString(e));
   }
   if (parts & FA_BWD_DQ) {
     CUtensorMap mq, mk, mv, mdo;
     int rc = map_of(&mq, p.q, rows_q, p.heads_q, p.q_strides, 128);
-    if (!rc) rc = map_of(&mk, p.k, rows_k, p.heads_kv, p.k_strides, 64);
-    if (!rc) rc = map_of(&mv, p.v, rows_k, p.heads_kv, p.v_strides, 64);
+    if (!rc) rc = map_of(&mk, p.k, rows_k, p.heads_kv, p.k_strides, 128);
+    if (!rc) rc = map_of(&mv, p.v, rows_k, p.heads_kv, p.v_strides, 128);
     if (!rc) rc = map_of(&mdo, p.dout, rows_q, p.heads_q, p.do_strides, 128);
     if (rc) return rc;
     auto kern = bwd_dq_kernel<T, D, kMods>;
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    constexpr int smem_dq = DqSmem<D>::kBytes;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_dq);
     if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "backward smem opt-in failed: %s", cudaGetErrorString(e));
     a.num_tiles = (p.seqlen_q + 127) / 128;
     const int n_items = a.num_tiles * p.batch * p.heads_q;
-    kern<<<dim3(n_items < sm_count() ? n_items : sm_count()), kBwdThreads, smem, stream>>>(mq, mk, mv, mdo, a);
+    kern<<<dim3(n_items < sm_count() ? n_items : sm_count()), kBwdThreads, smem_dq, stream>>>(mq, mk, mv, mdo, a);
     e = cudaGetLastError();
     if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "dQ launch failed: %s", cudaGetErrorString(e));
   }
