@@ -131,10 +131,6 @@ __device__ __forceinline__ void store_row_slice(T* dst, const uint32_t (&o)[32],
   }
 }
 
-__device__ __forceinline__ void group_sync(int wg) {
-  asm volatile("bar.sync %0, 128;" ::"r"(1 + wg) : "memory");  // the four warps of one compute group
-}
-
 // =============================================================================================
 // dK / dV
 // =============================================================================================
@@ -779,13 +775,6 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
 #pragma unroll
           for (int c = 0; c < kChunks; ++c) tma_load_4d(dst + c * 16384, map, bar, c * 64, row, head, tb);
         };
-        if (!mbar_wait(qdo_empty, (used & 1) ^ 1)) {
-          report_timeout(a.status, 300);
-          break;
-        }
-        mbar_arrive_expect_tx(qdo_full, 2 * kTileBytes);
-        load_tile(sQ, &map_q, qdo_full, it.q_start + it.q0, it.h);
-        load_tile(sDo, &map_do, qdo_full, it.q_start + it.q0, it.h);
         for (int n = 0; n < it.n_total; ++n, ++g) {
           const int ks = g % kKS, vs = g % kVS;
           const int row = it.k_start + (it.slo + n) * 128;
@@ -803,6 +792,16 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
           }
           mbar_arrive_expect_tx(&v_full[vs], kTileBytes);
           load_tile(sV + vs * kTileBytes, &map_v, &v_full[vs], row, it.hk);
+          if (n == 0) {  // after the first K/V tiles, whose ring slots free up before the previous item's Q/dO do
+            if (!mbar_wait(qdo_empty, (used & 1) ^ 1)) {
+              report_timeout(a.status, 300);
+              ok = false;
+              break;
+            }
+            mbar_arrive_expect_tx(qdo_full, 2 * kTileBytes);
+            load_tile(sQ, &map_q, qdo_full, it.q_start + it.q0, it.h);
+            load_tile(sDo, &map_do, qdo_full, it.q_start + it.q0, it.h);
+          }
         }
         ++used;
       }
@@ -903,6 +902,20 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     int g0 = 0, used = 0;
     bool ok = true;
     PROF_DECL;
+    // -lse*log2(e) (-inf = the row contributes nothing) and -delta of this thread's query row of an item
+    auto row_stats = [&](const DqItem& it, float& nlse2, float& ndelta) {
+      const int i = it.q0 + q_row;
+      const int64_t bo = a.varlen ? 0 : (int64_t)it.b;
+      nlse2 = kNegInf;
+      ndelta = 0.f;
+      if (i < it.Sq) {
+        const float l = a.lse[bo * a.l_sb + (int64_t)it.h * a.l_sh + (int64_t)(it.q_start + i) * a.l_ss];
+        nlse2 = (l == kNegInf) ? kNegInf : -l * kLog2e;
+        ndelta = -a.delta[bo * a.d_sb + (int64_t)it.h * a.d_sh + (int64_t)(it.q_start + i) * a.d_ss];
+      }
+    };
+    float pre_nlse2 = kNegInf, pre_ndelta = 0.f;
+    int pre_round = -1;
 
     for (int round = 0; ok; ++round) {
       const int w = snake_item(round, blockIdx.x, gridDim.x);
@@ -925,12 +938,8 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
       }
       const ScoreMods mods = make_mods(a, it.b, it.h, it.Sq, it.Sk);
       const int off = it.Sk - it.Sq;
-      float nlse2 = kNegInf, ndelta = 0.f;
-      if (i < it.Sq) {
-        const float l = a.lse[bo * a.l_sb + (int64_t)it.h * a.l_sh + (int64_t)(it.q_start + i) * a.l_ss];
-        nlse2 = (l == kNegInf) ? kNegInf : -l * kLog2e;
-        ndelta = -a.delta[bo * a.d_sb + (int64_t)it.h * a.d_sh + (int64_t)(it.q_start + i) * a.d_ss];
-      }
+      float nlse2 = pre_nlse2, ndelta = pre_ndelta;
+      if (pre_round != round) row_stats(it, nlse2, ndelta);
       const uint64_t sc2 = pack_f32x2(mods.scale_log2, mods.scale_log2);
       const uint64_t nl2 = pack_f32x2(nlse2, nlse2), nd2 = pack_f32x2(ndelta, ndelta);
       PROF_MARK(6);
@@ -1017,6 +1026,16 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
       }
       if (!ok) break;
 
+      {  // fetch the next item's row statistics now; the loads complete behind the epilogue
+        const int w2 = snake_item(round + 1, blockIdx.x, gridDim.x);
+        if (w2 < n_items) {
+          const DqItem it2 = dq_item(a, w2);
+          if (it2.valid && it2.n_total > 0) {
+            row_stats(it2, pre_nlse2, pre_ndelta);
+            pre_round = round + 1;
+          }
+        }
+      }
       // epilogue of the item: dQ * softmax_scale -> global, then hand the accumulator back
       const bool w_ok = mbar_wait(acc_done, used & 1);
       if (!__all_sync(kFull, w_ok)) {
