@@ -253,6 +253,8 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     bounded_sequence(a.cu_q, b, a.total_q, &q_start, &Sq);
     bounded_sequence(a.cu_k, b, a.total_k, &k_start, &Sk);
   }
+  // The dQ kernel launched behind this one needs none of its results: let its CTAs take over SMs as they free up.
+  grid_launch_dependents();
   const int k0 = ktile * 128;
   if (k0 >= Sk) return;
   const int tb = a.varlen ? 0 : b;
@@ -1121,8 +1123,22 @@ int launch_typed(const fa_attn_params& p, const BwdArgs& a0, int parts, cudaStre
     if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "backward smem opt-in failed: %s", cudaGetErrorString(e));
     a.num_tiles = (p.seqlen_q + 127) / 128;
     const int n_items = a.num_tiles * p.batch * p.heads_q;
-    kern<<<dim3(n_items < sm_count() ? n_items : sm_count()), kBwdThreads, smem_dq, stream>>>(mq, mk, mv, mdo, a);
-    e = cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(n_items < sm_count() ? n_items : sm_count());
+    cfg.blockDim = dim3(kBwdThreads);
+    cfg.dynamicSmemBytes = smem_dq;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr = {};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    if (parts & FA_BWD_DKDV) {
+      // dQ reads nothing the dK/dV kernel writes, and that kernel started only after delta was complete: its CTAs
+      // may begin while the last dK/dV CTAs drain.
+      cfg.attrs = &attr;
+      cfg.numAttrs = 1;
+    }
+    e = cudaLaunchKernelEx(&cfg, kern, mq, mk, mv, mdo, a);
+    if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "dQ launch failed: %s", cudaGetErrorString(e));
   }
   return 0;

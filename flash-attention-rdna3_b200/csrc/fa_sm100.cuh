@@ -75,6 +75,13 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
+// Programmatic dependent launch: tells the runtime that a kernel launched behind this one with the programmatic
+// stream-serialization attribute may start once every CTA of this grid has executed this (or has exited). Without
+// such a dependent kernel it does nothing.
+__device__ __forceinline__ void grid_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // ---------------------------------------------------------------------------------------------
 // TMA (tiled, 4-D, no cluster broadcast): global -> shared, completion on an mbarrier
 // ---------------------------------------------------------------------------------------------
