@@ -47,9 +47,10 @@ STEP_FLOPS = FWD_FLOPS + BWD_FLOPS
 KERNEL_FLOPS = {"fwd": FWD_FLOPS, "bwd_dkdv": 0.8 * BWD_FLOPS, "bwd_dq": 0.2 * BWD_FLOPS}
 DELTA_BYTES = 2 * B * H * S * D * 2 + B * H * S * 4   # reads O and dO, writes delta
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch from the committed ncu captures (profiles/); null
-# where no capture exists yet.
-NCU_TRAFFIC_BYTES = {"fwd": None, "bwd_dkdv": None, "bwd_dq": None}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of this workload, from the committed ncu captures
+# (profiles/fwd_bwd_2x16x2048x128_causal_fp16.md). Reads match the operand sizes (every input once); most of the
+# output is still in the write-back L2 when the kernel ends, so the write counter is below the output size.
+NCU_TRAFFIC_BYTES = {"fwd": 51.67e6, "bwd_dkdv": 75.36e6, "bwd_dq": 71.65e6}
 
 
 def load_peaks():
@@ -462,9 +463,15 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--skip-extras", action="store_true", help="skip decode numbers and the CPU baseline")
+    ap.add_argument("--decode-only", action="store_true", help="only the decode numbers (one GPU), as their own JSON line")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.decode_only:
+        import fa_b200  # noqa: F401  (fails loudly without the CUDA library)
+        device = torch.device("cuda", 0)
+        torch.cuda.set_device(0)
+        print(json.dumps({"decode": decode_extras(device, Flusher(device), load_peaks())}))
     else:
         gpu_arm(args)
 
