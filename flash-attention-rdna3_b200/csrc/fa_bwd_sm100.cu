@@ -1,25 +1,26 @@
 // FlashAttention-2 backward for sm_100a as two tcgen05 kernels (delta = rowsum(O*dO) is computed
 // before them). Accumulators live in tensor memory; operand tiles arrive by TMA. Both kernels walk their
-// streamed operand in steps of 64 rows and double-buffer the two score tiles of a step in TMEM, so the
-// tensor core works on step n+1 / n+2 while a compute group does the elementwise math of step n:
-//   warps 0-3   compute group 0: even steps, TMEM buffer 0   (thread = one TMEM lane = one row)
-//   warps 4-7   compute group 1: odd steps,  TMEM buffer 1
+// streamed operand in steps of 128 rows, so every MMA is 128 x 128 x 16 or 128 x D x 16 (N = 64 would run the
+// tensor pipe at half rate), and split the elementwise work of a step into two phases that overlap MMAs of the
+// neighbouring steps:   phase 1  P = exp2(S*c - lse)      phase 2  dS = P * (dP - delta)
+//   warps 0-3   compute group 0: columns [0,64) of every step   (thread = one TMEM lane = one row)
+//   warps 4-7   compute group 1: columns [64,128)
 //   warp  8     TMA producer (one lane)
 //   warp  9     MMA issuer (one lane)
 //
 // dK/dV kernel: one CTA per 128-key tile of one (batch, kv head); K and V stay in shared memory and
-// the CTA walks 64-query steps of every query head of the GQA group (no atomics, fixed summation order):
-//     S^T  = K Q^T          dP^T = V dO^T                  (M = 128 keys, N = 64 queries)
-//     P^T  = exp2(S^T*c - lse[q]) ;  dS^T = P^T * (dP^T - delta[q])      (registers; lse/delta per column)
+// the CTA walks 128-query steps of every query head of the GQA group (no atomics, fixed summation order):
+//     S^T  = K Q^T          dP^T = V dO^T                  (M = 128 keys, N = 128 queries)
+//     P^T  = exp2(S^T*c - lse[q]) ;  dS^T = P^T * (dP^T - delta[q])      (lse/delta per column, staged in smem)
 //     dV  += P^T dO         dK  += dS^T Q                  (A from TMEM, B = the same smem tiles, MN-major)
-// TMEM: S^T bufs [0,64) [64,128); dP^T bufs [128,192) [192,256); dK [256,256+D); dV [256+D,256+2D).
+// TMEM: S^T/P^T [0,128); dP^T/dS^T [128,256); dK [256,256+D); dV [256+D,256+2D).
 //
-// dQ kernel: one CTA per 128-query tile of one (batch, head); Q and dO stay resident, K/V stream in
-// 64-key steps:   S = Q K^T    dP = dO V^T    dS = P*(dP - delta[row])    dQ += dS K
-// TMEM: S bufs [0,64) [64,128); dP bufs [128,192) [192,256); dQ [256,256+D).
+// dQ kernel: persistent CTAs walking 128-query tiles; Q and dO stay resident, K/V stream in 128-key steps:
+//     S = Q K^T    dP = dO V^T    dS = P*(dP - delta[row])    dQ += dS K
+// TMEM: S buffers [0,128) [128,256); dP [256,384); dQ [384,384+D).
 //
-// The 16-bit P^T / dS^T (and dS) operands overwrite the first 32 columns of their own 64-column score
-// buffer, 16 columns at a time, only over columns the writing thread has already consumed.
+// The 16-bit P^T / dS^T (and dS) operands overwrite fp32 score columns of their own group's half, 16 columns at
+// a time, only over columns the writing thread has already consumed.
 //
 // Math follows fa_rdna3/kernels/_common.py:347-508 and fa_rdna3/kernels/backward.py:56-322 (varlen:
 // fa_rdna3/kernels/varlen.py:193-421): P recomputed from LSE, rows with LSE = -inf contribute nothing,
