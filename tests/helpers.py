@@ -55,6 +55,11 @@ def assert_close_o(got, want, dtype, what="out"):
 
 
 def assert_close_grad(got, want, what):
-    err = rel_l2(got, want)
+    """Relative L2 error <= 1e-2. A gradient that is identically zero in exact arithmetic (one visible key: P = 1, so
+    dS = P * (dP - delta) = 0 and dQ = dK = 0) has no scale to be relative to: when the reference's RMS is below
+    1e-3 (inputs are N(0,1), real gradients are far above that) the error is measured against an RMS of 1e-3."""
+    a, b = got.float().cpu(), want.float().cpu()
+    floor = 1e-3 * max(b.numel(), 1) ** 0.5
+    err = float((a - b).norm() / b.norm().clamp_min(floor))
     assert err <= GRAD_REL_L2, f"{what}: rel-L2 {err:.3e} > {GRAD_REL_L2:.1e}"
     assert not torch.isnan(got.float()).any(), f"{what}: NaN"
