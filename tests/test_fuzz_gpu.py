@@ -2,7 +2,8 @@
 
 The fixed grids of the other files follow the reference's tests; this file walks the corners between them
 (ragged lengths around the 128-row tile, cross-attention offsets, windows that start inside a tile, GQA ratios,
-empty and one-token sequences in a packed batch), 48 dense and 16 packed cases, every one reproducible from its index.
+empty and one-token sequences in a packed batch, decode and paged-decode shapes over both kernel families): 48 dense,
+16 packed, 32 decode and 32 paged cases, every one reproducible from its index.
 """
 import random
 
@@ -60,3 +61,69 @@ def packed_case(index):
 def test_packed_random_lengths(index):
     lengths, heads, kv_heads, head_dim, dtype, opts = packed_case(index)
     run_varlen(lengths, heads, kv_heads, head_dim, dtype=dtype, path="tcgen05", seed=index, **opts)
+
+
+# ------------------------------------------------------------------------------------------ decode
+def decode_case(index):
+    rng = random.Random(11000 + index)
+    kv_heads = rng.choice([1, 2, 8])
+    group = rng.choice([1, 4])
+    seqlen_k = rng.choice([1, 2, 127, 128, 129, 255, 257, rng.randint(300, 3000), 4096, rng.randint(4097, 9000)])
+    return dict(batch=rng.randint(1, 3), heads=kv_heads * group, kv_heads=kv_heads, seqlen_q=rng.choice([1, 1, 2, 4]),
+                seqlen_k=seqlen_k, head_dim=rng.choice([64, 128]), dtype=rng.choice([torch.float16, torch.bfloat16]),
+                splits=rng.choice([1, 2, 3, 4, 8, 16]), path=rng.choice([0, 1, 2]))
+
+
+@pytest.mark.parametrize("index", range(32))
+def test_decode_random_shape(index):
+    from fa_b200 import interface
+    from helpers import assert_close_o, seeded
+    from oracle import attention_oracle as oracle
+
+    c = decode_case(index)
+    q = seeded(index + 1, c["batch"], c["heads"], c["seqlen_q"], c["head_dim"], dtype=c["dtype"])
+    k = seeded(index + 2, c["batch"], c["kv_heads"], c["seqlen_k"], c["head_dim"], dtype=c["dtype"])
+    v = seeded(index + 3, c["batch"], c["kv_heads"], c["seqlen_k"], c["head_dim"], dtype=c["dtype"])
+    path = c["path"]
+    tc_ok = interface._tensor_core_decode_ok(q, c["head_dim"], c["heads"] // c["kv_heads"] * c["seqlen_q"], 0.1)
+    if path == 1 and not (tc_ok and c["splits"] >= 2 and c["splits"] % 2 == 0):
+        path = 0  # the tensor-core kernel does not take this case (it wants an even split count): library's choice
+    out = interface._decode_impl(q, k, v, 0.1, c["splits"], force_path=path)
+    ref, _ = oracle.decode_ref(q.cpu(), k.cpu(), v.cpu(), softmax_scale=0.1)
+    assert_close_o(out, ref, c["dtype"], str(c))
+
+
+def paged_case(index):
+    rng = random.Random(13000 + index)
+    kv_heads = rng.choice([1, 2, 8])
+    group = rng.choice([1, 4])
+    block_size = rng.choice([8, 16, 32, 64, 128])
+    batch = rng.randint(1, 4)
+    contexts = [rng.choice([0, 1, block_size - 1, block_size, block_size + 1, rng.randint(2, 3000)]) for _ in range(batch)]
+    if max(contexts) == 0:
+        contexts[0] = 7
+    return dict(batch=batch, heads=kv_heads * group, kv_heads=kv_heads, head_dim=rng.choice([64, 128]),
+                block_size=block_size, contexts=contexts, dtype=rng.choice([torch.float16, torch.bfloat16]),
+                splits=rng.choice([1, 2, 4, 6, 16]), path=rng.choice([0, 1, 2]))
+
+
+@pytest.mark.parametrize("index", range(32))
+def test_paged_random_shape(index):
+    import math
+
+    from fa_b200 import interface
+    from helpers import assert_close_o
+    from oracle import attention_oracle as oracle
+    from test_decode_gpu import make_paged
+
+    c = paged_case(index)
+    q, kc, vc, table, ctx = make_paged(c["batch"], c["heads"], c["kv_heads"], c["head_dim"], c["block_size"],
+                                       c["contexts"], dtype=c["dtype"], seed=index)
+    scale = 1.0 / math.sqrt(c["head_dim"])
+    path = c["path"]
+    tc_ok = interface._paged_tensor_core_ok(q, c["head_dim"], c["heads"], c["kv_heads"], c["block_size"], scale)
+    if path == 1 and not (tc_ok and c["splits"] >= 2 and c["splits"] % 2 == 0):
+        path = 0
+    out, _ = interface._paged_launch(q, kc, vc, table, ctx, scale, c["splits"], force_path=path)
+    ref, _ = oracle.paged_ref(q.cpu(), kc.cpu(), vc.cpu(), table.cpu(), ctx.cpu())
+    assert_close_o(out, ref, c["dtype"], str(c))
