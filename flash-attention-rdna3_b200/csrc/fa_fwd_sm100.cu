@@ -25,7 +25,9 @@
 namespace fa {
 namespace {
 
-constexpr int kFwdThreads = 320;
+// Three warpgroups: two softmax groups and one group whose first two warps are the TMA producer and the MMA issuer
+// (the other two only take part in the register hand-over and the final barrier).
+constexpr int kFwdThreads = 384;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 struct FwdArgs {
@@ -164,7 +166,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_base_s;
 
-  if (warp == 8) {
+  // Register hand-over (every warp of a warpgroup executes the same instruction): the service group gives registers
+  // back, the softmax groups take them so that a whole 128-column S row fits in registers. Per scheduler partition:
+  // two softmax warps at 224 plus one service warp at 56 stay within the 512 registers per lane.
+  if (warp >= 8) {
+   asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+   if (warp == 8) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0 && any_work) {
       tma_prefetch_desc(&map_q);
@@ -201,7 +208,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         }
       }
     }
-  } else if (warp == 9) {
+   } else if (warp == 9) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0 && any_work) {
       constexpr uint32_t idesc_qk = make_idesc(DType<T>::kFormat, 128, 128, 0, 0);
@@ -286,8 +293,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       PROF_MARK(2);
       PROF_FLUSH(2, true);
     }
-  } else if (warp < 8) {
+   }
+  } else {
     // ------------------------------------------------------------------ softmax groups
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
     const int t = warp / 4, w4 = warp % 4;
     const int r_tile = w4 * 32 + lane;
     const int row = row_base + t * 128 + r_tile;
@@ -378,26 +387,27 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
           }
           l += sum;
         } else {
-          // Fast path, two streaming passes over the S row in TMEM so that few registers stay live.
-          // Pass 1: row maximum (four independent chains of three-input max).
+          // Fast path: the whole S row (128 fp32 values) is read from TMEM once and stays in registers between
+          // the maximum and the exponentials.
+          uint32_t r[128];
+#pragma unroll
+          for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
           float mx[4] = {kNegInf, kNegInf, kNegInf, kNegInf};
 #pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            uint32_t r[64];
-            tmem_ld32(tS + half * 64, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
-            tmem_ld32(tS + half * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
-            tc_wait_ld_regs(*reinterpret_cast<uint32_t(*)[32]>(&r[0]));
-            tc_wait_ld_regs(*reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+          for (int c = 0; c < 4; ++c) {
+            // wait::ld covers every load issued so far; naming the chunk pins its uses behind the wait
+            if (c == 0) tc_wait_ld_regs(*reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+            else asm volatile("" : "+r"(r[c * 32]), "+r"(r[c * 32 + 31]));
             if (tile_masked) {
 #pragma unroll
-              for (int c = 0; c < 64; ++c)
-                if (half * 64 + c < c_lo || half * 64 + c > c_hi) r[c] = __float_as_uint(kNegInf);
+              for (int e = 0; e < 32; ++e)
+                if (c * 32 + e < c_lo || c * 32 + e > c_hi) r[c * 32 + e] = __float_as_uint(kNegInf);
             }
 #pragma unroll
-            for (int c = 0; c < 64; c += 8) {
+            for (int e = 0; e < 32; e += 8) {
 #pragma unroll
               for (int u = 0; u < 4; ++u)
-                mx[u] = fmax3(mx[u], __uint_as_float(r[c + 2 * u]), __uint_as_float(r[c + 2 * u + 1]));
+                mx[u] = fmax3(mx[u], __uint_as_float(r[c * 32 + e + 2 * u]), __uint_as_float(r[c * 32 + e + 2 * u + 1]));
             }
           }
           const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * mods.scale_log2;  // scale > 0 here
@@ -413,27 +423,17 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
           const float m_eff = (m_used == kNegInf) ? 0.f : m_used;
           PROF_MARK(3);
 
-          // Pass 2: p = exp2(s*scale - m) with packed fp32x2 FMA/ADD, 32 columns at a time; the 16-bit P chunk
-          // goes to columns [16c, 16c+16), which only covers S columns this thread has already consumed.
+          // p = exp2(s*scale - m) with packed fp32x2 FMA/ADD, 32 columns at a time; the 16-bit P chunk goes to
+          // columns [16c, 16c+16) of the S tile.
           const uint64_t sc2 = pack_f32x2(mods.scale_log2, mods.scale_log2);
           const uint64_t nm2 = pack_f32x2(-m_eff, -m_eff);
           uint64_t acc2[4] = {0ull, 0ull, 0ull, 0ull};
-          uint32_t rb[2][32];
-          tmem_ld32(tS, rb[0]);
-          tc_wait_ld_regs(rb[0]);
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
-            if (c < 3) tmem_ld32(tS + (c + 1) * 32, rb[(c + 1) & 1]);
-            uint32_t (&r)[32] = rb[c & 1];
-            if (tile_masked) {
-#pragma unroll
-              for (int e = 0; e < 32; ++e)
-                if (c * 32 + e < c_lo || c * 32 + e > c_hi) r[e] = __float_as_uint(kNegInf);
-            }
             uint32_t pk[16];
 #pragma unroll
             for (int e = 0; e < 16; ++e) {
-              const uint64_t x2 = fma_f32x2(pack_u32x2(r[2 * e], r[2 * e + 1]), sc2, nm2);
+              const uint64_t x2 = fma_f32x2(pack_u32x2(r[c * 32 + 2 * e], r[c * 32 + 2 * e + 1]), sc2, nm2);
               float x0, x1;
               unpack_f32x2(x2, &x0, &x1);
               const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
@@ -441,7 +441,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
               pk[e] = DType<T>::pack2(p0, p1);
             }
             tmem_st16(tS + c * 16, pk);
-            if (c < 3) tc_wait_ld_regs(rb[(c + 1) & 1]);
           }
           float s0, s1;
           unpack_f32x2(add_f32x2(add_f32x2(acc2[0], acc2[1]), add_f32x2(acc2[2], acc2[3])), &s0, &s1);
