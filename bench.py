@@ -405,7 +405,7 @@ def gpu_arm(args):
 
 
 def decode_extras(device, flush, peaks, iters=40, nsets=4):
-    """Split-K decode (4x32x8192x128) and paged decode (4 seqs, 32/8 heads, page 16, 16384 tokens each) through the
+    """Split-K decode (4x32x16384x128) and paged decode (4 seqs, 32/8 heads, page 16, 16384 tokens each) through the
     C ABI: `iters` launches back to back over `nsets` different K/V sets (each set is larger than L2, so every
     launch streams its K/V from HBM); GB/s counts K and V bytes once (kv heads)."""
     from fa_b200 import _lib, interface
@@ -428,7 +428,7 @@ def decode_extras(device, flush, peaks, iters=40, nsets=4):
         return s.elapsed_time(e) / iters
 
     # split-K decode, MHA
-    Bd, Hd, Sk, Dd = 4, 32, 8192, 128
+    Bd, Hd, Sk, Dd = 4, 32, 16384, 128
     q = seeded(1004, Bd, Hd, 1, Dd).to(device)
     out = torch.empty_like(q)
     splits = interface._decode_splits_b200(Bd, Hd, 1, Sk, sm, tensor_core=True)
@@ -450,7 +450,7 @@ def decode_extras(device, flush, peaks, iters=40, nsets=4):
         params.append(p)
     ms = run(lib.fa_decode_splitk, params)
     nbytes = 2 * Bd * Hd * Sk * Dd * 2
-    res["splitk_4x32x8192x128"] = {"us": ms * 1e3, "gbs": nbytes / ms / 1e6, "frac_hbm": nbytes / ms / 1e6 / peaks["hbm_gbs"],
+    res["splitk_4x32x16384x128"] = {"us": ms * 1e3, "gbs": nbytes / ms / 1e6, "frac_hbm": nbytes / ms / 1e6 / peaks["hbm_gbs"],
                                    "num_splits": splits}
     del sets, params
 
@@ -489,7 +489,7 @@ def decode_extras(device, flush, peaks, iters=40, nsets=4):
     nbytes = Bp * 16384 * 2 * Hk * Dd * 2
     res["paged_4x32/8x16384x128"] = {"us": ms * 1e3, "gbs": nbytes / ms / 1e6, "frac_hbm": nbytes / ms / 1e6 / peaks["hbm_gbs"],
                                      "num_splits": splits}
-    res["note"] = ("KV bytes read once (kv heads); %d launches back to back over %d K/V sets of 0.27-0.54 GB each "
+    res["note"] = ("KV bytes read once (kv heads); %d launches back to back over %d K/V sets of 0.27-1.07 GB each "
                    "(larger than L2); peak = measured copy bandwidth" % (iters, nsets))
     return res
 

@@ -129,9 +129,10 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     }
     mbar_fence_init();
   }
-  if (kPaged) {
-    // V tiles (the odd slots: kSlots is even) may be read at rows no load ever wrote (keys past the context):
-    // start them from zeros
+  if (kPaged && jhi == tiles_total) {
+    // V tiles (the odd slots: kSlots is even) may be read at rows no load ever wrote: tokens past the context in the
+    // sequence's last tile. Only the CTA that owns that tile can meet them before full tiles have filled its slots:
+    // it starts its V slots from zeros (every other CTA only ever reads rows a load of real, finite data wrote).
     static_assert(kSlots % 2 == 0, "K and V tiles must keep to their own slots");
     for (int i = tid; i < (kSlots / 2) * (kTileBytes / 16); i += kThreads) {
       const int slot = 2 * (i / (kTileBytes / 16)) + 1, w = i % (kTileBytes / 16);
@@ -139,6 +140,28 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     }
     fence_proxy_async_smem();
   }
+  // paged: lane u < upt of the producer warp holds the page id and the token counts of unit u of a tile. The first
+  // look-up is issued here, so that its global load runs behind the TMEM allocation and the barrier set-up.
+  auto lookup = [&](int t, int* phys_out, int* nvalid_out, int* tokoff_out) {
+    int phys = a.num_blocks, nvalid = 0, tokoff = 0;
+    if (kPaged) {
+      const int u = (jlo + t) * a.upt + lane;  // local unit index
+      const int lp = u / a.upp;
+      if (t < ntiles && lane < a.upt && lp < nlocal_pages) {
+        const int lb = a.first_block + lp * a.block_step;
+        tokoff = (u % a.upp) * a.tpt;
+        const int id = a.block_table[(int64_t)b * a.bt_sb + (int64_t)lb * a.bt_sk];
+        nvalid = max(0, min(a.tpt, ctx - (lb * a.block_size + tokoff)));
+        if (id >= 0 && id < a.num_blocks) phys = id;
+        else nvalid = -nvalid;  // present but unreadable: box aimed past the pool reads zeros, keys masked
+      }
+    }
+    *phys_out = phys;
+    *nvalid_out = nvalid;
+    *tokoff_out = tokoff;
+  };
+  int phys_next = 0, nvalid_next = 0, tokoff_next = 0;
+  if (kPaged && warp == 8 && ntiles > 0) lookup(0, &phys_next, &nvalid_next, &tokoff_next);
   if (warp == 9) {
     tmem_alloc(&tmem_base_s, 512);
     tmem_relinquish();
@@ -158,28 +181,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 #pragma unroll
         for (int c = 0; c < kChunks; ++c) tma_load_4d(sQ + c * 16384, &map_q, &q_full, c * 64, 0, hk, b);
       }
-      // paged: lane u < upt holds the page id and the token counts of unit u of a tile
       const int unit_rows_bytes = kPaged ? a.tpt * a.heads_kv * 128 : 0;
-      auto lookup = [&](int t, int* phys_out, int* nvalid_out, int* tokoff_out) {
-        int phys = a.num_blocks, nvalid = 0, tokoff = 0;
-        if (kPaged) {
-          const int u = (jlo + t) * a.upt + lane;  // local unit index
-          const int lp = u / a.upp;
-          if (t < ntiles && lane < a.upt && lp < nlocal_pages) {
-            const int lb = a.first_block + lp * a.block_step;
-            tokoff = (u % a.upp) * a.tpt;
-            const int id = a.block_table[(int64_t)b * a.bt_sb + (int64_t)lb * a.bt_sk];
-            nvalid = max(0, min(a.tpt, ctx - (lb * a.block_size + tokoff)));
-            if (id >= 0 && id < a.num_blocks) phys = id;
-            else nvalid = -nvalid;  // present but unreadable: box aimed past the pool reads zeros, keys masked
-          }
-        }
-        *phys_out = phys;
-        *nvalid_out = nvalid;
-        *tokoff_out = tokoff;
-      };
-      int phys_next = 0, nvalid_next = 0, tokoff_next = 0;
-      if (kPaged) lookup(0, &phys_next, &nvalid_next, &tokoff_next);
       bool ok = true;
       for (int t = 0; t < ntiles && ok; ++t) {
         const int phys = phys_next, nvalid = nvalid_next, tokoff = tokoff_next;
