@@ -1,8 +1,8 @@
 """Generate tests/golden/*.npz from the reference package itself.
 
-Run in the build container, where the reference checkout is mounted read-only:
+Run where a checkout of the reference (chelokot/flash-attention-rdna3) and Triton are available:
 
-    TRITON_INTERPRET=1 python tests/golden/make_golden.py [/root/reference]
+    TRITON_INTERPRET=1 python tests/golden/make_golden.py <path to the reference checkout>
 
 The reference's Triton kernels are executed on CPU tensors by Triton's interpreter, through the
 reference's own public functions and launch glue. Three things are patched, none of which touches the
@@ -18,7 +18,9 @@ import sys
 import types
 
 os.environ.setdefault("TRITON_INTERPRET", "1")
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    sys.exit("usage: make_golden.py <path to the reference checkout>")
+REF = sys.argv[1]
 sys.path.insert(0, REF)
 
 import numpy as np
