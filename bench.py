@@ -50,7 +50,7 @@ DELTA_BYTES = 2 * B * H * S * D * 2 + B * H * S * 4   # reads O and dO, writes d
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of this workload, from the committed ncu captures
 # (profiles/fwd_bwd_2x16x2048x128_causal_fp16.md). Reads match the operand sizes (every input once); most of the
 # output is still in the write-back L2 when the kernel ends, so the write counter is below the output size.
-NCU_TRAFFIC_BYTES = {"fwd": 51.67e6, "bwd_dkdv": 75.36e6, "bwd_dq": 71.65e6}
+NCU_TRAFFIC_BYTES = {"fwd": 52.0e6, "bwd_dkdv": 72.55e6, "bwd_dq": 71.51e6}
 
 
 def load_peaks():
