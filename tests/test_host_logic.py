@@ -38,6 +38,35 @@ def test_paged_split_heuristic():
     assert f(4, 32, 16, 1024, 96, requested_splits=7) == 7
 
 
+def test_b200_split_counts_fill_one_wave():
+    """The B200 defaults (not the reference's 48-CU table): properties every launch relies on."""
+    from fa_b200 import interface as I
+
+    sm = 148
+    # tensor-core split-K: even, one CTA per SM at most, at least two 128-key tiles per CTA
+    for batch, kv_heads, seqlen_k in [(4, 32, 8192), (4, 8, 16384), (1, 8, 16384), (16, 32, 8192), (1, 1, 256), (2, 4, 100)]:
+        s = I._decode_splits_b200(batch, kv_heads, 1, seqlen_k, sm, tensor_core=True)
+        assert s >= 2 and s % 2 == 0
+        assert batch * kv_heads * (s // 2) <= max(sm, batch * kv_heads)
+        assert (s // 2) <= max(1, -(-seqlen_k // 128) // 2)
+    assert I._decode_splits_b200(4, 32, 1, 16384, sm, tensor_core=True) == 2      # 128 CTAs already
+    assert I._decode_splits_b200(1, 8, 1, 16384, sm, tensor_core=True) == 36      # 18 CTAs per head -> 144 CTAs
+    # tensor-core paged: one CTA row per batch entry, even count, CTAs within one wave
+    s = I._paged_splits_b200(4, 8, 4, 16, 1024, sm, 16384, tensor_core=True)
+    assert s == 74 and 4 * (s // 2) == 148
+    s = I._paged_splits_b200(1, 8, 4, 16, 16, sm, 100, tensor_core=True)
+    assert s == 6                                                                  # 100 tokens = 7 tiles: 3 CTAs of 2-3 tiles
+    # CUDA-core kernels: slices of at least 512 keys (256 tokens paged), never more than 64 (32) of them
+    for seqlen_k in (100, 512, 4096, 100000):
+        s = I._decode_splits_b200(2, 4, 4, seqlen_k, sm)
+        assert 1 <= s <= 64 and (s == 1 or seqlen_k // s >= 256)
+    assert 1 <= I._paged_splits_b200(2, 4, 4, 16, 4096, sm) <= 32
+    # the fill rule: fewest splits within 3 % of the fullest last wave, once there is one full wave
+    assert I._fill_splits(32, 64, sm) == 18            # 576 CTAs on 296 slots: 97.3 % of two waves (37 would be 100 %: within 3 %)
+    assert I._fill_splits(1000, 8, sm) == 2            # 2000 CTAs: 96.5 % of 7 waves, 12 points better than one split
+    assert I._fill_splits(4, 64, sm, ctas_per_sm=1) == 37
+
+
 def test_alibi_slopes_values_and_errors():
     s = fa_b200.alibi_slopes(8, device="cpu")
     assert torch.allclose(s, torch.tensor([2.0 ** -(i + 1) for i in range(8)]))
