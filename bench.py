@@ -388,6 +388,10 @@ def gpu_arm(args):
         raise RuntimeError("end-to-end outputs did not arrive in host memory")
     tensor_bytes = B * H * S * D * 2
 
+    sharded = None
+    if distributed and not args.skip_extras:
+        sharded = sharded_decode_extra(device, rank, world)
+
     if rank != 0:
         if distributed:
             dist.destroy_process_group()
@@ -433,9 +437,49 @@ def gpu_arm(args):
     if not args.skip_extras and world == 1:
         line["decode"] = decode_extras(device, flush, peaks)
         line["cpu_baseline"] = cpu_baseline()
+    if sharded is not None:
+        line["decode_kv_sharded"] = sharded
     print(json.dumps(line))
     if distributed:
         dist.destroy_process_group()
+
+
+def sharded_decode_extra(device, rank, world, iters=20):
+    """Long-context paged decode with the KV pages of every sequence sharded block-cyclically over the ranks
+    (strong scaling of one fixed problem: 4 sequences x 262144 tokens, 32/8 heads, 16-token pages, 4.3 GB of KV):
+    local partial -> NCCL all-gather of (O, LSE) -> local merge. Every rank holds the whole pool here but reads only
+    the pages of its own blocks. Time = max over ranks of the CUDA-event time of `iters` calls."""
+    import torch.distributed as dist
+
+    from fa_b200 import distributed as fd
+
+    Bp, Hq, Hk, Dd, bs, ctx_len = 4, 32, 8, 128, 16, 262144
+    maxb = ctx_len // bs
+    nblocks = Bp * maxb
+    g = torch.Generator().manual_seed(1006)
+    q = torch.randn(Bp, Hq, Dd, generator=g).half().to(device)
+    table = torch.randperm(nblocks, generator=g).to(torch.int32).reshape(Bp, maxb).to(device)
+    ctx = torch.full((Bp,), ctx_len, dtype=torch.int32, device=device)
+    pools = [(torch.randn(nblocks, bs, Hk, Dd, device=device, dtype=torch.float16),
+              torch.randn(nblocks, bs, Hk, Dd, device=device, dtype=torch.float16)) for _ in range(2)]
+    for kc, vc in pools:
+        fd.paged_decode_kv_sharded(q, kc, vc, table, ctx)          # checks that the ranks agree, warms up NCCL
+    torch.cuda.synchronize()
+    dist.barrier()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for i in range(iters):
+        kc, vc = pools[i & 1]
+        fd.paged_decode_kv_sharded(q, kc, vc, table, ctx, check_ranks_agree=False)
+    e.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([s.elapsed_time(e) / iters], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    nbytes = Bp * ctx_len * 2 * Hk * Dd * 2
+    return {"us": ms * 1e3, "gbs_all_gpus": nbytes / ms / 1e6, "kv_bytes": nbytes, "n_gpus": world,
+            "workload": "paged decode, 4 seqs x 262144 tokens, 32/8 heads, page 16, pages sharded block-cyclically",
+            "collective": "all_gather of batch*heads*(head_dim+1) floats per rank + local merge", "scaling": "strong"}
 
 
 def decode_extras(device, flush, peaks, iters=40, nsets=4):

@@ -65,14 +65,15 @@ def _merge_partials_cuda(gathered_o, gathered_lse, out_dtype):
 
 
 def paged_decode_kv_sharded(query, k_cache, v_cache, block_table, context_lens, softmax_scale=None, *,
-                            group=None, max_context_len=None, num_splits=None,
+                            group=None, max_context_len=None, num_splits=None, check_ranks_agree=True,
                             _local_partial=None, _merge=None):
     """Paged decode with the KV pages of each sequence sharded block-cyclically over the ranks of `group`.
 
     Every rank passes the full ``query``, ``block_table`` and ``context_lens`` and its own page pool
     (only the pages of its logical blocks are read). Returns the merged ``(batch, q_heads, head_dim)``
-    result on every rank. ``_local_partial`` / ``_merge`` replace the CUDA kernels in CPU tests of the
-    protocol.
+    result on every rank. ``check_ranks_agree=False`` skips the exchange of problem shapes that guards against
+    ranks describing different problems (an object all-gather through the host, the only synchronising step of a
+    call). ``_local_partial`` / ``_merge`` replace the CUDA kernels in CPU tests of the protocol.
     """
     import torch.distributed as dist
 
@@ -88,11 +89,12 @@ def paged_decode_kv_sharded(query, k_cache, v_cache, block_table, context_lens, 
     scale = 1.0 / math.sqrt(head_dim) if softmax_scale is None else float(softmax_scale)
 
     # every rank must describe the same problem; a mismatch would corrupt the merge silently
-    meta = [batch, q_heads, head_dim, int(block_table.shape[1]), int(k_cache.shape[1])]
-    all_meta = [None] * world
-    dist.all_gather_object(all_meta, meta, group=group)
-    if any(m != meta for m in all_meta):
-        raise ValueError(f"ranks disagree on the decode problem: {all_meta}")
+    if check_ranks_agree:
+        meta = [batch, q_heads, head_dim, int(block_table.shape[1]), int(k_cache.shape[1])]
+        all_meta = [None] * world
+        dist.all_gather_object(all_meta, meta, group=group)
+        if any(m != meta for m in all_meta):
+            raise ValueError(f"ranks disagree on the decode problem: {all_meta}")
 
     if _local_partial is None:
         sm_count = torch.cuda.get_device_properties(query.device).multi_processor_count
