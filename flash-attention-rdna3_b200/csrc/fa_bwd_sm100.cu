@@ -71,6 +71,7 @@ __device__ __forceinline__ ScoreMods make_mods(const BwdArgs& a, int b, int h, i
   ScoreMods m;
   m.scale_log2 = a.softmax_scale * kLog2e;
   m.cap_log2 = a.softcap > 0.f ? a.softcap * kLog2e : 0.f;
+  m.inv_cap_log2 = a.softcap > 0.f ? 1.f / m.cap_log2 : 0.f;
   m.alibi_slope_log2 = a.alibi ? a.alibi[h] * kLog2e : 0.f;
   m.bias = nullptr;
   m.bias_dtype = a.bias_dtype;
@@ -100,22 +101,34 @@ __device__ __forceinline__ bool block_needs_mask(const ScoreMods& m, int r0, int
          (!m.causal && m.window_right >= 0 && (k0 + nk - 1 > r0 + off + m.window_right));
 }
 
-// General (slow) element: softcap / bias / ALiBi / dropout. nlse2 = -lse*log2(e) (or -inf), ndelta = -delta.
-__device__ __forceinline__ void bwd_element_mods(const ScoreMods& m, bool inside, float raw_s, float raw_dp, float nlse2,
-                                                 float ndelta, int i, int j, float* p_drop, float* ds) {
-  float t = 0.f;
-  float p = fast_exp2(m.logit(raw_s, i, j, &t) + nlse2);
-  if (!inside) p = 0.f;
-  float dp = raw_dp, pd = p;
-  if (m.dropout_p > 0.f) {
-    const bool kd = m.dropout_keep(i, j);
-    pd = kd ? p * m.inv_keep : 0.f;
-    dp = kd ? dp * m.inv_keep : 0.f;
+// General path (softcap / bias / ALiBi / dropout) for 32 consecutive elements of one accumulator row: element e is
+// (query i0, key j0 + e) when kAlongKeys (dQ kernel), (query i0 + e, key j0) otherwise (dK/dV kernel). In: x = raw
+// scores, g = raw dP. Out: x = probabilities as the dV product wants them (dropped and rescaled under dropout),
+// g = dS. nl / nd hold -lse*log2(e) (or -inf) and -delta of the query: one value when kAlongKeys, 32 otherwise.
+// Elements outside [e_lo, e_hi] are masked out.
+template <bool kAlongKeys>
+__device__ __forceinline__ void bwd_mods_chunk32(const ScoreMods& m, float (&x)[32], float (&g)[32], const float* nl,
+                                                 const float* nd, int i0, int j0, int e_lo, int e_hi) {
+  const uint32_t kept = mods_dropout_bits32<kAlongKeys>(m, i0, j0);
+  const bool dropout = m.dropout_p > 0.f;
+  const float inv_keep = m.inv_keep;
+  if (dropout) {
+#pragma unroll
+    for (int e = 0; e < 32; ++e) g[e] = ((kept >> e) & 1u) ? g[e] * inv_keep : 0.f;
   }
-  float d = p * (dp + ndelta);
-  if (m.cap_log2 > 0.f) d *= (1.f - t * t);
-  *p_drop = pd;
-  *ds = d;
+#pragma unroll
+  for (int e = 0; e < 32; ++e) g[e] += nd[kAlongKeys ? 0 : e];
+  mods_logits32<kAlongKeys>(m, x, i0, j0, &g);  // g picks up the soft-cap chain factor
+#pragma unroll
+  for (int e = 0; e < 32; ++e) {
+    const float p = (e >= e_lo && e <= e_hi) ? fast_exp2(x[e] + nl[kAlongKeys ? 0 : e]) : 0.f;
+    x[e] = p;
+    g[e] *= p;
+  }
+  if (dropout) {
+#pragma unroll
+    for (int e = 0; e < 32; ++e) x[e] = ((kept >> e) & 1u) ? x[e] * inv_keep : 0.f;
+  }
 }
 
 // Converts a 32-column fp32 slice of a TMEM accumulator to 16-bit and writes it to a global row.
@@ -520,26 +533,23 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         mbar_arrive(ds_full);
         PROF_MARK(5);
       } else {
-        // ---- general element path: both products at once
-#pragma unroll
+        // ---- general path: both products at once, 32 columns per (rolled) pass
+#pragma unroll 1
         for (int c = 0; c < 2; ++c) {
           uint32_t s[32], dp[32];
           tmem_ld32(tS + c * 32, s);
           tmem_ld32(tDP + c * 32, dp);
           tc_wait_ld_regs(s);
           tc_wait_ld_regs(dp);
+          const int col0 = wg * 64 + c * 32;
+          float(&x)[32] = *reinterpret_cast<float(*)[32]>(&s[0]);
+          float(&gr)[32] = *reinterpret_cast<float(*)[32]>(&dp[0]);
+          bwd_mods_chunk32<false>(mods, x, gr, nlse_s + col0, ndelta_s + col0, q0 + col0, j, c_lo - col0, c_hi - col0);
           uint32_t pkk[16], dsk[16];
 #pragma unroll
           for (int e = 0; e < 16; ++e) {
-            const int col = wg * 64 + c * 32 + 2 * e;
-            float p0, p1, d0, d1;
-            bwd_element_mods(mods, !masked || (col >= c_lo && col <= c_hi), __uint_as_float(s[2 * e]),
-                             __uint_as_float(dp[2 * e]), nlse_s[col], ndelta_s[col], q0 + col, j, &p0, &d0);
-            bwd_element_mods(mods, !masked || (col + 1 >= c_lo && col + 1 <= c_hi), __uint_as_float(s[2 * e + 1]),
-                             __uint_as_float(dp[2 * e + 1]), nlse_s[col + 1], ndelta_s[col + 1], q0 + col + 1, j, &p1,
-                             &d1);
-            pkk[e] = DType<T>::pack2(p0, p1);
-            dsk[e] = DType<T>::pack2(d0, d1);
+            pkk[e] = DType<T>::pack2(x[2 * e], x[2 * e + 1]);
+            dsk[e] = DType<T>::pack2(gr[2 * e], gr[2 * e + 1]);
           }
           tmem_st16(tS + c * 16, pkk);
           tmem_st16(tDP + c * 16, dsk);
@@ -1001,24 +1011,21 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
           dscore_row<T>(p1, d1, nd2, dsk);
           tmem_st16(tS + 16, dsk);
         } else {
-#pragma unroll
+          // ---- general path, 32 columns per (rolled) pass
+#pragma unroll 1
           for (int c = 0; c < 2; ++c) {
             uint32_t sv[32], dp[32];
             tmem_ld32(tS + c * 32, sv);
             tmem_ld32(tDP + c * 32, dp);
             tc_wait_ld_regs(sv);
             tc_wait_ld_regs(dp);
+            const int col0 = wg * 64 + c * 32;
+            float(&x)[32] = *reinterpret_cast<float(*)[32]>(&sv[0]);
+            float(&gr)[32] = *reinterpret_cast<float(*)[32]>(&dp[0]);
+            bwd_mods_chunk32<true>(mods, x, gr, &nlse2, &ndelta, i, ks + col0, c_lo - col0, c_hi - col0);
             uint32_t dsk[16];
 #pragma unroll
-            for (int e = 0; e < 16; ++e) {
-              const int col = wg * 64 + c * 32 + 2 * e;
-              float pa, pb, da, db;
-              bwd_element_mods(mods, !masked || (col >= c_lo && col <= c_hi), __uint_as_float(sv[2 * e]),
-                               __uint_as_float(dp[2 * e]), nlse2, ndelta, i, ks + col, &pa, &da);
-              bwd_element_mods(mods, !masked || (col + 1 >= c_lo && col + 1 <= c_hi), __uint_as_float(sv[2 * e + 1]),
-                               __uint_as_float(dp[2 * e + 1]), nlse2, ndelta, i, ks + col + 1, &pb, &db);
-              dsk[e] = DType<T>::pack2(da, db);
-            }
+            for (int e = 0; e < 16; ++e) dsk[e] = DType<T>::pack2(gr[2 * e], gr[2 * e + 1]);
             tmem_st16(tS + c * 16, dsk);
           }
         }

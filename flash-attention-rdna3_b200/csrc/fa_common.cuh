@@ -134,6 +134,21 @@ __host__ __device__ __forceinline__ float philox_uniform(uint64_t seed, uint64_t
   return static_cast<float>(x) * 4.6566127342e-10f;
 }
 
+// The same draw as a real call: the ten Philox rounds are about a hundred instructions, and the tensor-core kernels
+// would otherwise inline them once per element of their unrolled tile loops (hundreds of copies that cost
+// instruction-cache misses on every launch, dropout or not).
+static __device__ __noinline__ float philox_uniform_call(uint64_t seed, uint64_t offset) {
+  return philox_uniform(seed, offset);
+}
+
+// tanh(z) from one exp2 and one reciprocal of the special-function unit: 1 - 2 / (e^(2z) + 1). Absolute error about
+// 3e-7 (exact limits -1 and 1 for large |z|), far inside the tolerance of a soft-capped logit.
+__device__ __forceinline__ float fast_tanh(float z) {
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(z * 2.8853900817779268f));
+  return 1.f - __fdividef(2.f, e + 1.f);
+}
+
 // ---------------------------------------------------------------------------------------------
 // Score modifiers for one (batch, head): everything a kernel needs to turn a raw q.k dot product at
 // (query row i, key column j) of one sequence into a log2-domain logit, or -inf when masked.
@@ -141,6 +156,7 @@ __host__ __device__ __forceinline__ float philox_uniform(uint64_t seed, uint64_t
 struct ScoreMods {
   float scale_log2;      // softmax_scale * log2(e)
   float cap_log2;        // softcap * log2(e); 0 disables
+  float inv_cap_log2;    // 1 / cap_log2 (0 when disabled)
   float alibi_slope_log2;// slope * log2(e); 0 disables
   const void* bias;      // already offset to this (batch, head); nullptr disables
   int bias_dtype;
@@ -167,7 +183,7 @@ struct ScoreMods {
     float s = raw * scale_log2;
     float t = 0.f;
     if (cap_log2 > 0.f) {
-      t = tanhf(s / cap_log2);
+      t = fast_tanh(s * inv_cap_log2);
       s = cap_log2 * t;
     }
     if (bias != nullptr) {
@@ -187,9 +203,70 @@ struct ScoreMods {
   __device__ __forceinline__ bool dropout_keep(int i, int j) const {
     const uint64_t offs = (dropout_base + static_cast<uint64_t>(i)) * static_cast<uint64_t>(seqlen_k) +
                           static_cast<uint64_t>(j);
-    return philox_uniform(dropout_seed, offs) > dropout_p;
+    return philox_uniform_call(dropout_seed, offs) > dropout_p;
   }
 };
+
+// ---- chunk forms of the modifiers, for kernels that hold 32 consecutive scores of one accumulator row in registers.
+// Element e is (query i0, key j0 + e) when kAlongKeys, (query i0 + e, key j0) otherwise. Every modifier is one compact
+// unrolled block behind one warp-uniform branch, so a launch that uses none of them jumps over four small blocks
+// instead of 32 interleaved ones (the per-element form made the instruction stream so sparse that fetch misses
+// dominated the kernels).
+template <bool kAlongKeys, typename B>
+__device__ __forceinline__ void mods_add_bias32(const ScoreMods& m, float (&x)[32], int i0, int j0) {
+  const B* base = reinterpret_cast<const B*>(m.bias) + static_cast<int64_t>(i0) * m.bias_stride_m +
+                  static_cast<int64_t>(j0) * m.bias_stride_n;
+  const int64_t step = kAlongKeys ? m.bias_stride_n : m.bias_stride_m;
+  // rows/columns outside the sequence read nothing (the caller masks them afterwards)
+  const int room = kAlongKeys ? (i0 < m.seqlen_q ? m.seqlen_k - j0 : 0) : (j0 < m.seqlen_k ? m.seqlen_q - i0 : 0);
+#pragma unroll
+  for (int e = 0; e < 32; ++e)
+    if (e < room) x[e] += DType<B>::to_float(base[e * step]) * kLog2e;
+}
+
+// Raw scores -> unmasked logits in the log2 domain, in place. When chain != nullptr, (*chain)[e] is multiplied by the
+// soft-cap chain factor 1 - tanh^2 (left alone when soft-capping is off).
+template <bool kAlongKeys>
+__device__ __forceinline__ void mods_logits32(const ScoreMods& m, float (&x)[32], int i0, int j0, float (*chain)[32]) {
+  if (m.cap_log2 > 0.f) {
+    const float cap = m.cap_log2, pre = m.scale_log2 * m.inv_cap_log2;
+#pragma unroll
+    for (int e = 0; e < 32; ++e) {
+      const float t = fast_tanh(x[e] * pre);
+      x[e] = cap * t;
+      if (chain) (*chain)[e] *= fmaf(-t, t, 1.f);
+    }
+  } else {
+    const float sc = m.scale_log2;
+#pragma unroll
+    for (int e = 0; e < 32; ++e) x[e] *= sc;
+  }
+  if (m.bias != nullptr) {
+    if (m.bias_dtype == FA_F16) mods_add_bias32<kAlongKeys, __half>(m, x, i0, j0);
+    else if (m.bias_dtype == FA_BF16) mods_add_bias32<kAlongKeys, __nv_bfloat16>(m, x, i0, j0);
+    else mods_add_bias32<kAlongKeys, float>(m, x, i0, j0);
+  }
+  if (m.alibi_slope_log2 != 0.f) {
+    const float slope = m.alibi_slope_log2;
+    const int d0 = j0 - i0 - (m.seqlen_k - m.seqlen_q);
+#pragma unroll
+    for (int e = 0; e < 32; ++e) {
+      const int d = kAlongKeys ? d0 + e : d0 - e;
+      x[e] = fmaf(-slope, static_cast<float>(d < 0 ? -d : d), x[e]);
+    }
+  }
+}
+
+// Bit e set = element e survives dropout (all ones when dropout is off).
+template <bool kAlongKeys>
+__device__ __forceinline__ uint32_t mods_dropout_bits32(const ScoreMods& m, int i0, int j0) {
+  if (!(m.dropout_p > 0.f)) return 0xffffffffu;
+  uint32_t bits = 0u;
+#pragma unroll 1
+  for (int e = 0; e < 32; ++e)
+    bits |= static_cast<uint32_t>(m.dropout_keep(kAlongKeys ? i0 : i0 + e, kAlongKeys ? j0 + e : j0)) << e;
+  return bits;
+}
 
 // First and one-past-last key index any row of query rows [r0, r1] (inclusive, r1 < seqlen_q) may attend.
 __device__ __forceinline__ void key_range_for_rows(const ScoreMods& m, int r0, int r1, int* lo, int* hi) {

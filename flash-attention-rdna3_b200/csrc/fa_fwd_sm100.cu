@@ -102,6 +102,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
   ScoreMods mods;
   mods.scale_log2 = a.softmax_scale * kLog2e;
   mods.cap_log2 = a.softcap > 0.f ? a.softcap * kLog2e : 0.f;
+  mods.inv_cap_log2 = a.softcap > 0.f ? 1.f / mods.cap_log2 : 0.f;
   mods.alibi_slope_log2 = a.alibi ? a.alibi[h] * kLog2e : 0.f;
   mods.bias = nullptr;
   mods.bias_dtype = a.bias_dtype;
@@ -342,20 +343,26 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         }
 
         if (kMods) {
-          // General path: the whole row is transformed in registers (softcap, bias, ALiBi, dropout).
-          uint32_t r[128];
-#pragma unroll
-          for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
-          tc_wait_ld();
-          PROF_MARK(1);
+          // General path (softcap, bias, ALiBi, dropout): 32 columns at a time in rolled loops, so the code stays
+          // small; the transformed logits go back to TMEM in place between the maximum and the exponentials.
           float m_tile = kNegInf;
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            uint32_t r[32];
+            tmem_ld32(tS + c * 32, r);
+            tc_wait_ld_regs(r);
+            float(&x)[32] = *reinterpret_cast<float(*)[32]>(&r[0]);
+            mods_logits32<true>(mods, x, row, k0 + c * 32, nullptr);
+            if (tile_masked) {
 #pragma unroll
-          for (int c = 0; c < 128; ++c) {
-            float x = mods.logit(__uint_as_float(r[c]), row, k0 + c, nullptr);
-            if (tile_masked && (c < c_lo || c > c_hi)) x = kNegInf;
-            r[c] = __float_as_uint(x);
-            m_tile = fmaxf(m_tile, x);
+              for (int e = 0; e < 32; ++e)
+                if (c * 32 + e < c_lo || c * 32 + e > c_hi) x[e] = kNegInf;
+            }
+#pragma unroll
+            for (int e = 0; e < 32; e += 2) m_tile = fmax3(m_tile, x[e], x[e + 1]);
+            tmem_st32(tS + c * 32, r);
           }
+          tc_wait_st();
           PROF_MARK(2);
           const float m_new = fmaxf(m_used, m_tile);
           const bool grow = m_new > m_used + kRescaleThreshold;
@@ -368,22 +375,27 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
           const float m_eff = (m_used == kNegInf) ? 0.f : m_used;
           PROF_MARK(3);
           float sum = 0.f;
+          const float inv_keep = mods.inv_keep;
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            uint32_t r[32], pk[16];
+            tmem_ld32(tS + c * 32, r);
+            const uint32_t kept = mods_dropout_bits32<true>(mods, row, k0 + c * 32);
+            tc_wait_ld_regs(r);
+            float(&x)[32] = *reinterpret_cast<float(*)[32]>(&r[0]);
 #pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            uint32_t pk[32];
-#pragma unroll
-            for (int c = 0; c < 32; ++c) {
-              const int e0 = half * 64 + 2 * c;
-              float p0 = fast_exp2(__uint_as_float(r[e0]) - m_eff);
-              float p1 = fast_exp2(__uint_as_float(r[e0 + 1]) - m_eff);
-              sum += p0 + p1;
-              if (mods.dropout_p > 0.f) {
-                p0 = mods.dropout_keep(row, k0 + e0) ? p0 * mods.inv_keep : 0.f;
-                p1 = mods.dropout_keep(row, k0 + e0 + 1) ? p1 * mods.inv_keep : 0.f;
-              }
-              pk[c] = DType<T>::pack2(p0, p1);
+            for (int e = 0; e < 32; ++e) {
+              x[e] = fast_exp2(x[e] - m_eff);
+              sum += x[e];
             }
-            tmem_st32(tS + half * 32, pk);
+            if (mods.dropout_p > 0.f) {  // the row sum above is of the undropped probabilities
+#pragma unroll
+              for (int e = 0; e < 32; ++e) x[e] = ((kept >> e) & 1u) ? x[e] * inv_keep : 0.f;
+            }
+#pragma unroll
+            for (int e = 0; e < 16; ++e) pk[e] = DType<T>::pack2(x[2 * e], x[2 * e + 1]);
+            // the 16-bit chunk lands on columns [16c, 16c+16): all of them already read
+            tmem_st16(tS + c * 16, pk);
           }
           l += sum;
         } else {

@@ -56,6 +56,7 @@ __device__ __forceinline__ ScoreMods make_mods(const fa_attn_params& P, const Se
   ScoreMods m;
   m.scale_log2 = P.softmax_scale * kLog2e;
   m.cap_log2 = P.softcap > 0.f ? P.softcap * kLog2e : 0.f;
+  m.inv_cap_log2 = P.softcap > 0.f ? 1.f / m.cap_log2 : 0.f;
   m.alibi_slope_log2 = P.alibi_slopes ? P.alibi_slopes[s.h] * kLog2e : 0.f;
   m.bias = nullptr;
   m.bias_dtype = P.bias_dtype;
