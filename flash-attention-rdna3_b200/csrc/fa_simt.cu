@@ -365,6 +365,389 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) simt_bwd_dkdv_kernel(cons
   }
 }
 
+// =============================================================================================
+// Tiled forms of the three kernels above, used once the problem is larger than a tile. A CTA of 256 threads (16 x 16)
+// owns 16*kRows rows (queries; keys in dK/dV) and walks the other sequence 64 rows at a time. Two primitives on
+// shared-memory tiles do all the arithmetic in fp32 FMAs:
+//   tile_abt: scores[16*kRows][64] = A[rows][D] . B[64 rows][D]^T, the head dimension staged 32 columns at a time;
+//             thread (ty, tx) holds rows ty + 16a and columns tx + 16b in registers
+//   tile_pb : acc[rows][D] += P[rows][64] . B[64 rows][D], P in shared memory, B staged 64 columns at a time;
+//             thread (ty, tx) holds rows ty + 16a and columns 64c + 4tx + e
+// Every operand is read once per tile pair instead of once per row pair, which is what separates these kernels from
+// the one-warp-per-row forms (50-80x at 2048 tokens). Loads honour arbitrary strides and any of the three dtypes.
+// =============================================================================================
+constexpr int kTileThreads = 256;
+
+struct __align__(16) TileSmem {
+  float P[64][68];
+  union {
+    struct { float A[64][36]; float B[64][36]; } ab;
+    float V[64][64];
+  } u;
+};
+
+template <typename T>
+__device__ __forceinline__ float ld_elem(const void* base, int64_t idx) {
+  return DType<T>::to_float(reinterpret_cast<const T*>(base)[idx]);
+}
+
+template <typename T, int kRows>
+__device__ __forceinline__ void tile_abt(const void* A, int64_t a_off, int64_t a_rs, int64_t a_ds, int a_valid,
+                                         const void* B, int64_t b_off, int64_t b_rs, int64_t b_ds, int b_valid, int D,
+                                         TileSmem& sm, float (&acc)[kRows][4]) {
+  constexpr int BM = 16 * kRows;
+  const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
+#pragma unroll
+  for (int a = 0; a < kRows; ++a)
+#pragma unroll
+    for (int b = 0; b < 4; ++b) acc[a][b] = 0.f;
+  for (int d0 = 0; d0 < D; d0 += 32) {
+    __syncthreads();  // whoever read the staging buffers (or P's neighbours in the union) before is done
+    for (int idx = tid; idx < BM * 32; idx += kTileThreads) {
+      const int r = idx >> 5, d = idx & 31;
+      float v = 0.f;
+      if (r < a_valid && d0 + d < D) v = ld_elem<T>(A, a_off + (int64_t)r * a_rs + (int64_t)(d0 + d) * a_ds);
+      sm.u.ab.A[r][d] = v;
+    }
+    for (int idx = tid; idx < 64 * 32; idx += kTileThreads) {
+      const int r = idx >> 5, d = idx & 31;
+      float v = 0.f;
+      if (r < b_valid && d0 + d < D) v = ld_elem<T>(B, b_off + (int64_t)r * b_rs + (int64_t)(d0 + d) * b_ds);
+      sm.u.ab.B[r][d] = v;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int d = 0; d < 32; d += 4) {
+      float4 av[kRows], bv[4];
+#pragma unroll
+      for (int a = 0; a < kRows; ++a) av[a] = *reinterpret_cast<const float4*>(&sm.u.ab.A[ty + 16 * a][d]);
+#pragma unroll
+      for (int b = 0; b < 4; ++b) bv[b] = *reinterpret_cast<const float4*>(&sm.u.ab.B[tx + 16 * b][d]);
+#pragma unroll
+      for (int a = 0; a < kRows; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b)
+          acc[a][b] += av[a].x * bv[b].x + av[a].y * bv[b].y + av[a].z * bv[b].z + av[a].w * bv[b].w;
+    }
+  }
+}
+
+template <typename T, int kRows, int kDC>
+__device__ __forceinline__ void tile_pb(const void* B, int64_t b_off, int64_t b_rs, int64_t b_ds, int b_valid, int D,
+                                        TileSmem& sm, float (&acc)[kDC][kRows][4]) {
+  const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
+#pragma unroll
+  for (int c = 0; c < kDC; ++c) {
+    if (c * 64 < D) {
+      __syncthreads();  // P is written, the previous chunk is consumed
+      for (int idx = tid; idx < 64 * 64; idx += kTileThreads) {
+        const int k = idx >> 6, col = idx & 63;
+        float v = 0.f;
+        if (k < b_valid && c * 64 + col < D) v = ld_elem<T>(B, b_off + (int64_t)k * b_rs + (int64_t)(c * 64 + col) * b_ds);
+        sm.u.V[k][col] = v;
+      }
+      __syncthreads();
+#pragma unroll 4
+      for (int k = 0; k < 64; k += 4) {
+        float4 pv[kRows], bv[4];
+#pragma unroll
+        for (int a = 0; a < kRows; ++a) pv[a] = *reinterpret_cast<const float4*>(&sm.P[ty + 16 * a][k]);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) bv[kk] = *reinterpret_cast<const float4*>(&sm.u.V[k + kk][tx * 4]);
+#pragma unroll
+        for (int a = 0; a < kRows; ++a) {
+          acc[c][a][0] += pv[a].x * bv[0].x + pv[a].y * bv[1].x + pv[a].z * bv[2].x + pv[a].w * bv[3].x;
+          acc[c][a][1] += pv[a].x * bv[0].y + pv[a].y * bv[1].y + pv[a].z * bv[2].y + pv[a].w * bv[3].y;
+          acc[c][a][2] += pv[a].x * bv[0].z + pv[a].y * bv[1].z + pv[a].z * bv[2].z + pv[a].w * bv[3].z;
+          acc[c][a][3] += pv[a].x * bv[0].w + pv[a].y * bv[1].w + pv[a].z * bv[2].w + pv[a].w * bv[3].w;
+        }
+      }
+    }
+  }
+}
+
+// max / sum over the 16 threads (same ty) that share a row: lanes 16*(ty&1) + tx of one warp
+__device__ __forceinline__ float row16_max(float x) {
+  for (int o = 8; o > 0; o >>= 1) x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, o));
+  return x;
+}
+__device__ __forceinline__ float row16_sum(float x) {
+  for (int o = 8; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+  return x;
+}
+
+template <typename T, int kRows, int kDC>
+__global__ void __launch_bounds__(kTileThreads) tiled_fwd_kernel(const fa_attn_params P) {
+  __shared__ TileSmem sm;
+  constexpr int BM = 16 * kRows;
+  const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
+  const int i0 = blockIdx.x * BM;
+  const int b = blockIdx.y / P.heads_q, h = blockIdx.y % P.heads_q;
+  const int D = P.head_dim;
+  SeqView s;
+  make_view(P, b, h, &s);
+  if (i0 >= s.seqlen_q) return;
+  const ScoreMods mods = make_mods(P, s);
+  int lo, hi;
+  key_range_for_rows(mods, i0, min(i0 + BM, s.seqlen_q) - 1, &lo, &hi);
+
+  float m[kRows], l[kRows], acc[kDC][kRows][4];
+#pragma unroll
+  for (int a = 0; a < kRows; ++a) {
+    m[a] = kNegInf;
+    l[a] = 0.f;
+#pragma unroll
+    for (int c = 0; c < kDC; ++c)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[c][a][e] = 0.f;
+  }
+
+  for (int j0 = lo; j0 < hi; j0 += 64) {
+    float sc[kRows][4];
+    tile_abt<T, kRows>(P.q, s.q_off + (int64_t)i0 * P.q_strides[2], P.q_strides[2], P.q_strides[3], s.seqlen_q - i0,
+                       P.k, s.k_off + (int64_t)j0 * P.k_strides[2], P.k_strides[2], P.k_strides[3], s.seqlen_k - j0, D,
+                       sm, sc);
+#pragma unroll
+    for (int a = 0; a < kRows; ++a) {
+      const int i = i0 + ty + 16 * a;
+      float mx = kNegInf;
+#pragma unroll
+      for (int bb = 0; bb < 4; ++bb) {
+        const int j = j0 + tx + 16 * bb;
+        float x = kNegInf;
+        if (i < s.seqlen_q && mods.keep(i, j)) x = mods.logit(sc[a][bb], i, j, nullptr);
+        sc[a][bb] = x;
+        mx = fmaxf(mx, x);
+      }
+      const float m_new = fmaxf(m[a], row16_max(mx));
+      const float m_safe = (m_new == kNegInf) ? 0.f : m_new;
+      const float alpha = exp2f(m[a] - m_safe);
+      float sum = 0.f;
+#pragma unroll
+      for (int bb = 0; bb < 4; ++bb) {
+        float p = exp2f(sc[a][bb] - m_safe);
+        sum += p;
+        if (mods.dropout_p > 0.f && p != 0.f) p = mods.dropout_keep(i, j0 + tx + 16 * bb) ? p * mods.inv_keep : 0.f;
+        sm.P[ty + 16 * a][tx + 16 * bb] = p;  // the previous readers of P passed a barrier inside tile_abt
+      }
+      l[a] = l[a] * alpha + row16_sum(sum);
+#pragma unroll
+      for (int c = 0; c < kDC; ++c)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[c][a][e] *= alpha;
+      if (m_new != kNegInf) m[a] = m_new;
+    }
+    tile_pb<T, kRows, kDC>(P.v, s.v_off + (int64_t)j0 * P.v_strides[2], P.v_strides[2], P.v_strides[3],
+                           s.seqlen_k - j0, D, sm, acc);
+  }
+
+#pragma unroll
+  for (int a = 0; a < kRows; ++a) {
+    const int i = i0 + ty + 16 * a;
+    if (i >= s.seqlen_q) continue;
+    const float l_safe = (l[a] == 0.f) ? 1.f : l[a];
+    const float inv = 1.f / l_safe;
+#pragma unroll
+    for (int c = 0; c < kDC; ++c)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int d = c * 64 + tx * 4 + e;
+        if (d < D)
+          store_from_float(P.out, s.o_off + (int64_t)i * P.o_strides[2] + (int64_t)d * P.o_strides[3], P.dtype,
+                           acc[c][a][e] * inv);
+      }
+    if (tx == 0) P.lse[s.lse_off + (int64_t)i * s.lse_row_stride] = m[a] * kLn2 + logf(l_safe);
+  }
+}
+
+template <typename T, int kRows, int kDC>
+__global__ void __launch_bounds__(kTileThreads) tiled_bwd_dq_kernel(const fa_attn_params P) {
+  __shared__ TileSmem sm;
+  constexpr int BM = 16 * kRows;
+  const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
+  const int i0 = blockIdx.x * BM;
+  const int b = blockIdx.y / P.heads_q, h = blockIdx.y % P.heads_q;
+  const int D = P.head_dim;
+  SeqView s;
+  make_view(P, b, h, &s);
+  if (i0 >= s.seqlen_q) return;
+  const ScoreMods mods = make_mods(P, s);
+  int lo, hi;
+  key_range_for_rows(mods, i0, min(i0 + BM, s.seqlen_q) - 1, &lo, &hi);
+
+  float lse[kRows], delta[kRows], acc[kDC][kRows][4];
+#pragma unroll
+  for (int a = 0; a < kRows; ++a) {
+    const int i = i0 + ty + 16 * a;
+    lse[a] = i < s.seqlen_q ? P.lse[s.lse_off + (int64_t)i * s.lse_row_stride] : kNegInf;
+    delta[a] = i < s.seqlen_q ? P.delta[s.delta_off + (int64_t)i * s.delta_row_stride] : 0.f;
+#pragma unroll
+    for (int c = 0; c < kDC; ++c)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[c][a][e] = 0.f;
+  }
+
+  for (int j0 = lo; j0 < hi; j0 += 64) {
+    float sc[kRows][4], dp[kRows][4];
+    tile_abt<T, kRows>(P.q, s.q_off + (int64_t)i0 * P.q_strides[2], P.q_strides[2], P.q_strides[3], s.seqlen_q - i0,
+                       P.k, s.k_off + (int64_t)j0 * P.k_strides[2], P.k_strides[2], P.k_strides[3], s.seqlen_k - j0, D,
+                       sm, sc);
+    tile_abt<T, kRows>(P.dout, s.do_off + (int64_t)i0 * P.do_strides[2], P.do_strides[2], P.do_strides[3],
+                       s.seqlen_q - i0, P.v, s.v_off + (int64_t)j0 * P.v_strides[2], P.v_strides[2], P.v_strides[3],
+                       s.seqlen_k - j0, D, sm, dp);
+#pragma unroll
+    for (int a = 0; a < kRows; ++a) {
+      const int i = i0 + ty + 16 * a;
+#pragma unroll
+      for (int bb = 0; bb < 4; ++bb) {
+        const int j = j0 + tx + 16 * bb;
+        float ds = 0.f;
+        if (i < s.seqlen_q) ds = pair_grad(mods, sc[a][bb], dp[a][bb], lse[a], delta[a], i, j).ds;
+        sm.P[ty + 16 * a][tx + 16 * bb] = ds;
+      }
+    }
+    tile_pb<T, kRows, kDC>(P.k, s.k_off + (int64_t)j0 * P.k_strides[2], P.k_strides[2], P.k_strides[3],
+                           s.seqlen_k - j0, D, sm, acc);
+  }
+
+#pragma unroll
+  for (int a = 0; a < kRows; ++a) {
+    const int i = i0 + ty + 16 * a;
+    if (i >= s.seqlen_q) continue;
+#pragma unroll
+    for (int c = 0; c < kDC; ++c)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int d = c * 64 + tx * 4 + e;
+        if (d < D)
+          store_from_float(P.dq, s.dq_off + (int64_t)i * P.dq_strides[2] + (int64_t)d * P.dq_strides[3], P.dtype,
+                           acc[c][a][e] * P.softmax_scale);
+      }
+  }
+}
+
+// Rows of the tile are keys, columns are queries; the query heads of the group are summed in registers.
+template <typename T, int kRows, int kDC>
+__global__ void __launch_bounds__(kTileThreads) tiled_bwd_dkdv_kernel(const fa_attn_params P) {
+  __shared__ TileSmem sm;
+  constexpr int BM = 16 * kRows;
+  const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
+  const int j0 = blockIdx.x * BM;
+  const int b = blockIdx.y / P.heads_kv, hk = blockIdx.y % P.heads_kv;
+  const int D = P.head_dim;
+  const int group = P.heads_q / P.heads_kv;
+  SeqView s;
+  make_view(P, b, hk * group, &s);
+  if (j0 >= s.seqlen_k) return;
+
+  float dk[kDC][kRows][4], dv[kDC][kRows][4];
+#pragma unroll
+  for (int c = 0; c < kDC; ++c)
+#pragma unroll
+    for (int a = 0; a < kRows; ++a)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) dk[c][a][e] = dv[c][a][e] = 0.f;
+
+  for (int g = 0; g < group; ++g) {
+    make_view(P, b, hk * group + g, &s);
+    const ScoreMods mods = make_mods(P, s);
+    int lo, hi;
+    query_range_for_keys(mods, j0, min(j0 + BM, s.seqlen_k) - 1, &lo, &hi);
+    for (int i0 = lo; i0 < hi; i0 += 64) {
+      float sc[kRows][4], dp[kRows][4];
+      tile_abt<T, kRows>(P.k, s.k_off + (int64_t)j0 * P.k_strides[2], P.k_strides[2], P.k_strides[3], s.seqlen_k - j0,
+                         P.q, s.q_off + (int64_t)i0 * P.q_strides[2], P.q_strides[2], P.q_strides[3], s.seqlen_q - i0,
+                         D, sm, sc);
+      tile_abt<T, kRows>(P.v, s.v_off + (int64_t)j0 * P.v_strides[2], P.v_strides[2], P.v_strides[3], s.seqlen_k - j0,
+                         P.dout, s.do_off + (int64_t)i0 * P.do_strides[2], P.do_strides[2], P.do_strides[3],
+                         s.seqlen_q - i0, D, sm, dp);
+      float lse_i[4], delta_i[4];
+#pragma unroll
+      for (int bb = 0; bb < 4; ++bb) {
+        const int i = i0 + tx + 16 * bb;
+        lse_i[bb] = i < s.seqlen_q ? P.lse[s.lse_off + (int64_t)i * s.lse_row_stride] : kNegInf;
+        delta_i[bb] = i < s.seqlen_q ? P.delta[s.delta_off + (int64_t)i * s.delta_row_stride] : 0.f;
+      }
+#pragma unroll
+      for (int a = 0; a < kRows; ++a) {
+        const int j = j0 + ty + 16 * a;
+#pragma unroll
+        for (int bb = 0; bb < 4; ++bb) {
+          const int i = i0 + tx + 16 * bb;
+          PairGrad pg{0.f, 0.f};
+          if (i < s.seqlen_q && j < s.seqlen_k) pg = pair_grad(mods, sc[a][bb], dp[a][bb], lse_i[bb], delta_i[bb], i, j);
+          sm.P[ty + 16 * a][tx + 16 * bb] = pg.p_drop;
+          sc[a][bb] = pg.ds;
+        }
+      }
+      tile_pb<T, kRows, kDC>(P.dout, s.do_off + (int64_t)i0 * P.do_strides[2], P.do_strides[2], P.do_strides[3],
+                             s.seqlen_q - i0, D, sm, dv);
+      __syncthreads();  // every thread is done with the probabilities before the score gradients replace them
+#pragma unroll
+      for (int a = 0; a < kRows; ++a)
+#pragma unroll
+        for (int bb = 0; bb < 4; ++bb) sm.P[ty + 16 * a][tx + 16 * bb] = sc[a][bb];
+      tile_pb<T, kRows, kDC>(P.q, s.q_off + (int64_t)i0 * P.q_strides[2], P.q_strides[2], P.q_strides[3],
+                             s.seqlen_q - i0, D, sm, dk);
+    }
+  }
+
+#pragma unroll
+  for (int a = 0; a < kRows; ++a) {
+    const int j = j0 + ty + 16 * a;
+    if (j >= s.seqlen_k) continue;
+#pragma unroll
+    for (int c = 0; c < kDC; ++c)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int d = c * 64 + tx * 4 + e;
+        if (d < D) {
+          store_from_float(P.dk, s.dk_off + (int64_t)j * P.dk_strides[2] + (int64_t)d * P.dk_strides[3], P.dtype,
+                           dk[c][a][e] * P.softmax_scale);
+          store_from_float(P.dv, s.dv_off + (int64_t)j * P.dv_strides[2] + (int64_t)d * P.dv_strides[3], P.dtype,
+                           dv[c][a][e]);
+        }
+      }
+  }
+}
+
+// The tiled kernels pay off once both sequences span at least a tile; below that the one-warp-per-row kernels have
+// more parallelism.
+bool tiled_worthwhile(const fa_attn_params& p) { return p.seqlen_q >= 32 && p.seqlen_k >= 64; }
+
+enum TiledKind { kTiledFwd, kTiledDq, kTiledDkdv };
+
+template <typename T, int kRows, int kDC>
+void launch_tiled_one(TiledKind kind, const fa_attn_params& p, cudaStream_t stream) {
+  constexpr int BM = 16 * kRows;
+  if (kind == kTiledDkdv) {
+    dim3 grid((p.seqlen_k + BM - 1) / BM, p.batch * p.heads_kv);
+    tiled_bwd_dkdv_kernel<T, kRows, kDC><<<grid, kTileThreads, 0, stream>>>(p);
+  } else {
+    dim3 grid((p.seqlen_q + BM - 1) / BM, p.batch * p.heads_q);
+    if (kind == kTiledFwd) tiled_fwd_kernel<T, kRows, kDC><<<grid, kTileThreads, 0, stream>>>(p);
+    else tiled_bwd_dq_kernel<T, kRows, kDC><<<grid, kTileThreads, 0, stream>>>(p);
+  }
+}
+
+// Rows per thread and 64-column chunks by head dimension; dK/dV carries two accumulators, so it narrows sooner.
+template <typename T>
+void launch_tiled_typed(TiledKind kind, const fa_attn_params& p, cudaStream_t stream) {
+  const int D = p.head_dim;
+  if (D <= 64) launch_tiled_one<T, 4, 1>(kind, p, stream);
+  else if (D <= 128) launch_tiled_one<T, 4, 2>(kind, p, stream);
+  else if (D <= 256) {
+    if (kind == kTiledDkdv) launch_tiled_one<T, 2, 4>(kind, p, stream);
+    else launch_tiled_one<T, 4, 4>(kind, p, stream);
+  } else launch_tiled_one<T, 2, 8>(kind, p, stream);
+}
+
+void launch_tiled(TiledKind kind, const fa_attn_params& p, cudaStream_t stream) {
+  if (p.dtype == FA_F16) launch_tiled_typed<__half>(kind, p, stream);
+  else if (p.dtype == FA_BF16) launch_tiled_typed<__nv_bfloat16>(kind, p, stream);
+  else launch_tiled_typed<float>(kind, p, stream);
+}
+
 int check_launch(const char* what) {
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "%s launch failed: %s", what, cudaGetErrorString(e));
@@ -400,6 +783,10 @@ int launch_bwd_delta(const fa_attn_params& p, cudaStream_t stream) {
 
 int launch_fwd_simt(const fa_attn_params& p, cudaStream_t stream) {
   if (p.head_dim > kMaxD) return set_error(FA_ERR_UNSUPPORTED, "head_dim %d exceeds %d", p.head_dim, kMaxD);
+  if (tiled_worthwhile(p)) {
+    launch_tiled(kTiledFwd, p, stream);
+    return check_launch("tiled forward");
+  }
   dim3 grid((p.seqlen_q + kWarpsPerBlock - 1) / kWarpsPerBlock, p.batch * p.heads_q);
   simt_fwd_kernel<<<grid, kWarpsPerBlock * 32, 0, stream>>>(p);
   return check_launch("simt forward");
@@ -407,6 +794,18 @@ int launch_fwd_simt(const fa_attn_params& p, cudaStream_t stream) {
 
 int launch_bwd_simt(const fa_attn_params& p, int parts, cudaStream_t stream) {
   if (p.head_dim > kMaxD) return set_error(FA_ERR_UNSUPPORTED, "head_dim %d exceeds %d", p.head_dim, kMaxD);
+  if (tiled_worthwhile(p)) {
+    if (parts & FA_BWD_DKDV) {
+      launch_tiled(kTiledDkdv, p, stream);
+      int rc = check_launch("tiled dkdv");
+      if (rc) return rc;
+    }
+    if (parts & FA_BWD_DQ) {
+      launch_tiled(kTiledDq, p, stream);
+      return check_launch("tiled dq");
+    }
+    return 0;
+  }
   if (parts & FA_BWD_DKDV) {
     dim3 gk((p.seqlen_k + kWarpsPerBlock - 1) / kWarpsPerBlock, p.batch * p.heads_kv);
     simt_bwd_dkdv_kernel<<<gk, kWarpsPerBlock * 32, 0, stream>>>(p);
