@@ -1,0 +1,194 @@
+"""Parity of the tiled CUDA-core kernels (fp32 inputs, head dims outside 64/128) against the fp32 oracle.
+
+These kernels compute in fp32 throughout, so fp32 inputs are held to 2e-5 max-abs on O / LSE and 1e-4 relative L2 on
+the gradients, far inside the 2e-3 / 3e-3 the reference's tests/test_fp32_headdim.py allows. The shapes follow that
+file (fp32 512 x 64, head dims 256 and 512, non-power-of-two 48 / 80 / 96 / 192) and add grouped heads, unequal
+lengths, every score modifier, packed sequences (16-bit, head dim 256) and a strided view.
+"""
+import math
+
+import pytest
+import torch
+
+from helpers import assert_close_grad, assert_close_o, max_abs, rel_l2, seeded
+from oracle.attention_oracle import alibi_slopes_ref, attention_grads_ref
+
+pytestmark = pytest.mark.gpu
+
+FP32_O_TOL = 2e-5
+FP32_GRAD_REL_L2 = 1e-4
+
+
+def run_fp32(B, H, Hk, Sq, Sk, D, seed=0, **opts):
+    from fa_b200 import interface
+
+    dtype = torch.float32
+    q = seeded(seed + 1, B, H, Sq, D, dtype=dtype)
+    k = seeded(seed + 2, B, Hk, Sk, D, dtype=dtype)
+    v = seeded(seed + 3, B, Hk, Sk, D, dtype=dtype)
+    dout = seeded(seed + 4, B, H, Sq, D, dtype=dtype)
+    scale = 1.0 / math.sqrt(D)
+    causal = opts.get("causal", False)
+    window = opts.get("window", (-1, -1))
+    softcap = opts.get("softcap", 0.0)
+    bias = opts.get("bias")
+    p, dseed = opts.get("dropout_p", 0.0), opts.get("dropout_seed", 0)
+    slopes = alibi_slopes_ref(H).cuda() if opts.get("alibi") else None
+    out, lse = interface._forward(q, k, v, causal, scale, window, softcap, bias, slopes, p, dseed)
+    dq, dk, dv = interface._backward(dout, q, k, v, out, lse, causal, scale, window, softcap, bias, slopes, p, dseed)
+    assert interface.last_kernel_path() == "simt"
+    torch.cuda.synchronize()
+    ro, rl, rdq, rdk, rdv = attention_grads_ref(
+        q.cpu(), k.cpu(), v.cpu(), dout.cpu(), causal=causal, softmax_scale=scale, window=window, softcap=softcap,
+        bias=None if bias is None else bias.cpu(), alibi_slopes=None if slopes is None else slopes.cpu(),
+        dropout_p=p, dropout_seed=dseed)
+    assert max_abs(out, ro) <= FP32_O_TOL, f"out max-abs {max_abs(out, ro):.3e}"
+    finite = torch.isfinite(rl)
+    assert torch.equal(torch.isfinite(lse.cpu()), finite)
+    assert max_abs(lse.cpu()[finite], rl[finite]) <= FP32_O_TOL * 4, "lse"
+    for name, got, want in (("dq", dq, rdq), ("dk", dk, rdk), ("dv", dv, rdv)):
+        err = rel_l2(got, want)
+        assert err <= FP32_GRAD_REL_L2, f"{name}: rel-L2 {err:.3e}"
+        assert not torch.isnan(got).any()
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("head_dim", [32, 64, 128, 256, 512])
+def test_fp32_head_dims(causal, head_dim):
+    # 150 x 333: neither length is a multiple of the 64-row tiles, causal is bottom-right aligned
+    run_fp32(1, 4, 2, 150, 333, head_dim, seed=head_dim, causal=causal)
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_fp32_reference_shape(causal):
+    run_fp32(2, 4, 4, 512, 512, 64, seed=int(causal), causal=causal)
+
+
+@pytest.mark.parametrize("opts", [
+    dict(causal=True, window=(63, 0)),
+    dict(window=(40, 25)),
+    dict(softcap=15.0),
+    dict(causal=True, alibi=True),
+    dict(causal=True, softcap=30.0, alibi=True, window=(100, 0)),
+    dict(dropout_p=0.2, dropout_seed=1234),
+    dict(causal=True, dropout_p=0.1, dropout_seed=7, softcap=20.0),
+], ids=lambda o: "+".join(sorted(o)))
+@pytest.mark.parametrize("head_dim", [64, 256])
+def test_fp32_modifiers(opts, head_dim):
+    run_fp32(1, 4, 2, 200, 300, head_dim, seed=11, **opts)
+
+
+@pytest.mark.parametrize("bias_dtype", [torch.float32])
+@pytest.mark.parametrize("bias_shape", [(1, 1), (2, 4)])
+def test_fp32_bias(bias_shape, bias_dtype):
+    bias = seeded(9, bias_shape[0], bias_shape[1], 130, 260, dtype=bias_dtype) * 0.5
+    run_fp32(2, 4, 4, 130, 260, 128, seed=5, bias=bias.expand(2, 4, 130, 260).contiguous())
+
+
+def test_fp32_rows_without_keys():
+    # more queries than keys under a causal mask: the first Sq - Sk rows see nothing (O = 0, LSE = -inf, zero grads)
+    run_fp32(1, 2, 2, 300, 100, 64, seed=3, causal=True)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("head_dim", [256, 512])
+@pytest.mark.parametrize("causal", [False, True])
+def test_large_head_dim_16bit(dtype, head_dim, causal):
+    from fa_b200 import interface
+
+    B, H, Hk, S = 1, 4, 2, 320
+    q = seeded(1, B, H, S, head_dim, dtype=dtype)
+    k = seeded(2, B, Hk, S, head_dim, dtype=dtype)
+    v = seeded(3, B, Hk, S, head_dim, dtype=dtype)
+    dout = seeded(4, B, H, S, head_dim, dtype=dtype)
+    scale = 1.0 / math.sqrt(head_dim)
+    out, lse = interface._forward(q, k, v, causal, scale, (-1, -1), 0.0, None, None, 0.0, 0)
+    dq, dk, dv = interface._backward(dout, q, k, v, out, lse, causal, scale, (-1, -1), 0.0, None, None, 0.0, 0)
+    ro, rl, rdq, rdk, rdv = attention_grads_ref(q.cpu(), k.cpu(), v.cpu(), dout.cpu(), causal=causal,
+                                                softmax_scale=scale)
+    assert_close_o(out, ro, dtype)
+    assert_close_grad(dq, rdq, "dq")
+    assert_close_grad(dk, rdk, "dk")
+    assert_close_grad(dv, rdv, "dv")
+
+
+@pytest.mark.parametrize("head_dim", [48, 80, 96, 192])
+def test_non_power_of_two_head_dims(head_dim):
+    """Public entry point: zero-padded to the next supported head dim, gradients come back in the original one
+    (fa_rdna3/interface.py:386-396, tests/test_fp32_headdim.py)."""
+    import fa_b200
+
+    q, k, v = (seeded(i, 1, 2, 260, head_dim, dtype=torch.float16).requires_grad_(True) for i in (1, 2, 3))
+    dout = seeded(4, 1, 2, 260, head_dim, dtype=torch.float16)
+    out = fa_b200.flash_attention(q, k, v, causal=True)
+    out.backward(dout)
+    ro, _, rdq, rdk, rdv = attention_grads_ref(q.detach().cpu(), k.detach().cpu(), v.detach().cpu(), dout.cpu(),
+                                               causal=True, softmax_scale=1.0 / math.sqrt(head_dim))
+    assert out.shape == q.shape and q.grad.shape == q.shape
+    assert_close_o(out, ro, torch.float16)
+    assert_close_grad(q.grad, rdq, "dq")
+    assert_close_grad(k.grad, rdk, "dk")
+    assert_close_grad(v.grad, rdv, "dv")
+
+
+@pytest.mark.parametrize("head_dim", [16, 32])
+def test_small_head_dims_take_the_tensor_core_kernels(head_dim):
+    """16-bit head dims below 64 are padded to 64 by the public entry point once the problem spans a tile."""
+    import fa_b200
+    from fa_b200 import interface
+
+    q, k, v = (seeded(i, 2, 4, 300, head_dim, dtype=torch.bfloat16).requires_grad_(True) for i in (1, 2, 3))
+    dout = seeded(4, 2, 4, 300, head_dim, dtype=torch.bfloat16)
+    out = fa_b200.flash_attention(q, k, v, causal=True)
+    assert interface.last_kernel_path() == "tcgen05"
+    out.backward(dout)
+    ro, _, rdq, rdk, rdv = attention_grads_ref(q.detach().cpu(), k.detach().cpu(), v.detach().cpu(), dout.cpu(),
+                                               causal=True, softmax_scale=1.0 / math.sqrt(head_dim))
+    assert_close_o(out, ro, torch.bfloat16)
+    assert_close_grad(q.grad, rdq, "dq")
+    assert_close_grad(k.grad, rdk, "dk")
+    assert_close_grad(v.grad, rdv, "dv")
+
+
+def test_fp32_strided_views():
+    """(B, S, H, D) storage viewed as (B, H, S, D): rows are not contiguous per head."""
+    from fa_b200 import interface
+
+    q = seeded(1, 2, 200, 4, 128, dtype=torch.float32).transpose(1, 2)
+    k = seeded(2, 2, 330, 4, 128, dtype=torch.float32).transpose(1, 2)
+    v = seeded(3, 2, 330, 4, 128, dtype=torch.float32).transpose(1, 2)
+    dout = seeded(4, 2, 200, 4, 128, dtype=torch.float32).transpose(1, 2)
+    scale = 1.0 / math.sqrt(128)
+    out, lse = interface._forward(q, k, v, True, scale, (-1, -1), 0.0, None, None, 0.0, 0)
+    dq, dk, dv = interface._backward(dout, q, k, v, out, lse, True, scale, (-1, -1), 0.0, None, None, 0.0, 0)
+    ro, rl, rdq, rdk, rdv = attention_grads_ref(q.cpu(), k.cpu(), v.cpu(), dout.cpu(), causal=True,
+                                                softmax_scale=scale)
+    assert max_abs(out, ro) <= FP32_O_TOL
+    for got, want in ((dq, rdq), (dk, rdk), (dv, rdv)):
+        assert rel_l2(got, want) <= FP32_GRAD_REL_L2
+
+
+def test_packed_sequences_large_head_dim():
+    """Packed layout (16-bit only, as in the reference) at head dim 256 through the public varlen entry point,
+    compared per sequence with the dense oracle."""
+    import fa_b200
+
+    lengths = [70, 1, 193, 64, 300]
+    total, H, Hk, D = sum(lengths), 4, 2, 256
+    dtype = torch.bfloat16
+    q = seeded(1, total, H, D, dtype=dtype).requires_grad_(True)
+    k = seeded(2, total, Hk, D, dtype=dtype).requires_grad_(True)
+    v = seeded(3, total, Hk, D, dtype=dtype).requires_grad_(True)
+    dout = seeded(4, total, H, D, dtype=dtype)
+    cu = torch.tensor([0] + list(torch.tensor(lengths).cumsum(0)), dtype=torch.int32, device="cuda")
+    out = fa_b200.flash_attention_varlen(q, k, v, cu, cu, max(lengths), max(lengths), causal=True, softcap=25.0)
+    out.backward(dout)
+    start = 0
+    for n in lengths:
+        sl = slice(start, start + n)
+        args = [t.detach()[sl].transpose(0, 1).unsqueeze(0).cpu() for t in (q, k, v, dout)]
+        ro, _, rdq, rdk, rdv = attention_grads_ref(*args, causal=True, softmax_scale=1.0 / math.sqrt(D), softcap=25.0)
+        assert_close_o(out.detach()[sl].transpose(0, 1).unsqueeze(0), ro, dtype)
+        for got, want, name in ((q.grad, rdq, "dq"), (k.grad, rdk, "dk"), (v.grad, rdv, "dv")):
+            assert_close_grad(got[sl].transpose(0, 1).unsqueeze(0), want, f"{name} of a {n}-token sequence")
+        start += n
