@@ -1,7 +1,8 @@
 // CUDA-core attention kernels that accept everything the public API accepts: fp16 / bf16 / fp32,
 // any head_dim up to 512, arbitrary strides, every score modifier, dense and packed layouts.
 // They serve the shapes the tensor-core kernels do not take (fp32 inputs, head_dim outside {64, 128},
-// non-unit inner strides) and compute in fp32 throughout. One warp owns one query row (forward, dQ)
+// non-unit inner strides) and compute in fp32 throughout. Two forms: shared-memory tiled kernels (second half of the
+// file) once both sequences span a tile, and below that kernels where one warp owns one query row (forward, dQ)
 // or one key row (dK/dV); the lanes of the warp take 32 keys (or queries) at a time.
 //
 // Semantics follow fa_rdna3/kernels/_common.py:233-508 (inner loops) and
@@ -391,7 +392,76 @@ __device__ __forceinline__ float ld_elem(const void* base, int64_t idx) {
   return DType<T>::to_float(reinterpret_cast<const T*>(base)[idx]);
 }
 
-template <typename T, int kRows>
+// Two adjacent 16-bit elements with one 4-byte load (kPair kernels: unit inner stride, even outer strides and offsets).
+template <typename T>
+__device__ __forceinline__ float2 ld_pair(const void* base, int64_t idx) {
+  return DType<T>::unpack2(*reinterpret_cast<const uint32_t*>(reinterpret_cast<const T*>(base) + idx));
+}
+template <>
+__device__ __forceinline__ float2 ld_pair<float>(const void* base, int64_t idx) {
+  return *reinterpret_cast<const float2*>(reinterpret_cast<const float*>(base) + idx);
+}
+
+// Staging slot u of a thread -> (row, column) of a tile that is 1 << kLog2W columns wide. With kPair, slots 2v and
+// 2v + 1 are the two halves of one 4-byte load.
+template <bool kPair, int kLog2W>
+__device__ __forceinline__ void stage_pos(int tid, int u, int* r, int* c) {
+  if (kPair) {
+    const int pidx = tid + (u >> 1) * kTileThreads;
+    *r = pidx >> (kLog2W - 1);
+    *c = ((pidx & ((1 << (kLog2W - 1)) - 1)) << 1) | (u & 1);
+  } else {
+    const int idx = tid + u * kTileThreads;
+    *r = idx >> kLog2W;
+    *c = idx & ((1 << kLog2W) - 1);
+  }
+}
+
+template <typename T, bool kPair, int kLog2W, int kN>
+__device__ __forceinline__ void stage_fetch(float (&reg)[kN], const void* base, int64_t off, int64_t rs, int64_t ds,
+                                            int valid, int c0, int D) {
+  const int tid = threadIdx.x;
+  if (kPair) {
+#pragma unroll
+    for (int u = 0; u < kN; u += 2) {
+      int r, c;
+      stage_pos<true, kLog2W>(tid, u, &r, &c);
+      float2 v = make_float2(0.f, 0.f);
+      if (r < valid && c0 + c < D) v = ld_pair<T>(base, off + (int64_t)r * rs + (c0 + c));
+      reg[u] = v.x;
+      reg[u + 1] = v.y;
+    }
+  } else {
+#pragma unroll
+    for (int u = 0; u < kN; ++u) {
+      int r, c;
+      stage_pos<false, kLog2W>(tid, u, &r, &c);
+      reg[u] = (r < valid && c0 + c < D) ? ld_elem<T>(base, off + (int64_t)r * rs + (int64_t)(c0 + c) * ds) : 0.f;
+    }
+  }
+}
+
+template <bool kPair, int kLog2W, int kN, int kStride>
+__device__ __forceinline__ void stage_store(const float (&reg)[kN], float (*dst)[kStride]) {
+  const int tid = threadIdx.x;
+  if (kPair) {
+#pragma unroll
+    for (int u = 0; u < kN; u += 2) {
+      int r, c;
+      stage_pos<true, kLog2W>(tid, u, &r, &c);
+      *reinterpret_cast<float2*>(&dst[r][c]) = make_float2(reg[u], reg[u + 1]);
+    }
+  } else {
+#pragma unroll
+    for (int u = 0; u < kN; ++u) {
+      int r, c;
+      stage_pos<false, kLog2W>(tid, u, &r, &c);
+      dst[r][c] = reg[u];
+    }
+  }
+}
+
+template <typename T, int kRows, bool kPair>
 __device__ __forceinline__ void tile_abt(const void* A, int64_t a_off, int64_t a_rs, int64_t a_ds, int a_valid,
                                          const void* B, int64_t b_off, int64_t b_rs, int64_t b_ds, int b_valid, int D,
                                          TileSmem& sm, float (&acc)[kRows][4]) {
@@ -401,21 +471,21 @@ __device__ __forceinline__ void tile_abt(const void* A, int64_t a_off, int64_t a
   for (int a = 0; a < kRows; ++a)
 #pragma unroll
     for (int b = 0; b < 4; ++b) acc[a][b] = 0.f;
+  // Global loads run one 32-column chunk ahead of the arithmetic: chunk d0 + 32 is in flight (in registers) while
+  // chunk d0 is multiplied out of shared memory.
+  constexpr int kA = BM * 32 / kTileThreads, kB = 64 * 32 / kTileThreads;
+  float ra[kA], rb[kB];
+  auto fetch = [&](int d0) {
+    stage_fetch<T, kPair, 5>(ra, A, a_off, a_rs, a_ds, a_valid, d0, D);
+    stage_fetch<T, kPair, 5>(rb, B, b_off, b_rs, b_ds, b_valid, d0, D);
+  };
+  fetch(0);
   for (int d0 = 0; d0 < D; d0 += 32) {
     __syncthreads();  // whoever read the staging buffers (or P's neighbours in the union) before is done
-    for (int idx = tid; idx < BM * 32; idx += kTileThreads) {
-      const int r = idx >> 5, d = idx & 31;
-      float v = 0.f;
-      if (r < a_valid && d0 + d < D) v = ld_elem<T>(A, a_off + (int64_t)r * a_rs + (int64_t)(d0 + d) * a_ds);
-      sm.u.ab.A[r][d] = v;
-    }
-    for (int idx = tid; idx < 64 * 32; idx += kTileThreads) {
-      const int r = idx >> 5, d = idx & 31;
-      float v = 0.f;
-      if (r < b_valid && d0 + d < D) v = ld_elem<T>(B, b_off + (int64_t)r * b_rs + (int64_t)(d0 + d) * b_ds);
-      sm.u.ab.B[r][d] = v;
-    }
+    stage_store<kPair, 5>(ra, sm.u.ab.A);
+    stage_store<kPair, 5>(rb, sm.u.ab.B);
     __syncthreads();
+    if (d0 + 32 < D) fetch(d0 + 32);
 #pragma unroll
     for (int d = 0; d < 32; d += 4) {
       float4 av[kRows], bv[4];
@@ -432,21 +502,21 @@ __device__ __forceinline__ void tile_abt(const void* A, int64_t a_off, int64_t a
   }
 }
 
-template <typename T, int kRows, int kDC>
+template <typename T, int kRows, int kDC, bool kPair>
 __device__ __forceinline__ void tile_pb(const void* B, int64_t b_off, int64_t b_rs, int64_t b_ds, int b_valid, int D,
                                         TileSmem& sm, float (&acc)[kDC][kRows][4]) {
   const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
+  constexpr int kV = 64 * 64 / kTileThreads;
+  float rv[kV];
+  auto fetch = [&](int c) { stage_fetch<T, kPair, 6>(rv, B, b_off, b_rs, b_ds, b_valid, c * 64, D); };
+  fetch(0);
 #pragma unroll
   for (int c = 0; c < kDC; ++c) {
     if (c * 64 < D) {
       __syncthreads();  // P is written, the previous chunk is consumed
-      for (int idx = tid; idx < 64 * 64; idx += kTileThreads) {
-        const int k = idx >> 6, col = idx & 63;
-        float v = 0.f;
-        if (k < b_valid && c * 64 + col < D) v = ld_elem<T>(B, b_off + (int64_t)k * b_rs + (int64_t)(c * 64 + col) * b_ds);
-        sm.u.V[k][col] = v;
-      }
+      stage_store<kPair, 6>(rv, sm.u.V);
       __syncthreads();
+      if (c + 1 < kDC && (c + 1) * 64 < D) fetch(c + 1);
 #pragma unroll 4
       for (int k = 0; k < 64; k += 4) {
         float4 pv[kRows], bv[4];
@@ -476,8 +546,8 @@ __device__ __forceinline__ float row16_sum(float x) {
   return x;
 }
 
-template <typename T, int kRows, int kDC>
-__global__ void __launch_bounds__(kTileThreads) tiled_fwd_kernel(const fa_attn_params P) {
+template <typename T, int kRows, int kDC, bool kPair>
+__global__ void __launch_bounds__(kTileThreads, (kDC * kRows <= 8 ? 2 : 1)) tiled_fwd_kernel(const fa_attn_params P) {
   __shared__ TileSmem sm;
   constexpr int BM = 16 * kRows;
   const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
@@ -504,7 +574,7 @@ __global__ void __launch_bounds__(kTileThreads) tiled_fwd_kernel(const fa_attn_p
 
   for (int j0 = lo; j0 < hi; j0 += 64) {
     float sc[kRows][4];
-    tile_abt<T, kRows>(P.q, s.q_off + (int64_t)i0 * P.q_strides[2], P.q_strides[2], P.q_strides[3], s.seqlen_q - i0,
+    tile_abt<T, kRows, kPair>(P.q, s.q_off + (int64_t)i0 * P.q_strides[2], P.q_strides[2], P.q_strides[3], s.seqlen_q - i0,
                        P.k, s.k_off + (int64_t)j0 * P.k_strides[2], P.k_strides[2], P.k_strides[3], s.seqlen_k - j0, D,
                        sm, sc);
 #pragma unroll
@@ -537,7 +607,7 @@ __global__ void __launch_bounds__(kTileThreads) tiled_fwd_kernel(const fa_attn_p
         for (int e = 0; e < 4; ++e) acc[c][a][e] *= alpha;
       if (m_new != kNegInf) m[a] = m_new;
     }
-    tile_pb<T, kRows, kDC>(P.v, s.v_off + (int64_t)j0 * P.v_strides[2], P.v_strides[2], P.v_strides[3],
+    tile_pb<T, kRows, kDC, kPair>(P.v, s.v_off + (int64_t)j0 * P.v_strides[2], P.v_strides[2], P.v_strides[3],
                            s.seqlen_k - j0, D, sm, acc);
   }
 
@@ -560,8 +630,8 @@ __global__ void __launch_bounds__(kTileThreads) tiled_fwd_kernel(const fa_attn_p
   }
 }
 
-template <typename T, int kRows, int kDC>
-__global__ void __launch_bounds__(kTileThreads) tiled_bwd_dq_kernel(const fa_attn_params P) {
+template <typename T, int kRows, int kDC, bool kPair>
+__global__ void __launch_bounds__(kTileThreads, (kDC * kRows <= 8 ? 2 : 1)) tiled_bwd_dq_kernel(const fa_attn_params P) {
   __shared__ TileSmem sm;
   constexpr int BM = 16 * kRows;
   const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
@@ -589,10 +659,10 @@ __global__ void __launch_bounds__(kTileThreads) tiled_bwd_dq_kernel(const fa_att
 
   for (int j0 = lo; j0 < hi; j0 += 64) {
     float sc[kRows][4], dp[kRows][4];
-    tile_abt<T, kRows>(P.q, s.q_off + (int64_t)i0 * P.q_strides[2], P.q_strides[2], P.q_strides[3], s.seqlen_q - i0,
+    tile_abt<T, kRows, kPair>(P.q, s.q_off + (int64_t)i0 * P.q_strides[2], P.q_strides[2], P.q_strides[3], s.seqlen_q - i0,
                        P.k, s.k_off + (int64_t)j0 * P.k_strides[2], P.k_strides[2], P.k_strides[3], s.seqlen_k - j0, D,
                        sm, sc);
-    tile_abt<T, kRows>(P.dout, s.do_off + (int64_t)i0 * P.do_strides[2], P.do_strides[2], P.do_strides[3],
+    tile_abt<T, kRows, kPair>(P.dout, s.do_off + (int64_t)i0 * P.do_strides[2], P.do_strides[2], P.do_strides[3],
                        s.seqlen_q - i0, P.v, s.v_off + (int64_t)j0 * P.v_strides[2], P.v_strides[2], P.v_strides[3],
                        s.seqlen_k - j0, D, sm, dp);
 #pragma unroll
@@ -606,7 +676,7 @@ __global__ void __launch_bounds__(kTileThreads) tiled_bwd_dq_kernel(const fa_att
         sm.P[ty + 16 * a][tx + 16 * bb] = ds;
       }
     }
-    tile_pb<T, kRows, kDC>(P.k, s.k_off + (int64_t)j0 * P.k_strides[2], P.k_strides[2], P.k_strides[3],
+    tile_pb<T, kRows, kDC, kPair>(P.k, s.k_off + (int64_t)j0 * P.k_strides[2], P.k_strides[2], P.k_strides[3],
                            s.seqlen_k - j0, D, sm, acc);
   }
 
@@ -627,8 +697,8 @@ __global__ void __launch_bounds__(kTileThreads) tiled_bwd_dq_kernel(const fa_att
 }
 
 // Rows of the tile are keys, columns are queries; the query heads of the group are summed in registers.
-template <typename T, int kRows, int kDC>
-__global__ void __launch_bounds__(kTileThreads) tiled_bwd_dkdv_kernel(const fa_attn_params P) {
+template <typename T, int kRows, int kDC, bool kPair>
+__global__ void __launch_bounds__(kTileThreads, (kDC * kRows <= 4 ? 2 : 1)) tiled_bwd_dkdv_kernel(const fa_attn_params P) {
   __shared__ TileSmem sm;
   constexpr int BM = 16 * kRows;
   const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
@@ -655,10 +725,10 @@ __global__ void __launch_bounds__(kTileThreads) tiled_bwd_dkdv_kernel(const fa_a
     query_range_for_keys(mods, j0, min(j0 + BM, s.seqlen_k) - 1, &lo, &hi);
     for (int i0 = lo; i0 < hi; i0 += 64) {
       float sc[kRows][4], dp[kRows][4];
-      tile_abt<T, kRows>(P.k, s.k_off + (int64_t)j0 * P.k_strides[2], P.k_strides[2], P.k_strides[3], s.seqlen_k - j0,
+      tile_abt<T, kRows, kPair>(P.k, s.k_off + (int64_t)j0 * P.k_strides[2], P.k_strides[2], P.k_strides[3], s.seqlen_k - j0,
                          P.q, s.q_off + (int64_t)i0 * P.q_strides[2], P.q_strides[2], P.q_strides[3], s.seqlen_q - i0,
                          D, sm, sc);
-      tile_abt<T, kRows>(P.v, s.v_off + (int64_t)j0 * P.v_strides[2], P.v_strides[2], P.v_strides[3], s.seqlen_k - j0,
+      tile_abt<T, kRows, kPair>(P.v, s.v_off + (int64_t)j0 * P.v_strides[2], P.v_strides[2], P.v_strides[3], s.seqlen_k - j0,
                          P.dout, s.do_off + (int64_t)i0 * P.do_strides[2], P.do_strides[2], P.do_strides[3],
                          s.seqlen_q - i0, D, sm, dp);
       float lse_i[4], delta_i[4];
@@ -680,14 +750,14 @@ __global__ void __launch_bounds__(kTileThreads) tiled_bwd_dkdv_kernel(const fa_a
           sc[a][bb] = pg.ds;
         }
       }
-      tile_pb<T, kRows, kDC>(P.dout, s.do_off + (int64_t)i0 * P.do_strides[2], P.do_strides[2], P.do_strides[3],
+      tile_pb<T, kRows, kDC, kPair>(P.dout, s.do_off + (int64_t)i0 * P.do_strides[2], P.do_strides[2], P.do_strides[3],
                              s.seqlen_q - i0, D, sm, dv);
       __syncthreads();  // every thread is done with the probabilities before the score gradients replace them
 #pragma unroll
       for (int a = 0; a < kRows; ++a)
 #pragma unroll
         for (int bb = 0; bb < 4; ++bb) sm.P[ty + 16 * a][tx + 16 * bb] = sc[a][bb];
-      tile_pb<T, kRows, kDC>(P.q, s.q_off + (int64_t)i0 * P.q_strides[2], P.q_strides[2], P.q_strides[3],
+      tile_pb<T, kRows, kDC, kPair>(P.q, s.q_off + (int64_t)i0 * P.q_strides[2], P.q_strides[2], P.q_strides[3],
                              s.seqlen_q - i0, D, sm, dk);
     }
   }
@@ -717,35 +787,51 @@ bool tiled_worthwhile(const fa_attn_params& p) { return p.seqlen_q >= 32 && p.se
 
 enum TiledKind { kTiledFwd, kTiledDq, kTiledDkdv };
 
-template <typename T, int kRows, int kDC>
+template <typename T, int kRows, int kDC, bool kPair>
 void launch_tiled_one(TiledKind kind, const fa_attn_params& p, cudaStream_t stream) {
   constexpr int BM = 16 * kRows;
   if (kind == kTiledDkdv) {
     dim3 grid((p.seqlen_k + BM - 1) / BM, p.batch * p.heads_kv);
-    tiled_bwd_dkdv_kernel<T, kRows, kDC><<<grid, kTileThreads, 0, stream>>>(p);
+    tiled_bwd_dkdv_kernel<T, kRows, kDC, kPair><<<grid, kTileThreads, 0, stream>>>(p);
   } else {
     dim3 grid((p.seqlen_q + BM - 1) / BM, p.batch * p.heads_q);
-    if (kind == kTiledFwd) tiled_fwd_kernel<T, kRows, kDC><<<grid, kTileThreads, 0, stream>>>(p);
-    else tiled_bwd_dq_kernel<T, kRows, kDC><<<grid, kTileThreads, 0, stream>>>(p);
+    if (kind == kTiledFwd) tiled_fwd_kernel<T, kRows, kDC, kPair><<<grid, kTileThreads, 0, stream>>>(p);
+    else tiled_bwd_dq_kernel<T, kRows, kDC, kPair><<<grid, kTileThreads, 0, stream>>>(p);
   }
 }
 
 // Rows per thread and 64-column chunks by head dimension; dK/dV carries two accumulators, so it narrows sooner.
-template <typename T>
+template <typename T, bool kPair>
 void launch_tiled_typed(TiledKind kind, const fa_attn_params& p, cudaStream_t stream) {
   const int D = p.head_dim;
-  if (D <= 64) launch_tiled_one<T, 4, 1>(kind, p, stream);
-  else if (D <= 128) launch_tiled_one<T, 4, 2>(kind, p, stream);
+  if (D <= 64) launch_tiled_one<T, 4, 1, kPair>(kind, p, stream);
+  else if (D <= 128) launch_tiled_one<T, 4, 2, kPair>(kind, p, stream);
   else if (D <= 256) {
-    if (kind == kTiledDkdv) launch_tiled_one<T, 2, 4>(kind, p, stream);
-    else launch_tiled_one<T, 4, 4>(kind, p, stream);
-  } else launch_tiled_one<T, 2, 8>(kind, p, stream);
+    if (kind == kTiledDkdv) launch_tiled_one<T, 2, 4, kPair>(kind, p, stream);
+    else launch_tiled_one<T, 4, 4, kPair>(kind, p, stream);
+  } else launch_tiled_one<T, 2, 8, kPair>(kind, p, stream);
+}
+
+// Paired loads need 4-byte (16-bit types) or 8-byte (fp32) aligned element pairs everywhere a tile may start.
+bool pair_loadable(const void* ptr, const int64_t st[4], int elem_bytes) {
+  return ptr == nullptr || (st[3] == 1 && (reinterpret_cast<uintptr_t>(ptr) % (2 * elem_bytes)) == 0 && st[0] % 2 == 0 &&
+                            st[1] % 2 == 0 && st[2] % 2 == 0);
 }
 
 void launch_tiled(TiledKind kind, const fa_attn_params& p, cudaStream_t stream) {
-  if (p.dtype == FA_F16) launch_tiled_typed<__half>(kind, p, stream);
-  else if (p.dtype == FA_BF16) launch_tiled_typed<__nv_bfloat16>(kind, p, stream);
-  else launch_tiled_typed<float>(kind, p, stream);
+  const int eb = p.dtype == FA_F32 ? 4 : 2;
+  bool pair = p.head_dim % 2 == 0 && pair_loadable(p.q, p.q_strides, eb) && pair_loadable(p.k, p.k_strides, eb) &&
+              pair_loadable(p.v, p.v_strides, eb);
+  if (kind != kTiledFwd) pair = pair && pair_loadable(p.dout, p.do_strides, eb);
+  if (p.dtype == FA_F16) {
+    if (pair) launch_tiled_typed<__half, true>(kind, p, stream);
+    else launch_tiled_typed<__half, false>(kind, p, stream);
+  } else if (p.dtype == FA_BF16) {
+    if (pair) launch_tiled_typed<__nv_bfloat16, true>(kind, p, stream);
+    else launch_tiled_typed<__nv_bfloat16, false>(kind, p, stream);
+  } else {
+    launch_tiled_typed<float, false>(kind, p, stream);  // 4-byte loads already fill a 128-byte line per warp
+  }
 }
 
 int check_launch(const char* what) {
