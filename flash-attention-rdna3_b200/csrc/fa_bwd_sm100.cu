@@ -39,6 +39,7 @@ constexpr uint32_t kFull = 0xffffffffu;
 
 struct BwdArgs {
   int varlen, batch, heads_q, heads_kv, seqlen_q, seqlen_k, total_q, total_k;
+  int head_dim;  // the caller's; the kernels' D is 64 or 128 and the columns in between load as zeros
   const int32_t* cu_q;
   const int32_t* cu_k;
   const float* lse;
@@ -133,9 +134,10 @@ __device__ __forceinline__ void bwd_mods_chunk32(const ScoreMods& m, float (&x)[
 
 // Converts a 32-column fp32 slice of a TMEM accumulator to 16-bit and writes it to a global row.
 template <typename T>
-__device__ __forceinline__ void store_row_slice(T* dst, const uint32_t (&o)[32], float scale) {
+__device__ __forceinline__ void store_row_slice(T* dst, const uint32_t (&o)[32], float scale, int cols) {
 #pragma unroll
   for (int v = 0; v < 4; ++v) {
+    if (v * 8 >= cols) break;  // columns past the caller's head dimension do not exist
     uint4 pkt;
     pkt.x = DType<T>::pack2(__uint_as_float(o[v * 8 + 0]) * scale, __uint_as_float(o[v * 8 + 1]) * scale);
     pkt.y = DType<T>::pack2(__uint_as_float(o[v * 8 + 2]) * scale, __uint_as_float(o[v * 8 + 3]) * scale);
@@ -587,7 +589,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 #pragma unroll
           for (int e = 0; e < 32; ++e) o[e] = 0u;
         }
-        if (j < Sk) store_row_slice<T>(row_ptr + c * 32, o, sc);
+        if (j < Sk) store_row_slice<T>(row_ptr + c * 32, o, sc, a.head_dim - c * 32);
       }
     }
   }
@@ -945,7 +947,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
 #pragma unroll
           for (int e = 0; e < 32; ++e) z[e] = 0u;
 #pragma unroll
-          for (int cc = 0; cc < kSlices; ++cc) store_row_slice<T>(row_ptr + (wg * kSlices + cc) * 32, z, 0.f);
+          for (int cc = 0; cc < kSlices; ++cc) store_row_slice<T>(row_ptr + (wg * kSlices + cc) * 32, z, 0.f, a.head_dim - (wg * kSlices + cc) * 32);
         }
         continue;
       }
@@ -1065,7 +1067,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
           tc_fence_before_sync();
           mbar_arrive(acc_free);  // this thread's last read of dQ is in registers
         }
-        if (i < it.Sq) store_row_slice<T>(row_ptr + c * 32, o, a.softmax_scale);
+        if (i < it.Sq) store_row_slice<T>(row_ptr + c * 32, o, a.softmax_scale, a.head_dim - c * 32);
       }
       PROF_MARK(3);
       g0 += it.n_total;
@@ -1098,7 +1100,7 @@ int launch_typed(const fa_attn_params& p, const BwdArgs& a0, int parts, cudaStre
   const int rows_k = p.varlen ? p.total_k : p.seqlen_k;
   const int nb = p.varlen ? 1 : p.batch;
   auto map_of = [&](CUtensorMap* m, const void* ptr, int rows, int heads, const int64_t* st, int box_rows) {
-    return make_tile_map(m, ptr, p.dtype, D, rows, heads, nb, st[2], st[1], st[0], box_rows);
+    return make_tile_map(m, ptr, p.dtype, p.head_dim, rows, heads, nb, st[2], st[1], st[0], box_rows);
   };
   cudaError_t e;
   BwdArgs a = a0;
@@ -1158,7 +1160,7 @@ PROF_DEFINE_READER(fa_debug_read_prof_bwd)
 
 bool bwd_tcgen05_supported(const fa_attn_params& p) {
   if (p.dtype != FA_F16 && p.dtype != FA_BF16) return false;
-  if (p.head_dim != 64 && p.head_dim != 128) return false;
+  if (p.head_dim < 8 || p.head_dim > 128 || p.head_dim % 8) return false;  // narrower rows are zero-filled by TMA
   const int64_t nb = p.varlen ? 1 : p.batch;
   const int64_t sq[3] = {nb, p.heads_q, p.varlen ? p.total_q : p.seqlen_q};
   const int64_t sk[3] = {nb, p.heads_kv, p.varlen ? p.total_k : p.seqlen_k};
@@ -1173,6 +1175,7 @@ int launch_bwd_tcgen05(const fa_attn_params& p, int parts, cudaStream_t stream) 
   a.varlen = p.varlen;
   a.batch = p.batch;
   a.heads_q = p.heads_q;
+  a.head_dim = p.head_dim;
   a.heads_kv = p.heads_kv;
   a.seqlen_q = p.seqlen_q;
   a.seqlen_k = p.seqlen_k;
@@ -1218,7 +1221,7 @@ int launch_bwd_tcgen05(const fa_attn_params& p, int parts, cudaStream_t stream) 
   a.status = p.status;
   const bool mods = p.softcap > 0.f || p.bias != nullptr || p.alibi_slopes != nullptr || p.dropout_p > 0.f;
   const bool f16 = p.dtype == FA_F16;
-  if (p.head_dim == 128) {
+  if (p.head_dim > 64) {
     if (f16)
       return mods ? launch_typed<__half, 128, true>(p, a, parts, stream)
                   : launch_typed<__half, 128, false>(p, a, parts, stream);

@@ -32,6 +32,7 @@ constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 struct FwdArgs {
   int varlen, heads_q, heads_kv, seqlen_q, seqlen_k, total_q, total_k;
+  int head_dim;  // the caller's; the kernel's D is 64 or 128 and the columns in between load as zeros
   const int32_t* cu_q;
   const int32_t* cu_k;
   void* out;
@@ -497,7 +498,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
               pkt.y = DType<T>::pack2(__uint_as_float(o[v * 8 + 2]) * inv, __uint_as_float(o[v * 8 + 3]) * inv);
               pkt.z = DType<T>::pack2(__uint_as_float(o[v * 8 + 4]) * inv, __uint_as_float(o[v * 8 + 5]) * inv);
               pkt.w = DType<T>::pack2(__uint_as_float(o[v * 8 + 6]) * inv, __uint_as_float(o[v * 8 + 7]) * inv);
-              *reinterpret_cast<uint4*>(orow + c * 32 + v * 8) = pkt;
+              if (c * 32 + v * 8 < a.head_dim) *reinterpret_cast<uint4*>(orow + c * 32 + v * 8) = pkt;
             }
           }
         }
@@ -527,11 +528,11 @@ int launch_typed(const fa_attn_params& p, const FwdArgs& a, cudaStream_t stream)
   const int rows_q = p.varlen ? p.total_q : p.seqlen_q;
   const int rows_k = p.varlen ? p.total_k : p.seqlen_k;
   const int nb = p.varlen ? 1 : p.batch;
-  int rc = make_tile_map(&mq, p.q, p.dtype, D, rows_q, p.heads_q, nb, p.q_strides[2], p.q_strides[1], p.q_strides[0]);
+  int rc = make_tile_map(&mq, p.q, p.dtype, p.head_dim, rows_q, p.heads_q, nb, p.q_strides[2], p.q_strides[1], p.q_strides[0]);
   if (rc) return rc;
-  rc = make_tile_map(&mk, p.k, p.dtype, D, rows_k, p.heads_kv, nb, p.k_strides[2], p.k_strides[1], p.k_strides[0]);
+  rc = make_tile_map(&mk, p.k, p.dtype, p.head_dim, rows_k, p.heads_kv, nb, p.k_strides[2], p.k_strides[1], p.k_strides[0]);
   if (rc) return rc;
-  rc = make_tile_map(&mv, p.v, p.dtype, D, rows_k, p.heads_kv, nb, p.v_strides[2], p.v_strides[1], p.v_strides[0]);
+  rc = make_tile_map(&mv, p.v, p.dtype, p.head_dim, rows_k, p.heads_kv, nb, p.v_strides[2], p.v_strides[1], p.v_strides[0]);
   if (rc) return rc;
   auto kern = fwd_kernel<T, D, kMods>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -549,7 +550,7 @@ PROF_DEFINE_READER(fa_debug_read_prof)
 
 bool fwd_tcgen05_supported(const fa_attn_params& p) {
   if (p.dtype != FA_F16 && p.dtype != FA_BF16) return false;
-  if (p.head_dim != 64 && p.head_dim != 128) return false;
+  if (p.head_dim < 8 || p.head_dim > 128 || p.head_dim % 8) return false;  // narrower rows are zero-filled by TMA
   const int64_t nb = p.varlen ? 1 : p.batch;
   const int64_t sq[3] = {nb, p.heads_q, p.varlen ? p.total_q : p.seqlen_q};
   const int64_t sk[3] = {nb, p.heads_kv, p.varlen ? p.total_k : p.seqlen_k};
@@ -564,6 +565,7 @@ int launch_fwd_tcgen05(const fa_attn_params& p, cudaStream_t stream) {
   FwdArgs a;
   a.varlen = p.varlen;
   a.heads_q = p.heads_q;
+  a.head_dim = p.head_dim;
   a.heads_kv = p.heads_kv;
   a.seqlen_q = p.seqlen_q;
   a.seqlen_k = p.seqlen_k;
@@ -598,7 +600,7 @@ int launch_fwd_tcgen05(const fa_attn_params& p, cudaStream_t stream) {
   const bool mods = p.softcap > 0.f || p.bias != nullptr || p.alibi_slopes != nullptr || p.dropout_p > 0.f ||
                     !(p.softmax_scale > 0.f);
   const bool f16 = p.dtype == FA_F16;
-  if (p.head_dim == 128) {
+  if (p.head_dim > 64) {
     if (f16) return mods ? launch_typed<__half, 128, true>(p, a, stream) : launch_typed<__half, 128, false>(p, a, stream);
     return mods ? launch_typed<__nv_bfloat16, 128, true>(p, a, stream)
                 : launch_typed<__nv_bfloat16, 128, false>(p, a, stream);

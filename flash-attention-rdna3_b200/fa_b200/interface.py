@@ -454,17 +454,15 @@ def flash_attention(query, key, value, causal=False, softmax_scale=None, window_
 
     # Head dims that are not a supported power of two are zero-padded (zeros add nothing to q.k or p.v)
     # and the output is sliced back; pad and slice are autograd-tracked.
-    # 16-bit head dims below 64 are padded to 64 as well: that is the narrowest tile of the tensor-core kernels, and
-    # the CUDA-core kernels that take 16 and 32 directly are two orders of magnitude slower once the sequences are
-    # longer than a tile.
+    # 16-bit head dims that are a multiple of 8 up to 128 need no copy: the tensor-core kernels read the narrower rows
+    # through their tensor maps, which fill the columns up to 64 or 128 with zeros.
     pad = 0
     padded = head_dim
-    if head_dim not in _SUPPORTED_HEAD_DIMS:
+    direct = query.dtype in LOW_PRECISION_DTYPES and head_dim % 8 == 0 and head_dim <= 128
+    if not direct and head_dim not in _SUPPORTED_HEAD_DIMS:
         padded = max(16, _next_power_of_2(head_dim))
         if padded not in _SUPPORTED_HEAD_DIMS:
             raise ValueError(f"head_dim {head_dim} not supported (would pad to {padded})")
-    if padded < 64 and query.dtype in LOW_PRECISION_DTYPES and query.shape[2] * key.shape[2] >= 128 * 128:
-        padded = 64
     if padded != head_dim:
         pad = padded - head_dim
         query = torch.nn.functional.pad(query, (0, pad))

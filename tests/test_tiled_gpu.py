@@ -131,9 +131,35 @@ def test_non_power_of_two_head_dims(head_dim):
     assert_close_grad(v.grad, rdv, "dv")
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("head_dim", [8, 16, 24, 40, 56, 72, 80, 96, 120])
+def test_narrow_head_dims_through_the_c_abi(dtype, head_dim):
+    """16-bit head dims that are a multiple of 8 run on the tensor-core kernels without padding: the tensor maps
+    zero-fill the columns up to 64 or 128 and the stores stop at the caller's width. Grouped heads, unequal lengths,
+    a window; the buffers are poisoned first so a store past the row would show."""
+    from fa_b200 import interface
+
+    B, H, Hk, Sq, Sk = 2, 4, 2, 200, 333
+    q = seeded(1, B, H, Sq, head_dim, dtype=dtype)
+    k = seeded(2, B, Hk, Sk, head_dim, dtype=dtype)
+    v = seeded(3, B, Hk, Sk, head_dim, dtype=dtype)
+    dout = seeded(4, B, H, Sq, head_dim, dtype=dtype)
+    scale = 1.0 / math.sqrt(head_dim)
+    out, lse = interface._forward(q, k, v, True, scale, (150, 0), 0.0, None, None, 0.0, 0)
+    assert interface.last_kernel_path() == "tcgen05"
+    dq, dk, dv = interface._backward(dout, q, k, v, out, lse, True, scale, (150, 0), 0.0, None, None, 0.0, 0)
+    assert interface.last_kernel_path() == "tcgen05"
+    ro, rl, rdq, rdk, rdv = attention_grads_ref(q.cpu(), k.cpu(), v.cpu(), dout.cpu(), causal=True,
+                                                softmax_scale=scale, window=(150, 0))
+    assert_close_o(out, ro, dtype)
+    assert_close_grad(dq, rdq, "dq")
+    assert_close_grad(dk, rdk, "dk")
+    assert_close_grad(dv, rdv, "dv")
+
+
 @pytest.mark.parametrize("head_dim", [16, 32])
 def test_small_head_dims_take_the_tensor_core_kernels(head_dim):
-    """16-bit head dims below 64 are padded to 64 by the public entry point once the problem spans a tile."""
+    """16-bit head dims below 64 reach the tensor-core kernels through the public entry point."""
     import fa_b200
     from fa_b200 import interface
 
