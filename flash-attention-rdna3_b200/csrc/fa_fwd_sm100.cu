@@ -76,13 +76,17 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
            const __grid_constant__ CUtensorMap map_v, const FwdArgs a) {
   constexpr int kChunks = D / 64;
   constexpr int kTileBytes = kChunks * 16384;  // one 128-row operand tile (rows of 128 B, 128-byte swizzle)
-  constexpr int kSlots = (D == 128) ? 4 : 6;
+  // Head dims above 128 ("wide"): one 128-row query tile per CTA with a 256-column O accumulator, the S tile
+  // double-buffered in the 256 columns the second query tile would use, and one softmax group (the other idles).
+  constexpr bool kWide = D > 128;
+  constexpr int kQTiles = kWide ? 1 : 2;
+  constexpr int kSlots = kWide ? 2 : (D == 128) ? 4 : 6;
   constexpr uint32_t kFull = 0xffffffffu;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
-  uint8_t* sKV = smem + 2 * kTileBytes;
+  uint8_t* sKV = smem + kQTiles * kTileBytes;
   __shared__ uint64_t q_full[2], kv_full[kSlots], kv_empty[kSlots], s_full[2], p_full[2], o_ready[2];
   __shared__ uint32_t tmem_base_s;
 
@@ -96,7 +100,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
     bounded_sequence(a.cu_q, b, a.total_q, &q_start, &Sq);
     bounded_sequence(a.cu_k, b, a.total_k, &k_start, &Sk);
   }
-  const int row_base = pair * 256;
+  const int row_base = pair * (kQTiles * 128);
   if (row_base >= Sq) return;  // uniform: nothing allocated yet
   const int tb = a.varlen ? 0 : b;  // batch coordinate of the tensor maps
 
@@ -129,7 +133,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
 #pragma unroll
   for (int t = 0; t < 2; ++t) {
     const int r0 = row_base + t * 128;
-    active[t] = r0 < Sq;
+    active[t] = r0 < Sq && t < kQTiles;
     lo[t] = hi[t] = 0;
     if (active[t]) {
       int klo, khi;
@@ -226,21 +230,23 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         }
       };
       auto in_range = [&](int t, int j) { return j >= lo[t] && j < hi[t]; };
-      auto issue_qk = [&](int t, int n) {
+      // sbuf: which 128-column S buffer (and s_full barrier) the tile uses: the query tile's own, or for wide head dims
+      // the parity of the key tile
+      auto issue_qk = [&](int t, int n, int sbuf) {
         const uint32_t qa = sq_addr + t * kTileBytes, ka = slot_addr(n);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk / 4) * 16384 + (kk % 4) * 32;
-          mma_ss(tmem_base + t * 128, make_smem_desc(qa + off, 16, 1024), make_smem_desc(ka + off, 16, 1024),
+          mma_ss(tmem_base + sbuf * 128, make_smem_desc(qa + off, 16, 1024), make_smem_desc(ka + off, 16, 1024),
                  idesc_qk, kk > 0);
         }
-        tc_commit(&s_full[t]);
+        tc_commit(&s_full[sbuf]);
       };
-      auto issue_pv = [&](int t, int n, bool first) {
+      auto issue_pv = [&](int t, int n, bool first, int sbuf) {
         const uint32_t va = slot_addr(n);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
-          mma_ts(tmem_base + 256 + t * D, tmem_base + t * 128 + kk * 8, make_smem_desc(va + kk * 2048, 16384, 1024),
+          mma_ts(tmem_base + 256 + t * D, tmem_base + sbuf * 128 + kk * 8, make_smem_desc(va + kk * 2048, 16384, 1024),
                  idesc_pv, !(first && kk == 0));
         }
         tc_commit(&o_ready[t]);
@@ -253,12 +259,44 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
           ok = false;
         }
       tc_fence_after_sync();
+      if constexpr (kWide) {
+        // One query tile: Q K^T of key tile i + 1 goes to the other S buffer before P V of tile i is issued, so it runs
+        // while the softmax group works on tile i. Ring: K(i) and V(i) take the two slots in turn.
+        if (ok) {
+          wait_full(0);
+          if (ok) {
+            tc_fence_after_sync();
+            issue_qk(0, 0, 0);
+            tc_commit(&kv_empty[0]);
+          }
+        }
+        for (int j = jlo; j < jhi && ok; ++j) {
+          const int i = j - jlo, nv = 2 * i + 1, nk_next = 2 * i + 2;
+          if (j + 1 < jhi) {
+            wait_full(nk_next);
+            if (!ok) break;
+            tc_fence_after_sync();
+            issue_qk(0, nk_next, (i + 1) & 1);
+            tc_commit(&kv_empty[nk_next % kSlots]);
+          }
+          wait_full(nv);
+          if (!ok) break;
+          if (!mbar_wait(&p_full[0], i & 1)) {
+            report_timeout(a.status, 104);
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          issue_pv(0, nv, i == 0, i & 1);
+          tc_commit(&kv_empty[nv % kSlots]);
+        }
+      } else {
       if (ok) {
         wait_full(0);
         if (ok) {
           tc_fence_after_sync();
-          if (in_range(0, jlo)) issue_qk(0, 0);
-          if (in_range(1, jlo)) issue_qk(1, 0);
+          if (in_range(0, jlo)) issue_qk(0, 0, 0);
+          if (in_range(1, jlo)) issue_qk(1, 0, 1);
           tc_commit(&kv_empty[0 % kSlots]);
         }
       }
@@ -285,12 +323,13 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
             }
             PROF_MARK(1);
             tc_fence_after_sync();
-            issue_pv(t, nv, j == lo[t]);
+            issue_pv(t, nv, j == lo[t], t);
           }
           if (t == 1) tc_commit(&kv_empty[nv % kSlots]);
-          if (have_next && in_range(t, j + 1)) issue_qk(t, nk_next);
+          if (have_next && in_range(t, j + 1)) issue_qk(t, nk_next, t);
           if (t == 1 && have_next) tc_commit(&kv_empty[nk_next % kSlots]);
         }
+      }
       }
       PROF_MARK(2);
       PROF_FLUSH(2, true);
@@ -304,7 +343,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
     const int row = row_base + t * 128 + r_tile;
     const int r0 = row_base + t * 128;
     const uint32_t lane_addr = static_cast<uint32_t>(w4 * 32) << 16;
-    const uint32_t tS = tmem_base + lane_addr + t * 128;
+    const uint32_t tS_own = tmem_base + lane_addr + t * 128;
     const uint32_t tO = tmem_base + lane_addr + 256 + t * D;
     const int off = Sk - Sq;
 
@@ -320,7 +359,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       for (int it = 0; it < n_tiles; ++it) {
         const int j = lo_t + it;
         PROF_MARK(7);
-        bool w_ok = mbar_wait(&s_full[t], it & 1);
+        // wide head dims: the S tile alternates between the two 128-column buffers with the key tile
+        const uint32_t tS = kWide ? tmem_base + lane_addr + (it & 1) * 128 : tS_own;
+        bool w_ok = kWide ? mbar_wait(&s_full[it & 1], (it >> 1) & 1) : mbar_wait(&s_full[t], it & 1);
         if (w_ok && it > 0) w_ok = mbar_wait(&o_ready[t], (it - 1) & 1);
         if (!__all_sync(kFull, w_ok)) {
           report_timeout(a.status, 105);
@@ -522,8 +563,9 @@ template <typename T, int D, bool kMods>
 int launch_typed(const fa_attn_params& p, const FwdArgs& a, cudaStream_t stream) {
   constexpr int kChunks = D / 64;
   constexpr int kTileBytes = kChunks * 16384;
-  constexpr int kSlots = (D == 128) ? 4 : 6;
-  const int smem = (2 + kSlots) * kTileBytes + 1024;
+  constexpr int kQTiles = D > 128 ? 1 : 2;
+  constexpr int kSlots = D > 128 ? 2 : (D == 128) ? 4 : 6;
+  const int smem = (kQTiles + kSlots) * kTileBytes + 1024;
   CUtensorMap mq, mk, mv;
   const int rows_q = p.varlen ? p.total_q : p.seqlen_q;
   const int rows_k = p.varlen ? p.total_k : p.seqlen_k;
@@ -550,7 +592,7 @@ PROF_DEFINE_READER(fa_debug_read_prof)
 
 bool fwd_tcgen05_supported(const fa_attn_params& p) {
   if (p.dtype != FA_F16 && p.dtype != FA_BF16) return false;
-  if (p.head_dim < 8 || p.head_dim > 128 || p.head_dim % 8) return false;  // narrower rows are zero-filled by TMA
+  if (p.head_dim < 8 || p.head_dim > 256 || p.head_dim % 8) return false;  // narrower rows are zero-filled by TMA
   const int64_t nb = p.varlen ? 1 : p.batch;
   const int64_t sq[3] = {nb, p.heads_q, p.varlen ? p.total_q : p.seqlen_q};
   const int64_t sk[3] = {nb, p.heads_kv, p.varlen ? p.total_k : p.seqlen_k};
@@ -595,11 +637,16 @@ int launch_fwd_tcgen05(const fa_attn_params& p, cudaStream_t stream) {
   a.wr = p.window_right;
   a.dropout_p = p.dropout_p;
   a.seed = p.dropout_seed;
-  a.num_pairs = (p.seqlen_q + 255) / 256;
+  a.num_pairs = p.head_dim > 128 ? (p.seqlen_q + 127) / 128 : (p.seqlen_q + 255) / 256;  // CTAs along the queries
   a.status = p.status;
   const bool mods = p.softcap > 0.f || p.bias != nullptr || p.alibi_slopes != nullptr || p.dropout_p > 0.f ||
                     !(p.softmax_scale > 0.f);
   const bool f16 = p.dtype == FA_F16;
+  if (p.head_dim > 128) {
+    if (f16) return mods ? launch_typed<__half, 256, true>(p, a, stream) : launch_typed<__half, 256, false>(p, a, stream);
+    return mods ? launch_typed<__nv_bfloat16, 256, true>(p, a, stream)
+                : launch_typed<__nv_bfloat16, 256, false>(p, a, stream);
+  }
   if (p.head_dim > 64) {
     if (f16) return mods ? launch_typed<__half, 128, true>(p, a, stream) : launch_typed<__half, 128, false>(p, a, stream);
     return mods ? launch_typed<__nv_bfloat16, 128, true>(p, a, stream)

@@ -454,11 +454,12 @@ def flash_attention(query, key, value, causal=False, softmax_scale=None, window_
 
     # Head dims that are not a supported power of two are zero-padded (zeros add nothing to q.k or p.v)
     # and the output is sliced back; pad and slice are autograd-tracked.
-    # 16-bit head dims that are a multiple of 8 up to 128 need no copy: the tensor-core kernels read the narrower rows
-    # through their tensor maps, which fill the columns up to 64 or 128 with zeros.
+    # 16-bit head dims that are a multiple of 8 up to 256 need no copy: the tensor-core kernels read the narrower rows
+    # through their tensor maps, which fill the columns up to 64, 128 or 256 with zeros (above 128 the backward runs
+    # on the CUDA-core kernels, which take any width).
     pad = 0
     padded = head_dim
-    direct = query.dtype in LOW_PRECISION_DTYPES and head_dim % 8 == 0 and head_dim <= 128
+    direct = query.dtype in LOW_PRECISION_DTYPES and head_dim % 8 == 0 and head_dim <= 256
     if not direct and head_dim not in _SUPPORTED_HEAD_DIMS:
         padded = max(16, _next_power_of_2(head_dim))
         if padded not in _SUPPORTED_HEAD_DIMS:

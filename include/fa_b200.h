@@ -61,10 +61,11 @@ enum fa_path { FA_PATH_NONE = 0, FA_PATH_TCGEN05 = 1, FA_PATH_SIMT = 2 };
  * seqlen_q / seqlen_k are max_seqlen_q / max_seqlen_k. cu_seqlens_* hold batch + 1 int32 entries and
  * are clamped into [0, total] by the kernels (fa_rdna3/kernels/varlen.py:22-27).
  *
- * head_dim: any width up to 512. fp16 / bf16 widths that are a multiple of 8 up to 128 (unit inner stride, 16-byte
- * aligned rows) run on the tensor-core kernels as they are: the tensor maps fill the columns up to 64 or 128 with
- * zeros, so the padding the reference does in Python (fa_rdna3/interface.py:386-396) needs no copy here. Everything
- * else (fp32, 256, 512, odd strides) runs on the CUDA-core kernels.
+ * head_dim: any width up to 512. fp16 / bf16 widths that are a multiple of 8 up to 256 (forward) or 128 (backward),
+ * with unit inner stride and 16-byte aligned rows, run on the tensor-core kernels as they are: the tensor maps fill
+ * the columns up to 64, 128 or 256 with zeros, so the padding the reference does in Python
+ * (fa_rdna3/interface.py:386-396) needs no copy here. Everything else (fp32, 512, the backward above 128, odd
+ * strides) runs on the CUDA-core kernels.
  */
 typedef struct fa_attn_params {
   int32_t dtype;            /* fa_dtype of q, k, v, out, dout, dq, dk, dv */

@@ -218,3 +218,65 @@ def test_packed_sequences_large_head_dim():
         for got, want, name in ((q.grad, rdq, "dq"), (k.grad, rdk, "dk"), (v.grad, rdv, "dv")):
             assert_close_grad(got[sl].transpose(0, 1).unsqueeze(0), want, f"{name} of a {n}-token sequence")
         start += n
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# head dims above 128: the forward runs on the tensor-core kernel (one query tile per CTA, 256-column accumulator),
+# the backward on the tiled CUDA-core kernels
+# ---------------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("head_dim", [136, 160, 192, 256])
+@pytest.mark.parametrize("sq,sk,causal", [(128, 128, False), (300, 300, True), (200, 777, True), (700, 300, True),
+                                          (1000, 1000, False)])
+def test_wide_head_dims_forward(dtype, head_dim, sq, sk, causal):
+    from fa_b200 import interface
+
+    q = seeded(1, 2, 4, sq, head_dim, dtype=dtype)
+    k = seeded(2, 2, 2, sk, head_dim, dtype=dtype)
+    v = seeded(3, 2, 2, sk, head_dim, dtype=dtype)
+    scale = 1.0 / math.sqrt(head_dim)
+    out, lse = interface._forward(q, k, v, causal, scale, (-1, -1), 0.0, None, None, 0.0, 0)
+    assert interface.last_kernel_path() == "tcgen05"
+    ro, rl, *_ = attention_grads_ref(q.cpu(), k.cpu(), v.cpu(), torch.zeros_like(q).cpu(), causal=causal,
+                                     softmax_scale=scale)
+    assert_close_o(out, ro, dtype)
+    assert_close_o(lse, rl, torch.float16, "lse")
+
+
+@pytest.mark.parametrize("opts", [
+    dict(causal=True, window=(63, 0)),
+    dict(window=(40, 25)),
+    dict(softcap=15.0),
+    dict(causal=True, alibi=True),
+    dict(causal=True, softcap=30.0, alibi=True, window=(100, 0)),
+    dict(dropout_p=0.2, dropout_seed=1234),
+    dict(bias=True),
+], ids=lambda o: "+".join(sorted(o)))
+def test_wide_head_dim_modifiers(opts):
+    """Head dim 256, forward on the tensor-core kernel and backward on the CUDA-core kernels from its O and LSE."""
+    from fa_b200 import interface
+
+    dtype, B, H, Hk, Sq, Sk, D = torch.float16, 1, 4, 2, 260, 390, 256
+    q = seeded(1, B, H, Sq, D, dtype=dtype)
+    k = seeded(2, B, Hk, Sk, D, dtype=dtype)
+    v = seeded(3, B, Hk, Sk, D, dtype=dtype)
+    dout = seeded(4, B, H, Sq, D, dtype=dtype)
+    scale = 1.0 / math.sqrt(D)
+    causal = opts.get("causal", False)
+    window = opts.get("window", (-1, -1))
+    softcap = opts.get("softcap", 0.0)
+    bias = (seeded(9, B, H, Sq, Sk, dtype=dtype) * 0.5) if opts.get("bias") else None
+    p, dseed = opts.get("dropout_p", 0.0), opts.get("dropout_seed", 0)
+    slopes = alibi_slopes_ref(H).cuda() if opts.get("alibi") else None
+    out, lse = interface._forward(q, k, v, causal, scale, window, softcap, bias, slopes, p, dseed)
+    assert interface.last_kernel_path() == "tcgen05"
+    dq, dk, dv = interface._backward(dout, q, k, v, out, lse, causal, scale, window, softcap, bias, slopes, p, dseed)
+    assert interface.last_kernel_path() == "simt"
+    ro, rl, rdq, rdk, rdv = attention_grads_ref(
+        q.cpu(), k.cpu(), v.cpu(), dout.cpu(), causal=causal, softmax_scale=scale, window=window, softcap=softcap,
+        bias=None if bias is None else bias.cpu(), alibi_slopes=None if slopes is None else slopes.cpu(),
+        dropout_p=p, dropout_seed=dseed)
+    assert_close_o(out, ro, dtype)
+    assert_close_grad(dq, rdq, "dq")
+    assert_close_grad(dk, rdk, "dk")
+    assert_close_grad(dv, rdv, "dv")
