@@ -596,6 +596,41 @@ def decode_extras(device, flush, peaks, iters=40, nsets=4):
     return res
 
 
+def other_shapes(device, tokens=2048, batch=2, heads=16, repeats=5):
+    """Forward and forward+backward times of the shapes beside the headline one, through the Python API: head dims
+    the tensor-core kernels take unpadded (32, 80), the wide forward kernel (160, 256; backward on CUDA cores) and
+    the tiled CUDA-core kernels (fp32, 512). CUDA events around `repeats` calls after two warm-up calls (warm L2)."""
+    import fa_b200
+
+    def timed(fn):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(repeats):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / repeats * 1e3
+
+    out = {}
+    for head_dim, dtype in ((32, torch.float16), (80, torch.float16), (160, torch.float16), (256, torch.float16),
+                            (512, torch.float16), (128, torch.float32)):
+        gen = torch.Generator(device=device).manual_seed(head_dim)
+        q, k, v, dout = (torch.randn(batch, heads, tokens, head_dim, device=device, dtype=dtype, generator=gen)
+                         for _ in range(4))
+        q.requires_grad_(True), k.requires_grad_(True), v.requires_grad_(True)
+        with torch.no_grad():
+            fwd_us = timed(lambda: fa_b200.flash_attention(q, k, v, causal=True))
+        both_us = timed(lambda: fa_b200.flash_attention(q, k, v, causal=True).backward(dout))
+        flops = 4.0 * batch * heads * tokens * tokens * head_dim / 2
+        out[f"{batch}x{heads}x{tokens}x{head_dim}_{str(dtype)[6:]}_causal"] = {
+            "fwd_us": fwd_us, "fwd_tflops": flops / fwd_us / 1e6,
+            "fwd_bwd_us": both_us, "fwd_bwd_tflops": 3.5 * flops / both_us / 1e6}
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -604,6 +639,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--skip-extras", action="store_true", help="skip decode numbers and the CPU baseline")
     ap.add_argument("--decode-only", action="store_true", help="only the decode numbers (one GPU), as their own JSON line")
+    ap.add_argument("--other-shapes", action="store_true",
+                    help="only the times of other head dims and fp32 inputs (one GPU), as their own JSON line")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
@@ -612,6 +649,10 @@ def main():
         device = torch.device("cuda", 0)
         torch.cuda.set_device(0)
         print(json.dumps({"decode": decode_extras(device, Flusher(device), load_peaks())}))
+    elif args.other_shapes:
+        import fa_b200  # noqa: F401  (fails loudly without the CUDA library)
+        torch.cuda.set_device(0)
+        print(json.dumps({"other_shapes": other_shapes(torch.device("cuda", 0))}))
     else:
         gpu_arm(args)
 
