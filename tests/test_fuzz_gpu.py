@@ -2,8 +2,9 @@
 
 The fixed grids of the other files follow the reference's tests; this file walks the corners between them
 (ragged lengths around the 128-row tile, cross-attention offsets, windows that start inside a tile, GQA ratios,
-empty and one-token sequences in a packed batch, decode and paged-decode shapes over both kernel families): 48 dense,
-16 packed, 32 decode and 32 paged cases, every one reproducible from its index.
+empty and one-token sequences in a packed batch, head dims beside 64 and 128 and fp32 inputs, decode and paged-decode
+shapes over both kernel families): 48 dense, 64 other-head-dim, 16 packed, 32 decode and 32 paged cases, every one
+reproducible from its index.
 """
 import random
 
@@ -43,6 +44,49 @@ def test_dense_random_shape(index):
     case = dense_case(index)
     used = run_case(path="tcgen05", **case)
     assert used == "tcgen05", case
+
+
+def other_head_dim_case(index):
+    """Head dims beside 64 and 128: narrow and wide 16-bit widths on the tensor-core kernels (zero-filled by the tensor
+    maps), 512 and fp32 on the tiled CUDA-core kernels; lengths around the 64- and 128-row tiles, with modifiers."""
+    rng = random.Random(13000 + index)
+    kind = ("narrow", "wide", "fp32", "d512")[index % 4]
+    dtype = rng.choice([torch.float16, torch.bfloat16])
+    if kind == "narrow":
+        head_dim = rng.choice([8, 16, 24, 32, 40, 48, 56, 72, 80, 88, 96, 104, 112, 120])
+    elif kind == "wide":
+        head_dim = rng.choice([136, 144, 160, 176, 192, 200, 224, 248, 256])
+    elif kind == "fp32":
+        head_dim, dtype = rng.choice([16, 20, 32, 64, 100, 128, 256]), torch.float32
+    else:
+        head_dim = rng.choice([264, 320, 512])
+    kv_heads = rng.choice([1, 2, 3])
+    group = rng.choice([1, 2, 4])
+    seqlen_q = rng.choice([1, 7, 31, 32, 33, 64, 100, 128, 129, 200, 257, 400])
+    seqlen_k = rng.choice([1, 5, 63, 64, 65, 128, 130, 255, 256, 300, 513])
+    opts = {}
+    if rng.random() < 0.5:
+        opts["causal"] = True
+    if rng.random() < 0.3:
+        opts["window"] = (rng.choice([0, 10, 100]), 0 if opts.get("causal") else rng.choice([-1, 0, 20]))
+    if rng.random() < 0.3:
+        opts["softcap"] = 25.0
+    if rng.random() < 0.25:
+        opts["alibi"] = True
+    # Dropout only where the comparison is well posed: with one visible key per row the exact dQ and dK are zero and
+    # what is left is the rounding of O inside delta, and bfloat16 rounds the rescaled probabilities (1 / keep) to 8
+    # bits, which alone passes 1e-2 on rows that see a handful of keys.
+    if rng.random() < 0.3 and dtype != torch.bfloat16 and seqlen_k >= 63 and "window" not in opts:
+        opts["dropout_p"], opts["dropout_seed"] = 0.15, rng.randrange(1 << 20)
+    return kind, dict(dtype=dtype, B=rng.randint(1, 2), H=kv_heads * group, Hk=kv_heads, Sq=seqlen_q, Sk=seqlen_k,
+                      D=head_dim, seed=index, **opts)
+
+
+@pytest.mark.parametrize("index", range(64))
+def test_other_head_dims_random_shape(index):
+    kind, case = other_head_dim_case(index)
+    used = run_case(path="auto", **case)   # the path of the backward launch
+    assert used == ("tcgen05" if kind == "narrow" else "simt"), case
 
 
 def packed_case(index):
