@@ -436,6 +436,7 @@ def gpu_arm(args):
     }
     if not args.skip_extras and world == 1:
         line["decode"] = decode_extras(device, flush, peaks)
+        line["other_shapes"] = other_shapes(device)
         line["cpu_baseline"] = cpu_baseline()
     if sharded is not None:
         line["decode_kv_sharded"] = sharded
