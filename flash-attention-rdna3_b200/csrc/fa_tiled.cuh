@@ -442,10 +442,8 @@ void launch_tiled_typed(const fa_attn_params& p, cudaStream_t stream) {
   const int D = p.head_dim;
   if (D <= 64) launch_tiled_one<kind, T, 4, 1, kPair>(p, stream);
   else if (D <= 128) launch_tiled_one<kind, T, 4, 2, kPair>(p, stream);
-  else if (D <= 256) {
-    if (kind == kTiledDkdv) launch_tiled_one<kind, T, 2, 4, kPair>(p, stream);
-    else launch_tiled_one<kind, T, 4, 4, kPair>(p, stream);
-  } else launch_tiled_one<kind, T, 2, 8, kPair>(p, stream);
+  else if (D <= 256) launch_tiled_one<kind, T, 4, 4, kPair>(p, stream);
+  else launch_tiled_one<kind, T, 2, 8, kPair>(p, stream);
 }
 
 // Paired loads need 4-byte (16-bit types) or 8-byte (fp32) aligned element pairs everywhere a tile may start.
