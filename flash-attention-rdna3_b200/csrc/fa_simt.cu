@@ -57,27 +57,39 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) simt_delta_kernel(const f
 template <typename T, int D>
 __global__ void __launch_bounds__(256) delta_vec_kernel(const fa_attn_params P) {
   constexpr int LPR = D / 8;         // lanes per row
-  constexpr int RPW = 32 / LPR;      // rows per warp
+  constexpr int RPW = 32 / LPR;      // rows per warp and pass
+  constexpr int kPasses = 4;         // rows per lane group: all eight 16-byte loads are issued before the first use
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-  const int i = (blockIdx.x * 8 + warp) * RPW + lane / LPR;
+  const int i0 = (blockIdx.x * 8 + warp) * RPW * kPasses + lane / LPR;
   const int b = blockIdx.y / P.heads_q, h = blockIdx.y % P.heads_q;
   SeqView s;
   make_view(P, b, h, &s);
-  float acc = 0.f;
-  if (i < s.seqlen_q) {
-    const T* o = reinterpret_cast<const T*>(P.out) + s.o_off + (int64_t)i * P.o_strides[2] + (lane % LPR) * 8;
-    const T* d = reinterpret_cast<const T*>(P.dout) + s.do_off + (int64_t)i * P.do_strides[2] + (lane % LPR) * 8;
-    const uint4 ov = *reinterpret_cast<const uint4*>(o), dv = *reinterpret_cast<const uint4*>(d);
-    const uint32_t ow[4] = {ov.x, ov.y, ov.z, ov.w}, dw[4] = {dv.x, dv.y, dv.z, dv.w};
+  uint4 ov[kPasses], dv[kPasses];
+#pragma unroll
+  for (int r = 0; r < kPasses; ++r) {
+    const int i = i0 + r * RPW;
+    ov[r] = dv[r] = make_uint4(0u, 0u, 0u, 0u);
+    if (i < s.seqlen_q) {
+      ov[r] = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(P.out) + s.o_off + (int64_t)i * P.o_strides[2] +
+                                              (lane % LPR) * 8);
+      dv[r] = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(P.dout) + s.do_off +
+                                              (int64_t)i * P.do_strides[2] + (lane % LPR) * 8);
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < kPasses; ++r) {
+    const int i = i0 + r * RPW;
+    const uint32_t ow[4] = {ov[r].x, ov[r].y, ov[r].z, ov[r].w}, dw[4] = {dv[r].x, dv[r].y, dv[r].z, dv[r].w};
+    float acc = 0.f;
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const float2 a = DType<T>::unpack2(ow[e]), c = DType<T>::unpack2(dw[e]);
       acc += a.x * c.x + a.y * c.y;
     }
-  }
 #pragma unroll
-  for (int o = LPR / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-  if (i < s.seqlen_q && lane % LPR == 0) P.delta[s.delta_off + (int64_t)i * s.delta_row_stride] = acc;
+    for (int o = LPR / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (i < s.seqlen_q && lane % LPR == 0) P.delta[s.delta_off + (int64_t)i * s.delta_row_stride] = acc;
+  }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -282,7 +294,7 @@ bool tiled_worthwhile(const fa_attn_params& p) { return p.seqlen_q >= 32 && p.se
 
 template <typename T, int D>
 int launch_delta_vec(const fa_attn_params& p, cudaStream_t stream) {
-  constexpr int rows_per_block = 8 * (32 / (D / 8));
+  constexpr int rows_per_block = 8 * (32 / (D / 8)) * 4;  // eight warps, four passes each
   dim3 grid((p.seqlen_q + rows_per_block - 1) / rows_per_block, p.batch * p.heads_q);
   delta_vec_kernel<T, D><<<grid, 256, 0, stream>>>(p);
   return check_launch("delta");
