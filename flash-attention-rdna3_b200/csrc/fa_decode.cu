@@ -575,9 +575,13 @@ int launch_decode_splitk(const fa_decode_params& p, cudaStream_t stream) {
     return set_error(FA_ERR_INVALID_ARGUMENT, "decode with several splits needs partial buffers");
   const bool tc_ok = decode_tc_supported(p);
   if (p.force_path == FA_PATH_TCGEN05 && !tc_ok)
-    return set_error(FA_ERR_UNSUPPORTED, "tcgen05 decode needs fp16/bf16, head_dim 64/128, <= 128 rows per kv head, "
-                                         "TMA-compatible strides and an even num_splits >= 2");
-  if (tc_ok && p.force_path != FA_PATH_SIMT) {
+    return set_error(FA_ERR_UNSUPPORTED, "tcgen05 decode needs fp16/bf16, head_dim 64/128/256, <= 128 rows per kv head, "
+                                         "TMA-compatible strides and num_splits >= 2 (even below head_dim 256)");
+  // Head dim 256 has room for two 64 KB ring slots only, so its tensor-core kernel streams at about 4 TB/s; it wins
+  // once a kv head serves four or more query rows (the CUDA-core kernel is then bound by its FMAs: 2.7 TB/s at a group
+  // of four) and loses below that (5.8 TB/s on CUDA cores with one row per kv head).
+  const bool tc_pays = p.head_dim != 256 || (p.heads_q / p.heads_kv) * p.seqlen_q >= 4;
+  if (tc_ok && p.force_path != FA_PATH_SIMT && (tc_pays || p.force_path == FA_PATH_TCGEN05)) {
     set_path(FA_PATH_TCGEN05);
     return launch_decode_tc(p, stream);
   }

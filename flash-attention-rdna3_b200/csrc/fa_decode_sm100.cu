@@ -81,7 +81,12 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                  const DecArgs a) {
   constexpr int kChunks = D / 64;
   constexpr int kTileBytes = kChunks * 16384;
-  constexpr int kSlots = (D == 128) ? 6 : 10;  // ring of 128-key tiles: K_t, V_t, K_t+1, V_t+1, ...
+  // Head dim 256 ("wide", dense caches only): TMEM holds one 256-column O accumulator beside the two S buffers, so one
+  // softmax group walks every tile (the S tile still alternates between the two buffers, which lets Q K^T of the next
+  // tile run ahead) and the CTA emits one partial; K and V (64 KB each) take the two ring slots in turn.
+  constexpr bool kWide = D > 128;
+  static_assert(!(kWide && kPaged), "the paged kernel is not built for head dims above 128");
+  constexpr int kSlots = kWide ? 2 : (D == 128) ? 6 : 10;  // ring of 128-key tiles: K_t, V_t, K_t+1, V_t+1, ...
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -276,9 +281,9 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         const uint32_t v_addr = ring_addr + slot * kTileBytes;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          mma_ts(tmem_base + 256 + s * D, tmem_base + s * 128 + kk * 8, make_smem_desc(v_addr + kk * 2048, 16384, 1024),
-                 idesc_pv, !(t < 2 && kk == 0));
-        tc_commit(&o_ready[s]);
+          mma_ts(tmem_base + 256 + (kWide ? 0 : s * D), tmem_base + s * 128 + kk * 8,
+                 make_smem_desc(v_addr + kk * 2048, 16384, 1024), idesc_pv, !(t < (kWide ? 1 : 2) && kk == 0));
+        tc_commit(&o_ready[kWide ? 0 : s]);
         tc_commit(&empty[slot]);
         if (t + 2 < ntiles) issue_qk(t + 2);
       }
@@ -288,9 +293,9 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     const int s = warp / 4, w4 = warp % 4;
     const int row = w4 * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>(w4 * 32) << 16;
-    const uint32_t tS = tmem_base + lane_addr + s * 128;
-    const uint32_t tO = tmem_base + lane_addr + 256 + s * D;
-    const int n_mine = (ntiles + 1 - s) / 2;
+    const uint32_t tS_own = tmem_base + lane_addr + s * 128;
+    const uint32_t tO = tmem_base + lane_addr + 256 + (kWide ? 0 : s * D);
+    const int n_mine = kWide ? (s == 0 ? ntiles : 0) : (ntiles + 1 - s) / 2;
     const bool warp_active = w4 * 32 < a.rows;  // warps whose 32 rows are all padding only keep the barriers moving
     const float scale_log2 = a.softmax_scale * kLog2e;
     float m_used = kNegInf, l = 0.f;
@@ -308,8 +313,10 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     }
 
     for (int i = 0; i < n_mine; ++i) {
-      const int t = 2 * i + s, j = jlo + t;
-      bool w_ok = mbar_wait(&s_full[s], i & 1);
+      const int t = kWide ? i : 2 * i + s, j = jlo + t;
+      const int sb = kWide ? (i & 1) : s;  // S buffer and its barriers
+      const uint32_t tS = kWide ? tmem_base + lane_addr + sb * 128 : tS_own;
+      bool w_ok = mbar_wait(&s_full[sb], kWide ? (i >> 1) & 1 : i & 1);
       if (w_ok && i > 0) w_ok = mbar_wait(&o_ready[s], (i - 1) & 1);
       if (!__all_sync(kFull, w_ok)) {
         report_timeout(a.status, 406);
@@ -427,7 +434,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         tc_wait_st();
       }
       tc_fence_before_sync();
-      mbar_arrive(&p_full[s]);
+      mbar_arrive(&p_full[sb]);
     }
 
     // epilogue: normalised fp32 partial and LSE of this stream
@@ -438,9 +445,9 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         ok = false;
       }
     }
-    if (ok && warp_active) {
+    if (ok && warp_active && !(kWide && s == 1)) {
       tc_fence_after_sync();
-      const int part = 2 * blockIdx.x + s;
+      const int part = kWide ? blockIdx.x : 2 * blockIdx.x + s;
       const int g = row / a.seqlen_q, sq = row % a.seqlen_q;
       const int h = kPaged ? row : hk * a.group + g;
       int64_t flat_o, flat_l;
@@ -506,7 +513,7 @@ template <typename T, int D, bool kPaged>
 int launch_kernel(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mvr,
                   const DecArgs& a, int ctas, cudaStream_t stream) {
   constexpr int kTileBytes = (D / 64) * 16384;
-  constexpr int kSlots = (D == 128) ? 6 : 10;
+  constexpr int kSlots = D > 128 ? 2 : (D == 128) ? 6 : 10;
   const int smem = (1 + kSlots) * kTileBytes + 1024;
   auto kern = decode_tc_kernel<T, D, kPaged>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -520,6 +527,14 @@ int launch_kernel(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMa
 template <bool kPaged>
 int dispatch(int dtype, int D, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
              const CUtensorMap& mvr, const DecArgs& a, int ctas, cudaStream_t stream) {
+  if (D == 256) {
+    if constexpr (!kPaged) {
+      return dtype == FA_F16 ? launch_kernel<__half, 256, false>(mq, mk, mv, mvr, a, ctas, stream)
+                             : launch_kernel<__nv_bfloat16, 256, false>(mq, mk, mv, mvr, a, ctas, stream);
+    } else {
+      return set_error(FA_ERR_UNSUPPORTED, "paged tcgen05 decode takes head_dim 64 or 128");
+    }
+  }
   if (dtype == FA_F16)
     return D == 128 ? launch_kernel<__half, 128, kPaged>(mq, mk, mv, mvr, a, ctas, stream)
                     : launch_kernel<__half, 64, kPaged>(mq, mk, mv, mvr, a, ctas, stream);
@@ -531,12 +546,14 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 
 
 }  // namespace
 
-// Dense split-K decode on the tcgen05 path. num_splits must be even: each CTA produces two partials.
+// Dense split-K decode on the tcgen05 path. Head dims 64 and 128: num_splits must be even, each CTA produces two
+// partials. Head dim 256: one partial per CTA, any num_splits >= 2.
 bool decode_tc_supported(const fa_decode_params& p) {
   if (p.dtype != FA_F16 && p.dtype != FA_BF16) return false;
-  if (p.head_dim != 64 && p.head_dim != 128) return false;
+  if (p.head_dim != 64 && p.head_dim != 128 && p.head_dim != 256) return false;
   if (!(p.softmax_scale > 0.f)) return false;
-  if (p.num_splits < 2 || (p.num_splits & 1) || p.o_partial == nullptr || p.lse_partial == nullptr) return false;
+  if (p.num_splits < 2 || p.o_partial == nullptr || p.lse_partial == nullptr) return false;
+  if (p.head_dim != 256 && (p.num_splits & 1)) return false;
   if (p.heads_kv <= 0 || p.heads_q % p.heads_kv) return false;
   const int group = p.heads_q / p.heads_kv;
   if (group * p.seqlen_q > 128) return false;
@@ -577,7 +594,7 @@ int launch_decode_tc(const fa_decode_params& p, cudaStream_t stream) {
   a.o_partial = p.o_partial;
   a.lse_partial = p.lse_partial;
   a.status = nullptr;
-  rc = dispatch<false>(p.dtype, D, mq, mk, mv, mv, a, p.num_splits / 2, stream);
+  rc = dispatch<false>(p.dtype, D, mq, mk, mv, mv, a, D == 256 ? p.num_splits : p.num_splits / 2, stream);
   if (rc) return rc;
   const int nrows = p.batch * p.heads_q * p.seqlen_q;
   return launch_combine_internal(nrows, D, p.num_splits, p.o_partial, (int64_t)nrows * D, D, p.lse_partial, nrows, 1,

@@ -95,7 +95,7 @@ def _fill_splits(base_ctas, max_splits, sm_count, ctas_per_sm=2):
     return best
 
 
-def _decode_splits_b200(batch, kv_heads, group_rows, seqlen_k, sm_count, tensor_core=False):
+def _decode_splits_b200(batch, kv_heads, group_rows, seqlen_k, sm_count, tensor_core=False, head_dim=128):
     """Key slices for split-K decode on B200. Tensor-core kernel: one CTA per SM, every CTA walks two streams of
     128-key tiles and emits two partials, so the count is even and each CTA gets at least two tiles.
     CUDA-core kernel: CTAs are per (batch, kv head, chunk of 4 query rows), two per SM; slices are at least 512
@@ -105,6 +105,8 @@ def _decode_splits_b200(batch, kv_heads, group_rows, seqlen_k, sm_count, tensor_
         # one wave of long CTAs beats several waves of short ones (per-CTA start-up is not amortised otherwise)
         heads = batch * kv_heads
         ctas = max(1, sm_count // heads) if heads < sm_count else 1
+        if head_dim > 128:  # one stream and one partial per CTA; the kernel wants at least two partials
+            return max(2, min(ctas, 32, max(1, tiles // 2)))
         return 2 * min(ctas, 32, max(1, tiles // 2))
     rows_per_cta = 1 if group_rows == 1 else 2 if group_rows == 2 else 4
     base = batch * kv_heads * _cdiv(group_rows, rows_per_cta)
@@ -485,7 +487,9 @@ def _vector_friendly(t):
 
 def _tensor_core_decode_ok(query, head_dim, rows_per_kv_head, softmax_scale):
     """Host-side mirror of the tcgen05 decode kernel's shape limits (the library re-checks strides itself)."""
-    return (query.dtype in LOW_PRECISION_DTYPES and head_dim in (64, 128) and rows_per_kv_head <= 128
+    if head_dim == 256 and rows_per_kv_head < 4:  # the library keeps these on the CUDA-core kernel (faster there)
+        return False
+    return (query.dtype in LOW_PRECISION_DTYPES and head_dim in (64, 128, 256) and rows_per_kv_head <= 128
             and softmax_scale > 0)
 
 
@@ -553,7 +557,8 @@ def flash_attention_decode(query, key, value, softmax_scale=None):
     sm_count = torch.cuda.get_device_properties(query.device).multi_processor_count
     rows = (heads // key.shape[1]) * seqlen_q
     num_splits = _decode_splits_b200(batch, key.shape[1], rows, seqlen_k, sm_count,
-                                     tensor_core=_tensor_core_decode_ok(query, head_dim, rows, softmax_scale))
+                                     tensor_core=_tensor_core_decode_ok(query, head_dim, rows, softmax_scale),
+                                     head_dim=head_dim)
     return _decode_op(query, key, value, softmax_scale, num_splits)
 
 

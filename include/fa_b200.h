@@ -113,7 +113,8 @@ enum fa_bwd_part { FA_BWD_DELTA = 1, FA_BWD_DKDV = 2, FA_BWD_DQ = 4 };
 /* Split-K decode: q (batch, heads_q, seqlen_q, head_dim), k/v (batch, heads_kv, seqlen_k, head_dim).
    Two kernel families: with fp16/bf16, head_dim 64 or 128, at most 128 query rows per kv head, TMA-compatible
    strides and an EVEN num_splits >= 2 the TMA + tcgen05 kernel runs (num_splits / 2 CTAs per (batch, kv head),
-   two partials each); anything else runs on the CUDA-core kernel.
+   two partials each); head_dim 256 runs on it with any num_splits >= 2 (one partial per CTA); anything else runs
+   on the CUDA-core kernel.
    o_partial (num_splits, batch, heads_q, seqlen_q, head_dim) fp32 contiguous and
    lse_partial (num_splits, batch, heads_q, seqlen_q) fp32 contiguous are caller-allocated scratch. */
 typedef struct fa_decode_params {

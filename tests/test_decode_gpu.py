@@ -217,6 +217,35 @@ def test_decode_both_kernel_families(path, hq, hk, sq, sk, splits):
 
 
 @pytest.mark.parametrize("path", [1, 2])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("hq,hk,sq,sk,splits", [(8, 8, 1, 4096, 8), (32, 8, 1, 8192, 5), (8, 2, 4, 1000, 4),
+                                                (4, 4, 8, 300, 2), (16, 1, 3, 129, 2), (2, 2, 1, 128, 3),
+                                                (8, 2, 1, 16384, 7)])
+def test_decode_head_dim_256_both_kernel_families(path, dtype, hq, hk, sq, sk, splits):
+    """Head dim 256 on the tensor-core kernel (one softmax stream, one partial per CTA, any split count >= 2) and on
+    the CUDA-core kernel."""
+    from fa_b200 import _lib, interface
+
+    q, k, v = (seeded(1, 2, hq, sq, 256, dtype=dtype), seeded(2, 2, hk, sk, 256, dtype=dtype),
+               seeded(3, 2, hk, sk, 256, dtype=dtype))
+    out = interface._decode_impl(q, k, v, 0.0625, splits, force_path=path)
+    assert _lib.load().fa_last_path() == path
+    ref, _ = oracle.decode_ref(q.cpu(), k.cpu(), v.cpu(), softmax_scale=0.0625)
+    assert_close_o(out, ref, dtype)
+
+
+def test_decode_head_dim_256_public_entry():
+    import fa_b200
+    from fa_b200 import _lib
+
+    q, k, v = seeded(1, 4, 32, 1, 256), seeded(2, 4, 8, 5000, 256), seeded(3, 4, 8, 5000, 256)
+    out = fa_b200.flash_attention_decode(q, k, v)
+    assert _lib.load().fa_last_path() == 1
+    ref, _ = oracle.decode_ref(q.cpu(), k.cpu(), v.cpu(), softmax_scale=1.0 / 16.0)
+    assert_close_o(out, ref, torch.float16)
+
+
+@pytest.mark.parametrize("path", [1, 2])
 @pytest.mark.parametrize("dtype,head_dim", [(torch.float16, 64), (torch.bfloat16, 128)])
 @pytest.mark.parametrize("block_size,contexts", [(16, [1000, 333, 0, 16]), (8, [257, 64, 5, 1]), (64, [700, 64, 65, 1]),
                                                  (128, [900, 128, 129, 0])])
