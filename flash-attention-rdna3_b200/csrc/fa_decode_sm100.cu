@@ -23,6 +23,8 @@
 #include "fa_sm100.cuh"
 #include "fa_tma_host.h"
 
+#include <mutex>
+
 namespace fa {
 
 int launch_combine_internal(int rows, int D, int splits, const float* o_partial, int64_t o_split_stride,
@@ -54,6 +56,12 @@ struct DecArgs {
   float* o_partial;
   float* lse_partial;
   int* status;
+  // dense, merge inside the kernel: the last CTA of a (batch, kv head) to finish combines that head's partials.
+  // tickets == nullptr: the caller launches the merge kernel instead.
+  unsigned int* tickets;  // one word per (batch, kv head), zero between launches (atomicInc wraps it back)
+  void* out;
+  int out_dtype;
+  int64_t o_sb, o_sh, o_ss, o_sd;
 };
 
 __device__ __forceinline__ void report_timeout(int* status, int code) {
@@ -480,11 +488,93 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       }
       if (row < a.rows) a.lse_partial[flat_l] = (l == 0.f) ? kNegInf : (m_used * kLn2 + logf(l));
     }
+    if (!kPaged && a.tickets != nullptr) __threadfence();  // this thread's partial is visible before the ticket is taken
   }
 
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 9) tmem_dealloc(tmem_base, 512);
+
+  if (!kPaged && a.tickets != nullptr) {
+    // Merge inside the kernel: every CTA of this (batch, kv head) takes a ticket once its partials are written; the
+    // one that draws the last ticket sees all of them and writes the output rows (the LSE-weighted sum of
+    // fa_rdna3/kernels/decode.py:101-122). Nobody waits for anybody. atomicInc wraps the word back to zero.
+    __shared__ int is_last;
+    if (tid == 0) is_last = atomicInc(&a.tickets[blockIdx.y], gridDim.x - 1) == gridDim.x - 1;
+    __syncthreads();
+    if (is_last) {
+      __threadfence();
+      // The ring is idle by now: its first bytes hold the weights and the cross-group sums. Threads are spread over
+      // (partial group, row, four columns) so that the partial reads of a small problem are all in flight at once.
+      const int P = a.num_partials, n_items = a.rows * (D / 4);
+      const int64_t split_rows = (int64_t)a.batch * a.heads_q * a.seqlen_q;  // rows of one partial
+      float* w_s = reinterpret_cast<float*>(smem);               // [rows][P] LSE, then weight
+      float* inv_s = w_s + a.rows * P;                            // [rows] 1 / sum of weights
+      float4* red_s = reinterpret_cast<float4*>(smem + 16384);    // [groups][n_items]
+      auto partial_row = [&](int r) {
+        const int g = r / a.seqlen_q, sq = r % a.seqlen_q;
+        return ((int64_t)b * a.heads_q + hk * a.group + g) * a.seqlen_q + sq;
+      };
+      for (int i = tid; i < a.rows * P; i += kThreads)
+        w_s[i] = __ldcg(a.lse_partial + (i % P) * split_rows + partial_row(i / P));
+      __syncthreads();
+      for (int r = tid; r < a.rows; r += kThreads) {
+        float M = kNegInf, den = 0.f;
+        for (int sp = 0; sp < P; ++sp) M = fmaxf(M, w_s[r * P + sp]);
+        const float Ms = (M == kNegInf) ? 0.f : M;
+        for (int sp = 0; sp < P; ++sp) {
+          const float ls = w_s[r * P + sp];
+          const float w = (ls == kNegInf) ? 0.f : expf(ls - Ms);
+          w_s[r * P + sp] = w;
+          den += w;
+        }
+        inv_s[r] = 1.f / ((den == 0.f) ? 1.f : den);
+      }
+      __syncthreads();
+      const int groups = n_items >= kThreads ? 1 : min(P, kThreads / n_items);
+      for (int it0 = 0; it0 < n_items; it0 += kThreads) {  // one pass unless rows * D / 4 exceeds the CTA
+        const int grp = groups == 1 ? 0 : tid / n_items;
+        const int item = groups == 1 ? it0 + tid : tid % n_items;
+        const bool mine = item < n_items && grp < groups;
+        const int r = mine ? item / (D / 4) : 0, d4 = item % (D / 4);
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (mine) {
+          const float4* src = reinterpret_cast<const float4*>(a.o_partial + partial_row(r) * D) + d4;
+#pragma unroll 4
+          for (int sp = grp; sp < P; sp += groups) {
+            const float w = w_s[r * P + sp];
+            const float4 v = __ldcg(src + sp * split_rows * (D / 4));
+            acc.x += w * v.x;
+            acc.y += w * v.y;
+            acc.z += w * v.z;
+            acc.w += w * v.w;
+          }
+        }
+        if (groups > 1) {
+          if (mine) red_s[grp * n_items + item] = acc;
+          __syncthreads();
+          if (mine && grp == 0)
+            for (int g2 = 1; g2 < groups; ++g2) {
+              const float4 v = red_s[g2 * n_items + item];
+              acc.x += v.x;
+              acc.y += v.y;
+              acc.z += v.z;
+              acc.w += v.w;
+            }
+        }
+        if (mine && grp == 0) {
+          const float inv = inv_s[r];
+          const int g = r / a.seqlen_q, sq = r % a.seqlen_q, h = hk * a.group + g;
+          const int64_t obase =
+              (int64_t)b * a.o_sb + (int64_t)h * a.o_sh + (int64_t)sq * a.o_ss + (int64_t)(d4 * 4) * a.o_sd;
+          store_from_float(a.out, obase, a.out_dtype, acc.x * inv);
+          store_from_float(a.out, obase + a.o_sd, a.out_dtype, acc.y * inv);
+          store_from_float(a.out, obase + 2 * a.o_sd, a.out_dtype, acc.z * inv);
+          store_from_float(a.out, obase + 3 * a.o_sd, a.out_dtype, acc.w * inv);
+        }
+      }
+    }
+  }
 }
 
 typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -544,6 +634,57 @@ int dispatch(int dtype, int D, const CUtensorMap& mq, const CUtensorMap& mk, con
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
+// Ticket words of the in-kernel merge. Calls that may run at the same time (different streams) use different
+// partial buffers, so each partial buffer gets its own region of words: the most recently used kTicketRegions buffers
+// of a device keep theirs, zeroed when the device's block is allocated and left at zero by every finished launch.
+constexpr int kTicketRegions = 64, kTicketWords = 1024;
+struct TicketPool {
+  unsigned int* base = nullptr;
+  const void* owner[kTicketRegions] = {};
+  uint64_t stamp[kTicketRegions] = {};
+  uint64_t clock = 0;
+};
+std::mutex g_ticket_mutex;
+TicketPool g_ticket_pool[16];
+
+bool g_ticket_pool_ready() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) return false;
+  std::lock_guard<std::mutex> lock(g_ticket_mutex);
+  return g_ticket_pool[dev].base != nullptr;
+}
+
+unsigned int* ticket_region(const void* partial_buffer) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) return nullptr;
+  std::lock_guard<std::mutex> lock(g_ticket_mutex);
+  TicketPool& pool = g_ticket_pool[dev];
+  if (pool.base == nullptr) {
+    unsigned int* mem = nullptr;
+    if (cudaMalloc(&mem, sizeof(unsigned int) * kTicketRegions * kTicketWords) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return nullptr;
+    }
+    if (cudaMemset(mem, 0, sizeof(unsigned int) * kTicketRegions * kTicketWords) != cudaSuccess) {
+      (void)cudaGetLastError();
+      cudaFree(mem);
+      return nullptr;
+    }
+    pool.base = mem;
+  }
+  int pick = 0;
+  for (int i = 0; i < kTicketRegions; ++i) {
+    if (pool.owner[i] == partial_buffer) {
+      pick = i;
+      break;
+    }
+    if (pool.stamp[i] < pool.stamp[pick]) pick = i;
+  }
+  pool.owner[pick] = partial_buffer;
+  pool.stamp[pick] = ++pool.clock;
+  return pool.base + pick * kTicketWords;
+}
+
 }  // namespace
 
 // Dense split-K decode on the tcgen05 path. Head dims 64 and 128: num_splits must be even, each CTA produces two
@@ -594,8 +735,24 @@ int launch_decode_tc(const fa_decode_params& p, cudaStream_t stream) {
   a.o_partial = p.o_partial;
   a.lse_partial = p.lse_partial;
   a.status = nullptr;
+  // Small merges run inside the decode kernel (one launch instead of two); large ones (many rows x many partials
+  // through one CTA) keep the merge kernel, which spreads the rows over the GPU.
+  a.tickets = nullptr;
+  if ((int64_t)rows * D * p.num_splits <= 65536 && (int64_t)p.batch * p.heads_kv <= kTicketWords && D % 4 == 0) {
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    const bool capturing = cudaStreamIsCapturing(stream, &cap) == cudaSuccess && cap != cudaStreamCaptureStatusNone;
+    // the first use on a device allocates (not allowed inside a capture); later uses only look the region up
+    if (!capturing || g_ticket_pool_ready()) a.tickets = ticket_region(p.o_partial);
+  }
+  a.out = p.out;
+  a.out_dtype = p.dtype;
+  a.o_sb = p.o_strides[0];
+  a.o_sh = p.o_strides[1];
+  a.o_ss = p.o_strides[2];
+  a.o_sd = p.o_strides[3];
   rc = dispatch<false>(p.dtype, D, mq, mk, mv, mv, a, D == 256 ? p.num_splits : p.num_splits / 2, stream);
   if (rc) return rc;
+  if (a.tickets != nullptr) return 0;
   const int nrows = p.batch * p.heads_q * p.seqlen_q;
   return launch_combine_internal(nrows, D, p.num_splits, p.o_partial, (int64_t)nrows * D, D, p.lse_partial, nrows, 1,
                                  p.out, p.dtype, p.heads_q, p.seqlen_q, p.o_strides[0], p.o_strides[1], p.o_strides[2],
