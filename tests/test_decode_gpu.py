@@ -298,3 +298,43 @@ def test_paged_kv_shards_both_families(path):
                                      want_lse=True, out_f32=True, force_path=path) for r in range(G)]
     o, _ = oracle.combine_ref(torch.stack([p[0] for p in parts]).cpu(), torch.stack([p[1] for p in parts]).cpu())
     assert max_abs(o, whole) <= 2e-3
+
+
+# ------------------------------------------------------------------------------------------ merge inside the kernel
+@pytest.mark.parametrize("hq,hk,sq,sk,splits", [(8, 8, 1, 2048, 2),      # one CTA per head draws the only ticket
+                                                (8, 8, 1, 16384, 36),    # 18 CTAs per head, 36 partials
+                                                (32, 8, 4, 4096, 8),     # 16 rows per kv head
+                                                (64, 1, 2, 4096, 4),     # 128 rows x 128 x 4 = 64 Ki floats: still inside
+                                                (64, 1, 2, 4096, 6)])    # one step larger: the merge kernel
+def test_decode_merge_inside_and_outside_the_kernel(hq, hk, sq, sk, splits):
+    """Small merges are done by the last CTA of each kv head inside the decode kernel, larger ones by the merge
+    kernel; twice in a row, so a ticket word that did not return to zero would show."""
+    from fa_b200 import _lib, interface
+
+    q, k, v = seeded(1, 2, hq, sq, 128), seeded(2, 2, hk, sk, 128), seeded(3, 2, hk, sk, 128)
+    ref, _ = oracle.decode_ref(q.cpu(), k.cpu(), v.cpu(), softmax_scale=0.09)
+    for _ in range(2):
+        out = interface._decode_impl(q, k, v, 0.09, splits, force_path=1)
+        assert _lib.load().fa_last_path() == 1
+        assert_close_o(out, ref, torch.float16)
+
+
+def test_decode_merge_inside_the_kernel_on_two_streams():
+    """Calls that overlap on the GPU use different partial buffers and therefore different ticket words."""
+    from fa_b200 import interface
+
+    cases = []
+    for i, sk in enumerate((8192, 12288)):
+        q, k, v = seeded(10 + i, 1, 8, 1, 128), seeded(20 + i, 1, 8, sk, 128), seeded(30 + i, 1, 8, sk, 128)
+        ref, _ = oracle.decode_ref(q.cpu(), k.cpu(), v.cpu(), softmax_scale=0.09)
+        cases.append((q, k, v, ref, torch.cuda.Stream()))
+    torch.cuda.synchronize()
+    outs = [[], []]
+    for _ in range(8):
+        for i, (q, k, v, ref, stream) in enumerate(cases):
+            with torch.cuda.stream(stream):
+                outs[i].append(interface._decode_impl(q, k, v, 0.09, 16, force_path=1))
+    torch.cuda.synchronize()
+    for i, (q, k, v, ref, stream) in enumerate(cases):
+        for out in outs[i]:
+            assert_close_o(out, ref, torch.float16)
