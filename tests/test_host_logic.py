@@ -51,6 +51,10 @@ def test_b200_split_counts_fill_one_wave():
         assert (s // 2) <= max(1, -(-seqlen_k // 128) // 2)
     assert I._decode_splits_b200(4, 32, 1, 16384, sm, tensor_core=True) == 2      # 128 CTAs already
     assert I._decode_splits_b200(1, 8, 1, 16384, sm, tensor_core=True) == 36      # 18 CTAs per head -> 144 CTAs
+    # head dim 256: one partial per CTA, so the count is the CTA count (at least 2), still within one wave
+    assert I._decode_splits_b200(4, 8, 4, 16384, sm, tensor_core=True, head_dim=256) == 4   # 32 heads x 4 = 128 CTAs
+    assert I._decode_splits_b200(1, 8, 4, 16384, sm, tensor_core=True, head_dim=256) == 18  # 144 CTAs
+    assert I._decode_splits_b200(4, 64, 4, 16384, sm, tensor_core=True, head_dim=256) == 2  # the kernel's minimum
     # tensor-core paged: one CTA row per batch entry, even count, CTAs within one wave
     s = I._paged_splits_b200(4, 8, 4, 16, 1024, sm, 16384, tensor_core=True)
     assert s == 74 and 4 * (s // 2) == 148
