@@ -191,7 +191,7 @@ __global__ void __launch_bounds__(kTileThreads, (kDC * kRows <= 8 ? 2 : 1)) tile
   __shared__ TileSmem sm;
   constexpr int BM = 16 * kRows;
   const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
-  const int i0 = blockIdx.x * BM;
+  const int i0 = (gridDim.x - 1 - blockIdx.x) * BM;  // long (causal) rows first: the short ones fill the last wave
   const int b = blockIdx.y / P.heads_q, h = blockIdx.y % P.heads_q;
   const int D = P.head_dim;
   SeqView s;
@@ -275,7 +275,7 @@ __global__ void __launch_bounds__(kTileThreads, (kDC * kRows <= 8 ? 2 : 1)) tile
   __shared__ TileSmem sm;
   constexpr int BM = 16 * kRows;
   const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
-  const int i0 = blockIdx.x * BM;
+  const int i0 = (gridDim.x - 1 - blockIdx.x) * BM;  // long (causal) rows first: the short ones fill the last wave
   const int b = blockIdx.y / P.heads_q, h = blockIdx.y % P.heads_q;
   const int D = P.head_dim;
   SeqView s;
