@@ -69,8 +69,8 @@ int run_fwd(const fa_attn_params* p, void* stream, bool varlen) {
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool tc_ok = fwd_tcgen05_supported(*p);
   if (p->force_path == FA_PATH_TCGEN05 && !tc_ok)
-    return set_error(FA_ERR_UNSUPPORTED, "the tcgen05 forward needs fp16/bf16, head_dim 64 or 128, unit inner "
-                                         "strides and 16-byte aligned rows");
+    return set_error(FA_ERR_UNSUPPORTED, "the tcgen05 forward needs fp16/bf16, a head_dim that is a multiple of 8 up to "
+                                         "256, unit inner strides and 16-byte aligned rows");
   if (tc_ok && p->force_path != FA_PATH_SIMT) {
     set_path(FA_PATH_TCGEN05);
     return launch_fwd_tcgen05(*p, s);
@@ -91,8 +91,8 @@ int run_bwd(const fa_attn_params* p, void* stream, bool varlen) {
   if (!(parts & (FA_BWD_DKDV | FA_BWD_DQ))) return 0;
   const bool tc_ok = bwd_tcgen05_supported(*p);
   if (p->force_path == FA_PATH_TCGEN05 && !tc_ok)
-    return set_error(FA_ERR_UNSUPPORTED, "the tcgen05 backward needs fp16/bf16, head_dim 64 or 128, unit inner "
-                                         "strides and 16-byte aligned rows");
+    return set_error(FA_ERR_UNSUPPORTED, "the tcgen05 backward needs fp16/bf16, a head_dim that is a multiple of 8 up to "
+                                         "128, unit inner strides and 16-byte aligned rows");
   if (tc_ok && p->force_path != FA_PATH_SIMT) {
     set_path(FA_PATH_TCGEN05);
     return launch_bwd_tcgen05(*p, parts, s);
@@ -160,6 +160,41 @@ int32_t fa_decode_paged(const fa_paged_params* p, void* stream) {
       p->block_table == nullptr || p->context_lens == nullptr)
     return fa::set_error(FA_ERR_INVALID_ARGUMENT, "q, caches, block_table, context_lens and out must not be NULL");
   return fa::launch_decode_paged(*p, static_cast<cudaStream_t>(stream));
+}
+
+int64_t fa_workspace_bytes(int32_t kind, const void* params) {
+  if (params == nullptr) return fa::set_error(FA_ERR_INVALID_ARGUMENT, "params is NULL");
+  switch (kind) {
+    case FA_WS_BWD_DELTA: {
+      const fa_attn_params* p = static_cast<const fa_attn_params*>(params);
+      if (p->heads_q <= 0 || (p->varlen ? p->total_q <= 0 : (p->batch <= 0 || p->seqlen_q <= 0)))
+        return fa::set_error(FA_ERR_INVALID_ARGUMENT, "workspace query: sizes must be positive");
+      return 4 * (int64_t)p->heads_q * (p->varlen ? (int64_t)p->total_q : (int64_t)p->batch * p->seqlen_q);
+    }
+    case FA_WS_DECODE_O_PARTIAL:
+    case FA_WS_DECODE_LSE_PARTIAL: {
+      const fa_decode_params* p = static_cast<const fa_decode_params*>(params);
+      if (p->batch <= 0 || p->heads_q <= 0 || p->seqlen_q <= 0 || p->head_dim <= 0 || p->num_splits < 1)
+        return fa::set_error(FA_ERR_INVALID_ARGUMENT, "workspace query: sizes must be positive");
+      if (p->num_splits == 1) return 0;
+      const int64_t rows = (int64_t)p->num_splits * p->batch * p->heads_q * p->seqlen_q;
+      return 4 * rows * (kind == FA_WS_DECODE_O_PARTIAL ? p->head_dim : 1);
+    }
+    case FA_WS_PAGED_O_PARTIAL:
+    case FA_WS_PAGED_LSE_PARTIAL: {
+      const fa_paged_params* p = static_cast<const fa_paged_params*>(params);
+      if (p->batch <= 0 || p->heads_q <= 0 || p->head_dim <= 0 || p->num_splits < 1)
+        return fa::set_error(FA_ERR_INVALID_ARGUMENT, "workspace query: sizes must be positive");
+      if (p->num_splits == 1) return 0;
+      const int64_t rows = (int64_t)p->num_splits * p->batch * p->heads_q;
+      return 4 * rows * (kind == FA_WS_PAGED_O_PARTIAL ? p->head_dim : 1);
+    }
+  }
+  return fa::set_error(FA_ERR_INVALID_ARGUMENT, "unknown workspace kind %d", kind);
+}
+
+void fa_test_decode_fault(uint32_t poll_limit, int32_t skip_tile) {
+  fa::set_decode_fault_injection(poll_limit, skip_tile);
 }
 
 int32_t fa_tiny_fwd(const fa_tiny_params* p, void* stream) {

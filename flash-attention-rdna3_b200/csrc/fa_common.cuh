@@ -328,5 +328,6 @@ bool decode_tc_supported(const fa_decode_params& p);                       // fa
 int launch_decode_tc(const fa_decode_params& p, cudaStream_t stream);
 bool paged_tc_supported(const fa_paged_params& p);
 int launch_paged_tc(const fa_paged_params& p, cudaStream_t stream);
+void set_decode_fault_injection(uint32_t poll_limit, int skip_tile);
 
 }  // namespace fa

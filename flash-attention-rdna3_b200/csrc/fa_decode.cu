@@ -643,7 +643,7 @@ int launch_decode_paged(const fa_paged_params& p, cudaStream_t stream) {
 // ---------------------------------------------------------------------------------------------
 // Split-K decode for callers that cannot allocate device memory.
 //
-// Some callers of a decode step may not call cudaMalloc (or anything that allocates) at the point where
+// Some callers of a decode step may not allocate device memory (no cudaMalloc, nothing that allocates) where
 // they run attention: code that executes inside a serving engine's pre-sized arena, a plug-in that is only
 // handed input and output buffers, or a caller in a latency-critical loop where an allocator call (and the
 // device synchronisation it can imply) is not acceptable. Split-K decode needs scratch for the per-slice

@@ -56,6 +56,8 @@ struct DecArgs {
   float* o_partial;
   float* lse_partial;
   int* status;
+  uint32_t poll_limit;  // polls before a barrier wait is declared lost (kWaitPollLimit unless a test shortens it)
+  int skip_tile;        // test hook: the producer leaves out the loads of this tile of every CTA (-1: none)
   // dense, merge inside the kernel: the last CTA of a (batch, kv head) to finish combines that head's partials.
   // tickets == nullptr: the caller launches the merge kernel instead.
   unsigned int* tickets;  // one word per (batch, kv head), zero between launches (atomicInc wraps it back)
@@ -105,6 +107,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   __shared__ int nval_s[kSlots][16];  // paged: readable tokens of each unit of the tile in that K slot
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+  auto wait = [&](uint64_t* bar, uint32_t parity) { return mbar_wait_limit(bar, parity, a.poll_limit); };
   // dense: one CTA row per (batch, kv head). paged: one per batch entry; a tile interleaves all kv heads
   // (row = token * heads_kv + head), which is how a page lies in memory, so a page is fetched with few large boxes.
   const int b = kPaged ? blockIdx.y : blockIdx.y / a.heads_kv;
@@ -203,13 +206,14 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
           const int n = 2 * t + which, slot = n % kSlots;
           uint8_t* dst = sRing + slot * kTileBytes;
           bool w_ok = true;
-          if (lane == 0) w_ok = mbar_wait(&empty[slot], ((n / kSlots) & 1) ^ 1);
+          if (lane == 0) w_ok = wait(&empty[slot], ((n / kSlots) & 1) ^ 1);
           w_ok = __shfl_sync(kFull, w_ok, 0);
           if (!w_ok) {
             if (lane == 0) report_timeout(a.status, 401);
             ok = false;
             break;
           }
+          if (t == a.skip_tile) continue;  // test hook: this tile never arrives, its consumers' waits run out
           if (!kPaged) {
             if (lane == 0) {
               mbar_arrive_expect_tx(&full[slot], kTileBytes);
@@ -255,12 +259,12 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       constexpr uint32_t idesc_qk = make_idesc(DType<T>::kFormat, 128, 128, 0, 0);
       constexpr uint32_t idesc_pv = make_idesc(DType<T>::kFormat, 128, D, 0, 1);
       const uint32_t q_addr = smem_u32(sQ), ring_addr = smem_u32(sRing);
-      bool ok = mbar_wait(&q_full, 0);
+      bool ok = wait(&q_full, 0);
       if (!ok) report_timeout(a.status, 403);
 
       auto issue_qk = [&](int t) {  // tile t goes to stream t & 1
         const int n = 2 * t, slot = n % kSlots, s = t & 1;
-        if (!mbar_wait(&full[slot], (n / kSlots) & 1)) {
+        if (!wait(&full[slot], (n / kSlots) & 1)) {
           report_timeout(a.status, 404);
           ok = false;
           return;
@@ -281,7 +285,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       if (ok && ntiles > 1) issue_qk(1);
       for (int t = 0; t < ntiles && ok; ++t) {
         const int n = 2 * t + 1, slot = n % kSlots, s = t & 1;
-        if (!mbar_wait(&full[slot], (n / kSlots) & 1) || !mbar_wait(&p_full[s], (t >> 1) & 1)) {
+        if (!wait(&full[slot], (n / kSlots) & 1) || !wait(&p_full[s], (t >> 1) & 1)) {
           report_timeout(a.status, 405);
           break;
         }
@@ -324,8 +328,8 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       const int t = kWide ? i : 2 * i + s, j = jlo + t;
       const int sb = kWide ? (i & 1) : s;  // S buffer and its barriers
       const uint32_t tS = kWide ? tmem_base + lane_addr + sb * 128 : tS_own;
-      bool w_ok = mbar_wait(&s_full[sb], kWide ? (i >> 1) & 1 : i & 1);
-      if (w_ok && i > 0) w_ok = mbar_wait(&o_ready[s], (i - 1) & 1);
+      bool w_ok = wait(&s_full[sb], kWide ? (i >> 1) & 1 : i & 1);
+      if (w_ok && i > 0) w_ok = wait(&o_ready[s], (i - 1) & 1);
       if (!__all_sync(kFull, w_ok)) {
         report_timeout(a.status, 406);
         ok = false;
@@ -447,13 +451,13 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 
     // epilogue: normalised fp32 partial and LSE of this stream
     if (n_mine > 0) {
-      const bool w_ok = ok && mbar_wait(&o_ready[s], (n_mine - 1) & 1);
+      const bool w_ok = ok && wait(&o_ready[s], (n_mine - 1) & 1);
       if (!__all_sync(kFull, w_ok)) {
         if (ok) report_timeout(a.status, 407);
         ok = false;
       }
     }
-    if (ok && warp_active && !(kWide && s == 1)) {
+    if (warp_active && !(kWide && s == 1)) {
       tc_fence_after_sync();
       const int part = kWide ? blockIdx.x : 2 * blockIdx.x + s;
       const int g = row / a.seqlen_q, sq = row % a.seqlen_q;
@@ -466,12 +470,15 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         flat_l = (((int64_t)part * a.batch + b) * a.heads_q + h) * a.seqlen_q + sq;
         flat_o = flat_l * D;
       }
+      // A stream that gave up on a wait hands in an empty partial (zeros, LSE = -inf), which the merge ignores;
+      // the status word carries the failure.
+      if (!ok) l = 0.f;
       const float l_safe = (l == 0.f) ? 1.f : l;
       const float inv = 1.f / l_safe;
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
         uint32_t o[32];
-        if (n_mine > 0) {
+        if (n_mine > 0 && ok) {
           tmem_ld32(tO + c * 32, o);
           tc_wait_ld_regs(o);
         } else {
@@ -634,55 +641,56 @@ int dispatch(int dtype, int D, const CUtensorMap& mq, const CUtensorMap& mk, con
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
-// Ticket words of the in-kernel merge. Calls that may run at the same time (different streams) use different
-// partial buffers, so each partial buffer gets its own region of words: the most recently used kTicketRegions buffers
-// of a device keep theirs, zeroed when the device's block is allocated and left at zero by every finished launch.
-constexpr int kTicketRegions = 64, kTicketWords = 1024;
-struct TicketPool {
-  unsigned int* base = nullptr;
+// Ticket words of the in-kernel merge: a fixed array inside the library image (zero when the module is loaded, and
+// every finished launch leaves its words at zero again), so the library never allocates. Launches that may run at the
+// same time (different streams) must not share words; such launches use different partial buffers, so each partial
+// buffer address gets a region of its own, for good: once all kTicketRegions regions of a device belong to other
+// buffers, further buffers simply keep the separate merge kernel. Regions are never handed to a second buffer, so a
+// captured graph that holds a region pointer stays valid whatever runs later.
+constexpr int kTicketRegions = 64, kTicketWords = 1024, kTicketDevices = 64;
+static __device__ __align__(256) unsigned int g_ticket_words[kTicketRegions * kTicketWords];
+
+struct TicketTable {
+  unsigned int* base = nullptr;  // device address of g_ticket_words in this device's context
   const void* owner[kTicketRegions] = {};
-  uint64_t stamp[kTicketRegions] = {};
-  uint64_t clock = 0;
+  int used = 0;
 };
 std::mutex g_ticket_mutex;
-TicketPool g_ticket_pool[16];
+TicketTable g_ticket_table[kTicketDevices];
 
-bool g_ticket_pool_ready() {
+// Region for this partial buffer on the current device, or nullptr (no region left, or the array's address is not
+// known yet and cannot be asked for because the stream is being captured).
+unsigned int* ticket_region(const void* partial_buffer, bool capturing) {
   int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) return false;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kTicketDevices) return nullptr;
   std::lock_guard<std::mutex> lock(g_ticket_mutex);
-  return g_ticket_pool[dev].base != nullptr;
+  TicketTable& tab = g_ticket_table[dev];
+  if (tab.base == nullptr) {
+    if (capturing) return nullptr;
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_ticket_words) != cudaSuccess || ptr == nullptr) {
+      (void)cudaGetLastError();
+      return nullptr;
+    }
+    tab.base = static_cast<unsigned int*>(ptr);
+  }
+  for (int i = 0; i < tab.used; ++i)
+    if (tab.owner[i] == partial_buffer) return tab.base + i * kTicketWords;
+  if (tab.used == kTicketRegions) return nullptr;
+  tab.owner[tab.used] = partial_buffer;
+  return tab.base + (tab.used++) * kTicketWords;
 }
 
-unsigned int* ticket_region(const void* partial_buffer) {
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) return nullptr;
-  std::lock_guard<std::mutex> lock(g_ticket_mutex);
-  TicketPool& pool = g_ticket_pool[dev];
-  if (pool.base == nullptr) {
-    unsigned int* mem = nullptr;
-    if (cudaMalloc(&mem, sizeof(unsigned int) * kTicketRegions * kTicketWords) != cudaSuccess) {
-      (void)cudaGetLastError();
-      return nullptr;
-    }
-    if (cudaMemset(mem, 0, sizeof(unsigned int) * kTicketRegions * kTicketWords) != cudaSuccess) {
-      (void)cudaGetLastError();
-      cudaFree(mem);
-      return nullptr;
-    }
-    pool.base = mem;
-  }
-  int pick = 0;
-  for (int i = 0; i < kTicketRegions; ++i) {
-    if (pool.owner[i] == partial_buffer) {
-      pick = i;
-      break;
-    }
-    if (pool.stamp[i] < pool.stamp[pick]) pick = i;
-  }
-  pool.owner[pick] = partial_buffer;
-  pool.stamp[pick] = ++pool.clock;
-  return pool.base + pick * kTicketWords;
+// Test hook (fa_test_decode_fault): poll limit and tile to leave out for the next tensor-core decode launch of this
+// thread; consumed by that launch.
+thread_local uint32_t g_fault_poll_limit = 0;
+thread_local int g_fault_skip_tile = -1;
+
+void take_fault_injection(DecArgs* a) {
+  a->poll_limit = g_fault_poll_limit ? g_fault_poll_limit : kWaitPollLimit;
+  a->skip_tile = g_fault_skip_tile;
+  g_fault_poll_limit = 0;
+  g_fault_skip_tile = -1;
 }
 
 }  // namespace
@@ -734,15 +742,15 @@ int launch_decode_tc(const fa_decode_params& p, cudaStream_t stream) {
   a.num_partials = p.num_splits;
   a.o_partial = p.o_partial;
   a.lse_partial = p.lse_partial;
-  a.status = nullptr;
+  a.status = p.status;
+  take_fault_injection(&a);
   // Small merges run inside the decode kernel (one launch instead of two); large ones (many rows x many partials
   // through one CTA) keep the merge kernel, which spreads the rows over the GPU.
   a.tickets = nullptr;
   if ((int64_t)rows * D * p.num_splits <= 65536 && (int64_t)p.batch * p.heads_kv <= kTicketWords && D % 4 == 0) {
     cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
     const bool capturing = cudaStreamIsCapturing(stream, &cap) == cudaSuccess && cap != cudaStreamCaptureStatusNone;
-    // the first use on a device allocates (not allowed inside a capture); later uses only look the region up
-    if (!capturing || g_ticket_pool_ready()) a.tickets = ticket_region(p.o_partial);
+    a.tickets = ticket_region(p.o_partial, capturing);
   }
   a.out = p.out;
   a.out_dtype = p.dtype;
@@ -816,13 +824,19 @@ int launch_paged_tc(const fa_paged_params& p, cudaStream_t stream) {
   a.num_partials = p.num_splits;
   a.o_partial = p.o_partial;
   a.lse_partial = p.lse_partial;
-  a.status = nullptr;
+  a.status = p.status;
+  take_fault_injection(&a);
   rc = dispatch<true>(p.dtype, D, mq, mk, mv, mvr, a, p.num_splits / 2, stream);
   if (rc) return rc;
   const int nrows = p.batch * p.heads_q;
   return launch_combine_internal(nrows, D, p.num_splits, p.o_partial, D, (int64_t)p.num_splits * D, p.lse_partial, 1,
                                  p.num_splits, p.out, p.out_is_f32 ? (int)FA_F32 : p.dtype, p.heads_q, 1, p.o_strides[0],
                                  p.o_strides[1], 0, p.o_strides[2], p.lse_out, stream);
+}
+
+void set_decode_fault_injection(uint32_t poll_limit, int skip_tile) {
+  g_fault_poll_limit = poll_limit;
+  g_fault_skip_tile = skip_tile;
 }
 
 }  // namespace fa

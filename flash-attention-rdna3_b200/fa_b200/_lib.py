@@ -13,6 +13,8 @@ LIB_PATH = os.path.join(_HERE, "libfa_b200.so")
 FA_F16, FA_BF16, FA_F32 = 0, 1, 2
 FA_PATH_NONE, FA_PATH_TCGEN05, FA_PATH_SIMT = 0, 1, 2
 FA_BWD_DELTA, FA_BWD_DKDV, FA_BWD_DQ = 1, 2, 4
+FA_WS_BWD_DELTA, FA_WS_DECODE_O_PARTIAL, FA_WS_DECODE_LSE_PARTIAL, FA_WS_PAGED_O_PARTIAL, FA_WS_PAGED_LSE_PARTIAL = 1, 2, 3, 4, 5
+ABI_VERSION = 2
 
 I64x4 = C.c_int64 * 4
 I64x3 = C.c_int64 * 3
@@ -56,6 +58,7 @@ class DecodeParams(C.Structure):
         ("out", C.c_void_p), ("o_strides", I64x4),
         ("softmax_scale", C.c_float), ("num_splits", C.c_int32),
         ("o_partial", C.c_void_p), ("lse_partial", C.c_void_p), ("force_path", C.c_int32),
+        ("status", C.c_void_p),
     ]
 
 
@@ -84,6 +87,7 @@ class PagedParams(C.Structure):
         ("first_block", C.c_int32), ("block_step", C.c_int32),
         ("o_partial", C.c_void_p), ("lse_partial", C.c_void_p), ("lse_out", C.c_void_p),
         ("out_is_f32", C.c_int32), ("force_path", C.c_int32),
+        ("status", C.c_void_p),
     ]
 
 
@@ -115,6 +119,8 @@ SYMBOLS = {
     "fa_combine": (C.c_int32, [C.POINTER(CombineParams), C.c_void_p]),
     "fa_decode_paged": (C.c_int32, [C.POINTER(PagedParams), C.c_void_p]),
     "fa_tiny_fwd": (C.c_int32, [C.POINTER(TinyParams), C.c_void_p]),
+    "fa_workspace_bytes": (C.c_int64, [C.c_int32, C.c_void_p]),
+    "fa_test_decode_fault": (None, [C.c_uint32, C.c_int32]),
 }
 
 _lib = None
@@ -137,6 +143,9 @@ def load():
                 fn = getattr(lib, name)
                 fn.restype = restype
                 fn.argtypes = argtypes
+            if lib.fa_abi_version() != ABI_VERSION:
+                raise RuntimeError(f"fa_b200: {LIB_PATH} has ABI version {lib.fa_abi_version()}, this package expects "
+                                   f"{ABI_VERSION}; rebuild it with `python flash-attention-rdna3_b200/build.py`")
             _lib = lib
     return _lib
 

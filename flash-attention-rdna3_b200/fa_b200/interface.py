@@ -519,6 +519,7 @@ def _decode_impl(query, key, value, softmax_scale, num_splits, force_path=0):
     p.softmax_scale = float(softmax_scale)
     p.num_splits = int(num_splits)
     p.force_path = int(force_path)
+    p.status = _status_word(query.device).data_ptr()
     if num_splits > 1:
         o_partial = torch.empty((num_splits, batch, heads, seqlen_q, head_dim), dtype=torch.float32,
                                 device=query.device)
@@ -703,6 +704,7 @@ def _paged_launch(query, k_cache, v_cache, block_table, context_lens, softmax_sc
     p.first_block, p.block_step = int(first_block), int(block_step)
     p.out_is_f32 = int(out_f32)
     p.force_path = int(force_path)
+    p.status = _status_word(query.device).data_ptr()
     if lse is not None:
         p.lse_out = lse.data_ptr()
     if num_splits > 1:

@@ -9,8 +9,10 @@
  *
  * Conventions
  *  - Every pointer is a device pointer unless stated otherwise. The caller owns every buffer: the
- *    library allocates nothing (outputs and scratch are passed in, the way the reference allocates
- *    them with torch.empty before a launch).
+ *    library allocates nothing and frees nothing (outputs and scratch are passed in, the way the reference
+ *    allocates them with torch.empty before a launch; fa_workspace_bytes gives the scratch sizes). The two
+ *    fixed arrays the library does use (the scratch of fa_decode_splitk_noalloc and the ticket words of the
+ *    in-kernel decode merge) are part of its image.
  *  - Strides are in ELEMENTS of the tensor's dtype, one per dimension, as in the reference kernels'
  *    signatures (e.g. fa_rdna3/kernels/forward.py:30-40).
  *  - `stream` is a cudaStream_t passed as void*; work is enqueued on it and the call returns without
@@ -29,7 +31,7 @@
 extern "C" {
 #endif
 
-#define FA_B200_ABI_VERSION 1
+#define FA_B200_ABI_VERSION 2
 
 #if defined(__GNUC__)
 #define FA_API __attribute__((visibility("default")))
@@ -129,6 +131,8 @@ typedef struct fa_decode_params {
   float* o_partial;
   float* lse_partial;
   int32_t force_path;  /* 0 = automatic; FA_PATH_TCGEN05 (needs an even num_splits >= 2) or FA_PATH_SIMT */
+  int32_t* status;     /* device int32 or NULL; set by the tensor-core kernel when a bounded wait ran out (the
+                          abandoned slice then contributes an empty partial: zeros with LSE = -inf) */
 } fa_decode_params;
 
 /* LSE-weighted merge of `num_splits` partial results for `rows` independent rows.
@@ -170,6 +174,7 @@ typedef struct fa_paged_params {
   float* lse_out;           /* (batch, heads_q) fp32 contiguous or NULL */
   int32_t out_is_f32;       /* write out as fp32 regardless of dtype (shard partials) */
   int32_t force_path;       /* 0 = automatic; FA_PATH_TCGEN05 (needs an even num_splits >= 2) or FA_PATH_SIMT */
+  int32_t* status;          /* device int32 or NULL, as in fa_decode_params */
 } fa_paged_params;
 
 /* FP32 short-sequence attention: q, k, v, out (batch, heads, seqlen <= 32, 128), optional bias. */
@@ -191,6 +196,18 @@ FA_API int32_t fa_device_supported(int32_t device);
 FA_API const char* fa_last_error_string(void);
 /* fa_path of the calling thread's last fa_fwd / fa_bwd / fa_varlen_* call. */
 FA_API int32_t fa_last_path(void);
+
+/* Bytes of caller-provided scratch an entry point needs for the problem in `params` (the struct of that entry
+   point), or a negative fa_error. The reference sizes the same buffers inline with torch.empty
+   (fa_rdna3/interface.py:217-220 delta, :451-455 split-K partials, :696-699 paged partials). */
+enum fa_workspace_kind {
+  FA_WS_BWD_DELTA = 1,          /* fa_attn_params   -> delta */
+  FA_WS_DECODE_O_PARTIAL = 2,   /* fa_decode_params -> o_partial (0 when num_splits == 1) */
+  FA_WS_DECODE_LSE_PARTIAL = 3, /* fa_decode_params -> lse_partial */
+  FA_WS_PAGED_O_PARTIAL = 4,    /* fa_paged_params  -> o_partial */
+  FA_WS_PAGED_LSE_PARTIAL = 5   /* fa_paged_params  -> lse_partial */
+};
+FA_API int64_t fa_workspace_bytes(int32_t kind, const void* params);
 
 /* Dense forward: writes out and lse. Replaces the _attention_forward launch,
    fa_rdna3/interface.py:154-199 (kernel fa_rdna3/kernels/forward.py:28-164). */
@@ -232,6 +249,12 @@ FA_API int32_t fa_combine(const fa_combine_params* p, void* stream);
 /* Paged-KV decode. Replaces the _attention_decode_paged (+ combine) launches,
    fa_rdna3/interface.py:703-727 (kernel fa_rdna3/kernels/paged.py:17-89). */
 FA_API int32_t fa_decode_paged(const fa_paged_params* p, void* stream);
+
+/* Test hook, no counterpart in the reference: makes the NEXT tensor-core decode launch (dense or paged) of the
+   calling thread use `poll_limit` polls per barrier wait (0 = the default, about a second) and leave out the
+   loads of tile `skip_tile` of every CTA (-1 = none), so that a wait runs out, the kernel leaves through its
+   normal exit and the status word is set. Nothing faults and nothing hangs. */
+FA_API void fa_test_decode_fault(uint32_t poll_limit, int32_t skip_tile);
 
 /* FP32 short-sequence forward. Replaces the _attention_tiny_forward launch,
    fa_rdna3/interface.py:84-104 (kernel fa_rdna3/kernels/tiny.py:10-85). */

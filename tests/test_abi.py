@@ -29,7 +29,7 @@ def test_library_loads_and_exports_every_symbol():
     lib = ctypes.CDLL(_lib.LIB_PATH)
     for name in declared_symbols():
         assert hasattr(lib, name), name
-    assert _lib.load().fa_abi_version() == 1
+    assert _lib.load().fa_abi_version() == 2
 
 
 def test_struct_sizes_match_the_header():
@@ -64,6 +64,36 @@ def test_argument_errors_are_reported_without_a_gpu():
     assert lib.fa_decode_splitk(ctypes.byref(d), None) == -1
     t = _lib.TinyParams()
     assert lib.fa_tiny_fwd(ctypes.byref(t), None) == -1
+
+
+def test_workspace_bytes_match_what_the_python_layer_allocates():
+    from fa_b200 import _lib
+
+    lib = _lib.load()
+    d = _lib.DecodeParams()
+    d.batch, d.heads_q, d.heads_kv, d.seqlen_q, d.seqlen_k, d.head_dim, d.num_splits = 2, 8, 2, 3, 4096, 128, 6
+    assert lib.fa_workspace_bytes(_lib.FA_WS_DECODE_O_PARTIAL, ctypes.byref(d)) == 6 * 2 * 8 * 3 * 128 * 4
+    assert lib.fa_workspace_bytes(_lib.FA_WS_DECODE_LSE_PARTIAL, ctypes.byref(d)) == 6 * 2 * 8 * 3 * 4
+    d.num_splits = 1
+    assert lib.fa_workspace_bytes(_lib.FA_WS_DECODE_O_PARTIAL, ctypes.byref(d)) == 0
+    p = _lib.PagedParams()
+    p.batch, p.heads_q, p.heads_kv, p.head_dim, p.num_splits = 4, 32, 8, 128, 10
+    assert lib.fa_workspace_bytes(_lib.FA_WS_PAGED_O_PARTIAL, ctypes.byref(p)) == 4 * 32 * 10 * 128 * 4
+    assert lib.fa_workspace_bytes(_lib.FA_WS_PAGED_LSE_PARTIAL, ctypes.byref(p)) == 4 * 32 * 10 * 4
+    a = _lib.AttnParams()
+    a.batch, a.heads_q, a.seqlen_q = 2, 16, 2048
+    assert lib.fa_workspace_bytes(_lib.FA_WS_BWD_DELTA, ctypes.byref(a)) == 2 * 16 * 2048 * 4
+    assert lib.fa_workspace_bytes(99, ctypes.byref(a)) == -1
+
+
+def test_library_sources_call_no_allocator():
+    """The header promises that the library allocates and frees nothing: no source file may name an allocating or
+    freeing CUDA runtime call (the two fixed arrays it uses are file-scope __device__ arrays)."""
+    csrc = os.path.join(ROOT, "flash-attention-rdna3_b200", "csrc")
+    banned = re.compile(r"\bcuda(Malloc\w*|Free\w*|Memset\w*|HostAlloc|MallocAsync)\s*\(|\bcuMemAlloc\w*\s*\(")
+    for f in sorted(os.listdir(csrc)):
+        text = open(os.path.join(csrc, f)).read()
+        assert not banned.search(text), f
 
 
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):

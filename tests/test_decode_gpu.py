@@ -338,3 +338,43 @@ def test_decode_merge_inside_the_kernel_on_two_streams():
     for i, (q, k, v, ref, stream) in enumerate(cases):
         for out in outs[i]:
             assert_close_o(out, ref, torch.float16)
+
+
+# ---------------------------------------------------------------------------------------------------
+# The status path of the tensor-core decode kernels. The failure is made on purpose in the allowed form: the
+# library's test hook shortens the poll limit and makes the producer leave one tile out, so a wait on a barrier
+# that nothing completes runs out, every role leaves through the kernel's normal exit (TMEM freed), the abandoned
+# slice hands in an empty partial and the status word is set. Nothing traps, faults or spins without a bound.
+# ---------------------------------------------------------------------------------------------------
+def test_decode_lost_wait_sets_the_status_word_and_leaves_the_gpu_usable():
+    import fa_b200
+    from fa_b200 import _lib, interface
+
+    lib = _lib.load()
+    q, k, v = seeded(1, 1, 1, 1, 128), seeded(2, 1, 1, 512, 128), seeded(3, 1, 1, 512, 128)
+    ref, _ = oracle.decode_ref(q.cpu(), k.cpu(), v.cpu())
+    fa_b200.check_status()
+    lib.fa_test_decode_fault(1 << 12, 0)  # one CTA (two splits), tile 0 never arrives
+    out = interface._decode_impl(q, k, v, 1.0 / math.sqrt(128), 2, force_path=_lib.FA_PATH_TCGEN05)
+    with pytest.raises(RuntimeError, match="wait timeout"):
+        fa_b200.check_status()
+    assert torch.isfinite(out.float()).all()  # the empty partials merge to finite numbers, never to garbage
+    fa_b200.check_status()                    # the word was cleared by the failed check
+    # the hook is one-shot and the context is intact: the same call now gives the right answer
+    out = interface._decode_impl(q, k, v, 1.0 / math.sqrt(128), 2, force_path=_lib.FA_PATH_TCGEN05)
+    assert_close_o(out, ref, torch.float16)
+
+
+def test_paged_lost_wait_sets_the_status_word():
+    import fa_b200
+    from fa_b200 import _lib, interface
+
+    lib = _lib.load()
+    q, kc, vc, table, ctx = make_paged(1, 8, 2, 128, 16, [400], seed=5)
+    fa_b200.check_status()
+    lib.fa_test_decode_fault(1 << 12, 0)
+    out, _ = interface._paged_launch(q, kc, vc, table, ctx, 1.0 / math.sqrt(128), 2, force_path=_lib.FA_PATH_TCGEN05)
+    with pytest.raises(RuntimeError, match="wait timeout"):
+        fa_b200.check_status()
+    assert torch.isfinite(out.float()).all()
+    check_paged(q, kc, vc, table, ctx, num_splits=2)
