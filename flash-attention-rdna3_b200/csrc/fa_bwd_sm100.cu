@@ -356,18 +356,27 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         }
       };
       auto scores = [&](uint32_t col, uint32_t a_addr, uint32_t b_addr) {  // [128 keys x 128 queries] = A B^T over D
+        // descriptors as 32-bit halves: one add per operand and instruction (the issuing thread shares its scheduler
+        // with compute warps, so its instruction count is tensor-pipe time)
+        const uint32_t a_lo = smem_desc_lo(a_addr, 16), b_lo = smem_desc_lo(b_addr, 16);
+        constexpr uint32_t hi = smem_desc_hi(1024);
+        mma_ss_lo<0>(tmem_base + col, a_lo, hi, b_lo, hi, idesc_s);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t o = (kk / 4) * 16384 + (kk % 4) * 32;
-          mma_ss(tmem_base + col, make_smem_desc(a_addr + o, 16, 1024), make_smem_desc(b_addr + o, 16, 1024), idesc_s,
-                 kk > 0);
+        for (int kk = 1; kk < D / 16; ++kk) {
+          const uint32_t o = ((kk / 4) * 16384 + (kk % 4) * 32) >> 4;
+          mma_ss_lo<1>(tmem_base + col, a_lo + o, hi, b_lo + o, hi, idesc_s);
         }
       };
       auto accumulate = [&](uint32_t col_acc, uint32_t col_a, uint32_t b_addr, bool first) {  // += A^(tmem) B over queries
+        // 16 queries per instruction; each group's operand sits in its own half
+        const uint32_t b_lo = smem_desc_lo(b_addr, 16384);
+        constexpr uint32_t hi = smem_desc_hi(1024);
+        if (first) mma_ts_lo<0>(tmem_base + col_acc, tmem_base + col_a, b_lo, hi, idesc_acc);
+        else mma_ts_lo<1>(tmem_base + col_acc, tmem_base + col_a, b_lo, hi, idesc_acc);
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk)  // 16 queries per instruction; each group's operand sits in its own half
-          mma_ts(tmem_base + col_acc, tmem_base + col_a + (kk / 4) * 64 + (kk % 4) * 8,
-                 make_smem_desc(b_addr + kk * 2048, 16384, 1024), idesc_acc, !(first && kk == 0));
+        for (int kk = 1; kk < 8; ++kk)
+          mma_ts_lo<1>(tmem_base + col_acc, tmem_base + col_a + (kk / 4) * 64 + (kk % 4) * 8, b_lo + kk * (2048 >> 4), hi,
+                       idesc_acc);
       };
 
       wait_or_report(k_full, 0, 202);
@@ -838,11 +847,15 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         }
       };
       auto scores = [&](uint32_t col, uint32_t a_addr, uint32_t b_addr) {  // [128 queries x 128 keys] = A B^T over D
+        // descriptors as 32-bit halves: one add per operand and instruction (the issuing thread shares its scheduler
+        // with compute warps, so its instruction count is tensor-pipe time)
+        const uint32_t a_lo = smem_desc_lo(a_addr, 16), b_lo = smem_desc_lo(b_addr, 16);
+        constexpr uint32_t hi = smem_desc_hi(1024);
+        mma_ss_lo<0>(tmem_base + col, a_lo, hi, b_lo, hi, idesc_s);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t o = (kk / 4) * 16384 + (kk % 4) * 32;
-          mma_ss(tmem_base + col, make_smem_desc(a_addr + o, 16, 1024), make_smem_desc(b_addr + o, 16, 1024), idesc_s,
-                 kk > 0);
+        for (int kk = 1; kk < D / 16; ++kk) {
+          const uint32_t o = ((kk / 4) * 16384 + (kk % 4) * 32) >> 4;
+          mma_ss_lo<1>(tmem_base + col, a_lo + o, hi, b_lo + o, hi, idesc_s);
         }
       };
       auto issue_s = [&](int g) {  // S of global step g into score buffer g & 1
@@ -890,10 +903,15 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
           }
           if (!ok) break;
           const uint32_t kb = k_base + (g % kKS) * kTileBytes;
+          {  // 16 keys per instruction; each compute group's dS sits in its own half
+            const uint32_t kb_lo = smem_desc_lo(kb, 16384), ds_col = tmem_base + kColS + (g & 1) * 128;
+            constexpr uint32_t hi = smem_desc_hi(1024);
+            if (i == 0) mma_ts_lo<0>(tmem_base + kColDQ, ds_col, kb_lo, hi, idesc_acc);
+            else mma_ts_lo<1>(tmem_base + kColDQ, ds_col, kb_lo, hi, idesc_acc);
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk)  // 16 keys per instruction; each compute group's dS sits in its own half
-            mma_ts(tmem_base + kColDQ, tmem_base + kColS + (g & 1) * 128 + (kk / 4) * 64 + (kk % 4) * 8,
-                   make_smem_desc(kb + kk * 2048, 16384, 1024), idesc_acc, !(i == 0 && kk == 0));
+            for (int kk = 1; kk < 8; ++kk)
+              mma_ts_lo<1>(tmem_base + kColDQ, ds_col + (kk / 4) * 64 + (kk % 4) * 8, kb_lo + kk * (2048 >> 4), hi, idesc_acc);
+          }
           tc_commit(&k_empty[g % kKS]);
           PROF_MARK(2);
           if (i + 2 < n) {

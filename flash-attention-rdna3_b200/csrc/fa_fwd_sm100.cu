@@ -234,21 +234,27 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       // the parity of the key tile
       auto issue_qk = [&](int t, int n, int sbuf) {
         const uint32_t qa = sq_addr + t * kTileBytes, ka = slot_addr(n);
+        // descriptors as 32-bit halves: stepping along the tile is one add per operand (the issuing thread shares its
+        // scheduler with two softmax warps, so every instruction it saves is tensor-pipe time)
+        const uint32_t q_lo = smem_desc_lo(qa, 16), k_lo = smem_desc_lo(ka, 16);
+        constexpr uint32_t hi = smem_desc_hi(1024);
+        mma_ss_lo<0>(tmem_base + sbuf * 128, q_lo, hi, k_lo, hi, idesc_qk);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk / 4) * 16384 + (kk % 4) * 32;
-          mma_ss(tmem_base + sbuf * 128, make_smem_desc(qa + off, 16, 1024), make_smem_desc(ka + off, 16, 1024),
-                 idesc_qk, kk > 0);
+        for (int kk = 1; kk < D / 16; ++kk) {
+          const uint32_t off = ((kk / 4) * 16384 + (kk % 4) * 32) >> 4;
+          mma_ss_lo<1>(tmem_base + sbuf * 128, q_lo + off, hi, k_lo + off, hi, idesc_qk);
         }
         tc_commit(&s_full[sbuf]);
       };
       auto issue_pv = [&](int t, int n, bool first, int sbuf) {
         const uint32_t va = slot_addr(n);
+        const uint32_t v_lo = smem_desc_lo(va, 16384);
+        constexpr uint32_t hi = smem_desc_hi(1024);
+        if (first) mma_ts_lo<0>(tmem_base + 256 + t * D, tmem_base + sbuf * 128, v_lo, hi, idesc_pv);
+        else mma_ts_lo<1>(tmem_base + 256 + t * D, tmem_base + sbuf * 128, v_lo, hi, idesc_pv);
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          mma_ts(tmem_base + 256 + t * D, tmem_base + sbuf * 128 + kk * 8, make_smem_desc(va + kk * 2048, 16384, 1024),
-                 idesc_pv, !(first && kk == 0));
-        }
+        for (int kk = 1; kk < 8; ++kk)
+          mma_ts_lo<1>(tmem_base + 256 + t * D, tmem_base + sbuf * 128 + kk * 8, v_lo + kk * (2048 >> 4), hi, idesc_pv);
         tc_commit(&o_ready[t]);
       };
 
