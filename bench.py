@@ -47,9 +47,9 @@ STEP_FLOPS = FWD_FLOPS + BWD_FLOPS
 KERNEL_FLOPS = {"fwd": FWD_FLOPS, "bwd_dkdv": 0.8 * BWD_FLOPS, "bwd_dq": 0.2 * BWD_FLOPS}
 DELTA_BYTES = 2 * B * H * S * D * 2 + B * H * S * 4   # reads O and dO, writes delta
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of this workload, from the committed ncu captures
-# (profiles/fwd_bwd_2x16x2048x128_causal_fp16.md). Reads match the operand sizes (every input once); most of the
-# output is still in the write-back L2 when the kernel ends, so the write counter is below the output size.
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of this workload, from ncu captures of these kernels at this
+# size (a constant, not measured per run). Reads match the operand sizes (every input once); most of the output is
+# still in the write-back L2 when the kernel ends, so the write counter is below the output size.
 NCU_TRAFFIC_BYTES = {"fwd": 52.0e6, "bwd_dkdv": 72.55e6, "bwd_dq": 71.51e6}
 
 
@@ -419,7 +419,7 @@ def gpu_arm(args):
         "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f16", "data": "synthetic",
         "config": {"workload": f"fwd+bwd causal attention {B}x{H}x{S}x{D} fp16 per GPU, seeded N(0,1) "
-                               "(BASELINE configs[1])", "l2": "512 MB flush before the fa_fwd call and before the fa_bwd call of every step",
+                               "(the configuration the metric is quoted on)", "l2": "512 MB flush before the fa_fwd call and before the fa_bwd call of every step",
                    "parallelism": f"batch x head partition over {world} GPU(s), no collective"},
         "frac_of_measured_peak": value / world / peaks["tflops"],
         "fwd_tflops": FWD_FLOPS / (statistics.mean(per_call["fwd"]) * 1e-3) / 1e12,
@@ -436,6 +436,7 @@ def gpu_arm(args):
     }
     if not args.skip_extras and world == 1:
         line["decode"] = decode_extras(device, flush, peaks)
+        line["configs"] = baseline_configs(device, flush, peaks)
         line["other_shapes"] = other_shapes(device)
         line["cpu_baseline"] = cpu_baseline()
     if sharded is not None:
@@ -597,6 +598,139 @@ def decode_extras(device, flush, peaks, iters=40, nsets=4):
     return res
 
 
+def _fp32_reference_c5(q, k, v, slopes, window_left, softcap):
+    """fp32 math attention of one packed sequence (heads first) with the modifiers of the varlen configuration,
+    written out here so that the benchmark does not depend on the test oracle: scale, tanh soft-cap, ALiBi,
+    causal + left window, softmax, P V. q (Hq, L, D), k / v (Hkv, L, D) in fp32."""
+    Hq, L, Dh = q.shape
+    group = Hq // k.shape[0]
+    kk, vv = k.repeat_interleave(group, 0), v.repeat_interleave(group, 0)
+    s = torch.matmul(q, kk.transpose(1, 2)) / math.sqrt(Dh)
+    s = softcap * torch.tanh(s / softcap)
+    pos = torch.arange(L, device=q.device)
+    dist = (pos[None, :] - pos[:, None]).abs().float()
+    s = s - slopes[:, None, None] * dist[None]
+    keep = (pos[None, :] <= pos[:, None]) & (pos[None, :] >= pos[:, None] - window_left)
+    s = s.masked_fill(~keep[None], float("-inf"))
+    return torch.matmul(torch.softmax(s, -1), vv)
+
+
+def baseline_configs(device, flush, peaks, iters=10):
+    """Every other benchmark configuration through the public Python API, each launch behind an L2 flush (median of
+    `iters`): time, algorithmic FLOPs or KV bytes, achieved rate and its fraction of the measured peak. Seeds and
+    shapes are those of tests/test_baseline_configs_gpu.py, which holds the same calls to the oracle."""
+    import fa_b200
+
+    def median_us(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(iters):
+            flush()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            fn()
+            e.record()
+            torch.cuda.synchronize()
+            times.append(s.elapsed_time(e) * 1e3)
+        return statistics.median(times)
+
+    def tensor(us, flops):
+        return {"us": us, "algorithmic_flops": flops, "tflops": flops / us / 1e6,
+                "frac_of_measured_tensor_peak": flops / us / 1e6 / peaks["tflops"]}
+
+    def hbm(us, nbytes):
+        return {"us": us, "kv_bytes": nbytes, "gbs": nbytes / us / 1e3, "frac_hbm": nbytes / us / 1e3 / peaks["hbm_gbs"],
+                "frac_hbm_nominal_8000": nbytes / us / 1e3 / 8000.0}
+
+    def randn(g, *shape, dtype=torch.float16):
+        return torch.randn(*shape, generator=g, dtype=torch.float32).to(dtype).to(device)
+
+    res = {}
+    with torch.no_grad():
+        g = torch.Generator().manual_seed(1001)
+        q, k, v = (randn(g, 1, 16, 1024, 64) for _ in range(3))
+        res["c1_fwd_1x16x1024x64_noncausal_fp16"] = tensor(median_us(lambda: fa_b200.flash_attention(q, k, v)),
+                                                            4.0 * 16 * 1024 * 1024 * 64)
+    g = torch.Generator().manual_seed(1003)
+    q, k, v, dout = (randn(g, 1, 16, 4096, 64) for _ in range(4))
+    flops = 4.0 * 16 * 4096 * 4096 * 64 / 2
+    with torch.no_grad():
+        res["c2b_fwd_1x16x4096x64_causal_fp16"] = tensor(median_us(lambda: fa_b200.flash_attention(q, k, v, causal=True)),
+                                                          flops)
+    q.requires_grad_(True), k.requires_grad_(True), v.requires_grad_(True)
+    res["c2b_fwd_bwd_1x16x4096x64_causal_fp16"] = tensor(
+        median_us(lambda: fa_b200.flash_attention(q, k, v, causal=True).backward(dout)), 3.5 * flops)
+    del q, k, v, dout
+
+    with torch.no_grad():
+        for name, seed, Bd, Hd, Sk in (("c3a_splitk_4x32x8192x128", 1004, 4, 32, 8192),
+                                       ("c3b_splitk_1x8x16384x128", 1005, 1, 8, 16384)):
+            g = torch.Generator().manual_seed(seed)
+            q = randn(g, Bd, Hd, 1, 128)
+            k, v = randn(g, Bd, Hd, Sk, 128), randn(g, Bd, Hd, Sk, 128)
+            res[name] = hbm(median_us(lambda: fa_b200.flash_attention_decode(q, k, v)), 2 * Bd * Hd * Sk * 128 * 2)
+        del q, k, v
+
+        g = torch.Generator().manual_seed(1006)
+        ctx = torch.randint(1, 16385, (4,), generator=g).to(torch.int32)
+        kc, vc = randn(g, 4096, 16, 8, 128), randn(g, 4096, 16, 8, 128)
+        table = torch.randperm(4096, generator=g).to(torch.int32).reshape(4, 1024).to(device)
+        q = randn(g, 4, 32, 128)
+        ctx_d = ctx.to(device)
+        entry = hbm(median_us(lambda: fa_b200.flash_attention_decode_paged(q, kc, vc, table, ctx_d, max_context_len=16384)),
+                    int(ctx.sum()) * 2 * 8 * 128 * 2)
+        entry["context_lens"] = ctx.tolist()
+        res["c4_paged_4x32/8_ragged_contexts_page16"] = entry
+        del kc, vc
+
+        g = torch.Generator().manual_seed(7)
+        q, k, v = (randn(g, 2, 8, 19, 128, dtype=torch.float32) for _ in range(3))
+        res["tiny_fp32_2x8x19x128"] = {"us": median_us(lambda: fa_b200.flash_attention(q, k, v))}
+
+    # packed causal + window 1024 + ALiBi + soft-cap 30, bf16, 32/8 heads
+    seed = 1007
+    while True:
+        g = torch.Generator().manual_seed(seed)
+        lengths = torch.randint(128, 4097, (8,), generator=g).tolist()
+        if sum(lengths) <= 16384:
+            break
+        seed += 1
+    T = sum(lengths)
+    q, k, v, dout = (randn(g, T, h, 128, dtype=torch.bfloat16) for h in (32, 8, 8, 32))
+    cu = torch.tensor([0] + list(torch.tensor(lengths).cumsum(0)), dtype=torch.int32, device=device)
+    slopes = fa_b200.alibi_slopes(32, device=device)
+    pairs = sum(L * (L + 1) // 2 if L <= 1024 else 1024 * 1025 // 2 + (L - 1024) * 1024 for L in lengths)
+    flops = 4.0 * 32 * 128 * pairs
+
+    def c5():
+        return fa_b200.flash_attention_varlen(q, k, v, cu, cu, max(lengths), max(lengths), causal=True,
+                                              window_size=(1023, 0), softcap=30.0, alibi_slopes=slopes)
+
+    with torch.no_grad():
+        entry = tensor(median_us(c5), flops)
+        # worst absolute error of O against fp32 math attention (true fp32 matmuls), longest sequence
+        old_tf32 = torch.backends.cuda.matmul.allow_tf32
+        torch.backends.cuda.matmul.allow_tf32 = False
+        b = max(range(8), key=lambda i: lengths[i])
+        sl = slice(int(cu[b]), int(cu[b]) + lengths[b])
+        ref = _fp32_reference_c5(q[sl].float().transpose(0, 1), k[sl].float().transpose(0, 1),
+                                 v[sl].float().transpose(0, 1), slopes, 1023, 30.0)
+        got = c5()[sl].float().transpose(0, 1)
+        entry["max_abs_err_o_vs_fp32_longest_sequence"] = float((got - ref).abs().max())
+        entry["max_abs_o"] = float(ref.abs().max())
+        torch.backends.cuda.matmul.allow_tf32 = old_tf32
+        entry["lengths"] = lengths
+        res["c5_fwd_varlen_8seq_32/8x128_window1024_alibi_softcap30_bf16"] = entry
+    q.requires_grad_(True), k.requires_grad_(True), v.requires_grad_(True)
+    res["c5_fwd_bwd_varlen_8seq_32/8x128_window1024_alibi_softcap30_bf16"] = tensor(
+        median_us(lambda: c5().backward(dout)), 3.5 * flops)
+    res["note"] = ("public Python API, every launch behind a 512 MB L2 flush, median of %d; FLOPs count visible "
+                   "(query, key) pairs only; KV bytes are read once per kv head" % iters)
+    return res
+
+
 def other_shapes(device, tokens=2048, batch=2, heads=16, repeats=5):
     """Forward and forward+backward times of the shapes beside the headline one, through the Python API: head dims
     the tensor-core kernels take unpadded (32, 80), the wide forward kernel (160, 256; backward on CUDA cores) and
@@ -640,6 +774,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--skip-extras", action="store_true", help="skip decode numbers and the CPU baseline")
     ap.add_argument("--decode-only", action="store_true", help="only the decode numbers (one GPU), as their own JSON line")
+    ap.add_argument("--configs", action="store_true",
+                    help="only the other benchmark configurations (one GPU), as their own JSON line")
     ap.add_argument("--other-shapes", action="store_true",
                     help="only the times of other head dims and fp32 inputs (one GPU), as their own JSON line")
     args = ap.parse_args()
@@ -650,6 +786,11 @@ def main():
         device = torch.device("cuda", 0)
         torch.cuda.set_device(0)
         print(json.dumps({"decode": decode_extras(device, Flusher(device), load_peaks())}))
+    elif args.configs:
+        import fa_b200  # noqa: F401  (fails loudly without the CUDA library)
+        device = torch.device("cuda", 0)
+        torch.cuda.set_device(0)
+        print(json.dumps({"configs": baseline_configs(device, Flusher(device), load_peaks())}))
     elif args.other_shapes:
         import fa_b200  # noqa: F401  (fails loudly without the CUDA library)
         torch.cuda.set_device(0)
