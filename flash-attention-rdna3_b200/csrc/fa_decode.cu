@@ -460,6 +460,67 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(const CombineA
   if (tid == 0 && a.lse_out != nullptr) a.lse_out[row] = (den_all == 0.f) ? kNegInf : (Ms + logf(den_all));
 }
 
+// The same merge for many partials of a narrow row (head_dim <= 128, 16 to 1024 partials): 1024 threads per output
+// row, so that 32 groups of lanes each take every 32nd partial and all partial rows of a merge of up to 32 x 8
+// partials are in flight within a few load round trips (the 256-thread form walks them eight at a time).
+constexpr int kCombineWideThreads = 1024;
+constexpr int kCombineWideMaxSplits = 1024;
+
+__global__ void __launch_bounds__(kCombineWideThreads) combine_wide_kernel(const CombineArgs a) {
+  __shared__ float w_s[kCombineWideMaxSplits];
+  __shared__ float4 red_s[32][32];
+  __shared__ float part_s[32];
+  const int tid = threadIdx.x, grp = tid / 32, lane = tid % 32;
+  const int row = blockIdx.x;
+  const float* lse_row = a.lse_partial + (int64_t)row * a.lse_row_stride;
+  const float* o_row = a.o_partial + (int64_t)row * a.o_row_stride;
+
+  const float ls = tid < a.splits ? lse_row[(int64_t)tid * a.lse_split_stride] : kNegInf;
+  float M = ls;
+  for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+  if (lane == 0) part_s[grp] = M;
+  __syncthreads();
+  M = part_s[lane];
+  for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+  const float Ms = (M == kNegInf) ? 0.f : M;
+  const float w = (ls == kNegInf) ? 0.f : expf(ls - Ms);
+  if (tid < a.splits) w_s[tid] = w;
+  float den = w;
+  for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(0xffffffffu, den, o);
+  __syncthreads();  // everyone has read part_s; the weights are in place
+  if (lane == 0) part_s[grp] = den;
+
+  const int nd4 = a.D / 4;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (lane < nd4) {
+#pragma unroll 4
+    for (int s = grp; s < a.splits; s += 32) {
+      const float ws = w_s[s];
+      if (ws == 0.f) continue;
+      const float4 v = reinterpret_cast<const float4*>(o_row + (int64_t)s * a.o_split_stride)[lane];
+      acc.x += ws * v.x;
+      acc.y += ws * v.y;
+      acc.z += ws * v.z;
+      acc.w += ws * v.w;
+    }
+  }
+  red_s[grp][lane] = acc;
+  __syncthreads();
+  float den_all = part_s[lane];
+  for (int o = 16; o > 0; o >>= 1) den_all += __shfl_xor_sync(0xffffffffu, den_all, o);
+  const float den_safe = (den_all == 0.f) ? 1.f : den_all;
+  if (tid < a.D) {
+    const float* col = reinterpret_cast<const float*>(&red_s[0][0]) + tid;  // element tid of every group's row
+    float num = 0.f;
+#pragma unroll
+    for (int g = 0; g < 32; ++g) num += col[g * 128];
+    const int i2 = row % a.n2, i1 = (row / a.n2) % a.n1, i0 = row / (a.n2 * a.n1);
+    const int64_t obase = (int64_t)i0 * a.os0 + (int64_t)i1 * a.os1 + (int64_t)i2 * a.os2;
+    store_from_float(a.out, obase + (int64_t)tid * a.osd, a.out_dtype, num / den_safe);
+  }
+  if (tid == 0 && a.lse_out != nullptr) a.lse_out[row] = (den_all == 0.f) ? kNegInf : (Ms + logf(den_all));
+}
+
 int check_launch(const char* what) {
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "%s launch failed: %s", what, cudaGetErrorString(e));
@@ -549,7 +610,10 @@ int launch_combine_internal(int rows, int D, int splits, const float* o_partial,
   if (D > kCombineMaxD || D % 4 || o_split_stride % 4 || o_row_stride % 4 ||
       (reinterpret_cast<uintptr_t>(o_partial) & 15))
     return set_error(FA_ERR_UNSUPPORTED, "combine needs head_dim <= %d, and 16-byte aligned partial rows", kCombineMaxD);
-  combine_kernel<<<rows, kCombineThreads, 0, stream>>>(a);
+  if (D <= 128 && splits >= 16 && splits <= kCombineWideMaxSplits)
+    combine_wide_kernel<<<rows, kCombineWideThreads, 0, stream>>>(a);
+  else
+    combine_kernel<<<rows, kCombineThreads, 0, stream>>>(a);
   return check_launch("combine");
 }
 

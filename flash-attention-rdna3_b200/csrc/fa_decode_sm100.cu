@@ -52,7 +52,8 @@ struct DecArgs {
   const int32_t* context_lens;
   int64_t cl_stride;
   float softmax_scale;
-  int num_partials;  // 2 * gridDim.x
+  int num_partials;  // partial slots per row: 2 * gridDim.x, or the caller's capacity when balanced
+  int balanced;      // paged: gridDim.x CTAs are dealt to the sequences in proportion to their tile counts
   float* o_partial;
   float* lse_partial;
   int* status;
@@ -84,6 +85,84 @@ __device__ __forceinline__ void rescale_o(uint32_t tO, float alpha) {
   tc_wait_st();
 }
 
+// Paged decode, balanced mode: the grid is one row of CTAs (one per SM) and every CTA works out, from the context
+// lengths alone, which sequence it serves: each sequence gets one CTA, the rest are dealt in proportion to the
+// sequences' tile counts (never more than one CTA per two tiles, never more than the partial buffer has slots for).
+// Every CTA computes the same table, so no host read-back of the context lengths and no second launch is needed.
+// Returns false for a CTA that is left over. batch <= kBalancedMaxBatch and batch <= gridDim.x (checked on the host).
+constexpr int kBalancedMaxBatch = 256;
+
+__device__ __forceinline__ int paged_tiles_of(const DecArgs& a, int b, int* ctx_out, int* pages_out) {
+  const int bs = a.block_size;
+  int ctx = a.context_lens[(int64_t)b * a.cl_stride];
+  ctx = (int)min((int64_t)max(ctx, 0), (int64_t)a.max_blocks * bs);
+  const int nblk = (ctx + bs - 1) / bs;
+  const int pages = (nblk > a.first_block) ? (nblk - a.first_block + a.block_step - 1) / a.block_step : 0;
+  *ctx_out = ctx;
+  *pages_out = pages;
+  return (pages * a.upp + a.upt - 1) / a.upt;
+}
+
+// `scratch` is shared memory nobody uses yet (the tile ring), at least 4 * (2 * kBalancedMaxBatch + 4) bytes.
+__device__ __forceinline__ bool balanced_assignment(const DecArgs& a, void* scratch, int* b_out, int* x_out, int* n_out) {
+  long long& total_s = *reinterpret_cast<long long*>(scratch);
+  int* tiles_s = reinterpret_cast<int*>(scratch) + 2;
+  int* first_s = tiles_s + kBalancedMaxBatch;
+  const int tid = threadIdx.x, G = gridDim.x, B = a.batch;
+  if (tid < B) {
+    int ctx, pages;
+    tiles_s[tid] = paged_tiles_of(a, tid, &ctx, &pages);
+  }
+  __syncthreads();
+  if (tid < 32) {
+    long long t = 0;
+    for (int i = tid; i < B; i += 32) t += tiles_s[i];
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    if (tid == 0) total_s = t;
+  }
+  __syncthreads();
+  const long long T = total_s;
+  const int spare = G - B;  // CTAs beyond the one every sequence gets
+  if (tid < B) {
+    const int tl = tiles_s[tid];
+    int n = 1 + (T > 0 ? (int)((long long)spare * tl / T) : 0);
+    n = min(n, max(1, tl / 2));
+    n = min(n, max(1, a.num_partials / 2));
+    tiles_s[tid] = n;  // from here on: CTAs of the sequence
+  }
+  __syncthreads();
+  if (tid < 32) {  // exclusive prefix sums, eight sequences per lane
+    const int per = (B + 31) / 32;
+    int sum = 0;
+    for (int i = tid * per; i < min(B, (tid + 1) * per); ++i) sum += tiles_s[i];
+    int incl = sum;
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (tid >= o) incl += v;
+    }
+    int run = incl - sum;
+    for (int i = tid * per; i < min(B, (tid + 1) * per); ++i) {
+      first_s[i] = run;
+      run += tiles_s[i];
+    }
+    if (tid == 31) first_s[B] = incl;
+  }
+  __syncthreads();
+  const int c = blockIdx.x;
+  const bool mine = c < first_s[B];
+  int lo = 0, hi = B - 1;  // last sequence whose first CTA is <= c
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) / 2;
+    if (first_s[mid] <= c) lo = mid;
+    else hi = mid - 1;
+  }
+  *b_out = lo;
+  *x_out = c - first_s[lo];
+  *n_out = tiles_s[lo];
+  __syncthreads();  // the scratch goes back to its owner
+  return mine;
+}
+
 template <typename T, int D, bool kPaged>
 __global__ void __launch_bounds__(kThreads, 1)
 decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -110,23 +189,22 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   auto wait = [&](uint64_t* bar, uint32_t parity) { return mbar_wait_limit(bar, parity, a.poll_limit); };
   // dense: one CTA row per (batch, kv head). paged: one per batch entry; a tile interleaves all kv heads
   // (row = token * heads_kv + head), which is how a page lies in memory, so a page is fetched with few large boxes.
-  const int b = kPaged ? blockIdx.y : blockIdx.y / a.heads_kv;
+  int b = kPaged ? blockIdx.y : blockIdx.y / a.heads_kv;
   const int hk = kPaged ? 0 : blockIdx.y % a.heads_kv;
+  int cta_x = blockIdx.x, ctas_b = gridDim.x;  // this CTA's index among the CTAs of its (batch[, kv head]) row
+  if (kPaged && a.balanced) {
+    if (!balanced_assignment(a, sRing, &b, &cta_x, &ctas_b)) return;  // uniform: nothing allocated yet
+  }
 
   // keys seen by this call, in local order, and this CTA's tile range
   int nkeys = a.seqlen_k, ctx = 0, nlocal_pages = 0, tiles_total;
   if (kPaged) {
-    const int bs = a.block_size;
-    ctx = a.context_lens[(int64_t)b * a.cl_stride];
-    ctx = (int)min((int64_t)max(ctx, 0), (int64_t)a.max_blocks * bs);
-    const int nblk = (ctx + bs - 1) / bs;
-    nlocal_pages = (nblk > a.first_block) ? (nblk - a.first_block + a.block_step - 1) / a.block_step : 0;
-    tiles_total = (nlocal_pages * a.upp + a.upt - 1) / a.upt;
+    tiles_total = paged_tiles_of(a, b, &ctx, &nlocal_pages);
   } else {
     tiles_total = (nkeys + 127) / 128;
   }
-  const int tiles_per_cta = (tiles_total + gridDim.x - 1) / gridDim.x;
-  const int jlo = min((int)blockIdx.x * tiles_per_cta, tiles_total);
+  const int tiles_per_cta = (tiles_total + ctas_b - 1) / ctas_b;
+  const int jlo = min(cta_x * tiles_per_cta, tiles_total);
   const int jhi = min(jlo + tiles_per_cta, tiles_total);
   const int ntiles = jhi - jlo;
 
@@ -459,7 +537,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     }
     if (warp_active && !(kWide && s == 1)) {
       tc_fence_after_sync();
-      const int part = kWide ? blockIdx.x : 2 * blockIdx.x + s;
+      const int part = kWide ? cta_x : 2 * cta_x + s;
       const int g = row / a.seqlen_q, sq = row % a.seqlen_q;
       const int h = kPaged ? row : hk * a.group + g;
       int64_t flat_o, flat_l;
@@ -498,6 +576,12 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     if (!kPaged && a.tickets != nullptr) __threadfence();  // this thread's partial is visible before the ticket is taken
   }
 
+  if (kPaged && a.balanced && cta_x == 0) {
+    // the slots of this sequence that no CTA writes must not take part in the merge: LSE = -inf
+    const int used = 2 * ctas_b, spare = a.num_partials - used;
+    for (int i = tid; i < a.heads_q * spare; i += kThreads)
+      a.lse_partial[((int64_t)b * a.heads_q + i / spare) * a.num_partials + used + i % spare] = kNegInf;
+  }
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 9) tmem_dealloc(tmem_base, 512);
@@ -615,7 +699,7 @@ int launch_kernel(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMa
   auto kern = decode_tc_kernel<T, D, kPaged>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "decode smem opt-in failed: %s", cudaGetErrorString(e));
-  kern<<<dim3(ctas, kPaged ? a.batch : a.batch * a.heads_kv), kThreads, smem, stream>>>(mq, mk, mv, mvr, a);
+  kern<<<dim3(ctas, kPaged ? (a.balanced ? 1 : a.batch) : a.batch * a.heads_kv), kThreads, smem, stream>>>(mq, mk, mv, mvr, a);
   e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "tcgen05 decode launch failed: %s", cudaGetErrorString(e));
   return 0;
@@ -826,7 +910,19 @@ int launch_paged_tc(const fa_paged_params& p, cudaStream_t stream) {
   a.lse_partial = p.lse_partial;
   a.status = p.status;
   take_fault_injection(&a);
-  rc = dispatch<true>(p.dtype, D, mq, mk, mv, mvr, a, p.num_splits / 2, stream);
+  int ctas = p.num_splits / 2;
+  if (p.balance) {
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+      return set_error(FA_ERR_DEVICE, "cannot query the SM count of the current device");
+    if (p.batch > kBalancedMaxBatch || p.batch > sms)
+      return set_error(FA_ERR_UNSUPPORTED, "balanced paged decode takes at most %d sequences (and at most one per SM)",
+                       kBalancedMaxBatch);
+    a.balanced = 1;
+    ctas = sms;
+  }
+  rc = dispatch<true>(p.dtype, D, mq, mk, mv, mvr, a, ctas, stream);
   if (rc) return rc;
   const int nrows = p.batch * p.heads_q;
   return launch_combine_internal(nrows, D, p.num_splits, p.o_partial, D, (int64_t)p.num_splits * D, p.lse_partial, 1,

@@ -87,7 +87,7 @@ class PagedParams(C.Structure):
         ("first_block", C.c_int32), ("block_step", C.c_int32),
         ("o_partial", C.c_void_p), ("lse_partial", C.c_void_p), ("lse_out", C.c_void_p),
         ("out_is_f32", C.c_int32), ("force_path", C.c_int32),
-        ("status", C.c_void_p),
+        ("status", C.c_void_p), ("balance", C.c_int32),
     ]
 
 

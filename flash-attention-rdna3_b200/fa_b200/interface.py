@@ -127,6 +127,14 @@ def _paged_splits_b200(batch, kv_heads, group, block_size, max_blocks, sm_count,
     return _fill_splits(base, min(32, max(1, tokens // 256)), sm_count)
 
 
+def _paged_balanced_slots(kv_heads, block_size, max_blocks, sm_count, max_context_len=None):
+    """Partial slots per sequence for the balanced tensor-core paged kernel: two per CTA, and a sequence never gets
+    more CTAs than half its 128-row tiles (a tile holds 128 / kv_heads tokens of all kv heads) or than there are SMs."""
+    tokens = max_blocks * block_size if max_context_len is None else min(max_blocks * block_size, max_context_len)
+    tiles = _cdiv(tokens * kv_heads, 128)
+    return 2 * max(1, min(sm_count, tiles // 2))
+
+
 def alibi_slopes(n_heads, device="cuda"):
     """Standard ALiBi per-head slopes (Press et al., 2021) as an fp32 ``(n_heads,)`` tensor
     (fa_rdna3/interface.py:136-151)."""
@@ -674,7 +682,7 @@ def flash_attention_varlen(query, key, value, cu_seqlens_q, cu_seqlens_k,
 # paged-KV decode
 # ---------------------------------------------------------------------------------------------------
 def _paged_launch(query, k_cache, v_cache, block_table, context_lens, softmax_scale, num_splits,
-                  first_block=0, block_step=1, want_lse=False, out_f32=False, force_path=0):
+                  first_block=0, block_step=1, want_lse=False, out_f32=False, force_path=0, balance=False):
     """Launch paged decode over logical blocks first_block, first_block + block_step, ...; returns
     (out, lse or None). With want_lse the output is the fp32 partial of a KV shard."""
     lib = _lib.load()
@@ -705,6 +713,7 @@ def _paged_launch(query, k_cache, v_cache, block_table, context_lens, softmax_sc
     p.out_is_f32 = int(out_f32)
     p.force_path = int(force_path)
     p.status = _status_word(query.device).data_ptr()
+    p.balance = int(bool(balance))
     if lse is not None:
         p.lse_out = lse.data_ptr()
     if num_splits > 1:
@@ -718,12 +727,13 @@ def _paged_launch(query, k_cache, v_cache, block_table, context_lens, softmax_sc
 
 @torch.library.custom_op("fa_b200::decode_paged", mutates_args=())
 def _paged_op(query: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
-              context_lens: torch.Tensor, softmax_scale: float, num_splits: int) -> torch.Tensor:
-    return _paged_launch(query, k_cache, v_cache, block_table, context_lens, softmax_scale, num_splits)[0]
+              context_lens: torch.Tensor, softmax_scale: float, num_splits: int, balance: bool = False) -> torch.Tensor:
+    return _paged_launch(query, k_cache, v_cache, block_table, context_lens, softmax_scale, num_splits,
+                         balance=balance)[0]
 
 
 @_paged_op.register_fake
-def _(query, k_cache, v_cache, block_table, context_lens, softmax_scale, num_splits):
+def _(query, k_cache, v_cache, block_table, context_lens, softmax_scale, num_splits, balance=False):
     return torch.empty_like(query)
 
 
@@ -751,17 +761,23 @@ def flash_attention_decode_paged(query, k_cache, v_cache, block_table, context_l
     batch, q_heads, head_dim = query.shape
     block_size = k_cache.shape[1]
     softmax_scale = 1.0 / math.sqrt(head_dim) if softmax_scale is None else float(softmax_scale)
+    balance = False
     if num_splits is not None:
         selected = int(num_splits)
     else:
         sm_count = torch.cuda.get_device_properties(query.device).multi_processor_count
         kv_heads = k_cache.shape[2]
         group = q_heads // kv_heads
-        selected = _paged_splits_b200(batch, kv_heads, group, block_size, block_table.shape[1], sm_count,
-                                      None if max_context_len is None else int(max_context_len),
-                                      tensor_core=_paged_tensor_core_ok(query, head_dim, q_heads, kv_heads, block_size,
-                                                                        softmax_scale))
-    return _paged_op(query, k_cache, v_cache, block_table, context_lens, softmax_scale, selected)
+        tensor_core = _paged_tensor_core_ok(query, head_dim, q_heads, kv_heads, block_size, softmax_scale)
+        bound = None if max_context_len is None else int(max_context_len)
+        selected = _paged_splits_b200(batch, kv_heads, group, block_size, block_table.shape[1], sm_count, bound,
+                                      tensor_core=tensor_core)
+        if tensor_core and selected > 1 and batch <= min(256, sm_count):
+            # One CTA per SM, dealt to the sequences on the device in proportion to their context lengths (the host
+            # only knows the bound): `selected` becomes the partial slots per sequence, two per CTA it may get.
+            balance = True
+            selected = _paged_balanced_slots(kv_heads, block_size, block_table.shape[1], sm_count, bound)
+    return _paged_op(query, k_cache, v_cache, block_table, context_lens, softmax_scale, selected, balance)
 
 
 # Dao-AILab style spellings of the two training entry points (same functions, same layouts as above).

@@ -175,6 +175,12 @@ typedef struct fa_paged_params {
   int32_t out_is_f32;       /* write out as fp32 regardless of dtype (shard partials) */
   int32_t force_path;       /* 0 = automatic; FA_PATH_TCGEN05 (needs an even num_splits >= 2) or FA_PATH_SIMT */
   int32_t* status;          /* device int32 or NULL, as in fa_decode_params */
+  int32_t balance;          /* tensor-core kernel only. 0: num_splits / 2 CTAs per sequence, each sequence cut into
+                               equal parts. 1: one CTA per SM, dealt to the sequences on the device in proportion to
+                               their (clamped) context lengths, so ragged batches keep every SM busy without a host
+                               read-back of context_lens; num_splits is then the number of partial slots per
+                               sequence in o_partial / lse_partial (2 per CTA; 2 x SM count is always enough) and
+                               batch may be at most 256 and at most the SM count. */
 } fa_paged_params;
 
 /* FP32 short-sequence attention: q, k, v, out (batch, heads, seqlen <= 32, 128), optional bias. */

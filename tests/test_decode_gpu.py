@@ -378,3 +378,43 @@ def test_paged_lost_wait_sets_the_status_word():
         fa_b200.check_status()
     assert torch.isfinite(out.float()).all()
     check_paged(q, kc, vc, table, ctx, num_splits=2)
+
+
+# ------------------------------------------------------------------------------------------ balanced paged decode
+@pytest.mark.parametrize("contexts", [[6237, 3218, 12772, 15003], [16384], [1, 16, 17, 0, 300, 5000, 31, 2048],
+                                      [0, 0, 0], [100000, 7]])
+def test_paged_balanced_ragged_batches(contexts):
+    """One CTA per SM dealt to the sequences by context length (what the public entry point uses when the
+    tensor-core kernel applies): ragged, empty, tiny and very long sequences in one batch."""
+    q, kc, vc, table, ctx = make_paged(len(contexts), 32, 8, 128, 16, contexts, seed=len(contexts))
+    check_paged(q, kc, vc, table, ctx, max_context_len=max(max(contexts), 1))
+    check_paged(q, kc, vc, table, ctx)
+
+
+@pytest.mark.parametrize("slots", [2, 4, 10, 64, 296])
+def test_paged_balanced_partial_slot_capacity(slots):
+    """The number of partial slots per sequence caps the CTAs a sequence gets; unused slots must not reach the merge
+    (the buffers start from NaN here)."""
+    from fa_b200 import _lib, interface
+
+    contexts = [3000, 40, 9000]
+    q, kc, vc, table, ctx = make_paged(3, 8, 2, 64, 16, contexts, seed=9)
+    ref, _ = oracle.paged_ref(q.cpu(), kc.cpu(), vc.cpu(), table.cpu(), ctx.cpu(), None)
+    torch.empty(3 * 8 * slots * 65 + 4096, device="cuda").fill_(float("nan"))  # poison what the allocator hands out next
+    out, _ = interface._paged_launch(q, kc, vc, table, ctx, 1.0 / 8, slots, balance=True,
+                                     force_path=_lib.FA_PATH_TCGEN05)
+    assert_close_o(out, ref, torch.float16)
+
+
+def test_paged_balanced_kv_shards_merge_to_whole():
+    from fa_b200 import _lib, interface
+
+    contexts = [5000, 333, 12000, 64]
+    q, kc, vc, table, ctx = make_paged(4, 32, 8, 128, 16, contexts, seed=21)
+    ref, _ = oracle.paged_ref(q.cpu(), kc.cpu(), vc.cpu(), table.cpu(), ctx.cpu(), None)
+    G = 4
+    parts = [interface._paged_launch(q, kc, vc, table, ctx, 1 / math.sqrt(128), 64, first_block=r, block_step=G,
+                                     want_lse=True, out_f32=True, balance=True, force_path=_lib.FA_PATH_TCGEN05)
+             for r in range(G)]
+    o, _ = oracle.combine_ref(torch.stack([p[0] for p in parts]).cpu(), torch.stack([p[1] for p in parts]).cpu())
+    assert max_abs(o, ref) <= 2e-3
