@@ -383,14 +383,47 @@ def gpu_arm(args):
     if distributed:
         dist.all_reduce(e2e_total, op=dist.ReduceOp.MAX)
     e2e_value = world * STEP_FLOPS / (float(e2e_total.item()) / args.steps * 1e-3) / 1e12
+
+    def copies_only(n_steps):
+        """The same uploads and downloads with no compute in between (one copy per tensor, the two directions on
+        their own streams): the PCIe floor of a step at this number of GPUs."""
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record(s_main)
+        s_in.wait_stream(s_main)
+        s_out.wait_stream(s_main)
+        for i in range(n_steps):
+            b = i & 1
+            with torch.cuda.stream(s_in):
+                for dst, src in zip(dev_in[b], host):
+                    dst.copy_(src, non_blocking=True)
+            with torch.cuda.stream(s_out):
+                for dst, src in zip(host_out[b], dev_in[b ^ 1]):
+                    dst.copy_(src, non_blocking=True)
+        s_main.wait_stream(s_out)
+        s_main.wait_stream(s_in)
+        end.record(s_main)
+        return start, end
+
+    copies_only(2)
+    torch.cuda.synchronize()
+    if distributed:
+        dist.barrier()
+    s, e = copies_only(args.steps)
+    torch.cuda.synchronize()
+    copy_total = torch.tensor([s.elapsed_time(e)], dtype=torch.float64, device=device)
+    if distributed:
+        dist.all_reduce(copy_total, op=dist.ReduceOp.MAX)
+    copy_ms_per_step = float(copy_total.item()) / args.steps
+    e2e_ms_per_step = float(e2e_total.item()) / args.steps
     e2e_check = float(host_out[(args.steps - 1) & 1][0].float().abs().sum())  # the results did reach the host
     if not math.isfinite(e2e_check) or e2e_check == 0.0:
         raise RuntimeError("end-to-end outputs did not arrive in host memory")
     tensor_bytes = B * H * S * D * 2
 
-    sharded = None
+    sharded, sharded_configs = None, None
     if distributed and not args.skip_extras:
         sharded = sharded_decode_extra(device, rank, world)
+        sharded_configs = sharded_config_extras(device, rank, world, flush, peaks)
 
     if rank != 0:
         if distributed:
@@ -431,7 +464,12 @@ def gpu_arm(args):
                              "device time without launch gaps, inputs warm in L2", "roofline": roofline, "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": 4 * tensor_bytes,
                 "d2h_bytes_per_step": 4 * tensor_bytes,
-                "note": "steps pipelined over three streams and two buffer sets; time = first upload to last download"},
+                "ms_per_step": e2e_ms_per_step, "copies_only_ms_per_step": copy_ms_per_step,
+                "pcie_gbs_each_way_all_gpus": world * 4 * tensor_bytes / copy_ms_per_step / 1e6,
+                "frac_of_copy_bound": copy_ms_per_step / e2e_ms_per_step,
+                "note": "steps pipelined over three streams and two buffer sets; time = first upload to last download; "
+                        "copies_only = the same host<->device copies of every rank with no compute (max over ranks): "
+                        "the ranks of one node share the host's memory and PCIe paths, which is what bounds e2e"},
         "gpu_launches": 4 * args.steps,
     }
     if not args.skip_extras and world == 1:
@@ -441,6 +479,8 @@ def gpu_arm(args):
         line["cpu_baseline"] = cpu_baseline()
     if sharded is not None:
         line["decode_kv_sharded"] = sharded
+    if sharded_configs is not None:
+        line["configs_sharded"] = sharded_configs
     print(json.dumps(line))
     if distributed:
         dist.destroy_process_group()
@@ -465,7 +505,14 @@ def sharded_decode_extra(device, rank, world, iters=20):
     pools = [(torch.randn(nblocks, bs, Hk, Dd, device=device, dtype=torch.float16),
               torch.randn(nblocks, bs, Hk, Dd, device=device, dtype=torch.float16)) for _ in range(2)]
     for kc, vc in pools:
-        fd.paged_decode_kv_sharded(q, kc, vc, table, ctx)          # checks that the ranks agree, warms up NCCL
+        got = fd.paged_decode_kv_sharded(q, kc, vc, table, ctx)    # checks that the ranks agree, warms up NCCL
+    # every rank holds the whole pool here, so the sharded result can be held against the one-GPU call before timing
+    import fa_b200
+
+    whole = fa_b200.flash_attention_decode_paged(q, pools[-1][0], pools[-1][1], table, ctx, max_context_len=ctx_len)
+    max_err = float((got.float() - whole.float()).abs().max())
+    if not max_err <= 2e-3:
+        raise RuntimeError(f"KV-sharded decode differs from the single-GPU result by {max_err}")
     torch.cuda.synchronize()
     dist.barrier()
     s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -480,8 +527,81 @@ def sharded_decode_extra(device, rank, world, iters=20):
     ms = float(t.item())
     nbytes = Bp * ctx_len * 2 * Hk * Dd * 2
     return {"us": ms * 1e3, "gbs_all_gpus": nbytes / ms / 1e6, "kv_bytes": nbytes, "n_gpus": world,
+            "max_abs_vs_single_gpu": max_err,
             "workload": "paged decode, 4 seqs x 262144 tokens, 32/8 heads, page 16, pages sharded block-cyclically",
-            "collective": "all_gather of batch*heads*(head_dim+1) floats per rank + local merge", "scaling": "strong"}
+            "collective": "the local kernels write into the gather buffer, one in-place all_gather of "
+                          "batch*heads*(head_dim+1) floats per rank, local merge", "scaling": "strong"}
+
+
+def sharded_config_extras(device, rank, world, flush, peaks, iters=10):
+    """The two benchmark configurations that partition with no exchange, as strong scaling of one fixed problem:
+    split-K decode 4x32x8192x128 by (batch, head) and the packed causal + window + ALiBi + soft-cap configuration
+    (8 sequences, 32/8 heads, bf16, forward + backward) by kv-head group. Every rank builds the whole problem from the
+    same seeds and runs its own slice; time = max over ranks (CUDA events behind an L2 flush, median of `iters`)."""
+    import torch.distributed as dist
+
+    import fa_b200
+    from fa_b200 import distributed as fd
+
+    def median_ms(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(iters):
+            flush()
+            torch.cuda._sleep(600000)   # lets the host queue the launches before the start event fires
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            fn()
+            e.record()
+            torch.cuda.synchronize()
+            times.append(s.elapsed_time(e))
+        t = torch.tensor([statistics.median(times)], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def randn(g, *shape, dtype=torch.float16):
+        return torch.randn(*shape, generator=g, dtype=torch.float32).to(dtype).to(device)
+
+    res = {}
+    # split-K decode: the 128 (batch, head) pairs are dealt to the ranks (MHA: a kv head per query head)
+    g = torch.Generator().manual_seed(1004)
+    Bd, Hd, Sk = 4, 32, 8192
+    q = randn(g, Bd, Hd, 1, 128)
+    k, v = randn(g, Bd, Hd, Sk, 128), randn(g, Bd, Hd, Sk, 128)
+    lo, hi = fd.partition_batch_heads(Bd, Hd, world, rank)
+    qs, ks, vs = (t.reshape(1, Bd * Hd, *t.shape[2:])[:, lo:hi] for t in (q, k, v))
+    with torch.no_grad():
+        ms = median_ms(lambda: fa_b200.flash_attention_decode(qs, ks, vs))
+    nbytes = 2 * Bd * Hd * Sk * 128 * 2
+    res["c3a_splitk_4x32x8192x128_by_batch_x_head"] = {
+        "us": ms * 1e3, "gbs_all_gpus": nbytes / ms / 1e6, "frac_hbm_per_gpu": nbytes / ms / 1e6 / world / peaks["hbm_gbs"]}
+    del q, k, v, qs, ks, vs
+
+    seed = 1007
+    while True:
+        g = torch.Generator().manual_seed(seed)
+        lengths = torch.randint(128, 4097, (8,), generator=g).tolist()
+        if sum(lengths) <= 16384:
+            break
+        seed += 1
+    T = sum(lengths)
+    q, k, v, dout = (randn(g, T, h, 128, dtype=torch.bfloat16) for h in (32, 8, 8, 32))
+    cu = torch.tensor([0] + list(torch.tensor(lengths).cumsum(0)), dtype=torch.int32, device=device)
+    slopes = fa_b200.alibi_slopes(32, device=device)
+    per = 8 // world                      # kv heads per rank (world is 2, 4 or 8)
+    kvs, qsl = slice(rank * per, (rank + 1) * per), slice(rank * per * 4, (rank + 1) * per * 4)
+    ql, kl, vl, dl = (t[:, sl].contiguous() for t, sl in ((q, qsl), (k, kvs), (v, kvs), (dout, qsl)))
+    ql.requires_grad_(True), kl.requires_grad_(True), vl.requires_grad_(True)
+    ms = median_ms(lambda: fa_b200.flash_attention_varlen(ql, kl, vl, cu, cu, max(lengths), max(lengths), causal=True,
+                                                          window_size=(1023, 0), softcap=30.0,
+                                                          alibi_slopes=slopes[qsl]).backward(dl))
+    pairs = sum(L * (L + 1) // 2 if L <= 1024 else 1024 * 1025 // 2 + (L - 1024) * 1024 for L in lengths)
+    flops = 3.5 * 4.0 * 32 * 128 * pairs
+    res["c5_fwd_bwd_varlen_by_kv_head"] = {"us": ms * 1e3, "tflops_all_gpus": flops / ms / 1e9}
+    res["note"] = "strong scaling of one fixed problem; no collective on the data path; time = max over ranks"
+    return res
 
 
 def decode_extras(device, flush, peaks, iters=40, nsets=4):

@@ -7,10 +7,12 @@ The reference is single-GPU (no communication code anywhere in fa_rdna3); two mo
 
 2. KV-sharded long-context paged decode: rank r owns the pages of logical blocks r, r + G, r + 2G, ...
    of every sequence (block-cyclic, so ragged context lengths stay balanced), holds the whole query, runs
-   the paged kernel over its blocks only and produces a partial ``(O_r fp32, LSE_r)``. One all-gather of
-   ``batch * heads * (head_dim + 1)`` floats per rank brings the partials into local memory and the
-   LSE-weighted merge (``fa_combine``, the rule of fa_rdna3/kernels/decode.py:101-122) runs locally on
-   every rank. Shards without keys contribute ``LSE = -inf`` and are ignored by the merge.
+   the paged kernel over its blocks only and produces a partial ``(O_r fp32, LSE_r)``, written by the kernel
+   straight into this rank's slot of the gather buffer. One in-place all-gather of ``batch * heads *
+   (head_dim + 1)`` floats per rank brings the partials into local memory and the LSE-weighted merge
+   (``fa_combine``, the rule of fa_rdna3/kernels/decode.py:101-122) reads the gathered slots where they lie, on
+   every rank: two kernels of the local decode, one collective, one merge kernel, no copies in between.
+   Shards without keys contribute ``LSE = -inf`` and are ignored by the merge.
 
 The collective only ever reads local memory: partials are gathered by NCCL first and merged afterwards.
 """
@@ -20,7 +22,8 @@ import math
 import torch
 
 from . import _lib
-from .interface import _DTYPE_CODE, _paged_launch, _paged_splits_b200, _paged_tensor_core_ok, _stream
+from .interface import (_DTYPE_CODE, _paged_balanced_slots, _paged_launch, _paged_splits_b200,
+                        _paged_tensor_core_ok, _stream)
 from ._validation import validate_inference_only, validate_paged_inputs, validate_softmax_scale
 
 
@@ -50,18 +53,31 @@ def shard_dense_by_heads(query, key, value, world_size, rank):
 
 
 def _merge_partials_cuda(gathered_o, gathered_lse, out_dtype):
-    """gathered_o (G, rows, D) fp32, gathered_lse (G, rows) fp32, contiguous, on the GPU."""
+    """gathered_o (G, rows, D) fp32, gathered_lse (G, rows) fp32 on the GPU; rows and the D elements of a row are
+    contiguous, the stride between shards is free (the two may be views of one gather buffer)."""
     lib = _lib.load()
     G, rows, D = gathered_o.shape
     out = torch.empty(rows, D, dtype=out_dtype, device=gathered_o.device)
     p = _lib.CombineParams()
     p.out_dtype, p.rows, p.head_dim, p.num_splits = _DTYPE_CODE[out_dtype], rows, D, G
-    p.o_partial, p.o_split_stride, p.o_row_stride = gathered_o.data_ptr(), rows * D, D
-    p.lse_partial, p.lse_split_stride, p.lse_row_stride = gathered_lse.data_ptr(), rows, 1
+    p.o_partial, p.o_split_stride, p.o_row_stride = gathered_o.data_ptr(), gathered_o.stride(0), gathered_o.stride(1)
+    p.lse_partial, p.lse_split_stride, p.lse_row_stride = (gathered_lse.data_ptr(), gathered_lse.stride(0),
+                                                           gathered_lse.stride(1))
     p.out, p.out_row_stride = out.data_ptr(), D
     with torch.cuda.device(out.device):
         _lib.check(lib.fa_combine(C.byref(p), _stream(out.device)))
     return out
+
+
+def _gather_buffer(world, rows, head_dim, device):
+    """One buffer for the all-gather: shard r's slot holds its (rows, head_dim) partial followed by its rows LSEs,
+    padded to a multiple of four floats so that every slot starts 16-byte aligned. Returns (flat, o, lse) where o is
+    the (world, rows, head_dim) view and lse the (world, rows) view of the same memory."""
+    slot = -(-(rows * (head_dim + 1)) // 4) * 4
+    flat = torch.empty((world, slot), dtype=torch.float32, device=device)
+    o = flat[:, :rows * head_dim].view(world, rows, head_dim)
+    lse = flat[:, rows * head_dim:rows * (head_dim + 1)]
+    return flat, o, lse
 
 
 def paged_decode_kv_sharded(query, k_cache, v_cache, block_table, context_lens, softmax_scale=None, *,
@@ -96,25 +112,31 @@ def paged_decode_kv_sharded(query, k_cache, v_cache, block_table, context_lens, 
         if any(m != meta for m in all_meta):
             raise ValueError(f"ranks disagree on the decode problem: {all_meta}")
 
+    rows = batch * q_heads
+    flat, g_o, g_lse = _gather_buffer(world, rows, head_dim, query.device)
     if _local_partial is None:
         sm_count = torch.cuda.get_device_properties(query.device).multi_processor_count
         capacity = block_table.shape[1] * k_cache.shape[1]
         local_ctx = -(-(capacity if max_context_len is None else min(capacity, int(max_context_len))) // world)
         kv_heads = k_cache.shape[2]
-        splits = int(num_splits) if num_splits is not None else _paged_splits_b200(
-            batch, kv_heads, q_heads // kv_heads, k_cache.shape[1], block_table.shape[1], sm_count, local_ctx,
-            tensor_core=_paged_tensor_core_ok(query, head_dim, q_heads, kv_heads, k_cache.shape[1], scale))
-        o_r, lse_r = _paged_launch(query, k_cache, v_cache, block_table, context_lens, scale, splits,
-                                   first_block=rank, block_step=world, want_lse=True, out_f32=True)
+        tensor_core = _paged_tensor_core_ok(query, head_dim, q_heads, kv_heads, k_cache.shape[1], scale)
+        balance = False
+        if num_splits is not None:
+            splits = int(num_splits)
+        else:
+            splits = _paged_splits_b200(batch, kv_heads, q_heads // kv_heads, k_cache.shape[1], block_table.shape[1],
+                                        sm_count, local_ctx, tensor_core=tensor_core)
+            if tensor_core and splits > 1 and batch <= min(256, sm_count):
+                balance = True
+                splits = _paged_balanced_slots(kv_heads, k_cache.shape[1], block_table.shape[1], sm_count, local_ctx)
+        # the local kernels write this rank's partial straight into its slot of the gather buffer
+        _paged_launch(query, k_cache, v_cache, block_table, context_lens, scale, splits, first_block=rank,
+                      block_step=world, want_lse=True, out_f32=True, balance=balance,
+                      out_buffers=(g_o[rank].view(batch, q_heads, head_dim), g_lse[rank].view(batch, q_heads)))
     else:
         o_r, lse_r = _local_partial(query, k_cache, v_cache, block_table, context_lens, scale, rank, world)
-
-    rows = batch * q_heads
-    packed = torch.cat([o_r.reshape(rows, head_dim).float(), lse_r.reshape(rows, 1).float()], dim=1).contiguous()
-    flat = torch.empty((world * rows, head_dim + 1), dtype=torch.float32, device=packed.device)
-    dist.all_gather_into_tensor(flat, packed, group=group)
-    gathered = flat.view(world, rows, head_dim + 1)
-    g_o = gathered[:, :, :head_dim].contiguous()
-    g_lse = gathered[:, :, head_dim].contiguous()
+        g_o[rank].copy_(o_r.reshape(rows, head_dim))
+        g_lse[rank].copy_(lse_r.reshape(rows))
+    dist.all_gather_into_tensor(flat.view(-1), flat[rank], group=group)   # in place: the input is this rank's slot
     merge = _merge_partials_cuda if _merge is None else _merge
     return merge(g_o, g_lse, query.dtype).reshape(batch, q_heads, head_dim)

@@ -682,17 +682,22 @@ def flash_attention_varlen(query, key, value, cu_seqlens_q, cu_seqlens_k,
 # paged-KV decode
 # ---------------------------------------------------------------------------------------------------
 def _paged_launch(query, k_cache, v_cache, block_table, context_lens, softmax_scale, num_splits,
-                  first_block=0, block_step=1, want_lse=False, out_f32=False, force_path=0, balance=False):
+                  first_block=0, block_step=1, want_lse=False, out_f32=False, force_path=0, balance=False,
+                  out_buffers=None):
     """Launch paged decode over logical blocks first_block, first_block + block_step, ...; returns
-    (out, lse or None). With want_lse the output is the fp32 partial of a KV shard."""
+    (out, lse or None). With want_lse the output is the fp32 partial of a KV shard. `out_buffers` = (out, lse)
+    makes the kernels write into existing tensors (the slots of a gather buffer) instead of new ones."""
     lib = _lib.load()
     batch, q_heads, head_dim = query.shape
     if not _vector_friendly(k_cache):
         k_cache = k_cache.contiguous()
     if not _vector_friendly(v_cache):
         v_cache = v_cache.contiguous()
-    out = torch.empty(query.shape, dtype=torch.float32 if out_f32 else query.dtype, device=query.device)
-    lse = torch.empty((batch, q_heads), dtype=torch.float32, device=query.device) if want_lse else None
+    if out_buffers is not None:
+        out, lse = out_buffers
+    else:
+        out = torch.empty(query.shape, dtype=torch.float32 if out_f32 else query.dtype, device=query.device)
+        lse = torch.empty((batch, q_heads), dtype=torch.float32, device=query.device) if want_lse else None
     p = _lib.PagedParams()
     p.dtype = _DTYPE_CODE[query.dtype]
     p.batch, p.heads_q, p.heads_kv, p.head_dim = batch, q_heads, k_cache.shape[2], head_dim
