@@ -502,8 +502,11 @@ def sharded_decode_extra(device, rank, world, iters=20):
     q = torch.randn(Bp, Hq, Dd, generator=g).half().to(device)
     table = torch.randperm(nblocks, generator=g).to(torch.int32).reshape(Bp, maxb).to(device)
     ctx = torch.full((Bp,), ctx_len, dtype=torch.int32, device=device)
-    pools = [(torch.randn(nblocks, bs, Hk, Dd, device=device, dtype=torch.float16),
-              torch.randn(nblocks, bs, Hk, Dd, device=device, dtype=torch.float16)) for _ in range(2)]
+    # the same pools on every rank (same device-side seed), so that "rank r owns blocks r, r + G, ..." describes one
+    # problem and the sharded result can be compared with the one-GPU call
+    dg = torch.Generator(device=device).manual_seed(1006)
+    pools = [(torch.randn(nblocks, bs, Hk, Dd, device=device, dtype=torch.float16, generator=dg),
+              torch.randn(nblocks, bs, Hk, Dd, device=device, dtype=torch.float16, generator=dg)) for _ in range(2)]
     for kc, vc in pools:
         got = fd.paged_decode_kv_sharded(q, kc, vc, table, ctx)    # checks that the ranks agree, warms up NCCL
     # every rank holds the whole pool here, so the sharded result can be held against the one-GPU call before timing
