@@ -1,9 +1,15 @@
 """Build libfa_b200.so (the C-ABI CUDA library) in-tree with nvcc for sm_100a.
 
-Usage: python flash-attention-rdna3_b200/build.py [--force] [--verbose]
+Usage: python flash-attention-rdna3_b200/build.py [--force] [--verbose] [--prof]
 
 Each .cu file is compiled to an object only when it or a header is newer than the object, then all
 objects are linked into fa_b200/libfa_b200.so next to the Python package that loads it.
+
+--prof builds a second library, fa_b200/libfa_b200_prof.so, with -DFA_PROF: the tensor-core forward and backward
+kernels then count, per CTA and role, the cycles spent in each phase of their loops (csrc/fa_prof.cuh) and the library
+exports fa_debug_read_prof / fa_debug_read_prof_bwd, which copy the counters to the host. It is a tuning aid: the
+product library carries none of it, and nothing loads the profiling library unless a script points
+fa_b200._lib.LIB_PATH at it.
 """
 import os
 import subprocess
@@ -31,7 +37,11 @@ def _newest_header():
     return max(os.path.getmtime(p) for p in paths)
 
 
-def build(force=False, verbose=False):
+def build(force=False, verbose=False, prof=False):
+    global OBJ, OUT
+    if prof:
+        OBJ = os.path.join(HERE, "build", "prof")
+        OUT = os.path.join(HERE, "fa_b200", "libfa_b200_prof.so")
     os.makedirs(OBJ, exist_ok=True)
     header_time = _newest_header()
     jobs = []
@@ -40,7 +50,7 @@ def build(force=False, verbose=False):
         o = os.path.join(OBJ, src.replace(".cu", ".o"))
         stale = force or not os.path.exists(o) or os.path.getmtime(o) < max(os.path.getmtime(s), header_time)
         if stale:
-            cmd = [_nvcc(), *NVCC_FLAGS, "-c", s, "-o", o]
+            cmd = [_nvcc(), *NVCC_FLAGS, *(["-DFA_PROF"] if prof else []), "-c", s, "-o", o]
             if verbose:
                 cmd.insert(1, "-Xptxas=-v")
             jobs.append((src, cmd))
@@ -67,4 +77,4 @@ def build(force=False, verbose=False):
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, prof="--prof" in sys.argv))

@@ -3,9 +3,18 @@
 #include <stdarg.h>
 #include <stdio.h>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include "fa_common.cuh"
 
 namespace fa {
+
+// NVTX range around a C entry point (host side: argument checks, tensor-map encoding, launches). Header-only NVTX:
+// costs a null check per call unless a profiler is attached.
+struct NvtxRange {
+  explicit NvtxRange(const char* name) { nvtxRangePushA(name); }
+  ~NvtxRange() { nvtxRangePop(); }
+};
 
 namespace {
 thread_local char g_error[512] = "";
@@ -124,12 +133,25 @@ int32_t fa_device_supported(int32_t device) {
 const char* fa_last_error_string(void) { return fa::g_error; }
 int32_t fa_last_path(void) { return fa::g_path; }
 
-int32_t fa_fwd(const fa_attn_params* p, void* stream) { return fa::run_fwd(p, stream, false); }
-int32_t fa_varlen_fwd(const fa_attn_params* p, void* stream) { return fa::run_fwd(p, stream, true); }
-int32_t fa_bwd(const fa_attn_params* p, void* stream) { return fa::run_bwd(p, stream, false); }
-int32_t fa_varlen_bwd(const fa_attn_params* p, void* stream) { return fa::run_bwd(p, stream, true); }
+int32_t fa_fwd(const fa_attn_params* p, void* stream) {
+  fa::NvtxRange r("fa_fwd");
+  return fa::run_fwd(p, stream, false);
+}
+int32_t fa_varlen_fwd(const fa_attn_params* p, void* stream) {
+  fa::NvtxRange r("fa_varlen_fwd");
+  return fa::run_fwd(p, stream, true);
+}
+int32_t fa_bwd(const fa_attn_params* p, void* stream) {
+  fa::NvtxRange r("fa_bwd");
+  return fa::run_bwd(p, stream, false);
+}
+int32_t fa_varlen_bwd(const fa_attn_params* p, void* stream) {
+  fa::NvtxRange r("fa_varlen_bwd");
+  return fa::run_bwd(p, stream, true);
+}
 
 int32_t fa_bwd_delta(const fa_attn_params* p, void* stream) {
+  fa::NvtxRange r("fa_bwd_delta");
   if (p == nullptr || p->out == nullptr || p->dout == nullptr || p->delta == nullptr)
     return fa::set_error(FA_ERR_INVALID_ARGUMENT, "delta needs out, dout and delta");
   if (p->batch <= 0 || p->heads_q <= 0 || p->seqlen_q <= 0 || p->head_dim <= 0)
@@ -138,6 +160,7 @@ int32_t fa_bwd_delta(const fa_attn_params* p, void* stream) {
 }
 
 int32_t fa_decode_splitk(const fa_decode_params* p, void* stream) {
+  fa::NvtxRange r("fa_decode_splitk");
   if (p == nullptr) return fa::set_error(FA_ERR_INVALID_ARGUMENT, "params is NULL");
   if (p->batch <= 0 || p->heads_q <= 0 || p->heads_kv <= 0 || p->seqlen_q <= 0 || p->seqlen_k <= 0)
     return fa::set_error(FA_ERR_INVALID_ARGUMENT, "batch, heads and sequence lengths must be positive");
@@ -147,12 +170,14 @@ int32_t fa_decode_splitk(const fa_decode_params* p, void* stream) {
 }
 
 int32_t fa_combine(const fa_combine_params* p, void* stream) {
+  fa::NvtxRange r("fa_combine");
   if (p == nullptr || p->o_partial == nullptr || p->lse_partial == nullptr || p->out == nullptr)
     return fa::set_error(FA_ERR_INVALID_ARGUMENT, "combine needs o_partial, lse_partial and out");
   return fa::launch_combine(*p, static_cast<cudaStream_t>(stream));
 }
 
 int32_t fa_decode_paged(const fa_paged_params* p, void* stream) {
+  fa::NvtxRange r("fa_decode_paged");
   if (p == nullptr) return fa::set_error(FA_ERR_INVALID_ARGUMENT, "params is NULL");
   if (p->batch <= 0 || p->heads_q <= 0 || p->heads_kv <= 0 || p->num_blocks <= 0 || p->max_blocks <= 0)
     return fa::set_error(FA_ERR_INVALID_ARGUMENT, "paged batch, heads, blocks and block table width must be positive");
@@ -198,6 +223,7 @@ void fa_test_decode_fault(uint32_t poll_limit, int32_t skip_tile) {
 }
 
 int32_t fa_tiny_fwd(const fa_tiny_params* p, void* stream) {
+  fa::NvtxRange r("fa_tiny_fwd");
   if (p == nullptr || p->q == nullptr || p->k == nullptr || p->v == nullptr || p->out == nullptr)
     return fa::set_error(FA_ERR_INVALID_ARGUMENT, "tiny forward needs q, k, v and out");
   return fa::launch_tiny(*p, static_cast<cudaStream_t>(stream));

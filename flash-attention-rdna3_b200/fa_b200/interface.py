@@ -493,6 +493,25 @@ def _vector_friendly(t):
     return all(s % 8 == 0 for s, n in zip(t.stride()[:-1], t.shape[:-1]) if n > 1)
 
 
+_copy_warned = set()
+
+
+def _rows_readable(t, what):
+    """The decode kernels read K/V rows with 16-byte loads. A cache whose layout does not allow that (inner stride
+    not 1, or rows not 16-byte aligned) is accepted, as the reference accepts any strides, but it costs a copy of the
+    whole cache on every call: say so once per call site instead of hiding it."""
+    if _vector_friendly(t):
+        return t
+    if what not in _copy_warned:
+        _copy_warned.add(what)
+        import warnings
+
+        warnings.warn(f"fa_b200: {what} is not readable with 16-byte loads (strides {tuple(t.stride())}); it is copied "
+                      "to a contiguous tensor on every call. Pass caches with unit inner stride and rows aligned to "
+                      "16 bytes to avoid the copy.", RuntimeWarning, stacklevel=3)
+    return t.contiguous()
+
+
 def _tensor_core_decode_ok(query, head_dim, rows_per_kv_head, softmax_scale):
     """Host-side mirror of the tcgen05 decode kernel's shape limits (the library re-checks strides itself)."""
     if head_dim == 256 and rows_per_kv_head < 4:  # the library keeps these on the CUDA-core kernel (faster there)
@@ -510,10 +529,8 @@ def _paged_tensor_core_ok(query, head_dim, q_heads, kv_heads, block_size, softma
 def _decode_impl(query, key, value, softmax_scale, num_splits, force_path=0):
     lib = _lib.load()
     batch, heads, seqlen_q, head_dim = query.shape
-    if not _vector_friendly(key):
-        key = key.contiguous()
-    if not _vector_friendly(value):
-        value = value.contiguous()
+    key = _rows_readable(key, "the key cache of flash_attention_decode")
+    value = _rows_readable(value, "the value cache of flash_attention_decode")
     out = torch.empty_like(query)
     p = _lib.DecodeParams()
     p.dtype = _DTYPE_CODE[query.dtype]
@@ -596,6 +613,8 @@ def _backward_varlen(dout, query, key, value, out, lse, cu_seqlens_q, cu_seqlens
     gradients."""
     lib = _lib.load()
     dout = dout.contiguous()
+    # zeros, not empty: the packed tensors may hold rows that belong to no sequence (cu_seqlens need not cover them,
+    # and out-of-range entries are clamped), which no kernel visits and whose gradients are zero by definition
     delta = torch.zeros_like(lse)
     dq, dk, dv = torch.zeros_like(query), torch.zeros_like(key), torch.zeros_like(value)
     alibi_t = None if alibi is None else _alibi_args(alibi, query)[0]
@@ -689,10 +708,8 @@ def _paged_launch(query, k_cache, v_cache, block_table, context_lens, softmax_sc
     makes the kernels write into existing tensors (the slots of a gather buffer) instead of new ones."""
     lib = _lib.load()
     batch, q_heads, head_dim = query.shape
-    if not _vector_friendly(k_cache):
-        k_cache = k_cache.contiguous()
-    if not _vector_friendly(v_cache):
-        v_cache = v_cache.contiguous()
+    k_cache = _rows_readable(k_cache, "the key cache of flash_attention_decode_paged")
+    v_cache = _rows_readable(v_cache, "the value cache of flash_attention_decode_paged")
     if out_buffers is not None:
         out, lse = out_buffers
     else:

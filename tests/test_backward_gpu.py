@@ -152,3 +152,48 @@ def test_backward_run_to_run_identical():
     a = interface._backward(dout, q, k, v, out, lse, True, 0.0884, (-1, -1), 0.0, None, None, 0.0, 0)
     b = interface._backward(dout, q, k, v, out, lse, True, 0.0884, (-1, -1), 0.0, None, None, 0.0, 0)
     assert all(torch.equal(x, y) for x, y in zip(a, b))
+
+
+# ------------------------------------------------------------------------------------------------ output canaries
+# compute-sanitizer is not available where these tests run, so stray writes are looked for the plain way: every
+# output lives in the middle of a larger buffer that starts out as NaN. After the call the guard zones on both sides
+# must still be all NaN (nothing wrote outside) and the outputs must hold no NaN (every element was written).
+def _guarded(shape, dtype, guard=4096):
+    n = 1
+    for d in shape:
+        n *= d
+    buf = torch.full((n + 2 * guard,), float("nan"), dtype=dtype, device="cuda")
+    return buf, buf[guard:guard + n].view(*shape), guard
+
+
+def _assert_guards_intact(buf, view, guard, what):
+    assert torch.isnan(buf[:guard]).all() and torch.isnan(buf[guard + view.numel():]).all(), f"{what}: guard zone written"
+    assert not torch.isnan(view.float()).any(), f"{what}: an element was left unwritten"
+
+
+@pytest.mark.parametrize("path", [1, 2])  # tensor-core kernels, CUDA-core kernels
+@pytest.mark.parametrize("B,H,Hk,Sq,Sk,D,causal", [(2, 4, 2, 200, 333, 128, False), (1, 3, 3, 257, 257, 64, True),
+                                                   (1, 2, 1, 130, 77, 80, True)])
+def test_forward_backward_write_exactly_their_outputs(path, B, H, Hk, Sq, Sk, D, causal):
+    import ctypes as C
+
+    import fa_b200
+    from fa_b200 import _lib, interface
+
+    lib = _lib.load()
+    q, k, v, dout = seeded(1, B, H, Sq, D), seeded(2, B, Hk, Sk, D), seeded(3, B, Hk, Sk, D), seeded(4, B, H, Sq, D)
+    bufs = {"out": _guarded((B, H, Sq, D), torch.float16), "lse": _guarded((B, H, Sq), torch.float32),
+            "delta": _guarded((B, H, Sq), torch.float32), "dq": _guarded((B, H, Sq, D), torch.float16),
+            "dk": _guarded((B, Hk, Sk, D), torch.float16), "dv": _guarded((B, Hk, Sk, D), torch.float16)}
+    t = {name: b[1] for name, b in bufs.items()}
+    p = interface._attn_params(q, k, v, t["out"], t["lse"], causal, 1 / math.sqrt(D), (-1, -1), 0.0, None, None, 0.0, 0,
+                               force_path=path)
+    interface._fill_backward(p, dout, t["delta"], t["dq"], t["dk"], t["dv"], False)
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    _lib.check(lib.fa_fwd(C.byref(p), stream))
+    _lib.check(lib.fa_bwd(C.byref(p), stream))
+    torch.cuda.synchronize()
+    assert lib.fa_last_path() == path
+    for name, (buf, view, guard) in bufs.items():
+        _assert_guards_intact(buf, view, guard, name)
+    fa_b200.check_status()
