@@ -42,8 +42,8 @@ B, H, S, D = 2, 16, 2048, 128
 FWD_FLOPS = 4 * B * H * S * S * D / 2          # causal: half of 4*B*H*S^2*D
 BWD_FLOPS = 2.5 * FWD_FLOPS                    # reference convention (bench/benchmark.py:123 of fa_rdna3)
 STEP_FLOPS = FWD_FLOPS + BWD_FLOPS
-# Algorithmic share of the backward matmuls: dK/dV kernel = S^T, dP^T, dV, dK (4 of 5), dQ kernel = dQ (1 of 5;
-# its recomputed S and dP are not counted).
+# Algorithmic share of the backward matmuls: dK/dV kernel = S^T, dP^T, dV, dK (4 of 5), dQ kernel = dQ (1 of 5: with
+# the dS scratch it is exactly that GEMM; without it, its recomputed S and dP are not counted).
 KERNEL_FLOPS = {"fwd": FWD_FLOPS, "bwd_dkdv": 0.8 * BWD_FLOPS, "bwd_dq": 0.2 * BWD_FLOPS}
 DELTA_BYTES = 2 * B * H * S * D * 2 + B * H * S * 4   # reads O and dO, writes delta
 
@@ -226,6 +226,8 @@ def gpu_arm(args):
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
     p = interface._attn_params(q, k, v, out, lse, True, scale, (-1, -1), 0.0, None, None, 0.0, 0)
     interface._fill_backward(p, dout, delta, dq, dk, dv, False)
+    # the dS scratch of the dense backward (dQ = dS K as one GEMM), as the public API attaches it
+    ds_scratch = interface._ds_workspace(p, device)
     sptr = C.c_void_p(stream.cuda_stream)
 
     def launch_fwd():
@@ -471,6 +473,7 @@ def gpu_arm(args):
                         "copies_only = the same host<->device copies of every rank with no compute (max over ranks): "
                         "the ranks of one node share the host's memory and PCIe paths, which is what bounds e2e"},
         "gpu_launches": 4 * args.steps,
+        "bwd_ds_scratch_bytes": int(p.ds_workspace_bytes) if ds_scratch is not None else 0,
     }
     if not args.skip_extras and world == 1:
         line["decode"] = decode_extras(device, flush, peaks)

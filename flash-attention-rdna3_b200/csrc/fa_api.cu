@@ -196,6 +196,13 @@ int64_t fa_workspace_bytes(int32_t kind, const void* params) {
         return fa::set_error(FA_ERR_INVALID_ARGUMENT, "workspace query: sizes must be positive");
       return 4 * (int64_t)p->heads_q * (p->varlen ? (int64_t)p->total_q : (int64_t)p->batch * p->seqlen_q);
     }
+    case FA_WS_BWD_DS: {
+      const fa_attn_params* p = static_cast<const fa_attn_params*>(params);
+      if (p->batch <= 0 || p->heads_q <= 0 || p->seqlen_q <= 0 || p->seqlen_k <= 0)
+        return fa::set_error(FA_ERR_INVALID_ARGUMENT, "workspace query: sizes must be positive");
+      if ((p->dtype != FA_F16 && p->dtype != FA_BF16) || p->head_dim > 128 || p->head_dim % 8) return 0;
+      return fa::bwd_ds_workspace_bytes(*p);
+    }
     case FA_WS_DECODE_O_PARTIAL:
     case FA_WS_DECODE_LSE_PARTIAL: {
       const fa_decode_params* p = static_cast<const fa_decode_params*>(params);

@@ -62,6 +62,11 @@ struct BwdArgs {
   uint64_t seed;
   int num_tiles;
   int* status;
+  // dS workspace (dense only, may be null): the dK/dV kernel stores every 128 x 128 dS^T tile it forms (16-bit,
+  // [key][query], 32 KB) at tile index ((b * heads_q + h) * ds_kt + key tile) * ds_qt + query tile, and the dQ product
+  // is then one GEMM over those tiles (bwd_dq_gemm_kernel) instead of a second pass that recomputes S and dP.
+  void* ds_ws;
+  int ds_kt, ds_qt;
 };
 
 __device__ __forceinline__ void report_timeout(int* status, int code) {
@@ -194,6 +199,17 @@ __device__ __forceinline__ void dscore_chunk(const uint32_t (&dp)[32], const flo
       dsk[e] = DType<T>::pack2(d0, d1);
     }
   }
+}
+
+// A dS^T tile in the workspace is stored as 16 blocks of 8 queries; a block holds, key after key, the 16 bytes of
+// that key's 8 values. A warp (32 consecutive keys) therefore writes 512 contiguous bytes per store, and the tile is,
+// byte for byte, the unswizzled core-matrix layout the tensor core reads an operand "across its rows" from.
+// Stores 32 consecutive queries (four blocks, 16 packed words) of one key row; dst points at the key's 16 bytes in the
+// first of the four blocks.
+__device__ __forceinline__ void store_ds32(uint8_t* dst, const uint32_t (&dsk)[16]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    *reinterpret_cast<uint4*>(dst + i * 2048) = make_uint4(dsk[4 * i], dsk[4 * i + 1], dsk[4 * i + 2], dsk[4 * i + 3]);
 }
 
 // Shared-memory plan of the dK/dV kernel; everything is dynamic so that the tiles can take (almost) all of it.
@@ -495,6 +511,12 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         if (j >= Sk) c_hi = -1;
       }
       const uint64_t sc2 = pack_f32x2(mods.scale_log2, mods.scale_log2);
+      // this thread's key row in the first of its eight query blocks of the step's dS^T tile, if there is a workspace
+      uint8_t* ds_row = nullptr;
+      if (a.ds_ws != nullptr)
+        ds_row = reinterpret_cast<uint8_t*>(a.ds_ws) +
+                 ((((int64_t)b * a.heads_q + h) * a.ds_kt + ktile) * a.ds_qt + q0 / 128) * 32768 + wg * 8 * 2048 +
+                 key_row * 16;
 
       if (!kMods) {
         // ---- phase 1: P^T = exp2(S^T * c - lse[q]) -> TMEM (16-bit, in place) and registers
@@ -527,21 +549,26 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         }
         tc_fence_after_sync();
         PROF_MARK(1);
+        uint32_t dsk0[16], dsk1[16];
         {
-          uint32_t d0[32], d1[32], dsk[16];
+          uint32_t d0[32], d1[32];
           tmem_ld32(tDP, d0);
           tc_wait_ld_regs(d0);
           tmem_ld32(tDP + 32, d1);
           const float* nd = ndelta_s + wg * 64;
-          dscore_chunk<T>(d0, nd, &pk[0], dsk);
-          tmem_st16(tDP, dsk);
+          dscore_chunk<T>(d0, nd, &pk[0], dsk0);
+          tmem_st16(tDP, dsk0);
           tc_wait_ld_regs(d1);
-          dscore_chunk<T>(d1, nd + 32, &pk[16], dsk);
-          tmem_st16(tDP + 16, dsk);
+          dscore_chunk<T>(d1, nd + 32, &pk[16], dsk1);
+          tmem_st16(tDP + 16, dsk1);
         }
         tc_wait_st();
         tc_fence_before_sync();
         mbar_arrive(ds_full);
+        if (ds_row != nullptr) {  // behind the hand-over, so the stores are off the dP -> dS -> dK chain
+          store_ds32(ds_row, dsk0);
+          store_ds32(ds_row + 4 * 2048, dsk1);
+        }
         PROF_MARK(5);
       } else {
         // ---- general path: both products at once, 32 columns per (rolled) pass
@@ -564,6 +591,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           }
           tmem_st16(tS + c * 16, pkk);
           tmem_st16(tDP + c * 16, dsk);
+          if (ds_row != nullptr) store_ds32(ds_row + c * 4 * 2048, dsk);
         }
         tc_wait_st();
         tc_fence_before_sync();
@@ -1099,6 +1127,177 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
   if (warp == 9) tmem_dealloc(tmem_base, 512);
 }
 
+// =============================================================================================
+// dQ from the dS workspace
+// =============================================================================================
+// dQ = dS K as one GEMM over the dS^T tiles the dK/dV kernel stored: no score or dP product is recomputed (8 MMAs per
+// 128 x 128 tile pair instead of 24). Persistent CTAs walk 128-query tiles of one (batch, head), longest first; per
+// key tile the producer brings the dS^T tile [key][query] (32 KB) and the K tile [key][d] into a ring, and the MMA
+// thread accumulates dQ[query][d] += dS K with BOTH operands read across their rows (M and N are the contiguous
+// directions). Two accumulators in TMEM alternate between items, so four epilogue warps write one tile out while the
+// next one accumulates. HBM-bound: reads the workspace once.
+//   warps 0-3   epilogue (thread = one query row = one TMEM lane)
+//   warp  4     TMA producer (one lane)          warp 5     MMA issuer (one lane)
+constexpr int kGemmThreads = 192;
+
+template <int D>
+struct DqGemmSmem {
+  static constexpr int kKBytes = (D / 64) * 16384;     // one 128-key K tile
+  static constexpr int kStageBytes = 32768 + kKBytes;  // dS^T tile + K tile
+  static constexpr int kStages = D == 128 ? 3 : 4;
+  static constexpr int kBytes = kStages * kStageBytes + 1024;
+};
+
+template <typename T, int D>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+bwd_dq_gemm_kernel(const __grid_constant__ CUtensorMap map_k, const BwdArgs a) {
+  using L = DqGemmSmem<D>;
+  constexpr int kStages = L::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  __shared__ uint64_t full[kStages], empty[kStages], acc_full[2], acc_empty[2];
+  __shared__ uint32_t tmem_base_s;
+  const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+  const int n_items = a.num_tiles * a.batch * a.heads_q;
+  constexpr uint32_t kCols = 2 * D;  // two accumulators
+
+  if (tid == 0) {
+    for (int i = 0; i < kStages; ++i) {
+      mbar_init(&full[i], 1);
+      mbar_init(&empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&acc_full[i], 1);
+      mbar_init(&acc_empty[i], 128);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 5) {
+    tmem_alloc(&tmem_base_s, kCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_base_s;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      tma_prefetch_desc(&map_k);
+      int g = 0;  // ring entries issued so far
+      bool ok = true;
+      for (int round = 0; ok; ++round) {
+        const int w = snake_item(round, blockIdx.x, gridDim.x);
+        if (w >= n_items) break;
+        const DqItem it = dq_item(a, w);
+        if (!it.valid || it.n_total == 0) continue;
+        const int64_t tile0 = (((int64_t)it.b * a.heads_q + it.h) * a.ds_kt) * a.ds_qt + it.q0 / 128;
+        for (int n = 0; n < it.n_total; ++n, ++g) {
+          const int st = g % kStages, kt = it.slo + n;
+          if (!mbar_wait(&empty[st], ((g / kStages) & 1) ^ 1)) {
+            report_timeout(a.status, 501);
+            ok = false;
+            break;
+          }
+          uint8_t* dst = smem + st * L::kStageBytes;
+          mbar_arrive_expect_tx(&full[st], L::kStageBytes);
+          bulk_load(dst, reinterpret_cast<const uint8_t*>(a.ds_ws) + (tile0 + (int64_t)kt * a.ds_qt) * 32768, 32768,
+                    &full[st]);
+#pragma unroll
+          for (int c = 0; c < D / 64; ++c)
+            tma_load_4d(dst + 32768 + c * 16384, &map_k, &full[st], c * 64, it.k_start + kt * 128, it.hk, it.b);
+        }
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(DType<T>::kFormat, 128, D, 1, 1);  // both operands read across their rows
+      constexpr uint32_t hi = smem_desc_hi(1024);
+      // unswizzled operand read across its rows: the leading offset is the step between core matrices along the
+      // contraction (8 keys on: 128 bytes), the stride offset the step along the rows (8 queries on: 2048 bytes)
+      constexpr uint32_t kDsLbo = 128, kDsSbo = 2048;
+      constexpr uint32_t hi_ds = smem_desc_hi_noswizzle(kDsSbo);
+      const uint32_t base = smem_u32(smem);
+      int g = 0, used = 0;
+      bool ok = true;
+      for (int round = 0; ok; ++round) {
+        const int w = snake_item(round, blockIdx.x, gridDim.x);
+        if (w >= n_items) break;
+        const DqItem it = dq_item(a, w);
+        if (!it.valid || it.n_total == 0) continue;
+        const int buf = used & 1;
+        if (!mbar_wait(&acc_empty[buf], ((used >> 1) & 1) ^ 1)) {  // the epilogue has read this accumulator out
+          report_timeout(a.status, 502);
+          break;
+        }
+        tc_fence_after_sync();
+        for (int n = 0; n < it.n_total; ++n, ++g) {
+          const int st = g % kStages;
+          if (!mbar_wait(&full[st], (g / kStages) & 1)) {
+            report_timeout(a.status, 503);
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          // dS^T: unswizzled core matrices; a step of 16 keys is 256 bytes. K: the TMA tile, as V in the forward.
+          const uint32_t ds_lo = smem_desc_lo(base + st * L::kStageBytes, kDsLbo);
+          const uint32_t k_lo = smem_desc_lo(base + st * L::kStageBytes + 32768, 16384);
+          if (n == 0) mma_ss_lo<0>(tmem_base + buf * D, ds_lo, hi_ds, k_lo, hi, idesc);
+          else mma_ss_lo<1>(tmem_base + buf * D, ds_lo, hi_ds, k_lo, hi, idesc);
+#pragma unroll
+          for (int kk = 1; kk < 8; ++kk)  // 16 keys per instruction
+            mma_ss_lo<1>(tmem_base + buf * D, ds_lo + kk * (256 >> 4), hi_ds, k_lo + kk * (2048 >> 4), hi, idesc);
+          tc_commit(&empty[st]);
+        }
+        if (!ok) break;
+        tc_commit(&acc_full[buf]);
+        ++used;
+      }
+    }
+  } else if (warp < 4) {
+    const int r = warp * 32 + lane;
+    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    int used = 0;
+    for (int round = 0;; ++round) {
+      const int w = snake_item(round, blockIdx.x, gridDim.x);
+      if (w >= n_items) break;
+      const DqItem it = dq_item(a, w);
+      if (!it.valid) continue;
+      const int i = it.q0 + r;
+      T* row_ptr = reinterpret_cast<T*>(a.dq) + (a.varlen ? 0 : (int64_t)it.b * a.dq_sb) + (int64_t)it.h * a.dq_sh +
+                   (int64_t)(it.q_start + i) * a.dq_ss;
+      const int buf = used & 1;
+      if (it.n_total > 0) {
+        if (!__all_sync(kFull, mbar_wait(&acc_full[buf], (used >> 1) & 1))) {
+          report_timeout(a.status, 504);
+          break;
+        }
+        tc_fence_after_sync();
+      }
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t o[32];
+        if (it.n_total > 0) {
+          tmem_ld32(tmem_base + lane_addr + buf * D + c * 32, o);
+          tc_wait_ld_regs(o);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) o[e] = 0u;
+        }
+        if (i < it.Sq) store_row_slice<T>(row_ptr + c * 32, o, a.softmax_scale, a.head_dim - c * 32);
+      }
+      if (it.n_total > 0) {
+        tc_fence_before_sync();
+        mbar_arrive(&acc_empty[buf]);
+        ++used;
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 5) tmem_dealloc(tmem_base, kCols);
+}
+
 // Number of SMs of the current device (cached per device).
 int sm_count() {
   static int cached[64] = {};
@@ -1138,7 +1337,21 @@ int launch_typed(const fa_attn_params& p, const BwdArgs& a0, int parts, cudaStre
     e = cudaGetLastError();
     if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "dK/dV launch failed: %s", cudaGetErrorString(e));
   }
-  if (parts & FA_BWD_DQ) {
+  if ((parts & FA_BWD_DQ) && a.ds_ws != nullptr) {
+    // the dK/dV kernel of this (or of an earlier) call left every dS^T tile in the workspace: dQ is one GEMM over them
+    CUtensorMap mk;
+    int rc = map_of(&mk, p.k, rows_k, p.heads_kv, p.k_strides, 128);
+    if (rc) return rc;
+    auto kern = bwd_dq_gemm_kernel<T, D>;
+    constexpr int smem_gemm = DqGemmSmem<D>::kBytes;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_gemm);
+    if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "backward smem opt-in failed: %s", cudaGetErrorString(e));
+    a.num_tiles = (p.seqlen_q + 127) / 128;
+    const int n_items = a.num_tiles * p.batch * p.heads_q;
+    kern<<<n_items < sm_count() ? n_items : sm_count(), kGemmThreads, smem_gemm, stream>>>(mk, a);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "dQ (workspace) launch failed: %s", cudaGetErrorString(e));
+  } else if (parts & FA_BWD_DQ) {
     CUtensorMap mq, mk, mv, mdo;
     int rc = map_of(&mq, p.q, rows_q, p.heads_q, p.q_strides, 128);
     if (!rc) rc = map_of(&mk, p.k, rows_k, p.heads_kv, p.k_strides, 128);
@@ -1186,6 +1399,14 @@ bool bwd_tcgen05_supported(const fa_attn_params& p) {
          tma_operand_ok(p.v, p.v_strides, sk) && tma_operand_ok(p.dout, p.do_strides, sq) &&
          tma_operand_ok(p.dq, p.dq_strides, sq) && tma_operand_ok(p.dk, p.dk_strides, sk) &&
          tma_operand_ok(p.dv, p.dv_strides, sk);
+}
+
+// Bytes of the dS workspace for a dense problem: one 32 KB tile per (batch, query head, key tile, query tile). Zero
+// for problems the workspace form does not take (packed sequences).
+int64_t bwd_ds_workspace_bytes(const fa_attn_params& p) {
+  if (p.varlen) return 0;
+  const int64_t tiles = (int64_t)p.batch * p.heads_q * ((p.seqlen_k + 127) / 128) * ((p.seqlen_q + 127) / 128);
+  return tiles * 32768;
 }
 
 int launch_bwd_tcgen05(const fa_attn_params& p, int parts, cudaStream_t stream) {
@@ -1237,6 +1458,18 @@ int launch_bwd_tcgen05(const fa_attn_params& p, int parts, cudaStream_t stream) 
   a.seed = p.dropout_seed;
   a.num_tiles = 0;
   a.status = p.status;
+  a.ds_ws = nullptr;
+  a.ds_kt = (p.seqlen_k + 127) / 128;
+  a.ds_qt = (p.seqlen_q + 127) / 128;
+  if (p.ds_workspace != nullptr && !p.varlen) {
+    const int64_t need = bwd_ds_workspace_bytes(p);
+    if (p.ds_workspace_bytes < need)
+      return set_error(FA_ERR_INVALID_ARGUMENT, "ds_workspace holds %lld bytes, this problem needs %lld",
+                       (long long)p.ds_workspace_bytes, (long long)need);
+    if (reinterpret_cast<uintptr_t>(p.ds_workspace) & 1023)
+      return set_error(FA_ERR_INVALID_ARGUMENT, "ds_workspace must be aligned to 1024 bytes");
+    a.ds_ws = p.ds_workspace;
+  }
   const bool mods = p.softcap > 0.f || p.bias != nullptr || p.alibi_slopes != nullptr || p.dropout_p > 0.f;
   const bool f16 = p.dtype == FA_F16;
   if (p.head_dim > 64) {

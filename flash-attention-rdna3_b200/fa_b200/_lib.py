@@ -14,6 +14,7 @@ FA_F16, FA_BF16, FA_F32 = 0, 1, 2
 FA_PATH_NONE, FA_PATH_TCGEN05, FA_PATH_SIMT = 0, 1, 2
 FA_BWD_DELTA, FA_BWD_DKDV, FA_BWD_DQ = 1, 2, 4
 FA_WS_BWD_DELTA, FA_WS_DECODE_O_PARTIAL, FA_WS_DECODE_LSE_PARTIAL, FA_WS_PAGED_O_PARTIAL, FA_WS_PAGED_LSE_PARTIAL = 1, 2, 3, 4, 5
+FA_WS_BWD_DS = 6
 ABI_VERSION = 2
 
 I64x4 = C.c_int64 * 4
@@ -44,6 +45,7 @@ class AttnParams(C.Structure):
         ("causal", C.c_int32), ("window_left", C.c_int32), ("window_right", C.c_int32),
         ("dropout_p", C.c_float), ("dropout_seed", C.c_uint64),
         ("status", C.c_void_p), ("force_path", C.c_int32), ("bwd_parts", C.c_int32),
+        ("ds_workspace", C.c_void_p), ("ds_workspace_bytes", C.c_int64),
     ]
 
 

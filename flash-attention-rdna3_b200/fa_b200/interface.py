@@ -15,6 +15,7 @@ Reference entry points mirrored here:
 """
 import ctypes as C
 import math
+import os
 from numbers import Integral
 
 import torch
@@ -307,6 +308,29 @@ def _fill_backward(p, dout, delta, dq, dk, dv, is_varlen):
     _set4(p.delta_strides, (0, delta.stride(0), delta.stride(1)) if is_varlen else delta.stride())
 
 
+# The dense backward may keep dS (16 bits per score of every query head) in a scratch buffer so that dQ becomes one
+# GEMM instead of a second pass that recomputes the scores; above this many bytes it does not (set to 0 to switch the
+# scratch form off; the result is the same either way).
+DS_WORKSPACE_LIMIT_BYTES = int(os.environ.get("FA_B200_DS_WORKSPACE_MB", "512")) << 20
+
+
+_poison_ds_workspace = False
+
+
+def _ds_workspace(p, device):
+    """Scratch for the dS form of the dense backward, or None when the problem does not take one or it would be
+    larger than DS_WORKSPACE_LIMIT_BYTES. Attached to `p`; the caller keeps the returned tensor alive."""
+    need = _lib.load().fa_workspace_bytes(_lib.FA_WS_BWD_DS, C.byref(p))
+    if need <= 0 or need > DS_WORKSPACE_LIMIT_BYTES:
+        return None
+    ws = torch.empty(need + 1024, dtype=torch.uint8, device=device)
+    if _poison_ds_workspace:
+        ws.fill_(0xFF)   # tests: every 16-bit word a NaN, so a tile that is read without having been written shows
+    base = (ws.data_ptr() + 1023) & ~1023
+    p.ds_workspace, p.ds_workspace_bytes = base, need
+    return ws
+
+
 def _backward(dout, query, key, value, out, lse, causal, softmax_scale, window, softcap, bias, alibi,
               dropout_p, dropout_seed):
     """Dense backward launch: returns (dq, dk, dv) (fa_rdna3/interface.py:202-277)."""
@@ -318,6 +342,7 @@ def _backward(dout, query, key, value, out, lse, causal, softmax_scale, window, 
     p = _attn_params(query, key, value, out, lse, causal, softmax_scale, window, softcap, bias, alibi_t,
                      dropout_p, dropout_seed, force_path=_force_path)
     _fill_backward(p, dout, delta, dq, dk, dv, False)
+    ws = _ds_workspace(p, query.device)  # noqa: F841  (kept alive until the launch below is queued)
     with torch.cuda.device(query.device):
         _lib.check(lib.fa_bwd(C.byref(p), _stream(query.device)))
     return dq, dk, dv

@@ -108,6 +108,14 @@ typedef struct fa_attn_params {
   int32_t force_path;       /* 0 = automatic, else an fa_path to force (tests) */
   int32_t bwd_parts;        /* fa_bwd only: 0 = everything, else a mask of FA_BWD_* parts to run
                                (lets a caller time or schedule the three kernels separately) */
+  /* fa_bwd, dense, tensor-core kernels only; may be NULL. Scratch of fa_workspace_bytes(FA_WS_BWD_DS, p) bytes,
+     aligned to 1024. With it the dK/dV kernel stores every 128 x 128 tile of dS it forms (16-bit) and dQ = dS K is one
+     GEMM over those tiles; without it a second kernel recomputes the scores and dP for dQ (7 tile products instead of
+     5, no scratch). Same arithmetic on the same 16-bit dS either way, same fixed summation order, no atomics. The
+     size grows with seqlen_q * seqlen_k (2 bytes per score of every query head): meant for training shapes where
+     that is affordable; the Python layer uses it up to a cap and the reference never materialises anything. */
+  void* ds_workspace;
+  int64_t ds_workspace_bytes;
 } fa_attn_params;
 
 enum fa_bwd_part { FA_BWD_DELTA = 1, FA_BWD_DKDV = 2, FA_BWD_DQ = 4 };
@@ -211,7 +219,8 @@ enum fa_workspace_kind {
   FA_WS_DECODE_O_PARTIAL = 2,   /* fa_decode_params -> o_partial (0 when num_splits == 1) */
   FA_WS_DECODE_LSE_PARTIAL = 3, /* fa_decode_params -> lse_partial */
   FA_WS_PAGED_O_PARTIAL = 4,    /* fa_paged_params  -> o_partial */
-  FA_WS_PAGED_LSE_PARTIAL = 5   /* fa_paged_params  -> lse_partial */
+  FA_WS_PAGED_LSE_PARTIAL = 5,  /* fa_paged_params  -> lse_partial */
+  FA_WS_BWD_DS = 6              /* fa_attn_params   -> ds_workspace (optional; 0 when the problem cannot use one) */
 };
 FA_API int64_t fa_workspace_bytes(int32_t kind, const void* params);
 

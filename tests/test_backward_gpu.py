@@ -197,3 +197,24 @@ def test_forward_backward_write_exactly_their_outputs(path, B, H, Hk, Sq, Sk, D,
     for name, (buf, view, guard) in bufs.items():
         _assert_guards_intact(buf, view, guard, name)
     fa_b200.check_status()
+
+
+# ------------------------------------------------------------------------------------------------ dS workspace form
+@pytest.mark.parametrize("dtype,B,H,Hk,Sq,Sk,D,opts", [
+    (torch.float16, 2, 4, 4, 512, 512, 128, dict(causal=True)),
+    (torch.bfloat16, 1, 8, 2, 300, 700, 64, dict(causal=True)),
+    (torch.float16, 1, 4, 4, 700, 300, 128, dict(causal=True)),
+    (torch.float16, 1, 4, 2, 640, 640, 128, dict(causal=True, window=(100, 0))),
+    (torch.float16, 1, 4, 4, 400, 400, 80, dict(window=(48, 48))),
+    (torch.float16, 1, 2, 2, 384, 384, 128, dict(causal=True, softcap=30.0, alibi=True)),
+    (torch.float16, 1, 2, 2, 256, 256, 64, dict(dropout_p=0.2, dropout_seed=7)),
+])
+def test_backward_with_and_without_ds_workspace(dtype, B, H, Hk, Sq, Sk, D, opts, monkeypatch):
+    """dQ from the stored dS tiles (one GEMM) and dQ from the recomputing kernel both agree with the oracle; the
+    workspace starts out as NaN, so a tile read before it was written would show."""
+    from fa_b200 import interface
+
+    monkeypatch.setattr(interface, "_poison_ds_workspace", True)
+    for limit in (1 << 30, 0):
+        monkeypatch.setattr(interface, "DS_WORKSPACE_LIMIT_BYTES", limit)
+        assert run_case(dtype, B, H, Hk, Sq, Sk, D, path="tcgen05", **opts) == "tcgen05"
