@@ -50,7 +50,7 @@ DELTA_BYTES = 2 * B * H * S * D * 2 + B * H * S * 4   # reads O and dO, writes d
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of this workload, from ncu captures of these kernels at this
 # size (a constant, not measured per run). Reads match the operand sizes (every input once); most of the output is
 # still in the write-back L2 when the kernel ends, so the write counter is below the output size.
-NCU_TRAFFIC_BYTES = {"fwd": 52.0e6, "bwd_dkdv": 72.55e6, "bwd_dq": 71.51e6}
+NCU_TRAFFIC_BYTES = {"fwd": 51.6e6, "bwd_dkdv": 206.5e6, "bwd_dq": 171.8e6}   # with the dS scratch in use
 
 
 def load_peaks():
@@ -610,7 +610,37 @@ def sharded_config_extras(device, rank, world, flush, peaks, iters=10):
     return res
 
 
-def decode_extras(device, flush, peaks, iters=40, nsets=4):
+def _splitk_entry(res, device, lib, run, run_graph, entry, sm, nsets, Bd, Hd, Sk, Dd):
+    """Split-K decode, MHA 4x32x16384x128, through the C ABI (see decode_extras)."""
+    from fa_b200 import _lib, interface
+
+    q = seeded(1004, Bd, Hd, 1, Dd).to(device)
+    out = torch.empty_like(q)
+    splits = interface._decode_splits_b200(Bd, Hd, 1, Sk, sm, tensor_core=True)
+    op = torch.empty(splits, Bd, Hd, 1, Dd, dtype=torch.float32, device=device)
+    lp = torch.empty(splits, Bd, Hd, 1, dtype=torch.float32, device=device)
+    sets, params = [], []
+    for i in range(nsets):
+        k, v = (torch.randn(Bd, Hd, Sk, Dd, device=device, dtype=torch.float16) for _ in range(2))
+        sets.append((k, v))
+        p = _lib.DecodeParams()
+        p.dtype = _lib.FA_F16
+        p.batch, p.heads_q, p.heads_kv, p.seqlen_q, p.seqlen_k, p.head_dim = Bd, Hd, Hd, 1, Sk, Dd
+        p.q, p.k, p.v, p.out = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr()
+        for f, t in ((p.q_strides, q), (p.k_strides, k), (p.v_strides, v), (p.o_strides, out)):
+            for j, st in enumerate(t.stride()):
+                f[j] = st
+        p.softmax_scale, p.num_splits = 1.0 / math.sqrt(Dd), splits
+        p.o_partial, p.lse_partial = op.data_ptr(), lp.data_ptr()
+        params.append(p)
+    ms = run(lib.fa_decode_splitk, params)
+    ms_graph = run_graph(lib.fa_decode_splitk, params)
+    nbytes = 2 * Bd * Hd * Sk * Dd * 2
+    res["splitk_4x32x16384x128"] = entry(ms, ms_graph, nbytes, splits)
+
+
+
+def decode_extras(device, flush, peaks, iters=40, nsets=4, splitk=True):
     """Split-K decode (4x32x16384x128) and paged decode (4 seqs, 32/8 heads, page 16, 16384 tokens each) through the
     C ABI: `iters` launches back to back over `nsets` different K/V sets (each set is larger than L2, so every
     launch streams its K/V from HBM); GB/s counts K and V bytes once (kv heads)."""
@@ -656,32 +686,9 @@ def decode_extras(device, flush, peaks, iters=40, nsets=4):
                 "frac_hbm_nominal_8000": nbytes / ms / 1e6 / 8000.0, "graph_replay_us": ms_graph * 1e3,
                 "num_splits": splits}
 
-    # split-K decode, MHA
     Bd, Hd, Sk, Dd = 4, 32, 16384, 128
-    q = seeded(1004, Bd, Hd, 1, Dd).to(device)
-    out = torch.empty_like(q)
-    splits = interface._decode_splits_b200(Bd, Hd, 1, Sk, sm, tensor_core=True)
-    op = torch.empty(splits, Bd, Hd, 1, Dd, dtype=torch.float32, device=device)
-    lp = torch.empty(splits, Bd, Hd, 1, dtype=torch.float32, device=device)
-    sets, params = [], []
-    for i in range(nsets):
-        k, v = (torch.randn(Bd, Hd, Sk, Dd, device=device, dtype=torch.float16) for _ in range(2))
-        sets.append((k, v))
-        p = _lib.DecodeParams()
-        p.dtype = _lib.FA_F16
-        p.batch, p.heads_q, p.heads_kv, p.seqlen_q, p.seqlen_k, p.head_dim = Bd, Hd, Hd, 1, Sk, Dd
-        p.q, p.k, p.v, p.out = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr()
-        for f, t in ((p.q_strides, q), (p.k_strides, k), (p.v_strides, v), (p.o_strides, out)):
-            for j, st in enumerate(t.stride()):
-                f[j] = st
-        p.softmax_scale, p.num_splits = 1.0 / math.sqrt(Dd), splits
-        p.o_partial, p.lse_partial = op.data_ptr(), lp.data_ptr()
-        params.append(p)
-    ms = run(lib.fa_decode_splitk, params)
-    ms_graph = run_graph(lib.fa_decode_splitk, params)
-    nbytes = 2 * Bd * Hd * Sk * Dd * 2
-    res["splitk_4x32x16384x128"] = entry(ms, ms_graph, nbytes, splits)
-    del sets, params
+    if splitk:
+        _splitk_entry(res, device, lib, run, run_graph, entry, sm, nsets, Bd, Hd, Sk, Dd)
 
     # paged decode, GQA 32/8: full contexts and the ragged contexts of the paged benchmark configuration, through the
     # balanced tensor-core kernel the public entry point uses (one CTA per SM, dealt to the sequences on the device)
@@ -910,6 +917,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--skip-extras", action="store_true", help="skip decode numbers and the CPU baseline")
     ap.add_argument("--decode-only", action="store_true", help="only the decode numbers (one GPU), as their own JSON line")
+    ap.add_argument("--paged-only", action="store_true",
+                    help="with --decode-only: only the paged entries, over one K/V set (a small case for profilers)")
     ap.add_argument("--configs", action="store_true",
                     help="only the other benchmark configurations (one GPU), as their own JSON line")
     ap.add_argument("--other-shapes", action="store_true",
@@ -921,7 +930,10 @@ def main():
         import fa_b200  # noqa: F401  (fails loudly without the CUDA library)
         device = torch.device("cuda", 0)
         torch.cuda.set_device(0)
-        print(json.dumps({"decode": decode_extras(device, Flusher(device), load_peaks())}))
+        if args.paged_only:
+            print(json.dumps({"decode": decode_extras(device, None, load_peaks(), iters=4, nsets=1, splitk=False)}))
+        else:
+            print(json.dumps({"decode": decode_extras(device, Flusher(device), load_peaks())}))
     elif args.configs:
         import fa_b200  # noqa: F401  (fails loudly without the CUDA library)
         device = torch.device("cuda", 0)
