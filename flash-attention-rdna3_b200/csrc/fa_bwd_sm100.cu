@@ -1180,6 +1180,9 @@ bwd_dq_gemm_kernel(const __grid_constant__ CUtensorMap map_k, const BwdArgs a) {
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_base_s;
+  // Launched as a programmatic dependent of the dK/dV kernel, whose tiles it reads: everything above overlaps that
+  // kernel's tail, everything below waits for it to have completed.
+  grid_dependency_wait();
 
   if (warp == 4) {
     if (lane == 0) {
@@ -1348,8 +1351,20 @@ int launch_typed(const fa_attn_params& p, const BwdArgs& a0, int parts, cudaStre
     if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "backward smem opt-in failed: %s", cudaGetErrorString(e));
     a.num_tiles = (p.seqlen_q + 127) / 128;
     const int n_items = a.num_tiles * p.batch * p.heads_q;
-    kern<<<n_items < sm_count() ? n_items : sm_count(), kGemmThreads, smem_gemm, stream>>>(mk, a);
-    e = cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(n_items < sm_count() ? n_items : sm_count());
+    cfg.blockDim = dim3(kGemmThreads);
+    cfg.dynamicSmemBytes = smem_gemm;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr = {};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    if (parts & FA_BWD_DKDV) {  // its CTAs may set themselves up while the last dK/dV CTAs drain (they wait inside)
+      cfg.attrs = &attr;
+      cfg.numAttrs = 1;
+    }
+    e = cudaLaunchKernelEx(&cfg, kern, mk, a);
+    if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "dQ (workspace) launch failed: %s", cudaGetErrorString(e));
   } else if (parts & FA_BWD_DQ) {
     CUtensorMap mq, mk, mv, mdo;

@@ -91,6 +91,12 @@ __device__ __forceinline__ void grid_launch_dependents() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
+// The other side: blocks until the grid this kernel was launched behind (with the programmatic attribute) has
+// completed and its writes are visible. Without such a launch it returns at once.
+__device__ __forceinline__ void grid_dependency_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 // ---------------------------------------------------------------------------------------------
 // TMA (tiled, 4-D, no cluster broadcast): global -> shared, completion on an mbarrier
 // ---------------------------------------------------------------------------------------------

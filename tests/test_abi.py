@@ -84,6 +84,14 @@ def test_workspace_bytes_match_what_the_python_layer_allocates():
     a.batch, a.heads_q, a.seqlen_q = 2, 16, 2048
     assert lib.fa_workspace_bytes(_lib.FA_WS_BWD_DELTA, ctypes.byref(a)) == 2 * 16 * 2048 * 4
     assert lib.fa_workspace_bytes(99, ctypes.byref(a)) == -1
+    # dS scratch of the dense backward: one 32 KB tile per (batch, query head, key tile, query tile); none for packed
+    # sequences or for dtypes / head dims the tensor-core backward does not take
+    a.dtype, a.heads_kv, a.seqlen_k, a.head_dim = _lib.FA_F16, 4, 1000, 128
+    assert lib.fa_workspace_bytes(_lib.FA_WS_BWD_DS, ctypes.byref(a)) == 2 * 16 * 16 * 8 * 32768
+    a.varlen, a.total_q = 1, 4096
+    assert lib.fa_workspace_bytes(_lib.FA_WS_BWD_DS, ctypes.byref(a)) == 0
+    a.varlen, a.dtype = 0, _lib.FA_F32
+    assert lib.fa_workspace_bytes(_lib.FA_WS_BWD_DS, ctypes.byref(a)) == 0
 
 
 def test_library_sources_call_no_allocator():
