@@ -1,6 +1,6 @@
 """Build libfa_b200.so (the C-ABI CUDA library) in-tree with nvcc for sm_100a.
 
-Usage: python flash-attention-rdna3_b200/build.py [--force] [--verbose] [--prof]
+Usage: python flash-attention-rdna3_b200/build.py [--force] [--verbose] [--prof] [--debug-bounds]
 
 Each .cu file is compiled to an object only when it or a header is newer than the object, then all
 objects are linked into fa_b200/libfa_b200.so next to the Python package that loads it.
@@ -10,6 +10,11 @@ kernels then count, per CTA and role, the cycles spent in each phase of their lo
 exports fa_debug_read_prof / fa_debug_read_prof_bwd, which copy the counters to the host. It is a tuning aid: the
 product library carries none of it, and nothing loads the profiling library unless a script points
 fa_b200._lib.LIB_PATH at it.
+
+--debug-bounds builds fa_b200/libfa_b200_debug.so with -DFA_DEBUG_BOUNDS: every tiled TMA load checks its coordinates
+and destination (alignment of the innermost coordinate, no negative head / batch coordinate) before it is issued,
+prints a violation and skips the copy (csrc/fa_sm100.cuh). compute-sanitizer is not available everywhere these kernels
+are developed; this is the substitute for the one class of mistake that faults the GPU instead of giving wrong numbers.
 """
 import os
 import subprocess
@@ -37,11 +42,14 @@ def _newest_header():
     return max(os.path.getmtime(p) for p in paths)
 
 
-def build(force=False, verbose=False, prof=False):
+def build(force=False, verbose=False, prof=False, debug_bounds=False):
     global OBJ, OUT
     if prof:
         OBJ = os.path.join(HERE, "build", "prof")
         OUT = os.path.join(HERE, "fa_b200", "libfa_b200_prof.so")
+    if debug_bounds:
+        OBJ = os.path.join(HERE, "build", "debug")
+        OUT = os.path.join(HERE, "fa_b200", "libfa_b200_debug.so")
     os.makedirs(OBJ, exist_ok=True)
     header_time = _newest_header()
     jobs = []
@@ -50,7 +58,8 @@ def build(force=False, verbose=False, prof=False):
         o = os.path.join(OBJ, src.replace(".cu", ".o"))
         stale = force or not os.path.exists(o) or os.path.getmtime(o) < max(os.path.getmtime(s), header_time)
         if stale:
-            cmd = [_nvcc(), *NVCC_FLAGS, *(["-DFA_PROF"] if prof else []), "-c", s, "-o", o]
+            cmd = [_nvcc(), *NVCC_FLAGS, *(["-DFA_PROF"] if prof else []),
+                   *(["-DFA_DEBUG_BOUNDS"] if debug_bounds else []), "-c", s, "-o", o]
             if verbose:
                 cmd.insert(1, "-Xptxas=-v")
             jobs.append((src, cmd))
@@ -77,4 +86,5 @@ def build(force=False, verbose=False, prof=False):
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, prof="--prof" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, prof="--prof" in sys.argv,
+                debug_bounds="--debug-bounds" in sys.argv))

@@ -9,6 +9,9 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#ifdef FA_DEBUG_BOUNDS
+#include <stdio.h>
+#endif
 
 namespace fa {
 
@@ -100,8 +103,20 @@ __device__ __forceinline__ void grid_dependency_wait() {
 // ---------------------------------------------------------------------------------------------
 // TMA (tiled, 4-D, no cluster broadcast): global -> shared, completion on an mbarrier
 // ---------------------------------------------------------------------------------------------
+// With -DFA_DEBUG_BOUNDS (build.py --debug-bounds) every tiled load first checks what the hardware does not check
+// before it faults: the innermost coordinate must be a multiple of 16 bytes (8 elements of the 16-bit operands these
+// kernels load), the destination 128-byte aligned, the other coordinates not below the negative of a tile. A violation
+// is printed and the copy skipped, so the bounded wait on its barrier runs out and the status word reports it; no
+// illegal instruction reaches the GPU.
 __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0,
                                             int c1, int c2, int c3) {
+#ifdef FA_DEBUG_BOUNDS
+  if ((c0 & 7) || c0 < 0 || (smem_u32(smem_dst) & 127) || c1 < -128 || c2 < 0 || c3 < 0) {
+    printf("fa_b200 debug: TMA load refused: coords (%d, %d, %d, %d), smem offset %u, block (%d, %d)\n", c0, c1, c2, c3,
+           smem_u32(smem_dst), (int)blockIdx.x, (int)blockIdx.y);
+    return;
+  }
+#endif
   asm volatile(
       "cp.async.bulk.tensor.4d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
       ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1),
