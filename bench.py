@@ -36,6 +36,7 @@ sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.join(ROOT, "flash-attention-rdna3_b200"))
 
 import torch
+import torch.nn.functional as F
 
 METRIC = "fwd/bwd TFLOP/s (% tcgen05 peak) 2x16x2048x128 causal; decode KV GB/s (% HBM)"
 B, H, S, D = 2, 16, 2048, 128
@@ -795,6 +796,30 @@ def baseline_configs(device, flush, peaks, iters=10):
         q, k, v = (randn(g, 1, 16, 1024, 64) for _ in range(3))
         res["c1_fwd_1x16x1024x64_noncausal_fp16"] = tensor(median_us(lambda: fa_b200.flash_attention(q, k, v)),
                                                             4.0 * 16 * 1024 * 1024 * 64)
+        # the ComfyUI tensor layout, (batch, tokens, heads * head_dim), through the model-patch adapter: the shapes
+        # of the reference's bench/benchmark.py:43-89 (self-attention and cross-attention over 77 prompt tokens)
+        from fa_b200.comfyui import ComfyUIAttentionOverride
+
+        def no_fallback(*args, **kwargs):
+            raise RuntimeError("the ComfyUI adapter fell back in the benchmark")
+
+        override = ComfyUIAttentionOverride()
+        g = torch.Generator().manual_seed(1002)
+        for tokens_k in (77, 4096):
+            q, k, v = randn(g, 2, 4096, 8 * 64), randn(g, 2, tokens_k, 8 * 64), randn(g, 2, tokens_k, 8 * 64)
+            entry = tensor(median_us(lambda: override(no_fallback, q, k, v, 8)), 4.0 * 2 * 8 * 4096 * tokens_k * 64)
+
+            def heads_of(t):
+                return t.view(2, t.shape[1], 8, 64).transpose(1, 2)
+
+            entry["torch_sdpa_us"] = median_us(
+                lambda: F.scaled_dot_product_attention(heads_of(q), heads_of(k), heads_of(v)).transpose(1, 2).reshape(
+                    2, 4096, 512))
+            want = F.scaled_dot_product_attention(heads_of(q).float(), heads_of(k).float(), heads_of(v).float())
+            got = override(no_fallback, q, k, v, 8)
+            entry["max_abs_err_vs_fp32"] = float((heads_of(got).float() - want).abs().max())
+            res["comfyui_layout_2x4096x(8x64)_keys%d_fp16" % tokens_k] = entry
+        del q, k, v, want, got
     g = torch.Generator().manual_seed(1003)
     q, k, v, dout = (randn(g, 1, 16, 4096, 64) for _ in range(4))
     flops = 4.0 * 16 * 4096 * 4096 * 64 / 2
