@@ -98,13 +98,15 @@ int run_bwd(const fa_attn_params* p, void* stream, bool varlen) {
     if (rc) return rc;
   }
   if (!(parts & (FA_BWD_DKDV | FA_BWD_DQ))) return 0;
-  const bool tc_ok = bwd_tcgen05_supported(*p);
+  const bool wide_ok = bwd_wide_supported(*p);  // head dims above 128: dense problems that bring a workspace
+  const bool tc_ok = wide_ok || bwd_tcgen05_supported(*p);
   if (p->force_path == FA_PATH_TCGEN05 && !tc_ok)
     return set_error(FA_ERR_UNSUPPORTED, "the tcgen05 backward needs fp16/bf16, a head_dim that is a multiple of 8 up to "
-                                         "128, unit inner strides and 16-byte aligned rows");
+                                         "128 (up to 256 for dense problems with a ds_workspace), unit inner strides and "
+                                         "16-byte aligned rows");
   if (tc_ok && p->force_path != FA_PATH_SIMT) {
     set_path(FA_PATH_TCGEN05);
-    return launch_bwd_tcgen05(*p, parts, s);
+    return wide_ok ? launch_bwd_wide(*p, parts, s) : launch_bwd_tcgen05(*p, parts, s);
   }
   set_path(FA_PATH_SIMT);
   return launch_bwd_simt(*p, parts, s);
@@ -200,8 +202,8 @@ int64_t fa_workspace_bytes(int32_t kind, const void* params) {
       const fa_attn_params* p = static_cast<const fa_attn_params*>(params);
       if (p->batch <= 0 || p->heads_q <= 0 || p->seqlen_q <= 0 || p->seqlen_k <= 0)
         return fa::set_error(FA_ERR_INVALID_ARGUMENT, "workspace query: sizes must be positive");
-      if ((p->dtype != FA_F16 && p->dtype != FA_BF16) || p->head_dim > 128 || p->head_dim % 8) return 0;
-      return fa::bwd_ds_workspace_bytes(*p);
+      if ((p->dtype != FA_F16 && p->dtype != FA_BF16) || p->head_dim > 256 || p->head_dim % 8) return 0;
+      return p->head_dim > 128 ? fa::bwd_wide_workspace_bytes(*p) : fa::bwd_ds_workspace_bytes(*p);
     }
     case FA_WS_DECODE_O_PARTIAL:
     case FA_WS_DECODE_LSE_PARTIAL: {

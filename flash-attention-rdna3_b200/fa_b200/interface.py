@@ -312,6 +312,9 @@ def _fill_backward(p, dout, delta, dq, dk, dv, is_varlen):
 # GEMM instead of a second pass that recomputes the scores; above this many bytes it does not (set to 0 to switch the
 # scratch form off; the result is the same either way).
 DS_WORKSPACE_LIMIT_BYTES = int(os.environ.get("FA_B200_DS_WORKSPACE_MB", "512")) << 20
+# Head dims above 128 have no tensor-core backward without the scratch (it then holds P and dS, 4 bytes per score), and
+# the CUDA-core kernels are 50 times slower: the limit is higher, and a batch that does not fit is taken in pieces.
+DS_WORKSPACE_WIDE_LIMIT_BYTES = int(os.environ.get("FA_B200_DS_WORKSPACE_WIDE_MB", "4096")) << 20
 
 
 _poison_ds_workspace = False
@@ -319,9 +322,10 @@ _poison_ds_workspace = False
 
 def _ds_workspace(p, device):
     """Scratch for the dS form of the dense backward, or None when the problem does not take one or it would be
-    larger than DS_WORKSPACE_LIMIT_BYTES. Attached to `p`; the caller keeps the returned tensor alive."""
+    larger than the limit for its head dim. Attached to `p`; the caller keeps the returned tensor alive."""
     need = _lib.load().fa_workspace_bytes(_lib.FA_WS_BWD_DS, C.byref(p))
-    if need <= 0 or need > DS_WORKSPACE_LIMIT_BYTES:
+    limit = DS_WORKSPACE_WIDE_LIMIT_BYTES if p.head_dim > 128 else DS_WORKSPACE_LIMIT_BYTES
+    if need <= 0 or need > limit:
         return None
     ws = torch.empty(need + 1024, dtype=torch.uint8, device=device)
     if _poison_ds_workspace:
@@ -329,6 +333,21 @@ def _ds_workspace(p, device):
     base = (ws.data_ptr() + 1023) & ~1023
     p.ds_workspace, p.ds_workspace_bytes = base, need
     return ws
+
+
+def _wide_batch_pieces(query, key, dropout_p):
+    """Batch ranges of one backward launch each. One range, except for 16-bit head dims above 128 whose scratch
+    (4 bytes per score of every query head) exceeds its limit: those go batch entry by batch entry, as many per launch
+    as fit. Dropout counters depend on the batch index inside a launch, so a problem with dropout is never cut."""
+    batch, heads, seqlen_q, head_dim = query.shape
+    whole = [(0, batch)]
+    if head_dim <= 128 or head_dim > 256 or query.dtype not in (torch.float16, torch.bfloat16) or dropout_p > 0.0:
+        return whole
+    per_entry = 2 * heads * (-(-seqlen_q // 128)) * (-(-key.shape[2] // 128)) * 32768
+    if per_entry * batch <= DS_WORKSPACE_WIDE_LIMIT_BYTES or per_entry > DS_WORKSPACE_WIDE_LIMIT_BYTES:
+        return whole
+    step = DS_WORKSPACE_WIDE_LIMIT_BYTES // per_entry
+    return [(b0, min(b0 + step, batch)) for b0 in range(0, batch, step)]
 
 
 def _backward(dout, query, key, value, out, lse, causal, softmax_scale, window, softcap, bias, alibi,
@@ -339,12 +358,15 @@ def _backward(dout, query, key, value, out, lse, causal, softmax_scale, window, 
     delta = torch.empty_like(lse)
     dq, dk, dv = torch.empty_like(query), torch.empty_like(key), torch.empty_like(value)
     alibi_t = None if alibi is None else _alibi_args(alibi, query)[0]
-    p = _attn_params(query, key, value, out, lse, causal, softmax_scale, window, softcap, bias, alibi_t,
-                     dropout_p, dropout_seed, force_path=_force_path)
-    _fill_backward(p, dout, delta, dq, dk, dv, False)
-    ws = _ds_workspace(p, query.device)  # noqa: F841  (kept alive until the launch below is queued)
-    with torch.cuda.device(query.device):
-        _lib.check(lib.fa_bwd(C.byref(p), _stream(query.device)))
+    for b0, b1 in _wide_batch_pieces(query, key, dropout_p):
+        sl = slice(b0, b1)
+        bias_piece = bias[sl] if (bias is not None and bias.dim() == 4 and bias.shape[0] > 1) else bias
+        p = _attn_params(query[sl], key[sl], value[sl], out[sl], lse[sl], causal, softmax_scale, window, softcap,
+                         bias_piece, alibi_t, dropout_p, dropout_seed, force_path=_force_path)
+        _fill_backward(p, dout[sl], delta[sl], dq[sl], dk[sl], dv[sl], False)
+        ws = _ds_workspace(p, query.device)  # noqa: F841  (kept alive until the launch below is queued)
+        with torch.cuda.device(query.device):
+            _lib.check(lib.fa_bwd(C.byref(p), _stream(query.device)))
     return dq, dk, dv
 
 

@@ -88,6 +88,12 @@ def test_workspace_bytes_match_what_the_python_layer_allocates():
     # sequences or for dtypes / head dims the tensor-core backward does not take
     a.dtype, a.heads_kv, a.seqlen_k, a.head_dim = _lib.FA_F16, 4, 1000, 128
     assert lib.fa_workspace_bytes(_lib.FA_WS_BWD_DS, ctypes.byref(a)) == 2 * 16 * 16 * 8 * 32768
+    # head dims above 128 up to 256 keep the P tile beside the dS tile; above 256 there is no scratch form
+    a.head_dim = 160
+    assert lib.fa_workspace_bytes(_lib.FA_WS_BWD_DS, ctypes.byref(a)) == 2 * 2 * 16 * 16 * 8 * 32768
+    a.head_dim = 512
+    assert lib.fa_workspace_bytes(_lib.FA_WS_BWD_DS, ctypes.byref(a)) == 0
+    a.head_dim = 128
     a.varlen, a.total_q = 1, 4096
     assert lib.fa_workspace_bytes(_lib.FA_WS_BWD_DS, ctypes.byref(a)) == 0
     a.varlen, a.dtype = 0, _lib.FA_F32

@@ -218,3 +218,64 @@ def test_backward_with_and_without_ds_workspace(dtype, B, H, Hk, Sq, Sk, D, opts
     for limit in (1 << 30, 0):
         monkeypatch.setattr(interface, "DS_WORKSPACE_LIMIT_BYTES", limit)
         assert run_case(dtype, B, H, Hk, Sq, Sk, D, path="tcgen05", **opts) == "tcgen05"
+
+
+# ------------------------------------------------------------------------------------- head dims above 128 (to 256)
+def _bias_with_masked_rows(H, Sq, Sk):
+    g = torch.Generator().manual_seed(11)
+    bias = torch.randn(1, H, Sq, Sk, generator=g)
+    bias[..., 5:9, :] = float("-inf")
+    bias[..., :, 100:140] = float("-inf")
+    return bias.cuda()
+
+
+@pytest.mark.parametrize("dtype,B,H,Hk,Sq,Sk,D,opts", [
+    (torch.float16, 2, 4, 4, 512, 512, 256, dict(causal=True)),
+    (torch.bfloat16, 2, 4, 4, 512, 512, 256, dict()),
+    (torch.float16, 1, 2, 2, 128, 128, 256, dict(causal=True)),
+    (torch.float16, 1, 3, 3, 200, 200, 160, dict(causal=True)),
+    (torch.bfloat16, 1, 8, 2, 300, 700, 192, dict(causal=True)),
+    (torch.float16, 1, 4, 1, 700, 300, 256, dict(causal=True)),
+    (torch.float16, 1, 2, 2, 77, 1000, 256, dict()),
+    (torch.float16, 1, 4, 2, 640, 640, 256, dict(causal=True, window=(100, 0))),
+    (torch.float16, 1, 4, 4, 400, 400, 136, dict(window=(48, 48))),
+    (torch.float16, 1, 2, 2, 384, 384, 256, dict(causal=True, softcap=30.0, alibi=True)),
+    (torch.bfloat16, 1, 4, 4, 200, 333, 224, dict(softcap=50.0, alibi=True)),
+    (torch.float16, 2, 2, 2, 256, 264, 256, dict(dropout_p=0.2, dropout_seed=7)),
+    (torch.float16, 2, 4, 4, 200, 264, 256, dict(bias="masked_rows")),
+])
+def test_backward_wide_head_dims_on_tensor_cores(dtype, B, H, Hk, Sq, Sk, D, opts, monkeypatch):
+    """Head dims in (128, 256]: scores kernel + three products over the P / dS tiles. The workspace starts out as NaN,
+    so a tile that is read without having been written would show."""
+    from fa_b200 import interface
+
+    opts = dict(opts)
+    if opts.get("bias") == "masked_rows":
+        opts["bias"] = _bias_with_masked_rows(H, Sq, Sk)
+    monkeypatch.setattr(interface, "_poison_ds_workspace", True)
+    assert run_case(dtype, B, H, Hk, Sq, Sk, D, path="tcgen05", seed=Sq + D, **opts) == "tcgen05"
+
+
+def test_backward_wide_in_batch_pieces_matches_one_launch(monkeypatch):
+    """A batch whose scratch exceeds the limit is taken entry by entry; gradients are bit-identical to one launch."""
+    from fa_b200 import interface
+
+    B, H, S, D = 3, 2, 256, 256
+    q, k, v, dout = (seeded(40 + i, B, H, S, D) for i in range(4))
+    scale = 1.0 / math.sqrt(D)
+    out, lse = interface._forward(q, k, v, True, scale, (-1, -1), 0.0, None, None, 0.0, 0)
+    with interface.force_kernel_path("tcgen05"):
+        whole = interface._backward(dout, q, k, v, out, lse, True, scale, (-1, -1), 0.0, None, None, 0.0, 0)
+        per_entry = 2 * H * 2 * 2 * 32768
+        monkeypatch.setattr(interface, "DS_WORKSPACE_WIDE_LIMIT_BYTES", per_entry)
+        assert interface._wide_batch_pieces(q, k, 0.0) == [(0, 1), (1, 2), (2, 3)]
+        pieces = interface._backward(dout, q, k, v, out, lse, True, scale, (-1, -1), 0.0, None, None, 0.0, 0)
+    for a, b in zip(whole, pieces):
+        assert torch.equal(a, b)
+
+
+def test_backward_wide_without_scratch_falls_to_cuda_cores(monkeypatch):
+    from fa_b200 import interface
+
+    monkeypatch.setattr(interface, "DS_WORKSPACE_WIDE_LIMIT_BYTES", 0)
+    assert run_case(torch.float16, 1, 2, 2, 200, 200, 256, seed=3, causal=True) == "simt"

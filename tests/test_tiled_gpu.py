@@ -252,8 +252,10 @@ def test_wide_head_dims_forward(dtype, head_dim, sq, sk, causal):
     dict(dropout_p=0.2, dropout_seed=1234),
     dict(bias=True),
 ], ids=lambda o: "+".join(sorted(o)))
-def test_wide_head_dim_modifiers(opts):
-    """Head dim 256, forward on the tensor-core kernel and backward on the CUDA-core kernels from its O and LSE."""
+@pytest.mark.parametrize("bwd_path", ["tcgen05", "simt"])
+def test_wide_head_dim_modifiers(opts, bwd_path):
+    """Head dim 256, forward on the tensor-core kernel; backward from its O and LSE on the tensor-core kernels (scores +
+    products over the P / dS tiles) and, as the cross-check, on the CUDA-core kernels."""
     from fa_b200 import interface
 
     dtype, B, H, Hk, Sq, Sk, D = torch.float16, 1, 4, 2, 260, 390, 256
@@ -270,8 +272,9 @@ def test_wide_head_dim_modifiers(opts):
     slopes = alibi_slopes_ref(H).cuda() if opts.get("alibi") else None
     out, lse = interface._forward(q, k, v, causal, scale, window, softcap, bias, slopes, p, dseed)
     assert interface.last_kernel_path() == "tcgen05"
-    dq, dk, dv = interface._backward(dout, q, k, v, out, lse, causal, scale, window, softcap, bias, slopes, p, dseed)
-    assert interface.last_kernel_path() == "simt"
+    with interface.force_kernel_path(bwd_path):
+        dq, dk, dv = interface._backward(dout, q, k, v, out, lse, causal, scale, window, softcap, bias, slopes, p, dseed)
+    assert interface.last_kernel_path() == bwd_path
     ro, rl, rdq, rdk, rdv = attention_grads_ref(
         q.cpu(), k.cpu(), v.cpu(), dout.cpu(), causal=causal, softmax_scale=scale, window=window, softcap=softcap,
         bias=None if bias is None else bias.cpu(), alibi_slopes=None if slopes is None else slopes.cpu(),
