@@ -69,21 +69,21 @@ __device__ __forceinline__ int64_t ws_tile(const BwdArgs& a, int b, int h, int k
 // 1. scores -> P and dS tiles
 // =============================================================================================
 // Persistent CTAs walk 128-query tiles of one (batch, head), longest first. Q and dO of the item (64 KB each) stay in
-// shared memory; K and V stream as half tiles (128 keys x 128 columns, 32 KB) through a ring of three slots in the
-// order K lo, K hi, V lo, V hi, each released by the commit of the eight MMAs that read it. S and dP are both double
+// shared memory; K and V stream in pieces of 64 columns (128 keys x 64 columns, 16 KB) through a ring of six slots,
+// the pieces of K first, then those of V, each released by the commit of the four MMAs that read it. S and dP are both double
 // buffered in tensor memory (4 x 128 columns), and a buffer goes back to the MMA thread as soon as the compute warps
 // hold it in registers, so the products of step g + 1 run under the elementwise work of step g.
 //   warps 0-7   compute: thread = one query row; group wg = warp / 4 owns key columns [64 wg, 64 wg + 64) of a step
 //   warp  8     TMA producer (one lane)          warp 9     MMA issuer (one lane)
 template <int D>
 struct WideSmem {
-  static constexpr int kHalves = D / 128;           // 128-column pieces of the head dim
-  static constexpr int kTileBytes = kHalves * 32768;  // Q or dO of the item
+  static constexpr int kTileBytes = (D / 64) * 16384;  // Q or dO of the item
   static constexpr int kOffQ = 0;
   static constexpr int kOffDo = kTileBytes;
   static constexpr int kOffRing = 2 * kTileBytes;
-  static constexpr int kSlots = D == 256 ? 3 : 4;
-  static constexpr int kSlotBytes = 32768;
+  static constexpr int kChunks = D / 64;               // 64-column pieces: the unit of the ring
+  static constexpr int kSlotBytes = 16384;
+  static constexpr int kSlots = (232448 - 2048 - 2 * kTileBytes) / kSlotBytes > 8 ? 8 : (232448 - 2048 - 2 * kTileBytes) / kSlotBytes;
   static constexpr int kOffBars = kOffRing + kSlots * kSlotBytes;
   static constexpr int kNumBars = 10 + 2 * kSlots;
   static constexpr int kOffTmemPtr = kOffBars + kNumBars * 8;
@@ -113,7 +113,7 @@ bwd_wide_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
                        const BwdArgs a) {
   using L = WideSmem<D>;
-  constexpr int kSlots = L::kSlots, kHalves = L::kHalves;
+  constexpr int kSlots = L::kSlots, kChunks = L::kChunks;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem + L::kOffQ;
@@ -176,7 +176,7 @@ bwd_wide_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         for (int n = 0; n < it.n && ok; ++n) {
           const int row = (it.slo + n) * 128;
 #pragma unroll 1
-          for (int j = 0; j < 2 * kHalves && ok; ++j, ++r) {  // the pieces of K, then those of V
+          for (int j = 0; j < 2 * kChunks && ok; ++j, ++r) {  // the pieces of K, then those of V
             const int st = r % kSlots;
             if (!mbar_wait(&ring_empty[st], ((r / kSlots) & 1) ^ 1)) {
               report_timeout(a.status, 601);
@@ -184,10 +184,8 @@ bwd_wide_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
               break;
             }
             uint8_t* dst = sRing + st * L::kSlotBytes;
-            const CUtensorMap* map = j < kHalves ? &map_k : &map_v;
             mbar_arrive_expect_tx(&ring_full[st], L::kSlotBytes);
-            tma_load_4d(dst, map, &ring_full[st], (j % kHalves) * 128, row, it.hk, it.b);
-            tma_load_4d(dst + 16384, map, &ring_full[st], (j % kHalves) * 128 + 64, row, it.hk, it.b);
+            tma_load_4d(dst, j < kChunks ? &map_k : &map_v, &ring_full[st], (j % kChunks) * 64, row, it.hk, it.b);
             if (n == 0 && j == 0) {
               // Q and dO of the item behind its first half tile: the MMAs of the previous item that read the old
               // ones need nothing further from this thread, so this wait cannot block the ring
@@ -222,8 +220,8 @@ bwd_wide_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           ok = false;
         }
       };
-      // [128 queries x 128 keys] (+)= A[:, half] B[:, half]^T: 128 columns of the head dim, eight MMAs
-      auto half_product = [&](uint32_t col, uint32_t a_addr, bool first) {
+      // [128 queries x 128 keys] (+)= A[:, piece] B[:, piece]^T: 64 columns of the head dim, four MMAs
+      auto piece_product = [&](uint32_t col, uint32_t a_addr, bool first) {
         const int st = r % kSlots;
         wait_or_report(&ring_full[st], (r / kSlots) & 1, 603);
         if (!ok) return;
@@ -232,10 +230,7 @@ bwd_wide_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         if (first) mma_ss_lo<0>(tmem_base + col, a_lo, hi, b_lo, hi, idesc);
         else mma_ss_lo<1>(tmem_base + col, a_lo, hi, b_lo, hi, idesc);
 #pragma unroll
-        for (int kk = 1; kk < 8; ++kk) {
-          const uint32_t o = ((kk / 4) * 16384 + (kk % 4) * 32) >> 4;
-          mma_ss_lo<1>(tmem_base + col, a_lo + o, hi, b_lo + o, hi, idesc);
-        }
+        for (int kk = 1; kk < 4; ++kk) mma_ss_lo<1>(tmem_base + col, a_lo + kk * 2, hi, b_lo + kk * 2, hi, idesc);
         tc_commit(&ring_empty[st]);
         ++r;
       };
@@ -251,14 +246,14 @@ bwd_wide_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           if (!ok) break;
           tc_fence_after_sync();
 #pragma unroll
-          for (int h = 0; h < kHalves; ++h) half_product(kColS + buf * 128, q_addr + h * 32768, h == 0);
+          for (int c = 0; c < kChunks; ++c) piece_product(kColS + buf * 128, q_addr + c * 16384, c == 0);
           if (!ok) break;
           tc_commit(&s_full[buf]);
           wait_or_report(&dp_free[buf], ((g >> 1) & 1) ^ 1, 605);
           if (!ok) break;
           tc_fence_after_sync();
 #pragma unroll
-          for (int h = 0; h < kHalves; ++h) half_product(kColDP + buf * 128, do_addr + h * 32768, h == 0);
+          for (int c = 0; c < kChunks; ++c) piece_product(kColDP + buf * 128, do_addr + c * 16384, c == 0);
           if (!ok) break;
           tc_commit(&dp_full[buf]);
         }

@@ -52,8 +52,9 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) simt_delta_kernel(const f
   if (lane == 0) P.delta[s.delta_off + (int64_t)i * s.delta_row_stride] = acc;
 }
 
-// Same, for 16-bit rows of 64 or 128 contiguous elements: D/8 lanes cover one row with 16-byte loads,
-// so a warp reduces 4 (D=64) or 2 (D=128) rows at a time. HBM-bound: reads O and dO once.
+// Same, for 16-bit rows of up to D (64, 128 or 256) contiguous elements, a multiple of 8: D/8 lanes cover one row with
+// 16-byte loads (lanes past the row's width hold zeros), so a warp reduces 4, 2 or 1 rows at a time. HBM-bound: reads
+// O and dO once.
 template <typename T, int D>
 __global__ void __launch_bounds__(256) delta_vec_kernel(const fa_attn_params P) {
   constexpr int LPR = D / 8;         // lanes per row
@@ -69,7 +70,7 @@ __global__ void __launch_bounds__(256) delta_vec_kernel(const fa_attn_params P) 
   for (int r = 0; r < kPasses; ++r) {
     const int i = i0 + r * RPW;
     ov[r] = dv[r] = make_uint4(0u, 0u, 0u, 0u);
-    if (i < s.seqlen_q) {
+    if (i < s.seqlen_q && (lane % LPR) * 8 < P.head_dim) {
       ov[r] = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(P.out) + s.o_off + (int64_t)i * P.o_strides[2] +
                                               (lane % LPR) * 8);
       dv[r] = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(P.dout) + s.do_off +
@@ -307,12 +308,16 @@ bool rows_vectorisable(const void* ptr, const int64_t st[4]) {
 }  // namespace
 
 int launch_bwd_delta(const fa_attn_params& p, cudaStream_t stream) {
-  if ((p.dtype == FA_F16 || p.dtype == FA_BF16) && (p.head_dim == 64 || p.head_dim == 128) &&
+  if ((p.dtype == FA_F16 || p.dtype == FA_BF16) && p.head_dim % 8 == 0 && p.head_dim <= 256 &&
       rows_vectorisable(p.out, p.o_strides) && rows_vectorisable(p.dout, p.do_strides)) {
+    const int width = p.head_dim <= 64 ? 64 : (p.head_dim <= 128 ? 128 : 256);
     if (p.dtype == FA_F16)
-      return p.head_dim == 64 ? launch_delta_vec<__half, 64>(p, stream) : launch_delta_vec<__half, 128>(p, stream);
-    return p.head_dim == 64 ? launch_delta_vec<__nv_bfloat16, 64>(p, stream)
-                            : launch_delta_vec<__nv_bfloat16, 128>(p, stream);
+      return width == 64    ? launch_delta_vec<__half, 64>(p, stream)
+             : width == 128 ? launch_delta_vec<__half, 128>(p, stream)
+                            : launch_delta_vec<__half, 256>(p, stream);
+    return width == 64    ? launch_delta_vec<__nv_bfloat16, 64>(p, stream)
+           : width == 128 ? launch_delta_vec<__nv_bfloat16, 128>(p, stream)
+                          : launch_delta_vec<__nv_bfloat16, 256>(p, stream);
   }
   dim3 grid((p.seqlen_q + kWarpsPerBlock - 1) / kWarpsPerBlock, p.batch * p.heads_q);
   simt_delta_kernel<<<grid, kWarpsPerBlock * 32, 0, stream>>>(p);
