@@ -385,6 +385,9 @@ constexpr int kCombineThreads = 256;
 constexpr int kCombineMaxD = 512;
 
 __global__ void __launch_bounds__(kCombineThreads) combine_kernel(const CombineArgs a) {
+  // Launched as a programmatic dependent of the kernel that writes the partials, this CTA may already be resident
+  // while that kernel drains; it goes on once that grid has completed (at once when launched the ordinary way).
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   __shared__ float w_s[kCombineThreads];
   __shared__ float red_s[8][kCombineMaxD];
   __shared__ float stat_s[2];
@@ -467,6 +470,7 @@ constexpr int kCombineWideThreads = 1024;
 constexpr int kCombineWideMaxSplits = 1024;
 
 __global__ void __launch_bounds__(kCombineWideThreads) combine_wide_kernel(const CombineArgs a) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // see combine_kernel
   __shared__ float w_s[kCombineWideMaxSplits];
   __shared__ float4 red_s[32][32];
   __shared__ float part_s[32];
@@ -604,16 +608,29 @@ int launch_paged_dim(const PagedArgs& a, cudaStream_t stream) {
 int launch_combine_internal(int rows, int D, int splits, const float* o_partial, int64_t o_split_stride,
                             int64_t o_row_stride, const float* lse_partial, int64_t lse_split_stride,
                             int64_t lse_row_stride, void* out, int out_dtype, int n1, int n2, int64_t os0,
-                            int64_t os1, int64_t os2, int64_t osd, float* lse_out, cudaStream_t stream) {
+                            int64_t os1, int64_t os2, int64_t osd, float* lse_out, cudaStream_t stream,
+                            bool dependent) {
   CombineArgs a{rows, D, splits, o_partial, o_split_stride, o_row_stride, lse_partial, lse_split_stride,
                 lse_row_stride, out, out_dtype, n1, n2, os0, os1, os2, osd, lse_out};
   if (D > kCombineMaxD || D % 4 || o_split_stride % 4 || o_row_stride % 4 ||
       (reinterpret_cast<uintptr_t>(o_partial) & 15))
     return set_error(FA_ERR_UNSUPPORTED, "combine needs head_dim <= %d, and 16-byte aligned partial rows", kCombineMaxD);
-  if (D <= 128 && splits >= 16 && splits <= kCombineWideMaxSplits)
-    combine_wide_kernel<<<rows, kCombineWideThreads, 0, stream>>>(a);
-  else
-    combine_kernel<<<rows, kCombineThreads, 0, stream>>>(a);
+  // dependent: the kernel launched just before on this stream writes the partials and releases its dependents early,
+  // so these CTAs are set up while its last CTAs drain instead of after the grid has gone
+  const bool wide = D <= 128 && splits >= 16 && splits <= kCombineWideMaxSplits;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(rows);
+  cfg.blockDim = dim3(wide ? kCombineWideThreads : kCombineThreads);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr = {};
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  if (dependent) {
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+  }
+  const cudaError_t e = wide ? cudaLaunchKernelEx(&cfg, combine_wide_kernel, a) : cudaLaunchKernelEx(&cfg, combine_kernel, a);
+  if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "combine launch failed: %s", cudaGetErrorString(e));
   return check_launch("combine");
 }
 
@@ -622,7 +639,7 @@ int launch_combine(const fa_combine_params& p, cudaStream_t stream) {
     return set_error(FA_ERR_INVALID_ARGUMENT, "combine: rows, head_dim and num_splits must be positive");
   return launch_combine_internal(p.rows, p.head_dim, p.num_splits, p.o_partial, p.o_split_stride, p.o_row_stride,
                                  p.lse_partial, p.lse_split_stride, p.lse_row_stride, p.out, p.out_dtype, 1, p.rows,
-                                 0, 0, p.out_row_stride, 1, p.lse_out, stream);
+                                 0, 0, p.out_row_stride, 1, p.lse_out, stream, false);
 }
 
 int launch_decode_splitk(const fa_decode_params& p, cudaStream_t stream) {
@@ -662,7 +679,7 @@ int launch_decode_splitk(const fa_decode_params& p, cudaStream_t stream) {
     const int rows = p.batch * p.heads_q * p.seqlen_q;
     rc = launch_combine_internal(rows, p.head_dim, p.num_splits, p.o_partial, (int64_t)rows * p.head_dim, p.head_dim,
                                  p.lse_partial, rows, 1, p.out, p.dtype, p.heads_q, p.seqlen_q, p.o_strides[0],
-                                 p.o_strides[1], p.o_strides[2], p.o_strides[3], nullptr, stream);
+                                 p.o_strides[1], p.o_strides[2], p.o_strides[3], nullptr, stream, false);
   }
   return rc;
 }
@@ -699,7 +716,7 @@ int launch_decode_paged(const fa_paged_params& p, cudaStream_t stream) {
     rc = launch_combine_internal(rows, p.head_dim, p.num_splits, p.o_partial, p.head_dim,
                                  (int64_t)p.num_splits * p.head_dim, p.lse_partial, 1, p.num_splits, p.out,
                                  p.out_is_f32 ? (int)FA_F32 : p.dtype, p.heads_q, 1, p.o_strides[0], p.o_strides[1], 0,
-                                 p.o_strides[2], p.lse_out, stream);
+                                 p.o_strides[2], p.lse_out, stream, false);
   }
   return rc;
 }

@@ -30,7 +30,8 @@ namespace fa {
 int launch_combine_internal(int rows, int D, int splits, const float* o_partial, int64_t o_split_stride,
                             int64_t o_row_stride, const float* lse_partial, int64_t lse_split_stride,
                             int64_t lse_row_stride, void* out, int out_dtype, int n1, int n2, int64_t os0,
-                            int64_t os1, int64_t os2, int64_t osd, float* lse_out, cudaStream_t stream);
+                            int64_t os1, int64_t os2, int64_t osd, float* lse_out, cudaStream_t stream,
+                            bool dependent);
 
 namespace {
 
@@ -186,6 +187,8 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   __shared__ int nval_s[kSlots][16];  // paged: readable tokens of each unit of the tile in that K slot
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+  // The merge kernel launched behind this one is set up while the last CTAs here drain; it waits for the whole grid.
+  grid_launch_dependents();
   auto wait = [&](uint64_t* bar, uint32_t parity) { return mbar_wait_limit(bar, parity, a.poll_limit); };
   // dense: one CTA row per (batch, kv head). paged: one per batch entry; a tile interleaves all kv heads
   // (row = token * heads_kv + head), which is how a page lies in memory, so a page is fetched with few large boxes.
@@ -848,7 +851,7 @@ int launch_decode_tc(const fa_decode_params& p, cudaStream_t stream) {
   const int nrows = p.batch * p.heads_q * p.seqlen_q;
   return launch_combine_internal(nrows, D, p.num_splits, p.o_partial, (int64_t)nrows * D, D, p.lse_partial, nrows, 1,
                                  p.out, p.dtype, p.heads_q, p.seqlen_q, p.o_strides[0], p.o_strides[1], p.o_strides[2],
-                                 p.o_strides[3], nullptr, stream);
+                                 p.o_strides[3], nullptr, stream, true);
 }
 
 bool paged_tc_supported(const fa_paged_params& p) {
@@ -927,7 +930,7 @@ int launch_paged_tc(const fa_paged_params& p, cudaStream_t stream) {
   const int nrows = p.batch * p.heads_q;
   return launch_combine_internal(nrows, D, p.num_splits, p.o_partial, D, (int64_t)p.num_splits * D, p.lse_partial, 1,
                                  p.num_splits, p.out, p.out_is_f32 ? (int)FA_F32 : p.dtype, p.heads_q, 1, p.o_strides[0],
-                                 p.o_strides[1], 0, p.o_strides[2], p.lse_out, stream);
+                                 p.o_strides[1], 0, p.o_strides[2], p.lse_out, stream, true);
 }
 
 void set_decode_fault_injection(uint32_t poll_limit, int skip_tile) {
