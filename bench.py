@@ -767,10 +767,10 @@ def baseline_configs(device, flush, peaks, iters=10):
         times = []
         for _ in range(iters):
             flush()
-            # The calls below go through Python (validation, allocation of outputs and scratch, ctypes): a spin of
-            # about 0.3 ms on the device (no memory traffic, the cache stays cold) lets the host queue the launches
-            # before the start event fires, so host time is not counted as kernel time.
-            torch.cuda._sleep(600000)
+            # The calls below go through Python (validation, allocation of outputs and scratch, ctypes, autograd): a
+            # spin of about 1 ms on the device (no memory traffic, the cache stays cold) lets the host queue the
+            # launches before the start event fires, so host time is not counted as kernel time.
+            torch.cuda._sleep(2000000)
             s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             s.record()
             fn()
@@ -893,7 +893,7 @@ def baseline_configs(device, flush, peaks, iters=10):
     q.requires_grad_(True), k.requires_grad_(True), v.requires_grad_(True)
     res["c5_fwd_bwd_varlen_8seq_32/8x128_window1024_alibi_softcap30_bf16"] = tensor(
         median_us(lambda: c5().backward(dout)), 3.5 * flops)
-    res["note"] = ("public Python API, every launch behind a 512 MB L2 flush and a 0.3 ms device-side spin that hides "
+    res["note"] = ("public Python API, every launch behind a 512 MB L2 flush and a 1 ms device-side spin that hides "
                    "the host's launch work, median of %d; FLOPs count visible "
                    "(query, key) pairs only; KV bytes are read once per kv head" % iters)
     return res
@@ -901,21 +901,26 @@ def baseline_configs(device, flush, peaks, iters=10):
 
 def other_shapes(device, tokens=2048, batch=2, heads=16, repeats=5):
     """Forward and forward+backward times of the shapes beside the headline one, through the Python API: head dims
-    the tensor-core kernels take unpadded (32, 80), the wide forward kernel (160, 256; backward on CUDA cores) and
-    the tiled CUDA-core kernels (fp32, 512). CUDA events around `repeats` calls after two warm-up calls (warm L2)."""
+    the tensor-core kernels take unpadded (32, 80), the wide kernels (160, 256: one query tile per CTA forward, scores
+    + products over a scratch buffer backward) and the tiled CUDA-core kernels (fp32, 512). Median of `repeats` calls
+    (warm L2), each between CUDA events behind a device-side spin that lets the host queue the call's launches first:
+    a forward + backward through autograd is several hundred microseconds of host work, more than the kernels take."""
     import fa_b200
 
     def timed(fn):
         for _ in range(2):
             fn()
         torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
+        times = []
         for _ in range(repeats):
+            torch.cuda._sleep(2000000)   # about 1 ms; no memory traffic
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
             fn()
-        e1.record()
-        torch.cuda.synchronize()
-        return e0.elapsed_time(e1) / repeats * 1e3
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1) * 1e3)
+        return statistics.median(times)
 
     out = {}
     for head_dim, dtype in ((32, torch.float16), (80, torch.float16), (160, torch.float16), (256, torch.float16),

@@ -135,8 +135,12 @@ __device__ __forceinline__ void store_row_slice(T* dst, const uint32_t (&o)[32],
 // first of the four blocks.
 __device__ __forceinline__ void store_ds32(uint8_t* dst, const uint32_t (&dsk)[16]) {
 #pragma unroll
-  for (int i = 0; i < 4; ++i)
-    *reinterpret_cast<uint4*>(dst + i * 2048) = make_uint4(dsk[4 * i], dsk[4 * i + 1], dsk[4 * i + 2], dsk[4 * i + 3]);
+  for (int i = 0; i < 4; ++i) {
+    // streaming store: the tile is read once, by a later kernel, and should not push operand tiles out of L2
+    asm volatile("st.global.cs.v4.b32 [%0], {%1, %2, %3, %4};" ::"l"(dst + i * 2048), "r"(dsk[4 * i]), "r"(dsk[4 * i + 1]),
+                 "r"(dsk[4 * i + 2]), "r"(dsk[4 * i + 3])
+                 : "memory");
+  }
 }
 
 // Item a persistent CTA takes in its round-th turn: rounds alternate direction over the CTAs ("snake"), so with

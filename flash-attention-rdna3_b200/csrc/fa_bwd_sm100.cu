@@ -931,34 +931,42 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
 // directions). Two accumulators in TMEM alternate between items, so four epilogue warps write one tile out while the
 // next one accumulates. HBM-bound: reads the workspace once.
 //   warps 0-3   epilogue (thread = one query row = one TMEM lane)
-//   warp  4     TMA producer (one lane)          warp 5     MMA issuer (one lane)
-constexpr int kGemmThreads = 192;
+//   warp  4     dS^T tile producer (one lane)    warp 5     MMA issuer (one lane)    warp 6     K tile producer (one lane)
+// The dS^T tiles come from HBM (each is read once), the K tiles from L2: the two run through rings of their own, five
+// tile slots and two K slots, so that four or five HBM requests of 32 KB are in flight per SM whatever the K ring does
+// (with both in one three-stage ring the kernel was bound by the latency of two requests in flight: 3.6 TB/s).
+constexpr int kGemmThreads = 224;
 
 template <int D>
 struct DqGemmSmem {
-  static constexpr int kKBytes = (D / 64) * 16384;     // one 128-key K tile
-  static constexpr int kStageBytes = 32768 + kKBytes;  // dS^T tile + K tile
-  static constexpr int kStages = D == 128 ? 3 : 4;
-  static constexpr int kBytes = kStages * kStageBytes + 1024;
+  static constexpr int kKBytes = (D / 64) * 16384;  // one 128-key K tile
+  static constexpr int kTileSlots = 5;
+  static constexpr int kKSlots = D == 128 ? 2 : 3;
+  static constexpr int kOffK = kTileSlots * 32768;
+  static constexpr int kBytes = kOffK + kKSlots * kKBytes + 1024;
 };
 
 template <typename T, int D>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 bwd_dq_gemm_kernel(const __grid_constant__ CUtensorMap map_k, const BwdArgs a) {
   using L = DqGemmSmem<D>;
-  constexpr int kStages = L::kStages;
+  constexpr int kTS = L::kTileSlots, kKS = L::kKSlots;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  __shared__ uint64_t full[kStages], empty[kStages], acc_full[2], acc_empty[2];
+  __shared__ uint64_t t_full[kTS], t_empty[kTS], k_full[kKS], k_empty[kKS], acc_full[2], acc_empty[2];
   __shared__ uint32_t tmem_base_s;
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   const int n_items = a.num_tiles * a.batch * a.heads_q;
   constexpr uint32_t kCols = 2 * D;  // two accumulators
 
   if (tid == 0) {
-    for (int i = 0; i < kStages; ++i) {
-      mbar_init(&full[i], 1);
-      mbar_init(&empty[i], 1);
+    for (int i = 0; i < kTS; ++i) {
+      mbar_init(&t_full[i], 1);
+      mbar_init(&t_empty[i], 1);
+    }
+    for (int i = 0; i < kKS; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&acc_full[i], 1);
@@ -978,9 +986,10 @@ bwd_dq_gemm_kernel(const __grid_constant__ CUtensorMap map_k, const BwdArgs a) {
   // kernel's tail, everything below waits for it to have completed.
   grid_dependency_wait();
 
-  if (warp == 4) {
+  if (warp == 4 || warp == 6) {
     if (lane == 0) {
-      tma_prefetch_desc(&map_k);
+      const bool tiles = warp == 4;  // this thread's ring: dS^T tiles or K tiles
+      if (!tiles) tma_prefetch_desc(&map_k);
       int g = 0;  // ring entries issued so far
       bool ok = true;
       for (int round = 0; ok; ++round) {
@@ -990,19 +999,30 @@ bwd_dq_gemm_kernel(const __grid_constant__ CUtensorMap map_k, const BwdArgs a) {
         if (!it.valid || it.n_total == 0) continue;
         const int64_t tile0 = (((int64_t)it.b * a.heads_q + it.h) * a.ds_kt) * a.ds_qt + it.q0 / 128;
         for (int n = 0; n < it.n_total; ++n, ++g) {
-          const int st = g % kStages, kt = it.slo + n;
-          if (!mbar_wait(&empty[st], ((g / kStages) & 1) ^ 1)) {
-            report_timeout(a.status, 501);
-            ok = false;
-            break;
-          }
-          uint8_t* dst = smem + st * L::kStageBytes;
-          mbar_arrive_expect_tx(&full[st], L::kStageBytes);
-          bulk_load(dst, reinterpret_cast<const uint8_t*>(a.ds_ws) + (tile0 + (int64_t)kt * a.ds_qt) * 32768, 32768,
-                    &full[st]);
+          const int kt = it.slo + n;
+          if (tiles) {
+            const int st = g % kTS;
+            if (!mbar_wait(&t_empty[st], ((g / kTS) & 1) ^ 1)) {
+              report_timeout(a.status, 501);
+              ok = false;
+              break;
+            }
+            mbar_arrive_expect_tx(&t_full[st], 32768);
+            bulk_load_stream(smem + st * 32768, reinterpret_cast<const uint8_t*>(a.ds_ws) + (tile0 + (int64_t)kt * a.ds_qt) * 32768,
+                             32768, &t_full[st]);
+          } else {
+            const int st = g % kKS;
+            if (!mbar_wait(&k_empty[st], ((g / kKS) & 1) ^ 1)) {
+              report_timeout(a.status, 505);
+              ok = false;
+              break;
+            }
+            uint8_t* dst = smem + L::kOffK + st * L::kKBytes;
+            mbar_arrive_expect_tx(&k_full[st], L::kKBytes);
 #pragma unroll
-          for (int c = 0; c < D / 64; ++c)
-            tma_load_4d(dst + 32768 + c * 16384, &map_k, &full[st], c * 64, it.k_start + kt * 128, it.hk, it.b);
+            for (int c = 0; c < D / 64; ++c)
+              tma_load_4d(dst + c * 16384, &map_k, &k_full[st], c * 64, it.k_start + kt * 128, it.hk, it.b);
+          }
         }
       }
     }
@@ -1029,22 +1049,23 @@ bwd_dq_gemm_kernel(const __grid_constant__ CUtensorMap map_k, const BwdArgs a) {
         }
         tc_fence_after_sync();
         for (int n = 0; n < it.n_total; ++n, ++g) {
-          const int st = g % kStages;
-          if (!mbar_wait(&full[st], (g / kStages) & 1)) {
+          const int ts = g % kTS, ks = g % kKS;
+          if (!mbar_wait(&t_full[ts], (g / kTS) & 1) || !mbar_wait(&k_full[ks], (g / kKS) & 1)) {
             report_timeout(a.status, 503);
             ok = false;
             break;
           }
           tc_fence_after_sync();
           // dS^T: unswizzled core matrices; a step of 16 keys is 256 bytes. K: the TMA tile, as V in the forward.
-          const uint32_t ds_lo = smem_desc_lo(base + st * L::kStageBytes, kDsLbo);
-          const uint32_t k_lo = smem_desc_lo(base + st * L::kStageBytes + 32768, 16384);
+          const uint32_t ds_lo = smem_desc_lo(base + ts * 32768, kDsLbo);
+          const uint32_t k_lo = smem_desc_lo(base + L::kOffK + ks * L::kKBytes, 16384);
           if (n == 0) mma_ss_lo<0>(tmem_base + buf * D, ds_lo, hi_ds, k_lo, hi, idesc);
           else mma_ss_lo<1>(tmem_base + buf * D, ds_lo, hi_ds, k_lo, hi, idesc);
 #pragma unroll
           for (int kk = 1; kk < 8; ++kk)  // 16 keys per instruction
             mma_ss_lo<1>(tmem_base + buf * D, ds_lo + kk * (256 >> 4), hi_ds, k_lo + kk * (2048 >> 4), hi, idesc);
-          tc_commit(&empty[st]);
+          tc_commit(&t_empty[ts]);
+          tc_commit(&k_empty[ks]);
         }
         if (!ok) break;
         tc_commit(&acc_full[buf]);

@@ -28,7 +28,7 @@ namespace {
 
 constexpr int kWD = 256;              // compiled head dim; narrower rows load as zeros
 constexpr int kTileWs = 32768;        // one 128 x 128 16-bit tile in the workspace
-constexpr int kWideGemmThreads = 192;
+constexpr int kWideGemmThreads = 224;
 
 // Key tiles [slo, slo + n) that the 128-query tile qt sees (dense problem). Every kernel of this file derives its
 // loops from this one function, so the tiles that are read are exactly the tiles that were written.
@@ -398,17 +398,21 @@ bwd_wide_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 // Persistent CTAs walk work items (product, output tile of 128 rows x head dim): first the dV tiles, then the dK
 // tiles (both by key tile, longest first, all query heads of the kv head's group summed in the item), then the dQ
 // tiles. Per step the producer brings one workspace tile (untiled bulk copy, 32 KB) and the matching 128 rows of dO, Q
-// or K (TMA, 64 KB) into a two-stage ring; the MMA thread accumulates into one of two accumulators in tensor memory
-// (2 x 256 columns), so that four epilogue warps write one output tile while the next one accumulates.
+// or K (TMA, 64 KB), each through a ring of its own (three tile slots, two operand slots: the tiles come from HBM and
+// want more requests in flight than the operands, which come from L2); the MMA thread accumulates into one of two
+// accumulators in tensor memory (2 x 256 columns), so that four epilogue warps write one output tile while the next
+// one accumulates.
 //   warps 0-3   epilogue (thread = one output row = one TMEM lane)
-//   warp  4     producer (one lane)              warp 5     MMA issuer (one lane)
+//   warp  4     tile producer (one lane)     warp 5     MMA issuer (one lane)     warp 6     operand producer (one lane)
 enum WideRole { kRoleDV = 0, kRoleDK = 1, kRoleDQ = 2 };
 
 template <int D>
 struct GemmSmem {
-  static constexpr int kStageBytes = kTileWs + (D / 64) * 16384;  // workspace tile + 128 rows of the streamed operand
-  static constexpr int kStages = D == 256 ? 2 : 3;
-  static constexpr int kBytes = kStages * kStageBytes + 1024;
+  static constexpr int kOpBytes = (D / 64) * 16384;  // 128 rows of the streamed operand
+  static constexpr int kOpSlots = 2;
+  static constexpr int kTileSlots = (232448 - 2048 - kOpSlots * kOpBytes) / kTileWs > 5 ? 5 : (232448 - 2048 - kOpSlots * kOpBytes) / kTileWs;
+  static constexpr int kOffOp = kTileSlots * kTileWs;
+  static constexpr int kBytes = kOffOp + kOpSlots * kOpBytes + 1024;
 };
 
 struct GemmItem {
@@ -452,19 +456,23 @@ __global__ void __launch_bounds__(kWideGemmThreads, 1)
 bwd_wide_gemm_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                      const __grid_constant__ CUtensorMap map_do, const BwdArgs a, const int parts) {
   using L = GemmSmem<D>;
-  constexpr int kStages = L::kStages;
+  constexpr int kTS = L::kTileSlots, kOS = L::kOpSlots;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  __shared__ uint64_t full[kStages], empty[kStages], acc_full[2], acc_empty[2];
+  __shared__ uint64_t t_full[kTS], t_empty[kTS], o_full[kOS], o_empty[kOS], acc_full[2], acc_empty[2];
   __shared__ uint32_t tmem_base_s;
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   const int n_items = gemm_item_count(a, parts);
   constexpr uint32_t kCols = 2 * D;  // two accumulators
 
   if (tid == 0) {
-    for (int i = 0; i < kStages; ++i) {
-      mbar_init(&full[i], 1);
-      mbar_init(&empty[i], 1);
+    for (int i = 0; i < kTS; ++i) {
+      mbar_init(&t_full[i], 1);
+      mbar_init(&t_empty[i], 1);
+    }
+    for (int i = 0; i < kOS; ++i) {
+      mbar_init(&o_full[i], 1);
+      mbar_init(&o_empty[i], 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&acc_full[i], 1);
@@ -484,11 +492,14 @@ bwd_wide_gemm_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   // kernel's tail, everything below waits for it to have completed.
   grid_dependency_wait();
 
-  if (warp == 4) {
+  if (warp == 4 || warp == 6) {
     if (lane == 0) {
-      tma_prefetch_desc(&map_q);
-      tma_prefetch_desc(&map_k);
-      tma_prefetch_desc(&map_do);
+      const bool tiles = warp == 4;  // this thread's ring: workspace tiles or operand rows
+      if (!tiles) {
+        tma_prefetch_desc(&map_q);
+        tma_prefetch_desc(&map_k);
+        tma_prefetch_desc(&map_do);
+      }
       const uint8_t* ws_ds = reinterpret_cast<const uint8_t*>(a.ds_ws);
       const uint8_t* ws_p = ws_ds + (int64_t)a.batch * a.heads_q * a.ds_kt * a.ds_qt * kTileWs;
       const int group = a.heads_q / a.heads_kv;
@@ -499,14 +510,6 @@ bwd_wide_gemm_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         if (w >= n_items) break;
         const GemmItem it = gemm_item(a, parts, w);
         for (int n = 0; n < it.n; ++n, ++g) {
-          const int st = g % kStages;
-          if (!mbar_wait(&empty[st], ((g / kStages) & 1) ^ 1)) {
-            report_timeout(a.status, 611);
-            ok = false;
-            break;
-          }
-          uint8_t* dst = smem + st * L::kStageBytes;
-          mbar_arrive_expect_tx(&full[st], L::kStageBytes);
           const uint8_t* tile;
           const CUtensorMap* map;
           int row, head;
@@ -523,9 +526,27 @@ bwd_wide_gemm_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             row = qt * 128;
             head = h;
           }
-          bulk_load(dst, tile, kTileWs, &full[st]);
+          if (tiles) {
+            const int st = g % kTS;
+            if (!mbar_wait(&t_empty[st], ((g / kTS) & 1) ^ 1)) {
+              report_timeout(a.status, 611);
+              ok = false;
+              break;
+            }
+            mbar_arrive_expect_tx(&t_full[st], kTileWs);
+            bulk_load_stream(smem + st * kTileWs, tile, kTileWs, &t_full[st]);
+          } else {
+            const int st = g % kOS;
+            if (!mbar_wait(&o_empty[st], ((g / kOS) & 1) ^ 1)) {
+              report_timeout(a.status, 615);
+              ok = false;
+              break;
+            }
+            uint8_t* dst = smem + L::kOffOp + st * L::kOpBytes;
+            mbar_arrive_expect_tx(&o_full[st], L::kOpBytes);
 #pragma unroll
-          for (int c = 0; c < D / 64; ++c) tma_load_4d(dst + kTileWs + c * 16384, map, &full[st], c * 64, row, head, it.b);
+            for (int c = 0; c < D / 64; ++c) tma_load_4d(dst + c * 16384, map, &o_full[st], c * 64, row, head, it.b);
+          }
         }
       }
     }
@@ -560,21 +581,22 @@ bwd_wide_gemm_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         const uint32_t a_lbo = dq ? 2048u : 128u, a_step = dq ? (4096u >> 4) : (256u >> 4);
         const uint32_t acc = tmem_base + buf * D;
         for (int n = 0; n < it.n; ++n, ++g) {
-          const int st = g % kStages;
-          if (!mbar_wait(&full[st], (g / kStages) & 1)) {
+          const int ts = g % kTS, os = g % kOS;
+          if (!mbar_wait(&t_full[ts], (g / kTS) & 1) || !mbar_wait(&o_full[os], (g / kOS) & 1)) {
             report_timeout(a.status, 613);
             ok = false;
             break;
           }
           tc_fence_after_sync();
-          const uint32_t a_lo = smem_desc_lo(base + st * L::kStageBytes, a_lbo);
-          const uint32_t b_lo = smem_desc_lo(base + st * L::kStageBytes + kTileWs, 16384);
+          const uint32_t a_lo = smem_desc_lo(base + ts * kTileWs, a_lbo);
+          const uint32_t b_lo = smem_desc_lo(base + L::kOffOp + os * L::kOpBytes, 16384);
           if (n == 0) mma_ss_lo<0>(acc, a_lo, hi_a, b_lo, hi_b, idesc);
           else mma_ss_lo<1>(acc, a_lo, hi_a, b_lo, hi_b, idesc);
 #pragma unroll
           for (int kk = 1; kk < 8; ++kk)  // 16 rows of the streamed operand per instruction
             mma_ss_lo<1>(acc, a_lo + kk * a_step, hi_a, b_lo + kk * (2048 >> 4), hi_b, idesc);
-          tc_commit(&empty[st]);
+          tc_commit(&t_empty[ts]);
+          tc_commit(&o_empty[os]);
         }
         if (!ok) break;
         tc_commit(&acc_full[buf]);
