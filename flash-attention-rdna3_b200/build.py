@@ -25,7 +25,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 OUT = os.path.join(HERE, "fa_b200", "libfa_b200.so")
-SOURCES = ["fa_api.cu", "fa_simt.cu", "fa_tiled_fwd.cu", "fa_tiled_dq.cu", "fa_tiled_dkdv.cu", "fa_decode.cu", "fa_tiny.cu", "fa_fwd_sm100.cu", "fa_bwd_sm100.cu", "fa_bwd_wide_sm100.cu", "fa_decode_sm100.cu"]
+SOURCES = ["fa_api.cu", "fa_simt.cu", "fa_tiled_fwd.cu", "fa_tiled_dq.cu", "fa_tiled_dkdv.cu", "fa_decode.cu", "fa_tiny.cu", "fa_fwd_sm100.cu", "fa_bwd_sm100.cu", "fa_wide_sm100.cu", "fa_decode_sm100.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr",

@@ -76,13 +76,15 @@ int run_fwd(const fa_attn_params* p, void* stream, bool varlen) {
   int rc = check_attn(p, false, varlen);
   if (rc) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const bool tc_ok = fwd_tcgen05_supported(*p);
+  const bool wide_ok = !varlen && fwd_wide_supported(*p);  // head dims above 256: dense problems that bring a workspace
+  const bool tc_ok = wide_ok || fwd_tcgen05_supported(*p);
   if (p->force_path == FA_PATH_TCGEN05 && !tc_ok)
     return set_error(FA_ERR_UNSUPPORTED, "the tcgen05 forward needs fp16/bf16, a head_dim that is a multiple of 8 up to "
-                                         "256, unit inner strides and 16-byte aligned rows");
+                                         "256 (up to 512 for dense problems without score modifiers that bring a "
+                                         "ds_workspace), unit inner strides and 16-byte aligned rows");
   if (tc_ok && p->force_path != FA_PATH_SIMT) {
     set_path(FA_PATH_TCGEN05);
-    return launch_fwd_tcgen05(*p, s);
+    return wide_ok ? launch_fwd_wide(*p, s) : launch_fwd_tcgen05(*p, s);
   }
   set_path(FA_PATH_SIMT);
   return launch_fwd_simt(*p, s);
@@ -204,6 +206,13 @@ int64_t fa_workspace_bytes(int32_t kind, const void* params) {
         return fa::set_error(FA_ERR_INVALID_ARGUMENT, "workspace query: sizes must be positive");
       if ((p->dtype != FA_F16 && p->dtype != FA_BF16) || p->head_dim > 256 || p->head_dim % 8) return 0;
       return p->head_dim > 128 ? fa::bwd_wide_workspace_bytes(*p) : fa::bwd_ds_workspace_bytes(*p);
+    }
+    case FA_WS_FWD_P: {
+      const fa_attn_params* p = static_cast<const fa_attn_params*>(params);
+      if (p->batch <= 0 || p->heads_q <= 0 || p->seqlen_q <= 0 || p->seqlen_k <= 0)
+        return fa::set_error(FA_ERR_INVALID_ARGUMENT, "workspace query: sizes must be positive");
+      if ((p->dtype != FA_F16 && p->dtype != FA_BF16) || p->head_dim <= 256 || p->head_dim > 512 || p->head_dim % 8) return 0;
+      return fa::fwd_wide_workspace_bytes(*p);
     }
     case FA_WS_DECODE_O_PARTIAL:
     case FA_WS_DECODE_LSE_PARTIAL: {

@@ -43,6 +43,10 @@ struct BwdArgs {
   // is then one GEMM over those tiles (bwd_dq_gemm_kernel) instead of a second pass that recomputes S and dP.
   void* ds_ws;
   int ds_kt, ds_qt;
+  float* lse_out;  // forward kernels that share this block: where LSE is written
+  // forward over P tiles: per (batch, head, query row of the padded 128-row tiles) the row maximum (log2 domain) the P
+  // tiles are relative to and 1 / the row sum, which the product's epilogue applies. Null in the backward.
+  float2* row_stats;
 };
 
 __device__ __forceinline__ void report_timeout(int* status, int code) {

@@ -1228,7 +1228,7 @@ int64_t bwd_ds_workspace_bytes(const fa_attn_params& p) {
 }
 
 int launch_bwd_tcgen05(const fa_attn_params& p, int parts, cudaStream_t stream) {
-  BwdArgs a;
+  BwdArgs a = {};
   a.varlen = p.varlen;
   a.batch = p.batch;
   a.heads_q = p.heads_q;

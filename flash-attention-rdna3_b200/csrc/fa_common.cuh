@@ -315,9 +315,12 @@ bool fwd_tcgen05_supported(const fa_attn_params& p);
 int launch_bwd_tcgen05(const fa_attn_params& p, int parts, cudaStream_t stream);   // fa_bwd_sm100.cu
 bool bwd_tcgen05_supported(const fa_attn_params& p);
 int64_t bwd_ds_workspace_bytes(const fa_attn_params& p);
-int launch_bwd_wide(const fa_attn_params& p, int parts, cudaStream_t stream);      // fa_bwd_wide_sm100.cu
+int launch_bwd_wide(const fa_attn_params& p, int parts, cudaStream_t stream);      // fa_wide_sm100.cu
 bool bwd_wide_supported(const fa_attn_params& p);
 int64_t bwd_wide_workspace_bytes(const fa_attn_params& p);
+int launch_fwd_wide(const fa_attn_params& p, cudaStream_t stream);
+bool fwd_wide_supported(const fa_attn_params& p);
+int64_t fwd_wide_workspace_bytes(const fa_attn_params& p);
 int launch_fwd_simt(const fa_attn_params& p, cudaStream_t stream);      // fa_simt.cu
 int launch_bwd_simt(const fa_attn_params& p, int parts, cudaStream_t stream);      // fa_simt.cu
 int launch_tiled_fwd(const fa_attn_params& p, cudaStream_t stream);    // fa_tiled_fwd.cu

@@ -1,5 +1,8 @@
-// FlashAttention-2 backward on tcgen05 for head dims above 128 (up to 256), dense problems with a workspace.
+// Attention on tcgen05 for the head dims the fused kernels have no room for, dense problems with a workspace:
+// the backward above 128 (up to 256) and the forward above 256 (up to 512). Both are taken apart into plain products
+// whose 128 x 128 16-bit tiles (P, dS) pass through a scratch buffer in the layout an MMA reads its operand in.
 //
+// Backward, head dims 129-256.
 // dK and dV of a 128-key tile are 2 x 256 fp32 accumulator columns, all of tensor memory, so the fused form of
 // fa_bwd_sm100.cu does not fit. Here the backward is taken apart into the products it consists of:
 //
@@ -20,6 +23,15 @@
 // over queries) it is the A operand of dK = dS^T Q and dV = P^T dO.
 // Tile index: ((batch * heads_q + head) * key_tiles + key tile) * query_tiles + query tile; the P tiles follow the dS
 // tiles. Math as in fa_bwd_sm100.cu (fa_rdna3/kernels/_common.py:347-508, fa_rdna3/kernels/backward.py:56-322).
+//
+// Forward, head dims 257-512: the output accumulator of 128 rows alone is 512 columns, all of tensor memory, so there
+// is no room for a score tile beside it. Three steps (fa_rdna3/kernels/forward.py:28-164 computes the same O and LSE
+// in one kernel):
+//   1. fwd_wide_kernel<stats>   S = Q K^T, online row maximum and sum -> LSE
+//   2. fwd_wide_kernel<probs>   S = Q K^T again, P = exp2(S*c - row maximum) -> P tiles in the workspace (the largest
+//                               entry of a row is exactly 1, as in the fused kernels)
+//   3. bwd_wide_gemm_kernel     O = (P V) / row sum, the same product as dQ = dS K, once per half of the head dim
+// Rows that see no key get LSE = -inf and O = 0.
 #include "fa_bwd_shared.cuh"
 #include "fa_tma_host.h"
 
@@ -59,6 +71,10 @@ __device__ __forceinline__ void query_tiles_of(const BwdArgs& a, int kt, int* ql
   }
   *qlo = lo;
   *n = hi >= lo ? hi - lo + 1 : 0;
+}
+
+__device__ __forceinline__ void compute_sync_256() {
+  asm volatile("bar.sync 1, 256;" ::: "memory");  // the eight compute warps
 }
 
 __device__ __forceinline__ int64_t ws_tile(const BwdArgs& a, int b, int h, int kt, int qt) {
@@ -393,6 +409,283 @@ bwd_wide_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 }
 
 // =============================================================================================
+// forward for head dims above 256: row statistics, then normalised P tiles
+// =============================================================================================
+// The same persistent structure as the scores kernel above with one product per step: Q of the item resident
+// (8 pieces of 64 columns, 128 KB), K streamed piece by piece through a ring of six 16 KB slots, S double-buffered in
+// tensor memory. kProbs = false: every thread keeps the running maximum and sum of its 64 columns of every step; the two
+// column halves of a row are joined through shared memory at the end of the item; LSE and the pair (row maximum,
+// 1 / row sum) are written. kProbs = true: P = exp2(S * c - row maximum) goes to the workspace as a 16-bit tile (the
+// layout of the dS tiles above); the product's epilogue divides by the row sum in fp32.
+struct FwdWideSmem {
+  static constexpr int kD = 512;
+  static constexpr int kTileBytes = (kD / 64) * 16384;
+  static constexpr int kOffRing = kTileBytes;
+  static constexpr int kSlotBytes = 16384;
+  static constexpr int kSlots = 6;
+  static constexpr int kOffStats = kOffRing + kSlots * kSlotBytes;  // [128 rows] (max, sum) of compute group 1
+  static constexpr int kOffBars = kOffStats + 128 * 8;
+  static constexpr int kNumBars = 6 + 2 * kSlots;
+  static constexpr int kOffTmemPtr = kOffBars + kNumBars * 8;
+  static constexpr int kBytes = kOffTmemPtr + 8 + 1024;
+  static_assert(kBytes <= 232448, "shared memory plan exceeds one CTA's 227 KB");
+};
+
+template <typename T, bool kProbs>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+fwd_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, const BwdArgs a) {
+  using L = FwdWideSmem;
+  constexpr int kSlots = L::kSlots, kChunks = L::kD / 64;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sRing = smem + L::kOffRing;
+  float2* stats_s = reinterpret_cast<float2*>(smem + L::kOffStats);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kOffBars);
+  uint64_t* q_full = bars + 0;
+  uint64_t* q_empty = bars + 1;
+  uint64_t* s_full = bars + 2;  // [2]
+  uint64_t* s_free = bars + 4;  // [2]
+  uint64_t* ring_full = bars + 6;
+  uint64_t* ring_empty = ring_full + kSlots;
+  uint32_t* tmem_base_s = reinterpret_cast<uint32_t*>(smem + L::kOffTmemPtr);
+
+  const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+  const int n_items = a.ds_qt * a.batch * a.heads_q;
+
+  grid_launch_dependents();  // the kernel behind this one sets itself up early and waits inside
+  if (tid == 0) {
+    mbar_init(q_full, 1);
+    mbar_init(q_empty, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s_full[i], 1);
+      mbar_init(&s_free[i], 256);
+    }
+    for (int i = 0; i < kSlots; ++i) {
+      mbar_init(&ring_full[i], 1);
+      mbar_init(&ring_empty[i], 1);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 9) {
+    tmem_alloc(tmem_base_s, 256);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_base_s;
+  // kProbs: the statistics kernel launched before this one wrote the LSE this one reads
+  if (kProbs) grid_dependency_wait();
+
+  if (warp == 8) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&map_k);
+      int r = 0, used = 0;
+      bool ok = true;
+      for (int round = 0; ok; ++round) {
+        const int w = snake_item(round, blockIdx.x, gridDim.x);
+        if (w >= n_items) break;
+        const ScoreItem it = score_item(a, w);
+        if (it.n == 0) continue;
+        for (int n = 0; n < it.n && ok; ++n) {
+          const int row = (it.slo + n) * 128;
+#pragma unroll 1
+          for (int j = 0; j < kChunks && ok; ++j, ++r) {
+            const int st = r % kSlots;
+            if (!mbar_wait(&ring_empty[st], ((r / kSlots) & 1) ^ 1)) {
+              report_timeout(a.status, 621);
+              ok = false;
+              break;
+            }
+            mbar_arrive_expect_tx(&ring_full[st], L::kSlotBytes);
+            tma_load_4d(sRing + st * L::kSlotBytes, &map_k, &ring_full[st], j * 64, row, it.hk, it.b);
+            if (n == 0 && j == 0) {  // Q of the item behind its first K piece (see the scores kernel)
+              if (!mbar_wait(q_empty, (used & 1) ^ 1)) {
+                report_timeout(a.status, 620);
+                ok = false;
+                break;
+              }
+              mbar_arrive_expect_tx(q_full, L::kTileBytes);
+#pragma unroll
+              for (int c = 0; c < kChunks; ++c) tma_load_4d(sQ + c * 16384, &map_q, q_full, c * 64, it.qt * 128, it.h, it.b);
+            }
+          }
+        }
+        ++used;
+      }
+    }
+  } else if (warp == 9) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(DType<T>::kFormat, 128, 128, 0, 0);
+      constexpr uint32_t hi = smem_desc_hi(1024);
+      const uint32_t q_addr = smem_u32(sQ), ring_addr = smem_u32(sRing);
+      int g = 0, r = 0, used = 0;
+      bool ok = true;
+      for (int round = 0; ok; ++round) {
+        const int w = snake_item(round, blockIdx.x, gridDim.x);
+        if (w >= n_items) break;
+        const ScoreItem it = score_item(a, w);
+        if (it.n == 0) continue;
+        if (!mbar_wait(q_full, used & 1)) {
+          report_timeout(a.status, 622);
+          break;
+        }
+        for (int n = 0; n < it.n && ok; ++n, ++g) {
+          const int buf = g & 1;
+          if (!mbar_wait(&s_free[buf], ((g >> 1) & 1) ^ 1)) {  // the compute warps hold the old S in registers
+            report_timeout(a.status, 624);
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          for (int c = 0; c < kChunks && ok; ++c, ++r) {
+            const int st = r % kSlots;
+            if (!mbar_wait(&ring_full[st], (r / kSlots) & 1)) {
+              report_timeout(a.status, 623);
+              ok = false;
+              break;
+            }
+            tc_fence_after_sync();
+            const uint32_t a_lo = smem_desc_lo(q_addr + c * 16384, 16), b_lo = smem_desc_lo(ring_addr + st * L::kSlotBytes, 16);
+            if (c == 0) mma_ss_lo<0>(tmem_base + buf * 128, a_lo, hi, b_lo, hi, idesc);
+            else mma_ss_lo<1>(tmem_base + buf * 128, a_lo, hi, b_lo, hi, idesc);
+#pragma unroll
+            for (int kk = 1; kk < 4; ++kk) mma_ss_lo<1>(tmem_base + buf * 128, a_lo + kk * 2, hi, b_lo + kk * 2, hi, idesc);
+            tc_commit(&ring_empty[st]);
+          }
+          if (ok) tc_commit(&s_full[buf]);
+        }
+        if (ok) tc_commit(q_empty);  // every MMA that reads this item's Q is issued
+        ++used;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ compute warps
+    const int wg = warp / 4, w4 = warp % 4;
+    const int q_row = w4 * 32 + lane;
+    const uint32_t lane_addr = static_cast<uint32_t>(w4 * 32) << 16;
+    uint8_t* ws_p = reinterpret_cast<uint8_t*>(a.ds_ws);
+    const int thread_off = wg * 8 * 2048 + q_row * 16;
+    const float scale_log2 = a.softmax_scale * kLog2e;
+    int g = 0;
+    bool ok = true;
+    for (int round = 0; ok; ++round) {
+      const int w = snake_item(round, blockIdx.x, gridDim.x);
+      if (w >= n_items) break;
+      const ScoreItem it = score_item(a, w);
+      const int q0 = it.qt * 128, i = q0 + q_row;
+      const int64_t lse_idx = (int64_t)it.b * a.l_sb + (int64_t)it.h * a.l_sh + (int64_t)i * a.l_ss;
+      float2* stat = a.row_stats + ((int64_t)it.b * a.heads_q + it.h) * (a.ds_qt * 128) + i;
+      if (it.n == 0) {  // rows that see no key
+        if (!kProbs && wg == 0 && i < a.seqlen_q) a.lse_out[lse_idx] = kNegInf;
+        continue;
+      }
+      const ScoreMods mods = make_mods(a, it.b, it.h, a.seqlen_q, a.seqlen_k);
+      const int off = a.seqlen_k - a.seqlen_q;
+      float nlse2 = kNegInf;  // minus the row maximum; -inf for rows that keep nothing (their P is 0)
+      if (kProbs && i < a.seqlen_q) {
+        const float m = stat->x;
+        nlse2 = (m == kNegInf) ? kNegInf : -m;
+      }
+      const uint64_t sc2 = pack_f32x2(scale_log2, scale_log2), nl2 = pack_f32x2(nlse2, nlse2);
+      float m_run = kNegInf, l_run = 0.f;  // statistics of this thread's columns, log2 domain
+
+      for (int n = 0; n < it.n; ++n, ++g) {
+        const int buf = g & 1, kt = it.slo + n, ks = kt * 128;
+        const uint32_t tS = tmem_base + lane_addr + buf * 128 + wg * 64;
+        const bool masked = block_needs_mask(mods, q0, 128, ks, 128);
+        int c_lo = 0, c_hi = 127;
+        if (masked) {
+          c_hi = min(c_hi, a.seqlen_k - 1 - ks);
+          if (a.causal) c_hi = min(c_hi, i + off - ks);
+          else if (a.wr >= 0) c_hi = min(c_hi, i + off + a.wr - ks);
+          if (a.wl >= 0) c_lo = max(0, i + off - a.wl - ks);
+        }
+        if (!__all_sync(kFull, mbar_wait(&s_full[buf], (g >> 1) & 1))) {
+          report_timeout(a.status, 626);
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        uint32_t p0[32], p1[32];
+        tmem_ld32(tS, p0);
+        tmem_ld32(tS + 32, p1);
+        tc_wait_ld_regs(p0);
+        tc_wait_ld_regs(p1);
+        tc_fence_before_sync();
+        mbar_arrive(&s_free[buf]);
+        if (kProbs) {
+          uint32_t pk[16];
+          if (masked) {
+            probs_inplace<true>(p0, sc2, nl2, wg * 64, c_lo, c_hi);
+            probs_inplace<true>(p1, sc2, nl2, wg * 64 + 32, c_lo, c_hi);
+          } else {
+            probs_inplace<false>(p0, sc2, nl2, wg * 64, c_lo, c_hi);
+            probs_inplace<false>(p1, sc2, nl2, wg * 64 + 32, c_lo, c_hi);
+          }
+          uint8_t* p_dst = ws_p + ws_tile(a, it.b, it.h, kt, it.qt) * kTileWs + thread_off;
+#pragma unroll
+          for (int e = 0; e < 16; ++e) pk[e] = DType<T>::pack2(__uint_as_float(p0[2 * e]), __uint_as_float(p0[2 * e + 1]));
+          store_ds32(p_dst, pk);
+#pragma unroll
+          for (int e = 0; e < 16; ++e) pk[e] = DType<T>::pack2(__uint_as_float(p1[2 * e]), __uint_as_float(p1[2 * e + 1]));
+          store_ds32(p_dst + 4 * 2048, pk);
+        } else {
+          // maximum of the kept columns, then the sum relative to the new running maximum
+          float mt = kNegInf;
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            const int c0 = wg * 64 + e, c1 = c0 + 32;
+            const float x0 = (!masked || (c0 >= c_lo && c0 <= c_hi)) ? __uint_as_float(p0[e]) : kNegInf;
+            const float x1 = (!masked || (c1 >= c_lo && c1 <= c_hi)) ? __uint_as_float(p1[e]) : kNegInf;
+            p0[e] = __float_as_uint(x0);
+            p1[e] = __float_as_uint(x1);
+            mt = fmaxf(mt, fmaxf(x0, x1));
+          }
+          mt *= scale_log2;  // softmax_scale > 0 on this path
+          const float m_new = fmaxf(m_run, mt);
+          if (m_new != kNegInf) {
+            float sum = 0.f;
+#pragma unroll
+            for (int e = 0; e < 32; ++e)
+              sum += fast_exp2(__uint_as_float(p0[e]) * scale_log2 - m_new) + fast_exp2(__uint_as_float(p1[e]) * scale_log2 - m_new);
+            l_run = l_run * fast_exp2(m_run - m_new) + sum;
+            m_run = m_new;
+          }
+        }
+      }
+      if (!ok) break;
+      if (!kProbs) {
+        // join the two column halves of every row: group 1 hands its pair over, group 0 writes LSE
+        float2* slot = stats_s + q_row;
+        if (wg == 1) *slot = make_float2(m_run, l_run);
+        compute_sync_256();
+        if (wg == 0) {
+          const float2 other = *slot;
+          const float M = fmaxf(m_run, other.x);
+          float lse = kNegInf, inv = 0.f;
+          if (M != kNegInf) {
+            const float Lsum = l_run * fast_exp2(m_run - M) + other.y * fast_exp2(other.x - M);
+            lse = (M + log2f(Lsum)) * kLn2;
+            inv = 1.f / Lsum;
+          }
+          if (i < a.seqlen_q) a.lse_out[lse_idx] = lse;
+          *stat = make_float2(M, inv);  // rows past the sequence end lie inside the padded array
+        }
+        compute_sync_256();  // the slots may be written again
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 9) tmem_dealloc(tmem_base, 256);
+}
+
+// =============================================================================================
 // 2. the three products over the tiles
 // =============================================================================================
 // Persistent CTAs walk work items (product, output tile of 128 rows x head dim): first the dV tiles, then the dK
@@ -618,6 +911,8 @@ bwd_wide_gemm_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       if (it.role == kRoleDQ) {
         row_ptr = reinterpret_cast<T*>(a.dq) + (int64_t)it.b * a.dq_sb + (int64_t)it.head * a.dq_sh + (int64_t)row * a.dq_ss;
         rows = a.seqlen_q;
+        if (a.row_stats != nullptr && it.n > 0)  // forward: O = (P V) / row sum (tiles nothing reaches have no entry)
+          scale = a.row_stats[((int64_t)it.b * a.heads_q + it.head) * (a.ds_qt * 128) + row].y;
       } else if (it.role == kRoleDK) {
         row_ptr = reinterpret_cast<T*>(a.dk) + (int64_t)it.b * a.dk_sb + (int64_t)it.head * a.dk_sh + (int64_t)row * a.dk_ss;
         rows = a.seqlen_k;
@@ -658,6 +953,35 @@ bwd_wide_gemm_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   if (warp == 5) tmem_dealloc(tmem_base, kCols);
 }
 
+// The products kernel over the tiles in a.ds_ws. dependent: launched as a programmatic dependent of the kernel before
+// it on the stream (which wrote the tiles and releases its dependents early).
+template <typename T, int D>
+int launch_products(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mdo, const BwdArgs& a, int parts,
+                    bool dependent, cudaStream_t stream) {
+  auto kern = bwd_wide_gemm_kernel<T, D>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<D>::kBytes);
+  if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "products smem opt-in failed: %s", cudaGetErrorString(e));
+  const int sms = sm_count();
+  const int n_items = ((parts & FA_BWD_DKDV) ? 2 * a.ds_kt * a.batch * a.heads_kv : 0) +
+                      ((parts & FA_BWD_DQ) ? a.ds_qt * a.batch * a.heads_q : 0);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(n_items < sms ? n_items : sms);
+  cfg.blockDim = dim3(kWideGemmThreads);
+  cfg.dynamicSmemBytes = GemmSmem<D>::kBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr = {};
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  if (dependent) {  // its CTAs may set themselves up while the last CTAs of that kernel drain (they wait inside)
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+  }
+  e = cudaLaunchKernelEx(&cfg, kern, mq, mk, mdo, a, parts);
+  if (e == cudaSuccess) e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "products launch failed: %s", cudaGetErrorString(e));
+  return 0;
+}
+
 template <typename T, int D, bool kMods>
 int launch_wide_typed(const fa_attn_params& p, const BwdArgs& a, int parts, cudaStream_t stream) {
   auto map_of = [&](CUtensorMap* m, const void* ptr, int rows, int heads, const int64_t* st) {
@@ -680,27 +1004,63 @@ int launch_wide_typed(const fa_attn_params& p, const BwdArgs& a, int parts, cuda
     e = cudaGetLastError();
     if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "backward scores launch failed: %s", cudaGetErrorString(e));
   }
-  {
-    auto kern = bwd_wide_gemm_kernel<T, D>;
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<D>::kBytes);
-    if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "backward smem opt-in failed: %s", cudaGetErrorString(e));
-    const int n_items = ((parts & FA_BWD_DKDV) ? 2 * a.ds_kt * p.batch * p.heads_kv : 0) +
-                        ((parts & FA_BWD_DQ) ? a.ds_qt * p.batch * p.heads_q : 0);
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(n_items < sms ? n_items : sms);
-    cfg.blockDim = dim3(kWideGemmThreads);
-    cfg.dynamicSmemBytes = GemmSmem<D>::kBytes;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr = {};
-    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr.val.programmaticStreamSerializationAllowed = 1;
-    if (parts & FA_BWD_DKDV) {  // its CTAs may set themselves up while the last scores CTAs drain (they wait inside)
-      cfg.attrs = &attr;
-      cfg.numAttrs = 1;
-    }
-    e = cudaLaunchKernelEx(&cfg, kern, mq, mk, mdo, a, parts);
+  return launch_products<T, D>(mq, mk, mdo, a, parts, (parts & FA_BWD_DKDV) != 0, stream);
+}
+
+
+template <typename T>
+int launch_fwd_wide_typed(const fa_attn_params& p, const BwdArgs& a0, cudaStream_t stream) {
+  CUtensorMap mq, mk;
+  int rc = make_tile_map(&mq, p.q, p.dtype, p.head_dim, p.seqlen_q, p.heads_q, p.batch, p.q_strides[2], p.q_strides[1],
+                         p.q_strides[0], 128);
+  if (!rc) rc = make_tile_map(&mk, p.k, p.dtype, p.head_dim, p.seqlen_k, p.heads_kv, p.batch, p.k_strides[2],
+                              p.k_strides[1], p.k_strides[0], 128);
+  if (rc) return rc;
+  const int sms = sm_count();
+  const int n_items = a0.ds_qt * p.batch * p.heads_q;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(n_items < sms ? n_items : sms);
+  cfg.blockDim = dim3(kBwdThreads);
+  cfg.dynamicSmemBytes = FwdWideSmem::kBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr = {};
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cudaError_t e;
+  {  // 1. row statistics -> LSE
+    auto kern = fwd_wide_kernel<T, false>;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdWideSmem::kBytes);
+    if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, kern, mq, mk, a0);
     if (e == cudaSuccess) e = cudaGetLastError();
-    if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "backward products launch failed: %s", cudaGetErrorString(e));
+    if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "forward statistics launch failed: %s", cudaGetErrorString(e));
+  }
+  {  // 2. normalised P tiles; set up while the statistics kernel drains
+    auto kern = fwd_wide_kernel<T, true>;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdWideSmem::kBytes);
+    if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, kern, mq, mk, a0);
+    if (e == cudaSuccess) e = cudaGetLastError();
+    if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "forward probabilities launch failed: %s", cudaGetErrorString(e));
+  }
+  // 3. O = P V, the product dQ = dS K with V in the place of K, O in the place of dQ and no scale; one launch per
+  //    256 columns of the head dim
+  for (int col0 = 0; col0 < p.head_dim; col0 += kWD) {
+    const int width = p.head_dim - col0 < kWD ? p.head_dim - col0 : kWD;
+    const T* v = reinterpret_cast<const T*>(p.v) + col0;
+    CUtensorMap mv;
+    rc = make_tile_map(&mv, v, p.dtype, width, p.seqlen_k, p.heads_kv, p.batch, p.v_strides[2], p.v_strides[1],
+                       p.v_strides[0], 128);
+    if (rc) return rc;
+    BwdArgs a = a0;
+    a.head_dim = width;
+    a.softmax_scale = 1.f;
+    a.dq = reinterpret_cast<T*>(p.out) + col0;
+    a.dq_sb = p.o_strides[0];
+    a.dq_sh = p.o_strides[1];
+    a.dq_ss = p.o_strides[2];
+    rc = launch_products<T, kWD>(mv, mv, mv, a, FA_BWD_DQ, true, stream);
+    if (rc) return rc;
   }
   return 0;
 }
@@ -788,6 +1148,59 @@ int launch_bwd_wide(const fa_attn_params& p, int parts, cudaStream_t stream) {
                 : launch_wide_typed<__half, 256, false>(p, a, parts, stream);
   return mods ? launch_wide_typed<__nv_bfloat16, 256, true>(p, a, parts, stream)
               : launch_wide_typed<__nv_bfloat16, 256, false>(p, a, parts, stream);
+}
+
+// Forward for head dims above 256 up to 512: dense, 16-bit, no score modifier, with a workspace for the P tiles.
+bool fwd_wide_supported(const fa_attn_params& p) {
+  if (p.dtype != FA_F16 && p.dtype != FA_BF16) return false;
+  if (p.varlen || p.ds_workspace == nullptr || p.lse == nullptr) return false;
+  if (p.head_dim <= 256 || p.head_dim > 512 || p.head_dim % 8) return false;
+  if (p.softcap > 0.f || p.bias != nullptr || p.alibi_slopes != nullptr || p.dropout_p > 0.f) return false;
+  if (!(p.softmax_scale > 0.f)) return false;
+  const int64_t sq[3] = {p.batch, p.heads_q, p.seqlen_q};
+  const int64_t sk[3] = {p.batch, p.heads_kv, p.seqlen_k};
+  return tma_operand_ok(p.q, p.q_strides, sq) && tma_operand_ok(p.k, p.k_strides, sk) &&
+         tma_operand_ok(p.v, p.v_strides, sk) && tma_operand_ok(p.out, p.o_strides, sq);
+}
+
+// One P tile of 32 KB per (batch, query head, key tile, query tile), then 8 bytes per query row of the padded tiles.
+int64_t fwd_wide_workspace_bytes(const fa_attn_params& p) {
+  if (p.varlen) return 0;
+  const int64_t qt = (p.seqlen_q + 127) / 128;
+  const int64_t tiles = (int64_t)p.batch * p.heads_q * ((p.seqlen_k + 127) / 128) * qt;
+  return tiles * kTileWs + (int64_t)p.batch * p.heads_q * qt * 128 * 8;
+}
+
+int launch_fwd_wide(const fa_attn_params& p, cudaStream_t stream) {
+  const int64_t need = fwd_wide_workspace_bytes(p);
+  if (p.ds_workspace_bytes < need)
+    return set_error(FA_ERR_INVALID_ARGUMENT, "ds_workspace holds %lld bytes, this problem needs %lld",
+                     (long long)p.ds_workspace_bytes, (long long)need);
+  if (reinterpret_cast<uintptr_t>(p.ds_workspace) & 1023)
+    return set_error(FA_ERR_INVALID_ARGUMENT, "ds_workspace must be aligned to 1024 bytes");
+  BwdArgs a = {};
+  a.batch = p.batch;
+  a.heads_q = p.heads_q;
+  a.heads_kv = p.heads_kv;
+  a.head_dim = p.head_dim;
+  a.seqlen_q = p.seqlen_q;
+  a.seqlen_k = p.seqlen_k;
+  a.lse = p.lse;
+  a.lse_out = p.lse;
+  a.l_sb = p.lse_strides[0];
+  a.l_sh = p.lse_strides[1];
+  a.l_ss = p.lse_strides[2];
+  a.softmax_scale = p.softmax_scale;
+  a.causal = p.causal;
+  a.wl = p.window_left;
+  a.wr = p.window_right;
+  a.status = p.status;
+  a.ds_ws = p.ds_workspace;
+  a.ds_kt = (p.seqlen_k + 127) / 128;
+  a.ds_qt = (p.seqlen_q + 127) / 128;
+  a.row_stats = reinterpret_cast<float2*>(reinterpret_cast<uint8_t*>(p.ds_workspace) +
+                                          (int64_t)p.batch * p.heads_q * a.ds_kt * a.ds_qt * kTileWs);
+  return p.dtype == FA_F16 ? launch_fwd_wide_typed<__half>(p, a, stream) : launch_fwd_wide_typed<__nv_bfloat16>(p, a, stream);
 }
 
 }  // namespace fa

@@ -15,6 +15,7 @@ FA_PATH_NONE, FA_PATH_TCGEN05, FA_PATH_SIMT = 0, 1, 2
 FA_BWD_DELTA, FA_BWD_DKDV, FA_BWD_DQ = 1, 2, 4
 FA_WS_BWD_DELTA, FA_WS_DECODE_O_PARTIAL, FA_WS_DECODE_LSE_PARTIAL, FA_WS_PAGED_O_PARTIAL, FA_WS_PAGED_LSE_PARTIAL = 1, 2, 3, 4, 5
 FA_WS_BWD_DS = 6
+FA_WS_FWD_P = 7
 ABI_VERSION = 2
 
 I64x4 = C.c_int64 * 4

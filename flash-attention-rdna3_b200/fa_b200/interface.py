@@ -288,14 +288,22 @@ def last_kernel_path():
 def _forward(query, key, value, causal, softmax_scale, window, softcap, bias, alibi, dropout_p, dropout_seed):
     """Dense forward launch: allocates O and LSE, returns (out, lse) (fa_rdna3/interface.py:154-199)."""
     lib = _lib.load()
-    batch, heads, seqlen_q, _ = query.shape
+    batch, heads, seqlen_q, head_dim = query.shape
     out = torch.empty_like(query)
     lse = torch.empty((batch, heads, seqlen_q), dtype=torch.float32, device=query.device)
     alibi_t = None if alibi is None else _alibi_args(alibi, query)[0]
-    p = _attn_params(query, key, value, out, lse, causal, softmax_scale, window, softcap, bias, alibi_t,
-                     dropout_p, dropout_seed, force_path=_force_path)
-    with torch.cuda.device(query.device):
-        _lib.check(lib.fa_fwd(C.byref(p), _stream(query.device)))
+    # head dims above 256 run on the tensor cores when they get a scratch for their P tiles (2 bytes per score; no score
+    # modifier): a batch whose scratch exceeds the limit goes entry by entry
+    plain = softcap == 0.0 and bias is None and alibi is None and dropout_p == 0.0
+    pieces = _wide_batch_pieces(query, key, 1, 256) if plain else [(0, batch)]
+    for b0, b1 in pieces:
+        sl = slice(b0, b1)
+        bias_piece = bias[sl] if (bias is not None and bias.dim() == 4 and bias.shape[0] > 1) else bias
+        p = _attn_params(query[sl], key[sl], value[sl], out[sl], lse[sl], causal, softmax_scale, window, softcap,
+                         bias_piece, alibi_t, dropout_p, dropout_seed, force_path=_force_path)
+        ws = _scratch(p, _lib.FA_WS_FWD_P, query.device) if (plain and head_dim > 256) else None  # noqa: F841
+        with torch.cuda.device(query.device):
+            _lib.check(lib.fa_fwd(C.byref(p), _stream(query.device)))
     return out, lse
 
 
@@ -320,10 +328,10 @@ DS_WORKSPACE_WIDE_LIMIT_BYTES = int(os.environ.get("FA_B200_DS_WORKSPACE_WIDE_MB
 _poison_ds_workspace = False
 
 
-def _ds_workspace(p, device):
-    """Scratch for the dS form of the dense backward, or None when the problem does not take one or it would be
-    larger than the limit for its head dim. Attached to `p`; the caller keeps the returned tensor alive."""
-    need = _lib.load().fa_workspace_bytes(_lib.FA_WS_BWD_DS, C.byref(p))
+def _scratch(p, kind, device):
+    """Scratch of `kind` for the problem in `p`, or None when the problem does not take one or it would be larger than
+    the limit for its head dim. Attached to `p`; the caller keeps the returned tensor alive."""
+    need = _lib.load().fa_workspace_bytes(kind, C.byref(p))
     limit = DS_WORKSPACE_WIDE_LIMIT_BYTES if p.head_dim > 128 else DS_WORKSPACE_LIMIT_BYTES
     if need <= 0 or need > limit:
         return None
@@ -335,15 +343,21 @@ def _ds_workspace(p, device):
     return ws
 
 
-def _wide_batch_pieces(query, key, dropout_p):
-    """Batch ranges of one backward launch each. One range, except for 16-bit head dims above 128 whose scratch
-    (4 bytes per score of every query head) exceeds its limit: those go batch entry by batch entry, as many per launch
-    as fit. Dropout counters depend on the batch index inside a launch, so a problem with dropout is never cut."""
+def _ds_workspace(p, device):
+    """Scratch for the dS form of the dense backward (see _scratch)."""
+    return _scratch(p, _lib.FA_WS_BWD_DS, device)
+
+
+def _wide_batch_pieces(query, key, tiles_per_pair, above):
+    """Batch ranges of one launch each. One range, except for 16-bit head dims above `above` whose scratch
+    (`tiles_per_pair` 32 KB tiles per 128 x 128 block of scores of every query head) exceeds its limit: those go batch
+    entry by batch entry, as many per launch as fit."""
     batch, heads, seqlen_q, head_dim = query.shape
     whole = [(0, batch)]
-    if head_dim <= 128 or head_dim > 256 or query.dtype not in (torch.float16, torch.bfloat16) or dropout_p > 0.0:
+    if head_dim <= above or head_dim > 2 * above or query.dtype not in (torch.float16, torch.bfloat16):
         return whole
-    per_entry = 2 * heads * (-(-seqlen_q // 128)) * (-(-key.shape[2] // 128)) * 32768
+    qt = -(-seqlen_q // 128)
+    per_entry = heads * (tiles_per_pair * qt * (-(-key.shape[2] // 128)) * 32768 + (qt * 1024 if above == 256 else 0))
     if per_entry * batch <= DS_WORKSPACE_WIDE_LIMIT_BYTES or per_entry > DS_WORKSPACE_WIDE_LIMIT_BYTES:
         return whole
     step = DS_WORKSPACE_WIDE_LIMIT_BYTES // per_entry
@@ -358,7 +372,8 @@ def _backward(dout, query, key, value, out, lse, causal, softmax_scale, window, 
     delta = torch.empty_like(lse)
     dq, dk, dv = torch.empty_like(query), torch.empty_like(key), torch.empty_like(value)
     alibi_t = None if alibi is None else _alibi_args(alibi, query)[0]
-    for b0, b1 in _wide_batch_pieces(query, key, dropout_p):
+    # dropout counters depend on the batch index inside a launch, so a problem with dropout is never cut
+    for b0, b1 in (_wide_batch_pieces(query, key, 2, 128) if dropout_p == 0.0 else [(0, query.shape[0])]):
         sl = slice(b0, b1)
         bias_piece = bias[sl] if (bias is not None and bias.dim() == 4 and bias.shape[0] > 1) else bias
         p = _attn_params(query[sl], key[sl], value[sl], out[sl], lse[sl], causal, softmax_scale, window, softcap,

@@ -64,10 +64,12 @@ enum fa_path { FA_PATH_NONE = 0, FA_PATH_TCGEN05 = 1, FA_PATH_SIMT = 2 };
  * are clamped into [0, total] by the kernels (fa_rdna3/kernels/varlen.py:22-27).
  *
  * head_dim: any width up to 512. fp16 / bf16 widths that are a multiple of 8 up to 256 (forward) or 128 (backward),
- * with unit inner stride and 16-byte aligned rows, run on the tensor-core kernels as they are: the tensor maps fill
- * the columns up to 64, 128 or 256 with zeros, so the padding the reference does in Python
- * (fa_rdna3/interface.py:386-396) needs no copy here. Everything else (fp32, 512, the backward above 128, odd
- * strides) runs on the CUDA-core kernels.
+ * with unit inner stride and 16-byte aligned rows, run on the fused tensor-core kernels as they are: the tensor maps
+ * fill the columns up to 64, 128 or 256 with zeros, so the padding the reference does in Python
+ * (fa_rdna3/interface.py:386-396) needs no copy here. Dense problems that bring a ds_workspace also run on the tensor
+ * cores in the backward up to 256 and in the forward (without softcap, bias, ALiBi or dropout) up to 512, as separate
+ * products over 16-bit tiles kept in that workspace. Everything else (fp32, odd strides, those widths without a
+ * workspace or with packed sequences) runs on the CUDA-core kernels.
  */
 typedef struct fa_attn_params {
   int32_t dtype;            /* fa_dtype of q, k, v, out, dout, dq, dk, dv */
@@ -113,7 +115,11 @@ typedef struct fa_attn_params {
      GEMM over those tiles; without it a second kernel recomputes the scores and dP for dQ (7 tile products instead of
      5, no scratch). Same arithmetic on the same 16-bit dS either way, same fixed summation order, no atomics. The
      size grows with seqlen_q * seqlen_k (2 bytes per score of every query head): meant for training shapes where
-     that is affordable; the Python layer uses it up to a cap and the reference never materialises anything. */
+     that is affordable; the Python layer uses it up to a cap and the reference never materialises anything.
+     Head dims above 128 (to 256): the scratch holds P and dS (4 bytes per score) and is what puts the backward on the
+     tensor cores at all. fa_fwd, dense, head dims above 256 (to 512), no score modifier: scratch of
+     fa_workspace_bytes(FA_WS_FWD_P, p) bytes for the normalised P tiles (2 bytes per score); without it the forward
+     of those widths runs on the CUDA-core kernels. */
   void* ds_workspace;
   int64_t ds_workspace_bytes;
 } fa_attn_params;
@@ -220,7 +226,8 @@ enum fa_workspace_kind {
   FA_WS_DECODE_LSE_PARTIAL = 3, /* fa_decode_params -> lse_partial */
   FA_WS_PAGED_O_PARTIAL = 4,    /* fa_paged_params  -> o_partial */
   FA_WS_PAGED_LSE_PARTIAL = 5,  /* fa_paged_params  -> lse_partial */
-  FA_WS_BWD_DS = 6              /* fa_attn_params   -> ds_workspace (optional; 0 when the problem cannot use one) */
+  FA_WS_BWD_DS = 6,             /* fa_attn_params   -> ds_workspace of fa_bwd (optional; 0 when the problem cannot use one) */
+  FA_WS_FWD_P = 7               /* fa_attn_params   -> ds_workspace of fa_fwd (head dims above 256; 0 otherwise) */
 };
 FA_API int64_t fa_workspace_bytes(int32_t kind, const void* params);
 

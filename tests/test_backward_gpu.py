@@ -268,7 +268,7 @@ def test_backward_wide_in_batch_pieces_matches_one_launch(monkeypatch):
         whole = interface._backward(dout, q, k, v, out, lse, True, scale, (-1, -1), 0.0, None, None, 0.0, 0)
         per_entry = 2 * H * 2 * 2 * 32768
         monkeypatch.setattr(interface, "DS_WORKSPACE_WIDE_LIMIT_BYTES", per_entry)
-        assert interface._wide_batch_pieces(q, k, 0.0) == [(0, 1), (1, 2), (2, 3)]
+        assert interface._wide_batch_pieces(q, k, 2, 128) == [(0, 1), (1, 2), (2, 3)]
         pieces = interface._backward(dout, q, k, v, out, lse, True, scale, (-1, -1), 0.0, None, None, 0.0, 0)
     for a, b in zip(whole, pieces):
         assert torch.equal(a, b)

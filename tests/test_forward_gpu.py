@@ -166,3 +166,46 @@ def test_forward_matches_between_kernel_families():
     with interface.force_kernel_path("simt"):
         b, lb = interface._forward(q, k, v, True, 0.0884, (-1, -1), 0.0, None, None, 0.0, 0)
     assert max_abs(a, b) <= 2e-3 and max_abs(la, lb) <= 2e-3
+
+
+# ------------------------------------------------------------------------------------- head dims above 256 (to 512)
+@pytest.mark.parametrize("dtype,B,H,Hk,Sq,Sk,D,opts", [
+    (torch.float16, 2, 2, 2, 512, 512, 512, dict()),
+    (torch.bfloat16, 1, 4, 4, 512, 512, 512, dict(causal=True)),
+    (torch.float16, 1, 1, 1, 128, 128, 512, dict(causal=True)),
+    (torch.float16, 1, 3, 3, 200, 200, 320, dict(causal=True)),
+    (torch.bfloat16, 1, 8, 2, 300, 700, 384, dict(causal=True)),
+    (torch.float16, 1, 4, 1, 700, 300, 512, dict(causal=True)),      # the first 400 rows see no key
+    (torch.float16, 1, 2, 2, 77, 1000, 264, dict()),
+    (torch.float16, 1, 2, 2, 1, 333, 512, dict()),
+    (torch.float16, 1, 4, 2, 640, 640, 448, dict(causal=True, window=(100, 0))),
+    (torch.float16, 1, 2, 2, 400, 400, 512, dict(window=(48, 48))),
+])
+def test_forward_very_wide_head_dims_on_tensor_cores(dtype, B, H, Hk, Sq, Sk, D, opts, monkeypatch):
+    """Head dims in (256, 512] without score modifiers: row statistics, normalised P tiles in a scratch buffer (poisoned
+    with NaN here, so a tile read without having been written would show), O = P V as a product over those tiles."""
+    from fa_b200 import interface
+
+    monkeypatch.setattr(interface, "_poison_ds_workspace", True)
+    assert run_case(dtype, B, H, Hk, Sq, Sk, D, path="tcgen05", seed=Sq + D, **opts) == "tcgen05"
+
+
+def test_forward_very_wide_with_modifiers_or_without_scratch_runs_on_cuda_cores(monkeypatch):
+    from fa_b200 import interface
+
+    assert run_case(torch.float16, 1, 2, 2, 200, 200, 512, seed=1, softcap=20.0) == "simt"
+    monkeypatch.setattr(interface, "DS_WORKSPACE_WIDE_LIMIT_BYTES", 0)
+    assert run_case(torch.float16, 1, 2, 2, 200, 200, 512, seed=2, causal=True) == "simt"
+
+
+def test_forward_very_wide_in_batch_pieces_matches_one_launch(monkeypatch):
+    from fa_b200 import interface
+
+    B, H, S, D = 3, 2, 256, 512
+    q, k, v = (seeded(60 + i, B, H, S, D) for i in range(3))
+    scale = 1.0 / math.sqrt(D)
+    whole = interface._forward(q, k, v, True, scale, (-1, -1), 0.0, None, None, 0.0, 0)
+    monkeypatch.setattr(interface, "DS_WORKSPACE_WIDE_LIMIT_BYTES", H * (2 * 2 * 32768 + 2 * 1024))
+    assert interface._wide_batch_pieces(q, k, 1, 256) == [(0, 1), (1, 2), (2, 3)]
+    pieces = interface._forward(q, k, v, True, scale, (-1, -1), 0.0, None, None, 0.0, 0)
+    assert torch.equal(whole[0], pieces[0]) and torch.equal(whole[1], pieces[1])
