@@ -936,6 +936,13 @@ def other_shapes(device, tokens=2048, batch=2, heads=16, repeats=5):
         out[f"{batch}x{heads}x{tokens}x{head_dim}_{str(dtype)[6:]}_causal"] = {
             "fwd_us": fwd_us, "fwd_tflops": flops / fwd_us / 1e6,
             "fwd_bwd_us": both_us, "fwd_bwd_tflops": 3.5 * flops / both_us / 1e6}
+    # one head of 512 channels over a 128 x 128 latent: the attention block of an image autoencoder, which the SDPA
+    # hook serves when a whole pipeline runs under it (forward only, non-causal)
+    gen = torch.Generator(device=device).manual_seed(512)
+    q, k, v = (torch.randn(1, 1, 16384, 512, device=device, dtype=torch.float16, generator=gen) for _ in range(3))
+    with torch.no_grad():
+        us = timed(lambda: fa_b200.flash_attention(q, k, v))
+    out["1x1x16384x512_float16_full"] = {"fwd_us": us, "fwd_tflops": 4.0 * 16384 * 16384 * 512 / us / 1e6}
     return out
 
 

@@ -104,7 +104,7 @@ int run_bwd(const fa_attn_params* p, void* stream, bool varlen) {
   const bool tc_ok = wide_ok || bwd_tcgen05_supported(*p);
   if (p->force_path == FA_PATH_TCGEN05 && !tc_ok)
     return set_error(FA_ERR_UNSUPPORTED, "the tcgen05 backward needs fp16/bf16, a head_dim that is a multiple of 8 up to "
-                                         "128 (up to 256 for dense problems with a ds_workspace), unit inner strides and "
+                                         "128 (up to 512 for dense problems with a ds_workspace; above 256 without score modifiers), unit inner strides and "
                                          "16-byte aligned rows");
   if (tc_ok && p->force_path != FA_PATH_SIMT) {
     set_path(FA_PATH_TCGEN05);
@@ -204,7 +204,7 @@ int64_t fa_workspace_bytes(int32_t kind, const void* params) {
       const fa_attn_params* p = static_cast<const fa_attn_params*>(params);
       if (p->batch <= 0 || p->heads_q <= 0 || p->seqlen_q <= 0 || p->seqlen_k <= 0)
         return fa::set_error(FA_ERR_INVALID_ARGUMENT, "workspace query: sizes must be positive");
-      if ((p->dtype != FA_F16 && p->dtype != FA_BF16) || p->head_dim > 256 || p->head_dim % 8) return 0;
+      if ((p->dtype != FA_F16 && p->dtype != FA_BF16) || p->head_dim > 512 || p->head_dim % 8) return 0;
       return p->head_dim > 128 ? fa::bwd_wide_workspace_bytes(*p) : fa::bwd_ds_workspace_bytes(*p);
     }
     case FA_WS_FWD_P: {

@@ -413,10 +413,14 @@ bwd_wide_scores_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 // =============================================================================================
 // The same persistent structure as the scores kernel above with one product per step: Q of the item resident
 // (8 pieces of 64 columns, 128 KB), K streamed piece by piece through a ring of six 16 KB slots, S double-buffered in
-// tensor memory. kProbs = false: every thread keeps the running maximum and sum of its 64 columns of every step; the two
-// column halves of a row are joined through shared memory at the end of the item; LSE and the pair (row maximum,
-// 1 / row sum) are written. kProbs = true: P = exp2(S * c - row maximum) goes to the workspace as a 16-bit tile (the
-// layout of the dS tiles above); the product's epilogue divides by the row sum in fp32.
+// tensor memory. Statistics mode: every thread keeps the running maximum and sum of its 64 columns of every step; the
+// two column halves of a row are joined through shared memory at the end of the item; LSE and the pair (row maximum,
+// 1 / row sum) are written. Probabilities mode: P = exp2(S * c - row maximum) goes to the workspace as a 16-bit tile
+// (the layout of the dS tiles above); the product's epilogue divides by the row sum in fp32.
+// The backward of these widths runs the same kernel twice more (Q and dO, 128 KB each, cannot both be resident as in
+// the scores kernel above): once over (Q, K) for P = exp2(S * c - lse), once over (dO, V), where the accumulator is dP
+// and the compute warps read their P back from its tile to form dS = P * (dP - delta); then the three products, one
+// launch per 256 columns of the head dim.
 struct FwdWideSmem {
   static constexpr int kD = 512;
   static constexpr int kTileBytes = (kD / 64) * 16384;
@@ -431,7 +435,14 @@ struct FwdWideSmem {
   static_assert(kBytes <= 232448, "shared memory plan exceeds one CTA's 227 KB");
 };
 
-template <typename T, bool kProbs>
+enum WideMode {
+  kModeStats = 0,     // forward: row maximum and sum -> LSE and (maximum, 1 / sum)
+  kModeProbsMax = 1,  // forward: P = exp2(S * c - row maximum) -> tiles in the first region of the workspace
+  kModeProbsLse = 2,  // backward: P = exp2(S * c - lse) -> tiles in the second region
+  kModeDScores = 3    // backward, with dO and V in the places of Q and K: dS = P * (dP - delta) -> tiles in the first region
+};
+
+template <typename T, int kMode>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 fwd_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, const BwdArgs a) {
   using L = FwdWideSmem;
@@ -475,8 +486,8 @@ fwd_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_base_s;
-  // kProbs: the statistics kernel launched before this one wrote the LSE this one reads
-  if (kProbs) grid_dependency_wait();
+  // every mode but the first reads what the kernel launched before it wrote (statistics, delta, P tiles)
+  if (kMode != kModeStats) grid_dependency_wait();
 
   if (warp == 8) {
     // ------------------------------------------------------------------ TMA producer
@@ -567,7 +578,10 @@ fwd_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     const int wg = warp / 4, w4 = warp % 4;
     const int q_row = w4 * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>(w4 * 32) << 16;
-    uint8_t* ws_p = reinterpret_cast<uint8_t*>(a.ds_ws);
+    constexpr bool kProbs = kMode == kModeProbsMax || kMode == kModeProbsLse;
+    uint8_t* ws_first = reinterpret_cast<uint8_t*>(a.ds_ws);
+    uint8_t* ws_second = ws_first + (int64_t)a.batch * a.heads_q * a.ds_kt * a.ds_qt * kTileWs;
+    uint8_t* ws_p = kMode == kModeProbsMax ? ws_first : ws_second;
     const int thread_off = wg * 8 * 2048 + q_row * 16;
     const float scale_log2 = a.softmax_scale * kLog2e;
     int g = 0;
@@ -578,18 +592,25 @@ fwd_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       const ScoreItem it = score_item(a, w);
       const int q0 = it.qt * 128, i = q0 + q_row;
       const int64_t lse_idx = (int64_t)it.b * a.l_sb + (int64_t)it.h * a.l_sh + (int64_t)i * a.l_ss;
-      float2* stat = a.row_stats + ((int64_t)it.b * a.heads_q + it.h) * (a.ds_qt * 128) + i;
+      float2* stat = a.row_stats == nullptr ? nullptr : a.row_stats + ((int64_t)it.b * a.heads_q + it.h) * (a.ds_qt * 128) + i;
       if (it.n == 0) {  // rows that see no key
-        if (!kProbs && wg == 0 && i < a.seqlen_q) a.lse_out[lse_idx] = kNegInf;
+        if (kMode == kModeStats && wg == 0 && i < a.seqlen_q) a.lse_out[lse_idx] = kNegInf;
         continue;
       }
       const ScoreMods mods = make_mods(a, it.b, it.h, a.seqlen_q, a.seqlen_k);
       const int off = a.seqlen_k - a.seqlen_q;
-      float nlse2 = kNegInf;  // minus the row maximum; -inf for rows that keep nothing (their P is 0)
-      if (kProbs && i < a.seqlen_q) {
+      float nlse2 = kNegInf;  // minus the row maximum (or lse); -inf for rows that keep nothing (their P is 0)
+      float ndelta = 0.f;
+      if (kMode == kModeProbsMax && i < a.seqlen_q) {
         const float m = stat->x;
         nlse2 = (m == kNegInf) ? kNegInf : -m;
       }
+      if (kMode == kModeProbsLse && i < a.seqlen_q) {
+        const float l = a.lse[lse_idx];
+        nlse2 = (l == kNegInf) ? kNegInf : -l * kLog2e;
+      }
+      if (kMode == kModeDScores && i < a.seqlen_q)
+        ndelta = -a.delta[(int64_t)it.b * a.d_sb + (int64_t)it.h * a.d_sh + (int64_t)i * a.d_ss];
       const uint64_t sc2 = pack_f32x2(scale_log2, scale_log2), nl2 = pack_f32x2(nlse2, nlse2);
       float m_run = kNegInf, l_run = 0.f;  // statistics of this thread's columns, log2 domain
 
@@ -633,6 +654,33 @@ fwd_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 #pragma unroll
           for (int e = 0; e < 16; ++e) pk[e] = DType<T>::pack2(__uint_as_float(p1[2 * e]), __uint_as_float(p1[2 * e + 1]));
           store_ds32(p_dst + 4 * 2048, pk);
+        } else if (kMode == kModeDScores) {
+          // the accumulator holds dP; P comes back from its tile (this thread's own 16-byte pieces, zero where masked)
+          const int64_t tile = ws_tile(a, it.b, it.h, kt, it.qt) * kTileWs + thread_off;
+          const uint8_t* p_src = ws_second + tile;
+          uint8_t* ds_dst = ws_first + tile;
+          const uint64_t nd2 = pack_f32x2(ndelta, ndelta);
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            uint32_t (&dp)[32] = c == 0 ? p0 : p1;
+            uint32_t pk[16], dsk[16];
+#pragma unroll
+            for (int b4 = 0; b4 < 4; ++b4) {
+              const uint4 v = *reinterpret_cast<const uint4*>(p_src + (c * 4 + b4) * 2048);
+              pk[4 * b4] = v.x;
+              pk[4 * b4 + 1] = v.y;
+              pk[4 * b4 + 2] = v.z;
+              pk[4 * b4 + 3] = v.w;
+            }
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+              const float2 pf = DType<T>::unpack2(pk[e]);
+              float d0, d1;
+              unpack_f32x2(mul_f32x2(pack_f32x2(pf.x, pf.y), add_f32x2(pack_u32x2(dp[2 * e], dp[2 * e + 1]), nd2)), &d0, &d1);
+              dsk[e] = DType<T>::pack2(d0, d1);
+            }
+            store_ds32(ds_dst + c * 4 * 2048, dsk);
+          }
         } else {
           // maximum of the kept columns, then the sum relative to the new running maximum
           float mt = kNegInf;
@@ -658,7 +706,7 @@ fwd_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         }
       }
       if (!ok) break;
-      if (!kProbs) {
+      if (kMode == kModeStats) {
         // join the two column halves of every row: group 1 hands its pair over, group 0 writes LSE
         float2* slot = stats_s + q_row;
         if (wg == 1) *slot = make_float2(m_run, l_run);
@@ -1028,14 +1076,14 @@ int launch_fwd_wide_typed(const fa_attn_params& p, const BwdArgs& a0, cudaStream
   attr.val.programmaticStreamSerializationAllowed = 1;
   cudaError_t e;
   {  // 1. row statistics -> LSE
-    auto kern = fwd_wide_kernel<T, false>;
+    auto kern = fwd_wide_kernel<T, kModeStats>;
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdWideSmem::kBytes);
     if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, kern, mq, mk, a0);
     if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "forward statistics launch failed: %s", cudaGetErrorString(e));
   }
   {  // 2. normalised P tiles; set up while the statistics kernel drains
-    auto kern = fwd_wide_kernel<T, true>;
+    auto kern = fwd_wide_kernel<T, kModeProbsMax>;
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdWideSmem::kBytes);
@@ -1065,13 +1113,77 @@ int launch_fwd_wide_typed(const fa_attn_params& p, const BwdArgs& a0, cudaStream
   return 0;
 }
 
+// Backward for head dims above 256: P tiles, then dS tiles, then the products once per 256 columns.
+template <typename T>
+int launch_bwd_vwide_typed(const fa_attn_params& p, const BwdArgs& a0, int parts, cudaStream_t stream) {
+  auto map_of = [&](CUtensorMap* m, const void* ptr, int width, int rows, int heads, const int64_t* st) {
+    return make_tile_map(m, ptr, p.dtype, width, rows, heads, p.batch, st[2], st[1], st[0], 128);
+  };
+  const int sms = sm_count();
+  cudaError_t e;
+  int rc;
+  if (parts & FA_BWD_DKDV) {
+    CUtensorMap mq, mk, mv, mdo;
+    rc = map_of(&mq, p.q, p.head_dim, p.seqlen_q, p.heads_q, p.q_strides);
+    if (!rc) rc = map_of(&mk, p.k, p.head_dim, p.seqlen_k, p.heads_kv, p.k_strides);
+    if (!rc) rc = map_of(&mv, p.v, p.head_dim, p.seqlen_k, p.heads_kv, p.v_strides);
+    if (!rc) rc = map_of(&mdo, p.dout, p.head_dim, p.seqlen_q, p.heads_q, p.do_strides);
+    if (rc) return rc;
+    const int n_items = a0.ds_qt * p.batch * p.heads_q;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(n_items < sms ? n_items : sms);
+    cfg.blockDim = dim3(kBwdThreads);
+    cfg.dynamicSmemBytes = FwdWideSmem::kBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr = {};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    {
+      auto kern = fwd_wide_kernel<T, kModeProbsLse>;
+      e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdWideSmem::kBytes);
+      if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, kern, mq, mk, a0);
+      if (e == cudaSuccess) e = cudaGetLastError();
+      if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "backward probabilities launch failed: %s", cudaGetErrorString(e));
+    }
+    {
+      auto kern = fwd_wide_kernel<T, kModeDScores>;
+      cfg.attrs = &attr;
+      cfg.numAttrs = 1;
+      e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdWideSmem::kBytes);
+      if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, kern, mdo, mv, a0);
+      if (e == cudaSuccess) e = cudaGetLastError();
+      if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "backward dS launch failed: %s", cudaGetErrorString(e));
+    }
+  }
+  for (int col0 = 0; col0 < p.head_dim; col0 += kWD) {
+    const int width = p.head_dim - col0 < kWD ? p.head_dim - col0 : kWD;
+    CUtensorMap mq, mk, mdo;
+    rc = map_of(&mq, reinterpret_cast<const T*>(p.q) + col0, width, p.seqlen_q, p.heads_q, p.q_strides);
+    if (!rc) rc = map_of(&mk, reinterpret_cast<const T*>(p.k) + col0, width, p.seqlen_k, p.heads_kv, p.k_strides);
+    if (!rc) rc = map_of(&mdo, reinterpret_cast<const T*>(p.dout) + col0, width, p.seqlen_q, p.heads_q, p.do_strides);
+    if (rc) return rc;
+    BwdArgs a = a0;
+    a.head_dim = width;
+    a.dq = reinterpret_cast<T*>(p.dq) + col0;
+    a.dk = reinterpret_cast<T*>(p.dk) + col0;
+    a.dv = reinterpret_cast<T*>(p.dv) + col0;
+    rc = launch_products<T, kWD>(mq, mk, mdo, a, parts, (parts & FA_BWD_DKDV) != 0 || col0 > 0, stream);
+    if (rc) return rc;
+  }
+  return 0;
+}
+
 }  // namespace
 
-// Head dims above 128 up to 256, dense, 16-bit, with a workspace for the P and dS tiles.
+// Head dims above 128 up to 512, dense, 16-bit, with a workspace for the P and dS tiles; above 256 without score
+// modifiers only.
 bool bwd_wide_supported(const fa_attn_params& p) {
   if (p.dtype != FA_F16 && p.dtype != FA_BF16) return false;
   if (p.varlen || p.ds_workspace == nullptr) return false;
-  if (p.head_dim <= 128 || p.head_dim > kWD || p.head_dim % 8) return false;
+  if (p.head_dim <= 128 || p.head_dim > 512 || p.head_dim % 8) return false;
+  if (p.head_dim > kWD && (p.softcap > 0.f || p.bias != nullptr || p.alibi_slopes != nullptr || p.dropout_p > 0.f ||
+                           !(p.softmax_scale > 0.f)))
+    return false;
   const int64_t sq[3] = {p.batch, p.heads_q, p.seqlen_q};
   const int64_t sk[3] = {p.batch, p.heads_kv, p.seqlen_k};
   return tma_operand_ok(p.q, p.q_strides, sq) && tma_operand_ok(p.k, p.k_strides, sk) &&
@@ -1142,6 +1254,9 @@ int launch_bwd_wide(const fa_attn_params& p, int parts, cudaStream_t stream) {
   a.ds_ws = p.ds_workspace;
   a.ds_kt = (p.seqlen_k + 127) / 128;
   a.ds_qt = (p.seqlen_q + 127) / 128;
+  if (p.head_dim > kWD)
+    return p.dtype == FA_F16 ? launch_bwd_vwide_typed<__half>(p, a, parts, stream)
+                             : launch_bwd_vwide_typed<__nv_bfloat16>(p, a, parts, stream);
   const bool mods = p.softcap > 0.f || p.bias != nullptr || p.alibi_slopes != nullptr || p.dropout_p > 0.f;
   if (p.dtype == FA_F16)
     return mods ? launch_wide_typed<__half, 256, true>(p, a, parts, stream)

@@ -354,7 +354,7 @@ def _wide_batch_pieces(query, key, tiles_per_pair, above):
     entry by batch entry, as many per launch as fit."""
     batch, heads, seqlen_q, head_dim = query.shape
     whole = [(0, batch)]
-    if head_dim <= above or head_dim > 2 * above or query.dtype not in (torch.float16, torch.bfloat16):
+    if head_dim <= above or head_dim > 512 or query.dtype not in (torch.float16, torch.bfloat16):
         return whole
     qt = -(-seqlen_q // 128)
     per_entry = heads * (tiles_per_pair * qt * (-(-key.shape[2] // 128)) * 32768 + (qt * 1024 if above == 256 else 0))

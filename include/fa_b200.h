@@ -67,8 +67,8 @@ enum fa_path { FA_PATH_NONE = 0, FA_PATH_TCGEN05 = 1, FA_PATH_SIMT = 2 };
  * with unit inner stride and 16-byte aligned rows, run on the fused tensor-core kernels as they are: the tensor maps
  * fill the columns up to 64, 128 or 256 with zeros, so the padding the reference does in Python
  * (fa_rdna3/interface.py:386-396) needs no copy here. Dense problems that bring a ds_workspace also run on the tensor
- * cores in the backward up to 256 and in the forward (without softcap, bias, ALiBi or dropout) up to 512, as separate
- * products over 16-bit tiles kept in that workspace. Everything else (fp32, odd strides, those widths without a
+ * cores above those widths, up to 512 (above 256 without softcap, bias, ALiBi or dropout), as separate products over
+ * 16-bit tiles kept in that workspace. Everything else (fp32, odd strides, those widths without a
  * workspace or with packed sequences) runs on the CUDA-core kernels.
  */
 typedef struct fa_attn_params {
@@ -116,8 +116,8 @@ typedef struct fa_attn_params {
      5, no scratch). Same arithmetic on the same 16-bit dS either way, same fixed summation order, no atomics. The
      size grows with seqlen_q * seqlen_k (2 bytes per score of every query head): meant for training shapes where
      that is affordable; the Python layer uses it up to a cap and the reference never materialises anything.
-     Head dims above 128 (to 256): the scratch holds P and dS (4 bytes per score) and is what puts the backward on the
-     tensor cores at all. fa_fwd, dense, head dims above 256 (to 512), no score modifier: scratch of
+     Head dims above 128 (to 512; above 256 without score modifiers): the scratch holds P and dS (4 bytes per score)
+     and is what puts the backward on the tensor cores at all. fa_fwd, dense, head dims above 256 (to 512), no score modifier: scratch of
      fa_workspace_bytes(FA_WS_FWD_P, p) bytes for the normalised P tiles (2 bytes per score); without it the forward
      of those widths runs on the CUDA-core kernels. */
   void* ds_workspace;

@@ -88,11 +88,17 @@ def test_workspace_bytes_match_what_the_python_layer_allocates():
     # sequences or for dtypes / head dims the tensor-core backward does not take
     a.dtype, a.heads_kv, a.seqlen_k, a.head_dim = _lib.FA_F16, 4, 1000, 128
     assert lib.fa_workspace_bytes(_lib.FA_WS_BWD_DS, ctypes.byref(a)) == 2 * 16 * 16 * 8 * 32768
-    # head dims above 128 up to 256 keep the P tile beside the dS tile; above 256 there is no scratch form
-    a.head_dim = 160
-    assert lib.fa_workspace_bytes(_lib.FA_WS_BWD_DS, ctypes.byref(a)) == 2 * 2 * 16 * 16 * 8 * 32768
-    a.head_dim = 512
+    # head dims above 128 up to 512 keep the P tile beside the dS tile; above 512 there is no scratch form
+    for wide in (160, 512):
+        a.head_dim = wide
+        assert lib.fa_workspace_bytes(_lib.FA_WS_BWD_DS, ctypes.byref(a)) == 2 * 2 * 16 * 16 * 8 * 32768
+    a.head_dim = 520
     assert lib.fa_workspace_bytes(_lib.FA_WS_BWD_DS, ctypes.byref(a)) == 0
+    # forward scratch, head dims above 256 only: one P tile per tile pair and 8 bytes per row of the padded query tiles
+    a.head_dim = 512
+    assert lib.fa_workspace_bytes(_lib.FA_WS_FWD_P, ctypes.byref(a)) == 2 * 16 * (16 * 8 * 32768 + 16 * 128 * 8)
+    a.head_dim = 256
+    assert lib.fa_workspace_bytes(_lib.FA_WS_FWD_P, ctypes.byref(a)) == 0
     a.head_dim = 128
     a.varlen, a.total_q = 1, 4096
     assert lib.fa_workspace_bytes(_lib.FA_WS_BWD_DS, ctypes.byref(a)) == 0

@@ -279,3 +279,26 @@ def test_backward_wide_without_scratch_falls_to_cuda_cores(monkeypatch):
 
     monkeypatch.setattr(interface, "DS_WORKSPACE_WIDE_LIMIT_BYTES", 0)
     assert run_case(torch.float16, 1, 2, 2, 200, 200, 256, seed=3, causal=True) == "simt"
+
+
+# ------------------------------------------------------------------------------------- head dims above 256 (to 512)
+@pytest.mark.parametrize("dtype,B,H,Hk,Sq,Sk,D,opts", [
+    (torch.float16, 2, 2, 2, 512, 512, 512, dict(causal=True)),
+    (torch.bfloat16, 1, 4, 4, 384, 384, 512, dict()),
+    (torch.float16, 1, 3, 3, 200, 200, 320, dict(causal=True)),
+    (torch.bfloat16, 1, 8, 2, 300, 700, 384, dict(causal=True)),
+    (torch.float16, 1, 4, 1, 700, 300, 512, dict(causal=True)),
+    (torch.float16, 1, 2, 2, 77, 1000, 264, dict()),
+    (torch.float16, 1, 4, 2, 640, 640, 448, dict(causal=True, window=(100, 0))),
+])
+def test_backward_very_wide_head_dims_on_tensor_cores(dtype, B, H, Hk, Sq, Sk, D, opts, monkeypatch):
+    """Head dims in (256, 512] without score modifiers: P tiles, dS tiles (P read back from its tile), then the three
+    products once per 256 columns. The scratch starts out as NaN."""
+    from fa_b200 import interface
+
+    monkeypatch.setattr(interface, "_poison_ds_workspace", True)
+    assert run_case(dtype, B, H, Hk, Sq, Sk, D, path="tcgen05", seed=Sq + D, **opts) == "tcgen05"
+
+
+def test_backward_very_wide_with_modifiers_runs_on_cuda_cores():
+    assert run_case(torch.float16, 1, 2, 2, 200, 200, 512, seed=4, causal=True, softcap=20.0) == "simt"
