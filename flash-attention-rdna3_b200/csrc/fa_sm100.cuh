@@ -253,6 +253,20 @@ __device__ __forceinline__ void mma_ss_lo(uint32_t d_tmem, uint32_t a_lo, uint32
       ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "n"(kAccumulate)
       : "memory");
 }
+// The same for 32-bit operands read as tf32 (8 elements = 32 bytes of contraction per instruction); the instruction
+// descriptor carries format 2 for both operands.
+template <int kAccumulate>
+__device__ __forceinline__ void mma_ss_lo_tf32(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                               uint32_t idesc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "mov.b64 da, {%1, %2};\n\t"
+      "mov.b64 db, {%3, %4};\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], da, db, %5, p;\n\t}\n"
+      ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "n"(kAccumulate)
+      : "memory");
+}
 template <int kAccumulate>
 __device__ __forceinline__ void mma_ts_lo(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi, uint32_t idesc) {
   asm volatile(

@@ -60,4 +60,23 @@ inline int make_tile_map(CUtensorMap* map, const void* ptr, int dtype, int head_
   return 0;
 }
 
+// The same for fp32 operands: a box of 32 elements (128 bytes) x box_rows rows. Base 16-byte aligned, strides (in
+// elements) multiples of 4.
+inline int make_tile_map_f32(CUtensorMap* map, const void* ptr, int head_dim, int64_t rows, int64_t heads, int64_t batch,
+                             int64_t stride_row, int64_t stride_head, int64_t stride_batch, int box_rows = 128) {
+  TensorMapEncodeFn enc = tensor_map_encoder();
+  if (enc == nullptr) return set_error(FA_ERR_DEVICE, "cuTensorMapEncodeTiled is not available from this driver");
+  const cuuint64_t dims[4] = {(cuuint64_t)head_dim, (cuuint64_t)rows, (cuuint64_t)heads, (cuuint64_t)batch};
+  const int64_t legal = (int64_t)head_dim;
+  auto bytes = [&](int64_t s, int64_t n) { return (cuuint64_t)((n > 1 && s > 0) ? s : legal) * 4; };
+  const cuuint64_t strides[3] = {bytes(stride_row, rows), bytes(stride_head, heads), bytes(stride_batch, batch)};
+  const cuuint32_t box[4] = {32, (cuuint32_t)box_rows, 1, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<void*>(ptr), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return set_error(FA_ERR_LAUNCH, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return 0;
+}
+
 }  // namespace fa

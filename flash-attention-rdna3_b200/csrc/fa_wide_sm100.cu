@@ -442,11 +442,15 @@ enum WideMode {
   kModeDScores = 3    // backward, with dO and V in the places of Q and K: dS = P * (dP - delta) -> tiles in the first region
 };
 
-template <typename T, int kMode>
+// TIn = float: Q and K are fp32 tiles (a piece is 32 columns, the same 128 bytes per row) and the product is a tf32 MMA;
+// T is then the 16-bit type of the P tiles.
+template <typename T, int kMode, typename TIn = T>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 fwd_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, const BwdArgs a) {
   using L = FwdWideSmem;
   constexpr int kSlots = L::kSlots, kChunks = L::kD / 64;
+  constexpr int kPieceCols = 128 / (int)sizeof(TIn);  // columns of a 128-byte piece
+  constexpr bool kTf32 = sizeof(TIn) == 4;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
@@ -511,7 +515,7 @@ fwd_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
               break;
             }
             mbar_arrive_expect_tx(&ring_full[st], L::kSlotBytes);
-            tma_load_4d(sRing + st * L::kSlotBytes, &map_k, &ring_full[st], j * 64, row, it.hk, it.b);
+            tma_load_4d(sRing + st * L::kSlotBytes, &map_k, &ring_full[st], j * kPieceCols, row, it.hk, it.b);
             if (n == 0 && j == 0) {  // Q of the item behind its first K piece (see the scores kernel)
               if (!mbar_wait(q_empty, (used & 1) ^ 1)) {
                 report_timeout(a.status, 620);
@@ -520,7 +524,7 @@ fwd_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
               }
               mbar_arrive_expect_tx(q_full, L::kTileBytes);
 #pragma unroll
-              for (int c = 0; c < kChunks; ++c) tma_load_4d(sQ + c * 16384, &map_q, q_full, c * 64, it.qt * 128, it.h, it.b);
+              for (int c = 0; c < kChunks; ++c) tma_load_4d(sQ + c * 16384, &map_q, q_full, c * kPieceCols, it.qt * 128, it.h, it.b);
             }
           }
         }
@@ -530,7 +534,7 @@ fwd_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   } else if (warp == 9) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(DType<T>::kFormat, 128, 128, 0, 0);
+      constexpr uint32_t idesc = make_idesc(DType<TIn>::kFormat, 128, 128, 0, 0);
       constexpr uint32_t hi = smem_desc_hi(1024);
       const uint32_t q_addr = smem_u32(sQ), ring_addr = smem_u32(sRing);
       int g = 0, r = 0, used = 0;
@@ -561,10 +565,18 @@ fwd_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
             }
             tc_fence_after_sync();
             const uint32_t a_lo = smem_desc_lo(q_addr + c * 16384, 16), b_lo = smem_desc_lo(ring_addr + st * L::kSlotBytes, 16);
-            if (c == 0) mma_ss_lo<0>(tmem_base + buf * 128, a_lo, hi, b_lo, hi, idesc);
-            else mma_ss_lo<1>(tmem_base + buf * 128, a_lo, hi, b_lo, hi, idesc);
+            if (kTf32) {  // 8 fp32 columns (32 bytes) per instruction
+              if (c == 0) mma_ss_lo_tf32<0>(tmem_base + buf * 128, a_lo, hi, b_lo, hi, idesc);
+              else mma_ss_lo_tf32<1>(tmem_base + buf * 128, a_lo, hi, b_lo, hi, idesc);
 #pragma unroll
-            for (int kk = 1; kk < 4; ++kk) mma_ss_lo<1>(tmem_base + buf * 128, a_lo + kk * 2, hi, b_lo + kk * 2, hi, idesc);
+              for (int kk = 1; kk < 4; ++kk)
+                mma_ss_lo_tf32<1>(tmem_base + buf * 128, a_lo + kk * 2, hi, b_lo + kk * 2, hi, idesc);
+            } else {  // 16 sixteen-bit columns (32 bytes) per instruction
+              if (c == 0) mma_ss_lo<0>(tmem_base + buf * 128, a_lo, hi, b_lo, hi, idesc);
+              else mma_ss_lo<1>(tmem_base + buf * 128, a_lo, hi, b_lo, hi, idesc);
+#pragma unroll
+              for (int kk = 1; kk < 4; ++kk) mma_ss_lo<1>(tmem_base + buf * 128, a_lo + kk * 2, hi, b_lo + kk * 2, hi, idesc);
+            }
             tc_commit(&ring_empty[st]);
           }
           if (ok) tc_commit(&s_full[buf]);
@@ -792,7 +804,24 @@ __device__ __forceinline__ GemmItem gemm_item(const BwdArgs& a, int parts, int w
   return it;
 }
 
-template <typename T, int D>
+// Converts a 32-column fp32 slice of a TMEM accumulator to the output type and writes it to a global row.
+template <typename TO>
+__device__ __forceinline__ void store_out_slice(TO* dst, const uint32_t (&o)[32], float scale, int cols) {
+  store_row_slice<TO>(dst, o, scale, cols);
+}
+template <>
+__device__ __forceinline__ void store_out_slice<float>(float* dst, const uint32_t (&o)[32], float scale, int cols) {
+#pragma unroll
+  for (int v = 0; v < 8; ++v) {
+    if (v * 4 >= cols) break;  // columns past the caller's head dimension do not exist
+    *reinterpret_cast<float4*>(dst + v * 4) =
+        make_float4(__uint_as_float(o[v * 4]) * scale, __uint_as_float(o[v * 4 + 1]) * scale,
+                    __uint_as_float(o[v * 4 + 2]) * scale, __uint_as_float(o[v * 4 + 3]) * scale);
+  }
+}
+
+// T: the 16-bit type of the tiles and of the streamed operand; TO: the type of the output rows.
+template <typename T, int D, typename TO = T>
 __global__ void __launch_bounds__(kWideGemmThreads, 1)
 bwd_wide_gemm_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                      const __grid_constant__ CUtensorMap map_do, const BwdArgs a, const int parts) {
@@ -953,19 +982,19 @@ bwd_wide_gemm_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       if (w >= n_items) break;
       const GemmItem it = gemm_item(a, parts, w);
       const int row = it.t * 128 + r;
-      T* row_ptr;
+      TO* row_ptr;
       int rows;
       float scale = a.softmax_scale;
       if (it.role == kRoleDQ) {
-        row_ptr = reinterpret_cast<T*>(a.dq) + (int64_t)it.b * a.dq_sb + (int64_t)it.head * a.dq_sh + (int64_t)row * a.dq_ss;
+        row_ptr = reinterpret_cast<TO*>(a.dq) + (int64_t)it.b * a.dq_sb + (int64_t)it.head * a.dq_sh + (int64_t)row * a.dq_ss;
         rows = a.seqlen_q;
         if (a.row_stats != nullptr && it.n > 0)  // forward: O = (P V) / row sum (tiles nothing reaches have no entry)
           scale = a.row_stats[((int64_t)it.b * a.heads_q + it.head) * (a.ds_qt * 128) + row].y;
       } else if (it.role == kRoleDK) {
-        row_ptr = reinterpret_cast<T*>(a.dk) + (int64_t)it.b * a.dk_sb + (int64_t)it.head * a.dk_sh + (int64_t)row * a.dk_ss;
+        row_ptr = reinterpret_cast<TO*>(a.dk) + (int64_t)it.b * a.dk_sb + (int64_t)it.head * a.dk_sh + (int64_t)row * a.dk_ss;
         rows = a.seqlen_k;
       } else {
-        row_ptr = reinterpret_cast<T*>(a.dv) + (int64_t)it.b * a.dv_sb + (int64_t)it.head * a.dv_sh + (int64_t)row * a.dv_ss;
+        row_ptr = reinterpret_cast<TO*>(a.dv) + (int64_t)it.b * a.dv_sb + (int64_t)it.head * a.dv_sh + (int64_t)row * a.dv_ss;
         rows = a.seqlen_k;
         scale = 1.f;
       }
@@ -987,7 +1016,7 @@ bwd_wide_gemm_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 #pragma unroll
           for (int e = 0; e < 32; ++e) o[e] = 0u;
         }
-        if (row < rows) store_row_slice<T>(row_ptr + c * 32, o, scale, a.head_dim - c * 32);
+        if (row < rows) store_out_slice<TO>(row_ptr + c * 32, o, scale, a.head_dim - c * 32);
       }
       if (it.n > 0) {
         tc_fence_before_sync();
@@ -1003,10 +1032,10 @@ bwd_wide_gemm_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 
 // The products kernel over the tiles in a.ds_ws. dependent: launched as a programmatic dependent of the kernel before
 // it on the stream (which wrote the tiles and releases its dependents early).
-template <typename T, int D>
+template <typename T, int D, typename TO = T>
 int launch_products(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mdo, const BwdArgs& a, int parts,
                     bool dependent, cudaStream_t stream) {
-  auto kern = bwd_wide_gemm_kernel<T, D>;
+  auto kern = bwd_wide_gemm_kernel<T, D, TO>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<D>::kBytes);
   if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "products smem opt-in failed: %s", cudaGetErrorString(e));
   const int sms = sm_count();
@@ -1111,6 +1140,85 @@ int launch_fwd_wide_typed(const fa_attn_params& p, const BwdArgs& a0, cudaStream
     if (rc) return rc;
   }
   return 0;
+}
+
+// fp32 inputs: V rounded to fp16 once, rows made contiguous, for the O = P V product (P is 16-bit too).
+__global__ void __launch_bounds__(256) convert_rows_f16_kernel(const float* src, int64_t sb, int64_t sh, int64_t ss,
+                                                               __half* dst, int heads, int rows, int head_dim, int64_t total8) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const int per_row = head_dim / 8;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total8; i += (int64_t)gridDim.x * blockDim.x) {
+    const int c = (int)(i % per_row);
+    const int64_t row_flat = i / per_row;
+    const int r = (int)(row_flat % rows), h = (int)((row_flat / rows) % heads);
+    const int64_t b = row_flat / ((int64_t)rows * heads);
+    const float* p = src + b * sb + (int64_t)h * sh + (int64_t)r * ss + c * 8;
+    const float4 x = *reinterpret_cast<const float4*>(p), y = *reinterpret_cast<const float4*>(p + 4);
+    uint4 o;
+    o.x = DType<__half>::pack2(x.x, x.y);
+    o.y = DType<__half>::pack2(x.z, x.w);
+    o.z = DType<__half>::pack2(y.x, y.y);
+    o.w = DType<__half>::pack2(y.z, y.w);
+    *reinterpret_cast<uint4*>(dst + row_flat * head_dim + c * 8) = o;
+  }
+}
+
+// Forward for fp32 inputs (head dims to 256): Q K^T as tf32 MMAs on the fp32 tiles, P as fp16 tiles, V rounded to fp16,
+// O and LSE in fp32.
+int launch_fwd_wide_f32(const fa_attn_params& p, const BwdArgs& a0, cudaStream_t stream) {
+  CUtensorMap mq, mk;
+  int rc = make_tile_map_f32(&mq, p.q, p.head_dim, p.seqlen_q, p.heads_q, p.batch, p.q_strides[2], p.q_strides[1],
+                             p.q_strides[0], 128);
+  if (!rc) rc = make_tile_map_f32(&mk, p.k, p.head_dim, p.seqlen_k, p.heads_kv, p.batch, p.k_strides[2], p.k_strides[1],
+                                  p.k_strides[0], 128);
+  if (rc) return rc;
+  // V in fp16 behind the P tiles and the row statistics
+  __half* v16 = reinterpret_cast<__half*>(reinterpret_cast<uint8_t*>(a0.row_stats) +
+                                          (int64_t)p.batch * p.heads_q * a0.ds_qt * 128 * 8);
+  const int64_t total8 = (int64_t)p.batch * p.heads_kv * p.seqlen_k * (p.head_dim / 8);
+  const int sms = sm_count();
+  const int64_t want = (total8 + 255) / 256;
+  convert_rows_f16_kernel<<<(int)(want < 8 * sms ? want : 8 * sms), 256, 0, stream>>>(
+      reinterpret_cast<const float*>(p.v), p.v_strides[0], p.v_strides[1], p.v_strides[2], v16, p.heads_kv, p.seqlen_k,
+      p.head_dim, total8);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "forward V conversion launch failed: %s", cudaGetErrorString(e));
+  const int n_items = a0.ds_qt * p.batch * p.heads_q;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(n_items < sms ? n_items : sms);
+  cfg.blockDim = dim3(kBwdThreads);
+  cfg.dynamicSmemBytes = FwdWideSmem::kBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr = {};
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  {
+    auto kern = fwd_wide_kernel<__half, kModeStats, float>;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdWideSmem::kBytes);
+    if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, kern, mq, mk, a0);
+    if (e == cudaSuccess) e = cudaGetLastError();
+    if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "forward statistics launch failed: %s", cudaGetErrorString(e));
+  }
+  {
+    auto kern = fwd_wide_kernel<__half, kModeProbsMax, float>;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdWideSmem::kBytes);
+    if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, kern, mq, mk, a0);
+    if (e == cudaSuccess) e = cudaGetLastError();
+    if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "forward probabilities launch failed: %s", cudaGetErrorString(e));
+  }
+  CUtensorMap mv;
+  rc = make_tile_map(&mv, v16, FA_F16, p.head_dim, p.seqlen_k, p.heads_kv, p.batch, p.head_dim,
+                     (int64_t)p.seqlen_k * p.head_dim, (int64_t)p.heads_kv * p.seqlen_k * p.head_dim, 128);
+  if (rc) return rc;
+  BwdArgs a = a0;
+  a.softmax_scale = 1.f;
+  a.dq = p.out;
+  a.dq_sb = p.o_strides[0];
+  a.dq_sh = p.o_strides[1];
+  a.dq_ss = p.o_strides[2];
+  return launch_products<__half, kWD, float>(mv, mv, mv, a, FA_BWD_DQ, true, stream);
 }
 
 // Backward for head dims above 256: P tiles, then dS tiles, then the products once per 256 columns.
@@ -1266,12 +1374,30 @@ int launch_bwd_wide(const fa_attn_params& p, int parts, cudaStream_t stream) {
 }
 
 // Forward for head dims above 256 up to 512: dense, 16-bit, no score modifier, with a workspace for the P tiles.
+namespace {
+// An fp32 operand (batch, head, row, dim) TMA can read: unit inner stride, 16-byte aligned base and rows.
+bool tma_operand_ok_f32(const void* ptr, const int64_t strides[4], const int64_t sizes[3]) {
+  if (ptr == nullptr || (reinterpret_cast<uintptr_t>(ptr) & 15) || strides[3] != 1) return false;
+  for (int i = 0; i < 3; ++i)
+    if (sizes[i] > 1 && (strides[i] <= 0 || (strides[i] % 4) != 0)) return false;
+  return true;
+}
+}  // namespace
+
 bool fwd_wide_supported(const fa_attn_params& p) {
-  if (p.dtype != FA_F16 && p.dtype != FA_BF16) return false;
   if (p.varlen || p.ds_workspace == nullptr || p.lse == nullptr) return false;
-  if (p.head_dim <= 256 || p.head_dim > 512 || p.head_dim % 8) return false;
   if (p.softcap > 0.f || p.bias != nullptr || p.alibi_slopes != nullptr || p.dropout_p > 0.f) return false;
   if (!(p.softmax_scale > 0.f)) return false;
+  if (p.dtype == FA_F32) {
+    // fp32 inputs that bring a workspace opt into tf32 / fp16 products (head dims to 256)
+    if (p.head_dim < 8 || p.head_dim > 256 || p.head_dim % 8) return false;
+    const int64_t fq[3] = {p.batch, p.heads_q, p.seqlen_q};
+    const int64_t fk[3] = {p.batch, p.heads_kv, p.seqlen_k};
+    return tma_operand_ok_f32(p.q, p.q_strides, fq) && tma_operand_ok_f32(p.k, p.k_strides, fk) &&
+           tma_operand_ok_f32(p.v, p.v_strides, fk) && tma_operand_ok_f32(p.out, p.o_strides, fq);
+  }
+  if (p.dtype != FA_F16 && p.dtype != FA_BF16) return false;
+  if (p.head_dim <= 256 || p.head_dim > 512 || p.head_dim % 8) return false;
   const int64_t sq[3] = {p.batch, p.heads_q, p.seqlen_q};
   const int64_t sk[3] = {p.batch, p.heads_kv, p.seqlen_k};
   return tma_operand_ok(p.q, p.q_strides, sq) && tma_operand_ok(p.k, p.k_strides, sk) &&
@@ -1283,7 +1409,9 @@ int64_t fwd_wide_workspace_bytes(const fa_attn_params& p) {
   if (p.varlen) return 0;
   const int64_t qt = (p.seqlen_q + 127) / 128;
   const int64_t tiles = (int64_t)p.batch * p.heads_q * ((p.seqlen_k + 127) / 128) * qt;
-  return tiles * kTileWs + (int64_t)p.batch * p.heads_q * qt * 128 * 8;
+  int64_t bytes = tiles * kTileWs + (int64_t)p.batch * p.heads_q * qt * 128 * 8;
+  if (p.dtype == FA_F32) bytes += (int64_t)p.batch * p.heads_kv * p.seqlen_k * p.head_dim * 2;  // V rounded to fp16
+  return bytes;
 }
 
 int launch_fwd_wide(const fa_attn_params& p, cudaStream_t stream) {
@@ -1315,6 +1443,7 @@ int launch_fwd_wide(const fa_attn_params& p, cudaStream_t stream) {
   a.ds_qt = (p.seqlen_q + 127) / 128;
   a.row_stats = reinterpret_cast<float2*>(reinterpret_cast<uint8_t*>(p.ds_workspace) +
                                           (int64_t)p.batch * p.heads_q * a.ds_kt * a.ds_qt * kTileWs);
+  if (p.dtype == FA_F32) return launch_fwd_wide_f32(p, a, stream);
   return p.dtype == FA_F16 ? launch_fwd_wide_typed<__half>(p, a, stream) : launch_fwd_wide_typed<__nv_bfloat16>(p, a, stream);
 }
 

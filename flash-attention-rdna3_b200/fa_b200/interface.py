@@ -295,13 +295,14 @@ def _forward(query, key, value, causal, softmax_scale, window, softcap, bias, al
     # head dims above 256 run on the tensor cores when they get a scratch for their P tiles (2 bytes per score; no score
     # modifier): a batch whose scratch exceeds the limit goes entry by entry
     plain = softcap == 0.0 and bias is None and alibi is None and dropout_p == 0.0
+    fp32_tc = plain and FP32_ON_TENSOR_CORES and query.dtype == torch.float32 and head_dim <= 256 and head_dim % 8 == 0
     pieces = _wide_batch_pieces(query, key, 1, 256) if plain else [(0, batch)]
     for b0, b1 in pieces:
         sl = slice(b0, b1)
         bias_piece = bias[sl] if (bias is not None and bias.dim() == 4 and bias.shape[0] > 1) else bias
         p = _attn_params(query[sl], key[sl], value[sl], out[sl], lse[sl], causal, softmax_scale, window, softcap,
                          bias_piece, alibi_t, dropout_p, dropout_seed, force_path=_force_path)
-        ws = _scratch(p, _lib.FA_WS_FWD_P, query.device) if (plain and head_dim > 256) else None  # noqa: F841
+        ws = _scratch(p, _lib.FA_WS_FWD_P, query.device) if (plain and (head_dim > 256 or fp32_tc)) else None  # noqa: F841
         with torch.cuda.device(query.device):
             _lib.check(lib.fa_fwd(C.byref(p), _stream(query.device)))
     return out, lse
@@ -325,6 +326,13 @@ DS_WORKSPACE_LIMIT_BYTES = int(os.environ.get("FA_B200_DS_WORKSPACE_MB", "512"))
 DS_WORKSPACE_WIDE_LIMIT_BYTES = int(os.environ.get("FA_B200_DS_WORKSPACE_WIDE_MB", "4096")) << 20
 
 
+# fp32 inputs run exact fp32 arithmetic on the CUDA cores (2e-5 against fp64 math) unless this is switched on: then
+# the dense forward without score modifiers, head dims to 256, computes Q K^T as tf32 products and P V in fp16 on the
+# tensor cores (about 1e-3 absolute error on N(0,1) inputs, inside the 2e-3 / 3e-3 the reference's own fp32 tests allow,
+# fa_rdna3 tests/test_fp32_headdim.py:35-53; V must stay inside the fp16 range). Off by default: a caller who passes
+# fp32 asked for fp32. The backward of fp32 inputs is exact either way.
+FP32_ON_TENSOR_CORES = os.environ.get("FA_B200_FP32_TENSOR_CORES", "0") == "1"
+
 _poison_ds_workspace = False
 
 
@@ -332,7 +340,7 @@ def _scratch(p, kind, device):
     """Scratch of `kind` for the problem in `p`, or None when the problem does not take one or it would be larger than
     the limit for its head dim. Attached to `p`; the caller keeps the returned tensor alive."""
     need = _lib.load().fa_workspace_bytes(kind, C.byref(p))
-    limit = DS_WORKSPACE_WIDE_LIMIT_BYTES if p.head_dim > 128 else DS_WORKSPACE_LIMIT_BYTES
+    limit = DS_WORKSPACE_WIDE_LIMIT_BYTES if (p.head_dim > 128 or kind == _lib.FA_WS_FWD_P) else DS_WORKSPACE_LIMIT_BYTES
     if need <= 0 or need > limit:
         return None
     ws = torch.empty(need + 1024, dtype=torch.uint8, device=device)

@@ -118,8 +118,10 @@ typedef struct fa_attn_params {
      that is affordable; the Python layer uses it up to a cap and the reference never materialises anything.
      Head dims above 128 (to 512; above 256 without score modifiers): the scratch holds P and dS (4 bytes per score)
      and is what puts the backward on the tensor cores at all. fa_fwd, dense, head dims above 256 (to 512), no score modifier: scratch of
-     fa_workspace_bytes(FA_WS_FWD_P, p) bytes for the normalised P tiles (2 bytes per score); without it the forward
-     of those widths runs on the CUDA-core kernels. */
+     fa_workspace_bytes(FA_WS_FWD_P, p) bytes for the P tiles (2 bytes per score); without it the forward of those
+     widths runs on the CUDA-core kernels. fa_fwd, dense, fp32 inputs, head dims to 256, no score modifier: passing a
+     scratch of FA_WS_FWD_P bytes opts into tensor-core products (Q K^T in tf32, P V in fp16 with V rounded to fp16,
+     about 1e-3 absolute error on unit-variance inputs); without it fp32 inputs are computed in exact fp32. */
   void* ds_workspace;
   int64_t ds_workspace_bytes;
 } fa_attn_params;
@@ -227,7 +229,7 @@ enum fa_workspace_kind {
   FA_WS_PAGED_O_PARTIAL = 4,    /* fa_paged_params  -> o_partial */
   FA_WS_PAGED_LSE_PARTIAL = 5,  /* fa_paged_params  -> lse_partial */
   FA_WS_BWD_DS = 6,             /* fa_attn_params   -> ds_workspace of fa_bwd (optional; 0 when the problem cannot use one) */
-  FA_WS_FWD_P = 7               /* fa_attn_params   -> ds_workspace of fa_fwd (head dims above 256; 0 otherwise) */
+  FA_WS_FWD_P = 7               /* fa_attn_params   -> ds_workspace of fa_fwd (16-bit head dims above 256, fp32 to 256; else 0) */
 };
 FA_API int64_t fa_workspace_bytes(int32_t kind, const void* params);
 

@@ -99,6 +99,11 @@ def test_workspace_bytes_match_what_the_python_layer_allocates():
     assert lib.fa_workspace_bytes(_lib.FA_WS_FWD_P, ctypes.byref(a)) == 2 * 16 * (16 * 8 * 32768 + 16 * 128 * 8)
     a.head_dim = 256
     assert lib.fa_workspace_bytes(_lib.FA_WS_FWD_P, ctypes.byref(a)) == 0
+    # fp32 inputs (head dims to 256) that opt into tensor-core products: the same plus V rounded to fp16
+    a.dtype, a.head_dim = _lib.FA_F32, 128
+    assert lib.fa_workspace_bytes(_lib.FA_WS_FWD_P, ctypes.byref(a)) == (2 * 16 * (16 * 8 * 32768 + 16 * 128 * 8)
+                                                                          + 2 * 4 * 1000 * 128 * 2)
+    a.dtype = _lib.FA_F16
     a.head_dim = 128
     a.varlen, a.total_q = 1, 4096
     assert lib.fa_workspace_bytes(_lib.FA_WS_BWD_DS, ctypes.byref(a)) == 0

@@ -283,3 +283,39 @@ def test_wide_head_dim_modifiers(opts, bwd_path):
     assert_close_grad(dq, rdq, "dq")
     assert_close_grad(dk, rdk, "dk")
     assert_close_grad(dv, rdv, "dv")
+
+
+# fp32 inputs with the tensor-core switch on: Q K^T as tf32 products, P V in fp16; the bound is the one of the
+# reference's own fp32 test (tests/test_fp32_headdim.py:46 there: atol 2e-3, rtol 2e-3), N(0,1) inputs
+@pytest.mark.parametrize("B,H,Hk,Sq,Sk,D,opts", [
+    (2, 4, 4, 512, 512, 128, dict(causal=True)),
+    (1, 4, 4, 512, 512, 64, dict()),
+    (1, 8, 2, 300, 700, 128, dict(causal=True)),
+    (1, 2, 2, 700, 300, 256, dict(causal=True)),
+    (1, 2, 2, 77, 1000, 80, dict()),
+    (1, 4, 2, 640, 640, 128, dict(causal=True, window=(100, 0))),
+])
+def test_fp32_forward_on_tensor_cores(B, H, Hk, Sq, Sk, D, opts, monkeypatch):
+    from fa_b200 import interface
+
+    monkeypatch.setattr(interface, "FP32_ON_TENSOR_CORES", True)
+    monkeypatch.setattr(interface, "_poison_ds_workspace", True)
+    q = seeded(Sq + 1, B, H, Sq, D, dtype=torch.float32)
+    k = seeded(Sq + 2, B, Hk, Sk, D, dtype=torch.float32)
+    v = seeded(Sq + 3, B, Hk, Sk, D, dtype=torch.float32)
+    scale = 1.0 / math.sqrt(D)
+    causal, window = opts.get("causal", False), opts.get("window", (-1, -1))
+    out, lse = interface._forward(q, k, v, causal, scale, window, 0.0, None, None, 0.0, 0)
+    assert interface.last_kernel_path() == "tcgen05" and out.dtype == torch.float32
+    from oracle.attention_oracle import attention_ref
+    ro, rl = attention_ref(q.cpu(), k.cpu(), v.cpu(), causal=causal, softmax_scale=scale, window=window)
+    assert not torch.isnan(out).any()
+    torch.testing.assert_close(out.cpu(), ro, atol=2e-3, rtol=2e-3)
+    finite = torch.isfinite(rl)
+    assert torch.equal(torch.isfinite(lse.cpu()), finite)
+    assert (lse.cpu()[finite] - rl[finite]).abs().max().item() <= 2e-3
+    # the switch leaves the backward exact: gradients through the public op still match the fp32 bound
+    monkeypatch.setattr(interface, "FP32_ON_TENSOR_CORES", False)
+    out2, _ = interface._forward(q, k, v, causal, scale, window, 0.0, None, None, 0.0, 0)
+    assert interface.last_kernel_path() == "simt"
+    assert max_abs(out2, ro) <= FP32_O_TOL
