@@ -936,18 +936,22 @@ def other_shapes(device, tokens=2048, batch=2, heads=16, repeats=5):
         out[f"{batch}x{heads}x{tokens}x{head_dim}_{str(dtype)[6:]}_causal"] = {
             "fwd_us": fwd_us, "fwd_tflops": flops / fwd_us / 1e6,
             "fwd_bwd_us": both_us, "fwd_bwd_tflops": 3.5 * flops / both_us / 1e6}
-    # fp32 inputs with the tensor-core switch on (tf32 scores, fp16 P V; forward only, the backward stays exact)
+    # fp32 inputs with the tensor-core switch on (tf32 scores, fp16 tiles and operands, fp32 results)
     from fa_b200 import interface as _interface
     gen = torch.Generator(device=device).manual_seed(128)
-    q, k, v = (torch.randn(batch, heads, tokens, 128, device=device, dtype=torch.float32, generator=gen) for _ in range(3))
+    q, k, v, dout = (torch.randn(batch, heads, tokens, 128, device=device, dtype=torch.float32, generator=gen)
+                     for _ in range(4))
+    q.requires_grad_(True), k.requires_grad_(True), v.requires_grad_(True)
     previous, _interface.FP32_ON_TENSOR_CORES = _interface.FP32_ON_TENSOR_CORES, True
     try:
         with torch.no_grad():
             us = timed(lambda: fa_b200.flash_attention(q, k, v, causal=True))
+        both_us = timed(lambda: fa_b200.flash_attention(q, k, v, causal=True).backward(dout))
     finally:
         _interface.FP32_ON_TENSOR_CORES = previous
+    flops = 4.0 * batch * heads * tokens * tokens * 128 / 2
     out[f"{batch}x{heads}x{tokens}x128_float32_causal_tf32_switch_on"] = {
-        "fwd_us": us, "fwd_tflops": 4.0 * batch * heads * tokens * tokens * 128 / 2 / us / 1e6}
+        "fwd_us": us, "fwd_tflops": flops / us / 1e6, "fwd_bwd_us": both_us, "fwd_bwd_tflops": 3.5 * flops / both_us / 1e6}
     # one head of 512 channels over a 128 x 128 latent: the attention block of an image autoencoder, which the SDPA
     # hook serves when a whole pipeline runs under it (forward only, non-causal)
     gen = torch.Generator(device=device).manual_seed(512)

@@ -204,7 +204,8 @@ int64_t fa_workspace_bytes(int32_t kind, const void* params) {
       const fa_attn_params* p = static_cast<const fa_attn_params*>(params);
       if (p->batch <= 0 || p->heads_q <= 0 || p->seqlen_q <= 0 || p->seqlen_k <= 0)
         return fa::set_error(FA_ERR_INVALID_ARGUMENT, "workspace query: sizes must be positive");
-      if ((p->dtype != FA_F16 && p->dtype != FA_BF16) || p->head_dim > 512 || p->head_dim % 8) return 0;
+      if (p->head_dim > 512 || p->head_dim % 8) return 0;
+      if (p->dtype == FA_F32) return (p->head_dim > 256 || p->varlen) ? 0 : fa::bwd_wide_workspace_bytes(*p);
       return p->head_dim > 128 ? fa::bwd_wide_workspace_bytes(*p) : fa::bwd_ds_workspace_bytes(*p);
     }
     case FA_WS_FWD_P: {

@@ -1142,7 +1142,7 @@ int launch_fwd_wide_typed(const fa_attn_params& p, const BwdArgs& a0, cudaStream
   return 0;
 }
 
-// fp32 inputs: V rounded to fp16 once, rows made contiguous, for the O = P V product (P is 16-bit too).
+// fp32 inputs: an operand rounded to fp16 once, rows made contiguous, for the products over the 16-bit tiles.
 __global__ void __launch_bounds__(256) convert_rows_f16_kernel(const float* src, int64_t sb, int64_t sh, int64_t ss,
                                                                __half* dst, int heads, int rows, int head_dim, int64_t total8) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -1221,6 +1221,77 @@ int launch_fwd_wide_f32(const fa_attn_params& p, const BwdArgs& a0, cudaStream_t
   return launch_products<__half, kWD, float>(mv, mv, mv, a, FA_BWD_DQ, true, stream);
 }
 
+// Backward for fp32 inputs (head dims to 256, no score modifier): S and dP as tf32 products on the fp32 tiles, P and dS
+// as fp16 tiles, Q, K and dO rounded to fp16 for the three products, fp32 gradients.
+int launch_bwd_wide_f32(const fa_attn_params& p, const BwdArgs& a0, int parts, cudaStream_t stream) {
+  const int sms = sm_count();
+  cudaError_t e;
+  int rc;
+  const int64_t tiles = (int64_t)p.batch * p.heads_q * a0.ds_kt * a0.ds_qt;
+  const int64_t nq = (int64_t)p.batch * p.heads_q * p.seqlen_q * p.head_dim;
+  const int64_t nk = (int64_t)p.batch * p.heads_kv * p.seqlen_k * p.head_dim;
+  __half* q16 = reinterpret_cast<__half*>(reinterpret_cast<uint8_t*>(p.ds_workspace) + 2 * tiles * kTileWs);
+  __half* do16 = q16 + nq;
+  __half* k16 = do16 + nq;
+  if (parts & FA_BWD_DKDV) {
+    auto convert = [&](const void* src, const int64_t* st, __half* dst, int heads, int rows) {
+      const int64_t total8 = (int64_t)p.batch * heads * rows * (p.head_dim / 8);
+      const int64_t want = (total8 + 255) / 256;
+      convert_rows_f16_kernel<<<(int)(want < 8 * sms ? want : 8 * sms), 256, 0, stream>>>(
+          reinterpret_cast<const float*>(src), st[0], st[1], st[2], dst, heads, rows, p.head_dim, total8);
+    };
+    convert(p.q, p.q_strides, q16, p.heads_q, p.seqlen_q);
+    convert(p.dout, p.do_strides, do16, p.heads_q, p.seqlen_q);
+    convert(p.k, p.k_strides, k16, p.heads_kv, p.seqlen_k);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "backward conversion launch failed: %s", cudaGetErrorString(e));
+    CUtensorMap mq, mk, mv, mdo;
+    auto map32 = [&](CUtensorMap* m, const void* ptr, int rows, int heads, const int64_t* st) {
+      return make_tile_map_f32(m, ptr, p.head_dim, rows, heads, p.batch, st[2], st[1], st[0], 128);
+    };
+    rc = map32(&mq, p.q, p.seqlen_q, p.heads_q, p.q_strides);
+    if (!rc) rc = map32(&mk, p.k, p.seqlen_k, p.heads_kv, p.k_strides);
+    if (!rc) rc = map32(&mv, p.v, p.seqlen_k, p.heads_kv, p.v_strides);
+    if (!rc) rc = map32(&mdo, p.dout, p.seqlen_q, p.heads_q, p.do_strides);
+    if (rc) return rc;
+    const int n_items = a0.ds_qt * p.batch * p.heads_q;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(n_items < sms ? n_items : sms);
+    cfg.blockDim = dim3(kBwdThreads);
+    cfg.dynamicSmemBytes = FwdWideSmem::kBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr = {};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    {
+      auto kern = fwd_wide_kernel<__half, kModeProbsLse, float>;
+      e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdWideSmem::kBytes);
+      if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, kern, mq, mk, a0);
+      if (e == cudaSuccess) e = cudaGetLastError();
+      if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "backward probabilities launch failed: %s", cudaGetErrorString(e));
+    }
+    {
+      auto kern = fwd_wide_kernel<__half, kModeDScores, float>;
+      cfg.attrs = &attr;
+      cfg.numAttrs = 1;
+      e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdWideSmem::kBytes);
+      if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, kern, mdo, mv, a0);
+      if (e == cudaSuccess) e = cudaGetLastError();
+      if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "backward dS launch failed: %s", cudaGetErrorString(e));
+    }
+  }
+  CUtensorMap mq, mk, mdo;
+  auto map16 = [&](CUtensorMap* m, const __half* ptr, int rows, int heads) {
+    return make_tile_map(m, ptr, FA_F16, p.head_dim, rows, heads, p.batch, p.head_dim, (int64_t)rows * p.head_dim,
+                         (int64_t)heads * rows * p.head_dim, 128);
+  };
+  rc = map16(&mq, q16, p.seqlen_q, p.heads_q);
+  if (!rc) rc = map16(&mk, k16, p.seqlen_k, p.heads_kv);
+  if (!rc) rc = map16(&mdo, do16, p.seqlen_q, p.heads_q);
+  if (rc) return rc;
+  return launch_products<__half, kWD, float>(mq, mk, mdo, a0, parts, (parts & FA_BWD_DKDV) != 0, stream);
+}
+
 // Backward for head dims above 256: P tiles, then dS tiles, then the products once per 256 columns.
 template <typename T>
 int launch_bwd_vwide_typed(const fa_attn_params& p, const BwdArgs& a0, int parts, cudaStream_t stream) {
@@ -1283,11 +1354,32 @@ int launch_bwd_vwide_typed(const fa_attn_params& p, const BwdArgs& a0, int parts
 
 }  // namespace
 
+namespace {
+// An fp32 operand (batch, head, row, dim) TMA can read: unit inner stride, 16-byte aligned base and rows.
+bool tma_operand_ok_f32(const void* ptr, const int64_t strides[4], const int64_t sizes[3]) {
+  if (ptr == nullptr || (reinterpret_cast<uintptr_t>(ptr) & 15) || strides[3] != 1) return false;
+  for (int i = 0; i < 3; ++i)
+    if (sizes[i] > 1 && (strides[i] <= 0 || (strides[i] % 4) != 0)) return false;
+  return true;
+}
+}  // namespace
+
 // Head dims above 128 up to 512, dense, 16-bit, with a workspace for the P and dS tiles; above 256 without score
-// modifiers only.
+// modifiers only. fp32 inputs that bring a workspace opt into tf32 / fp16 products (head dims to 256, no modifier).
 bool bwd_wide_supported(const fa_attn_params& p) {
-  if (p.dtype != FA_F16 && p.dtype != FA_BF16) return false;
   if (p.varlen || p.ds_workspace == nullptr) return false;
+  if (p.dtype == FA_F32) {
+    if (p.head_dim < 8 || p.head_dim > kWD || p.head_dim % 8) return false;
+    if (p.softcap > 0.f || p.bias != nullptr || p.alibi_slopes != nullptr || p.dropout_p > 0.f || !(p.softmax_scale > 0.f))
+      return false;
+    const int64_t fq[3] = {p.batch, p.heads_q, p.seqlen_q};
+    const int64_t fk[3] = {p.batch, p.heads_kv, p.seqlen_k};
+    return tma_operand_ok_f32(p.q, p.q_strides, fq) && tma_operand_ok_f32(p.k, p.k_strides, fk) &&
+           tma_operand_ok_f32(p.v, p.v_strides, fk) && tma_operand_ok_f32(p.dout, p.do_strides, fq) &&
+           tma_operand_ok_f32(p.dq, p.dq_strides, fq) && tma_operand_ok_f32(p.dk, p.dk_strides, fk) &&
+           tma_operand_ok_f32(p.dv, p.dv_strides, fk);
+  }
+  if (p.dtype != FA_F16 && p.dtype != FA_BF16) return false;
   if (p.head_dim <= 128 || p.head_dim > 512 || p.head_dim % 8) return false;
   if (p.head_dim > kWD && (p.softcap > 0.f || p.bias != nullptr || p.alibi_slopes != nullptr || p.dropout_p > 0.f ||
                            !(p.softmax_scale > 0.f)))
@@ -1304,7 +1396,10 @@ bool bwd_wide_supported(const fa_attn_params& p) {
 int64_t bwd_wide_workspace_bytes(const fa_attn_params& p) {
   if (p.varlen) return 0;
   const int64_t tiles = (int64_t)p.batch * p.heads_q * ((p.seqlen_k + 127) / 128) * ((p.seqlen_q + 127) / 128);
-  return 2 * tiles * kTileWs;
+  int64_t bytes = 2 * tiles * kTileWs;
+  if (p.dtype == FA_F32)  // Q, dO and K rounded to fp16
+    bytes += 2 * ((int64_t)p.batch * p.head_dim * (2 * (int64_t)p.heads_q * p.seqlen_q + (int64_t)p.heads_kv * p.seqlen_k));
+  return bytes;
 }
 
 int launch_bwd_wide(const fa_attn_params& p, int parts, cudaStream_t stream) {
@@ -1362,6 +1457,7 @@ int launch_bwd_wide(const fa_attn_params& p, int parts, cudaStream_t stream) {
   a.ds_ws = p.ds_workspace;
   a.ds_kt = (p.seqlen_k + 127) / 128;
   a.ds_qt = (p.seqlen_q + 127) / 128;
+  if (p.dtype == FA_F32) return launch_bwd_wide_f32(p, a, parts, stream);
   if (p.head_dim > kWD)
     return p.dtype == FA_F16 ? launch_bwd_vwide_typed<__half>(p, a, parts, stream)
                              : launch_bwd_vwide_typed<__nv_bfloat16>(p, a, parts, stream);
@@ -1374,16 +1470,6 @@ int launch_bwd_wide(const fa_attn_params& p, int parts, cudaStream_t stream) {
 }
 
 // Forward for head dims above 256 up to 512: dense, 16-bit, no score modifier, with a workspace for the P tiles.
-namespace {
-// An fp32 operand (batch, head, row, dim) TMA can read: unit inner stride, 16-byte aligned base and rows.
-bool tma_operand_ok_f32(const void* ptr, const int64_t strides[4], const int64_t sizes[3]) {
-  if (ptr == nullptr || (reinterpret_cast<uintptr_t>(ptr) & 15) || strides[3] != 1) return false;
-  for (int i = 0; i < 3; ++i)
-    if (sizes[i] > 1 && (strides[i] <= 0 || (strides[i] % 4) != 0)) return false;
-  return true;
-}
-}  // namespace
-
 bool fwd_wide_supported(const fa_attn_params& p) {
   if (p.varlen || p.ds_workspace == nullptr || p.lse == nullptr) return false;
   if (p.softcap > 0.f || p.bias != nullptr || p.alibi_slopes != nullptr || p.dropout_p > 0.f) return false;

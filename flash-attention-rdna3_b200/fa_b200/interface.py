@@ -340,7 +340,8 @@ def _scratch(p, kind, device):
     """Scratch of `kind` for the problem in `p`, or None when the problem does not take one or it would be larger than
     the limit for its head dim. Attached to `p`; the caller keeps the returned tensor alive."""
     need = _lib.load().fa_workspace_bytes(kind, C.byref(p))
-    limit = DS_WORKSPACE_WIDE_LIMIT_BYTES if (p.head_dim > 128 or kind == _lib.FA_WS_FWD_P) else DS_WORKSPACE_LIMIT_BYTES
+    limit = (DS_WORKSPACE_WIDE_LIMIT_BYTES if (p.head_dim > 128 or kind == _lib.FA_WS_FWD_P or p.dtype == _lib.FA_F32)
+             else DS_WORKSPACE_LIMIT_BYTES)
     if need <= 0 or need > limit:
         return None
     ws = torch.empty(need + 1024, dtype=torch.uint8, device=device)
@@ -352,7 +353,10 @@ def _scratch(p, kind, device):
 
 
 def _ds_workspace(p, device):
-    """Scratch for the dS form of the dense backward (see _scratch)."""
+    """Scratch for the dS form of the dense backward (see _scratch). fp32 inputs only get one (and with it tensor-core
+    products) when FP32_ON_TENSOR_CORES is on."""
+    if p.dtype == _lib.FA_F32 and not FP32_ON_TENSOR_CORES:
+        return None
     return _scratch(p, _lib.FA_WS_BWD_DS, device)
 
 

@@ -107,7 +107,11 @@ def test_workspace_bytes_match_what_the_python_layer_allocates():
     a.head_dim = 128
     a.varlen, a.total_q = 1, 4096
     assert lib.fa_workspace_bytes(_lib.FA_WS_BWD_DS, ctypes.byref(a)) == 0
+    # fp32 inputs that opt into tensor-core products: the two tiles plus Q, dO and K rounded to fp16
     a.varlen, a.dtype = 0, _lib.FA_F32
+    assert lib.fa_workspace_bytes(_lib.FA_WS_BWD_DS, ctypes.byref(a)) == (2 * 2 * 16 * 16 * 8 * 32768
+                                                                           + 2 * 2 * 128 * (2 * 16 * 2048 + 4 * 1000))
+    a.head_dim = 512
     assert lib.fa_workspace_bytes(_lib.FA_WS_BWD_DS, ctypes.byref(a)) == 0
 
 

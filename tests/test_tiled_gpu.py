@@ -295,7 +295,7 @@ def test_wide_head_dim_modifiers(opts, bwd_path):
     (1, 2, 2, 77, 1000, 80, dict()),
     (1, 4, 2, 640, 640, 128, dict(causal=True, window=(100, 0))),
 ])
-def test_fp32_forward_on_tensor_cores(B, H, Hk, Sq, Sk, D, opts, monkeypatch):
+def test_fp32_on_tensor_cores(B, H, Hk, Sq, Sk, D, opts, monkeypatch):
     from fa_b200 import interface
 
     monkeypatch.setattr(interface, "FP32_ON_TENSOR_CORES", True)
@@ -314,7 +314,19 @@ def test_fp32_forward_on_tensor_cores(B, H, Hk, Sq, Sk, D, opts, monkeypatch):
     finite = torch.isfinite(rl)
     assert torch.equal(torch.isfinite(lse.cpu()), finite)
     assert (lse.cpu()[finite] - rl[finite]).abs().max().item() <= 2e-3
-    # the switch leaves the backward exact: gradients through the public op still match the fp32 bound
+    # the backward with the switch on: tf32 scores, fp16 tiles and operands, fp32 gradients. The reference's fp32 test
+    # allows atol 3e-3, rtol 3e-3 on gradients (tests/test_fp32_headdim.py:51 there); here the absolute part is 5e-3:
+    # on rows that see one or two keys dP and delta cancel, and the tf32 rounding of dO and V inside dP (delta is exact
+    # fp32) leaves up to 4e-3 on a handful of elements (13 of 524288 in the first case). Relative L2 stays below 2e-3.
+    dout = seeded(Sq + 4, B, H, Sq, D, dtype=torch.float32)
+    dq, dk, dv = interface._backward(dout, q, k, v, out, lse, causal, scale, window, 0.0, None, None, 0.0, 0)
+    assert interface.last_kernel_path() == "tcgen05" and dq.dtype == torch.float32
+    _, _, rdq, rdk, rdv = attention_grads_ref(q.cpu(), k.cpu(), v.cpu(), dout.cpu(), causal=causal, softmax_scale=scale,
+                                              window=window)
+    for got, want in ((dq, rdq), (dk, rdk), (dv, rdv)):
+        torch.testing.assert_close(got.cpu(), want, atol=5e-3, rtol=3e-3)
+        assert rel_l2(got, want) <= 2e-3, f"relative L2 {rel_l2(got, want):.3e}"
+    # switch off: exact fp32 on the CUDA cores
     monkeypatch.setattr(interface, "FP32_ON_TENSOR_CORES", False)
     out2, _ = interface._forward(q, k, v, causal, scale, window, 0.0, None, None, 0.0, 0)
     assert interface.last_kernel_path() == "simt"
