@@ -180,6 +180,31 @@ int32_t fa_combine(const fa_combine_params* p, void* stream) {
   return fa::launch_combine(*p, static_cast<cudaStream_t>(stream));
 }
 
+int32_t fa_peer_merge(const fa_peer_merge_params* p, void* stream) {
+  fa::NvtxRange r("fa_peer_merge");
+  if (p == nullptr) return fa::set_error(FA_ERR_INVALID_ARGUMENT, "params is NULL");
+  return fa::launch_peer_merge(*p, static_cast<cudaStream_t>(stream));
+}
+
+int32_t fa_enable_peer_access(int32_t peer_device) {
+  int dev = 0, can = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fa::set_error(FA_ERR_DEVICE, "cudaGetDevice failed: %s", cudaGetErrorString(e));
+  if (dev == peer_device) return 0;
+  e = cudaDeviceCanAccessPeer(&can, dev, peer_device);
+  if (e != cudaSuccess || !can) {
+    cudaGetLastError();
+    return fa::set_error(FA_ERR_UNSUPPORTED, "device %d has no peer path to device %d", dev, peer_device);
+  }
+  e = cudaDeviceEnablePeerAccess(peer_device, 0);
+  if (e == cudaErrorPeerAccessAlreadyEnabled) {
+    cudaGetLastError();  // not an error for this call
+    return 0;
+  }
+  if (e != cudaSuccess) return fa::set_error(FA_ERR_DEVICE, "cudaDeviceEnablePeerAccess failed: %s", cudaGetErrorString(e));
+  return 0;
+}
+
 int32_t fa_decode_paged(const fa_paged_params* p, void* stream) {
   fa::NvtxRange r("fa_decode_paged");
   if (p == nullptr) return fa::set_error(FA_ERR_INVALID_ARGUMENT, "params is NULL");

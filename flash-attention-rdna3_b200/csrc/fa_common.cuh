@@ -326,6 +326,7 @@ int launch_bwd_simt(const fa_attn_params& p, int parts, cudaStream_t stream);   
 int launch_tiled_fwd(const fa_attn_params& p, cudaStream_t stream);    // fa_tiled_fwd.cu
 int launch_tiled_dq(const fa_attn_params& p, cudaStream_t stream);     // fa_tiled_dq.cu
 int launch_tiled_dkdv(const fa_attn_params& p, cudaStream_t stream);   // fa_tiled_dkdv.cu
+int launch_peer_merge(const fa_peer_merge_params& p, cudaStream_t stream);  // fa_decode.cu
 int launch_bwd_delta(const fa_attn_params& p, cudaStream_t stream);     // fa_simt.cu
 int launch_decode_splitk(const fa_decode_params& p, cudaStream_t stream);  // fa_decode.cu
 int launch_combine(const fa_combine_params& p, cudaStream_t stream);       // fa_decode.cu

@@ -376,7 +376,39 @@ struct CombineArgs {
   int n1, n2;                       // row = (i0 * n1 + i1) * n2 + i2
   int64_t os0, os1, os2, osd;       // element strides of out for (i0, i1, i2, d)
   float* lse_out;
+  // multi-GPU merge: partial s (s != wait_skip) may be read once wait_flags[s] >= wait_value (raised by rank s over
+  // NVLink after its stores); null for every other use
+  const int* wait_flags;
+  int wait_count, wait_skip, wait_value;
+  int* status;
 };
+
+// Bounded wait of a merge CTA for the partials other GPUs deliver. Returns false (and records it) when a flag did not
+// arrive in about a second; the CTA then writes nothing.
+__device__ __forceinline__ bool wait_for_peers(const CombineArgs& a) {
+  __shared__ int lost;
+  if (threadIdx.x == 0) lost = 0;
+  __syncthreads();
+  const int t = threadIdx.x;
+  if (t < a.wait_count && t != a.wait_skip) {
+    bool seen = false;
+    for (uint32_t i = 0; i < (1u << 22); ++i) {
+      int v;
+      asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(a.wait_flags + t) : "memory");
+      if (v >= a.wait_value) {
+        seen = true;
+        break;
+      }
+      __nanosleep(200);
+    }
+    if (!seen) {
+      lost = 1;
+      if (a.status != nullptr) atomicCAS(a.status, 0, 701);
+    }
+  }
+  __syncthreads();
+  return lost == 0;
+}
 
 // One 256-thread CTA per output row. The merge weights of all partials are computed once into shared memory;
 // then eight groups of 32 lanes each take every eighth partial (independent loads, all in flight together)
@@ -388,6 +420,7 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(const CombineA
   // Launched as a programmatic dependent of the kernel that writes the partials, this CTA may already be resident
   // while that kernel drains; it goes on once that grid has completed (at once when launched the ordinary way).
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (a.wait_flags != nullptr && !wait_for_peers(a)) return;
   __shared__ float w_s[kCombineThreads];
   __shared__ float red_s[8][kCombineMaxD];
   __shared__ float stat_s[2];
@@ -611,7 +644,7 @@ int launch_combine_internal(int rows, int D, int splits, const float* o_partial,
                             int64_t os1, int64_t os2, int64_t osd, float* lse_out, cudaStream_t stream,
                             bool dependent) {
   CombineArgs a{rows, D, splits, o_partial, o_split_stride, o_row_stride, lse_partial, lse_split_stride,
-                lse_row_stride, out, out_dtype, n1, n2, os0, os1, os2, osd, lse_out};
+                lse_row_stride, out, out_dtype, n1, n2, os0, os1, os2, osd, lse_out, nullptr, 0, 0, 0, nullptr};
   if (D > kCombineMaxD || D % 4 || o_split_stride % 4 || o_row_stride % 4 ||
       (reinterpret_cast<uintptr_t>(o_partial) & 15))
     return set_error(FA_ERR_UNSUPPORTED, "combine needs head_dim <= %d, and 16-byte aligned partial rows", kCombineMaxD);
@@ -632,6 +665,62 @@ int launch_combine_internal(int rows, int D, int splits, const float* o_partial,
   const cudaError_t e = wide ? cudaLaunchKernelEx(&cfg, combine_wide_kernel, a) : cudaLaunchKernelEx(&cfg, combine_kernel, a);
   if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "combine launch failed: %s", cudaGetErrorString(e));
   return check_launch("combine");
+}
+
+// ---------------------------------------------------------------------------------------------
+// multi-GPU merge without a collective
+// ---------------------------------------------------------------------------------------------
+struct PeerPushArgs {
+  const float4* src;
+  int64_t n4;
+  float4* dst[FA_MAX_PEERS];
+  int* flag[FA_MAX_PEERS];
+  int rank, epoch;
+};
+
+// One CTA per peer: copies this rank's slot into the peer's buffer (plain 16-byte stores over NVLink), makes the
+// stores visible system-wide, then raises the peer's flag for this rank.
+__global__ void __launch_bounds__(1024) peer_push_kernel(const PeerPushArgs a) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const int peer = blockIdx.x < a.rank ? blockIdx.x : blockIdx.x + 1;
+  float4* dst = a.dst[peer];
+  for (int64_t i = threadIdx.x; i < a.n4; i += blockDim.x) dst[i] = a.src[i];
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(a.flag[peer]), "r"(a.epoch) : "memory");
+}
+
+int launch_peer_merge(const fa_peer_merge_params& p, cudaStream_t stream) {
+  if (p.world < 1 || p.world > FA_MAX_PEERS || p.rank < 0 || p.rank >= p.world)
+    return set_error(FA_ERR_INVALID_ARGUMENT, "peer merge: world must be in [1, %d] and rank inside it", FA_MAX_PEERS);
+  if (p.rows <= 0 || p.head_dim <= 0 || p.head_dim % 4 || p.head_dim > kCombineMaxD || p.epoch <= 0)
+    return set_error(FA_ERR_INVALID_ARGUMENT, "peer merge: rows, head_dim (multiple of 4) and epoch must be positive");
+  if (p.slot_floats < (int64_t)p.rows * (p.head_dim + 1) || p.slot_floats % 4)
+    return set_error(FA_ERR_INVALID_ARGUMENT, "peer merge: a slot holds rows * (head_dim + 1) floats, a multiple of four");
+  for (int r = 0; r < p.world; ++r)
+    if (p.peer_base[r] == nullptr || p.peer_flags[r] == nullptr || (reinterpret_cast<uintptr_t>(p.peer_base[r]) & 15))
+      return set_error(FA_ERR_INVALID_ARGUMENT, "peer merge: buffer %d is NULL or not 16-byte aligned", r);
+  if (p.out == nullptr) return set_error(FA_ERR_INVALID_ARGUMENT, "peer merge: out is NULL");
+  float* local = p.peer_base[p.rank];
+  if (p.world > 1) {
+    PeerPushArgs a = {};
+    a.src = reinterpret_cast<const float4*>(local + (int64_t)p.rank * p.slot_floats);
+    a.n4 = p.slot_floats / 4;
+    for (int r = 0; r < p.world; ++r) {
+      a.dst[r] = reinterpret_cast<float4*>(p.peer_base[r] + (int64_t)p.rank * p.slot_floats);
+      a.flag[r] = p.peer_flags[r] + p.rank;
+    }
+    a.rank = p.rank;
+    a.epoch = p.epoch;
+    peer_push_kernel<<<p.world - 1, 1024, 0, stream>>>(a);
+    int rc = check_launch("peer push");
+    if (rc) return rc;
+  }
+  CombineArgs c{p.rows, p.head_dim, p.world, local, p.slot_floats, p.head_dim, local + (int64_t)p.rows * p.head_dim,
+                p.slot_floats, 1, p.out, p.out_dtype, 1, p.rows, 0, 0, p.out_row_stride, 1, p.lse_out,
+                p.world > 1 ? p.peer_flags[p.rank] : nullptr, p.world, p.rank, p.epoch, p.status};
+  combine_kernel<<<p.rows, kCombineThreads, 0, stream>>>(c);
+  return check_launch("peer merge");
 }
 
 int launch_combine(const fa_combine_params& p, cudaStream_t stream) {

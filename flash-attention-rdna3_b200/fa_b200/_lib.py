@@ -16,7 +16,7 @@ FA_BWD_DELTA, FA_BWD_DKDV, FA_BWD_DQ = 1, 2, 4
 FA_WS_BWD_DELTA, FA_WS_DECODE_O_PARTIAL, FA_WS_DECODE_LSE_PARTIAL, FA_WS_PAGED_O_PARTIAL, FA_WS_PAGED_LSE_PARTIAL = 1, 2, 3, 4, 5
 FA_WS_BWD_DS = 6
 FA_WS_FWD_P = 7
-ABI_VERSION = 2
+ABI_VERSION = 3
 
 I64x4 = C.c_int64 * 4
 I64x3 = C.c_int64 * 3
@@ -75,6 +75,23 @@ class CombineParams(C.Structure):
     ]
 
 
+FA_MAX_PEERS = 16
+
+
+class PeerMergeParams(C.Structure):
+    _fields_ = [
+        ("world", C.c_int32), ("rank", C.c_int32),
+        ("out_dtype", C.c_int32), ("rows", C.c_int32), ("head_dim", C.c_int32),
+        ("epoch", C.c_int32),
+        ("slot_floats", C.c_int64),
+        ("peer_base", C.c_void_p * FA_MAX_PEERS),
+        ("peer_flags", C.c_void_p * FA_MAX_PEERS),
+        ("out", C.c_void_p), ("out_row_stride", C.c_int64),
+        ("lse_out", C.c_void_p),
+        ("status", C.c_void_p),
+    ]
+
+
 class PagedParams(C.Structure):
     _fields_ = [
         ("dtype", C.c_int32),
@@ -124,6 +141,8 @@ SYMBOLS = {
     "fa_tiny_fwd": (C.c_int32, [C.POINTER(TinyParams), C.c_void_p]),
     "fa_workspace_bytes": (C.c_int64, [C.c_int32, C.c_void_p]),
     "fa_test_decode_fault": (None, [C.c_uint32, C.c_int32]),
+    "fa_peer_merge": (C.c_int32, [C.POINTER(PeerMergeParams), C.c_void_p]),
+    "fa_enable_peer_access": (C.c_int32, [C.c_int32]),
 }
 
 _lib = None

@@ -15,6 +15,13 @@ The reference is single-GPU (no communication code anywhere in fa_rdna3); two mo
    Shards without keys contribute ``LSE = -inf`` and are ignored by the merge.
 
 The collective only ever reads local memory: partials are gathered by NCCL first and merged afterwards.
+
+Between the GPUs of one node the gather needs no collective at all (`transport="push"`, the default where it can be
+set up): every rank keeps its gather buffer in memory that the other ranks have mapped through CUDA IPC, the local
+kernels write this rank's partial into its own slot, and `fa_peer_merge` copies that slot into every peer's buffer with
+ordinary stores over NVLink, raises a flag there, waits (bounded) for the peers' flags on its own buffer and merges.
+Only stores cross the link, nothing reads peer memory, no TMA or multicast instruction is involved. Two buffers
+alternate between calls so that a fast rank cannot overwrite a slot a slow rank is still merging.
 """
 import ctypes as C
 import math
@@ -23,7 +30,7 @@ import torch
 
 from . import _lib
 from .interface import (_DTYPE_CODE, _paged_balanced_slots, _paged_launch, _paged_splits_b200,
-                        _paged_tensor_core_ok, _stream)
+                        _paged_tensor_core_ok, _status_word, _stream)
 from ._validation import validate_inference_only, validate_paged_inputs, validate_softmax_scale
 
 
@@ -80,16 +87,98 @@ def _gather_buffer(world, rows, head_dim, device):
     return flat, o, lse
 
 
+class _PeerGather:
+    """Gather buffers of all ranks of `group` for partials of (rows, head_dim), mapped into this process: two sets of
+    `world` slots and `world` flags per rank, in one allocation per rank that the others open through CUDA IPC."""
+
+    def __init__(self, world, rank, rows, head_dim, device, group):
+        import torch.distributed as dist
+        from torch.multiprocessing.reductions import reduce_tensor
+
+        self.world, self.rank, self.rows, self.head_dim = world, rank, rows, head_dim
+        self.slot = -(-(rows * (head_dim + 1)) // 4) * 4
+        self.set_floats = world * self.slot
+        flag_floats = -(-world // 4) * 4
+        # [set 0 slots][set 1 slots][set 0 flags][set 1 flags]; zero-initialised: no flag has been raised
+        self.local = torch.zeros(2 * self.set_floats + 2 * flag_floats, dtype=torch.float32, device=device)
+        self.flag_offset = [2 * self.set_floats + s * flag_floats for s in range(2)]
+        rebuild, args = reduce_tensor(self.local)
+        everyone = [None] * world
+        dist.all_gather_object(everyone, args, group=group)
+        self.peers = [self.local if r == rank else rebuild(*everyone[r]) for r in range(world)]
+        lib = _lib.load()
+        with torch.cuda.device(device):
+            for r, t in enumerate(self.peers):
+                if r != rank:
+                    _lib.check(lib.fa_enable_peer_access(t.device.index))
+        self.calls = 0
+
+    def views(self, which):
+        """(o, lse) views of this rank's own slot in set `which`, where the local kernels write the partial."""
+        base = which * self.set_floats + self.rank * self.slot
+        mine = self.local[base:base + self.slot]
+        return (mine[:self.rows * self.head_dim].view(self.rows, self.head_dim),
+                mine[self.rows * self.head_dim:self.rows * (self.head_dim + 1)])
+
+    def merge(self, which, epoch, out_dtype, device):
+        lib = _lib.load()
+        out = torch.empty(self.rows, self.head_dim, dtype=out_dtype, device=device)
+        p = _lib.PeerMergeParams()
+        p.world, p.rank, p.out_dtype, p.rows, p.head_dim = self.world, self.rank, _DTYPE_CODE[out_dtype], self.rows, self.head_dim
+        p.epoch, p.slot_floats = epoch, self.slot
+        for r, t in enumerate(self.peers):
+            p.peer_base[r] = t.data_ptr() + which * self.set_floats * 4
+            p.peer_flags[r] = t.data_ptr() + self.flag_offset[which] * 4
+        p.out, p.out_row_stride = out.data_ptr(), self.head_dim
+        p.status = _status_word(device).data_ptr()
+        with torch.cuda.device(device):
+            _lib.check(lib.fa_peer_merge(C.byref(p), _stream(device)))
+        return out
+
+
+_peer_gathers = {}
+_push_unavailable = set()
+
+
+def _peer_gather(world, rank, rows, head_dim, device, group):
+    """The cached _PeerGather for this problem, or None when the ranks cannot all set one up (every rank then takes the
+    NCCL path: the decision is taken together, one object all-gather per new problem shape)."""
+    import torch.distributed as dist
+
+    key = (id(group), world, rank, rows, head_dim, torch.device(device).index)
+    if key in _peer_gathers:
+        return _peer_gathers[key]
+    if id(group) in _push_unavailable:
+        return None
+    made, error = None, None
+    try:
+        made = _PeerGather(world, rank, rows, head_dim, device, group)
+    except Exception as exc:   # no IPC in this environment, no peer path, ...
+        error = f"{type(exc).__name__}: {exc}"
+    verdicts = [None] * world
+    dist.all_gather_object(verdicts, error, group=group)
+    if any(v is not None for v in verdicts):
+        _push_unavailable.add(id(group))
+        import warnings
+        warnings.warn("fa_b200: peer-store merge unavailable, using the NCCL all-gather: "
+                      + "; ".join(f"rank {r}: {v}" for r, v in enumerate(verdicts) if v is not None), RuntimeWarning)
+        return None
+    _peer_gathers[key] = made
+    return made
+
+
 def paged_decode_kv_sharded(query, k_cache, v_cache, block_table, context_lens, softmax_scale=None, *,
                             group=None, max_context_len=None, num_splits=None, check_ranks_agree=True,
-                            _local_partial=None, _merge=None):
+                            transport=None, _local_partial=None, _merge=None):
     """Paged decode with the KV pages of each sequence sharded block-cyclically over the ranks of `group`.
 
     Every rank passes the full ``query``, ``block_table`` and ``context_lens`` and its own page pool
     (only the pages of its logical blocks are read). Returns the merged ``(batch, q_heads, head_dim)``
     result on every rank. ``check_ranks_agree=False`` skips the exchange of problem shapes that guards against
     ranks describing different problems (an object all-gather through the host, the only synchronising step of a
-    call). ``_local_partial`` / ``_merge`` replace the CUDA kernels in CPU tests of the protocol.
+    call). ``transport``: "push" (peer stores between the GPUs of one node, no collective), "nccl" (one all-gather) or
+    None: push where it can be set up, else NCCL - all ranks must pass the same value.
+    ``_local_partial`` / ``_merge`` replace the CUDA kernels in CPU tests of the protocol.
     """
     import torch.distributed as dist
 
@@ -113,7 +202,20 @@ def paged_decode_kv_sharded(query, k_cache, v_cache, block_table, context_lens, 
             raise ValueError(f"ranks disagree on the decode problem: {all_meta}")
 
     rows = batch * q_heads
-    flat, g_o, g_lse = _gather_buffer(world, rows, head_dim, query.device)
+    if transport not in (None, "push", "nccl"):
+        raise ValueError('transport must be None, "push" or "nccl"')
+    peer = None
+    if _local_partial is None and transport != "nccl" and world > 1 and world <= _lib.FA_MAX_PEERS:
+        peer = _peer_gather(world, rank, rows, head_dim, query.device, group)
+        if peer is None and transport == "push":
+            raise RuntimeError("paged_decode_kv_sharded: the peer-store transport could not be set up on every rank")
+    if peer is not None:
+        which, epoch = peer.calls % 2, peer.calls // 2 + 1
+        peer.calls += 1
+        mine_o, mine_lse = peer.views(which)
+    else:
+        flat, g_o, g_lse = _gather_buffer(world, rows, head_dim, query.device)
+        mine_o, mine_lse = g_o[rank], g_lse[rank]
     if _local_partial is None:
         sm_count = torch.cuda.get_device_properties(query.device).multi_processor_count
         capacity = block_table.shape[1] * k_cache.shape[1]
@@ -132,11 +234,13 @@ def paged_decode_kv_sharded(query, k_cache, v_cache, block_table, context_lens, 
         # the local kernels write this rank's partial straight into its slot of the gather buffer
         _paged_launch(query, k_cache, v_cache, block_table, context_lens, scale, splits, first_block=rank,
                       block_step=world, want_lse=True, out_f32=True, balance=balance,
-                      out_buffers=(g_o[rank].view(batch, q_heads, head_dim), g_lse[rank].view(batch, q_heads)))
+                      out_buffers=(mine_o.view(batch, q_heads, head_dim), mine_lse.view(batch, q_heads)))
     else:
         o_r, lse_r = _local_partial(query, k_cache, v_cache, block_table, context_lens, scale, rank, world)
         g_o[rank].copy_(o_r.reshape(rows, head_dim))
         g_lse[rank].copy_(lse_r.reshape(rows))
+    if peer is not None:   # stores into the peers' buffers, flags, bounded wait, merge: no collective
+        return peer.merge(which, epoch, query.dtype, query.device).reshape(batch, q_heads, head_dim)
     dist.all_gather_into_tensor(flat.view(-1), flat[rank], group=group)   # in place: the input is this rank's slot
     merge = _merge_partials_cuda if _merge is None else _merge
     return merge(g_o, g_lse, query.dtype).reshape(batch, q_heads, head_dim)

@@ -31,7 +31,7 @@
 extern "C" {
 #endif
 
-#define FA_B200_ABI_VERSION 2
+#define FA_B200_ABI_VERSION 3
 
 #if defined(__GNUC__)
 #define FA_API __attribute__((visibility("default")))
@@ -165,6 +165,29 @@ typedef struct fa_combine_params {
   float* lse_out;
 } fa_combine_params;
 
+/* Multi-GPU merge of per-rank partials without a collective (no counterpart in the reference, which is single-GPU;
+   the merge rule is fa_rdna3/kernels/decode.py:101-122). Every rank owns a buffer of `world` slots of slot_floats
+   floats (a slot: rows * head_dim partial values, then rows LSEs) and `world` int32 flags, mapped into every other
+   rank's address space (CUDA IPC or any other peer mapping: the caller's business). A call copies this rank's slot
+   `rank` of its own buffer into slot `rank` of every peer's buffer with ordinary stores over NVLink, then raises
+   flag `rank` there to `epoch`; a second kernel waits (bounded; a lost wait sets `status` and leaves out unwritten)
+   until every flag of the local buffer has reached `epoch` and merges the local slots into `out`. Only stores cross
+   the link; nothing here reads peer memory, and no TMA or multicast instruction is involved. `epoch` must grow with
+   every call on a buffer; callers alternate between two buffers so that a fast rank cannot overwrite a slot a slow
+   rank is still merging. */
+#define FA_MAX_PEERS 16
+typedef struct fa_peer_merge_params {
+  int32_t world, rank;
+  int32_t out_dtype, rows, head_dim;
+  int32_t epoch;
+  int64_t slot_floats;
+  float* peer_base[FA_MAX_PEERS];     /* peer_base[r]: rank r's buffer as this process addresses it; [rank] = local */
+  int32_t* peer_flags[FA_MAX_PEERS];  /* likewise the flag arrays */
+  void* out; int64_t out_row_stride;
+  float* lse_out;                     /* may be NULL */
+  int32_t* status;                    /* may be NULL */
+} fa_peer_merge_params;
+
 /* Paged-KV decode: q (batch, heads_q, head_dim); caches (num_blocks, block_size, heads_kv, head_dim);
    block_table int32 (batch, max_blocks) and context_lens int32 (batch) with arbitrary strides.
    first_block / block_step restrict the call to logical blocks first_block, first_block + block_step, ...
@@ -269,6 +292,13 @@ FA_API int32_t fa_decode_splitk_noalloc(const fa_decode_params* p, void* stream)
 /* Stand-alone LSE merge; also merges per-GPU shard partials. Replaces the _attention_combine launch,
    fa_rdna3/kernels/decode.py:80-125. */
 FA_API int32_t fa_combine(const fa_combine_params* p, void* stream);
+
+/* See fa_peer_merge_params. */
+FA_API int32_t fa_peer_merge(const fa_peer_merge_params* p, void* stream);
+
+/* Lets kernels of the current device store into memory of `peer_device` (cudaDeviceEnablePeerAccess; already enabled
+   counts as success). Returns FA_ERR_UNSUPPORTED when the two devices have no peer path. */
+FA_API int32_t fa_enable_peer_access(int32_t peer_device);
 
 /* Paged-KV decode. Replaces the _attention_decode_paged (+ combine) launches,
    fa_rdna3/interface.py:703-727 (kernel fa_rdna3/kernels/paged.py:17-89). */

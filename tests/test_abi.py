@@ -29,7 +29,7 @@ def test_library_loads_and_exports_every_symbol():
     lib = ctypes.CDLL(_lib.LIB_PATH)
     for name in declared_symbols():
         assert hasattr(lib, name), name
-    assert _lib.load().fa_abi_version() == 2
+    assert _lib.load().fa_abi_version() == 3
 
 
 def test_struct_sizes_match_the_header():

@@ -1,5 +1,5 @@
-"""Two ranks on two GPUs over NCCL: KV-sharded paged decode against the single-GPU result, and the batch x head
-partition of the dense path. Skipped when fewer than two GPUs are visible. Ranks are child processes; every rank
+"""Two ranks on two GPUs: KV-sharded paged decode against the single-GPU result over NCCL and over peer stores, and
+the batch x head partition of the dense path. Skipped when fewer than two GPUs are visible. Ranks are child processes; every rank
 joins and leaves the process group between steps, none of them fails on purpose."""
 import os
 import socket
@@ -36,8 +36,22 @@ def _worker(rank, world, port, results):
 
         # every rank builds the same problem on its own GPU; rank r only reads the pages of blocks r, r + world, ...
         q, kc, vc, table, ctx = make_paged(3, 32, 8, 128, 16, [4000, 0, 777], seed=11)
-        out = fd.paged_decode_kv_sharded(q, kc, vc, table, ctx)
+        out = fd.paged_decode_kv_sharded(q, kc, vc, table, ctx, transport="nccl")
         whole = fa_b200.flash_attention_decode_paged(q, kc, vc, table, ctx)
+        # the same through peer stores instead of the all-gather: several calls in a row (the two buffer sets and the
+        # epochs), then a different query so that a stale slot would show
+        push_error, push_diff = None, 0.0
+        try:
+            for _ in range(5):
+                pushed = fd.paged_decode_kv_sharded(q, kc, vc, table, ctx, transport="push")
+                push_diff = max(push_diff, max_abs(pushed, out))
+            q2 = (q.float() * 0.5 + 0.25).to(q.dtype)
+            want2 = fd.paged_decode_kv_sharded(q2, kc, vc, table, ctx, transport="nccl")
+            for _ in range(3):
+                push_diff = max(push_diff, max_abs(fd.paged_decode_kv_sharded(q2, kc, vc, table, ctx, transport="push"),
+                                                   want2))
+        except Exception as exc:   # reported to the parent, which fails the test with the reason
+            push_error = f"{type(exc).__name__}: {exc}"
         ref, _ = oracle.paged_ref(q.cpu(), kc.cpu(), vc.cpu(), table.cpu(), ctx.cpu())
         err_sharded = max_abs(out, ref)
         err_vs_whole = max_abs(out, whole)
@@ -52,7 +66,7 @@ def _worker(rank, world, port, results):
         err_dense = max_abs(torch.cat(parts, dim=1), full)
         torch.cuda.synchronize()
         fa_b200.check_status(torch.device("cuda", rank))
-        results[rank] = (err_sharded, err_vs_whole, err_dense)
+        results[rank] = (err_sharded, err_vs_whole, err_dense, push_error, push_diff)
     finally:
         dist.destroy_process_group()
 
@@ -72,7 +86,9 @@ def test_two_ranks_kv_sharded_decode_and_head_partition():
             p.join(300)
         assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
         for rank in range(2):
-            err_sharded, err_vs_whole, err_dense = results[rank]
+            err_sharded, err_vs_whole, err_dense, push_error, push_diff = results[rank]
+            assert push_error is None, (rank, push_error)
+            assert push_diff == 0.0, (rank, push_diff)           # same partials, same merge order: identical
             assert err_sharded <= 2e-3, (rank, err_sharded)      # fp16 output tolerance against the oracle
             assert err_vs_whole <= 2e-3, (rank, err_vs_whole)
             assert err_dense == 0.0, (rank, err_dense)           # same kernels on the same rows: identical
