@@ -422,7 +422,7 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(const CombineA
   asm volatile("griddepcontrol.wait;" ::: "memory");
   if (a.wait_flags != nullptr && !wait_for_peers(a)) return;
   __shared__ float w_s[kCombineThreads];
-  __shared__ float red_s[8][kCombineMaxD];
+  __shared__ __align__(16) float red_s[8][kCombineMaxD];  // written as float4
   __shared__ float stat_s[2];
   const int tid = threadIdx.x, grp = tid / 32, lane = tid % 32;
   const int row = blockIdx.x;

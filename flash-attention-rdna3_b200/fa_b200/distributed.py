@@ -99,18 +99,41 @@ class _PeerGather:
         self.slot = -(-(rows * (head_dim + 1)) // 4) * 4
         self.set_floats = world * self.slot
         flag_floats = -(-world // 4) * 4
-        # [set 0 slots][set 1 slots][set 0 flags][set 1 flags]; zero-initialised: no flag has been raised
-        self.local = torch.zeros(2 * self.set_floats + 2 * flag_floats, dtype=torch.float32, device=device)
+        # [set 0 slots][set 1 slots][set 0 flags][set 1 flags][probe words]; zero-initialised: no flag has been raised
+        self.local = torch.zeros(2 * self.set_floats + 3 * flag_floats, dtype=torch.float32, device=device)
         self.flag_offset = [2 * self.set_floats + s * flag_floats for s in range(2)]
+        probe_offset = 2 * self.set_floats + 2 * flag_floats
         rebuild, args = reduce_tensor(self.local)
         everyone = [None] * world
-        dist.all_gather_object(everyone, args, group=group)
-        self.peers = [self.local if r == rank else rebuild(*everyone[r]) for r in range(world)]
+        dist.all_gather_object(everyone, (torch.device(device).index, args), group=group)
         lib = _lib.load()
+        mine = torch.device(device).index
+        self.peers = []
         with torch.cuda.device(device):
+            for r, (owner, peer_args) in enumerate(everyone):
+                if r == rank:
+                    self.peers.append(self.local)
+                    continue
+                _lib.check(lib.fa_enable_peer_access(owner))
+                # An IPC handle is mapped into the address space of the device that is current when it is opened, and
+                # the kernels that store through it run on THIS rank's GPU: open it as memory of this device (argument
+                # 6 of the rebuild call is the device index), not of the owner's as a consumer on the same GPU would.
+                peer_args = list(peer_args)
+                peer_args[6] = mine
+                self.peers.append(rebuild(*peer_args))
+            # Before any kernel stores through these mappings, prove them with copies the driver validates: every rank
+            # writes its number into its word of every peer's probe area, and after a barrier finds the peers' numbers
+            # in its own.
+            stamp = torch.full((1,), float(rank + 1), dtype=torch.float32, device=device)
             for r, t in enumerate(self.peers):
                 if r != rank:
-                    _lib.check(lib.fa_enable_peer_access(t.device.index))
+                    t[probe_offset + rank:probe_offset + rank + 1].copy_(stamp)
+            torch.cuda.synchronize(device)
+            dist.barrier(group=group)
+            seen = self.local[probe_offset:probe_offset + world].tolist()
+            missing = [r for r in range(world) if r != rank and seen[r] != float(r + 1)]
+            if missing:
+                raise RuntimeError(f"peer buffers of rank(s) {missing} did not take a store from this process")
         self.calls = 0
 
     def views(self, which):
