@@ -92,6 +92,8 @@ class _PeerGather:
     `world` slots and `world` flags per rank, in one allocation per rank that the others open through CUDA IPC."""
 
     def __init__(self, world, rank, rows, head_dim, device, group):
+        """Collective: every rank of `group` runs the same three collectives whatever fails locally (a failure is kept
+        in `self.error` and reported by the caller's vote), so no rank is left waiting in one of them."""
         import torch.distributed as dist
         from torch.multiprocessing.reductions import reduce_tensor
 
@@ -99,42 +101,53 @@ class _PeerGather:
         self.slot = -(-(rows * (head_dim + 1)) // 4) * 4
         self.set_floats = world * self.slot
         flag_floats = -(-world // 4) * 4
-        # [set 0 slots][set 1 slots][set 0 flags][set 1 flags][probe words]; zero-initialised: no flag has been raised
-        self.local = torch.zeros(2 * self.set_floats + 3 * flag_floats, dtype=torch.float32, device=device)
         self.flag_offset = [2 * self.set_floats + s * flag_floats for s in range(2)]
         probe_offset = 2 * self.set_floats + 2 * flag_floats
-        rebuild, args = reduce_tensor(self.local)
-        everyone = [None] * world
-        dist.all_gather_object(everyone, (torch.device(device).index, args), group=group)
-        lib = _lib.load()
+        self.calls, self.error, self.peers = 0, None, []
         mine = torch.device(device).index
-        self.peers = []
-        with torch.cuda.device(device):
-            for r, (owner, peer_args) in enumerate(everyone):
-                if r == rank:
-                    self.peers.append(self.local)
-                    continue
-                _lib.check(lib.fa_enable_peer_access(owner))
-                # An IPC handle is mapped into the address space of the device that is current when it is opened, and
-                # the kernels that store through it run on THIS rank's GPU: open it as memory of this device (argument
-                # 6 of the rebuild call is the device index), not of the owner's as a consumer on the same GPU would.
-                peer_args = list(peer_args)
-                peer_args[6] = mine
-                self.peers.append(rebuild(*peer_args))
-            # Before any kernel stores through these mappings, prove them with copies the driver validates: every rank
-            # writes its number into its word of every peer's probe area, and after a barrier finds the peers' numbers
-            # in its own.
-            stamp = torch.full((1,), float(rank + 1), dtype=torch.float32, device=device)
-            for r, t in enumerate(self.peers):
-                if r != rank:
-                    t[probe_offset + rank:probe_offset + rank + 1].copy_(stamp)
-            torch.cuda.synchronize(device)
-            dist.barrier(group=group)
+        rebuild = args = None
+        try:
+            # [set 0 slots][set 1 slots][set 0 flags][set 1 flags][probe words]; zero-initialised: no flag is raised
+            self.local = torch.zeros(2 * self.set_floats + 3 * flag_floats, dtype=torch.float32, device=device)
+            rebuild, args = reduce_tensor(self.local)
+        except Exception as exc:
+            self.error = f"{type(exc).__name__}: {exc}"
+        everyone = [None] * world
+        dist.all_gather_object(everyone, (mine, args), group=group)                       # collective 1
+        if self.error is None and any(a is None for _, a in everyone):
+            self.error = "a peer could not export its buffer"
+        if self.error is None:
+            try:
+                lib = _lib.load()
+                with torch.cuda.device(device):
+                    for r, (owner, peer_args) in enumerate(everyone):
+                        if r == rank:
+                            self.peers.append(self.local)
+                            continue
+                        _lib.check(lib.fa_enable_peer_access(owner))
+                        # An IPC handle is mapped into the address space of the device that is current when it is
+                        # opened, and the kernels that store through it run on THIS rank's GPU: open it as memory of
+                        # this device (argument 6 of the rebuild call is the device index), not of the owner's as a
+                        # consumer on the same GPU would.
+                        peer_args = list(peer_args)
+                        peer_args[6] = mine
+                        self.peers.append(rebuild(*peer_args))
+                    # Before any kernel stores through these mappings, prove them with copies the driver validates:
+                    # every rank writes its number into its word of every peer's probe area ...
+                    stamp = torch.full((1,), float(rank + 1), dtype=torch.float32, device=device)
+                    for r, t in enumerate(self.peers):
+                        if r != rank:
+                            t[probe_offset + rank:probe_offset + rank + 1].copy_(stamp)
+                    torch.cuda.synchronize(device)
+            except Exception as exc:
+                self.error = f"{type(exc).__name__}: {exc}"
+        dist.barrier(group=group)                                                          # collective 2
+        if self.error is None:
+            # ... and finds the peers' numbers in its own
             seen = self.local[probe_offset:probe_offset + world].tolist()
             missing = [r for r in range(world) if r != rank and seen[r] != float(r + 1)]
             if missing:
-                raise RuntimeError(f"peer buffers of rank(s) {missing} did not take a store from this process")
-        self.calls = 0
+                self.error = f"the buffer of this rank did not receive the stores of rank(s) {missing}"
 
     def views(self, which):
         """(o, lse) views of this rank's own slot in set `which`, where the local kernels write the partial."""
@@ -173,13 +186,9 @@ def _peer_gather(world, rank, rows, head_dim, device, group):
         return _peer_gathers[key]
     if id(group) in _push_unavailable:
         return None
-    made, error = None, None
-    try:
-        made = _PeerGather(world, rank, rows, head_dim, device, group)
-    except Exception as exc:   # no IPC in this environment, no peer path, ...
-        error = f"{type(exc).__name__}: {exc}"
+    made = _PeerGather(world, rank, rows, head_dim, device, group)   # no IPC here, no peer path, ...: made.error
     verdicts = [None] * world
-    dist.all_gather_object(verdicts, error, group=group)
+    dist.all_gather_object(verdicts, made.error, group=group)                              # collective 3
     if any(v is not None for v in verdicts):
         _push_unavailable.add(id(group))
         import warnings
