@@ -427,6 +427,8 @@ def gpu_arm(args):
     if distributed and not args.skip_extras:
         sharded = sharded_decode_extra(device, rank, world)
         sharded_configs = sharded_config_extras(device, rank, world, flush, peaks)
+        from fa_b200 import distributed as _fd
+        _fd.release_peer_buffers()   # collective: nobody exits while a peer still maps its gather buffers
 
     if rank != 0:
         if distributed:
@@ -493,8 +495,10 @@ def gpu_arm(args):
 def sharded_decode_extra(device, rank, world, iters=20):
     """Long-context paged decode with the KV pages of every sequence sharded block-cyclically over the ranks
     (strong scaling of one fixed problem: 4 sequences x 262144 tokens, 32/8 heads, 16-token pages, 4.3 GB of KV):
-    local partial -> NCCL all-gather of (O, LSE) -> local merge. Every rank holds the whole pool here but reads only
-    the pages of its own blocks. Time = max over ranks of the CUDA-event time of `iters` calls."""
+    local partial -> every rank stores its (O, LSE) into the peers' gather buffers over NVLink and raises a flag ->
+    bounded wait and local merge (no collective; "push"), or one NCCL all-gather in its place ("nccl", also timed).
+    Every rank holds the whole pool here but reads only the pages of its own blocks. Time = max over ranks of the
+    CUDA-event time of `iters` calls."""
     import torch.distributed as dist
 
     from fa_b200 import distributed as fd
@@ -520,24 +524,36 @@ def sharded_decode_extra(device, rank, world, iters=20):
     max_err = float((got.float() - whole.float()).abs().max())
     if not max_err <= 2e-3:
         raise RuntimeError(f"KV-sharded decode differs from the single-GPU result by {max_err}")
-    torch.cuda.synchronize()
-    dist.barrier()
-    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    s.record()
-    for i in range(iters):
-        kc, vc = pools[i & 1]
-        fd.paged_decode_kv_sharded(q, kc, vc, table, ctx, check_ranks_agree=False)
-    e.record()
-    torch.cuda.synchronize()
-    t = torch.tensor([s.elapsed_time(e) / iters], dtype=torch.float64, device=device)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item())
+    def timed(transport):
+        for kc, vc in pools:   # warm-up of this transport
+            fd.paged_decode_kv_sharded(q, kc, vc, table, ctx, check_ranks_agree=False, transport=transport)
+        torch.cuda.synchronize()
+        dist.barrier()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for i in range(iters):
+            kc, vc = pools[i & 1]
+            fd.paged_decode_kv_sharded(q, kc, vc, table, ctx, check_ranks_agree=False, transport=transport)
+        e.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([s.elapsed_time(e) / iters], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # the default transport: peer stores where every rank could set them up, else the all-gather
+    pushed = len(fd._peer_gathers) > 0
+    ms = timed(None)
+    ms_nccl = timed("nccl") if pushed else ms
     nbytes = Bp * ctx_len * 2 * Hk * Dd * 2
     return {"us": ms * 1e3, "gbs_all_gpus": nbytes / ms / 1e6, "kv_bytes": nbytes, "n_gpus": world,
-            "max_abs_vs_single_gpu": max_err,
+            "max_abs_vs_single_gpu": max_err, "transport": "push" if pushed else "nccl",
+            "us_with_nccl_all_gather": ms_nccl * 1e3,
             "workload": "paged decode, 4 seqs x 262144 tokens, 32/8 heads, page 16, pages sharded block-cyclically",
-            "collective": "the local kernels write into the gather buffer, one in-place all_gather of "
-                          "batch*heads*(head_dim+1) floats per rank, local merge", "scaling": "strong"}
+            "collective": ("none: the local kernels write this rank's (O, LSE) into its own slot, fa_peer_merge stores "
+                           "it into every peer's buffer over NVLink, raises a flag, waits for the peers' flags and "
+                           "merges") if pushed else
+                          ("the local kernels write into the gather buffer, one in-place all_gather of "
+                           "batch*heads*(head_dim+1) floats per rank, local merge"), "scaling": "strong"}
 
 
 def sharded_config_extras(device, rank, world, flush, peaks, iters=10):

@@ -199,6 +199,21 @@ def _peer_gather(world, rank, rows, head_dim, device, group):
     return made
 
 
+def release_peer_buffers(group=None):
+    """Collective: drops the mappings of the peers' gather buffers, then (after a barrier) this rank's own buffers, so
+    that no process ends while another still maps its memory. Call it before destroying the process group."""
+    import torch.distributed as dist
+
+    held = list(_peer_gathers.values())
+    _peer_gathers.clear()
+    for g in held:
+        g.peers = []
+    torch.cuda.synchronize()
+    if dist.is_available() and dist.is_initialized():
+        dist.barrier(group=group)
+    del held
+
+
 def paged_decode_kv_sharded(query, k_cache, v_cache, block_table, context_lens, softmax_scale=None, *,
                             group=None, max_context_len=None, num_splits=None, check_ranks_agree=True,
                             transport=None, _local_partial=None, _merge=None):

@@ -65,6 +65,7 @@ def _worker(rank, world, port, results):
         full = fa_b200.flash_attention(qd, kd, vd, causal=True)
         err_dense = max_abs(torch.cat(parts, dim=1), full)
         torch.cuda.synchronize()
+        fd.release_peer_buffers()
         fa_b200.check_status(torch.device("cuda", rank))
         results[rank] = (err_sharded, err_vs_whole, err_dense, push_error, push_diff)
     finally:
