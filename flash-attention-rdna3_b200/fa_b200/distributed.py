@@ -208,6 +208,9 @@ def release_peer_buffers(group=None):
     _peer_gathers.clear()
     for g in held:
         g.peers = []
+    import gc
+    gc.collect()
+    torch.cuda.ipc_collect()   # hands the released mappings back to their producers
     torch.cuda.synchronize()
     if dist.is_available() and dist.is_initialized():
         dist.barrier(group=group)
