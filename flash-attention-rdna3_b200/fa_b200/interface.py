@@ -15,6 +15,7 @@ Reference entry points mirrored here:
 """
 import ctypes as C
 import math
+import functools
 import os
 from numbers import Integral
 
@@ -79,6 +80,7 @@ def _paged_num_splits(batch, heads, block_size, max_blocks, target_programs,
     return min(cap, max(by_occupancy, by_work))
 
 
+@functools.lru_cache(maxsize=4096)
 def _fill_splits(base_ctas, max_splits, sm_count, ctas_per_sm=2):
     """Split count for the B200 decode kernels: the grid is `base_ctas * splits` CTAs and `ctas_per_sm * sm_count`
     of them are resident at once, so pick the split count whose last wave is fullest (fewest splits within 3 %
@@ -201,7 +203,15 @@ def check_status(device=None):
 
 
 def _stream(device):
-    return C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+    """The raw handle of torch's current stream on `device` (the private accessor is several times cheaper than
+    building a Stream object per launch; the public route is the fall-back)."""
+    index = device.index if isinstance(device, torch.device) else torch.device(device).index
+    if index is None:
+        index = torch.cuda.current_device()
+    try:
+        return C.c_void_p(torch._C._cuda_getCurrentRawStream(index))
+    except AttributeError:
+        return C.c_void_p(torch.cuda.current_stream(index).cuda_stream)
 
 
 def _set4(field, strides):

@@ -24,11 +24,13 @@ def test_platform_gate_message_on_cpu():
 
 
 def test_gate_accepts_compute_capability_10(monkeypatch):
+    monkeypatch.setattr(_validation, "_supported_devices", set())   # the gate remembers devices it has accepted
     monkeypatch.setattr(torch.cuda, "is_available", lambda: True)
     monkeypatch.setattr(torch.cuda, "current_device", lambda: 0)
     monkeypatch.setattr(_validation, "_device_arch", lambda index: (10, 0))
     assert fa_b200.unsupported_reason("cuda:0") is None
     monkeypatch.setattr(_validation, "_device_arch", lambda index: (9, 0))
+    monkeypatch.setattr(_validation, "_supported_devices", set())
     assert "compute capability 10.x" in fa_b200.unsupported_reason("cuda:0")
     assert "CUDA GPU tensor" in fa_b200.unsupported_reason("cpu")
 
