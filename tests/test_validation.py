@@ -16,6 +16,7 @@ def t(*shape, dtype=torch.float16):
     return torch.zeros(*shape, dtype=dtype)
 
 
+@pytest.mark.skipif(torch.cuda.is_available(), reason="describes a machine without a GPU")
 def test_platform_gate_message_on_cpu():
     assert fa_b200.unsupported_reason() is not None
     assert not fa_b200.is_available()
