@@ -418,3 +418,70 @@ def test_paged_balanced_kv_shards_merge_to_whole():
              for r in range(G)]
     o, _ = oracle.combine_ref(torch.stack([p[0] for p in parts]).cpu(), torch.stack([p[1] for p in parts]).cpu())
     assert max_abs(o, ref) <= 2e-3
+
+
+# ---------------------------------------------------------------------------------------------------
+# fa_peer_merge on one GPU: the "peer" buffer is a second local allocation and the peer's partial and flag are put
+# into this rank's buffer by the host beforehand, so no kernel waits for another one. The two-GPU form is in
+# tests/test_multi_gpu.py.
+# ---------------------------------------------------------------------------------------------------
+def _peer_merge_setup(rows, head_dim, epoch, deliver_peer):
+    import ctypes as C
+
+    from fa_b200 import _lib, interface
+
+    g = torch.Generator().manual_seed(rows + head_dim)
+    o = torch.randn(2, rows, head_dim, generator=g)
+    lse = torch.randn(2, rows, generator=g) * 2
+    lse[1, 3] = float("-inf")      # a shard that saw no key for this row
+    slot = -(-(rows * (head_dim + 1)) // 4) * 4
+
+    def buffer():
+        return torch.zeros(2 * slot, device="cuda"), torch.zeros(4, dtype=torch.int32, device="cuda")
+
+    mine, my_flags = buffer()
+    other, other_flags = buffer()
+    for r in (0, 1) if deliver_peer else (0,):
+        mine[r * slot:r * slot + rows * head_dim] = o[r].reshape(-1).cuda()
+        mine[r * slot + rows * head_dim:r * slot + rows * (head_dim + 1)] = lse[r].cuda()
+    if deliver_peer:
+        my_flags[1] = epoch
+    out = torch.empty(rows, head_dim, dtype=torch.float16, device="cuda")
+    lse_out = torch.empty(rows, device="cuda")
+    p = _lib.PeerMergeParams()
+    p.world, p.rank, p.out_dtype, p.rows, p.head_dim, p.epoch, p.slot_floats = 2, 0, _lib.FA_F16, rows, head_dim, epoch, slot
+    p.peer_base[0], p.peer_base[1] = mine.data_ptr(), other.data_ptr()
+    p.peer_flags[0], p.peer_flags[1] = my_flags.data_ptr(), other_flags.data_ptr()
+    p.out, p.out_row_stride, p.lse_out = out.data_ptr(), head_dim, lse_out.data_ptr()
+    p.status = interface._status_word(torch.device("cuda", torch.cuda.current_device())).data_ptr()
+    torch.cuda.synchronize()
+    _lib.check(_lib.load().fa_peer_merge(C.byref(p), interface._stream(torch.device("cuda", torch.cuda.current_device()))))
+    torch.cuda.synchronize()
+    return o, lse, out, lse_out, mine, other, other_flags, slot
+
+
+def test_peer_merge_pushes_this_ranks_slot_and_merges_what_has_arrived():
+    rows, head_dim, epoch = 96, 128, 7
+    o, lse, out, lse_out, mine, other, other_flags, slot = _peer_merge_setup(rows, head_dim, epoch, deliver_peer=True)
+    # this rank's slot went into slot 0 of the peer's buffer, bit for bit, and the peer's flag 0 carries the epoch
+    assert torch.equal(other[:slot], mine[:slot])
+    assert other_flags.tolist() == [epoch, 0, 0, 0]
+    # the merge is the LSE-weighted sum over the two shards
+    m = torch.maximum(lse[0], lse[1])
+    w = torch.exp(lse - m)
+    want = (w[0, :, None] * o[0] + w[1, :, None] * o[1]) / (w[0] + w[1])[:, None]
+    assert max_abs(out, want) <= 2e-3
+    assert (lse_out.cpu() - (m + torch.log(w[0] + w[1]))).abs().max().item() <= 1e-5
+
+
+def test_peer_merge_lost_wait_sets_the_status_word():
+    """Nobody raises the peer's flag: every merge CTA gives up after its bound (about a second), the status word is set
+    and the context stays usable."""
+    import fa_b200
+
+    fa_b200.check_status()
+    _peer_merge_setup(8, 64, 3, deliver_peer=False)
+    with pytest.raises(RuntimeError, match="wait timeout"):
+        fa_b200.check_status()
+    fa_b200.check_status()
+    test_peer_merge_pushes_this_ranks_slot_and_merges_what_has_arrived()
