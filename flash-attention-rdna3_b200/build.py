@@ -5,9 +5,9 @@ Usage: python flash-attention-rdna3_b200/build.py [--force] [--verbose] [--prof]
 Each .cu file is compiled to an object only when it or a header is newer than the object, then all
 objects are linked into fa_b200/libfa_b200.so next to the Python package that loads it.
 
---prof builds a second library, fa_b200/libfa_b200_prof.so, with -DFA_PROF: the tensor-core forward and backward
+--prof builds a second library, fa_b200/libfa_b200_prof.so, with -DFA_PROF: the tensor-core forward, backward and decode
 kernels then count, per CTA and role, the cycles spent in each phase of their loops (csrc/fa_prof.cuh) and the library
-exports fa_debug_read_prof / fa_debug_read_prof_bwd, which copy the counters to the host. It is a tuning aid: the
+exports fa_debug_read_prof / fa_debug_read_prof_bwd / fa_debug_read_prof_decode, which copy the counters to the host. It is a tuning aid: the
 product library carries none of it, and nothing loads the profiling library unless a script points
 fa_b200._lib.LIB_PATH at it.
 

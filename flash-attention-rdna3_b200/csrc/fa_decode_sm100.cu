@@ -22,6 +22,7 @@
 #include "fa_common.cuh"
 #include "fa_sm100.cuh"
 #include "fa_tma_host.h"
+#include "fa_prof.cuh"
 
 #include <mutex>
 
@@ -55,6 +56,7 @@ struct DecArgs {
   float softmax_scale;
   int num_partials;  // partial slots per row: 2 * gridDim.x, or the caller's capacity when balanced
   int balanced;      // paged: gridDim.x CTAs are dealt to the sequences in proportion to their tile counts
+  int spread;        // paged, 8 kv heads, 16 tokens per tile: query heads are spread over the four lane quarters (see below)
   float* o_partial;
   float* lse_partial;
   int* status;
@@ -164,6 +166,52 @@ __device__ __forceinline__ bool balanced_assignment(const DecArgs& a, void* scra
   return mine;
 }
 
+// Spread mode of the paged kernel (8 kv heads, 16 tokens x 8 heads per tile, at most 4 query heads per kv head):
+// column c of a score tile is (token c / 8, kv head c % 8), so a query row only wants every eighth column. With all
+// query rows in the first lane quarter one warp walks 128 columns per row and masks 112 of them; instead the rows of
+// kv heads 2w and 2w + 1 sit in lane quarter w (Q is loaded as four boxes), every softmax warp picks the 16 columns of
+// each of its rows out of the tile (a switch on the row's kv head, two cases per warp, compile-time register indices)
+// and works on those alone. pick<HK> takes the four columns of one 32-column chunk, place<HK> puts four probabilities
+// back as 16-bit halves of an otherwise zero chunk of P.
+template <int HK, int C>
+__device__ __forceinline__ void pick_cols(const uint32_t (&r)[32], float (&x)[16]) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) x[4 * C + j] = __uint_as_float(r[HK + 8 * j]);
+}
+template <typename T, int HK, int C>
+__device__ __forceinline__ void place_cols(uint32_t (&pk)[16], const float (&p)[16]) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    pk[4 * j + HK / 2] = (HK & 1) ? DType<T>::pack2(0.f, p[4 * C + j]) : DType<T>::pack2(p[4 * C + j], 0.f);
+}
+// the two switches on the row's kv head, for chunk C of the tile
+template <int C>
+__device__ __forceinline__ void pick_chunk(int hk, const uint32_t (&r)[32], float (&x)[16]) {
+  switch (hk) {
+    case 0: pick_cols<0, C>(r, x); break;
+    case 1: pick_cols<1, C>(r, x); break;
+    case 2: pick_cols<2, C>(r, x); break;
+    case 3: pick_cols<3, C>(r, x); break;
+    case 4: pick_cols<4, C>(r, x); break;
+    case 5: pick_cols<5, C>(r, x); break;
+    case 6: pick_cols<6, C>(r, x); break;
+    default: pick_cols<7, C>(r, x); break;
+  }
+}
+template <typename T, int C>
+__device__ __forceinline__ void place_chunk(int hk, uint32_t (&pk)[16], const float (&p)[16]) {
+  switch (hk) {
+    case 0: place_cols<T, 0, C>(pk, p); break;
+    case 1: place_cols<T, 1, C>(pk, p); break;
+    case 2: place_cols<T, 2, C>(pk, p); break;
+    case 3: place_cols<T, 3, C>(pk, p); break;
+    case 4: place_cols<T, 4, C>(pk, p); break;
+    case 5: place_cols<T, 5, C>(pk, p); break;
+    case 6: place_cols<T, 6, C>(pk, p); break;
+    default: place_cols<T, 7, C>(pk, p); break;
+  }
+}
+
 template <typename T, int D, bool kPaged>
 __global__ void __launch_bounds__(kThreads, 1)
 decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -184,11 +232,15 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   uint8_t* sRing = smem + kTileBytes;
   __shared__ uint64_t q_full, full[kSlots], empty[kSlots], s_full[2], p_full[2], o_ready[2];
   __shared__ uint32_t tmem_base_s;
-  __shared__ int nval_s[kSlots][16];  // paged: readable tokens of each unit of the tile in that K slot
+  // paged: readable tokens of each unit of tile t, in entry t % 8. The producer is at most three tiles ahead of the
+  // Q K^T products and a tile's softmax has read its entry before the product three tiles on is even issued, so eight
+  // entries never hold two live tiles.
+  __shared__ int nval_s[8][16];
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   // The merge kernel launched behind this one is set up while the last CTAs here drain; it waits for the whole grid.
   grid_launch_dependents();
+  PROF_STAMP(3);
   auto wait = [&](uint64_t* bar, uint32_t parity) { return mbar_wait_limit(bar, parity, a.poll_limit); };
   // dense: one CTA row per (batch, kv head). paged: one per batch entry; a tile interleaves all kv heads
   // (row = token * heads_kv + head), which is how a page lies in memory, so a page is fetched with few large boxes.
@@ -237,28 +289,37 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     }
     fence_proxy_async_smem();
   }
-  // paged: lane u < upt of the producer warp holds the page id and the token counts of unit u of a tile. The first
-  // look-up is issued here, so that its global load runs behind the TMEM allocation and the barrier set-up.
-  auto lookup = [&](int t, int* phys_out, int* nvalid_out, int* tokoff_out) {
-    int phys = a.num_blocks, nvalid = 0, tokoff = 0;
+  // paged: lane u < upt of the producer warp holds the page id and the token counts of unit u of a tile. The look-up is
+  // split in two so that the table read never stalls the producer: `request` only issues the load of the raw id (for
+  // the tile after the one being queued), `resolve` turns it into box coordinates an iteration later. The first
+  // request is made here, so that its load runs behind the TMEM allocation and the barrier set-up.
+  constexpr int kNoPage = -0x7fffffff;  // no page behind this unit (past the context, past this lane's units)
+  auto request = [&](int t) -> int {
+    int id = kNoPage;
     if (kPaged) {
       const int u = (jlo + t) * a.upt + lane;  // local unit index
       const int lp = u / a.upp;
-      if (t < ntiles && lane < a.upt && lp < nlocal_pages) {
-        const int lb = a.first_block + lp * a.block_step;
-        tokoff = (u % a.upp) * a.tpt;
-        const int id = a.block_table[(int64_t)b * a.bt_sb + (int64_t)lb * a.bt_sk];
-        nvalid = max(0, min(a.tpt, ctx - (lb * a.block_size + tokoff)));
-        if (id >= 0 && id < a.num_blocks) phys = id;
-        else nvalid = -nvalid;  // present but unreadable: box aimed past the pool reads zeros, keys masked
-      }
+      if (t < ntiles && lane < a.upt && lp < nlocal_pages)
+        id = a.block_table[(int64_t)b * a.bt_sb + (int64_t)(a.first_block + lp * a.block_step) * a.bt_sk];
+    }
+    return id;
+  };
+  auto resolve = [&](int t, int id, int* phys_out, int* nvalid_out, int* tokoff_out) {
+    int phys = a.num_blocks, nvalid = 0, tokoff = 0;
+    if (kPaged && id != kNoPage) {
+      const int u = (jlo + t) * a.upt + lane;
+      const int lb = a.first_block + (u / a.upp) * a.block_step;
+      tokoff = (u % a.upp) * a.tpt;
+      nvalid = max(0, min(a.tpt, ctx - (lb * a.block_size + tokoff)));
+      if (id >= 0 && id < a.num_blocks) phys = id;
+      else nvalid = -nvalid;  // present but unreadable: box aimed past the pool reads zeros, keys masked
     }
     *phys_out = phys;
     *nvalid_out = nvalid;
     *tokoff_out = tokoff;
   };
-  int phys_next = 0, nvalid_next = 0, tokoff_next = 0;
-  if (kPaged && warp == 8 && ntiles > 0) lookup(0, &phys_next, &nvalid_next, &tokoff_next);
+  int id_next = kNoPage;
+  if (kPaged && warp == 8 && ntiles > 0) id_next = request(0);
   if (warp == 9) {
     tmem_alloc(&tmem_base_s, 512);
     tmem_relinquish();
@@ -274,21 +335,38 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       if (lane == 0) {
         tma_prefetch_desc(&map_k);
         tma_prefetch_desc(&map_v);
-        mbar_arrive_expect_tx(&q_full, kTileBytes);
+        if (kPaged && a.spread) {
+          // four boxes of 2 * group rows: the query heads of kv heads 2w, 2w + 1 to rows 32w... (the rows in between
+          // stay as they are: their lanes never look at their scores and hand in zero probabilities)
+          mbar_arrive_expect_tx(&q_full, 4 * 2 * a.group * 128 * kChunks);
+          for (int w = 0; w < 4; ++w)
 #pragma unroll
-        for (int c = 0; c < kChunks; ++c) tma_load_4d(sQ + c * 16384, &map_q, &q_full, c * 64, 0, hk, b);
+            for (int c = 0; c < kChunks; ++c)
+              tma_load_4d(sQ + c * 16384 + w * 4096, &map_q, &q_full, c * 64, w * 2 * a.group, hk, b);
+        } else {
+          mbar_arrive_expect_tx(&q_full, kTileBytes);
+#pragma unroll
+          for (int c = 0; c < kChunks; ++c) tma_load_4d(sQ + c * 16384, &map_q, &q_full, c * 64, 0, hk, b);
+        }
       }
       const int unit_rows_bytes = kPaged ? a.tpt * a.heads_kv * 128 : 0;
+      // One unit per tile (a page of at least 128 rows, or exactly one): lane 0 does everything and the warp-wide
+      // steps (vote, byte count, barriers between lanes) drop out; they cost more than the two boxes they serve.
+      const bool single = kPaged && a.upt == 1;
       bool ok = true;
-      for (int t = 0; t < ntiles && ok; ++t) {
-        const int phys = phys_next, nvalid = nvalid_next, tokoff = tokoff_next;
-        if (kPaged) lookup(t + 1, &phys_next, &nvalid_next, &tokoff_next);  // in flight while this tile is issued
+      PROF_DECL;
+      for (int t = 0; t < ntiles && ok && (!single || lane == 0); ++t) {
+        int phys, nvalid, tokoff;
+        resolve(t, id_next, &phys, &nvalid, &tokoff);
+        if (kPaged) id_next = request(t + 1);  // in flight while this tile is queued; not looked at before the next turn
         for (int which = 0; which < 2 && ok; ++which) {
           const int n = 2 * t + which, slot = n % kSlots;
           uint8_t* dst = sRing + slot * kTileBytes;
           bool w_ok = true;
+          PROF_MARK(1);  // issuing
           if (lane == 0) w_ok = wait(&empty[slot], ((n / kSlots) & 1) ^ 1);
-          w_ok = __shfl_sync(kFull, w_ok, 0);
+          if (!single) w_ok = __shfl_sync(kFull, w_ok, 0);
+          PROF_MARK(0);  // waiting for a free slot
           if (!w_ok) {
             if (lane == 0) report_timeout(a.status, 401);
             ok = false;
@@ -305,16 +383,20 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             continue;
           }
           // paged: bytes this tile delivers, token counts for the softmax groups, then the boxes
+          PROF_MARK(2);  // from the slot wait to here (look-up of the next tile included)
           const int present = nvalid < 0 ? -nvalid : nvalid;  // tokens inside the context
           const int readable = nvalid > 0 ? nvalid : 0;       // ... that may be used
           int mybytes = (which == 0) ? (present > 0 ? a.tpt : 0) : present;
           mybytes *= a.heads_kv * 128 * kChunks;
+          if (!single) {
 #pragma unroll
-          for (int o = 16; o > 0; o >>= 1) mybytes += __shfl_xor_sync(kFull, mybytes, o);
-          if (which == 0 && lane < 16) nval_s[slot][lane] = readable;
-          __syncwarp();
+            for (int o = 16; o > 0; o >>= 1) mybytes += __shfl_xor_sync(kFull, mybytes, o);
+          }
+          if (which == 0 && lane < 16) nval_s[t & 7][lane] = readable;
+          if (!single) __syncwarp();
           if (lane == 0) mbar_arrive_expect_tx(&full[slot], (uint32_t)mybytes);
-          __syncwarp();
+          if (!single) __syncwarp();
+          PROF_MARK(3);  // byte count, token counts, expect_tx
           // every lane issues the boxes of its own unit, so the copies of a tile are queued in parallel
           if (lane < a.upt && present > 0) {
             uint8_t* udst = dst + lane * unit_rows_bytes;
@@ -330,9 +412,12 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                               phys);
             }
           }
-          __syncwarp();
+          if (!single) __syncwarp();
+          PROF_MARK(4);  // queueing the boxes
         }
       }
+      PROF_MARK(1);
+      PROF_FLUSH(2, lane == 0);
     }
   } else if (warp == 9) {
     // ------------------------------------------------------------------ MMA issuer
@@ -342,44 +427,67 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       const uint32_t q_addr = smem_u32(sQ), ring_addr = smem_u32(sRing);
       bool ok = wait(&q_full, 0);
       if (!ok) report_timeout(a.status, 403);
+      PROF_DECL;
 
       auto issue_qk = [&](int t) {  // tile t goes to stream t & 1
         const int n = 2 * t, slot = n % kSlots, s = t & 1;
+        PROF_MARK(3);
         if (!wait(&full[slot], (n / kSlots) & 1)) {
           report_timeout(a.status, 404);
           ok = false;
           return;
         }
+        PROF_MARK(0);  // waiting for a K tile
         tc_fence_after_sync();
         const uint32_t k_addr = ring_addr + slot * kTileBytes;
+        {  // descriptors as 32-bit halves, one add per operand and instruction (this thread's issue slots are the
+           // stream's latency)
+          const uint32_t q_lo = smem_desc_lo(q_addr, 16), k_lo = smem_desc_lo(k_addr, 16);
+          constexpr uint32_t hi = smem_desc_hi(1024);
+          mma_ss_lo<0>(tmem_base + s * 128, q_lo, hi, k_lo, hi, idesc_qk);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk / 4) * 16384 + (kk % 4) * 32;
-          mma_ss(tmem_base + s * 128, make_smem_desc(q_addr + off, 16, 1024), make_smem_desc(k_addr + off, 16, 1024),
-                 idesc_qk, kk > 0);
+          for (int kk = 1; kk < D / 16; ++kk) {
+            const uint32_t off = ((kk / 4) * 16384 + (kk % 4) * 32) >> 4;
+            mma_ss_lo<1>(tmem_base + s * 128, q_lo + off, hi, k_lo + off, hi, idesc_qk);
+          }
         }
         tc_commit(&s_full[s]);
-        if (!kPaged) tc_commit(&empty[slot]);  // paged: the softmax group releases it after reading the validity mask
+        tc_commit(&empty[slot]);
+        PROF_MARK(1);  // issuing Q K^T
       };
 
       if (ok) issue_qk(0);
       if (ok && ntiles > 1) issue_qk(1);
       for (int t = 0; t < ntiles && ok; ++t) {
         const int n = 2 * t + 1, slot = n % kSlots, s = t & 1;
-        if (!wait(&full[slot], (n / kSlots) & 1) || !wait(&p_full[s], (t >> 1) & 1)) {
+        PROF_MARK(3);
+        if (!wait(&full[slot], (n / kSlots) & 1)) {
           report_timeout(a.status, 405);
           break;
         }
+        PROF_MARK(4);  // waiting for a V tile
+        if (!wait(&p_full[s], (t >> 1) & 1)) {
+          report_timeout(a.status, 405);
+          break;
+        }
+        PROF_MARK(2);  // waiting for P
         tc_fence_after_sync();
         const uint32_t v_addr = ring_addr + slot * kTileBytes;
+        {
+          const uint32_t v_lo = smem_desc_lo(v_addr, 16384), o_col = tmem_base + 256 + (kWide ? 0 : s * D);
+          constexpr uint32_t hi = smem_desc_hi(1024);
+          if (t < (kWide ? 1 : 2)) mma_ts_lo<0>(o_col, tmem_base + s * 128, v_lo, hi, idesc_pv);  // the stream's first tile
+          else mma_ts_lo<1>(o_col, tmem_base + s * 128, v_lo, hi, idesc_pv);
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          mma_ts(tmem_base + 256 + (kWide ? 0 : s * D), tmem_base + s * 128 + kk * 8,
-                 make_smem_desc(v_addr + kk * 2048, 16384, 1024), idesc_pv, !(t < (kWide ? 1 : 2) && kk == 0));
+          for (int kk = 1; kk < 8; ++kk)
+            mma_ts_lo<1>(o_col, tmem_base + s * 128 + kk * 8, v_lo + kk * (2048 >> 4), hi, idesc_pv);
+        }
         tc_commit(&o_ready[kWide ? 0 : s]);
         tc_commit(&empty[slot]);
+        PROF_MARK(3);  // issuing P V
         if (t + 2 < ntiles) issue_qk(t + 2);
       }
+      PROF_FLUSH(1, true);
     }
   } else {
     // ------------------------------------------------------------------ softmax of stream s
@@ -389,10 +497,17 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     const uint32_t tS_own = tmem_base + lane_addr + s * 128;
     const uint32_t tO = tmem_base + lane_addr + 256 + (kWide ? 0 : s * D);
     const int n_mine = kWide ? (s == 0 ? ntiles : 0) : (ntiles + 1 - s) / 2;
-    const bool warp_active = w4 * 32 < a.rows;  // warps whose 32 rows are all padding only keep the barriers moving
+    const bool spread = kPaged && a.spread;
+    // warps whose 32 rows are all padding only keep the barriers moving (spread: every warp has rows)
+    const bool warp_active = spread || w4 * 32 < a.rows;
+    // spread: this lane's kv head and whether the lane holds a query row at all
+    // (lanes without a row take the second head's case, so that a warp runs two cases of the switches, not eight)
+    const int sp_hk = 2 * w4 + min(lane / max(a.group, 1), 1);
+    const bool sp_row = spread && lane < 2 * a.group;
     const float scale_log2 = a.softmax_scale * kLog2e;
     float m_used = kNegInf, l = 0.f;
     bool ok = true;
+    PROF_DECL;
     // paged: columns of this row's kv head when every token of the tile is readable
     uint32_t full_pat[4] = {0u, 0u, 0u, 0u};
     const int my_hk = kPaged ? min(row, a.heads_q - 1) / a.group : 0;
@@ -409,8 +524,11 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       const int t = kWide ? i : 2 * i + s, j = jlo + t;
       const int sb = kWide ? (i & 1) : s;  // S buffer and its barriers
       const uint32_t tS = kWide ? tmem_base + lane_addr + sb * 128 : tS_own;
+      PROF_MARK(5);
       bool w_ok = wait(&s_full[sb], kWide ? (i >> 1) & 1 : i & 1);
+      PROF_MARK(0);  // waiting for S
       if (w_ok && i > 0) w_ok = wait(&o_ready[s], (i - 1) & 1);
+      PROF_MARK(6);  // waiting for the previous P V
       if (!__all_sync(kFull, w_ok)) {
         report_timeout(a.status, 406);
         ok = false;
@@ -419,18 +537,20 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       tc_fence_after_sync();
       // validity of the tile's 128 columns for this row as a bit mask
       uint32_t vmask[4] = {kFull, kFull, kFull, kFull};
+      int nv_first = 0;  // paged: readable tokens of the tile's first unit (all there is in spread mode)
       if (kPaged) {
         // column = (unit * tpt + token) * heads_kv + kv head: this row only sees the columns of its own kv head,
         // and of those only the readable tokens
-        const int kslot = (2 * t) % kSlots;
+        const int* nval = nval_s[t & 7];
+        nv_first = nval[0];
         bool all_full = true;
-        for (int u = 0; u < a.upt; ++u) all_full = all_full && (nval_s[kslot][u] == a.tpt);
+        for (int u = 0; u < a.upt && !spread; ++u) all_full = all_full && (nval[u] == a.tpt);
 #pragma unroll
         for (int w = 0; w < 4; ++w) vmask[w] = full_pat[w];
         if (!all_full) {
           vmask[0] = vmask[1] = vmask[2] = vmask[3] = 0u;
           for (int u = 0; u < a.upt; ++u) {
-            const int nv = nval_s[kslot][u];
+            const int nv = nval[u];
             for (int tok = 0; tok < nv; ++tok) {
               const int c = (u * a.tpt + tok) * a.heads_kv + my_hk;
 #pragma unroll
@@ -439,9 +559,6 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             }
           }
         }
-        // the K slot (and its counts) may be reused once every thread of this stream has read them
-        asm volatile("bar.sync %0, 128;" ::"r"(1 + s) : "memory");
-        if (w4 == 0 && lane == 0) mbar_arrive(&empty[kslot]);
       } else if (j * 128 + 128 > nkeys) {
         const int nv = nkeys - j * 128;
 #pragma unroll
@@ -451,7 +568,73 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         }
       }
       const bool masked = (vmask[0] & vmask[1] & vmask[2] & vmask[3]) != kFull;
-      if (warp_active) {
+      PROF_MARK(1);  // validity mask, slot release
+      if (spread) {
+        // the 16 scores of this row: column 8 * token + kv head of every chunk
+        const int nv = nv_first;
+        float x[16];
+        {
+          uint32_t r[32];
+          tmem_ld32(tS, r);
+          tc_wait_ld_regs(r);
+          pick_chunk<0>(sp_hk, r, x);
+          tmem_ld32(tS + 32, r);
+          tc_wait_ld_regs(r);
+          pick_chunk<1>(sp_hk, r, x);
+          tmem_ld32(tS + 64, r);
+          tc_wait_ld_regs(r);
+          pick_chunk<2>(sp_hk, r, x);
+          tmem_ld32(tS + 96, r);
+          tc_wait_ld_regs(r);
+          pick_chunk<3>(sp_hk, r, x);
+        }
+        float m_tile = kNegInf;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          if (!sp_row || j >= nv) x[j] = kNegInf;  // lanes without a row and tokens past the context
+          m_tile = fmaxf(m_tile, x[j]);
+        }
+        PROF_MARK(2);
+        m_tile *= scale_log2;  // softmax_scale > 0 on this path
+        const float m_new = fmaxf(m_used, m_tile);
+        const bool grow = m_new > m_used + kRescaleThreshold;
+        if (__any_sync(kFull, grow)) {
+          const float alpha = (m_new == kNegInf) ? 1.f : exp2f(m_used - m_new);
+          l *= alpha;
+          if (i > 0) rescale_o<D>(tO, alpha);
+          m_used = m_new;
+        }
+        const float m_eff = (m_used == kNegInf) ? 0.f : m_used;
+        PROF_MARK(3);
+        float pr[16], sum = 0.f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          pr[j] = fast_exp2(x[j] * scale_log2 - m_eff);
+          sum += pr[j];
+        }
+        l += sum;
+        {
+          uint32_t pk[16];
+#pragma unroll
+          for (int e = 0; e < 16; ++e) pk[e] = 0u;
+          place_chunk<T, 0>(sp_hk, pk, pr);
+          tmem_st16(tS, pk);
+#pragma unroll
+          for (int e = 0; e < 16; ++e) pk[e] = 0u;
+          place_chunk<T, 1>(sp_hk, pk, pr);
+          tmem_st16(tS + 16, pk);
+#pragma unroll
+          for (int e = 0; e < 16; ++e) pk[e] = 0u;
+          place_chunk<T, 2>(sp_hk, pk, pr);
+          tmem_st16(tS + 32, pk);
+#pragma unroll
+          for (int e = 0; e < 16; ++e) pk[e] = 0u;
+          place_chunk<T, 3>(sp_hk, pk, pr);
+          tmem_st16(tS + 48, pk);
+        }
+        tc_wait_st();
+        PROF_MARK(4);
+      } else if (warp_active) {
         // pass 1: row maximum
         float mx[4] = {kNegInf, kNegInf, kNegInf, kNegInf};
 #pragma unroll
@@ -473,6 +656,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
               mx[u] = fmax3(mx[u], __uint_as_float(r[c + 2 * u]), __uint_as_float(r[c + 2 * u + 1]));
         }
         float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+        PROF_MARK(2);  // pass 1
         m_tile *= scale_log2;  // softmax_scale > 0 on this path
         const float m_new = fmaxf(m_used, m_tile);
         const bool grow = m_new > m_used + kRescaleThreshold;
@@ -483,6 +667,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
           m_used = m_new;
         }
         const float m_eff = (m_used == kNegInf) ? 0.f : m_used;
+        PROF_MARK(3);  // rescale
 
         // pass 2: p = exp2(s*scale - m), 32 columns at a time, P written over consumed S columns
         const uint64_t sc2 = pack_f32x2(scale_log2, scale_log2);
@@ -517,6 +702,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         unpack_f32x2(add_f32x2(add_f32x2(acc2[0], acc2[1]), add_f32x2(acc2[2], acc2[3])), &s0, &s1);
         l += s0 + s1;
         tc_wait_st();
+        PROF_MARK(4);  // pass 2
       } else {
         // padding-only warp: P rows of its lanes must still be finite zeros for the MMA
         uint32_t z[32];
@@ -530,6 +716,8 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       mbar_arrive(&p_full[sb]);
     }
 
+    PROF_MARK(5);
+    PROF_FLUSH(0, s == 0 && w4 == 0 && lane == 0);
     // epilogue: normalised fp32 partial and LSE of this stream
     if (n_mine > 0) {
       const bool w_ok = ok && wait(&o_ready[s], (n_mine - 1) & 1);
@@ -542,7 +730,8 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       tc_fence_after_sync();
       const int part = kWide ? cta_x : 2 * cta_x + s;
       const int g = row / a.seqlen_q, sq = row % a.seqlen_q;
-      const int h = kPaged ? row : hk * a.group + g;
+      const int h = spread ? sp_hk * a.group + lane % a.group : (kPaged ? row : hk * a.group + g);
+      const bool has_row = spread ? sp_row : row < a.rows;
       int64_t flat_o, flat_l;
       if (kPaged) {  // (batch, heads_q, partials, D) and (batch, heads_q, partials)
         flat_l = ((int64_t)b * a.heads_q + h) * a.num_partials + part;
@@ -566,7 +755,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 #pragma unroll
           for (int e = 0; e < 32; ++e) o[e] = 0u;
         }
-        if (row < a.rows) {
+        if (has_row) {
           float4* dst = reinterpret_cast<float4*>(a.o_partial + flat_o + c * 32);
 #pragma unroll
           for (int v = 0; v < 8; ++v)
@@ -574,7 +763,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                                  __uint_as_float(o[4 * v + 2]) * inv, __uint_as_float(o[4 * v + 3]) * inv);
         }
       }
-      if (row < a.rows) a.lse_partial[flat_l] = (l == 0.f) ? kNegInf : (m_used * kLn2 + logf(l));
+      if (has_row) a.lse_partial[flat_l] = (l == 0.f) ? kNegInf : (m_used * kLn2 + logf(l));
     }
     if (!kPaged && a.tickets != nullptr) __threadfence();  // this thread's partial is visible before the ticket is taken
   }
@@ -588,6 +777,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 9) tmem_dealloc(tmem_base, 512);
+  PROF_STAMP(7);
 
   if (!kPaged && a.tickets != nullptr) {
     // Merge inside the kernel: every CTA of this (batch, kv head) takes a ticket once its partials are written; the
@@ -881,7 +1071,10 @@ int launch_paged_tc(const fa_paged_params& p, cudaStream_t stream) {
   const int tpt = p.block_size * p.heads_kv <= 128 ? p.block_size : 128 / p.heads_kv;
   const int upp = p.block_size / tpt;
   const int upt = upp == 1 ? 128 / (tpt * p.heads_kv) : 1;
-  int rc = make_tile_map(&mq, p.q, p.dtype, D, p.heads_q, 1, p.batch, p.q_strides[1], 0, p.q_strides[0]);
+  // spread mode (see pick_cols): 8 kv heads, a tile of 16 tokens x 8 heads, at most 4 query heads per kv head
+  const bool spread = p.heads_kv == 8 && tpt == 16 && upt == 1 && group <= 4;
+  int rc = make_tile_map(&mq, p.q, p.dtype, D, p.heads_q, 1, p.batch, p.q_strides[1], 0, p.q_strides[0],
+                         spread ? 2 * group : 128);
   if (!rc) rc = make_page_map(&mk, p.k_cache, p.dtype, D, p.heads_kv, p.block_size, p.num_blocks, p.k_strides, tpt);
   if (!rc) rc = make_page_map(&mv, p.v_cache, p.dtype, D, p.heads_kv, p.block_size, p.num_blocks, p.v_strides, tpt);
   if (!rc) rc = make_page_map(&mvr, p.v_cache, p.dtype, D, p.heads_kv, p.block_size, p.num_blocks, p.v_strides, 1);
@@ -912,6 +1105,7 @@ int launch_paged_tc(const fa_paged_params& p, cudaStream_t stream) {
   a.o_partial = p.o_partial;
   a.lse_partial = p.lse_partial;
   a.status = p.status;
+  a.spread = spread ? 1 : 0;
   take_fault_injection(&a);
   int ctas = p.num_splits / 2;
   if (p.balance) {
@@ -932,6 +1126,8 @@ int launch_paged_tc(const fa_paged_params& p, cudaStream_t stream) {
                                  p.num_splits, p.out, p.out_is_f32 ? (int)FA_F32 : p.dtype, p.heads_q, 1, p.o_strides[0],
                                  p.o_strides[1], 0, p.o_strides[2], p.lse_out, stream, true);
 }
+
+PROF_DEFINE_READER(fa_debug_read_prof_decode)
 
 void set_decode_fault_injection(uint32_t poll_limit, int skip_tile) {
   g_fault_poll_limit = poll_limit;
