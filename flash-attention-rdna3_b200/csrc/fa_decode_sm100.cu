@@ -64,7 +64,9 @@ struct DecArgs {
   int skip_tile;        // test hook: the producer leaves out the loads of this tile of every CTA (-1: none)
   // dense, merge inside the kernel: the last CTA of a (batch, kv head) to finish combines that head's partials.
   // tickets == nullptr: the caller launches the merge kernel instead.
-  unsigned int* tickets;  // one word per (batch, kv head), zero between launches (atomicInc wraps it back)
+  unsigned int* tickets;  // dense: one word per (batch, kv head), zero between launches (atomicInc wraps it back);
+                          // paged (balanced, cooperative launch): two words per sequence, arrivals and departures
+  float* lse_out;         // paged merge inside the kernel: merged LSE per (batch, head), may be null
   void* out;
   int out_dtype;
   int64_t o_sb, o_sh, o_ss, o_sd;
@@ -768,7 +770,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     if (!kPaged && a.tickets != nullptr) __threadfence();  // this thread's partial is visible before the ticket is taken
   }
 
-  if (kPaged && a.balanced && cta_x == 0) {
+  if (kPaged && a.balanced && cta_x == 0 && a.tickets == nullptr) {
     // the slots of this sequence that no CTA writes must not take part in the merge: LSE = -inf
     const int used = 2 * ctas_b, spare = a.num_partials - used;
     for (int i = tid; i < a.heads_q * spare; i += kThreads)
@@ -778,6 +780,92 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   __syncthreads();
   if (warp == 9) tmem_dealloc(tmem_base, 512);
   PROF_STAMP(7);
+
+  if (kPaged && a.tickets != nullptr) {
+    // Merge inside the kernel, balanced mode under a cooperative launch (all CTAs are resident, so waiting for the
+    // others is legitimate): a CTA announces its partials, waits - with a bound - until all ctas_b CTAs of its sequence
+    // have done so, then merges the rows cta_x, cta_x + ctas_b, ... of the sequence (the LSE-weighted sum of
+    // fa_rdna3/kernels/decode.py:101-122 over the 2 * ctas_b partials that were written). The last CTA to leave puts
+    // the two counters back to zero; nobody can still be polling then, because a CTA only leaves after its wait ended.
+    __shared__ int all_here;
+    unsigned int* arrive = a.tickets + 2 * b;
+    unsigned int* depart = arrive + 1;
+    __threadfence();  // this thread's partial is visible device-wide before the CTA is counted
+    __syncthreads();
+    if (tid == 0) {
+      atomicAdd(arrive, 1u);
+      bool seen = false;
+      for (uint32_t i = 0; i < a.poll_limit; ++i) {
+        unsigned int v;
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(arrive) : "memory");
+        if (v >= (unsigned int)ctas_b) {
+          seen = true;
+          break;
+        }
+        __nanosleep(100);
+      }
+      if (!seen) report_timeout(a.status, 408);
+      all_here = seen ? 1 : 0;
+    }
+    __syncthreads();
+    if (all_here) {
+      const int P = 2 * ctas_b, lane4 = tid % 32, grp = tid / 32;  // ten groups of 32 lanes; a lane owns four columns
+      float* w_s = reinterpret_cast<float*>(smem);                         // [P] weights (P <= 2 * 148)
+      float* part_s = w_s + 320;                                           // [10]
+      float4* red_s = reinterpret_cast<float4*>(smem + 2048);              // [10][32]
+      for (int r = cta_x; r < a.heads_q; r += ctas_b) {
+        const int64_t row0 = ((int64_t)b * a.heads_q + r) * a.num_partials;
+        const float ls = tid < P ? __ldcg(a.lse_partial + row0 + tid) : kNegInf;
+        float M = ls;
+        for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(kFull, M, o));
+        if (lane4 == 0) part_s[grp] = M;
+        __syncthreads();
+        M = lane4 < kThreads / 32 ? part_s[lane4] : kNegInf;
+        for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(kFull, M, o));
+        const float Ms = (M == kNegInf) ? 0.f : M;
+        const float w = (ls == kNegInf) ? 0.f : expf(ls - Ms);
+        if (tid < P) w_s[tid] = w;
+        float den = w;
+        for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(kFull, den, o);
+        __syncthreads();  // everyone has read part_s; the weights are in place
+        if (lane4 == 0) part_s[grp] = den;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (lane4 < D / 4) {
+          const float4* src = reinterpret_cast<const float4*>(a.o_partial + row0 * D) + lane4;
+#pragma unroll 4
+          for (int sp = grp; sp < P; sp += kThreads / 32) {
+            const float ws = w_s[sp];
+            if (ws == 0.f) continue;
+            const float4 v = __ldcg(src + (int64_t)sp * (D / 4));
+            acc.x += ws * v.x;
+            acc.y += ws * v.y;
+            acc.z += ws * v.z;
+            acc.w += ws * v.w;
+          }
+        }
+        red_s[grp * 32 + lane4] = acc;
+        __syncthreads();
+        float den_all = lane4 < kThreads / 32 ? part_s[lane4] : 0.f;
+        for (int o = 16; o > 0; o >>= 1) den_all += __shfl_xor_sync(kFull, den_all, o);
+        const float inv = 1.f / ((den_all == 0.f) ? 1.f : den_all);
+        if (tid < D) {
+          const float* col = reinterpret_cast<const float*>(red_s) + tid;  // element tid of every group's row
+          float num = 0.f;
+#pragma unroll
+          for (int g2 = 0; g2 < kThreads / 32; ++g2) num += col[g2 * 128];
+          store_from_float(a.out, (int64_t)b * a.o_sb + (int64_t)r * a.o_sh + (int64_t)tid * a.o_sd, a.out_dtype, num * inv);
+        }
+        if (tid == 0 && a.lse_out != nullptr)
+          a.lse_out[(int64_t)b * a.heads_q + r] = (den_all == 0.f) ? kNegInf : (Ms + logf(den_all));
+        __syncthreads();  // the staging arrays are free for the next row
+      }
+    }
+    if (tid == 0 && atomicAdd(depart, 1u) == (unsigned int)ctas_b - 1u) {
+      *arrive = 0u;
+      *depart = 0u;
+      __threadfence();
+    }
+  }
 
   if (!kPaged && a.tickets != nullptr) {
     // Merge inside the kernel: every CTA of this (batch, kv head) takes a ticket once its partials are written; the
@@ -883,6 +971,8 @@ int make_page_map(CUtensorMap* map, const void* ptr, int dtype, int D, int heads
   return 0;
 }
 
+constexpr int kCooperativeRefused = 1;  // launch_kernel: the cooperative launch was not accepted, nothing was launched
+
 template <typename T, int D, bool kPaged>
 int launch_kernel(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mvr,
                   const DecArgs& a, int ctas, cudaStream_t stream) {
@@ -892,7 +982,29 @@ int launch_kernel(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMa
   auto kern = decode_tc_kernel<T, D, kPaged>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "decode smem opt-in failed: %s", cudaGetErrorString(e));
-  kern<<<dim3(ctas, kPaged ? (a.balanced ? 1 : a.batch) : a.batch * a.heads_kv), kThreads, smem, stream>>>(mq, mk, mv, mvr, a);
+  const dim3 grid(ctas, kPaged ? (a.balanced ? 1 : a.batch) : a.batch * a.heads_kv);
+  if (kPaged && a.tickets != nullptr) {
+    // the CTAs of a sequence wait for one another before they merge: only under a launch that guarantees that all of
+    // them are resident
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr = {};
+    attr.id = cudaLaunchAttributeCooperative;
+    attr.val.cooperative = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    e = cudaLaunchKernelEx(&cfg, kern, mq, mk, mv, mvr, a);
+    if (e == cudaSuccess) e = cudaGetLastError();
+    if (e != cudaSuccess) {
+      (void)cudaGetLastError();
+      return kCooperativeRefused;  // the caller launches the two-kernel form instead
+    }
+    return 0;
+  }
+  kern<<<grid, kThreads, smem, stream>>>(mq, mk, mv, mvr, a);
   e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "tcgen05 decode launch failed: %s", cudaGetErrorString(e));
   return 0;
@@ -956,6 +1068,18 @@ unsigned int* ticket_region(const void* partial_buffer, bool capturing) {
   if (tab.used == kTicketRegions) return nullptr;
   tab.owner[tab.used] = partial_buffer;
   return tab.base + (tab.used++) * kTicketWords;
+}
+
+// Whether the current device takes cooperative launches (asked once per device).
+bool cooperative_launch_ok() {
+  static int cached[kTicketDevices] = {};  // 0 unknown, 1 yes, 2 no
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kTicketDevices) return false;
+  if (cached[dev] == 0) {
+    int v = 0;
+    cached[dev] = (cudaDeviceGetAttribute(&v, cudaDevAttrCooperativeLaunch, dev) == cudaSuccess && v) ? 1 : 2;
+  }
+  return cached[dev] == 1;
 }
 
 // Test hook (fa_test_decode_fault): poll limit and tile to leave out for the next tensor-core decode launch of this
@@ -1119,8 +1243,29 @@ int launch_paged_tc(const fa_paged_params& p, cudaStream_t stream) {
     a.balanced = 1;
     ctas = sms;
   }
+  // Balanced mode merges inside the kernel when the launch can be cooperative (every CTA resident, so the CTAs of a
+  // sequence may wait for one another), there is a ticket region for this partial buffer and the stream is not being
+  // captured; otherwise the merge kernel follows.
+  if (p.balance && 2 * ctas <= kThreads && 2 * p.batch <= kTicketWords) {
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    const bool capturing = cudaStreamIsCapturing(stream, &cap) == cudaSuccess && cap != cudaStreamCaptureStatusNone;
+    if (!capturing && cooperative_launch_ok()) {
+      a.tickets = ticket_region(p.o_partial, false);
+      a.out = p.out;
+      a.out_dtype = p.out_is_f32 ? (int)FA_F32 : p.dtype;
+      a.o_sb = p.o_strides[0];
+      a.o_sh = p.o_strides[1];
+      a.o_sd = p.o_strides[2];
+      a.lse_out = p.lse_out;
+    }
+  }
   rc = dispatch<true>(p.dtype, D, mq, mk, mv, mvr, a, ctas, stream);
+  if (rc == kCooperativeRefused) {
+    a.tickets = nullptr;
+    rc = dispatch<true>(p.dtype, D, mq, mk, mv, mvr, a, ctas, stream);
+  }
   if (rc) return rc;
+  if (a.tickets != nullptr) return 0;
   const int nrows = p.batch * p.heads_q;
   return launch_combine_internal(nrows, D, p.num_splits, p.o_partial, D, (int64_t)p.num_splits * D, p.lse_partial, 1,
                                  p.num_splits, p.out, p.out_is_f32 ? (int)FA_F32 : p.dtype, p.heads_q, 1, p.o_strides[0],
