@@ -244,3 +244,28 @@ def test_unsupported_calls_fall_through_on_cpu():
     with fa_b200.use_flash_attention():
         out = F.scaled_dot_product_attention(q, q, q)
     assert torch.allclose(out, F.scaled_dot_product_attention(q, q, q))
+
+
+def test_wide_batch_pieces(monkeypatch):
+    """Batch ranges for the scratch-buffer kernels of wide head dims: one range while the scratch fits its limit, else as
+    many batch entries per launch as fit; never for widths or dtypes those kernels do not take."""
+    from fa_b200 import interface as I
+
+    q = torch.empty(6, 4, 300, 256, dtype=torch.float16)
+    k = torch.empty(6, 2, 500, 256, dtype=torch.float16)
+    per_entry = 2 * 4 * 3 * 4 * 32768                      # two tiles per 128 x 128 block, 4 heads, 3 x 4 blocks
+    monkeypatch.setattr(I, "DS_WORKSPACE_WIDE_LIMIT_BYTES", 6 * per_entry)
+    assert I._wide_batch_pieces(q, k, 2, 128) == [(0, 6)]
+    monkeypatch.setattr(I, "DS_WORKSPACE_WIDE_LIMIT_BYTES", 2 * per_entry + 5)
+    assert I._wide_batch_pieces(q, k, 2, 128) == [(0, 2), (2, 4), (4, 6)]
+    monkeypatch.setattr(I, "DS_WORKSPACE_WIDE_LIMIT_BYTES", 4 * per_entry)
+    assert I._wide_batch_pieces(q, k, 2, 128) == [(0, 4), (4, 6)]
+    monkeypatch.setattr(I, "DS_WORKSPACE_WIDE_LIMIT_BYTES", per_entry - 1)   # not even one entry: left to the caller
+    assert I._wide_batch_pieces(q, k, 2, 128) == [(0, 6)]
+    monkeypatch.setattr(I, "DS_WORKSPACE_WIDE_LIMIT_BYTES", per_entry)
+    assert I._wide_batch_pieces(q[..., :128], k[..., :128], 2, 128) == [(0, 6)]            # fused kernels' width
+    assert I._wide_batch_pieces(q.float(), k.float(), 2, 128) == [(0, 6)]                  # fp32 is never cut
+    # forward scratch of head dims above 256: one tile per block plus 8 bytes per padded query row
+    q5, k5 = torch.empty(3, 2, 256, 512, dtype=torch.bfloat16), torch.empty(3, 2, 256, 512, dtype=torch.bfloat16)
+    monkeypatch.setattr(I, "DS_WORKSPACE_WIDE_LIMIT_BYTES", 2 * (2 * 2 * 32768 + 2 * 1024))
+    assert I._wide_batch_pieces(q5, k5, 1, 256) == [(0, 1), (1, 2), (2, 3)]
