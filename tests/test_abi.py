@@ -141,3 +141,14 @@ def test_product_does_not_import_the_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".h")):
                 text = open(os.path.join(dirpath, f)).read()
                 assert "oracle" not in text.replace("forced-split oracle", ""), os.path.join(dirpath, f)
+
+
+def test_build_entry_point_runs():
+    """The repository's build entry compiles what is out of date (nothing, after a build), loads the library and checks
+    its ABI version and exports against the package; it broke once on an ABI bump that only changed the header."""
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("graft_entry_under_test", os.path.join(ROOT, "__graft_entry__.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    mod.build()
