@@ -187,13 +187,13 @@ def _peer_gather(world, rank, rows, head_dim, device, group):
     if id(group) in _push_unavailable:
         return None
     made = _PeerGather(world, rank, rows, head_dim, device, group)   # no IPC here, no peer path, ...: made.error
-    verdicts = [None] * world
-    dist.all_gather_object(verdicts, made.error, group=group)                              # collective 3
-    if any(v is not None for v in verdicts):
+    votes = [None] * world
+    dist.all_gather_object(votes, made.error, group=group)                              # collective 3
+    if any(v is not None for v in votes):
         _push_unavailable.add(id(group))
         import warnings
         warnings.warn("fa_b200: peer-store merge unavailable, using the NCCL all-gather: "
-                      + "; ".join(f"rank {r}: {v}" for r, v in enumerate(verdicts) if v is not None), RuntimeWarning)
+                      + "; ".join(f"rank {r}: {v}" for r, v in enumerate(votes) if v is not None), RuntimeWarning)
         return None
     _peer_gathers[key] = made
     return made
