@@ -25,6 +25,8 @@
 #include "fa_prof.cuh"
 
 #include <mutex>
+#include <unordered_map>
+#include <utility>
 
 namespace fa {
 
@@ -1033,24 +1035,26 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 
 // Ticket words of the in-kernel merge: a fixed array inside the library image (zero when the module is loaded, and
 // every finished launch leaves its words at zero again), so the library never allocates. Launches that may run at the
 // same time (different streams) must not share words; such launches use different partial buffers, so each partial
-// buffer address gets a region of its own, for good: once all kTicketRegions regions of a device belong to other
-// buffers, further buffers simply keep the separate merge kernel. Regions are never handed to a second buffer, so a
-// captured graph that holds a region pointer stays valid whatever runs later.
-constexpr int kTicketRegions = 64, kTicketWords = 1024, kTicketDevices = 64;
-static __device__ __align__(256) unsigned int g_ticket_words[kTicketRegions * kTicketWords];
+// buffer address gets a region of its own, for good, of as many words as its problem needs (rounded up to 16): 256 KB
+// serve some thousand buffers. Once the array is used up, further buffers simply keep the separate merge kernel.
+// Regions are never handed to a second buffer, so a captured graph that holds a region pointer stays valid whatever
+// runs later; a buffer that comes back with a larger problem gets a new, larger region.
+constexpr int kTicketWordsTotal = 64 * 1024, kTicketWords = 1024, kTicketDevices = 64;
+static __device__ __align__(256) unsigned int g_ticket_words[kTicketWordsTotal];
 
 struct TicketTable {
   unsigned int* base = nullptr;  // device address of g_ticket_words in this device's context
-  const void* owner[kTicketRegions] = {};
-  int used = 0;
+  std::unordered_map<const void*, std::pair<int, int>> region;  // partial buffer -> (first word, words)
+  int next = 0;
 };
 std::mutex g_ticket_mutex;
 TicketTable g_ticket_table[kTicketDevices];
 
-// Region for this partial buffer on the current device, or nullptr (no region left, or the array's address is not
+// `words` ticket words for this partial buffer on the current device, or nullptr (array used up, or its address is not
 // known yet and cannot be asked for because the stream is being captured).
-unsigned int* ticket_region(const void* partial_buffer, bool capturing) {
+unsigned int* ticket_region(const void* partial_buffer, int words, bool capturing) {
   int dev = 0;
+  if (words <= 0 || words > kTicketWords) return nullptr;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kTicketDevices) return nullptr;
   std::lock_guard<std::mutex> lock(g_ticket_mutex);
   TicketTable& tab = g_ticket_table[dev];
@@ -1063,11 +1067,14 @@ unsigned int* ticket_region(const void* partial_buffer, bool capturing) {
     }
     tab.base = static_cast<unsigned int*>(ptr);
   }
-  for (int i = 0; i < tab.used; ++i)
-    if (tab.owner[i] == partial_buffer) return tab.base + i * kTicketWords;
-  if (tab.used == kTicketRegions) return nullptr;
-  tab.owner[tab.used] = partial_buffer;
-  return tab.base + (tab.used++) * kTicketWords;
+  auto it = tab.region.find(partial_buffer);
+  if (it != tab.region.end() && it->second.second >= words) return tab.base + it->second.first;
+  const int take = (words + 15) & ~15;
+  if (tab.next + take > kTicketWordsTotal) return nullptr;
+  tab.region[partial_buffer] = std::make_pair(tab.next, take);
+  unsigned int* out = tab.base + tab.next;
+  tab.next += take;
+  return out;
 }
 
 // Whether the current device takes cooperative launches (asked once per device).
@@ -1151,7 +1158,7 @@ int launch_decode_tc(const fa_decode_params& p, cudaStream_t stream) {
   if ((int64_t)rows * D * p.num_splits <= 65536 && (int64_t)p.batch * p.heads_kv <= kTicketWords && D % 4 == 0) {
     cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
     const bool capturing = cudaStreamIsCapturing(stream, &cap) == cudaSuccess && cap != cudaStreamCaptureStatusNone;
-    a.tickets = ticket_region(p.o_partial, capturing);
+    a.tickets = ticket_region(p.o_partial, p.batch * p.heads_kv, capturing);
   }
   a.out = p.out;
   a.out_dtype = p.dtype;
@@ -1250,7 +1257,7 @@ int launch_paged_tc(const fa_paged_params& p, cudaStream_t stream) {
     cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
     const bool capturing = cudaStreamIsCapturing(stream, &cap) == cudaSuccess && cap != cudaStreamCaptureStatusNone;
     if (!capturing && cooperative_launch_ok()) {
-      a.tickets = ticket_region(p.o_partial, false);
+      a.tickets = ticket_region(p.o_partial, 2 * p.batch, false);
       a.out = p.out;
       a.out_dtype = p.out_is_f32 ? (int)FA_F32 : p.dtype;
       a.o_sb = p.o_strides[0];

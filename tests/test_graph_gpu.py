@@ -58,3 +58,28 @@ def test_decode_replays_from_a_graph():
     graph.replay()
     torch.cuda.synchronize()
     assert max_abs(captured, eager) == 0.0
+
+
+def test_paged_decode_replays_from_a_graph():
+    """Under capture the paged kernel keeps its separate merge kernel (the merge inside the kernel needs a cooperative
+    launch); the replayed result equals the eager one up to the different summation order of the two merges."""
+    import fa_b200
+    from test_decode_gpu import make_paged
+
+    q, kc, vc, table, ctx = make_paged(3, 32, 8, 128, 16, [3000, 40, 1777], seed=21)
+    eager = fa_b200.flash_attention_decode_paged(q, kc, vc, table, ctx)
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        fa_b200.flash_attention_decode_paged(q, kc, vc, table, ctx)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        captured = fa_b200.flash_attention_decode_paged(q, kc, vc, table, ctx)
+    for _ in range(3):
+        captured.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert max_abs(captured, eager) <= 1e-3
+    fa_b200.check_status()
