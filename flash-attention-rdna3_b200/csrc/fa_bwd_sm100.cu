@@ -13,14 +13,14 @@
 //     S^T  = K Q^T          dP^T = V dO^T                  (M = 128 keys, N = 128 queries)
 //     P^T  = exp2(S^T*c - lse[q]) ;  dS^T = P^T * (dP^T - delta[q])      (lse/delta per column, staged in smem)
 //     dV  += P^T dO         dK  += dS^T Q                  (A from TMEM, B = the same smem tiles, MN-major)
-// TMEM: S^T/P^T [0,128); dP^T/dS^T [128,256); dK [256,256+D); dV [256+D,256+2D).
+// TMEM: S^T [0,128); dP^T, then P^T and dS^T [128,256); dK [256,256+D); dV [256+D,256+2D).
 //
 // dQ kernel: persistent CTAs walking 128-query tiles; Q and dO stay resident, K/V stream in 128-key steps:
 //     S = Q K^T    dP = dO V^T    dS = P*(dP - delta[row])    dQ += dS K
 // TMEM: S buffers [0,128) [128,256); dP [256,384); dQ [384,384+D).
 //
-// The 16-bit P^T / dS^T (and dS) operands overwrite fp32 score columns of their own group's half, 16 columns at
-// a time, only over columns the writing thread has already consumed.
+// The 16-bit P^T / dS^T (and dS) operands overwrite fp32 score columns of their own group's half, only over columns
+// the writing thread has already consumed.
 //
 // Math follows fa_rdna3/kernels/_common.py:347-508 and fa_rdna3/kernels/backward.py:56-322 (varlen:
 // fa_rdna3/kernels/varlen.py:193-421): P recomputed from LSE, rows with LSE = -inf contribute nothing,
@@ -97,7 +97,7 @@ struct DkdvSmem {
   static constexpr int kOffDo = kOffQ + kQStages * kTileBytes;
   static constexpr int kOffStage = kOffDo + kDoStages * kTileBytes;  // 128 x (-lse*log2e), 128 x (-delta)
   static constexpr int kOffBars = kOffStage + 256 * 4;
-  static constexpr int kNumBars = 7 + 2 * kQStages + 2 * kDoStages;
+  static constexpr int kNumBars = 8 + 2 * kQStages + 2 * kDoStages;
   static constexpr int kOffTmemPtr = kOffBars + kNumBars * 8;
   static constexpr int kBytes = kOffTmemPtr + 8 + 1024;  // + slack to round the base up to 1024
   static_assert(kBytes <= 232448, "dK/dV shared memory plan exceeds one CTA's 227 KB");
@@ -107,14 +107,18 @@ __device__ __forceinline__ void compute_sync() {
   asm volatile("bar.sync 1, 256;" ::: "memory");  // the eight compute warps
 }
 
-// One CTA per 128-key tile of one (batch, kv head). The tensor pipe is kept busy by a two-phase software pipeline
-// over 128-query steps (step i of the pipe, all issued by one thread, in this order):
-//     dV  += P^T(i) dO(i)         needs phase 1 of step i
-//     S^T(i+1) = K Q(i+1)^T       overwrites P^T(i); phase 1 of step i+1 starts when it lands
+// One CTA per 128-key tile of one (batch, kv head). Step i of the pipe (128 queries; all MMAs issued by one thread, in
+// this order):
+//     S^T(i+1) = K Q(i+1)^T       as soon as the compute warps hold S^T(i) in registers (start of phase 1 of step i)
+//     dV  += P^T(i) dO(i)         needs phase 1 of step i and dP^T(i) read into registers
 //     dK  += dS^T(i) Q(i)         needs phase 2 of step i
-//     dP^T(i+1) = V dO(i+1)^T     overwrites dS^T(i); phase 2 of step i+1 starts when it lands
-// so each elementwise phase overlaps two MMAs of the neighbouring steps and all 512 TMEM columns are in use
-// without double buffering: S^T/P^T [0,128), dP^T/dS^T [128,256), dK [256,256+D), dV [256+D,256+2D).
+//     dP^T(i+1) = V dO(i+1)^T     overwrites P^T(i) and dS^T(i)
+// The 16-bit P^T and dS^T of a group both live in that group's 64 dP^T columns (first and second 32), which a thread
+// overwrites only after it has read its dP^T values; the S^T columns are therefore free during the whole of phase 1
+// and the next scores are formed behind it, off the phase 1 -> dV -> S^T -> phase 1 chain. All 512 TMEM columns are in
+// use without double buffering: S^T [0,128), dP^T/P^T/dS^T [128,256), dK [256,256+D), dV [256+D,256+2D).
+// With score modifiers (kMods) both score tiles are consumed in one pass, P^T stays in its S^T columns and S^T(i+1)
+// follows dV(i) instead.
 template <typename T, int D, bool kMods>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -141,7 +145,8 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   uint64_t* dp_full = bars + 4;
   uint64_t* ds_full = bars + 5;
   uint64_t* acc_done = bars + 6;
-  uint64_t* q_full = bars + 7;
+  uint64_t* s_free = bars + 7;
+  uint64_t* q_full = bars + 8;
   uint64_t* q_empty = q_full + kQS;
   uint64_t* do_full = q_empty + kQS;
   uint64_t* do_empty = do_full + kDS;
@@ -180,6 +185,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     mbar_init(dp_full, 1);
     mbar_init(ds_full, 256);
     mbar_init(acc_done, 1);
+    mbar_init(s_free, 256);
     for (int i = 0; i < kQS; ++i) {
       mbar_init(&q_full[i], 1);
       mbar_init(&q_empty[i], 1);
@@ -211,9 +217,9 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         for (int c = 0; c < kChunks; ++c) tma_load_4d(dst + c * 16384, map, bar, c * 64, row, head, tb);
       };
       load_tile(sK, &map_k, k_full, k_start + k0, hk);
+      int h = hk * group, step = 0;
       for (int n = 0; n < n_total; ++n) {
-        const int h = hk * group + n / steps_per_head;
-        const int row = q_start + (slo + n % steps_per_head) * 128;
+        const int row = q_start + (slo + step) * 128;
         const int qs = n % kQS, ds = n % kDS;
         if (!mbar_wait(&q_empty[qs], ((n / kQS) & 1) ^ 1)) {
           report_timeout(a.status, 201);
@@ -226,6 +232,10 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           break;
         }
         load_tile(sDo + ds * kTileBytes, &map_do, &do_full[ds], row, h);
+        if (++step == steps_per_head) {
+          step = 0;
+          ++h;
+        }
       }
     }
   } else if (warp == 9) {
@@ -286,14 +296,28 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         const int qs = n % kQS, ds = n % kDS;
         const int qs1 = (n + 1) % kQS, ds1 = (n + 1) % kDS;
         const bool more = n + 1 < n_total;
+        // Plain path: P^T and dS^T both sit in the dP^T columns (the first and the second 32 of each group's 64), so
+        // the S^T columns are free as soon as the compute warps hold step n's scores in registers and the next
+        // scores are formed during phase 1 instead of behind dV. Modified scores: P^T stays in its S^T columns.
+        constexpr uint32_t kColP = kMods ? kColS : kColDP, kColDs = kMods ? kColDP : kColDP + 32;
+        if (!kMods && more) {
+          wait_or_report(s_free, n & 1, 210);
+          wait_or_report(&q_full[qs1], ((n + 1) / kQS) & 1, 203);
+          PROF_MARK(3);
+          if (!ok) break;
+          tc_fence_after_sync();
+          scores(kColS, k_addr, q_base + qs1 * kTileBytes);
+          tc_commit(s_full);
+          PROF_MARK(2);
+        }
         wait_or_report(p_full, n & 1, 204);
         PROF_MARK(1);
         if (!ok) break;
         tc_fence_after_sync();
-        accumulate(kColDV, kColS, do_base + ds * kTileBytes, n == 0);
+        accumulate(kColDV, kColP, do_base + ds * kTileBytes, n == 0);
         tc_commit(&do_empty[ds]);
         PROF_MARK(2);
-        if (more) {
+        if (kMods && more) {
           wait_or_report(&q_full[qs1], ((n + 1) / kQS) & 1, 203);
           PROF_MARK(3);
           if (!ok) break;
@@ -306,7 +330,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         PROF_MARK(4);
         if (!ok) break;
         tc_fence_after_sync();
-        accumulate(kColDK, kColDP, q_base + qs * kTileBytes, n == 0);
+        accumulate(kColDK, kColDs, q_base + qs * kTileBytes, n == 0);
         tc_commit(&q_empty[qs]);
         PROF_MARK(2);
         if (more) {
@@ -335,33 +359,51 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     const int64_t bo = a.varlen ? 0 : (int64_t)b;
     bool ok = true;
     PROF_DECL;
-    // threads 0-127 fetch -lse*log2(e) (-inf = contributes nothing), threads 128-255 fetch -delta, of query tid & 127
-    auto fetch_row_stat = [&](int n) {
-      const int h = hk * group + n / steps_per_head;
-      const int i = (slo + n % steps_per_head) * 128 + (tid & 127);
-      float val = tid < 128 ? kNegInf : 0.f;
-      if (i < Sq) {
-        if (tid < 128) {
-          const float l = a.lse[bo * a.l_sb + (int64_t)h * a.l_sh + (int64_t)(q_start + i) * a.l_ss];
-          val = (l == kNegInf) ? kNegInf : -l * kLog2e;
-        } else {
-          val = -a.delta[bo * a.d_sb + (int64_t)h * a.d_sh + (int64_t)(q_start + i) * a.d_ss];
-        }
+    // threads 0-127 fetch -lse*log2(e) (-inf = contributes nothing), threads 128-255 fetch -delta, of query tid & 127.
+    // Head and step are carried along instead of divided out of n, and the address is kept as a pointer: with two
+    // compute warps per scheduler a chain of dependent integer instructions costs its full latency every step.
+    const bool is_lse = tid < 128;
+    const int64_t st_sh = is_lse ? a.l_sh : a.d_sh, st_ss = is_lse ? a.l_ss : a.d_ss;
+    const int f_i0 = slo * 128 + (tid & 127);
+    const float* f_head = (is_lse ? a.lse + bo * a.l_sb : a.delta + bo * a.d_sb) + (int64_t)(hk * group) * st_sh +
+                          (int64_t)(q_start + f_i0) * st_ss;
+    const float* f_ptr = f_head;
+    int f_i = f_i0, f_step = 0;
+    auto fetch_row_stat = [&]() {  // the next step's value; advances the position
+      float val = is_lse ? kNegInf : 0.f;
+      if (f_i < Sq) {
+        const float l = *f_ptr;
+        val = is_lse ? ((l == kNegInf) ? kNegInf : -l * kLog2e) : -l;
+      }
+      if (++f_step == steps_per_head) {
+        f_step = 0;
+        f_head += st_sh;
+        f_ptr = f_head;
+        f_i = f_i0;
+      } else {
+        f_ptr += 128 * st_ss;
+        f_i += 128;
       }
       return val;
     };
-    float staged = n_total > 0 ? fetch_row_stat(0) : 0.f;
+    float staged = n_total > 0 ? fetch_row_stat() : 0.f;
+    const int64_t ds_head_stride = (int64_t)a.ds_kt * a.ds_qt * 32768;
+    uint8_t* ds_head = a.ds_ws == nullptr
+                           ? nullptr
+                           : reinterpret_cast<uint8_t*>(a.ds_ws) +
+                                 (((int64_t)b * a.heads_q + hk * group) * a.ds_kt + ktile) * a.ds_qt * 32768 +
+                                 wg * 8 * 2048 + key_row * 16;
+    int h = hk * group, step = 0;
 
     for (int n = 0; n < n_total; ++n) {
-      const int h = hk * group + n / steps_per_head;
-      const int q0 = (slo + n % steps_per_head) * 128;
+      const int q0 = (slo + step) * 128;
       const int par = n & 1;
       if (kMods) mods = make_mods(a, b, h, Sq, Sk);
       // publish -lse*log2(e) / -delta of this step's 128 queries (fetched one step ahead), then fetch the next
       compute_sync();  // every thread is done reading the previous step's values
       nlse_s[tid] = staged;  // nlse_s[0,128) then ndelta_s[0,128)
       compute_sync();
-      if (n + 1 < n_total) staged = fetch_row_stat(n + 1);
+      if (n + 1 < n_total) staged = fetch_row_stat();
       PROF_MARK(6);
       bool w_ok = mbar_wait(s_full, par);
       if (kMods) w_ok = mbar_wait(dp_full, par) && w_ok;
@@ -384,35 +426,34 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       }
       const uint64_t sc2 = pack_f32x2(mods.scale_log2, mods.scale_log2);
       // this thread's key row in the first of its eight query blocks of the step's dS^T tile, if there is a workspace
-      uint8_t* ds_row = nullptr;
-      if (a.ds_ws != nullptr)
-        ds_row = reinterpret_cast<uint8_t*>(a.ds_ws) +
-                 ((((int64_t)b * a.heads_q + h) * a.ds_kt + ktile) * a.ds_qt + q0 / 128) * 32768 + wg * 8 * 2048 +
-                 key_row * 16;
+      uint8_t* ds_row = ds_head == nullptr ? nullptr : ds_head + (int64_t)(slo + step) * 32768;
+      if (++step == steps_per_head) {  // for the next iteration
+        step = 0;
+        ++h;
+        if (ds_head != nullptr) ds_head += ds_head_stride;
+      }
 
       if (!kMods) {
-        // ---- phase 1: P^T = exp2(S^T * c - lse[q]) -> TMEM (16-bit, in place) and registers
+        // ---- phase 1: P^T = exp2(S^T * c - lse[q]) in registers; the S^T columns go back to the MMA thread at once
         uint32_t pk[32];
         {
           uint32_t s0[32], s1[32];
           tmem_ld32(tS, s0);
+          tmem_ld32(tS + 32, s1);
           tc_wait_ld_regs(s0);
-          tmem_ld32(tS + 32, s1);  // in flight while the first half is processed
+          tc_wait_ld_regs(s1);
+          tc_fence_before_sync();
+          mbar_arrive(s_free);
           const float* nl = nlse_s + wg * 64;
           if (masked) probs_chunk<T, true>(s0, nl, sc2, wg * 64, c_lo, c_hi, &pk[0]);
           else probs_chunk<T, false>(s0, nl, sc2, wg * 64, c_lo, c_hi, &pk[0]);
-          tmem_st16(tS, *reinterpret_cast<uint32_t(*)[16]>(&pk[0]));
-          tc_wait_ld_regs(s1);
           if (masked) probs_chunk<T, true>(s1, nl + 32, sc2, wg * 64 + 32, c_lo, c_hi, &pk[16]);
           else probs_chunk<T, false>(s1, nl + 32, sc2, wg * 64 + 32, c_lo, c_hi, &pk[16]);
-          tmem_st16(tS + 16, *reinterpret_cast<uint32_t(*)[16]>(&pk[16]));
         }
-        tc_wait_st();
-        tc_fence_before_sync();
-        mbar_arrive(p_full);
         PROF_MARK(4);
 
-        // ---- phase 2: dS^T = P^T * (dP^T - delta[q]) -> TMEM (16-bit, in place)
+        // ---- phase 2: dP^T into registers, then P^T (16-bit) over the first half of this group's dP^T columns and
+        // dS^T = P^T * (dP^T - delta[q]) over the second half
         const bool d_ok = mbar_wait(dp_full, par);
         if (!__all_sync(kFull, d_ok)) {
           report_timeout(a.status, 209);
@@ -425,14 +466,19 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         {
           uint32_t d0[32], d1[32];
           tmem_ld32(tDP, d0);
-          tc_wait_ld_regs(d0);
           tmem_ld32(tDP + 32, d1);
+          tc_wait_ld_regs(d0);
+          tc_wait_ld_regs(d1);
+          tmem_st16(tDP, *reinterpret_cast<uint32_t(*)[16]>(&pk[0]));
+          tmem_st16(tDP + 16, *reinterpret_cast<uint32_t(*)[16]>(&pk[16]));
+          tc_wait_st();
+          tc_fence_before_sync();
+          mbar_arrive(p_full);
           const float* nd = ndelta_s + wg * 64;
           dscore_chunk<T>(d0, nd, &pk[0], dsk0);
-          tmem_st16(tDP, dsk0);
-          tc_wait_ld_regs(d1);
+          tmem_st16(tDP + 32, dsk0);
           dscore_chunk<T>(d1, nd + 32, &pk[16], dsk1);
-          tmem_st16(tDP + 16, dsk1);
+          tmem_st16(tDP + 48, dsk1);
         }
         tc_wait_st();
         tc_fence_before_sync();
