@@ -95,11 +95,11 @@ struct DkdvSmem {
   static constexpr int kOffV = kTileBytes;
   static constexpr int kOffQ = 2 * kTileBytes;
   static constexpr int kOffDo = kOffQ + kQStages * kTileBytes;
-  static constexpr int kOffStage = kOffDo + kDoStages * kTileBytes;  // 128 x (-lse*log2e), 128 x (-delta)
-  static constexpr int kOffBars = kOffStage + 256 * 4;
+  static constexpr int kOffStage = kOffDo + kDoStages * kTileBytes;  // two sets of 128 x (-lse*log2e), 128 x (-delta)
+  static constexpr int kOffBars = kOffStage + 2 * 256 * 4;
   static constexpr int kNumBars = 8 + 2 * kQStages + 2 * kDoStages;
   static constexpr int kOffTmemPtr = kOffBars + kNumBars * 8;
-  static constexpr int kBytes = kOffTmemPtr + 8 + 1024;  // + slack to round the base up to 1024
+  static constexpr int kBytes = kOffTmemPtr + 8;  // the dynamic region is declared 1024-byte aligned (and checked)
   static_assert(kBytes <= 232448, "dK/dV shared memory plan exceeds one CTA's 227 KB");
 };
 
@@ -129,14 +129,18 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   constexpr int kTileBytes = L::kTileBytes;
   constexpr int kQS = L::kQStages, kDS = L::kDoStages;
 
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  // The 128-byte swizzle wants tiles on 1 KB boundaries and the plan leaves no room to round the base up.
+  extern __shared__ __align__(1024) uint8_t smem_dkdv[];
+  uint8_t* smem = smem_dkdv;
+  if ((smem_u32(smem) & 1023u) != 0) {  // never seen; leave before anything is set up rather than run past the end
+    if (threadIdx.x == 0) report_timeout(a.status, 211);
+    return;
+  }
   uint8_t* sK = smem + L::kOffK;
   uint8_t* sV = smem + L::kOffV;
   uint8_t* sQ = smem + L::kOffQ;
   uint8_t* sDo = smem + L::kOffDo;
-  float* nlse_s = reinterpret_cast<float*>(smem + L::kOffStage);
-  float* ndelta_s = nlse_s + 128;
+  float* stage_s = reinterpret_cast<float*>(smem + L::kOffStage);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kOffBars);
   uint64_t* k_full = bars + 0;
   uint64_t* v_full = bars + 1;
@@ -369,12 +373,11 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
                           (int64_t)(q_start + f_i0) * st_ss;
     const float* f_ptr = f_head;
     int f_i = f_i0, f_step = 0;
+    // The raw value is returned and only converted when it is published a step later: anything computed from it here
+    // would wait for the load, a trip to L2, in every step.
     auto fetch_row_stat = [&]() {  // the next step's value; advances the position
       float val = is_lse ? kNegInf : 0.f;
-      if (f_i < Sq) {
-        const float l = *f_ptr;
-        val = is_lse ? ((l == kNegInf) ? kNegInf : -l * kLog2e) : -l;
-      }
+      if (f_i < Sq) val = *f_ptr;
       if (++f_step == steps_per_head) {
         f_step = 0;
         f_head += st_sh;
@@ -400,8 +403,11 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       const int par = n & 1;
       if (kMods) mods = make_mods(a, b, h, Sq, Sk);
       // publish -lse*log2(e) / -delta of this step's 128 queries (fetched one step ahead), then fetch the next
-      compute_sync();  // every thread is done reading the previous step's values
-      nlse_s[tid] = staged;  // nlse_s[0,128) then ndelta_s[0,128)
+      // (two sets in turn: a thread may still be reading step n - 1's values; nobody is behind that, because everybody
+      // passed the barrier of step n - 1)
+      float* nlse_s = stage_s + (n & 1) * 256;  // nlse_s[0,128) then ndelta_s[0,128)
+      float* ndelta_s = nlse_s + 128;
+      nlse_s[tid] = is_lse ? ((staged == kNegInf) ? kNegInf : -staged * kLog2e) : -staged;
       compute_sync();
       if (n + 1 < n_total) staged = fetch_row_stat();
       PROF_MARK(6);
