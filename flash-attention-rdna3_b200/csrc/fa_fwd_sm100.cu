@@ -329,11 +329,13 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         for (int t = 0; t < 2; ++t) {
           if (kSpareP && have_next && in_range(t, j + 1)) {
             // the next scores first: their S tile is free once the softmax group has read the current ones
+            PROF_MARK(2);
             if (in_range(t, j) && !mbar_wait(&s_free[t], (j - lo[t]) & 1)) {
               report_timeout(a.status, 107);
               ok = false;
               break;
             }
+            PROF_MARK(3);
             tc_fence_after_sync();
             issue_qk(t, nk_next, t);
           }
