@@ -82,17 +82,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
   constexpr int kQTiles = kWide ? 1 : 2;
   constexpr int kSlots = kWide ? 2 : (D == 128) ? 4 : 6;
   constexpr uint32_t kFull = 0xffffffffu;
-  // D = 64 leaves 128 TMEM columns unused: P gets 64 of them per query tile instead of overwriting its S tile, so the
-  // S tile is free as soon as the softmax group holds the row in registers and the next Q K^T runs during the softmax
-  // instead of behind P V (the softmax, not the tensor pipe, bounds this head dim).
-  constexpr bool kSpareP = (D == 64);
-  constexpr uint32_t kColP = 256 + 2 * D;  // first spare column
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
   uint8_t* sKV = smem + kQTiles * kTileBytes;
-  __shared__ uint64_t q_full[2], kv_full[kSlots], kv_empty[kSlots], s_full[2], p_full[2], o_ready[2], s_free[2];
+  __shared__ uint64_t q_full[2], kv_full[kSlots], kv_empty[kSlots], s_full[2], p_full[2], o_ready[2];
   __shared__ uint32_t tmem_base_s;
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
@@ -160,7 +155,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       mbar_init(&s_full[t], 1);
       mbar_init(&p_full[t], 128);
       mbar_init(&o_ready[t], 1);
-      mbar_init(&s_free[t], 128);
     }
 #pragma unroll
     for (int s = 0; s < kSlots; ++s) {
@@ -256,12 +250,11 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         const uint32_t va = slot_addr(n);
         const uint32_t v_lo = smem_desc_lo(va, 16384);
         constexpr uint32_t hi = smem_desc_hi(1024);
-        const uint32_t p_addr = tmem_base + (kSpareP ? kColP + t * 64 : sbuf * 128);
-        if (first) mma_ts_lo<0>(tmem_base + 256 + t * D, p_addr, v_lo, hi, idesc_pv);
-        else mma_ts_lo<1>(tmem_base + 256 + t * D, p_addr, v_lo, hi, idesc_pv);
+        if (first) mma_ts_lo<0>(tmem_base + 256 + t * D, tmem_base + sbuf * 128, v_lo, hi, idesc_pv);
+        else mma_ts_lo<1>(tmem_base + 256 + t * D, tmem_base + sbuf * 128, v_lo, hi, idesc_pv);
 #pragma unroll
         for (int kk = 1; kk < 8; ++kk)
-          mma_ts_lo<1>(tmem_base + 256 + t * D, p_addr + kk * 8, v_lo + kk * (2048 >> 4), hi, idesc_pv);
+          mma_ts_lo<1>(tmem_base + 256 + t * D, tmem_base + sbuf * 128 + kk * 8, v_lo + kk * (2048 >> 4), hi, idesc_pv);
         tc_commit(&o_ready[t]);
       };
 
@@ -327,18 +320,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         PROF_MARK(0);
 #pragma unroll
         for (int t = 0; t < 2; ++t) {
-          if (kSpareP && have_next && in_range(t, j + 1)) {
-            // the next scores first: their S tile is free once the softmax group has read the current ones
-            PROF_MARK(2);
-            if (in_range(t, j) && !mbar_wait(&s_free[t], (j - lo[t]) & 1)) {
-              report_timeout(a.status, 107);
-              ok = false;
-              break;
-            }
-            PROF_MARK(3);
-            tc_fence_after_sync();
-            issue_qk(t, nk_next, t);
-          }
           if (in_range(t, j)) {
             PROF_MARK(2);
             if (!mbar_wait(&p_full[t], (j - lo[t]) & 1)) {
@@ -351,7 +332,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
             issue_pv(t, nv, j == lo[t], t);
           }
           if (t == 1) tc_commit(&kv_empty[nv % kSlots]);
-          if (!kSpareP && have_next && in_range(t, j + 1)) issue_qk(t, nk_next, t);
+          if (have_next && in_range(t, j + 1)) issue_qk(t, nk_next, t);
           if (t == 1 && have_next) tc_commit(&kv_empty[nk_next % kSlots]);
         }
       }
@@ -387,10 +368,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         // wide head dims: the S tile alternates between the two 128-column buffers with the key tile
         const uint32_t tS = kWide ? tmem_base + lane_addr + (it & 1) * 128 : tS_own;
         bool w_ok = kWide ? mbar_wait(&s_full[it & 1], (it >> 1) & 1) : mbar_wait(&s_full[t], it & 1);
-        // P V of the previous key tile must be complete before O is rescaled or P overwritten. With P in columns of
-        // its own that is checked where it matters (pv_done below), so that P V is not on the path between two softmax
-        // passes; otherwise here.
-        if (!kSpareP && w_ok && it > 0) w_ok = mbar_wait(&o_ready[t], (it - 1) & 1);
+        if (w_ok && it > 0) w_ok = mbar_wait(&o_ready[t], (it - 1) & 1);
         if (!__all_sync(kFull, w_ok)) {
           report_timeout(a.status, 105);
           ok = false;
@@ -398,15 +376,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         }
         tc_fence_after_sync();
         PROF_MARK(0);
-        const uint32_t tP = kSpareP ? tmem_base + lane_addr + kColP + t * 64 : tS;  // where the 16-bit P goes
-        bool pv_pending = kSpareP && it > 0;
-        auto pv_done = [&]() {
-          if (!pv_pending) return true;
-          pv_pending = false;
-          const bool d_ok = mbar_wait(&o_ready[t], (it - 1) & 1);
-          tc_fence_after_sync();
-          return d_ok;
-        };
 
         const int k0 = j * 128;
         const bool tile_masked = (k0 + 128 > Sk) || (a.causal && (k0 + 127 > r0 + off)) ||
@@ -445,19 +414,11 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
           PROF_MARK(2);
           const float m_new = fmaxf(m_used, m_tile);
           const bool grow = m_new > m_used + kRescaleThreshold;
-          bool d_ok = true;
           if (__any_sync(kFull, grow)) {
             const float alpha = (m_new == kNegInf) ? 1.f : exp2f(m_used - m_new);
             l *= alpha;
-            d_ok = pv_done();
             if (it > 0) rescale_o<D>(tO, alpha);
             m_used = m_new;
-          }
-          d_ok = pv_done() && d_ok;
-          if (!__all_sync(kFull, d_ok)) {
-            report_timeout(a.status, 108);
-            ok = false;
-            break;
           }
           const float m_eff = (m_used == kNegInf) ? 0.f : m_used;
           PROF_MARK(3);
@@ -482,13 +443,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
 #pragma unroll
             for (int e = 0; e < 16; ++e) pk[e] = DType<T>::pack2(x[2 * e], x[2 * e + 1]);
             // the 16-bit chunk lands on columns [16c, 16c+16): all of them already read
-            tmem_st16(tP + c * 16, pk);
+            tmem_st16(tS + c * 16, pk);
           }
           l += sum;
-          if (kSpareP) {  // every score has been read: the next Q K^T may overwrite the tile
-            tc_fence_before_sync();
-            mbar_arrive(&s_free[t]);
-          }
         } else {
           // Fast path: the whole S row (128 fp32 values) is read from TMEM once and stays in registers between
           // the maximum and the exponentials.
@@ -499,15 +456,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
             // wait::ld covers every load issued so far; naming the chunk pins its uses behind the wait
-            if (c == 0) {
-              tc_wait_ld_regs(*reinterpret_cast<uint32_t(*)[32]>(&r[0]));
-              if (kSpareP) {  // the whole row is in registers: the next Q K^T may overwrite the tile
-                tc_fence_before_sync();
-                mbar_arrive(&s_free[t]);
-              }
-            } else {
-              asm volatile("" : "+r"(r[c * 32]), "+r"(r[c * 32 + 31]));
-            }
+            if (c == 0) tc_wait_ld_regs(*reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+            else asm volatile("" : "+r"(r[c * 32]), "+r"(r[c * 32 + 31]));
             if (tile_masked) {
 #pragma unroll
               for (int e = 0; e < 32; ++e)
@@ -524,11 +474,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
           PROF_MARK(2);
           const float m_new = fmaxf(m_used, m_tile);
           const bool grow = m_new > m_used + kRescaleThreshold;
-          bool d_ok = true;
           if (__any_sync(kFull, grow)) {
             const float alpha = (m_new == kNegInf) ? 1.f : exp2f(m_used - m_new);
             l *= alpha;
-            d_ok = pv_done();
             if (it > 0) rescale_o<D>(tO, alpha);
             m_used = m_new;
           }
@@ -552,16 +500,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
               acc2[e & 3] = add_f32x2(acc2[e & 3], pack_f32x2(p0, p1));
               pk[e] = DType<T>::pack2(p0, p1);
             }
-            if (c == 0) {  // the first store of P: the previous P V has read the old one (no-op unless kSpareP)
-              d_ok = pv_done() && d_ok;
-              if (!__all_sync(kFull, d_ok)) break;
-            }
-            tmem_st16(tP + c * 16, pk);
-          }
-          if (!__all_sync(kFull, d_ok)) {
-            report_timeout(a.status, 108);
-            ok = false;
-            break;
+            tmem_st16(tS + c * 16, pk);
           }
           float s0, s1;
           unpack_f32x2(add_f32x2(add_f32x2(acc2[0], acc2[1]), add_f32x2(acc2[2], acc2[3])), &s0, &s1);
