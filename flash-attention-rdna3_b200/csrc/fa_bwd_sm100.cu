@@ -168,6 +168,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   }
   // The dQ kernel launched behind this one needs none of its results: let its CTAs take over SMs as they free up.
   grid_launch_dependents();
+  PROF_STAMP(3);
   const int k0 = ktile * 128;
   if (k0 >= Sk) return;
   const int tb = a.varlen ? 0 : b;
@@ -558,6 +559,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 9) tmem_dealloc(tmem_base, 512);
+  PROF_STAMP(7);
 }
 
 // =============================================================================================
@@ -971,6 +973,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 9) tmem_dealloc(tmem_base, 512);
+  PROF_STAMP(7);
 }
 
 // =============================================================================================
