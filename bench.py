@@ -51,7 +51,7 @@ DELTA_BYTES = 2 * B * H * S * D * 2 + B * H * S * 4   # reads O and dO, writes d
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of this workload, from ncu captures of these kernels at this
 # size (a constant, not measured per run). Reads match the operand sizes (every input once); most of the output is
 # still in the write-back L2 when the kernel ends, so the write counter is below the output size.
-NCU_TRAFFIC_BYTES = {"fwd": 51.6e6, "bwd_dkdv": 206.5e6, "bwd_dq": 171.8e6}   # with the dS scratch in use
+NCU_TRAFFIC_BYTES = {"fwd": 51.6e6, "bwd_dkdv": 199.0e6, "bwd_dq": 171.8e6}   # with the dS scratch in use
 
 
 def load_peaks():
