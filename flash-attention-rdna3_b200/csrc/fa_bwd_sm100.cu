@@ -305,9 +305,12 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         // the S^T columns are free as soon as the compute warps hold step n's scores in registers and the next
         // scores are formed during phase 1 instead of behind dV. Modified scores: P^T stays in its S^T columns.
         constexpr uint32_t kColP = kMods ? kColS : kColDP, kColDs = kMods ? kColDP : kColDP + 32;
+        // the next step's tiles were requested steps ago: ask for both now, look at the answers when they are needed
+        const bool q_there = more && mbar_test(&q_full[qs1], ((n + 1) / kQS) & 1);
+        const bool do_there = more && mbar_test(&do_full[ds1], ((n + 1) / kDS) & 1);
         if (!kMods && more) {
           wait_or_report(s_free, n & 1, 210);
-          wait_or_report(&q_full[qs1], ((n + 1) / kQS) & 1, 203);
+          if (!q_there) wait_or_report(&q_full[qs1], ((n + 1) / kQS) & 1, 203);
           PROF_MARK(3);
           if (!ok) break;
           tc_fence_after_sync();
@@ -323,7 +326,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         tc_commit(&do_empty[ds]);
         PROF_MARK(2);
         if (kMods && more) {
-          wait_or_report(&q_full[qs1], ((n + 1) / kQS) & 1, 203);
+          if (!q_there) wait_or_report(&q_full[qs1], ((n + 1) / kQS) & 1, 203);
           PROF_MARK(3);
           if (!ok) break;
           tc_fence_after_sync();
@@ -339,7 +342,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         tc_commit(&q_empty[qs]);
         PROF_MARK(2);
         if (more) {
-          wait_or_report(&do_full[ds1], ((n + 1) / kDS) & 1, 203);
+          if (!do_there) wait_or_report(&do_full[ds1], ((n + 1) / kDS) & 1, 203);
           PROF_MARK(3);
           if (!ok) break;
           tc_fence_after_sync();

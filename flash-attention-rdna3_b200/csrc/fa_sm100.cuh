@@ -61,6 +61,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// The same question without any waiting: for barriers that are usually long complete (operand tiles requested steps
+// ahead), asked early and side by side so that the answers' latencies (about 54 clocks each) overlap instead of adding up.
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // Poll limit for every barrier wait. try_wait itself blocks for a short hardware-defined time, so
 // this is on the order of a second before a wait is declared lost.
 constexpr uint32_t kWaitPollLimit = 1u << 22;
