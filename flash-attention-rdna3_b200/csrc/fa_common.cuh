@@ -334,6 +334,9 @@ int launch_decode_paged(const fa_paged_params& p, cudaStream_t stream);    // fa
 int launch_tiny(const fa_tiny_params& p, cudaStream_t stream);             // fa_tiny.cu
 bool decode_tc_supported(const fa_decode_params& p);                       // fa_decode_sm100.cu
 int launch_decode_tc(const fa_decode_params& p, cudaStream_t stream);
+// `words` zeroed ticket words of the library's fixed array for launches that use this partial buffer, or nullptr (array
+// used up, or first use on this device while the stream is being captured); every launch leaves its words at zero
+unsigned int* decode_ticket_words(const void* partial_buffer, int words, cudaStream_t stream);
 bool paged_tc_supported(const fa_paged_params& p);
 int launch_paged_tc(const fa_paged_params& p, cudaStream_t stream);
 void set_decode_fault_injection(uint32_t poll_limit, int skip_tile);

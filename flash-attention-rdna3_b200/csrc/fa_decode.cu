@@ -23,6 +23,7 @@ struct DecodeArgs {
   int group;
   int rows_total;      // group * seqlen_q
   int keys_per_split;
+  unsigned int* tickets;  // one word per (batch, kv head, row block): the merge runs inside the kernel; or nullptr
 };
 
 template <typename T>
@@ -258,6 +259,38 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_splitk_kernel(const 
   }
   merge_workers_and_store<D, R>(sm, WORKERS, rows_here, tid, kDecodeThreads, opart_rows, lse_rows, out_rows,
                                 p.dtype, p.o_strides[3]);
+
+  // Merge inside the kernel: every CTA of these rows takes a ticket behind its partials (atomicInc wraps the word
+  // back to zero), and the one that draws the last ticket merges all splits (the rule of combine_kernel) and writes
+  // the output rows. Nobody waits for anybody; it saves the launch of the merge kernel, which for a short decode is a
+  // sixth of the call.
+  if (!direct && a.tickets != nullptr) {
+    __shared__ int last_s;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) last_s = atomicInc(a.tickets + (blockIdx.z * gridDim.y + blockIdx.y), gridDim.x - 1) == gridDim.x - 1;
+    __syncthreads();
+    if (last_s) {
+      __threadfence();
+      const int64_t stride_l = (int64_t)p.batch * p.heads_q * p.seqlen_q, stride_o = stride_l * D;
+      for (int idx = tid; idx < rows_here * D; idx += kDecodeThreads) {
+        const int r = idx / D, d = idx % D;
+        const float* l0 = lse_rows[r] - (int64_t)split * stride_l;
+        const float* o0 = opart_rows[r] - (int64_t)split * stride_o + d;
+        float M = kNegInf;
+        for (int s = 0; s < p.num_splits; ++s) M = fmaxf(M, __ldcg(l0 + s * stride_l));
+        const float Ms = (M == kNegInf) ? 0.f : M;
+        float num = 0.f, den = 0.f;
+        for (int s = 0; s < p.num_splits; ++s) {
+          const float ls = __ldcg(l0 + s * stride_l);
+          const float w = (ls == kNegInf) ? 0.f : expf(ls - Ms);
+          den += w;
+          if (w != 0.f) num += w * __ldcg(o0 + s * stride_o);
+        }
+        store_from_float(out_rows[r], (int64_t)d * p.o_strides[3], p.dtype, num / ((den == 0.f) ? 1.f : den));
+      }
+    }
+  }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -762,9 +795,17 @@ int launch_decode_splitk(const fa_decode_params& p, cudaStream_t stream) {
   a.rows_total = a.group * p.seqlen_q;
   const int blocks64 = (p.seqlen_k + 63) / 64;
   a.keys_per_split = ((blocks64 + p.num_splits - 1) / p.num_splits) * 64;
+  a.tickets = nullptr;
+  {
+    // rows per CTA as launch_split_rows chooses them; one ticket word per (batch, kv head, row block)
+    const int rows_per_cta = a.rows_total <= 2 ? a.rows_total : (p.head_dim >= 256 ? 2 : 4);
+    const int64_t words = (int64_t)p.batch * p.heads_kv * ((a.rows_total + rows_per_cta - 1) / rows_per_cta);
+    if (p.num_splits > 1 && p.num_splits <= 64 && words <= 1024)
+      a.tickets = decode_ticket_words(p.o_partial, (int)words, stream);
+  }
   int rc = (p.dtype == FA_F16) ? launch_split_dim<__half>(a, stream) : launch_split_dim<__nv_bfloat16>(a, stream);
   if (rc) return rc;
-  if (p.num_splits > 1) {
+  if (p.num_splits > 1 && a.tickets == nullptr) {
     const int rows = p.batch * p.heads_q * p.seqlen_q;
     rc = launch_combine_internal(rows, p.head_dim, p.num_splits, p.o_partial, (int64_t)rows * p.head_dim, p.head_dim,
                                  p.lse_partial, rows, 1, p.out, p.dtype, p.heads_q, p.seqlen_q, p.o_strides[0],

@@ -1175,6 +1175,12 @@ int launch_decode_tc(const fa_decode_params& p, cudaStream_t stream) {
                                  p.o_strides[3], nullptr, stream, true);
 }
 
+unsigned int* decode_ticket_words(const void* partial_buffer, int words, cudaStream_t stream) {
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  const bool capturing = cudaStreamIsCapturing(stream, &cap) == cudaSuccess && cap != cudaStreamCaptureStatusNone;
+  return ticket_region(partial_buffer, words, capturing);
+}
+
 bool paged_tc_supported(const fa_paged_params& p) {
   if (p.dtype != FA_F16 && p.dtype != FA_BF16) return false;
   if (p.head_dim != 64 && p.head_dim != 128) return false;
