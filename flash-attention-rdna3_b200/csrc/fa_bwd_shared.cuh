@@ -47,6 +47,7 @@ struct BwdArgs {
   // forward over P tiles: per (batch, head, query row of the padded 128-row tiles) the row maximum (log2 domain) the P
   // tiles are relative to and 1 / the row sum, which the product's epilogue applies. Null in the backward.
   float2* row_stats;
+  int compact;  // dK/dV of a packed batch on the compact grid (kv head, key tile number): see find_packed_tile
 };
 
 __device__ __forceinline__ void report_timeout(int* status, int code) {

@@ -157,8 +157,8 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   uint32_t* tmem_base_s = reinterpret_cast<uint32_t*>(smem + L::kOffTmemPtr);
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
-  const int ktile = blockIdx.y;
-  const int b = blockIdx.x / a.heads_kv, hk = blockIdx.x % a.heads_kv;
+  int ktile = blockIdx.y;
+  int b = blockIdx.x / a.heads_kv, hk = blockIdx.x % a.heads_kv;
   const int group = a.heads_q / a.heads_kv;
 
   int q_start = 0, k_start = 0, Sq = a.seqlen_q, Sk = a.seqlen_k;
@@ -169,6 +169,15 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   // The dQ kernel launched behind this one needs none of its results: let its CTAs take over SMs as they free up.
   grid_launch_dependents();
   PROF_STAMP(3);
+  if (a.compact) {
+    const PackedTile pt = find_packed_tile<false>(a.cu_k, a.batch, a.total_k, 128, a.num_tiles, blockIdx.y);
+    if (pt.seq < 0) return;
+    b = pt.seq;
+    ktile = pt.tile;
+    hk = blockIdx.x;
+    bounded_sequence(a.cu_q, b, a.total_q, &q_start, &Sq);
+    bounded_sequence(a.cu_k, b, a.total_k, &k_start, &Sk);
+  }
   const int k0 = ktile * 128;
   if (k0 >= Sk) return;
   const int tb = a.varlen ? 0 : b;
@@ -1197,7 +1206,11 @@ int launch_typed(const fa_attn_params& p, const BwdArgs& a0, int parts, cudaStre
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_dkdv);
     if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "backward smem opt-in failed: %s", cudaGetErrorString(e));
     a.num_tiles = (p.seqlen_k + 127) / 128;
-    kern<<<dim3(p.batch * p.heads_kv, a.num_tiles), kBwdThreads, smem_dkdv, stream>>>(mq, mk, mv, mdo, a);
+    dim3 grid(p.batch * p.heads_kv, a.num_tiles);
+    a.compact = (p.varlen && p.batch <= kPackedMaxSequences) ? 1 : 0;
+    if (a.compact) grid = dim3(p.heads_kv, (p.total_k + 127) / 128 + p.batch);
+    kern<<<grid, kBwdThreads, smem_dkdv, stream>>>(mq, mk, mv, mdo, a);
+    a.compact = 0;  // the dQ kernels walk their own item list
     e = cudaGetLastError();
     if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "dK/dV launch failed: %s", cudaGetErrorString(e));
   }

@@ -303,6 +303,62 @@ __device__ __forceinline__ void bounded_sequence(const int32_t* cu, int b, int t
   *len = max(e - s, 0);
 }
 
+// Packed batches on a compact grid. The host knows the total number of rows but not the lengths, so it launches
+// ceil(total / rows_per_tile) + sequences CTAs per head (at least the sum of the sequences' tile counts) and CTA `t`
+// finds its (sequence, tile) here: tiles are numbered by falling tile index (kLastFirst: query tiles, whose work under
+// a causal mask grows with the index) or by rising tile index (key tiles of the dK/dV kernel, whose work falls with
+// it), and among the sequences that have a given tile index by sequence number, so that the long tiles of the long
+// sequences start first. seq is -1 for the few CTAs past the last tile. Every thread of the CTA calls it (each warp works it out for itself: 32
+// sequences per ballot, at most kPackedMaxSequences); a grid of one CTA per (sequence, possible tile) instead costs
+// about 0.9 us of an SM for every tile a sequence does not have.
+constexpr int kPackedMaxSequences = 128;
+struct PackedTile {
+  int seq, tile;
+};
+template <bool kLastFirst>
+__device__ __forceinline__ PackedTile find_packed_tile(const int32_t* cu, int nseq, int total_rows, int rows_per_tile,
+                                                       int max_tiles, int t) {
+  const int lane = threadIdx.x & 31;
+  int tiles[kPackedMaxSequences / 32];
+#pragma unroll
+  for (int k = 0; k < kPackedMaxSequences / 32; ++k) {
+    const int b = k * 32 + lane;
+    tiles[k] = 0;
+    if (b < nseq) {
+      int start, len;
+      bounded_sequence(cu, b, total_rows, &start, &len);
+      tiles[k] = (len + rows_per_tile - 1) / rows_per_tile;
+    }
+  }
+  PackedTile found = {-1, 0};
+  int before = 0;  // tiles numbered before this index
+  for (int step = 0; step < max_tiles; ++step) {
+    const int idx = kLastFirst ? max_tiles - 1 - step : step;
+    unsigned has[kPackedMaxSequences / 32];
+    int n = 0;
+#pragma unroll
+    for (int k = 0; k < kPackedMaxSequences / 32; ++k) {
+      has[k] = __ballot_sync(0xffffffffu, tiles[k] > idx);
+      n += __popc(has[k]);
+    }
+    if (t < before + n) {
+      int r = t - before;  // the r-th of the sequences that have this tile
+#pragma unroll
+      for (int k = 0; k < kPackedMaxSequences / 32; ++k) {
+        const int c = __popc(has[k]);
+        if (found.seq < 0 && r < c) {
+          found.seq = k * 32 + (int)__fns(has[k], 0, r + 1);
+          found.tile = idx;
+        }
+        r -= c;
+      }
+      break;
+    }
+    before += n;
+  }
+  return found;
+}
+
 // ---------------------------------------------------------------------------------------------
 // Host-side error bookkeeping (definitions in fa_api.cu)
 // ---------------------------------------------------------------------------------------------

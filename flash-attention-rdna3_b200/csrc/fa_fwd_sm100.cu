@@ -48,6 +48,8 @@ struct FwdArgs {
   float dropout_p;
   uint64_t seed;
   int num_pairs;
+  int batch;    // sequences of a packed batch
+  int compact;  // packed batch on the compact grid (head, tile number): see find_packed_tile
   int* status;
 };
 
@@ -91,8 +93,15 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
   __shared__ uint32_t tmem_base_s;
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
-  const int pair = a.num_pairs - 1 - blockIdx.y;  // blocks are issued x-fastest: all the long (causal) tiles go first
-  const int b = blockIdx.x / a.heads_q, h = blockIdx.x % a.heads_q;
+  int pair = a.num_pairs - 1 - blockIdx.y;  // blocks are issued x-fastest: all the long (causal) tiles go first
+  int b = blockIdx.x / a.heads_q, h = blockIdx.x % a.heads_q;
+  if (a.compact) {
+    const PackedTile pt = find_packed_tile<true>(a.cu_q, a.batch, a.total_q, kQTiles * 128, a.num_pairs, blockIdx.y);
+    if (pt.seq < 0) return;  // uniform: nothing allocated yet
+    b = pt.seq;
+    pair = pt.tile;
+    h = blockIdx.x;
+  }
   const int hk = h / (a.heads_q / a.heads_kv);
 
   int q_start = 0, k_start = 0, Sq = a.seqlen_q, Sk = a.seqlen_k;
@@ -586,6 +595,7 @@ int launch_typed(const fa_attn_params& p, const FwdArgs& a, cudaStream_t stream)
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "forward smem opt-in failed: %s", cudaGetErrorString(e));
   dim3 grid(p.batch * p.heads_q, a.num_pairs);
+  if (a.compact) grid = dim3(p.heads_q, (p.total_q + kQTiles * 128 - 1) / (kQTiles * 128) + p.batch);
   kern<<<grid, kFwdThreads, smem, stream>>>(mq, mk, mv, a);
   e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "forward launch failed: %s", cudaGetErrorString(e));
@@ -645,6 +655,8 @@ int launch_fwd_tcgen05(const fa_attn_params& p, cudaStream_t stream) {
   a.seed = p.dropout_seed;
   a.num_pairs = p.head_dim > 128 ? (p.seqlen_q + 127) / 128 : (p.seqlen_q + 255) / 256;  // CTAs along the queries
   a.status = p.status;
+  a.batch = p.batch;
+  a.compact = (p.varlen && p.batch <= kPackedMaxSequences) ? 1 : 0;
   const bool mods = p.softcap > 0.f || p.bias != nullptr || p.alibi_slopes != nullptr || p.dropout_p > 0.f ||
                     !(p.softmax_scale > 0.f);
   const bool f16 = p.dtype == FA_F16;

@@ -90,3 +90,16 @@ def test_varlen_out_of_range_metadata_is_clamped():
     out = fa_b200.flash_attention_varlen(q, k, v, cu.cuda(), cu.cuda(), 300, 300, causal=True)
     ref, _ = oracle.varlen_ref(q.cpu(), k.cpu(), v.cpu(), cu, cu, causal=True)
     assert_close_o(out, ref, torch.float16)
+
+
+@pytest.mark.parametrize("count", [40, 128, 140])
+def test_varlen_many_sequences_with_empty_ones(count):
+    """Packed batches on the compact grid: CTAs find their (sequence, tile) from cu_seqlens, 32 sequences per ballot.
+    40 sequences take two ballots, 128 is the most the compact grid takes, 140 falls back to one CTA per (sequence,
+    possible tile); every third sequence is empty, one is much longer than the rest."""
+    import random
+
+    rng = random.Random(count)
+    lengths = [0 if i % 3 == 1 else rng.randint(1, 70) for i in range(count)]
+    lengths[count // 2] = 700
+    run_varlen(lengths, 4, 2, 64, path="tcgen05", causal=True, seed=count)
