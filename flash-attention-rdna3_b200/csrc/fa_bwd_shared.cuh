@@ -48,6 +48,7 @@ struct BwdArgs {
   // tiles are relative to and 1 / the row sum, which the product's epilogue applies. Null in the backward.
   float2* row_stats;
   int compact;  // dK/dV of a packed batch on the compact grid (kv head, key tile number): see find_packed_tile
+  int after_delta;  // dK/dV was launched as a programmatic dependent of the delta kernel: wait for it before reading delta
 };
 
 __device__ __forceinline__ void report_timeout(int* status, int code) {

@@ -402,6 +402,10 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       }
       return val;
     };
+    // Launched behind the delta kernel with the programmatic attribute, this CTA may be running before that kernel has
+    // finished: everything so far (and the loads of K, V, Q, dO and the first scores, which other warps are at) needs
+    // nothing of it; delta is first read here. (Without that kind of launch the wait returns at once.)
+    if (a.after_delta && !is_lse) grid_dependency_wait();
     float staged = n_total > 0 ? fetch_row_stat() : 0.f;
     const int64_t ds_head_stride = (int64_t)a.ds_kt * a.ds_qt * 32768;
     uint8_t* ds_head = a.ds_ws == nullptr
@@ -1209,9 +1213,27 @@ int launch_typed(const fa_attn_params& p, const BwdArgs& a0, int parts, cudaStre
     dim3 grid(p.batch * p.heads_kv, a.num_tiles);
     a.compact = (p.varlen && p.batch <= kPackedMaxSequences) ? 1 : 0;
     if (a.compact) grid = dim3(p.heads_kv, (p.total_k + 127) / 128 + p.batch);
-    kern<<<grid, kBwdThreads, smem_dkdv, stream>>>(mq, mk, mv, mdo, a);
+    // Behind the delta kernel of the same call the CTAs may start as that kernel's CTAs leave their SMs (they wait
+    // inside, where delta is first read) - unless the dQ kernel that follows is the recomputing one, which is itself
+    // let loose early on the grounds that delta was complete before this kernel started.
+    const bool early = (parts & FA_BWD_DELTA) && !((parts & FA_BWD_DQ) && a.ds_ws == nullptr);
+    a.after_delta = early ? 1 : 0;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kBwdThreads);
+    cfg.dynamicSmemBytes = smem_dkdv;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr = {};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    if (early) {
+      cfg.attrs = &attr;
+      cfg.numAttrs = 1;
+    }
+    e = cudaLaunchKernelEx(&cfg, kern, mq, mk, mv, mdo, a);
     a.compact = 0;  // the dQ kernels walk their own item list
-    e = cudaGetLastError();
+    a.after_delta = 0;
+    if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) return set_error(FA_ERR_LAUNCH, "dK/dV launch failed: %s", cudaGetErrorString(e));
   }
   if ((parts & FA_BWD_DQ) && a.ds_ws != nullptr) {

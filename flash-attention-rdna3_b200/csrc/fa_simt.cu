@@ -60,6 +60,9 @@ __global__ void __launch_bounds__(256) delta_vec_kernel(const fa_attn_params P) 
   constexpr int LPR = D / 8;         // lanes per row
   constexpr int RPW = 32 / LPR;      // rows per warp and pass
   constexpr int kPasses = 4;         // rows per lane group: all eight 16-byte loads are issued before the first use
+  // the dK/dV kernel launched behind this one waits inside for this grid to finish: its CTAs may set themselves up as
+  // SMs free
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const int i0 = (blockIdx.x * 8 + warp) * RPW * kPasses + lane / LPR;
   const int b = blockIdx.y / P.heads_q, h = blockIdx.y % P.heads_q;
