@@ -154,6 +154,44 @@ def test_backward_run_to_run_identical():
     assert all(torch.equal(x, y) for x, y in zip(a, b))
 
 
+def test_backward_one_call_equals_three_calls():
+    """fa_bwd with every part in one call starts dK/dV behind the delta kernel as its programmatic dependent (dK/dV CTAs
+    may run before delta has finished and wait where they first read it). The gradients must be bit-identical to
+    delta, dK/dV and dQ launched as three calls, each behind the completed one before it; stale delta values would
+    show here. Large enough for several waves of dK/dV CTAs; with and without the dS scratch."""
+    import ctypes as C
+
+    from fa_b200 import _lib, interface
+
+    lib = _lib.load()
+    q, k, v, dout = (seeded(i, 2, 16, 2048, 128) for i in (11, 12, 13, 14))
+    scale = 0.0884
+    out, lse = interface._forward(q, k, v, True, scale, (-1, -1), 0.0, None, None, 0.0, 0)
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    for scratch in (True, False):
+        results = []
+        for split in (False, True):
+            delta = torch.full_like(lse, float("nan"))  # a read before delta is written would poison the gradients
+            dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+            p = interface._attn_params(q, k, v, out, lse, True, scale, (-1, -1), 0.0, None, None, 0.0, 0)
+            interface._fill_backward(p, dout, delta, dq, dk, dv, False)
+            ws = interface._ds_workspace(p, q.device) if scratch else None
+            assert (ws is not None) == scratch
+            for parts in ((_lib.FA_BWD_DELTA, _lib.FA_BWD_DKDV, _lib.FA_BWD_DQ) if split else (0,)):
+                p.bwd_parts = parts
+                _lib.check(lib.fa_bwd(C.byref(p), stream))
+                if split:
+                    torch.cuda.synchronize()
+            torch.cuda.synchronize()
+            results.append((dq, dk, dv))
+            del ws
+        for one, three, name in zip(results[0], results[1], ("dq", "dk", "dv")):
+            assert not torch.isnan(one).any(), name
+            assert torch.equal(one, three), (name, scratch)
+    import fa_b200
+    fa_b200.check_status()
+
+
 # ------------------------------------------------------------------------------------------------ output canaries
 # compute-sanitizer is not available where these tests run, so stray writes are looked for the plain way: every
 # output lives in the middle of a larger buffer that starts out as NaN. After the call the guard zones on both sides
