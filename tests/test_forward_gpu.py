@@ -209,3 +209,32 @@ def test_forward_very_wide_in_batch_pieces_matches_one_launch(monkeypatch):
     assert interface._wide_batch_pieces(q, k, 1, 256) == [(0, 1), (1, 2), (2, 3)]
     pieces = interface._forward(q, k, v, True, scale, (-1, -1), 0.0, None, None, 0.0, 0)
     assert torch.equal(whole[0], pieces[0]) and torch.equal(whole[1], pieces[1])
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("head_dim", [64, 128, 256])
+@pytest.mark.parametrize("pattern", ["rising", "sawtooth"])
+def test_forward_running_maximum_keeps_growing(causal, head_dim, pattern):
+    """Scores that rise along the keys, so that the running maximum of every row grows by more than the rescale
+    threshold in (almost) every key tile (`rising`), or in every other one (`sawtooth`): the softmax path that
+    exponentiates against the old maximum and redoes the tile when the maximum grew is taken tile after tile, next to
+    tiles where it is not. Forward and, through the LSE it hands on, the backward must still match the oracle."""
+    from fa_b200 import interface
+
+    S, H = 1024, 2
+    g = torch.Generator().manual_seed(head_dim + (1 if causal else 0))
+    u = torch.ones(head_dim) / math.sqrt(head_dim)
+    steps = torch.arange(S, dtype=torch.float32)
+    if pattern == "sawtooth":
+        steps = torch.where((steps // 128) % 2 == 0, steps, steps - 128.0)
+    q = (u * 1.5 + 0.05 * torch.randn(1, H, S, head_dim, generator=g)).to(torch.float16).cuda()
+    k = (u * steps[None, None, :, None] * 1.0 + 0.05 * torch.randn(1, H, S, head_dim, generator=g))
+    k = k.to(torch.float16).cuda()
+    v = torch.randn(1, H, S, head_dim, generator=g).to(torch.float16).cuda()
+    scale = 1.0 / math.sqrt(head_dim)
+    with interface.force_kernel_path("tcgen05"):
+        out, lse = interface._forward(q, k, v, causal, scale, (-1, -1), 0.0, None, None, 0.0, 0)
+    torch.cuda.synchronize()
+    ref_o, ref_l = attention_ref(q.cpu(), k.cpu(), v.cpu(), causal=causal, softmax_scale=scale)
+    assert_close_o(out, ref_o, torch.float16)
+    assert_close_o(lse, ref_l, torch.float16, "lse")
